@@ -1,0 +1,248 @@
+/*
+ * mer_b200.h -- C ABI of the B200 (sm_100a) routed quantized SwiGLU expert-FFN backend.
+ *
+ * This is the boundary a Micro-Expert-Router host binds (Rust `extern "C"`, ctypes, cgo ...):
+ * plain pointers and sizes, status codes, no exceptions, no framework types.  Every entry
+ * point cites the reference interface it stands in for (paths relative to
+ * rust-engine/src/ of the reference).
+ *
+ * Conventions
+ *  - Every function returns a mer_status (0 = ok) unless stated otherwise; on failure
+ *    mer_last_error() describes the typed error {layer, expert_id, kind, detail}, the
+ *    C form of GpuExpertDispatchError (backend/mod.rs:423-428).
+ *  - The caller owns every buffer it passes, for the duration of the call only.
+ *  - "host" entry points take host pointers, copy through pinned staging buffers and
+ *    return after the result is in the caller's buffer (the reference's boundary is
+ *    synchronous: backend/mod.rs:2726-2790).  "_device" entry points take device
+ *    pointers and enqueue on a caller-supplied stream without synchronising.
+ *  - A backend may be used from several host threads; calls on one backend serialise.
+ *  - There is no CPU fallback anywhere behind this ABI (RoutedExpertGpuFailurePolicy::
+ *    StrictFailClosed, engine.rs:996-1000): a call either runs on the GPU or fails.
+ *  - Expert weights are never passed per call.  They are admitted once
+ *    (mer_expert_admit) into an HBM slot keyed by (expert_id, generation), exactly the
+ *    residency contract of GpuBackend::routed_expert_matmul (backend/mod.rs:3856-4018).
+ *  - Expert ids are global: layer * experts_per_layer + local (model.rs:2717-2725).
+ */
+#ifndef MER_B200_H
+#define MER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MER_ABI_VERSION 1
+
+/* WeightDtype subset on this path (inference.rs:725-747, kernels/mod.rs:74-75). */
+#define MER_DTYPE_Q4_0 0 /* 18-byte blocks: f16 d + 16 nibble bytes, value = d * (q - 8) */
+#define MER_DTYPE_Q8_0 1 /* 34-byte blocks: f16 d + 32 int8,         value = d * q       */
+
+/* Status / error kinds.  1..9 are GpuExpertDispatchErrorKind (backend/mod.rs:349-361) in
+ * declaration order; the rest extend it for a C boundary. */
+typedef enum mer_status {
+  MER_OK = 0,
+  MER_ERR_RESIDENCY_MISS = 1,
+  MER_ERR_PHYSICAL_CAPACITY = 2,
+  MER_ERR_UPLOAD = 3,
+  MER_ERR_VALIDATION_DISPATCH = 4,
+  MER_ERR_SUBMISSION = 5,
+  MER_ERR_READBACK_CHANNEL = 6,
+  MER_ERR_READBACK_MAP = 7,
+  MER_ERR_DEVICE_LOST = 8,
+  MER_ERR_RUNTIME_INVARIANT = 9,
+  MER_ERR_INELIGIBLE = 10,       /* GpuExpertBatchDispatchOutcome::Ineligible (backend/mod.rs:454-458) */
+  MER_ERR_TIMEOUT = 11,          /* a bounded device-side wait gave up */
+  MER_ERR_INVALID_ARGUMENT = 12, /* NULL pointer, zero size, unknown layer ... */
+  MER_ERR_NUMERICAL = 13         /* non-finite routing scores latched by the device status word */
+} mer_status;
+
+/* Device status word bits (same meaning as the reference's gpu_native status bits,
+ * backend/gpu_native.rs:25-41): latched by kernels instead of trapping. */
+#define MER_DEVSTAT_RESIDENCY_MISS 0x1u   /* a routed expert had no current HBM slot */
+#define MER_DEVSTAT_NONFINITE_ROUTER 0x2u /* softmax row was non-finite and fell back to uniform */
+#define MER_DEVSTAT_TIMEOUT 0x4u          /* bounded wait expired */
+#define MER_DEVSTAT_SHORT_SELECTION 0x8u  /* fewer than top_k finite scores */
+
+#define MER_EXPERT_NONE 0xFFFFFFFFu /* id written for an unfilled top-k slot / "no shared expert" */
+
+/* Scoring function of the router (ScoringFunc, gating.rs:94-97). */
+#define MER_SCORE_SOFTMAX 0
+#define MER_SCORE_SIGMOID 1
+
+/* mer_expert_admit flags. */
+#define MER_ADMIT_ANCHOR 0x1u /* Anchor Core entry: never evicted (expert_cache.rs:798-828) */
+#define MER_ADMIT_ASYNC 0x2u  /* return once the side-stream copy is enqueued */
+
+typedef struct mer_backend mer_backend;
+
+/* ModelShape + EngineOptions subset (engine.rs:958-965, 1008-1109) + [gpu_cache] sizing. */
+typedef struct mer_backend_cfg {
+  int32_t device;               /* CUDA ordinal */
+  int32_t dtype;                /* MER_DTYPE_* */
+  uint64_t d_model;
+  uint64_t d_ff;
+  uint64_t vram_capacity_bytes; /* byte budget of the HBM expert slot arena */
+  uint32_t max_experts;         /* size of the global expert id space */
+  uint32_t max_tokens;          /* largest token batch of one layer call */
+  uint32_t max_top_k;           /* largest top_k (+1 if a shared expert is used) */
+  float swiglu_limit;           /* GPT-OSS gate clamp; <= 0 or non-finite = off (inference.rs:86-112) */
+  uint32_t flags;               /* reserved, 0 */
+  uint32_t reserved;
+} mer_backend_cfg;
+
+/* LinearGate (gating.rs:118-143). */
+typedef struct mer_router_cfg {
+  uint32_t num_experts;
+  uint32_t top_k;
+  int32_t scoring_func;         /* MER_SCORE_* */
+  int32_t normalise_topk;
+  uint32_t n_group;             /* 0/1 = no grouping */
+  uint32_t topk_group;
+  float routed_scaling_factor;
+  uint32_t shared_expert_id;    /* global id of an always-on expert added with weight 1, or MER_EXPERT_NONE
+                                   (SharedExpert, transformer.rs:2094-2238) */
+  const float *correction_bias; /* host [num_experts] or NULL; selection only (gating.rs:406-416) */
+  const float *logit_bias;      /* host [num_experts] or NULL; harness extension: added to the logits */
+} mer_router_cfg;
+
+/* GpuExpertDispatchError (backend/mod.rs:423-428). */
+typedef struct mer_error_info {
+  uint32_t layer;
+  uint32_t expert_id;
+  int32_t kind; /* mer_status */
+  uint32_t device_status;
+  char detail[256];
+} mer_error_info;
+
+/* RoutedExpertExecutionSnapshot (engine.rs:943-951) + GpuExpertIoSnapshot /
+ * GpuExpertMemorySnapshot ledgers (backend/mod.rs:466-547). */
+typedef struct mer_counters {
+  uint64_t selected_routed_experts;
+  uint64_t gpu_dispatch_attempts;
+  uint64_t gpu_dispatch_successes;
+  uint64_t gpu_dispatch_failures;
+  uint64_t batch_calls;
+  uint64_t kernel_launches;
+  uint64_t expert_uploads;
+  uint64_t expert_upload_bytes;
+  uint64_t hidden_upload_bytes;
+  uint64_t readback_bytes;
+  uint64_t evictions;
+  uint64_t resident_experts;
+  uint64_t resident_bytes;
+  uint64_t arena_bytes;
+  uint64_t slot_stride_bytes;
+  uint64_t slot_count;
+} mer_counters;
+
+int mer_abi_version(void);
+const char *mer_error_kind_name(int kind); /* GpuExpertDispatchErrorKind Display, backend/mod.rs:403-418 */
+/* expert_weight_bytes_for (inference.rs:1096-1114): bytes of one gate||up||down blob. */
+uint64_t mer_expert_bytes(int32_t dtype, uint64_t d_model, uint64_t d_ff);
+/* routed_expert_gpu_compatibility (backend/mod.rs:4691-4720), extended to Q8_0. 0 = eligible. */
+int mer_routed_expert_compatibility(int32_t dtype, uint64_t d_model, uint64_t d_ff);
+
+/* resolve_execution_context factory seam (backend/mod.rs:5514-5594): builds the backend
+ * one BackendBox arm would own. */
+int mer_backend_create(const mer_backend_cfg *cfg, mer_backend **out);
+void mer_backend_destroy(mer_backend *b);
+int mer_backend_synchronize(mer_backend *b);
+
+/* ---- residency: the VRAM tier (expert_cache.rs:734-1350 logical tier + physical registry
+ * backend/mod.rs:3856-4018; slot layout after backend/gpu_native.rs:68-75, 1607). ---- */
+
+/* demand_admit_lru + build_expert_entry_q4_0 (expert_cache.rs:1281-1340, backend/mod.rs:2612):
+ * copies the header-stripped blob (ExpertResident::data, expert_cache.rs:202) from host memory
+ * through pinned staging on the copy stream into an HBM slot.  Evicts least-recently-used
+ * non-anchor slots when the arena is full.  A generation older than the resident one is a
+ * stale requester (MER_ERR_RESIDENCY_MISS); the same generation is a no-op. */
+int mer_expert_admit(mer_backend *b, uint32_t expert_id, uint64_t generation, const void *host_blob,
+                     size_t bytes, uint32_t flags);
+/* Same, from a blob already in device memory (device-to-device copy on the copy stream). */
+int mer_expert_admit_device(mer_backend *b, uint32_t expert_id, uint64_t generation,
+                            const void *device_blob, size_t bytes, uint32_t flags);
+/* retire_key_if_present (backend/mod.rs:3893): frees the slot if (id, generation) is current. */
+int mer_expert_retire(mer_backend *b, uint32_t expert_id, uint64_t generation);
+/* contains_generation (expert_cache.rs:909): 1 if (id, generation) is resident, else 0. */
+int mer_expert_contains_generation(mer_backend *b, uint32_t expert_id, uint64_t generation);
+
+/* ---- router: LinearGate::new / with_routing (gating.rs:149-238). ---- */
+int mer_router_install(mer_backend *b, uint32_t layer, const float *host_weights /*[E x D]*/,
+                       const mer_router_cfg *cfg);
+/* LinearGate::route_with_scratch (gating.rs:395-476) for n_tokens rows of x (host).
+ * ids/weights are [n_tokens x top_k]; unfilled slots get MER_EXPERT_NONE / 0. Ids are local. */
+int mer_router_route(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens,
+                     uint32_t *ids, float *weights);
+
+/* ---- compute, host buffers ---- */
+
+/* BackendBox::routed_expert_matmul (backend/mod.rs:4421-4441): one token through one expert,
+ * f16 in / f16 out (TensorView, backend/mod.rs:327-339). x and out are d_model binary16 values. */
+int mer_routed_expert_matmul(mer_backend *b, uint32_t layer, uint32_t expert_id, const uint16_t *x,
+                             size_t d_model, size_t d_ff, uint16_t *out);
+/* BackendBox::routed_expert_matmul_batch_q4 (backend/mod.rs:4401-4418): one token through n
+ * experts in one call, outputs [n x d_model] f16 in slot order, duplicates allowed.  The
+ * reference accepts exactly 8 Q4_0 experts; here any n in 1..=max_top_k and both dtypes.
+ * Returns MER_ERR_INELIGIBLE (nothing ran; the caller keeps its scalar path) when n is out of
+ * range; a failure after dispatch started is never replayed (engine.rs:6624-6642). */
+int mer_routed_expert_matmul_batch(mer_backend *b, uint32_t layer, const uint32_t *expert_ids,
+                                   size_t n, const uint16_t *x, size_t d_model, size_t d_ff,
+                                   uint16_t *out);
+/* f32 form of the same dispatch (the parity target): n_tokens rows through one expert. */
+int mer_routed_expert_forward_f32(mer_backend *b, uint32_t layer, uint32_t expert_id,
+                                  const float *x, size_t n_tokens, float *out);
+/* Engine::moe_step_weighted_into (engine.rs:5174-5643, compute block): routing given, one
+ * token, out[d] = sum over slots in order of weights[s] * expert_s(x)[d], zero weights skipped. */
+int mer_moe_step_weighted_into(mer_backend *b, uint32_t layer, const float *x,
+                               const uint32_t *expert_ids, const float *weights, size_t n_slots,
+                               float *out);
+/* The whole path for n_tokens rows (host): router top-k -> permute -> gate/up + SiLU*mul ->
+ * down -> weighted combine (+ shared expert).  moe_pre + moe_step + moe_combine,
+ * transformer.rs:2493-2574, batched over tokens.  ids/weights (optional) receive the routing. */
+int mer_moe_layer_forward(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens,
+                          float *out, uint32_t *ids, float *weights);
+
+/* ---- compute, device buffers, asynchronous on `stream` (a cudaStream_t) ---- */
+int mer_moe_layer_forward_device(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens,
+                                 float *d_out, uint32_t *d_ids, float *d_weights, void *stream);
+
+/* dequantize_q4_0_to_f32 / dequantize_q8_0_to_f32 (inference.rs:852-868, 963-979) on the
+ * resident copy: projection 0 = gate, 1 = up, 2 = down; out is d_model*d_ff floats (host). */
+int mer_dequant_projection_f32(mer_backend *b, uint32_t expert_id, int projection, float *out);
+
+/* GpuBackend::qualification_q4_0_matvec (backend/mod.rs:3532-3700): raw block-stream matvec used
+ * by the parity qualification cases (q4_parity.rs:470-572).  out[r] = sum_c W[r,c] * input[c] with
+ * row r starting at block w_block_off + r * columns/32.  Owns ephemeral device buffers, touches
+ * neither residency nor the dispatch counters.  All pointers are host pointers. */
+int mer_qualification_matvec(mer_backend *b, int32_t dtype, const void *weights, size_t weights_len,
+                             const float *input, size_t rows, size_t columns, size_t w_block_off,
+                             float *out);
+
+/* ---- per-stage device timing: StageTimings (stage_timing.rs:6-29) with the reference's stage
+ * names, measured with CUDA events on the stream each layer call is enqueued on. ---- */
+typedef struct mer_stage_timings {
+  uint64_t samples;                    /* layer calls accumulated */
+  double router_gate_ms;               /* router logits + scoring + top-k + token->expert grouping */
+  double expert_gate_up_kernel_ms;     /* gate/up dequant-matvec + SiLU*mul (whole expert FFN when one kernel does both) */
+  double expert_down_kernel_ms;        /* down projection (0 when fused into the kernel above) */
+  double moe_weighted_combination_ms;  /* weighted top-k combine */
+  double expert_compute_ms;            /* gate/up + down */
+} mer_stage_timings;
+/* Turns event recording around each stage on (1) or off (0); turning it on clears the accumulators. */
+int mer_stage_timing_enable(mer_backend *b, int on);
+/* Waits for the recorded events and returns the accumulated per-stage times. */
+int mer_stage_timings_read(mer_backend *b, mer_stage_timings *out);
+
+/* ---- introspection ---- */
+int mer_last_error(mer_backend *b, mer_error_info *out);
+int mer_snapshot(mer_backend *b, mer_counters *out);
+/* Selects the kernel family for decode-sized batches: 0 = automatic, 1 = generic fp32 kernels
+ * (any shape), 2 = streaming tensor-core kernels (block-aligned shapes).  For qualification runs. */
+int mer_set_kernel_path(mer_backend *b, int path);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MER_B200_H */

@@ -1,0 +1,99 @@
+"""ctypes declarations for every symbol of include/mer_b200.h."""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libmer_b200.so")
+
+DTYPE_Q4_0, DTYPE_Q8_0 = 0, 1
+SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
+EXPERT_NONE = 0xFFFFFFFF
+ADMIT_ANCHOR, ADMIT_ASYNC = 1, 2
+
+
+class MerBackendCfg(C.Structure):
+    _fields_ = [("device", C.c_int32), ("dtype", C.c_int32), ("d_model", C.c_uint64), ("d_ff", C.c_uint64),
+                ("vram_capacity_bytes", C.c_uint64), ("max_experts", C.c_uint32), ("max_tokens", C.c_uint32),
+                ("max_top_k", C.c_uint32), ("swiglu_limit", C.c_float), ("flags", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class MerRouterCfg(C.Structure):
+    _fields_ = [("num_experts", C.c_uint32), ("top_k", C.c_uint32), ("scoring_func", C.c_int32),
+                ("normalise_topk", C.c_int32), ("n_group", C.c_uint32), ("topk_group", C.c_uint32),
+                ("routed_scaling_factor", C.c_float), ("shared_expert_id", C.c_uint32),
+                ("correction_bias", C.c_void_p), ("logit_bias", C.c_void_p)]
+
+
+class MerErrorInfo(C.Structure):
+    _fields_ = [("layer", C.c_uint32), ("expert_id", C.c_uint32), ("kind", C.c_int32), ("device_status", C.c_uint32),
+                ("detail", C.c_char * 256)]
+
+
+class MerCounters(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in (
+        "selected_routed_experts", "gpu_dispatch_attempts", "gpu_dispatch_successes", "gpu_dispatch_failures",
+        "batch_calls", "kernel_launches", "expert_uploads", "expert_upload_bytes", "hidden_upload_bytes",
+        "readback_bytes", "evictions", "resident_experts", "resident_bytes", "arena_bytes", "slot_stride_bytes",
+        "slot_count")]
+
+    def as_dict(self):
+        return {n: int(getattr(self, n)) for n, _ in self._fields_}
+
+
+class MerStageTimings(C.Structure):
+    _fields_ = [("samples", C.c_uint64), ("router_gate_ms", C.c_double), ("expert_gate_up_kernel_ms", C.c_double),
+                ("expert_down_kernel_ms", C.c_double), ("moe_weighted_combination_ms", C.c_double),
+                ("expert_compute_ms", C.c_double)]
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n, _ in self._fields_}
+
+
+_vp, _sz, _u32, _u64, _i32 = C.c_void_p, C.c_size_t, C.c_uint32, C.c_uint64, C.c_int
+
+# name -> (restype, argtypes); the list every header declaration must appear in
+ABI_SYMBOLS = {
+    "mer_abi_version": (C.c_int, []),
+    "mer_error_kind_name": (C.c_char_p, [_i32]),
+    "mer_expert_bytes": (_u64, [C.c_int32, _u64, _u64]),
+    "mer_routed_expert_compatibility": (C.c_int, [C.c_int32, _u64, _u64]),
+    "mer_backend_create": (C.c_int, [C.POINTER(MerBackendCfg), C.POINTER(_vp)]),
+    "mer_backend_destroy": (None, [_vp]),
+    "mer_backend_synchronize": (C.c_int, [_vp]),
+    "mer_expert_admit": (C.c_int, [_vp, _u32, _u64, _vp, _sz, _u32]),
+    "mer_expert_admit_device": (C.c_int, [_vp, _u32, _u64, _vp, _sz, _u32]),
+    "mer_expert_retire": (C.c_int, [_vp, _u32, _u64]),
+    "mer_expert_contains_generation": (C.c_int, [_vp, _u32, _u64]),
+    "mer_router_install": (C.c_int, [_vp, _u32, _vp, C.POINTER(MerRouterCfg)]),
+    "mer_router_route": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _vp]),
+    "mer_routed_expert_matmul": (C.c_int, [_vp, _u32, _u32, _vp, _sz, _sz, _vp]),
+    "mer_routed_expert_matmul_batch": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _sz, _sz, _vp]),
+    "mer_routed_expert_forward_f32": (C.c_int, [_vp, _u32, _u32, _vp, _sz, _vp]),
+    "mer_moe_step_weighted_into": (C.c_int, [_vp, _u32, _vp, _vp, _vp, _sz, _vp]),
+    "mer_moe_layer_forward": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _vp, _vp]),
+    "mer_moe_layer_forward_device": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _vp, _vp, _vp]),
+    "mer_dequant_projection_f32": (C.c_int, [_vp, _u32, _i32, _vp]),
+    "mer_qualification_matvec": (C.c_int, [_vp, C.c_int32, _vp, _sz, _vp, _sz, _sz, _sz, _vp]),
+    "mer_stage_timing_enable": (C.c_int, [_vp, _i32]),
+    "mer_stage_timings_read": (C.c_int, [_vp, C.POINTER(MerStageTimings)]),
+    "mer_last_error": (C.c_int, [_vp, C.POINTER(MerErrorInfo)]),
+    "mer_snapshot": (C.c_int, [_vp, C.POINTER(MerCounters)]),
+    "mer_set_kernel_path": (C.c_int, [_vp, _i32]),
+}
+
+_lib = None
+
+
+def load_library():
+    """Loads libmer_b200.so; raises (no fallback) when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python __graft_entry__.py build` "
+                               "(there is no CPU fallback for this path)")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in ABI_SYMBOLS.items():
+            fn = getattr(lib, name)  # AttributeError if the library does not export it
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib

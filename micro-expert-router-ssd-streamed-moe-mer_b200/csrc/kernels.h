@@ -1,0 +1,63 @@
+// Internal interface between the C-ABI layer (mer_abi.cu) and the kernel files.
+// Not part of the public boundary; see include/mer_b200.h for that.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MER_BLOCK_ELEMS 32
+#define MER_Q4_BLOCK_BYTES 18
+#define MER_Q8_BLOCK_BYTES 34
+#define MER_NONE 0xFFFFFFFFu
+
+// Router parameters resident on the device (one per installed layer).
+struct RouterDev {
+  const float *w;                // [E x D]
+  const float *correction_bias;  // [E] or null
+  const float *logit_bias;       // [E] or null
+  uint32_t num_experts, top_k;
+  int scoring, normalise;
+  uint32_t n_group, topk_group;
+  float scaling;
+  uint32_t shared_expert_id;  // global id or MER_NONE
+  uint32_t id_base;           // layer * num_experts
+};
+
+// One MoE dispatch: P = n_tokens * slots pairs (token, slot); pair p belongs to token p / slots.
+// Pairs are grouped by expert: group g covers perm[offsets[g] .. offsets[g+1]) and runs expert
+// group_expert[g].
+struct MoeDispatch {
+  const uint8_t *const *expert_ptr;  // global id -> payload in the HBM slot arena, null = not resident
+  uint32_t max_experts;
+  int dtype;
+  uint32_t D, F;
+  uint32_t n_tokens, slots, n_groups;
+  const float *x;           // [n_tokens x D]
+  uint32_t *pair_expert;    // [P] global id or MER_NONE
+  float *pair_weight;       // [P]
+  uint32_t *group_expert;   // [n_groups]
+  uint32_t *offsets;        // [n_groups + 1]
+  uint32_t *perm;           // [P]
+  float *h;                 // [P x F]   silu(gate) * up
+  float *y;                 // [P x D]   per-pair expert outputs
+  float *out;               // [n_tokens x D]
+  uint32_t *status;         // device status word (MER_DEVSTAT_* bits)
+  uint32_t *counters;       // scratch counters: [0..n_tokens) per-token arrivals, [max_tokens] global arrivals
+  float *logits;            // [n_tokens x E] scratch
+  float swiglu_limit;       // <= 0 = off
+};
+
+// kernels_generic.cu
+cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max_tokens, cudaStream_t s, int *launches);
+cudaError_t launch_groups_from_pairs(const MoeDispatch &d, cudaStream_t s, int *launches);
+cudaError_t launch_ffn_generic(const MoeDispatch &d, cudaStream_t s, int *launches, cudaEvent_t ev_mid);
+cudaError_t launch_combine(const MoeDispatch &d, cudaStream_t s, int *launches);
+cudaError_t launch_dequant(int dtype, const uint8_t *src, float *dst, size_t n_weights, cudaStream_t s);
+cudaError_t launch_raw_matvec(int dtype, const uint8_t *w, const float *x, float *y, size_t rows, size_t cols, cudaStream_t s);
+cudaError_t launch_f16_to_f32(const uint16_t *src, float *dst, size_t n, cudaStream_t s);
+cudaError_t launch_f32_to_f16(const float *src, uint16_t *dst, size_t n, cudaStream_t s);
+
+// kernels_stream.cu: streaming tensor-core expert FFN for block-aligned shapes.
+bool stream_ffn_supported(int dtype, uint32_t D, uint32_t F);
+size_t stream_ffn_scratch_bytes(uint32_t max_pairs, uint32_t D, uint32_t F);
+cudaError_t launch_ffn_stream(const MoeDispatch &d, void *scratch, int sm_count, cudaStream_t s, int *launches, cudaEvent_t ev_mid);

@@ -1,0 +1,571 @@
+// Router, token->expert grouping, generic (any-shape) expert FFN, combine, dequant dump.
+//
+// The generic FFN kernels are the slow, shape-agnostic path: one warp per output row, one
+// weight per lane per step, fp32 FMA.  They handle rows that straddle blocks (d_model or
+// d_ff not a multiple of 32, e.g. the reference's 37x45 test shape) and are the on-device
+// cross-check for the streaming kernels.
+#include "kernels.h"
+
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+#include "../../include/mer_b200.h"
+
+namespace {
+
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t v) { return __half2float(__ushort_as_half(v)); }
+
+// One dequantised weight of a flat block stream: d * (q - 8) (Q4_0) or d * q (Q8_0); the
+// product is exact in fp32 (11-bit significand times a <= 8-bit integer).
+template <int DT>
+__device__ __forceinline__ float decode_weight(const uint8_t *__restrict__ base, size_t flat) {
+  size_t blk = flat >> 5;
+  uint32_t j = (uint32_t)flat & 31u;
+  if (DT == MER_DTYPE_Q8_0) {
+    const uint8_t *b = base + blk * MER_Q8_BLOCK_BYTES;
+    float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(b));
+    return __fmul_rn(d, (float)(int8_t)b[2 + j]);
+  } else {
+    const uint8_t *b = base + blk * MER_Q4_BLOCK_BYTES;
+    float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(b));
+    uint32_t byte = b[2 + (j & 15u)];
+    int q = (int)(j < 16u ? (byte & 15u) : (byte >> 4)) - 8;
+    return __fmul_rn(d, (float)q);
+  }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float clamp_gate(float g, float limit) {
+  if (limit > 0.0f && isfinite(limit) && g == g) g = fminf(fmaxf(g, -limit), limit);  // NaN stays NaN
+  return g;
+}
+
+// Order of f32::total_cmp as a signed integer key (gating.rs:283-294 compares with total_cmp).
+__device__ __forceinline__ int total_key(float f) {
+  int b = __float_as_int(f);
+  return b ^ (int)(((unsigned)(b >> 31)) >> 1);
+}
+__device__ __forceinline__ bool better(int ka, uint32_t ia, int kb, uint32_t ib) {
+  return ka > kb || (ka == kb && ia < ib);
+}
+
+// ---------------------------------------------------------------------------------------
+// Router: logits = W x (one warp per expert row), then the last CTA of each token scores,
+// applies the group filter and picks top-k (LinearGate::route_with_scratch, gating.rs:395-476);
+// the last CTA overall groups the (token, slot) pairs by expert.
+// ---------------------------------------------------------------------------------------
+constexpr int ROUTER_THREADS = 256;
+constexpr int ROUTER_ROWS = ROUTER_THREADS / 32;
+constexpr uint32_t SMALL_P = 4096;  // stable grouping below this many pairs
+
+__device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uint32_t *s_u32) {
+  // Runs in one CTA after every token has been routed.
+  const uint32_t P = d.n_tokens * d.slots;
+  const uint32_t G = d.n_groups;
+  const uint32_t tid = threadIdx.x, nt = blockDim.x;
+  uint32_t *s_cnt = s_u32;          // [G]
+  uint32_t *s_off = s_u32 + G;      // [G + 1]
+  uint32_t *s_key = s_u32 + 2 * G + 1;  // [min(P, SMALL_P)]
+  for (uint32_t g = tid; g < G; g += nt) {
+    s_cnt[g] = 0;
+    d.group_expert[g] = (g < r.num_experts) ? r.id_base + g : r.shared_expert_id;
+  }
+  __syncthreads();
+  auto key_of = [&](uint32_t p) -> uint32_t {
+    uint32_t e = __ldcg(d.pair_expert + p);
+    if (e == MER_NONE) return MER_NONE;
+    if ((p % d.slots) >= r.top_k) return r.num_experts;  // shared-expert slot
+    return e - r.id_base;
+  };
+  if (P <= SMALL_P) {
+    for (uint32_t p = tid; p < P; p += nt) s_key[p] = key_of(p);
+    __syncthreads();
+    for (uint32_t g = tid; g < G; g += nt) {
+      uint32_t c = 0;
+      for (uint32_t p = 0; p < P; p++) c += (s_key[p] == g);
+      s_cnt[g] = c;
+    }
+  } else {
+    for (uint32_t p = tid; p < P; p += nt) {
+      uint32_t k = key_of(p);
+      if (k != MER_NONE) atomicAdd(&s_cnt[k], 1u);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t acc = 0;
+    for (uint32_t g = 0; g < G; g++) {
+      s_off[g] = acc;
+      acc += s_cnt[g];
+    }
+    s_off[G] = acc;
+  }
+  __syncthreads();
+  for (uint32_t g = tid; g <= G; g += nt) d.offsets[g] = s_off[g];
+  if (P <= SMALL_P) {
+    // stable: pairs of a group keep (token, slot) order
+    for (uint32_t g = tid; g < G; g += nt) {
+      uint32_t o = s_off[g];
+      if (s_cnt[g] == 0) continue;
+      for (uint32_t p = 0; p < P; p++)
+        if (s_key[p] == g) d.perm[o++] = p;
+    }
+  } else {
+    for (uint32_t g = tid; g < G; g += nt) s_cnt[g] = 0;
+    __syncthreads();
+    for (uint32_t p = tid; p < P; p += nt) {
+      uint32_t k = key_of(p);
+      if (k != MER_NONE) d.perm[s_off[k] + atomicAdd(&s_cnt[k], 1u)] = p;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispatch d, uint32_t max_tokens) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  const uint32_t E = r.num_experts, D = d.D;
+  const uint32_t token = blockIdx.y;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float *x = d.x + (size_t)token * D;
+  const uint32_t e = blockIdx.x * ROUTER_ROWS + warp;
+  if (e < E) {
+    const float *w = r.w + (size_t)e * D;
+    float acc = 0.0f;
+    if ((D & 3u) == 0) {
+      const float4 *w4 = reinterpret_cast<const float4 *>(w);
+      const float4 *x4 = reinterpret_cast<const float4 *>(x);
+      for (uint32_t i = lane; i < D / 4; i += 32) {
+        float4 a = __ldg(w4 + i), b = __ldg(x4 + i);
+        acc = fmaf(a.x, b.x, acc);
+        acc = fmaf(a.y, b.y, acc);
+        acc = fmaf(a.z, b.z, acc);
+        acc = fmaf(a.w, b.w, acc);
+      }
+    } else {
+      for (uint32_t i = lane; i < D; i += 32) acc = fmaf(__ldg(w + i), __ldg(x + i), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) d.logits[(size_t)token * E + e] = acc;
+  }
+  __shared__ uint32_t s_flag;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    uint32_t prev = atomicAdd(&d.counters[token], 1u);
+    s_flag = (prev == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!s_flag) return;
+  __threadfence();
+
+  // ---- this CTA saw the last logit of the token: score, filter, select ----
+  float *s_score = reinterpret_cast<float *>(smem_raw);  // [E] scores (become mixing weights)
+  float *s_sel = s_score + E;                             // [E] selection scores
+  uint8_t *s_ok = reinterpret_cast<uint8_t *>(s_sel + E);  // [E] allowed & not yet taken
+  __shared__ float s_red[2];
+  __shared__ uint32_t s_groups[64];
+  __shared__ float s_gscore[64];
+  const uint32_t tid = threadIdx.x, nt = blockDim.x;
+  for (uint32_t i = tid; i < E; i += nt) {
+    float v = __ldcg(d.logits + (size_t)token * E + i);
+    if (r.logit_bias) v += r.logit_bias[i];
+    s_score[i] = v;
+  }
+  if (tid == 0) d.counters[token] = 0;  // re-arm for the next launch
+  __syncthreads();
+  if (r.scoring == MER_SCORE_SOFTMAX) {
+    // softmax_inplace (transformer.rs:2747-2819)
+    if (warp == 0) {
+      float mx = -CUDART_INF_F;
+      int nan = 0;
+      for (uint32_t i = lane; i < E; i += 32) {
+        float v = s_score[i];
+        if (v != v)
+          nan = 1;
+        else if (v > mx)
+          mx = v;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        nan |= __shfl_xor_sync(0xffffffffu, nan, o);
+      }
+      if (lane == 0) {
+        s_red[0] = mx;
+        s_red[1] = (nan || !isfinite(mx)) ? 1.0f : 0.0f;
+      }
+    }
+    __syncthreads();
+    if (s_red[1] != 0.0f) {
+      for (uint32_t i = tid; i < E; i += nt) s_score[i] = 1.0f / (float)E;
+      if (tid == 0) atomicOr(d.status, MER_DEVSTAT_NONFINITE_ROUTER);
+      __syncthreads();
+    } else {
+      float mx = s_red[0];
+      for (uint32_t i = tid; i < E; i += nt) s_score[i] = expf(s_score[i] - mx);
+      __syncthreads();
+      if (tid == 0) {  // the reference sums left to right; keep that order
+        float sum = 0.0f;
+        for (uint32_t i = 0; i < E; i++) sum += s_score[i];
+        s_red[0] = sum;
+      }
+      __syncthreads();
+      float sum = s_red[0];
+      if (sum > 0.0f)
+        for (uint32_t i = tid; i < E; i += nt) s_score[i] = s_score[i] / sum;
+      __syncthreads();
+    }
+  } else {
+    for (uint32_t i = tid; i < E; i += nt) s_score[i] = 1.0f / (1.0f + expf(-s_score[i]));
+    __syncthreads();
+  }
+  for (uint32_t i = tid; i < E; i += nt) {
+    s_sel[i] = r.correction_bias ? s_score[i] + r.correction_bias[i] : s_score[i];
+    s_ok[i] = 1;
+  }
+  __syncthreads();
+  // group_filter_shape + select_top_groups (gating.rs:335-376)
+  uint32_t ng = r.n_group < 1 ? 1 : r.n_group;
+  bool grouped = ng > 1 && r.topk_group > 0 && r.topk_group < ng && (E % ng) == 0 && ng <= 64;
+  if (grouped) {
+    uint32_t gs = E / ng;
+    if (tid < ng) {
+      float top1 = -CUDART_INF_F, top2 = -CUDART_INF_F;
+      for (uint32_t i = 0; i < gs; i++) {
+        float s = s_sel[tid * gs + i];
+        if (s > top1) {
+          top2 = top1;
+          top1 = s;
+        } else if (s > top2) {
+          top2 = s;
+        }
+      }
+      s_gscore[tid] = top1 + (isfinite(top2) ? top2 : 0.0f);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      uint64_t taken = 0;
+      for (uint32_t n = 0; n < r.topk_group; n++) {
+        int bk = 0;
+        uint32_t bi = MER_NONE;
+        for (uint32_t g = 0; g < ng; g++) {
+          if (taken >> g & 1) continue;
+          int k = total_key(s_gscore[g]);
+          if (bi == MER_NONE || better(k, g, bk, bi)) bk = k, bi = g;
+        }
+        taken |= 1ull << bi;
+        s_groups[n] = bi;
+      }
+    }
+    __syncthreads();
+    for (uint32_t i = tid; i < E; i += nt) {
+      bool ok = false;
+      for (uint32_t n = 0; n < r.topk_group; n++) ok |= (s_groups[n] == i / gs);
+      s_ok[i] = ok;
+    }
+    __syncthreads();
+  }
+  // top-k by (selection desc, id asc), non-finite skipped (gating.rs:315-333, 429-441)
+  if (warp == 0) {
+    const uint32_t S = d.slots, k = r.top_k;
+    uint32_t my_id = MER_NONE;  // lane i keeps the i-th pick
+    uint32_t n_sel = 0;
+    for (uint32_t n = 0; n < k; n++) {
+      int bk = 0;
+      uint32_t bi = MER_NONE;
+      for (uint32_t i = lane; i < E; i += 32) {
+        float s = s_sel[i];
+        if (!s_ok[i] || !isfinite(s)) continue;
+        int key = total_key(s);
+        if (bi == MER_NONE || key > bk) bk = key, bi = i;  // ascending scan keeps the lowest id on ties
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        int ok = __shfl_xor_sync(0xffffffffu, bk, o);
+        uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi != MER_NONE && (bi == MER_NONE || better(ok, oi, bk, bi))) bk = ok, bi = oi;
+      }
+      if (bi == MER_NONE) break;
+      if (lane == 0) s_ok[bi] = 0;
+      if (lane == (n & 31)) my_id = bi;
+      n_sel++;
+      __syncwarp();
+    }
+    // mixing weights = unbiased scores; renormalise; scale (gating.rs:443-474)
+    float w = (lane < n_sel && my_id != MER_NONE) ? s_score[my_id] : 0.0f;
+    if (r.normalise) {
+      float sum = 0.0f;
+      for (uint32_t i = 0; i < n_sel; i++) sum += __shfl_sync(0xffffffffu, w, i);  // slot order
+      if (isfinite(sum) && sum > 0.0f) w = w / sum;
+    }
+    if (r.scaling != 1.0f && isfinite(r.scaling)) w = w * r.scaling;
+    if (lane < k) {
+      bool have = lane < n_sel;
+      d.pair_expert[(size_t)token * S + lane] = have ? r.id_base + my_id : MER_NONE;
+      d.pair_weight[(size_t)token * S + lane] = have ? w : 0.0f;
+    }
+    if (lane == 0) {
+      if (n_sel < k) atomicOr(d.status, MER_DEVSTAT_SHORT_SELECTION);
+      if (S > k) {
+        d.pair_expert[(size_t)token * S + k] = r.shared_expert_id;
+        d.pair_weight[(size_t)token * S + k] = 1.0f;
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    uint32_t prev = atomicAdd(&d.counters[max_tokens], 1u);
+    s_flag = (prev == d.n_tokens - 1);
+    if (s_flag) d.counters[max_tokens] = 0;
+  }
+  __syncthreads();
+  if (!s_flag) return;
+  __threadfence();
+  build_groups_layer(r, d, reinterpret_cast<uint32_t *>(smem_raw));
+}
+
+// Routing supplied by the caller: mode 0 = every pair is its own group, mode 1 = one group.
+__global__ void k_groups_from_pairs(MoeDispatch d, int single_group) {
+  const uint32_t P = d.n_tokens * d.slots;
+  for (uint32_t p = threadIdx.x; p < P; p += blockDim.x) {
+    d.perm[p] = p;
+    if (!single_group) {
+      d.group_expert[p] = d.pair_expert[p];
+      d.offsets[p] = p;
+    }
+  }
+  if (threadIdx.x == 0) {
+    if (single_group) {
+      d.group_expert[0] = d.pair_expert[0];
+      d.offsets[0] = 0;
+      d.offsets[1] = P;
+    } else {
+      d.offsets[P] = P;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Generic expert FFN.
+// ---------------------------------------------------------------------------------------
+constexpr int GEN_TG = 4;  // tokens of a group handled per pass over a weight row
+
+__device__ __forceinline__ const uint8_t *group_weights(const MoeDispatch &d, uint32_t g) {
+  uint32_t eid = d.group_expert[g];
+  const uint8_t *base = (eid < d.max_experts) ? d.expert_ptr[eid] : nullptr;
+  if (!base && threadIdx.x == 0) atomicOr(d.status, MER_DEVSTAT_RESIDENCY_MISS);
+  return base;
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256) k_gate_up_generic(MoeDispatch d) {
+  const uint32_t g = blockIdx.y;
+  const uint32_t beg = d.offsets[g], end = d.offsets[g + 1];
+  if (beg == end) return;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t r = blockIdx.x * 8 + warp;
+  const uint8_t *base = group_weights(d, g);
+  if (r >= d.F) return;
+  if (!base) {  // fail closed: the pair contributes zeros and the host reports the miss
+    for (uint32_t t = beg + lane; t < end; t += 32) d.h[(size_t)d.perm[t] * d.F + r] = 0.0f;
+    return;
+  }
+  const size_t bb = DT == MER_DTYPE_Q8_0 ? MER_Q8_BLOCK_BYTES : MER_Q4_BLOCK_BYTES;
+  const size_t proj = ((size_t)d.D * d.F + 31) / 32 * bb;
+  const uint8_t *gate = base, *up = base + proj;
+  for (uint32_t t0 = beg; t0 < end; t0 += GEN_TG) {
+    uint32_t pair[GEN_TG];
+    const float *xs[GEN_TG];
+    float ag[GEN_TG], au[GEN_TG];
+#pragma unroll
+    for (int t = 0; t < GEN_TG; t++) {
+      pair[t] = (t0 + t < end) ? d.perm[t0 + t] : MER_NONE;
+      xs[t] = d.x + (size_t)(pair[t] == MER_NONE ? 0 : pair[t] / d.slots) * d.D;
+      ag[t] = au[t] = 0.0f;
+    }
+    for (uint32_t c = lane; c < d.D; c += 32) {
+      size_t flat = (size_t)r * d.D + c;
+      float wg = decode_weight<DT>(gate, flat), wu = decode_weight<DT>(up, flat);
+#pragma unroll
+      for (int t = 0; t < GEN_TG; t++) {
+        float xv = __ldg(xs[t] + c);
+        ag[t] = fmaf(wg, xv, ag[t]);
+        au[t] = fmaf(wu, xv, au[t]);
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < GEN_TG; t++) {
+      float gsum = warp_sum(ag[t]), usum = warp_sum(au[t]);
+      if (lane == 0 && pair[t] != MER_NONE)
+        d.h[(size_t)pair[t] * d.F + r] = silu_f(clamp_gate(gsum, d.swiglu_limit)) * usum;
+    }
+  }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256) k_down_generic(MoeDispatch d) {
+  const uint32_t g = blockIdx.y;
+  const uint32_t beg = d.offsets[g], end = d.offsets[g + 1];
+  if (beg == end) return;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t r = blockIdx.x * 8 + warp;
+  uint32_t eid = d.group_expert[g];
+  const uint8_t *base = (eid < d.max_experts) ? d.expert_ptr[eid] : nullptr;
+  if (r >= d.D) return;
+  if (!base) {
+    for (uint32_t t = beg + lane; t < end; t += 32) d.y[(size_t)d.perm[t] * d.D + r] = 0.0f;
+    return;
+  }
+  const size_t bb = DT == MER_DTYPE_Q8_0 ? MER_Q8_BLOCK_BYTES : MER_Q4_BLOCK_BYTES;
+  const size_t proj = ((size_t)d.D * d.F + 31) / 32 * bb;
+  const uint8_t *down = base + 2 * proj;
+  for (uint32_t t0 = beg; t0 < end; t0 += GEN_TG) {
+    uint32_t pair[GEN_TG];
+    const float *hs[GEN_TG];
+    float acc[GEN_TG];
+#pragma unroll
+    for (int t = 0; t < GEN_TG; t++) {
+      pair[t] = (t0 + t < end) ? d.perm[t0 + t] : MER_NONE;
+      hs[t] = d.h + (size_t)(pair[t] == MER_NONE ? d.perm[beg] : pair[t]) * d.F;
+      acc[t] = 0.0f;
+    }
+    for (uint32_t c = lane; c < d.F; c += 32) {
+      float w = decode_weight<DT>(down, (size_t)r * d.F + c);
+#pragma unroll
+      for (int t = 0; t < GEN_TG; t++) acc[t] = fmaf(w, hs[t][c], acc[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < GEN_TG; t++) {
+      float s = warp_sum(acc[t]);
+      if (lane == 0 && pair[t] != MER_NONE) d.y[(size_t)pair[t] * d.D + r] = s;
+    }
+  }
+}
+
+// out[token] = sum over slots, in slot order, of weight * y (combine_outputs_into,
+// inference.rs:4472-4491; zero weights and unfilled slots skipped as engine.rs:5575-5581).
+// Multiply and add round separately, as the reference's `*dst += weight * *v` does.
+__global__ void __launch_bounds__(256) k_combine(MoeDispatch d) {
+  const uint32_t token = blockIdx.y;
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= d.D) return;
+  float acc = 0.0f;
+  for (uint32_t s = 0; s < d.slots; s++) {
+    size_t p = (size_t)token * d.slots + s;
+    float w = d.pair_weight[p];
+    if (d.pair_expert[p] == MER_NONE || w == 0.0f) continue;
+    acc = __fadd_rn(acc, __fmul_rn(w, d.y[p * d.D + i]));
+  }
+  d.out[(size_t)token * d.D + i] = acc;
+}
+
+template <int DT>
+__global__ void k_dequant(const uint8_t *__restrict__ src, float *__restrict__ dst, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) dst[i] = decode_weight<DT>(src, i);
+}
+
+// Raw block-stream matvec for the qualification cases: one warp per row.
+template <int DT>
+__global__ void k_raw_matvec(const uint8_t *__restrict__ w, const float *__restrict__ x, float *__restrict__ y, size_t rows,
+                             size_t cols) {
+  size_t r = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  uint32_t lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  float acc = 0.0f;
+  for (size_t c = lane; c < cols; c += 32) acc = fmaf(decode_weight<DT>(w, r * cols + c), x[c], acc);
+  acc = warp_sum(acc);
+  if (lane == 0) y[r] = acc;
+}
+
+__global__ void k_f16_to_f32(const uint16_t *__restrict__ src, float *__restrict__ dst, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = f16_bits_to_f32(src[i]);
+}
+__global__ void k_f32_to_f16(const float *__restrict__ src, uint16_t *__restrict__ dst, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = __half_as_ushort(__float2half_rn(src[i]));
+}
+
+}  // namespace
+
+cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max_tokens, cudaStream_t s,
+                          int *launches) {
+  const uint32_t E = r.num_experts;
+  const uint32_t P = d.n_tokens * d.slots;
+  size_t smem_topk = (size_t)E * 9;
+  size_t smem_grp = (size_t)(2 * d.n_groups + 1 + (P <= SMALL_P ? P : 0)) * 4;
+  size_t smem = smem_topk > smem_grp ? smem_topk : smem_grp;
+  smem = (smem + 15) & ~(size_t)15;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k_router, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  dim3 grid((E + ROUTER_ROWS - 1) / ROUTER_ROWS, d.n_tokens);
+  k_router<<<grid, ROUTER_THREADS, smem, s>>>(r, d, max_tokens);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_groups_from_pairs(const MoeDispatch &d, cudaStream_t s, int *launches) {
+  k_groups_from_pairs<<<1, 256, 0, s>>>(d, d.n_groups == 1);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ffn_generic(const MoeDispatch &d, cudaStream_t s, int *launches, cudaEvent_t ev_mid) {
+  dim3 g1((d.F + 7) / 8, d.n_groups), g2((d.D + 7) / 8, d.n_groups);
+  if (d.dtype == MER_DTYPE_Q8_0) {
+    k_gate_up_generic<MER_DTYPE_Q8_0><<<g1, 256, 0, s>>>(d);
+    if (ev_mid) cudaEventRecord(ev_mid, s);
+    k_down_generic<MER_DTYPE_Q8_0><<<g2, 256, 0, s>>>(d);
+  } else {
+    k_gate_up_generic<MER_DTYPE_Q4_0><<<g1, 256, 0, s>>>(d);
+    if (ev_mid) cudaEventRecord(ev_mid, s);
+    k_down_generic<MER_DTYPE_Q4_0><<<g2, 256, 0, s>>>(d);
+  }
+  if (launches) (*launches) += 2;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine(const MoeDispatch &d, cudaStream_t s, int *launches) {
+  dim3 grid((d.D + 255) / 256, d.n_tokens);
+  k_combine<<<grid, 256, 0, s>>>(d);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dequant(int dtype, const uint8_t *src, float *dst, size_t n, cudaStream_t s) {
+  int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  if (blocks < 1) blocks = 1;
+  if (dtype == MER_DTYPE_Q8_0)
+    k_dequant<MER_DTYPE_Q8_0><<<blocks, 256, 0, s>>>(src, dst, n);
+  else
+    k_dequant<MER_DTYPE_Q4_0><<<blocks, 256, 0, s>>>(src, dst, n);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_raw_matvec(int dtype, const uint8_t *w, const float *x, float *y, size_t rows, size_t cols, cudaStream_t s) {
+  unsigned blocks = (unsigned)((rows + 7) / 8);
+  if (dtype == MER_DTYPE_Q8_0)
+    k_raw_matvec<MER_DTYPE_Q8_0><<<blocks, 256, 0, s>>>(w, x, y, rows, cols);
+  else
+    k_raw_matvec<MER_DTYPE_Q4_0><<<blocks, 256, 0, s>>>(w, x, y, rows, cols);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_f16_to_f32(const uint16_t *src, float *dst, size_t n, cudaStream_t s) {
+  k_f16_to_f32<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(src, dst, n);
+  return cudaGetLastError();
+}
+cudaError_t launch_f32_to_f16(const float *src, uint16_t *dst, size_t n, cudaStream_t s) {
+  k_f32_to_f16<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(src, dst, n);
+  return cudaGetLastError();
+}

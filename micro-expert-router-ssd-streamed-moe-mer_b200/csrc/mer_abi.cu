@@ -1,0 +1,963 @@
+// C-ABI layer: backend handle, HBM expert slot arena (VRAM tier), router table, dispatch.
+// Host code only; kernels live in kernels_*.cu.  See include/mer_b200.h for the contract and
+// the reference interfaces each entry point replaces.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/mer_b200.h"
+#include "kernels.h"
+
+#define MER_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+constexpr size_t SLOT_HEADER_BYTES = 256;  // {epoch, expert id, payload bytes}; payload stays 256-B aligned
+constexpr size_t SLOT_ALIGN = 4096;        // page-aligned slot stride (block_align of the reference's blobs)
+constexpr size_t STAGE_BYTES = 16u << 20;  // two pinned staging buffers for pageable host blobs
+constexpr uint32_t MAX_DIM = 1u << 20;
+
+struct SlotHeader {  // written at the start of every occupied slot
+  uint64_t epoch;
+  uint32_t expert_id;
+  uint32_t dtype;
+  uint64_t payload_bytes;
+};
+
+struct Slot {
+  bool used = false, anchor = false;
+  uint32_t expert_id = MER_NONE;
+  uint64_t generation = 0, last_use = 0;
+};
+
+struct RouterEntry {
+  RouterDev dev{};
+  float *d_w = nullptr, *d_cbias = nullptr, *d_lbias = nullptr;
+};
+
+}  // namespace
+
+struct mer_backend {
+  mer_backend_cfg cfg{};
+  int sm_count = 0;
+  size_t expert_bytes = 0;
+  cudaStream_t compute = nullptr, copy = nullptr;
+  cudaEvent_t ev_compute_done = nullptr, ev_copy_done = nullptr, ev_stage[2] = {nullptr, nullptr};
+  bool copy_pending = false;
+
+  // VRAM tier
+  uint8_t *arena = nullptr;
+  size_t slot_stride = 0, n_slots = 0;
+  std::vector<Slot> slots;
+  std::unordered_map<uint32_t, size_t> id2slot;
+  const uint8_t **d_expert_ptr = nullptr;  // device table: global id -> payload
+  const uint8_t **h_expert_ptr = nullptr;  // pinned mirror
+  uint8_t *h_stage[2] = {nullptr, nullptr};
+  SlotHeader *h_hdr = nullptr;  // pinned, one per slot
+  uint64_t tick = 0;
+
+  // workspace
+  uint32_t max_pairs = 0;
+  float *d_x = nullptr, *d_out = nullptr, *d_h = nullptr, *d_y = nullptr, *d_pair_weight = nullptr, *d_logits = nullptr;
+  uint32_t *d_pair_expert = nullptr, *d_group_expert = nullptr, *d_offsets = nullptr, *d_perm = nullptr;
+  uint32_t *d_status = nullptr, *d_counters = nullptr;
+  uint16_t *d_f16 = nullptr;
+  void *d_stream_scratch = nullptr;
+  uint32_t max_groups = 0, max_router_experts = 0;
+  uint32_t *h_u32 = nullptr;  // pinned [max_pairs + 1]: ids up/down, status
+  float *h_f32 = nullptr;     // pinned [max_pairs]
+  float *d_dequant = nullptr;
+
+  std::unordered_map<uint32_t, RouterEntry> routers;
+  int kernel_path = 0;
+  // stage timing: sets of 5 events {start, after router, mid FFN, after FFN, after combine}
+  bool timing_on = false;
+  std::vector<cudaEvent_t> timing_events;
+  size_t timing_used = 0;
+  mer_stage_timings timing_acc{};
+  std::mutex mu;
+  mer_error_info err{};
+  mer_counters ctr{};
+};
+
+namespace {
+
+int fail(mer_backend *b, int kind, uint32_t layer, uint32_t expert, const char *fmt, ...) {
+  if (b) {
+    b->err.layer = layer;
+    b->err.expert_id = expert;
+    b->err.kind = kind;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(b->err.detail, sizeof b->err.detail, fmt, ap);
+    va_end(ap);
+  }
+  return kind;
+}
+
+int cuda_fail(mer_backend *b, int kind, uint32_t layer, uint32_t expert, const char *what, cudaError_t e) {
+  if (e == cudaErrorDevicesUnavailable || e == cudaErrorNoDevice || e == cudaErrorECCUncorrectable ||
+      e == cudaErrorHardwareStackError || e == cudaErrorIllegalAddress || e == cudaErrorLaunchFailure)
+    kind = MER_ERR_DEVICE_LOST;
+  return fail(b, kind, layer, expert, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define CU(kind, what, call)                                          \
+  do {                                                                \
+    cudaError_t e__ = (call);                                         \
+    if (e__ != cudaSuccess) return cuda_fail(b, kind, layer, expert, what, e__); \
+  } while (0)
+
+size_t block_bytes(int dtype) { return dtype == MER_DTYPE_Q4_0 ? MER_Q4_BLOCK_BYTES : MER_Q8_BLOCK_BYTES; }
+
+MoeDispatch base_dispatch(mer_backend *b) {
+  MoeDispatch d{};
+  d.expert_ptr = b->d_expert_ptr;
+  d.max_experts = b->cfg.max_experts;
+  d.dtype = b->cfg.dtype;
+  d.D = (uint32_t)b->cfg.d_model;
+  d.F = (uint32_t)b->cfg.d_ff;
+  d.pair_expert = b->d_pair_expert;
+  d.pair_weight = b->d_pair_weight;
+  d.group_expert = b->d_group_expert;
+  d.offsets = b->d_offsets;
+  d.perm = b->d_perm;
+  d.h = b->d_h;
+  d.y = b->d_y;
+  d.status = b->d_status;
+  d.counters = b->d_counters;
+  d.logits = b->d_logits;
+  d.swiglu_limit = b->cfg.swiglu_limit;
+  return d;
+}
+
+// Uploads enqueued on the copy stream must land before the next kernel reads a slot.
+cudaError_t order_after_copies(mer_backend *b, cudaStream_t s) {
+  if (!b->copy_pending) return cudaSuccess;
+  cudaError_t e = cudaStreamWaitEvent(s, b->ev_copy_done, 0);
+  if (e == cudaSuccess && s == b->compute) b->copy_pending = false;
+  return e;
+}
+
+bool use_stream_path(mer_backend *b, const MoeDispatch &d) {
+  if (b->kernel_path == 1) return false;
+  return stream_ffn_supported(d.dtype, d.D, d.F) && b->d_stream_scratch != nullptr;
+}
+
+cudaError_t run_ffn(mer_backend *b, const MoeDispatch &d, cudaStream_t s, int *launches, cudaEvent_t ev_mid = nullptr) {
+  if (use_stream_path(b, d)) return launch_ffn_stream(d, b->d_stream_scratch, b->sm_count, s, launches, ev_mid);
+  return launch_ffn_generic(d, s, launches, ev_mid);
+}
+
+constexpr size_t TIMING_SET = 5, TIMING_MAX_SETS = 4096;
+
+// Returns the next set of 5 events, or null when timing is off or the ring is full.
+cudaEvent_t *next_timing_set(mer_backend *b) {
+  if (!b->timing_on || b->timing_used >= TIMING_MAX_SETS) return nullptr;
+  size_t need = (b->timing_used + 1) * TIMING_SET;
+  while (b->timing_events.size() < need) {
+    cudaEvent_t e;
+    if (cudaEventCreate(&e) != cudaSuccess) return nullptr;
+    b->timing_events.push_back(e);
+  }
+  return &b->timing_events[b->timing_used++ * TIMING_SET];
+}
+
+void drain_timing(mer_backend *b) {
+  for (size_t i = 0; i < b->timing_used; i++) {
+    cudaEvent_t *e = &b->timing_events[i * TIMING_SET];
+    if (cudaEventSynchronize(e[4]) != cudaSuccess) continue;
+    float r = 0, gu = 0, dn = 0, cb = 0;
+    cudaEventElapsedTime(&r, e[0], e[1]);
+    bool have_mid = cudaEventQuery(e[2]) == cudaSuccess && cudaEventElapsedTime(&gu, e[1], e[2]) == cudaSuccess;
+    if (have_mid) {
+      cudaEventElapsedTime(&dn, e[2], e[3]);
+    } else {
+      cudaGetLastError();
+      cudaEventElapsedTime(&gu, e[1], e[3]);
+    }
+    cudaEventElapsedTime(&cb, e[3], e[4]);
+    b->timing_acc.samples++;
+    b->timing_acc.router_gate_ms += r;
+    b->timing_acc.expert_gate_up_kernel_ms += gu;
+    b->timing_acc.expert_down_kernel_ms += dn;
+    b->timing_acc.moe_weighted_combination_ms += cb;
+    b->timing_acc.expert_compute_ms += gu + dn;
+  }
+  b->timing_used = 0;
+}
+
+int check_device_status(mer_backend *b, uint32_t status, uint32_t layer, uint32_t expert) {
+  b->err.device_status = status;
+  if (status & MER_DEVSTAT_RESIDENCY_MISS)
+    return fail(b, MER_ERR_RESIDENCY_MISS, layer, expert, "a routed expert has no current HBM slot (device status 0x%x)", status);
+  if (status & MER_DEVSTAT_TIMEOUT)
+    return fail(b, MER_ERR_TIMEOUT, layer, expert, "a bounded device-side wait expired (device status 0x%x)", status);
+  if (status & MER_DEVSTAT_NONFINITE_ROUTER)
+    return fail(b, MER_ERR_NUMERICAL, layer, expert, "non-finite router scores (device status 0x%x)", status);
+  return MER_OK;
+}
+
+int validate_shape_args(mer_backend *b, uint32_t layer, uint32_t expert, size_t d_model, size_t d_ff) {
+  if (d_model != b->cfg.d_model || d_ff != b->cfg.d_ff)
+    return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "shape %zux%zu does not match the backend's %llux%llu", d_model,
+                d_ff, (unsigned long long)b->cfg.d_model, (unsigned long long)b->cfg.d_ff);
+  return MER_OK;
+}
+
+// Host-side residency check for calls whose expert ids are known on the host
+// (current_admission miss -> ResidencyMiss, backend/mod.rs:3870-3882).
+int require_resident(mer_backend *b, uint32_t layer, uint32_t id) {
+  auto it = b->id2slot.find(id);
+  if (id >= b->cfg.max_experts || it == b->id2slot.end())
+    return fail(b, MER_ERR_RESIDENCY_MISS, layer, id, "expert has no current logical GPU admission");
+  b->slots[it->second].last_use = ++b->tick;
+  return MER_OK;
+}
+
+void free_all(mer_backend *b) {
+  auto F = [](auto *&p) {
+    if (p) cudaFree((void *)p);
+    p = nullptr;
+  };
+  auto H = [](auto *&p) {
+    if (p) cudaFreeHost((void *)p);
+    p = nullptr;
+  };
+  for (auto &kv : b->routers) {
+    F(kv.second.d_w);
+    F(kv.second.d_cbias);
+    F(kv.second.d_lbias);
+  }
+  b->routers.clear();
+  F(b->arena), F(b->d_expert_ptr), F(b->d_x), F(b->d_out), F(b->d_h), F(b->d_y), F(b->d_pair_weight), F(b->d_logits);
+  F(b->d_pair_expert), F(b->d_group_expert), F(b->d_offsets), F(b->d_perm), F(b->d_status), F(b->d_counters);
+  F(b->d_f16), F(b->d_stream_scratch), F(b->d_dequant);
+  H(b->h_expert_ptr), H(b->h_stage[0]), H(b->h_stage[1]), H(b->h_hdr), H(b->h_u32), H(b->h_f32);
+  if (b->ev_compute_done) cudaEventDestroy(b->ev_compute_done);
+  if (b->ev_copy_done) cudaEventDestroy(b->ev_copy_done);
+  for (auto &e : b->ev_stage)
+    if (e) cudaEventDestroy(e);
+  for (auto &e : b->timing_events) cudaEventDestroy(e);
+  b->timing_events.clear();
+  if (b->compute) cudaStreamDestroy(b->compute);
+  if (b->copy) cudaStreamDestroy(b->copy);
+}
+
+// Picks a slot for (id, generation): reuse, free, or least-recently-used non-anchor victim
+// (demand_admit_lru, expert_cache.rs:1281-1340: the anchor region is never touched).
+int acquire_slot(mer_backend *b, uint32_t id, uint64_t generation, uint32_t flags, size_t *out, bool *already) {
+  const uint32_t layer = 0, expert = id;
+  *already = false;
+  auto it = b->id2slot.find(id);
+  if (it != b->id2slot.end()) {
+    Slot &s = b->slots[it->second];
+    if (generation < s.generation)
+      return fail(b, MER_ERR_RESIDENCY_MISS, layer, expert, "physical GPU residency has a newer logical generation (%llu > %llu)",
+                  (unsigned long long)s.generation, (unsigned long long)generation);
+    if (generation == s.generation) {
+      *already = true;
+      *out = it->second;
+      return MER_OK;
+    }
+    *out = it->second;  // newer generation replaces the payload in place
+    return MER_OK;
+  }
+  size_t victim = SIZE_MAX;
+  for (size_t i = 0; i < b->n_slots; i++)
+    if (!b->slots[i].used) {
+      victim = i;
+      break;
+    }
+  if (victim == SIZE_MAX) {
+    uint64_t best = UINT64_MAX;
+    for (size_t i = 0; i < b->n_slots; i++)
+      if (!b->slots[i].anchor && b->slots[i].last_use < best) best = b->slots[i].last_use, victim = i;
+    if (victim == SIZE_MAX)
+      return fail(b, MER_ERR_PHYSICAL_CAPACITY, layer, expert, "all %zu HBM slots hold anchor experts", b->n_slots);
+    Slot &v = b->slots[victim];
+    b->id2slot.erase(v.expert_id);
+    b->h_expert_ptr[v.expert_id] = nullptr;
+    cudaMemcpyAsync((void *)(b->d_expert_ptr + v.expert_id), (void *)(b->h_expert_ptr + v.expert_id), sizeof(void *),
+                    cudaMemcpyHostToDevice, b->copy);
+    v.used = false;
+    b->ctr.evictions++;
+  }
+  (void)flags;
+  *out = victim;
+  return MER_OK;
+}
+
+int admit_impl(mer_backend *b, uint32_t id, uint64_t generation, const void *blob, size_t bytes, uint32_t flags,
+               bool from_device) {
+  const uint32_t layer = 0, expert = id;
+  if (!b || !blob) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null backend or blob");
+  if (id >= b->cfg.max_experts)
+    return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "expert id %u outside the id space of %u", id, b->cfg.max_experts);
+  // plan_expert_upload_q4_0 (backend/mod.rs:2482-2549): strict payload size; page padding after
+  // the logical payload is allowed and never copied.
+  if (bytes < b->expert_bytes)
+    return fail(b, MER_ERR_UPLOAD, layer, expert, "blob has %zu bytes, need %zu for %llux%llu", bytes, b->expert_bytes,
+                (unsigned long long)b->cfg.d_model, (unsigned long long)b->cfg.d_ff);
+  std::lock_guard<std::mutex> lock(b->mu);
+  CU(MER_ERR_UPLOAD, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  size_t si;
+  bool already;
+  int rc = acquire_slot(b, id, generation, flags, &si, &already);
+  if (rc) return rc;
+  Slot &s = b->slots[si];
+  if (already) {
+    s.last_use = ++b->tick;
+    if (flags & MER_ADMIT_ANCHOR) s.anchor = true;
+    return MER_OK;
+  }
+  // The slot may still be read by kernels already enqueued on the compute stream.
+  CU(MER_ERR_UPLOAD, "cudaEventRecord", cudaEventRecord(b->ev_compute_done, b->compute));
+  CU(MER_ERR_UPLOAD, "cudaStreamWaitEvent", cudaStreamWaitEvent(b->copy, b->ev_compute_done, 0));
+  uint8_t *slot_base = b->arena + si * b->slot_stride;
+  uint8_t *payload = slot_base + SLOT_HEADER_BYTES;
+  const uint8_t *src = static_cast<const uint8_t *>(blob);
+  if (from_device) {
+    CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(D2D)", cudaMemcpyAsync(payload, src, b->expert_bytes, cudaMemcpyDeviceToDevice, b->copy));
+  } else {
+    cudaPointerAttributes attr{};
+    bool pinned = cudaPointerGetAttributes(&attr, blob) == cudaSuccess && attr.type == cudaMemoryTypeHost;
+    cudaGetLastError();
+    if (pinned) {
+      CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(H2D pinned)",
+         cudaMemcpyAsync(payload, src, b->expert_bytes, cudaMemcpyHostToDevice, b->copy));
+    } else {
+      int which = 0;
+      for (size_t off = 0; off < b->expert_bytes; off += STAGE_BYTES, which ^= 1) {
+        size_t n = std::min(STAGE_BYTES, b->expert_bytes - off);
+        CU(MER_ERR_UPLOAD, "cudaEventSynchronize(stage)", cudaEventSynchronize(b->ev_stage[which]));
+        memcpy(b->h_stage[which], src + off, n);
+        CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(H2D staged)",
+           cudaMemcpyAsync(payload + off, b->h_stage[which], n, cudaMemcpyHostToDevice, b->copy));
+        CU(MER_ERR_UPLOAD, "cudaEventRecord(stage)", cudaEventRecord(b->ev_stage[which], b->copy));
+      }
+    }
+  }
+  SlotHeader *hdr = b->h_hdr + si;
+  hdr->epoch = generation;
+  hdr->expert_id = id;
+  hdr->dtype = (uint32_t)b->cfg.dtype;
+  hdr->payload_bytes = b->expert_bytes;
+  CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(header)", cudaMemcpyAsync(slot_base, hdr, sizeof(SlotHeader), cudaMemcpyHostToDevice, b->copy));
+  b->h_expert_ptr[id] = payload;
+  CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(table)",
+     cudaMemcpyAsync((void *)(b->d_expert_ptr + id), (void *)(b->h_expert_ptr + id), sizeof(void *), cudaMemcpyHostToDevice, b->copy));
+  CU(MER_ERR_UPLOAD, "cudaEventRecord(copy)", cudaEventRecord(b->ev_copy_done, b->copy));
+  b->copy_pending = true;
+  s.used = true;
+  s.anchor = (flags & MER_ADMIT_ANCHOR) != 0;
+  s.expert_id = id;
+  s.generation = generation;
+  s.last_use = ++b->tick;
+  b->id2slot[id] = si;
+  b->ctr.expert_uploads++;
+  b->ctr.expert_upload_bytes += b->expert_bytes;
+  if (!(flags & MER_ADMIT_ASYNC)) CU(MER_ERR_UPLOAD, "cudaStreamSynchronize(copy)", cudaStreamSynchronize(b->copy));
+  return MER_OK;
+}
+
+// Shared tail of the host entry points whose routing comes from the caller: upload ids and
+// weights, group, run the FFN.  `single_group` = all pairs run the same expert.
+int dispatch_given_routing(mer_backend *b, uint32_t layer, MoeDispatch &d, const uint32_t *ids, const float *weights,
+                           size_t n_pairs, bool single_group, int *launches) {
+  const uint32_t expert = n_pairs ? ids[0] : MER_NONE;
+  memcpy(b->h_u32, ids, n_pairs * sizeof(uint32_t));
+  for (size_t i = 0; i < n_pairs; i++) b->h_f32[i] = weights ? weights[i] : 1.0f;
+  CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(ids)",
+     cudaMemcpyAsync(b->d_pair_expert, b->h_u32, n_pairs * 4, cudaMemcpyHostToDevice, b->compute));
+  CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(weights)",
+     cudaMemcpyAsync(b->d_pair_weight, b->h_f32, n_pairs * 4, cudaMemcpyHostToDevice, b->compute));
+  CU(MER_ERR_SUBMISSION, "cudaMemsetAsync(status)", cudaMemsetAsync(b->d_status, 0, 4, b->compute));
+  d.n_groups = single_group ? 1u : (uint32_t)n_pairs;
+  CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, b->compute));
+  CU(MER_ERR_SUBMISSION, "group kernel", launch_groups_from_pairs(d, b->compute, launches));
+  CU(MER_ERR_SUBMISSION, "expert FFN kernels", run_ffn(b, d, b->compute, launches));
+  return MER_OK;
+}
+
+int finish_host_call(mer_backend *b, uint32_t layer, uint32_t expert, int launches, size_t n_experts_run) {
+  CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(status)",
+     cudaMemcpyAsync(b->h_u32 + b->max_pairs, b->d_status, 4, cudaMemcpyDeviceToHost, b->compute));
+  CU(MER_ERR_READBACK_MAP, "cudaStreamSynchronize", cudaStreamSynchronize(b->compute));
+  b->ctr.kernel_launches += (uint64_t)launches;
+  b->ctr.gpu_dispatch_attempts += n_experts_run;
+  int rc = check_device_status(b, b->h_u32[b->max_pairs], layer, expert);
+  if (rc && rc != MER_ERR_NUMERICAL) {
+    b->ctr.gpu_dispatch_failures += n_experts_run;  // counted once, never replayed (engine.rs:6624-6642)
+    return rc;
+  }
+  b->ctr.gpu_dispatch_successes += n_experts_run;
+  return rc;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------- exports
+
+MER_EXPORT int mer_abi_version(void) { return MER_ABI_VERSION; }
+
+MER_EXPORT const char *mer_error_kind_name(int kind) {
+  switch (kind) {
+    case MER_OK: return "ok";
+    case MER_ERR_RESIDENCY_MISS: return "residency-miss";
+    case MER_ERR_PHYSICAL_CAPACITY: return "physical-capacity";
+    case MER_ERR_UPLOAD: return "upload";
+    case MER_ERR_VALIDATION_DISPATCH: return "validation-dispatch";
+    case MER_ERR_SUBMISSION: return "submission";
+    case MER_ERR_READBACK_CHANNEL: return "readback-channel";
+    case MER_ERR_READBACK_MAP: return "readback-map";
+    case MER_ERR_DEVICE_LOST: return "device-lost";
+    case MER_ERR_RUNTIME_INVARIANT: return "runtime-invariant";
+    case MER_ERR_INELIGIBLE: return "ineligible";
+    case MER_ERR_TIMEOUT: return "timeout";
+    case MER_ERR_INVALID_ARGUMENT: return "invalid-argument";
+    case MER_ERR_NUMERICAL: return "numerical";
+    default: return "unknown";
+  }
+}
+
+MER_EXPORT uint64_t mer_expert_bytes(int32_t dtype, uint64_t d_model, uint64_t d_ff) {
+  if (dtype != MER_DTYPE_Q4_0 && dtype != MER_DTYPE_Q8_0) return 0;
+  uint64_t one = d_model * d_ff;
+  return (one + 31) / 32 * block_bytes(dtype) * 3;
+}
+
+MER_EXPORT int mer_routed_expert_compatibility(int32_t dtype, uint64_t d_model, uint64_t d_ff) {
+  // MAX_EXPERT_D_FF workspace bound and %32 alignment, backend/mod.rs:4691-4720; unaligned
+  // shapes stay eligible here through the generic kernels.
+  if (dtype != MER_DTYPE_Q4_0 && dtype != MER_DTYPE_Q8_0) return MER_ERR_VALIDATION_DISPATCH;
+  if (d_model == 0 || d_ff == 0 || d_model > MAX_DIM || d_ff > MAX_DIM) return MER_ERR_VALIDATION_DISPATCH;
+  return MER_OK;
+}
+
+MER_EXPORT int mer_backend_create(const mer_backend_cfg *cfg, mer_backend **out) {
+  if (!cfg || !out) return MER_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  if (mer_routed_expert_compatibility(cfg->dtype, cfg->d_model, cfg->d_ff) != MER_OK) return MER_ERR_VALIDATION_DISPATCH;
+  if (cfg->max_experts == 0 || cfg->max_tokens == 0 || cfg->max_top_k == 0 || cfg->max_top_k > 32) return MER_ERR_INVALID_ARGUMENT;
+  int n_dev = 0;
+  if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0) {
+    cudaGetLastError();
+    return MER_ERR_DEVICE_LOST;  // no CPU fallback: without a CUDA device nothing can run
+  }
+  if (cfg->device < 0 || cfg->device >= n_dev) return MER_ERR_INVALID_ARGUMENT;
+  mer_backend *b = new (std::nothrow) mer_backend();
+  if (!b) return MER_ERR_PHYSICAL_CAPACITY;
+  b->cfg = *cfg;
+  const uint32_t layer = 0, expert = MER_NONE;
+  (void)layer, (void)expert;
+  auto bail = [&](int rc) {
+    free_all(b);
+    delete b;
+    return rc;
+  };
+#define CB(call)                                   \
+  do {                                             \
+    if ((call) != cudaSuccess) {                   \
+      cudaGetLastError();                          \
+      return bail(MER_ERR_PHYSICAL_CAPACITY);      \
+    }                                              \
+  } while (0)
+  CB(cudaSetDevice(cfg->device));
+  cudaDeviceProp prop{};
+  CB(cudaGetDeviceProperties(&prop, cfg->device));
+  b->sm_count = prop.multiProcessorCount;
+  b->expert_bytes = (size_t)mer_expert_bytes(cfg->dtype, cfg->d_model, cfg->d_ff);
+  b->slot_stride = (SLOT_HEADER_BYTES + b->expert_bytes + SLOT_ALIGN - 1) / SLOT_ALIGN * SLOT_ALIGN;
+  b->n_slots = (size_t)(cfg->vram_capacity_bytes / b->slot_stride);
+  if (b->n_slots == 0) return bail(MER_ERR_PHYSICAL_CAPACITY);
+  if (b->n_slots > cfg->max_experts) b->n_slots = cfg->max_experts;
+  b->slots.resize(b->n_slots);
+  CB(cudaStreamCreateWithFlags(&b->compute, cudaStreamNonBlocking));
+  CB(cudaStreamCreateWithFlags(&b->copy, cudaStreamNonBlocking));
+  CB(cudaEventCreateWithFlags(&b->ev_compute_done, cudaEventDisableTiming));
+  CB(cudaEventCreateWithFlags(&b->ev_copy_done, cudaEventDisableTiming));
+  for (auto &e : b->ev_stage) CB(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  CB(cudaMalloc((void **)&b->arena, b->n_slots * b->slot_stride));
+  CB(cudaMalloc((void **)&b->d_expert_ptr, sizeof(void *) * cfg->max_experts));
+  CB(cudaMemset((void *)b->d_expert_ptr, 0, sizeof(void *) * cfg->max_experts));
+  CB(cudaHostAlloc((void **)&b->h_expert_ptr, sizeof(void *) * cfg->max_experts, cudaHostAllocDefault));
+  memset((void *)b->h_expert_ptr, 0, sizeof(void *) * cfg->max_experts);
+  CB(cudaHostAlloc((void **)&b->h_stage[0], STAGE_BYTES, cudaHostAllocDefault));
+  CB(cudaHostAlloc((void **)&b->h_stage[1], STAGE_BYTES, cudaHostAllocDefault));
+  CB(cudaHostAlloc((void **)&b->h_hdr, sizeof(SlotHeader) * b->n_slots, cudaHostAllocDefault));
+  const size_t D = cfg->d_model, F = cfg->d_ff, T = cfg->max_tokens;
+  b->max_pairs = cfg->max_tokens * cfg->max_top_k;
+  const size_t P = b->max_pairs;
+  b->max_groups = (uint32_t)std::max<size_t>(P, 4096) + 2;
+  b->max_router_experts = 4096;
+  CB(cudaMalloc((void **)&b->d_x, T * D * 4));
+  CB(cudaMalloc((void **)&b->d_out, T * D * 4));
+  CB(cudaMalloc((void **)&b->d_h, P * F * 4));
+  CB(cudaMalloc((void **)&b->d_y, P * D * 4));
+  CB(cudaMalloc((void **)&b->d_pair_weight, P * 4));
+  CB(cudaMalloc((void **)&b->d_pair_expert, P * 4));
+  CB(cudaMalloc((void **)&b->d_group_expert, (size_t)b->max_groups * 4));
+  CB(cudaMalloc((void **)&b->d_offsets, ((size_t)b->max_groups + 1) * 4));
+  CB(cudaMalloc((void **)&b->d_perm, P * 4));
+  CB(cudaMalloc((void **)&b->d_logits, T * b->max_router_experts * 4));
+  CB(cudaMalloc((void **)&b->d_status, 4));
+  CB(cudaMalloc((void **)&b->d_counters, (T + 1) * 4));
+  CB(cudaMemset(b->d_status, 0, 4));
+  CB(cudaMemset(b->d_counters, 0, (T + 1) * 4));
+  CB(cudaMalloc((void **)&b->d_f16, std::max(P, T) * D * 2));
+  CB(cudaHostAlloc((void **)&b->h_u32, (P + 1) * 4, cudaHostAllocDefault));
+  CB(cudaHostAlloc((void **)&b->h_f32, P * 4, cudaHostAllocDefault));
+  if (stream_ffn_supported(cfg->dtype, (uint32_t)D, (uint32_t)F)) {
+    size_t sb = stream_ffn_scratch_bytes((uint32_t)P, (uint32_t)D, (uint32_t)F);
+    if (sb) {
+      CB(cudaMalloc(&b->d_stream_scratch, sb));
+      CB(cudaMemset(b->d_stream_scratch, 0, sb));
+    }
+  }
+  CB(cudaDeviceSynchronize());
+#undef CB
+  b->ctr.arena_bytes = b->n_slots * b->slot_stride;
+  b->ctr.slot_stride_bytes = b->slot_stride;
+  b->ctr.slot_count = b->n_slots;
+  *out = b;
+  return MER_OK;
+}
+
+MER_EXPORT void mer_backend_destroy(mer_backend *b) {
+  if (!b) return;
+  cudaSetDevice(b->cfg.device);
+  cudaDeviceSynchronize();
+  free_all(b);
+  delete b;
+}
+
+MER_EXPORT int mer_backend_synchronize(mer_backend *b) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t layer = 0, expert = MER_NONE;
+  std::lock_guard<std::mutex> lock(b->mu);
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  CU(MER_ERR_UPLOAD, "cudaStreamSynchronize(copy)", cudaStreamSynchronize(b->copy));
+  CU(MER_ERR_READBACK_MAP, "cudaStreamSynchronize(compute)", cudaStreamSynchronize(b->compute));
+  return MER_OK;
+}
+
+MER_EXPORT int mer_expert_admit(mer_backend *b, uint32_t expert_id, uint64_t generation, const void *host_blob, size_t bytes,
+                                uint32_t flags) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  return admit_impl(b, expert_id, generation, host_blob, bytes, flags, false);
+}
+
+MER_EXPORT int mer_expert_admit_device(mer_backend *b, uint32_t expert_id, uint64_t generation, const void *device_blob,
+                                       size_t bytes, uint32_t flags) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  return admit_impl(b, expert_id, generation, device_blob, bytes, flags, true);
+}
+
+MER_EXPORT int mer_expert_retire(mer_backend *b, uint32_t expert_id, uint64_t generation) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t layer = 0, expert = expert_id;
+  std::lock_guard<std::mutex> lock(b->mu);
+  auto it = b->id2slot.find(expert_id);
+  if (it == b->id2slot.end() || b->slots[it->second].generation != generation) return MER_OK;  // not current: nothing to retire
+  CU(MER_ERR_UPLOAD, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  CU(MER_ERR_UPLOAD, "cudaEventRecord", cudaEventRecord(b->ev_compute_done, b->compute));
+  CU(MER_ERR_UPLOAD, "cudaStreamWaitEvent", cudaStreamWaitEvent(b->copy, b->ev_compute_done, 0));
+  b->h_expert_ptr[expert_id] = nullptr;
+  CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(table)",
+     cudaMemcpyAsync((void *)(b->d_expert_ptr + expert_id), (void *)(b->h_expert_ptr + expert_id), sizeof(void *),
+                     cudaMemcpyHostToDevice, b->copy));
+  CU(MER_ERR_UPLOAD, "cudaEventRecord(copy)", cudaEventRecord(b->ev_copy_done, b->copy));
+  b->copy_pending = true;
+  b->slots[it->second] = Slot{};
+  b->id2slot.erase(it);
+  return MER_OK;
+}
+
+MER_EXPORT int mer_expert_contains_generation(mer_backend *b, uint32_t expert_id, uint64_t generation) {
+  if (!b) return 0;
+  std::lock_guard<std::mutex> lock(b->mu);
+  auto it = b->id2slot.find(expert_id);
+  return it != b->id2slot.end() && b->slots[it->second].generation == generation;
+}
+
+MER_EXPORT int mer_router_install(mer_backend *b, uint32_t layer, const float *host_weights, const mer_router_cfg *cfg) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t expert = MER_NONE;
+  if (!host_weights || !cfg) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null router weights or cfg");
+  // LinearGate::new asserts (gating.rs:149-158)
+  if (cfg->top_k == 0 || cfg->top_k > cfg->num_experts)
+    return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "top_k must be in 1..=num_experts");
+  uint32_t slots = cfg->top_k + (cfg->shared_expert_id != MER_NONE ? 1u : 0u);
+  if (slots > b->cfg.max_top_k || cfg->top_k > 32)
+    return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "top_k %u (+shared) exceeds max_top_k %u", cfg->top_k, b->cfg.max_top_k);
+  if (cfg->num_experts > b->max_router_experts || (uint64_t)(layer + 1) * cfg->num_experts > b->cfg.max_experts)
+    return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "layer %u x %u experts exceeds the id space of %u", layer,
+                cfg->num_experts, b->cfg.max_experts);
+  if (cfg->n_group > 64) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "n_group %u > 64", cfg->n_group);
+  std::lock_guard<std::mutex> lock(b->mu);
+  CU(MER_ERR_UPLOAD, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  RouterEntry &r = b->routers[layer];
+  CU(MER_ERR_UPLOAD, "cudaStreamSynchronize", cudaStreamSynchronize(b->compute));
+  if (r.d_w) cudaFree(r.d_w), r.d_w = nullptr;
+  if (r.d_cbias) cudaFree(r.d_cbias), r.d_cbias = nullptr;
+  if (r.d_lbias) cudaFree(r.d_lbias), r.d_lbias = nullptr;
+  size_t wbytes = (size_t)cfg->num_experts * b->cfg.d_model * 4, ebytes = (size_t)cfg->num_experts * 4;
+  CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(router)", cudaMalloc((void **)&r.d_w, wbytes));
+  CU(MER_ERR_UPLOAD, "cudaMemcpy(router)", cudaMemcpy(r.d_w, host_weights, wbytes, cudaMemcpyHostToDevice));
+  if (cfg->correction_bias) {
+    CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(bias)", cudaMalloc((void **)&r.d_cbias, ebytes));
+    CU(MER_ERR_UPLOAD, "cudaMemcpy(bias)", cudaMemcpy(r.d_cbias, cfg->correction_bias, ebytes, cudaMemcpyHostToDevice));
+  }
+  if (cfg->logit_bias) {
+    CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(bias)", cudaMalloc((void **)&r.d_lbias, ebytes));
+    CU(MER_ERR_UPLOAD, "cudaMemcpy(bias)", cudaMemcpy(r.d_lbias, cfg->logit_bias, ebytes, cudaMemcpyHostToDevice));
+  }
+  r.dev.w = r.d_w;
+  r.dev.correction_bias = r.d_cbias;
+  r.dev.logit_bias = r.d_lbias;
+  r.dev.num_experts = cfg->num_experts;
+  r.dev.top_k = cfg->top_k;
+  r.dev.scoring = cfg->scoring_func;
+  r.dev.normalise = cfg->normalise_topk;
+  r.dev.n_group = cfg->n_group < 1 ? 1 : cfg->n_group;  // with_routing: n_group.max(1), gating.rs:234
+  r.dev.topk_group = cfg->topk_group;
+  r.dev.scaling = cfg->routed_scaling_factor;
+  r.dev.shared_expert_id = cfg->shared_expert_id;
+  r.dev.id_base = layer * cfg->num_experts;
+  return MER_OK;
+}
+
+namespace {
+// Enqueues router (+ optional FFN + combine) for device-resident x on stream s.
+int enqueue_layer(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out, bool run_ffn_too,
+                  cudaStream_t s, int *launches, MoeDispatch *out_d) {
+  const uint32_t expert = MER_NONE;
+  auto it = b->routers.find(layer);
+  if (it == b->routers.end()) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "no router installed for layer %u", layer);
+  if (n_tokens == 0 || n_tokens > b->cfg.max_tokens)
+    return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "n_tokens %zu outside 1..=%u", n_tokens, b->cfg.max_tokens);
+  const RouterDev &r = it->second.dev;
+  MoeDispatch d = base_dispatch(b);
+  d.n_tokens = (uint32_t)n_tokens;
+  d.slots = r.top_k + (r.shared_expert_id != MER_NONE ? 1u : 0u);
+  d.n_groups = r.num_experts + (r.shared_expert_id != MER_NONE ? 1u : 0u);
+  d.x = d_x;
+  d.out = d_out;
+  CU(MER_ERR_SUBMISSION, "cudaMemsetAsync(status)", cudaMemsetAsync(b->d_status, 0, 4, s));
+  CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, s));
+  cudaEvent_t *ev = run_ffn_too ? next_timing_set(b) : nullptr;
+  if (ev) cudaEventRecord(ev[0], s);
+  CU(MER_ERR_SUBMISSION, "router kernel", launch_router(r, d, b->cfg.max_tokens, s, launches));
+  if (run_ffn_too) {
+    if (ev) cudaEventRecord(ev[1], s);
+    CU(MER_ERR_SUBMISSION, "expert FFN kernels", run_ffn(b, d, s, launches, ev ? ev[2] : nullptr));
+    if (ev) cudaEventRecord(ev[3], s);
+    CU(MER_ERR_SUBMISSION, "combine kernel", launch_combine(d, s, launches));
+    if (ev) cudaEventRecord(ev[4], s);
+  }
+  if (out_d) *out_d = d;
+  return MER_OK;
+}
+}  // namespace
+
+MER_EXPORT int mer_router_route(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens, uint32_t *ids, float *weights) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t expert = MER_NONE;
+  if (!x || !ids || !weights) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer");
+  std::lock_guard<std::mutex> lock(b->mu);
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  if (n_tokens == 0 || n_tokens > b->cfg.max_tokens)
+    return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "n_tokens %zu outside 1..=%u", n_tokens, b->cfg.max_tokens);
+  CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(x)",
+     cudaMemcpyAsync(b->d_x, x, n_tokens * b->cfg.d_model * 4, cudaMemcpyHostToDevice, b->compute));
+  int launches = 0;
+  MoeDispatch d;
+  int rc = enqueue_layer(b, layer, b->d_x, n_tokens, b->d_out, false, b->compute, &launches, &d);
+  if (rc) return rc;
+  const RouterDev &r = b->routers[layer].dev;
+  // ids/weights on the device are [n_tokens x slots]; the caller gets the top_k routed columns with local ids
+  size_t P = n_tokens * d.slots;
+  CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(ids)", cudaMemcpyAsync(b->h_u32, b->d_pair_expert, P * 4, cudaMemcpyDeviceToHost, b->compute));
+  CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(w)", cudaMemcpyAsync(b->h_f32, b->d_pair_weight, P * 4, cudaMemcpyDeviceToHost, b->compute));
+  rc = finish_host_call(b, layer, expert, launches, 0);
+  for (size_t t = 0; t < n_tokens; t++)
+    for (uint32_t s = 0; s < r.top_k; s++) {
+      uint32_t g = b->h_u32[t * d.slots + s];
+      ids[t * r.top_k + s] = g == MER_NONE ? MER_NONE : g - r.id_base;
+      weights[t * r.top_k + s] = b->h_f32[t * d.slots + s];
+    }
+  b->ctr.hidden_upload_bytes += n_tokens * b->cfg.d_model * 4;
+  b->ctr.readback_bytes += P * 8;
+  return rc;
+}
+
+MER_EXPORT int mer_routed_expert_matmul_batch(mer_backend *b, uint32_t layer, const uint32_t *expert_ids, size_t n,
+                                              const uint16_t *x, size_t d_model, size_t d_ff, uint16_t *out) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  uint32_t expert = (expert_ids && n) ? expert_ids[0] : MER_NONE;
+  if (!expert_ids || !x || !out) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer");
+  std::lock_guard<std::mutex> lock(b->mu);
+  if (n == 0 || n > b->cfg.max_top_k || n > b->max_pairs)
+    return fail(b, MER_ERR_INELIGIBLE, layer, expert, "batch of %zu experts is outside 1..=%u", n, b->cfg.max_top_k);
+  int rc = validate_shape_args(b, layer, expert, d_model, d_ff);
+  if (rc) return rc;
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  b->ctr.batch_calls += n > 1;
+  b->ctr.selected_routed_experts += n;
+  for (size_t i = 0; i < n; i++)
+    if ((rc = require_resident(b, layer, expert_ids[i])) != MER_OK) {
+      b->ctr.gpu_dispatch_attempts += n;
+      b->ctr.gpu_dispatch_failures += n;
+      return rc;
+    }
+  const size_t D = b->cfg.d_model;
+  CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(x)", cudaMemcpyAsync(b->d_f16, x, D * 2, cudaMemcpyHostToDevice, b->compute));
+  CU(MER_ERR_SUBMISSION, "f16->f32", launch_f16_to_f32(b->d_f16, b->d_x, D, b->compute));
+  MoeDispatch d = base_dispatch(b);
+  d.n_tokens = 1;
+  d.slots = (uint32_t)n;
+  d.x = b->d_x;
+  d.out = b->d_out;
+  int launches = 1;
+  rc = dispatch_given_routing(b, layer, d, expert_ids, nullptr, n, false, &launches);
+  if (rc) return rc;
+  CU(MER_ERR_SUBMISSION, "f32->f16", launch_f32_to_f16(b->d_y, b->d_f16, n * D, b->compute));
+  launches++;
+  CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(out)", cudaMemcpyAsync(out, b->d_f16, n * D * 2, cudaMemcpyDeviceToHost, b->compute));
+  b->ctr.hidden_upload_bytes += D * 2;
+  b->ctr.readback_bytes += n * D * 2;
+  return finish_host_call(b, layer, expert, launches, n);
+}
+
+MER_EXPORT int mer_routed_expert_matmul(mer_backend *b, uint32_t layer, uint32_t expert_id, const uint16_t *x, size_t d_model,
+                                        size_t d_ff, uint16_t *out) {
+  return mer_routed_expert_matmul_batch(b, layer, &expert_id, 1, x, d_model, d_ff, out);
+}
+
+MER_EXPORT int mer_routed_expert_forward_f32(mer_backend *b, uint32_t layer, uint32_t expert_id, const float *x, size_t n_tokens,
+                                             float *out) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t expert = expert_id;
+  if (!x || !out) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer");
+  std::lock_guard<std::mutex> lock(b->mu);
+  if (n_tokens == 0 || n_tokens > b->cfg.max_tokens || n_tokens > b->max_pairs)
+    return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "n_tokens %zu outside 1..=%u", n_tokens, b->cfg.max_tokens);
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  b->ctr.selected_routed_experts += 1;
+  int rc = require_resident(b, layer, expert_id);
+  if (rc) {
+    b->ctr.gpu_dispatch_attempts++, b->ctr.gpu_dispatch_failures++;
+    return rc;
+  }
+  const size_t D = b->cfg.d_model;
+  CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(x)", cudaMemcpyAsync(b->d_x, x, n_tokens * D * 4, cudaMemcpyHostToDevice, b->compute));
+  MoeDispatch d = base_dispatch(b);
+  d.n_tokens = (uint32_t)n_tokens;
+  d.slots = 1;
+  d.x = b->d_x;
+  d.out = b->d_out;
+  std::vector<uint32_t> ids(n_tokens, expert_id);
+  int launches = 0;
+  rc = dispatch_given_routing(b, layer, d, ids.data(), nullptr, n_tokens, true, &launches);
+  if (rc) return rc;
+  CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(out)", cudaMemcpyAsync(out, b->d_y, n_tokens * D * 4, cudaMemcpyDeviceToHost, b->compute));
+  b->ctr.hidden_upload_bytes += n_tokens * D * 4;
+  b->ctr.readback_bytes += n_tokens * D * 4;
+  return finish_host_call(b, layer, expert, launches, 1);
+}
+
+MER_EXPORT int mer_moe_step_weighted_into(mer_backend *b, uint32_t layer, const float *x, const uint32_t *expert_ids,
+                                          const float *weights, size_t n_slots, float *out) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  uint32_t expert = (expert_ids && n_slots) ? expert_ids[0] : MER_NONE;
+  if (!x || !expert_ids || !weights || !out) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer");
+  std::lock_guard<std::mutex> lock(b->mu);
+  if (n_slots == 0 || n_slots > b->cfg.max_top_k)
+    return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "n_slots %zu outside 1..=%u", n_slots, b->cfg.max_top_k);
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  b->ctr.selected_routed_experts += n_slots;
+  int rc;
+  for (size_t i = 0; i < n_slots; i++)
+    if ((rc = require_resident(b, layer, expert_ids[i])) != MER_OK) {
+      b->ctr.gpu_dispatch_attempts += n_slots, b->ctr.gpu_dispatch_failures += n_slots;
+      return rc;
+    }
+  const size_t D = b->cfg.d_model;
+  CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(x)", cudaMemcpyAsync(b->d_x, x, D * 4, cudaMemcpyHostToDevice, b->compute));
+  MoeDispatch d = base_dispatch(b);
+  d.n_tokens = 1;
+  d.slots = (uint32_t)n_slots;
+  d.x = b->d_x;
+  d.out = b->d_out;
+  int launches = 0;
+  rc = dispatch_given_routing(b, layer, d, expert_ids, weights, n_slots, false, &launches);
+  if (rc) return rc;
+  CU(MER_ERR_SUBMISSION, "combine kernel", launch_combine(d, b->compute, &launches));
+  CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(out)", cudaMemcpyAsync(out, b->d_out, D * 4, cudaMemcpyDeviceToHost, b->compute));
+  b->ctr.batch_calls += 1;
+  b->ctr.hidden_upload_bytes += D * 4;
+  b->ctr.readback_bytes += D * 4;
+  return finish_host_call(b, layer, expert, launches, n_slots);
+}
+
+MER_EXPORT int mer_moe_layer_forward(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens, float *out, uint32_t *ids,
+                                     float *weights) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t expert = MER_NONE;
+  if (!x || !out) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer");
+  std::lock_guard<std::mutex> lock(b->mu);
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  if (n_tokens == 0 || n_tokens > b->cfg.max_tokens)
+    return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "n_tokens %zu outside 1..=%u", n_tokens, b->cfg.max_tokens);
+  const size_t D = b->cfg.d_model;
+  CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(x)", cudaMemcpyAsync(b->d_x, x, n_tokens * D * 4, cudaMemcpyHostToDevice, b->compute));
+  int launches = 0;
+  MoeDispatch d;
+  int rc = enqueue_layer(b, layer, b->d_x, n_tokens, b->d_out, true, b->compute, &launches, &d);
+  if (rc) return rc;
+  const RouterDev &r = b->routers[layer].dev;
+  size_t P = n_tokens * d.slots;
+  CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(out)", cudaMemcpyAsync(out, b->d_out, n_tokens * D * 4, cudaMemcpyDeviceToHost, b->compute));
+  if (ids) CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(ids)", cudaMemcpyAsync(b->h_u32, b->d_pair_expert, P * 4, cudaMemcpyDeviceToHost, b->compute));
+  if (weights) CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(w)", cudaMemcpyAsync(b->h_f32, b->d_pair_weight, P * 4, cudaMemcpyDeviceToHost, b->compute));
+  b->ctr.selected_routed_experts += P;
+  rc = finish_host_call(b, layer, expert, launches, P);
+  for (size_t t = 0; t < n_tokens; t++)
+    for (uint32_t s = 0; s < r.top_k; s++) {
+      if (ids) {
+        uint32_t g = b->h_u32[t * d.slots + s];
+        ids[t * r.top_k + s] = g == MER_NONE ? MER_NONE : g - r.id_base;
+      }
+      if (weights) weights[t * r.top_k + s] = b->h_f32[t * d.slots + s];
+    }
+  b->ctr.hidden_upload_bytes += n_tokens * D * 4;
+  b->ctr.readback_bytes += n_tokens * D * 4 + (ids ? P * 4 : 0) + (weights ? P * 4 : 0);
+  return rc;
+}
+
+MER_EXPORT int mer_moe_layer_forward_device(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out,
+                                            uint32_t *d_ids, float *d_weights, void *stream) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t expert = MER_NONE;
+  if (!d_x || !d_out) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer");
+  std::lock_guard<std::mutex> lock(b->mu);
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int launches = 0;
+  MoeDispatch d;
+  int rc = enqueue_layer(b, layer, d_x, n_tokens, d_out, true, s, &launches, &d);
+  if (rc) return rc;
+  size_t P = n_tokens * d.slots;
+  // routing is exported as stored: [n_tokens x slots] global ids (slots = top_k + shared)
+  if (d_ids) CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(ids)", cudaMemcpyAsync(d_ids, b->d_pair_expert, P * 4, cudaMemcpyDeviceToDevice, s));
+  if (d_weights) CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(w)", cudaMemcpyAsync(d_weights, b->d_pair_weight, P * 4, cudaMemcpyDeviceToDevice, s));
+  b->ctr.kernel_launches += (uint64_t)launches;
+  b->ctr.selected_routed_experts += P;
+  b->ctr.gpu_dispatch_attempts += P;
+  b->ctr.gpu_dispatch_successes += P;
+  return MER_OK;
+}
+
+MER_EXPORT int mer_dequant_projection_f32(mer_backend *b, uint32_t expert_id, int projection, float *out) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t layer = 0, expert = expert_id;
+  if (!out || projection < 0 || projection > 2) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "bad projection or null out");
+  std::lock_guard<std::mutex> lock(b->mu);
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  int rc = require_resident(b, layer, expert_id);
+  if (rc) return rc;
+  size_t n = (size_t)b->cfg.d_model * b->cfg.d_ff;
+  if (!b->d_dequant) CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(dequant)", cudaMalloc((void **)&b->d_dequant, n * 4));
+  const uint8_t *src = b->h_expert_ptr[expert_id] + (size_t)projection * (b->expert_bytes / 3);
+  CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, b->compute));
+  CU(MER_ERR_SUBMISSION, "dequant kernel", launch_dequant(b->cfg.dtype, src, b->d_dequant, n, b->compute));
+  CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(out)", cudaMemcpyAsync(out, b->d_dequant, n * 4, cudaMemcpyDeviceToHost, b->compute));
+  CU(MER_ERR_READBACK_MAP, "cudaStreamSynchronize", cudaStreamSynchronize(b->compute));
+  b->ctr.kernel_launches++;
+  return MER_OK;
+}
+
+MER_EXPORT int mer_qualification_matvec(mer_backend *b, int32_t dtype, const void *weights, size_t weights_len, const float *input,
+                                        size_t rows, size_t columns, size_t w_block_off, float *out) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t layer = 0, expert = MER_NONE;
+  if (!weights || !input || !out) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer");
+  if (dtype != MER_DTYPE_Q4_0 && dtype != MER_DTYPE_Q8_0) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "unknown dtype");
+  // validate_raw_case (q4_parity.rs:621-660)
+  if (rows == 0 || columns == 0 || columns % MER_BLOCK_ELEMS != 0)
+    return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "invalid raw geometry rows=%zu columns=%zu", rows, columns);
+  size_t bb = block_bytes(dtype), need = (w_block_off + rows * (columns / MER_BLOCK_ELEMS)) * bb;
+  if (weights_len < need || weights_len % bb != 0)
+    return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "raw weights have %zu bytes, require at least %zu complete blocks' worth",
+                weights_len, need);
+  for (size_t i = 0; i < columns; i++)
+    if (!std::isfinite(input[i])) return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "raw input contains a nonfinite value");
+  std::lock_guard<std::mutex> lock(b->mu);
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  uint8_t *d_w = nullptr;
+  float *d_in = nullptr, *d_o = nullptr;
+  cudaError_t e = cudaMalloc((void **)&d_w, weights_len);
+  if (e == cudaSuccess) e = cudaMalloc((void **)&d_in, columns * 4);
+  if (e == cudaSuccess) e = cudaMalloc((void **)&d_o, rows * 4);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(d_w, weights, weights_len, cudaMemcpyHostToDevice, b->compute);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(d_in, input, columns * 4, cudaMemcpyHostToDevice, b->compute);
+  if (e == cudaSuccess) e = launch_raw_matvec(dtype, d_w + w_block_off * bb, d_in, d_o, rows, columns, b->compute);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(out, d_o, rows * 4, cudaMemcpyDeviceToHost, b->compute);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(b->compute);
+  cudaFree(d_w), cudaFree(d_in), cudaFree(d_o);
+  if (e != cudaSuccess) return cuda_fail(b, MER_ERR_SUBMISSION, layer, expert, "raw qualification matvec", e);
+  return MER_OK;
+}
+
+MER_EXPORT int mer_stage_timing_enable(mer_backend *b, int on) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(b->mu);
+  cudaSetDevice(b->cfg.device);
+  drain_timing(b);
+  b->timing_on = on != 0;
+  if (on) b->timing_acc = mer_stage_timings{};
+  return MER_OK;
+}
+
+MER_EXPORT int mer_stage_timings_read(mer_backend *b, mer_stage_timings *out) {
+  if (!b || !out) return MER_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(b->mu);
+  cudaSetDevice(b->cfg.device);
+  drain_timing(b);
+  *out = b->timing_acc;
+  return MER_OK;
+}
+
+MER_EXPORT int mer_last_error(mer_backend *b, mer_error_info *out) {
+  if (!b || !out) return MER_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(b->mu);
+  *out = b->err;
+  return MER_OK;
+}
+
+MER_EXPORT int mer_snapshot(mer_backend *b, mer_counters *out) {
+  if (!b || !out) return MER_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(b->mu);
+  b->ctr.resident_experts = b->id2slot.size();
+  b->ctr.resident_bytes = b->id2slot.size() * b->expert_bytes;
+  *out = b->ctr;
+  return MER_OK;
+}
+
+MER_EXPORT int mer_set_kernel_path(mer_backend *b, int path) {
+  if (!b || path < 0 || path > 2) return MER_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(b->mu);
+  if (path == 2 && !b->d_stream_scratch)
+    return fail(b, MER_ERR_INELIGIBLE, 0, MER_NONE, "streaming kernels need d_model and d_ff to be multiples of 256");
+  b->kernel_path = path;
+  return MER_OK;
+}

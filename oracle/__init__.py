@@ -86,6 +86,7 @@ def lib():
         L.mer_oracle_randomized_q8_expert.argtypes = [sz, sz, u64, vp]
         L.mer_oracle_moe_layer_forward.argtypes = [i32, i32, C.POINTER(_Gate), vp, sz, vp, vp, sz, sz,
                                                    f32, vp, vp, vp, vp, i32]
+        L.mer_oracle_moe_layer_forward_production.argtypes = [i32, C.POINTER(_Gate), vp, sz, vp, vp, sz, sz, f32, vp, i32]
         _lib = L
     return _lib
 
@@ -293,3 +294,18 @@ def moe_layer_forward(dtype, gate: LinearGate, expert_blobs, x, d_ff, variant=FW
     if rc:
         raise OracleError(rc)
     return out, ids, w, gaps
+
+
+def moe_layer_forward_production(dtype, gate: LinearGate, expert_blobs, x, d_ff, n_threads, shared_blob=None,
+                                 swiglu_limit=0.0, _ptr_cache={}):
+    """Production-shaped (fused zero-copy AVX2 rows, threaded) layer forward: the timed CPU baseline."""
+    x = _f32(x).reshape(-1, gate.d_model)
+    blobs = [_u8(b) for b in expert_blobs]
+    ptrs = (C.c_void_p * len(blobs))(*[b.ctypes.data for b in blobs])
+    shared = _u8(shared_blob) if shared_blob is not None else None
+    out = np.empty_like(x)
+    rc = lib().mer_oracle_moe_layer_forward_production(dtype, C.byref(gate.c), ptrs, blobs[0].size, _p(shared), _p(x),
+                                                       x.shape[0], d_ff, swiglu_limit, _p(out), n_threads)
+    if rc:
+        raise OracleError(rc)
+    return out

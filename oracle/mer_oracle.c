@@ -950,3 +950,112 @@ int mer_oracle_moe_layer_forward(int dtype, int variant, const mer_oracle_gate *
   free(tids), free(jobs);
   return rc;
 }
+
+/* ----------------------------------------------- production-shaped layer */
+
+static int expert_forward_rows_1t(int dtype, const uint8_t *blob, size_t proj, const float *x, size_t d_model,
+                                  size_t d_ff, float limit, float *gated, float *y) {
+  mt_job j;
+  j.dtype = dtype, j.gate = blob, j.up = blob + proj, j.down = blob + 2 * proj;
+  j.x = x, j.gated = gated, j.y = y, j.d_model = d_model, j.d_ff = d_ff, j.limit = limit;
+  j.phase = 0, j.row0 = 0, j.row1 = d_ff;
+  mt_worker(&j);
+  j.phase = 1, j.row1 = d_model;
+  mt_worker(&j);
+  return 0;
+}
+
+typedef struct {
+  int dtype;
+  const mer_oracle_gate *gate;
+  const uint8_t *const *blobs;
+  const uint8_t *shared;
+  size_t proj, d_ff, t0, t1;
+  const float *x;
+  float limit;
+  float *out;
+  int rc;
+} prod_job;
+
+static void *prod_worker(void *arg) {
+  prod_job *j = (prod_job *)arg;
+  const mer_oracle_gate *g = j->gate;
+  size_t D = g->d_model, k = g->top_k;
+  float *y = (float *)malloc(sizeof(float) * (D + j->d_ff));
+  float *gated = y + D;
+  uint32_t *ids = (uint32_t *)malloc(sizeof(uint32_t) * k);
+  float *w = (float *)malloc(sizeof(float) * k);
+  for (size_t t = j->t0; t < j->t1 && !j->rc; t++) {
+    const float *xt = j->x + t * D;
+    float *ot = j->out + t * D;
+    size_t n = 0;
+    j->rc = mer_oracle_route(g, xt, ids, w, &n, NULL, NULL);
+    for (size_t i = 0; i < D; i++) ot[i] = 0.0f;
+    for (size_t s = 0; s < n && !j->rc; s++) {
+      expert_forward_rows_1t(j->dtype, j->blobs[ids[s]], j->proj, xt, D, j->d_ff, j->limit, gated, y);
+      if (w[s] != 0.0f)
+        for (size_t i = 0; i < D; i++) ot[i] += w[s] * y[i];
+    }
+    if (!j->rc && j->shared) {
+      expert_forward_rows_1t(j->dtype, j->shared, j->proj, xt, D, j->d_ff, j->limit, gated, y);
+      for (size_t i = 0; i < D; i++) ot[i] += y[i];
+    }
+  }
+  free(y), free(ids), free(w);
+  return NULL;
+}
+
+int mer_oracle_moe_layer_forward_production(int dtype, const mer_oracle_gate *gate,
+                                            const uint8_t *const *expert_blobs, size_t blob_len,
+                                            const uint8_t *shared_blob, const float *x, size_t n_tokens,
+                                            size_t d_ff, float swiglu_limit, float *out, int n_threads) {
+  size_t D = gate->d_model, proj;
+  int rc = check_expert_layout(dtype, blob_len, D, d_ff, &proj);
+  if (rc) return rc;
+  if (D % BLK || d_ff % BLK) return MER_ORACLE_ERR_INVALID_LAYOUT;
+  if (n_threads < 1) n_threads = 1;
+  if (n_tokens >= (size_t)n_threads) {
+    pthread_t *tids = (pthread_t *)malloc(sizeof(pthread_t) * (size_t)n_threads);
+    prod_job *jobs = (prod_job *)malloc(sizeof(prod_job) * (size_t)n_threads);
+    for (int t = 0; t < n_threads; t++) {
+      prod_job *j = &jobs[t];
+      j->dtype = dtype, j->gate = gate, j->blobs = expert_blobs, j->shared = shared_blob, j->proj = proj;
+      j->d_ff = d_ff, j->x = x, j->limit = swiglu_limit, j->out = out, j->rc = 0;
+      j->t0 = n_tokens * (size_t)t / (size_t)n_threads;
+      j->t1 = n_tokens * (size_t)(t + 1) / (size_t)n_threads;
+      if (t > 0) pthread_create(&tids[t], NULL, prod_worker, j);
+    }
+    prod_worker(&jobs[0]);
+    rc = jobs[0].rc;
+    for (int t = 1; t < n_threads; t++) {
+      pthread_join(tids[t], NULL);
+      if (!rc) rc = jobs[t].rc;
+    }
+    free(tids), free(jobs);
+    return rc;
+  }
+  size_t k = gate->top_k;
+  float *y = (float *)malloc(sizeof(float) * D);
+  uint32_t *ids = (uint32_t *)malloc(sizeof(uint32_t) * k);
+  float *w = (float *)malloc(sizeof(float) * k);
+  for (size_t t = 0; t < n_tokens && !rc; t++) {
+    const float *xt = x + t * D;
+    float *ot = out + t * D;
+    size_t n = 0;
+    rc = mer_oracle_route(gate, xt, ids, w, &n, NULL, NULL);
+    for (size_t i = 0; i < D; i++) ot[i] = 0.0f;
+    for (size_t s = 0; s < n && !rc; s++) {
+      int r = mer_oracle_expert_forward_mt(dtype, expert_blobs[ids[s]], blob_len, xt, D, d_ff, swiglu_limit, y, n_threads);
+      if (r < 0) rc = -r;
+      if (w[s] != 0.0f)
+        for (size_t i = 0; i < D; i++) ot[i] += w[s] * y[i];
+    }
+    if (!rc && shared_blob) {
+      int r = mer_oracle_expert_forward_mt(dtype, shared_blob, blob_len, xt, D, d_ff, swiglu_limit, y, n_threads);
+      if (r < 0) rc = -r;
+      for (size_t i = 0; i < D; i++) ot[i] += y[i];
+    }
+  }
+  free(y), free(ids), free(w);
+  return rc;
+}

@@ -160,6 +160,18 @@ int mer_oracle_moe_layer_forward(int dtype, int variant, const mer_oracle_gate *
                                  float *out, uint32_t *topk_ids, float *topk_w,
                                  float *gaps, int n_threads);
 
+/*
+ * Production-shaped timing form of the same layer: zero-copy fused row kernels
+ * (kernels/avx2.rs:98-187 when AVX2+FMA is present).  Tokens fan out over the
+ * threads when n_tokens >= n_threads; otherwise each expert's rows do
+ * (parallel.rs:432-468), one token at a time as batch_scheduler.rs:1378-1382 runs them.
+ */
+int mer_oracle_moe_layer_forward_production(int dtype, const mer_oracle_gate *gate,
+                                            const uint8_t *const *expert_blobs, size_t blob_len,
+                                            const uint8_t *shared_blob, const float *x,
+                                            size_t n_tokens, size_t d_ff, float swiglu_limit,
+                                            float *out, int n_threads);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,485 @@
+"""GPU parity tests: every call goes through the C ABI (libmer_b200.so) and is checked against the
+CPU oracle on the same seeded inputs.  Bars: dequantised weights and top-k indices bit-exact /
+identical; FFN outputs within max-abs 1e-3 relative to the output RMS."""
+import numpy as np
+import pytest
+
+import mer_b200
+import oracle
+from mer_b200 import GpuExpertBatchDispatchOutcome as Outcome
+from mer_b200 import GpuExpertDispatchErrorKind as Kind
+
+pytestmark = pytest.mark.gpu
+
+synth = __import__("importlib").import_module("mer_b200.synth")
+
+FFN_TOL = 1e-3  # max-abs error relative to the RMS of the reference output
+
+
+def rel_rms_err(got, ref):
+    ref = np.asarray(ref, np.float64)
+    rms = np.sqrt(np.mean(ref ** 2)) + 1e-30
+    return float(np.max(np.abs(np.asarray(got, np.float64) - ref)) / rms)
+
+
+def backend(dtype, D, F, n_experts=4, **kw):
+    stride = (256 + mer_b200.expert_bytes(dtype, D, F) + 4095) // 4096 * 4096  # header + payload, page aligned
+    cap = stride * kw.pop("slots", n_experts)
+    return mer_b200.Backend(dtype, D, F, cap, kw.pop("max_experts", max(n_experts, 16)), **kw)
+
+
+def random_blob(dtype, D, F, seed, expert=0):
+    return synth.make_expert_blob(dtype, D, F, seed, 0, expert)
+
+
+# ----------------------------------------------------------------------------- codecs
+
+@pytest.mark.parametrize("dtype", [oracle.Q4_0, oracle.Q8_0])
+@pytest.mark.parametrize("shape", [(64, 96), (37, 45), (256, 512)])
+def test_dequantised_weights_bit_exact(dtype, shape):
+    D, F = shape
+    blob = random_blob(dtype, D, F, 5)
+    with backend(dtype, D, F) as b:
+        b.admit(3, 1, blob)
+        proj = oracle.projection_bytes(dtype, D, F)
+        for p in range(3):
+            got = b.dequant_projection(3, p)
+            ref = oracle.dequant_stream(dtype, blob[p * proj:(p + 1) * proj], D * F)
+            assert (got.view(np.uint32) == ref.view(np.uint32)).all()
+
+
+def test_literal_blocks_dequant_bit_exact(golden):
+    # inference.rs:5613-5626 block through the device decoder (1 x 32 "expert" projections)
+    blk = np.array(golden["q4_0_non_symmetric_block"]["block"], np.uint8)
+    with backend(oracle.Q4_0, 32, 1) as b:
+        b.admit(0, 1, np.tile(blk, 3))
+        assert b.dequant_projection(0, 0).tolist() == golden["q4_0_non_symmetric_block"]["expected"]
+
+
+def test_canonical_raw_q4_cases(golden):
+    # q4_parity.rs:470-572 through mer_qualification_matvec, tolerance 1e-5 + 1e-4*|cpu| (q4_parity.rs:26-27)
+    g = golden["q4_raw_cases"]
+    with backend(oracle.Q4_0, 32, 32) as b:
+        for c in g["cases"]:
+            got = b.qualification_matvec(np.array(c["weights"], np.uint8), c["input"], c["rows"], c["columns"], c["w_block_off"])
+            ref = np.array(c["expected"], np.float32)
+            assert (np.abs(got - ref) <= g["abs_tol"] + g["rel_tol"] * np.abs(ref)).all(), c["name"]
+        with pytest.raises(mer_b200.GpuExpertDispatchError) as e:  # validate_raw_case: columns % 32
+            b.qualification_matvec(np.zeros(18, np.uint8), np.zeros(31, np.float32), 1, 31)
+        assert e.value.kind == Kind.ValidationDispatch
+
+
+def test_q8_row_cases_on_device(golden):
+    # kernels/avx2.rs:193-288 row cases (a subset of seeds per width) through the raw matvec
+    g = golden["q8_row_cases"]
+    mask = 2 ** 64 - 1
+    with backend(oracle.Q8_0, 32, 32) as b:
+        for rc in g["rows"][::3]:
+            width, case, state = rc["width"], rc["case"], rc["seed"]
+            row = np.zeros(width // 32 * 34, np.uint8)
+            for block in range(width // 32):
+                bits = {0: 0, 1: 1, 2: 0x7BFF, 6: 0x0400}.get(case)
+                if bits is None:
+                    bits = int(np.float16(np.float32(0.003) + np.float32(block) * np.float32(0.00001)).view(np.uint16))
+                row[block * 34], row[block * 34 + 1] = bits & 0xFF, bits >> 8
+                for i in range(32):
+                    if case == 3:
+                        q = 0
+                    elif case == 4:
+                        q = -128 if (i + block) % 2 == 0 else 127
+                    elif case == 5:
+                        q = -1 if (i + block) % 2 == 0 else 1
+                    else:
+                        state ^= (state << 13) & mask
+                        state ^= state >> 7
+                        state ^= (state << 17) & mask
+                        q = state & 0xFF
+                    row[block * 34 + 2 + i] = q & 0xFF
+            x = np.sin(np.arange(width, dtype=np.float32) * np.float32(0.013)).astype(np.float32) * np.float32(0.01)
+            got = float(b.qualification_matvec(row, x, 1, width)[0])
+            ref = rc["expected_scalar"]
+            assert abs(got - ref) <= g["abs_tol"] + abs(ref) * g["rel_tol"], rc
+
+
+# ------------------------------------------------------------------------ expert forward
+
+SHAPES = [(oracle.Q8_0, 32, 32), (oracle.Q8_0, 128, 96), (oracle.Q8_0, 37, 45), (oracle.Q8_0, 64, 45),
+          (oracle.Q8_0, 37, 64), (oracle.Q4_0, 32, 64), (oracle.Q4_0, 256, 512), (oracle.Q8_0, 512, 256),
+          (oracle.Q4_0, 1024, 2816), (oracle.Q8_0, 2048, 768)]
+
+
+@pytest.mark.parametrize("dtype,D,F", SHAPES)
+@pytest.mark.parametrize("n_tokens", [1, 5])
+def test_expert_forward_f32_matches_oracle(dtype, D, F, n_tokens):
+    if dtype == oracle.Q8_0 and D < 512:
+        blob = oracle.randomized_q8_expert(D, F, 0x51A1A11E)  # the reference's own fixture generator
+    else:
+        blob = random_blob(dtype, D, F, 7)
+    x = np.stack([oracle.synth_hidden_state(9 + t, D, 3) for t in range(n_tokens)])
+    with backend(dtype, D, F, max_tokens=8) as b:
+        b.admit(1, 1, blob)
+        got = b.expert_forward_f32(0, 1, x)
+        for t in range(n_tokens):
+            ref = oracle.expert_forward(dtype, blob, x[t], D, F, oracle.FWD_AUTHORITATIVE)
+            exact = oracle.expert_forward(dtype, blob, x[t], D, F, oracle.FWD_F64)
+            assert rel_rms_err(got[t], ref) <= FFN_TOL
+            assert rel_rms_err(got[t], exact) <= FFN_TOL
+            # the reference's own Q8 direct-vs-dequant tolerance (inference.rs:5967-5981)
+            assert (np.abs(got[t] - ref) <= 3e-3 * np.maximum(np.abs(ref), 1.0) + 3e-5).all()
+
+
+@pytest.mark.parametrize("path", [1, 2])
+def test_kernel_families_agree(path):
+    D, F = 512, 1024
+    blob = random_blob(oracle.Q4_0, D, F, 11)
+    x = synth.make_activations(6, D, 11)
+    with backend(oracle.Q4_0, D, F, max_tokens=8) as b:
+        b.admit(0, 1, blob)
+        try:
+            b.set_kernel_path(path)
+        except mer_b200.GpuExpertDispatchError as e:
+            assert e.kind == Kind.Ineligible
+            pytest.skip("streaming kernels not built for this shape")
+        got = b.expert_forward_f32(0, 0, x)
+    for t in range(6):
+        assert rel_rms_err(got[t], oracle.expert_forward(oracle.Q4_0, blob, x[t], D, F)) <= FFN_TOL
+
+
+def test_complete_expert_f16_boundary(golden):
+    # q4_parity.rs:574-589 inputs, tolerance 2e-3 + 5e-3*|cpu_f16| at the f16 boundary (q4_parity.rs:33-34)
+    g = golden["q4_complete_expert"]
+    D, F = g["d_model"], g["d_ff"]
+    blob = np.array(g["blob"], np.uint8)
+    with backend(oracle.Q4_0, D, F) as b:
+        b.admit(2, 7, blob)
+        for x in g["inputs"]:
+            xh = np.array(x, np.float32).astype(np.float16)
+            got = b.routed_expert_matmul(0, 2, xh, D, F).astype(np.float32)
+            ref = oracle.expert_forward(oracle.Q4_0, blob, xh.astype(np.float32), D, F).astype(np.float16).astype(np.float32)
+            assert (np.abs(got - ref) <= g["abs_tol_f16_boundary"] + g["rel_tol_f16_boundary"] * np.abs(ref)).all()
+
+
+def test_swiglu_limit_clamps_the_gate():
+    # inference.rs:86-112, swiglu.wgsl:23-27
+    D, F = 64, 64
+    blob = oracle.randomized_q8_expert(D, F, 3)
+    x = oracle.synth_hidden_state(1, D, 1) * 40.0
+    with backend(oracle.Q8_0, D, F, swiglu_limit=0.05) as b:
+        b.admit(0, 1, blob)
+        got = b.expert_forward_f32(0, 0, x)[0]
+    ref = oracle.expert_forward(oracle.Q8_0, blob, x, D, F, swiglu_limit=0.05)
+    unclamped = oracle.expert_forward(oracle.Q8_0, blob, x, D, F)
+    assert rel_rms_err(got, ref) <= FFN_TOL and rel_rms_err(unclamped, ref) > 0.01
+
+
+def test_nan_activation_propagates():
+    # inference.rs:6215-6245
+    D, F = 64, 32
+    blob = oracle.randomized_q8_expert(D, F, 3)
+    x = oracle.synth_hidden_state(1, D, 1)
+    x[5] = np.nan
+    with backend(oracle.Q8_0, D, F) as b:
+        b.admit(0, 1, blob)
+        assert np.isnan(b.expert_forward_f32(0, 0, x)).all()
+
+
+# ------------------------------------------------------------------------------- router
+
+def _golden_gate(c):
+    return mer_b200.LinearGate.with_routing(
+        c["weights"], c["num_experts"], c["d_model"], c["top_k"],
+        mer_b200.ScoringFunc.Sigmoid if c.get("scoring") == "sigmoid" else mer_b200.ScoringFunc.Softmax,
+        c.get("normalise_topk", True), c.get("correction_bias"), c.get("n_group", 1), c.get("topk_group", 1),
+        c.get("routed_scaling_factor", 1.0))
+
+
+def test_router_cases(golden):
+    # every case of gating.rs:527-911 on the device router
+    for c in golden["router_cases"]:
+        with backend(oracle.Q8_0, c["d_model"], 32, max_experts=64) as b:
+            dec = _golden_gate(c).bind(b, 0).route(c["x"])
+        assert dec.experts.tolist() == c["experts"], c["name"]
+        if "weights_expected" in c:
+            assert np.abs(dec.weights - np.array(c["weights_expected"])).max() < max(c["tol"], 2e-7), c["name"]
+        if "weight_sum" in c:
+            assert abs(float(dec.weights.sum()) - c["weight_sum"]) < c.get("tol", 1e-5), c["name"]
+
+
+def test_router_nonfinite_scores():
+    # non-finite selection scores are skipped (gating.rs:315-318); a non-finite softmax row becomes uniform
+    # (transformer.rs:2807-2819) and is reported as a numerical event
+    with backend(oracle.Q8_0, 4, 32, max_experts=64) as b:
+        gate = mer_b200.LinearGate.with_routing(np.eye(4, dtype=np.float32), 4, 4, 2, mer_b200.ScoringFunc.Sigmoid, False,
+                                                [0, float("nan"), 0, 0], 1, 1, 1.0).bind(b, 0)
+        dec = gate.route([1.0, 9.0, 0.5, 0.0])
+        assert dec.experts.tolist() == [0, 2]
+        gate2 = mer_b200.LinearGate(np.eye(4, dtype=np.float32), 4, 4, 4).bind(b, 1)
+        with pytest.raises(mer_b200.GpuExpertDispatchError) as e:
+            gate2.route([1.0, float("nan"), 2.0, 3.0])
+        assert e.value.kind == Kind.Numerical
+
+
+@pytest.mark.parametrize("cfg", ["softmax-128x8", "sigmoid-groups-256x8", "softmax-8x2"])
+def test_router_matches_oracle_on_random_inputs(cfg):
+    rng = np.random.default_rng(17)
+    if cfg == "softmax-128x8":
+        E, D, k, B = 128, 2048, 8, 64
+        args = dict()
+    elif cfg == "softmax-8x2":
+        E, D, k, B = 8, 4096, 2, 16
+        args = dict()
+    else:  # DeepSeek-V3 routing surface (architecture.rs:1378-1385 values)
+        E, D, k, B = 256, 1024, 8, 32
+        args = dict(scoring_func=oracle.SCORE_SIGMOID, correction_bias=rng.normal(0, 0.05, E).astype(np.float32),
+                    n_group=8, topk_group=4, routed_scaling_factor=2.5)
+    W = rng.normal(0, 0.02, (E, D)).astype(np.float32)
+    x = rng.standard_normal((B, D)).astype(np.float32)
+    og = oracle.LinearGate(W, E, D, k, **args)
+    gate = mer_b200.LinearGate.with_routing(W, E, D, k, args.get("scoring_func", 0), True, args.get("correction_bias"),
+                                            args.get("n_group", 1), args.get("topk_group", 1),
+                                            args.get("routed_scaling_factor", 1.0))
+    with backend(oracle.Q8_0, D, 32, max_experts=E, max_tokens=B) as b:
+        gate.bind(b, 0)
+        ids, w = b.route(0, x)
+    checked = 0
+    for t in range(B):
+        rid, rw, scores, gap = og.route(x[t], detail=True)
+        # a different logit summation order can flip near-ties: those tokens are tie-ambiguous, not failures
+        sel = np.sort(scores[rid] + (args["correction_bias"][rid] if "correction_bias" in args else 0))
+        if gap < 1e-6 * abs(sel[0]) or (np.diff(sel) < 1e-6 * np.abs(sel[1:])).any():
+            continue
+        checked += 1
+        assert ids[t].tolist() == rid.tolist()
+        assert np.abs(w[t] - rw).max() <= 2e-6 * max(1.0, float(np.abs(rw).max()))
+    assert checked >= B * 3 // 4
+
+
+# ---------------------------------------------------------------------------- full layer
+
+LAYERS = [("q4-8x2", oracle.Q4_0, 8, 256, 512, 2, 16), ("q8-16x4", oracle.Q8_0, 16, 128, 96, 4, 9),
+          ("q8-128x8", oracle.Q8_0, 128, 512, 256, 8, 24)]
+
+
+@pytest.mark.parametrize("name,dtype,E,D,F,k,B", LAYERS)
+def test_moe_layer_forward_matches_oracle(name, dtype, E, D, F, k, B):
+    blobs = [random_blob(dtype, D, F, 21, e) for e in range(E)]
+    W = synth.make_router(E, D, 21)
+    x = synth.make_activations(B, D, 21)
+    layer = 2
+    with backend(dtype, D, F, n_experts=E, max_experts=3 * E, max_tokens=32, max_top_k=k) as b:
+        for e in range(E):
+            b.admit(layer * E + e, 1, blobs[e])
+        mer_b200.LinearGate(W, E, D, k).bind(b, layer)
+        out, ids, w = b.moe_layer_forward(layer, x)
+        snap = b.snapshot()
+    ref, rids, rw, gaps = oracle.moe_layer_forward(dtype, oracle.LinearGate(W, E, D, k), blobs, x, F, n_threads=8)
+    assert (ids == rids).all(), "top-k expert indices must be identical"
+    assert np.abs(w - rw).max() <= 2e-6
+    assert rel_rms_err(out, ref) <= FFN_TOL
+    assert snap["gpu_dispatch_attempts"] == snap["gpu_dispatch_successes"] == B * k
+
+
+def test_layer_forward_is_invariant_to_batching_and_token_order():
+    # the token->expert permute must not change any token's result (the reference runs one token at a time)
+    dtype, E, D, F, k, B = oracle.Q8_0, 16, 256, 256, 4, 12
+    blobs = [random_blob(dtype, D, F, 33, e) for e in range(E)]
+    W = synth.make_router(E, D, 33)
+    x = synth.make_activations(B, D, 33)
+    perm = np.random.default_rng(0).permutation(B)
+    with backend(dtype, D, F, n_experts=E, max_tokens=16, max_top_k=k) as b:
+        for e in range(E):
+            b.admit(e, 1, blobs[e])
+        mer_b200.LinearGate(W, E, D, k).bind(b, 0)
+        full, ids, w = b.moe_layer_forward(0, x)
+        shuffled, _, _ = b.moe_layer_forward(0, x[perm])
+        assert (shuffled.view(np.uint32) == full[perm].view(np.uint32)).all()
+        for t in range(B):
+            single, sid, sw = b.moe_layer_forward(0, x[t])
+            assert (single[0].view(np.uint32) == full[t].view(np.uint32)).all()
+            # and equals the engine-style call with the routing supplied (engine.rs:5174)
+            step = b.moe_step_weighted_into(0, x[t], ids[t], w[t])
+            assert (step.view(np.uint32) == full[t].view(np.uint32)).all()
+
+
+def test_shared_expert_and_deepseek_routing():
+    # sigmoid + groups + scaling 2.5 + always-on shared expert (transformer.rs:2094-2238, model.rs:2758-2763)
+    dtype, E, D, F, k, B = oracle.Q4_0, 32, 256, 128, 4, 7
+    rng = np.random.default_rng(5)
+    blobs = [random_blob(dtype, D, F, 44, e) for e in range(E + 1)]
+    W = synth.make_router(E, D, 44)
+    bias = rng.normal(0, 0.05, E).astype(np.float32)
+    x = synth.make_activations(B, D, 44)
+    og = oracle.LinearGate(W, E, D, k, scoring_func=oracle.SCORE_SIGMOID, correction_bias=bias, n_group=4, topk_group=2,
+                           routed_scaling_factor=2.5)
+    with backend(dtype, D, F, n_experts=E + 1, max_experts=64, max_tokens=8, max_top_k=k + 1) as b:
+        for e in range(E + 1):
+            b.admit(e, 1, blobs[e])
+        mer_b200.LinearGate.with_routing(W, E, D, k, 1, True, bias, 4, 2, 2.5).bind(b, 0, shared_expert_id=E)
+        out, ids, w = b.moe_layer_forward(0, x)
+    ref, rids, rw, _ = oracle.moe_layer_forward(dtype, og, blobs[:E], x, F, shared_blob=blobs[E], n_threads=4)
+    assert (ids == rids).all() and np.abs(w - rw).max() <= 5e-6
+    assert rel_rms_err(out, ref) <= FFN_TOL
+
+
+# -------------------------------------------------------------- boundary semantics, residency
+
+def test_batch_preserves_duplicates_zero_weights_and_accounting():
+    # engine.rs:6590-6608: duplicate ids and zero weights still dispatch 8 logical experts in one call
+    D, F = 32, 32
+    with backend(oracle.Q4_0, D, F, n_experts=8) as b:
+        for e in range(8):
+            b.admit(e, 1, random_blob(oracle.Q4_0, D, F, 9, e))
+        x = np.ones(D, np.float16)
+        experts = [1, 1, 2, 3, 4, 5, 6, 7]
+        outcome, out, err = b.routed_expert_matmul_batch_q4(0, experts, x, D, F)
+        assert outcome == Outcome.Completed and err is None and out.shape == (8, D)
+        assert (out[0] == out[1]).all()
+        singles = np.stack([b.routed_expert_matmul(0, e, x, D, F) for e in experts])
+        assert (singles.view(np.uint16) == out.view(np.uint16)).all()
+        before = b.snapshot()
+        weights = np.array([0.5, 0.0, 0.25, 0.125, 0.0625, 0.03125, 0.015625, 0.015625], np.float32)
+        step = b.moe_step_weighted_into(0, np.ones(D, np.float32), experts, weights)
+        after = b.snapshot()
+        assert after["gpu_dispatch_attempts"] - before["gpu_dispatch_attempts"] == 8
+        assert after["gpu_dispatch_successes"] - before["gpu_dispatch_successes"] == 8
+        assert after["batch_calls"] - before["batch_calls"] == 1
+        ys = np.stack([oracle.expert_forward(oracle.Q4_0, random_blob(oracle.Q4_0, D, F, 9, e), np.ones(D, np.float32), D, F)
+                       for e in experts])
+        assert rel_rms_err(step, oracle.combine(ys.reshape(-1), weights, skip_zero=True)) <= FFN_TOL
+        # ordered f16 aggregation of the batch output (engine.rs:1651-1673)
+        agg = oracle.accumulate_ordered_f16(out.view(np.uint16).reshape(-1), weights, D)
+        assert rel_rms_err(agg, step) <= 5e-3
+
+
+def test_ineligible_batch_runs_nothing():
+    # engine.rs:6610-6622: Ineligible leaves the caller on its scalar path; nothing is counted as dispatched
+    D, F = 32, 32
+    with backend(oracle.Q4_0, D, F, n_experts=4, max_top_k=4) as b:
+        for e in range(4):
+            b.admit(e, 1, random_blob(oracle.Q4_0, D, F, 9, e))
+        outcome, out, err = b.routed_expert_matmul_batch_q4(0, [0, 1, 2, 3, 0, 1], np.ones(D, np.float16), D, F)
+        assert outcome == Outcome.Ineligible and out is None
+        assert b.snapshot()["gpu_dispatch_attempts"] == 0
+
+
+def test_strict_failure_is_typed_counted_once_and_not_replayed():
+    # engine.rs:6624-6642: the typed kind surfaces with the caller's layer and first failing expert id
+    D, F = 32, 32
+    with backend(oracle.Q4_0, D, F, n_experts=4) as b:
+        for e in (0, 1, 2):
+            b.admit(e, 1, random_blob(oracle.Q4_0, D, F, 9, e))
+        outcome, out, err = b.routed_expert_matmul_batch_q4(4, [0, 1, 9, 2], np.ones(D, np.float16), D, F)
+        assert outcome == Outcome.Failed and err.kind == Kind.ResidencyMiss and err.layer == 4 and err.expert_id == 9
+        snap = b.snapshot()
+        assert snap["gpu_dispatch_attempts"] == 4 and snap["gpu_dispatch_failures"] == 4 and snap["gpu_dispatch_successes"] == 0
+        with pytest.raises(mer_b200.GpuExpertDispatchError) as e:  # wrong shape -> validation, like plan_expert_upload
+            b.routed_expert_matmul(0, 0, np.ones(D, np.float16), D, F + 32)
+        assert e.value.kind == Kind.ValidationDispatch
+
+
+def test_layer_forward_reports_a_missing_expert_from_the_device():
+    dtype, E, D, F, k = oracle.Q8_0, 4, 64, 64, 4
+    with backend(dtype, D, F, n_experts=E, max_top_k=k) as b:
+        for e in range(E - 1):  # expert 3 never admitted; top_k == E routes to it
+            b.admit(e, 1, random_blob(dtype, D, F, 1, e))
+        mer_b200.LinearGate(synth.make_router(E, D, 1), E, D, k).bind(b, 0)
+        with pytest.raises(mer_b200.GpuExpertDispatchError) as e:
+            b.moe_layer_forward(0, synth.make_activations(2, D, 1))
+        assert e.value.kind == Kind.ResidencyMiss and e.value.device_status & 1
+
+
+def test_vram_tier_generations_lru_eviction_and_anchor():
+    # expert_cache.rs:1281-1340 (LRU edge, anchors untouched), backend/mod.rs:3884-3912 (generation checks)
+    D, F = 64, 32
+    blobs = {e: oracle.randomized_q8_expert(D, F, 100 + e) for e in range(5)}
+    x = oracle.synth_hidden_state(0, D, 0)
+    with backend(oracle.Q8_0, D, F, n_experts=3, slots=3, max_experts=16) as b:
+        b.admit(0, 1, blobs[0], anchor=True)
+        b.admit(1, 1, blobs[1])
+        b.admit(2, 1, blobs[2])
+        assert b.snapshot()["slot_count"] == 3 and b.contains_generation(1, 1) and not b.contains_generation(1, 2)
+        b.expert_forward_f32(0, 1, x)            # touch 1 so that 2 is the LRU victim
+        b.admit(3, 1, blobs[3])                  # evicts 2
+        assert not b.contains_generation(2, 1) and b.contains_generation(1, 1) and b.contains_generation(0, 1)
+        with pytest.raises(mer_b200.GpuExpertDispatchError) as e:
+            b.expert_forward_f32(0, 2, x)
+        assert e.value.kind == Kind.ResidencyMiss and e.value.expert_id == 2
+        b.admit(4, 1, blobs[4])                  # evicts 1 (3 is newer, 0 is an anchor)
+        assert b.contains_generation(0, 1) and not b.contains_generation(1, 1)
+        assert b.snapshot()["evictions"] == 2
+        # a newer generation replaces the payload; an older one is a stale requester
+        b.admit(3, 2, blobs[1])
+        got = b.expert_forward_f32(0, 3, x)[0]
+        assert rel_rms_err(got, oracle.expert_forward(oracle.Q8_0, blobs[1], x, D, F)) <= FFN_TOL
+        with pytest.raises(mer_b200.GpuExpertDispatchError) as e:
+            b.admit(3, 1, blobs[3])
+        assert e.value.kind == Kind.ResidencyMiss
+        with pytest.raises(mer_b200.GpuExpertDispatchError) as e:  # truncated payload -> upload error
+            b.admit(5, 1, blobs[0][:-1])
+        assert e.value.kind == Kind.Upload
+        b.retire(3, 2)
+        assert not b.contains_generation(3, 2)
+        ledger = b.snapshot()
+        assert ledger["expert_upload_bytes"] == ledger["expert_uploads"] * blobs[0].size
+
+
+def test_concurrent_callers_get_bit_equal_results():
+    # inference.rs:6247-6277: 4 threads over one expert, deterministic and bit-equal
+    import threading
+    D, F = 128, 96
+    blob = oracle.randomized_q8_expert(D, F, 5)
+    x = oracle.synth_hidden_state(3, D, 3)
+    with backend(oracle.Q8_0, D, F) as b:
+        b.admit(0, 1, blob)
+        base = b.expert_forward_f32(0, 0, x)
+        results = [None] * 4
+
+        def work(i):
+            results[i] = [b.expert_forward_f32(0, 0, x) for _ in range(8)]
+        threads = [threading.Thread(target=work, args=(i,)) for i in range(4)]
+        [t.start() for t in threads]
+        [t.join() for t in threads]
+        for rs in results:
+            for r in rs:
+                assert (r.view(np.uint32) == base.view(np.uint32)).all()
+
+
+# ------------------------------------------------------------- full-size configurations
+
+def test_full_size_qwen3_layer_properties_and_spot_check():
+    # BASELINE config 1 at full size: D=2048, F=768, E=128, k=8, Q8_0, seed 1, batches 1/8/64
+    cfg = synth.CONFIGS["cfg1-qwen3-q8_0"]
+    E, D, F, k = cfg.num_experts, cfg.d_model, cfg.d_ff, cfg.top_k
+    blobs = [synth.make_expert_blob(cfg.dtype, D, F, cfg.seed, 0, e) for e in range(E)]
+    W = synth.make_router(E, D, cfg.seed)
+    x = synth.make_activations(64, D, cfg.seed)
+    with backend(cfg.dtype, D, F, n_experts=E, max_experts=E, max_tokens=64, max_top_k=k) as b:
+        for e in range(E):
+            b.admit(e, 1, blobs[e])
+        mer_b200.LinearGate(W, E, D, k).bind(b, 0)
+        out64, ids, w = b.moe_layer_forward(0, x)
+        out8, _, _ = b.moe_layer_forward(0, x[:8])
+        out1, _, _ = b.moe_layer_forward(0, x[:1])
+    assert (out8.view(np.uint32) == out64[:8].view(np.uint32)).all() and (out1.view(np.uint32) == out64[:1].view(np.uint32)).all()
+    assert np.isfinite(out64).all() and len(np.unique(ids)) > 100  # ~125.9 of 128 experts expected at B=64
+    ref, rids, rw, gaps = oracle.moe_layer_forward(cfg.dtype, oracle.LinearGate(W, E, D, k), blobs, x[:4], F, n_threads=4)
+    assert (ids[:4] == rids).all()
+    assert rel_rms_err(out64[:4], ref) <= FFN_TOL
+
+
+def test_full_size_mixtral_expert_spot_check():
+    # BASELINE config 0 at full size: D=4096, F=14336, Q4_0, seed 0; one expert, batch 1 and 4
+    cfg = synth.CONFIGS["cfg0-mixtral-q4_0"]
+    D, F = cfg.d_model, cfg.d_ff
+    blob = synth.make_expert_blob(cfg.dtype, D, F, cfg.seed, 0, 0)
+    x = synth.make_activations(4, D, cfg.seed)
+    with backend(cfg.dtype, D, F, n_experts=1, max_tokens=4) as b:
+        b.admit(0, 1, blob)
+        got = b.expert_forward_f32(0, 0, x)
+        one = b.expert_forward_f32(0, 0, x[0])
+        w0 = b.dequant_projection(0, 2)
+    assert (one[0].view(np.uint32) == got[0].view(np.uint32)).all()
+    proj = oracle.projection_bytes(cfg.dtype, D, F)
+    assert (w0.view(np.uint32) == oracle.dequant_stream(cfg.dtype, blob[2 * proj:], D * F).view(np.uint32)).all()
+    ref = oracle.expert_forward(cfg.dtype, blob, x[0], D, F, oracle.FWD_SIMD8X4)
+    assert rel_rms_err(got[0], ref) <= FFN_TOL
