@@ -1,7 +1,659 @@
-// Streaming tensor-core expert FFN (placeholder until the kernels land: reports "unsupported"
-// so every dispatch takes the generic path).
+// Streaming expert FFN for decode-sized token groups (a few tokens per expert): HBM-bound.
+//
+// Data flow per projection phase (gate/up, then down):
+//   * Raw Q4_0 / Q8_0 row segments are copied global -> shared memory by bulk async copies
+//     (cp.async.bulk, completion on an mbarrier) through a multi-stage ring: every byte of an
+//     expert is read from HBM once, 16-byte aligned and fully coalesced.
+//   * Warps unpack the integer part of the weights straight into f16 mma.sync A fragments.  A
+//     4-bit or 8-bit field masked into the low mantissa bits of an f16 IS the subnormal value
+//     q * 2^-24 (q * 2^-20 for a field at bits 4..7), so unpacking is one LOP3 per two weights and
+//     the integers are exact.  The zero point (8 for Q4_0, 128 for the sign-flipped Q8_0 byte) is
+//     folded in as the accumulator's initial value -zp * sum(x_block).
+//   * Activations are pre-split into f16 hi + lo parts (22+ significant bits) after an exact
+//     power-of-two per-token scaling; hi and lo are two columns of the n=8 MMA tile, so one tile
+//     carries 4 tokens.  Products are exact, accumulation is fp32 in the tensor core.
+//   * The per-block f16 scale d is applied in fp32 when a block's partial is folded into the row
+//     accumulator: acc += d * partial (the ordering of matmul_q4_0.wgsl:65-85 in the reference).
+//
+// Work is cut into items (token pass, K split, 16-row-slot tile pair); each persistent CTA takes a
+// contiguous item range, so a CTA reloads activation fragments only when its (pass, K split)
+// changes and no atomics or inter-CTA waits are needed.  Every mbarrier wait is bounded: on
+// expiry the CTA latches MER_DEVSTAT_TIMEOUT, drains its own copies in flight and returns.
 #include "kernels.h"
 
-bool stream_ffn_supported(int, uint32_t, uint32_t) { return false; }
-size_t stream_ffn_scratch_bytes(uint32_t, uint32_t, uint32_t) { return 0; }
-cudaError_t launch_ffn_stream(const MoeDispatch &, void *, int, cudaStream_t, int *, cudaEvent_t) { return cudaErrorNotSupported; }
+#include <cuda_fp16.h>
+
+#include "../../include/mer_b200.h"
+
+namespace {
+
+constexpr int CONSUMER_WARPS = 8;
+constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;  // + one producer warp
+constexpr int ROWCHUNKS = 32;                       // row segments per stage: 2 M-tiles x 16 row slots
+constexpr int KSPLIT_WARPS = CONSUMER_WARPS / 2;    // warps that split the K range of one M-tile
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr float POW2_24 = 16777216.0f;
+
+struct StreamParams {
+  MoeDispatch d;
+  int phase;                 // 0 = gate/up (+SiLU*mul), 1 = down
+  const uint16_t *afrag;     // [n_act][2 parts][kb_total][32] f16, fragment order
+  const float *ainit;        // [n_act][kb_total]  -zp * 2^-24 * sum of the block's scaled activations
+  const float *aunscale;     // [n_act]  2^24 / s  (s = the activation's power-of-two scale)
+  uint32_t act_per_pair;     // 1: activations indexed by pair (down); 0: by token = pair / slots (gate/up)
+  uint32_t rows;             // output rows of the projection (F for gate/up, D for down)
+  uint32_t kb_total;         // 32-weight blocks per row
+  uint32_t kb_split;         // blocks per K split (kb_total when n_ksplit == 1)
+  uint32_t n_ksplit;
+  uint32_t kc;               // blocks per pipeline stage
+  uint32_t n_stages;
+  uint32_t row_stride;       // bytes between row segments in a stage (padded against bank conflicts)
+  uint32_t frag_stride;      // bytes between (token, part) fragment arrays in shared memory
+  uint32_t tokens_per_pass;  // 4 * NT
+  const uint32_t *n_passes;  // device scalar
+  const uint32_t *pass_group, *pass_start, *pass_count;
+  float *out;                // phase 0: h [P x F];  phase 1: y partials [n_ksplit][P x D]
+  uint32_t *amax;            // phase 0: per-pair max |h| as float bits (for the down phase's scaling)
+};
+
+// ----------------------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait: false when the phase did not complete within SPIN_LIMIT polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < SPIN_LIMIT; i++) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+
+// ------------------------------------------------------------------- activation fragments
+// Position of block element j in the per-block fragment order, and the extra exact scale of
+// that slot (Q4_0 high nibbles sit 4 mantissa bits higher, so their activations carry 2^-4).
+template <int DT>
+__device__ __forceinline__ void frag_slot(uint32_t j, uint32_t &pos, float &slot_scale) {
+  if (DT == MER_DTYPE_Q4_0) {
+    uint32_t hi = j >> 4, jj = j & 15u, t = jj >> 2, e = jj & 3u;
+    // thread t order: [4t, 4t+2, 4t+1, 4t+3 | same +16]
+    uint32_t within = (e == 0) ? 0 : (e == 2) ? 1 : (e == 1) ? 2 : 3;
+    pos = t * 8 + hi * 4 + within;
+    slot_scale = hi ? 0.0625f : 1.0f;
+  } else {
+    uint32_t t = j >> 3, e = j & 7u, half = e >> 2, ee = e & 3u;
+    uint32_t within = (ee == 0) ? 0 : (ee == 2) ? 1 : (ee == 1) ? 2 : 3;
+    pos = t * 8 + half * 4 + within;
+    slot_scale = 1.0f;
+  }
+}
+
+// One CTA per activation row: exact power-of-two scaling so that max |a| lands in [256, 512),
+// f16 hi/lo split in fragment order, and the per-block accumulator seed.
+template <int DT>
+__global__ void __launch_bounds__(256) k_act_prep(const float *__restrict__ a, uint32_t K, const uint32_t *__restrict__ amax_bits,
+                                                  uint16_t *__restrict__ frag, float *__restrict__ init,
+                                                  float *__restrict__ unscale) {
+  const uint32_t row = blockIdx.x;
+  const float *src = a + (size_t)row * K;
+  __shared__ float s_red[8];
+  __shared__ float s_scale;
+  float mx;
+  if (amax_bits) {
+    mx = __uint_as_float(amax_bits[row]);
+  } else {
+    mx = 0.0f;
+    for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) {
+      float v = fabsf(src[i]);
+      mx = (v > mx || v != v) ? v : mx;  // NaN sticks
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float other = __shfl_xor_sync(0xffffffffu, mx, o);
+      mx = (other > mx || other != other) ? other : mx;
+    }
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < 8; w++) mx = (s_red[w] > mx || s_red[w] != s_red[w]) ? s_red[w] : mx;
+      s_red[0] = mx;
+    }
+    __syncthreads();
+    mx = s_red[0];
+  }
+  if (threadIdx.x == 0) {
+    float s = 1.0f;
+    if (mx > 0.0f && isfinite(mx)) {
+      int e;
+      frexpf(mx, &e);             // mx = m * 2^e, m in [0.5, 1)
+      s = ldexpf(1.0f, 9 - e);    // mx * s in [256, 512)
+    } else if (mx != mx || isinf(mx)) {
+      s = mx;  // non-finite activations poison the row, as they would in fp32
+    }
+    s_scale = s;
+    unscale[row] = POW2_24 / s;
+  }
+  __syncthreads();
+  const float s = s_scale;
+  const uint32_t KB = K / 32;
+  const float zp = DT == MER_DTYPE_Q4_0 ? 8.0f : 128.0f;
+  uint16_t *hi_dst = frag + (size_t)row * 2 * K;
+  uint16_t *lo_dst = hi_dst + K;
+  // one warp per block: lane j handles element j
+  for (uint32_t kb = threadIdx.x >> 5; kb < KB; kb += blockDim.x >> 5) {
+    uint32_t j = threadIdx.x & 31;
+    float v = src[kb * 32 + j] * s;  // exact (power of two) unless it overflows
+    uint32_t pos;
+    float ss;
+    frag_slot<DT>(j, pos, ss);
+    float vs = v * ss;
+    __half h = __float2half_rn(vs);
+    __half l = __float2half_rn(vs - __half2float(h));
+    hi_dst[kb * 32 + pos] = __half_as_ushort(h);
+    lo_dst[kb * 32 + pos] = __half_as_ushort(l);
+    float sum = v;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (j == 0) init[(size_t)row * KB + kb] = -zp * sum * (1.0f / POW2_24);
+  }
+}
+
+// ------------------------------------------------------------------------ weight unpacking
+// Eight weights of one row of one block -> four f16x2 registers holding the integer fields as
+// subnormals: {MMA0.k(2t,2t+1), MMA0.k(2t+8,2t+9), MMA1.k(2t,2t+1), MMA1.k(2t+8,2t+9)}.
+template <int DT>
+__device__ __forceinline__ void unpack_row(const uint8_t *blk, uint32_t t, uint32_t (&r)[4]) {
+  if (DT == MER_DTYPE_Q4_0) {
+    // bytes 2 + 4t .. 2 + 4t + 3: low nibbles = elements 4t..4t+3, high nibbles = 16 + the same
+    const uint8_t *p = blk + 2 + 4 * t;
+    uint32_t mis = (uint32_t)(size_t)p & 3u;  // 0 or 2
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(p - mis);
+    uint32_t v = __funnelshift_r(w[0], w[1], mis * 8);
+    uint32_t v8 = v >> 8;
+    r[0] = v & 0x000F000Fu;
+    r[2] = v & 0x00F000F0u;
+    r[1] = v8 & 0x000F000Fu;
+    r[3] = v8 & 0x00F000F0u;
+  } else {
+    const uint8_t *p = blk + 2 + 8 * t;
+    uint32_t mis = (uint32_t)(size_t)p & 3u;
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(p - mis);
+    uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
+    uint32_t lo = __funnelshift_r(w0, w1, mis * 8), hi = __funnelshift_r(w1, w2, mis * 8);
+    lo ^= 0x80808080u;  // int8 -> biased unsigned byte (q + 128)
+    hi ^= 0x80808080u;
+    r[0] = lo & 0x00FF00FFu;
+    r[1] = (lo >> 8) & 0x00FF00FFu;
+    r[2] = hi & 0x00FF00FFu;
+    r[3] = (hi >> 8) & 0x00FF00FFu;
+  }
+}
+
+template <int DT>
+struct BlockBytes {
+  static constexpr uint32_t value = DT == MER_DTYPE_Q4_0 ? MER_Q4_BLOCK_BYTES : MER_Q8_BLOCK_BYTES;
+};
+
+// --------------------------------------------------------------------------- main kernel
+template <int DT, int NT>
+__global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr uint32_t BB = BlockBytes<DT>::value;
+  constexpr uint32_t TP = 4 * NT;
+  const MoeDispatch &d = p.d;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // shared memory carve-up
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem);  // [n_stages]
+  uint64_t *empty = full + p.n_stages;                   // [n_stages]
+  uint64_t *actbar = empty + p.n_stages;                 // [1]
+  uint32_t *s_abort = reinterpret_cast<uint32_t *>(actbar + 1);
+  float *s_red = reinterpret_cast<float *>(smem + 256);                     // [8 warps][NT][4][32]
+  float *s_init = s_red + CONSUMER_WARPS * NT * 128;                        // [kb_split][TP]
+  uint8_t *s_frag = reinterpret_cast<uint8_t *>(s_init + p.kb_split * TP);  // [TP*2][frag_stride]
+  s_frag = reinterpret_cast<uint8_t *>(((size_t)s_frag + 127) & ~(size_t)127);
+  uint8_t *s_stage = s_frag + (size_t)TP * 2 * p.frag_stride;               // [n_stages][32 * row_stride + 128]
+  const uint32_t stage_bytes = ROWCHUNKS * p.row_stride + 128;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < p.n_stages; s++) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], CONSUMER_WARPS);
+    }
+    mbar_init(actbar, 1);
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  const uint32_t n_tiles = p.rows / (p.phase == 0 ? 16u : 32u);
+  const uint32_t n_passes = *p.n_passes;
+  const uint64_t n_items = (uint64_t)n_passes * p.n_ksplit * n_tiles;
+  const uint64_t item_beg = n_items * blockIdx.x / gridDim.x, item_end = n_items * (blockIdx.x + 1) / gridDim.x;
+  if (item_beg >= item_end) return;
+  const size_t proj_bytes = (size_t)d.D * d.F / 32 * BB;
+  const size_t row_bytes = (size_t)p.kb_total * BB;
+
+  auto decode = [&](uint64_t item, uint32_t &pp, uint32_t &ks, uint32_t &tile) {
+    tile = (uint32_t)(item % n_tiles);
+    uint64_t rest = item / n_tiles;
+    ks = (uint32_t)(rest % p.n_ksplit);
+    pp = (uint32_t)(rest / p.n_ksplit);
+  };
+  auto kb_range = [&](uint32_t ks, uint32_t &kb0, uint32_t &kbn) {
+    kb0 = ks * p.kb_split;
+    kbn = min(p.kb_split, p.kb_total - kb0);
+  };
+
+  if (warp == CONSUMER_WARPS) {
+    // ------------------------------ producer warp: lane i copies row segment i of every stage
+    uint32_t stage = 0, round = 0;
+    bool ok = true;
+    for (uint64_t item = item_beg; item < item_end && ok; item++) {
+      uint32_t pp, ks, tile, kb0, kbn;
+      decode(item, pp, ks, tile);
+      kb_range(ks, kb0, kbn);
+      uint32_t eid = d.group_expert[p.pass_group[pp]];
+      const uint8_t *base = (eid < d.max_experts) ? d.expert_ptr[eid] : nullptr;
+      if (!base) continue;  // consumers skip the same item
+      const uint8_t *src;
+      if (p.phase == 0) {
+        uint32_t m = lane >> 4, r = lane & 15;
+        uint32_t row = tile * 16 + m * 8 + (r & 7);
+        src = base + (r >= 8 ? proj_bytes : 0) + (size_t)row * row_bytes;
+      } else {
+        src = base + 2 * proj_bytes + (size_t)(tile * 32 + lane) * row_bytes;
+      }
+      for (uint32_t c0 = 0; c0 < kbn && ok; c0 += p.kc) {
+        uint32_t nb = min(p.kc, kbn - c0);
+        if (round > 0) ok = mbar_wait(&empty[stage], (round - 1) & 1);
+        if (*(volatile uint32_t *)s_abort) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) mbar_expect_tx(&full[stage], ROWCHUNKS * nb * BB);
+        __syncwarp();
+        bulk_g2s(s_stage + (size_t)stage * stage_bytes + lane * p.row_stride, src + (size_t)(kb0 + c0) * BB, nb * BB,
+                 &full[stage]);
+        if (++stage == p.n_stages) stage = 0, round++;
+      }
+    }
+    if (!ok) {
+      if (lane == 0) {
+        *(volatile uint32_t *)s_abort = 1;
+        atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
+      }
+      // drain: give copies already in flight a bounded chance to land before the CTA's memory is released
+      for (uint32_t s = 0; s < p.n_stages; s++) (void)mbar_wait(&full[s], 0), (void)mbar_wait(&full[s], 1);
+    }
+    return;
+  }
+
+  // ---------------------------------------------------------------------- consumer warps
+  const uint32_t g = lane >> 2, t = lane & 3;
+  const uint32_t mtile = warp & 1, kpart = warp >> 1;  // M-tile of the stage, quarter of its K range
+  uint32_t stage = 0, round = 0, act_round = 0;
+  uint32_t cur_pp = MER_NONE, cur_ks = MER_NONE;
+  bool ok = true;
+
+  for (uint64_t item = item_beg; item < item_end; item++) {
+    uint32_t pp, ks, tile, kb0, kbn;
+    decode(item, pp, ks, tile);
+    kb_range(ks, kb0, kbn);
+    const uint32_t grp = p.pass_group[pp], pstart = p.pass_start[pp], pcount = p.pass_count[pp];
+    const uint32_t eid = d.group_expert[grp];
+    const bool resident = eid < d.max_experts && d.expert_ptr[eid] != nullptr;
+
+    if (pp != cur_pp || ks != cur_ks) {
+      // new activation fragments: everyone is done with the old ones, then one thread issues the copies
+      consumer_sync();
+      cur_pp = pp, cur_ks = ks;
+      if (threadIdx.x == 0) {
+        uint32_t bytes_each = kbn * 64;
+        mbar_expect_tx(actbar, pcount * (2 * bytes_each + kbn * 4));
+        for (uint32_t i = 0; i < pcount; i++) {
+          uint32_t pair = d.perm[pstart + i];
+          uint32_t a = p.act_per_pair ? pair : pair / d.slots;
+          const uint16_t *fsrc = p.afrag + (size_t)a * 2 * p.kb_total * 32;
+          bulk_g2s(s_frag + (size_t)(2 * i) * p.frag_stride, fsrc + (size_t)kb0 * 32, bytes_each, actbar);
+          bulk_g2s(s_frag + (size_t)(2 * i + 1) * p.frag_stride, fsrc + (size_t)(p.kb_total + kb0) * 32, bytes_each, actbar);
+          bulk_g2s(s_init + (size_t)i * p.kb_split, p.ainit + (size_t)a * p.kb_total + kb0, kbn * 4, actbar);
+        }
+      }
+      ok = ok && mbar_wait(actbar, act_round & 1);
+      act_round++;
+    }
+    if (*(volatile uint32_t *)s_abort) ok = false;
+    if (!ok) break;
+    if (!resident) {
+      if (threadIdx.x == 0) atomicOr(d.status, MER_DEVSTAT_RESIDENCY_MISS);
+      // fail closed: zero outputs for this tile
+      const uint32_t rows_here = p.phase == 0 ? 16u : 32u;
+      for (uint32_t i = threadIdx.x; i < rows_here * pcount; i += CONSUMER_WARPS * 32) {
+        uint32_t pair = d.perm[pstart + i / rows_here], row = tile * rows_here + i % rows_here;
+        if (p.phase == 0)
+          p.out[(size_t)pair * d.F + row] = 0.0f;
+        else
+          p.out[((size_t)ks * d.n_tokens * d.slots + pair) * d.D + row] = 0.0f;
+      }
+      continue;
+    }
+
+    float acc[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; n++) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+
+    for (uint32_t c0 = 0; c0 < kbn; c0 += p.kc) {
+      const uint32_t nb = min(p.kc, kbn - c0);
+      ok = mbar_wait(&full[stage], round & 1);
+      if (!ok) break;
+      const uint8_t *st = s_stage + (size_t)stage * stage_bytes + (size_t)(mtile * 16) * p.row_stride;
+      const uint8_t *row_lo = st + (size_t)g * p.row_stride, *row_hi = st + (size_t)(g + 8) * p.row_stride;
+      for (uint32_t b = kpart; b < nb; b += KSPLIT_WARPS) {
+        const uint8_t *blo = row_lo + b * BB, *bhi = row_hi + b * BB;
+        uint32_t a_lo[4], a_hi[4];
+        unpack_row<DT>(blo, t, a_lo);
+        unpack_row<DT>(bhi, t, a_hi);
+        float d_lo = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(blo)));
+        float d_hi = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(bhi)));
+        const uint32_t kb_local = c0 + b;
+#pragma unroll
+        for (int n = 0; n < NT; n++) {
+          // column g of this N-tile = (token n*4 + g/2, part g&1)
+          const uint32_t tokpart = n * 8 + g;
+          uint4 bf = make_uint4(0, 0, 0, 0);
+          if ((tokpart >> 1) < pcount)
+            bf = *reinterpret_cast<const uint4 *>(s_frag + (size_t)tokpart * p.frag_stride + kb_local * 64 + t * 16);
+          float c[4];
+          float seed = (n * 4 + t < pcount) ? s_init[(size_t)(n * 4 + t) * p.kb_split + kb_local] : 0.0f;
+          c[0] = seed, c[1] = 0.0f, c[2] = seed, c[3] = 0.0f;
+          mma_f16(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], bf.x, bf.y);
+          mma_f16(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], bf.z, bf.w);
+          acc[n][0] = fmaf(d_lo, c[0], acc[n][0]);
+          acc[n][1] = fmaf(d_lo, c[1], acc[n][1]);
+          acc[n][2] = fmaf(d_hi, c[2], acc[n][2]);
+          acc[n][3] = fmaf(d_hi, c[3], acc[n][3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[stage]);
+      if (++stage == p.n_stages) stage = 0, round++;
+    }
+    if (!ok) break;
+
+    // ---- item epilogue: sum the K-split partials of the four warps of each M-tile, then write
+    consumer_sync();  // s_red free (previous item's readers are done)
+#pragma unroll
+    for (int n = 0; n < NT; n++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) s_red[((warp * NT + n) * 4 + i) * 32 + lane] = acc[n][i];
+    consumer_sync();
+    if (warp < 2) {  // warp m finishes M-tile m
+#pragma unroll
+      for (int n = 0; n < NT; n++) {
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          float s0 = 0.0f;
+#pragma unroll
+          for (int kp = 0; kp < KSPLIT_WARPS; kp++) s0 += s_red[(((kp * 2 + warp) * NT + n) * 4 + i) * 32 + lane];
+          v[i] = s0;
+        }
+        const uint32_t tok = n * 4 + t;
+        if (tok < pcount) {
+          const uint32_t pair = d.perm[pstart + tok];
+          const uint32_t a = p.act_per_pair ? pair : pair / d.slots;
+          const float un = p.aunscale[a];
+          float r_lo = (v[0] + v[1]) * un, r_hi = (v[2] + v[3]) * un;  // rows g and g+8 of the M-tile
+          if (p.phase == 0) {
+            // rows 0..7 are gate rows, rows 8..15 the matching up rows
+            float gate = r_lo;
+            if (d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit) && gate == gate)
+              gate = fminf(fmaxf(gate, -d.swiglu_limit), d.swiglu_limit);
+            float hval = silu_f(gate) * r_hi;
+            uint32_t row = tile * 16 + warp * 8 + g;
+            p.out[(size_t)pair * d.F + row] = hval;
+            float ah = fabsf(hval);
+            uint32_t bits = (ah != ah) ? 0x7fc00000u : __float_as_uint(ah);
+            // max over the 8 rows held by lanes with the same t (xor over g bits)
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
+            if (g == 0) atomicMax(p.amax + pair, bits);
+          } else {
+            float *yo = p.out + ((size_t)ks * d.n_tokens * d.slots + pair) * d.D + tile * 32 + warp * 16;
+            yo[g] = r_lo;
+            yo[g + 8] = r_hi;
+          }
+        } else if (p.phase == 0) {
+          uint32_t bits = 0;
+#pragma unroll
+          for (int o = 4; o < 32; o <<= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
+        }
+      }
+    }
+  }
+  if (!ok) {
+    if (lane == 0) {
+      *(volatile uint32_t *)s_abort = 1;
+      atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
+      // release the producer if it is waiting for this warp
+      for (uint32_t s = 0; s < p.n_stages; s++) mbar_arrive(&empty[s]);
+    }
+  }
+}
+
+// Token passes: every group with tokens is cut into passes of at most tokens_per_pass pairs.
+__global__ void k_build_passes(MoeDispatch d, uint32_t tokens_per_pass, uint32_t *n_passes, uint32_t *pass_group,
+                               uint32_t *pass_start, uint32_t *pass_count, uint32_t *amax, uint32_t n_pairs) {
+  for (uint32_t i = threadIdx.x; i < n_pairs; i += blockDim.x) amax[i] = 0;
+  if (threadIdx.x == 0) {
+    uint32_t np = 0;
+    for (uint32_t g = 0; g < d.n_groups; g++) {
+      uint32_t beg = d.offsets[g], end = d.offsets[g + 1];
+      for (uint32_t s = beg; s < end; s += tokens_per_pass) {
+        pass_group[np] = g;
+        pass_start[np] = s;
+        pass_count[np] = min(tokens_per_pass, end - s);
+        np++;
+      }
+    }
+    *n_passes = np;
+  }
+}
+
+__global__ void k_reduce_ksplit(const float *__restrict__ part, float *__restrict__ y, size_t n, uint32_t n_ksplit) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = part[i];
+  for (uint32_t k = 1; k < n_ksplit; k++) acc += part[(size_t)k * n + i];
+  y[i] = acc;
+}
+
+struct Plan {
+  uint32_t nt, kc, n_stages, row_stride, frag_stride, kb_split, n_ksplit;
+  size_t smem;
+};
+
+constexpr size_t SMEM_LIMIT = 227 * 1024;
+
+// Chooses the K split, stage depth and stage size for one phase so that everything fits in
+// shared memory with at least three stages in flight.
+Plan make_plan(int dtype, uint32_t kb_total, int phase, uint32_t nt) {
+  const uint32_t bb = dtype == MER_DTYPE_Q4_0 ? MER_Q4_BLOCK_BYTES : MER_Q8_BLOCK_BYTES;
+  const uint32_t tp = 4 * nt;
+  Plan best{};
+  // the K split applies to the down phase only (gate/up needs whole rows before SiLU)
+  uint32_t max_split_blocks = phase == 0 ? kb_total : 64u;
+  uint32_t n_ksplit = (kb_total + max_split_blocks - 1) / max_split_blocks;
+  uint32_t kb_split = ((kb_total + n_ksplit - 1) / n_ksplit + 7) / 8 * 8;
+  n_ksplit = (kb_total + kb_split - 1) / kb_split;
+  uint32_t frag_stride = kb_split * 64 + 64;
+  size_t fixed = 256 + (size_t)CONSUMER_WARPS * nt * 128 * 4 + (size_t)kb_split * tp * 4 + 128 + (size_t)tp * 2 * frag_stride;
+  for (uint32_t kc = 64; kc >= 8; kc -= 8) {
+    if (kc > kb_split && kc != 8) continue;
+    uint32_t chunk = kc * bb;
+    uint32_t want = dtype == MER_DTYPE_Q4_0 ? 16u : 32u;  // row stride mod 128 that spreads 8 rows over the banks
+    uint32_t row_stride = chunk + ((want + 128 - chunk % 128) % 128);
+    if (row_stride < chunk + 16) row_stride += 128;  // slack for the aligned over-read of the last words
+    size_t stage = (size_t)ROWCHUNKS * row_stride + 128;
+    if (fixed + 3 * stage > SMEM_LIMIT) continue;
+    uint32_t n_stages = (uint32_t)((SMEM_LIMIT - fixed) / stage);
+    if (n_stages > 6) n_stages = 6;
+    best = Plan{nt, kc, n_stages, row_stride, frag_stride, kb_split, n_ksplit, fixed + n_stages * stage};
+    break;
+  }
+  return best;
+}
+
+uint32_t pick_nt(int dtype, uint32_t D, uint32_t F) {
+  // two N-tiles (8 tokens per pass) when both phases still fit three stages
+  Plan a = make_plan(dtype, D / 32, 0, 2), b = make_plan(dtype, F / 32, 1, 2);
+  return (a.n_stages >= 3 && b.n_stages >= 3) ? 2u : 1u;
+}
+
+struct ScratchLayout {
+  size_t xfrag, xinit, xun, hfrag, hinit, hun, amax, npass, pgroup, pstart, pcount, ypart, total;
+};
+
+ScratchLayout scratch_layout(uint32_t max_pairs, uint32_t D, uint32_t F) {
+  ScratchLayout L{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t o = off;
+    off += (bytes + 255) & ~(size_t)255;
+    return o;
+  };
+  L.xfrag = take((size_t)max_pairs * 2 * D * 2);
+  L.xinit = take((size_t)max_pairs * (D / 32) * 4);
+  L.xun = take((size_t)max_pairs * 4);
+  L.hfrag = take((size_t)max_pairs * 2 * F * 2);
+  L.hinit = take((size_t)max_pairs * (F / 32) * 4);
+  L.hun = take((size_t)max_pairs * 4);
+  L.amax = take((size_t)max_pairs * 4);
+  L.npass = take(256);
+  L.pgroup = take((size_t)max_pairs * 4);
+  L.pstart = take((size_t)max_pairs * 4);
+  L.pcount = take((size_t)max_pairs * 4);
+  uint32_t n_ksplit = (F / 32 + 63) / 64 + 1;
+  L.ypart = take((size_t)n_ksplit * max_pairs * D * 4);
+  L.total = off;
+  return L;
+}
+
+template <int DT>
+cudaError_t launch_phase(const StreamParams &p, uint32_t nt, size_t smem, int grid, cudaStream_t s) {
+  cudaError_t e;
+  if (nt == 2) {
+    e = cudaFuncSetAttribute(k_ffn_stream<DT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    k_ffn_stream<DT, 2><<<grid, THREADS, smem, s>>>(p);
+  } else {
+    e = cudaFuncSetAttribute(k_ffn_stream<DT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    k_ffn_stream<DT, 1><<<grid, THREADS, smem, s>>>(p);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool stream_ffn_supported(int dtype, uint32_t D, uint32_t F) {
+  if (dtype != MER_DTYPE_Q4_0 && dtype != MER_DTYPE_Q8_0) return false;
+  if (D == 0 || F == 0 || D % 256 != 0 || F % 256 != 0) return false;  // 16-byte aligned rows, whole tiles
+  Plan a = make_plan(dtype, D / 32, 0, 1), b = make_plan(dtype, F / 32, 1, 1);
+  return a.n_stages >= 3 && b.n_stages >= 3;
+}
+
+size_t stream_ffn_scratch_bytes(uint32_t max_pairs, uint32_t D, uint32_t F) { return scratch_layout(max_pairs, D, F).total; }
+
+cudaError_t launch_ffn_stream(const MoeDispatch &d, void *scratch, int sm_count, cudaStream_t s, int *launches,
+                              cudaEvent_t ev_mid) {
+  const uint32_t P = d.n_tokens * d.slots;
+  uint8_t *base = static_cast<uint8_t *>(scratch);
+  // the layout is a function of the allocation-time maxima; only offsets matter here
+  static thread_local ScratchLayout L;
+  static thread_local uint32_t L_key[3] = {0, 0, 0};
+  (void)L_key;
+  L = scratch_layout(d.scratch_pairs, d.D, d.F);
+  const uint32_t nt = pick_nt(d.dtype, d.D, d.F);
+  const Plan pg = make_plan(d.dtype, d.D / 32, 0, nt), pd = make_plan(d.dtype, d.F / 32, 1, nt);
+  uint32_t *n_passes = reinterpret_cast<uint32_t *>(base + L.npass);
+  uint32_t *pgroup = reinterpret_cast<uint32_t *>(base + L.pgroup), *pstart = reinterpret_cast<uint32_t *>(base + L.pstart),
+           *pcount = reinterpret_cast<uint32_t *>(base + L.pcount), *amax = reinterpret_cast<uint32_t *>(base + L.amax);
+  cudaError_t e;
+  k_build_passes<<<1, 256, 0, s>>>(d, 4 * nt, n_passes, pgroup, pstart, pcount, amax, P);
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  uint16_t *xfrag = reinterpret_cast<uint16_t *>(base + L.xfrag), *hfrag = reinterpret_cast<uint16_t *>(base + L.hfrag);
+  float *xinit = reinterpret_cast<float *>(base + L.xinit), *xun = reinterpret_cast<float *>(base + L.xun);
+  float *hinit = reinterpret_cast<float *>(base + L.hinit), *hun = reinterpret_cast<float *>(base + L.hun);
+  if (d.dtype == MER_DTYPE_Q4_0)
+    k_act_prep<MER_DTYPE_Q4_0><<<d.n_tokens, 256, 0, s>>>(d.x, d.D, nullptr, xfrag, xinit, xun);
+  else
+    k_act_prep<MER_DTYPE_Q8_0><<<d.n_tokens, 256, 0, s>>>(d.x, d.D, nullptr, xfrag, xinit, xun);
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+
+  StreamParams p{};
+  p.d = d;
+  p.n_passes = n_passes, p.pass_group = pgroup, p.pass_start = pstart, p.pass_count = pcount;
+  p.tokens_per_pass = 4 * nt;
+  // phase 0: gate/up
+  p.phase = 0, p.afrag = xfrag, p.ainit = xinit, p.aunscale = xun, p.act_per_pair = 0;
+  p.rows = d.F, p.kb_total = d.D / 32, p.kb_split = pg.kb_split, p.n_ksplit = pg.n_ksplit, p.kc = pg.kc;
+  p.n_stages = pg.n_stages, p.row_stride = pg.row_stride, p.frag_stride = pg.frag_stride;
+  p.out = d.h, p.amax = amax;
+  e = d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, pg.smem, sm_count, s)
+                                : launch_phase<MER_DTYPE_Q8_0>(p, nt, pg.smem, sm_count, s);
+  if (e != cudaSuccess) return e;
+  if (ev_mid) cudaEventRecord(ev_mid, s);
+  // activations of the down phase: h, scaled per pair by the max the gate/up epilogue collected
+  if (d.dtype == MER_DTYPE_Q4_0)
+    k_act_prep<MER_DTYPE_Q4_0><<<P, 256, 0, s>>>(d.h, d.F, amax, hfrag, hinit, hun);
+  else
+    k_act_prep<MER_DTYPE_Q8_0><<<P, 256, 0, s>>>(d.h, d.F, amax, hfrag, hinit, hun);
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  // phase 1: down
+  float *ypart = pd.n_ksplit > 1 ? reinterpret_cast<float *>(base + L.ypart) : d.y;
+  p.phase = 1, p.afrag = hfrag, p.ainit = hinit, p.aunscale = hun, p.act_per_pair = 1;
+  p.rows = d.D, p.kb_total = d.F / 32, p.kb_split = pd.kb_split, p.n_ksplit = pd.n_ksplit, p.kc = pd.kc;
+  p.n_stages = pd.n_stages, p.row_stride = pd.row_stride, p.frag_stride = pd.frag_stride;
+  p.out = ypart, p.amax = nullptr;
+  e = d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, pd.smem, sm_count, s)
+                                : launch_phase<MER_DTYPE_Q8_0>(p, nt, pd.smem, sm_count, s);
+  if (e != cudaSuccess) return e;
+  int n = 5;
+  if (pd.n_ksplit > 1) {
+    size_t cnt = (size_t)P * d.D;
+    k_reduce_ksplit<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(ypart, d.y, cnt, pd.n_ksplit);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    n++;
+  }
+  if (launches) *launches += n;
+  return cudaSuccess;
+}
