@@ -45,6 +45,7 @@ struct MoeDispatch {
   uint32_t *counters;       // scratch counters: [0..n_tokens) per-token arrivals, [max_tokens] global arrivals
   float *logits;            // [n_tokens x E] scratch
   float swiglu_limit;       // <= 0 = off
+  uint32_t scratch_pairs;   // pair capacity the streaming scratch was sized for
 };
 
 // kernels_generic.cu

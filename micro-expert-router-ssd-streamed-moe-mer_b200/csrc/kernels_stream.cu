@@ -321,7 +321,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   const uint32_t mtile = warp & 1, kpart = warp >> 1;  // M-tile of the stage, quarter of its K range
   uint32_t stage = 0, round = 0, act_round = 0;
   uint32_t cur_pp = MER_NONE, cur_ks = MER_NONE;
-  bool ok = true;
+  // A warp whose bounded wait expired goes "dead": it stops computing and waiting but still walks
+  // the same loop structure, so the named barriers below always see all eight warps.
+  bool dead = false;
 
   for (uint64_t item = item_beg; item < item_end; item++) {
     uint32_t pp, ks, tile, kb0, kbn;
@@ -347,11 +349,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
           bulk_g2s(s_init + (size_t)i * p.kb_split, p.ainit + (size_t)a * p.kb_total + kb0, kbn * 4, actbar);
         }
       }
-      ok = ok && mbar_wait(actbar, act_round & 1);
+      if (!dead && !mbar_wait(actbar, act_round & 1)) dead = true;
+      dead = __any_sync(0xffffffffu, dead);
       act_round++;
     }
-    if (*(volatile uint32_t *)s_abort) ok = false;
-    if (!ok) break;
     if (!resident) {
       if (threadIdx.x == 0) atomicOr(d.status, MER_DEVSTAT_RESIDENCY_MISS);
       // fail closed: zero outputs for this tile
@@ -372,41 +373,42 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
 
     for (uint32_t c0 = 0; c0 < kbn; c0 += p.kc) {
       const uint32_t nb = min(p.kc, kbn - c0);
-      ok = mbar_wait(&full[stage], round & 1);
-      if (!ok) break;
-      const uint8_t *st = s_stage + (size_t)stage * stage_bytes + (size_t)(mtile * 16) * p.row_stride;
-      const uint8_t *row_lo = st + (size_t)g * p.row_stride, *row_hi = st + (size_t)(g + 8) * p.row_stride;
-      for (uint32_t b = kpart; b < nb; b += KSPLIT_WARPS) {
-        const uint8_t *blo = row_lo + b * BB, *bhi = row_hi + b * BB;
-        uint32_t a_lo[4], a_hi[4];
-        unpack_row<DT>(blo, t, a_lo);
-        unpack_row<DT>(bhi, t, a_hi);
-        float d_lo = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(blo)));
-        float d_hi = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(bhi)));
-        const uint32_t kb_local = c0 + b;
+      if (!dead && !mbar_wait(&full[stage], round & 1)) dead = true;
+      dead = __any_sync(0xffffffffu, dead);
+      if (!dead) {
+        const uint8_t *st = s_stage + (size_t)stage * stage_bytes + (size_t)(mtile * 16) * p.row_stride;
+        const uint8_t *row_lo = st + (size_t)g * p.row_stride, *row_hi = st + (size_t)(g + 8) * p.row_stride;
+        for (uint32_t b = kpart; b < nb; b += KSPLIT_WARPS) {
+          const uint8_t *blo = row_lo + b * BB, *bhi = row_hi + b * BB;
+          uint32_t a_lo[4], a_hi[4];
+          unpack_row<DT>(blo, t, a_lo);
+          unpack_row<DT>(bhi, t, a_hi);
+          float d_lo = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(blo)));
+          float d_hi = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(bhi)));
+          const uint32_t kb_local = c0 + b;
 #pragma unroll
-        for (int n = 0; n < NT; n++) {
-          // column g of this N-tile = (token n*4 + g/2, part g&1)
-          const uint32_t tokpart = n * 8 + g;
-          uint4 bf = make_uint4(0, 0, 0, 0);
-          if ((tokpart >> 1) < pcount)
-            bf = *reinterpret_cast<const uint4 *>(s_frag + (size_t)tokpart * p.frag_stride + kb_local * 64 + t * 16);
-          float c[4];
-          float seed = (n * 4 + t < pcount) ? s_init[(size_t)(n * 4 + t) * p.kb_split + kb_local] : 0.0f;
-          c[0] = seed, c[1] = 0.0f, c[2] = seed, c[3] = 0.0f;
-          mma_f16(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], bf.x, bf.y);
-          mma_f16(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], bf.z, bf.w);
-          acc[n][0] = fmaf(d_lo, c[0], acc[n][0]);
-          acc[n][1] = fmaf(d_lo, c[1], acc[n][1]);
-          acc[n][2] = fmaf(d_hi, c[2], acc[n][2]);
-          acc[n][3] = fmaf(d_hi, c[3], acc[n][3]);
+          for (int n = 0; n < NT; n++) {
+            // column g of this N-tile = (token n*4 + g/2, part g&1)
+            const uint32_t tokpart = n * 8 + g;
+            uint4 bf = make_uint4(0, 0, 0, 0);
+            if ((tokpart >> 1) < pcount)
+              bf = *reinterpret_cast<const uint4 *>(s_frag + (size_t)tokpart * p.frag_stride + kb_local * 64 + t * 16);
+            float c[4];
+            float seed = (n * 4 + t < pcount) ? s_init[(size_t)(n * 4 + t) * p.kb_split + kb_local] : 0.0f;
+            c[0] = seed, c[1] = 0.0f, c[2] = seed, c[3] = 0.0f;
+            mma_f16(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], bf.x, bf.y);
+            mma_f16(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], bf.z, bf.w);
+            acc[n][0] = fmaf(d_lo, c[0], acc[n][0]);
+            acc[n][1] = fmaf(d_lo, c[1], acc[n][1]);
+            acc[n][2] = fmaf(d_hi, c[2], acc[n][2]);
+            acc[n][3] = fmaf(d_hi, c[3], acc[n][3]);
+          }
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[stage]);
       if (++stage == p.n_stages) stage = 0, round++;
     }
-    if (!ok) break;
 
     // ---- item epilogue: sum the K-split partials of the four warps of each M-tile, then write
     consumer_sync();  // s_red free (previous item's readers are done)
@@ -415,7 +417,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
 #pragma unroll
       for (int i = 0; i < 4; i++) s_red[((warp * NT + n) * 4 + i) * 32 + lane] = acc[n][i];
     consumer_sync();
-    if (warp < 2) {  // warp m finishes M-tile m
+    if (warp < 2 && !dead) {  // warp m finishes M-tile m
 #pragma unroll
       for (int n = 0; n < NT; n++) {
         float v[4];
@@ -427,45 +429,35 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
           v[i] = s0;
         }
         const uint32_t tok = n * 4 + t;
-        if (tok < pcount) {
-          const uint32_t pair = d.perm[pstart + tok];
-          const uint32_t a = p.act_per_pair ? pair : pair / d.slots;
-          const float un = p.aunscale[a];
-          float r_lo = (v[0] + v[1]) * un, r_hi = (v[2] + v[3]) * un;  // rows g and g+8 of the M-tile
-          if (p.phase == 0) {
-            // rows 0..7 are gate rows, rows 8..15 the matching up rows
-            float gate = r_lo;
-            if (d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit) && gate == gate)
-              gate = fminf(fmaxf(gate, -d.swiglu_limit), d.swiglu_limit);
-            float hval = silu_f(gate) * r_hi;
-            uint32_t row = tile * 16 + warp * 8 + g;
-            p.out[(size_t)pair * d.F + row] = hval;
-            float ah = fabsf(hval);
-            uint32_t bits = (ah != ah) ? 0x7fc00000u : __float_as_uint(ah);
-            // max over the 8 rows held by lanes with the same t (xor over g bits)
-#pragma unroll
-            for (int o = 4; o < 32; o <<= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
-            if (g == 0) atomicMax(p.amax + pair, bits);
-          } else {
-            float *yo = p.out + ((size_t)ks * d.n_tokens * d.slots + pair) * d.D + tile * 32 + warp * 16;
-            yo[g] = r_lo;
-            yo[g + 8] = r_hi;
-          }
-        } else if (p.phase == 0) {
-          uint32_t bits = 0;
+        const bool valid = tok < pcount;
+        const uint32_t pair = valid ? d.perm[pstart + tok] : 0;
+        const uint32_t a = p.act_per_pair ? pair : pair / d.slots;
+        const float un = valid ? p.aunscale[a] : 0.0f;
+        const float r_lo = (v[0] + v[1]) * un, r_hi = (v[2] + v[3]) * un;  // rows g and g+8 of the M-tile
+        if (p.phase == 0) {
+          // rows 0..7 of an M-tile are gate rows, rows 8..15 the matching up rows
+          float gate = r_lo;
+          if (d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit) && gate == gate)
+            gate = fminf(fmaxf(gate, -d.swiglu_limit), d.swiglu_limit);
+          const float hval = silu_f(gate) * r_hi;
+          if (valid) p.out[(size_t)pair * d.F + tile * 16 + warp * 8 + g] = hval;
+          const float ah = fabsf(hval);
+          uint32_t bits = !valid ? 0u : (ah != ah) ? 0x7fc00000u : __float_as_uint(ah);
+          // max over the 8 rows held by the lanes that share t (all lanes take part in the shuffles)
 #pragma unroll
           for (int o = 4; o < 32; o <<= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
+          if (valid && g == 0) atomicMax(p.amax + pair, bits);
+        } else if (valid) {
+          float *yo = p.out + ((size_t)ks * d.n_tokens * d.slots + pair) * d.D + tile * 32 + warp * 16;
+          yo[g] = r_lo;
+          yo[g + 8] = r_hi;
         }
       }
     }
   }
-  if (!ok) {
-    if (lane == 0) {
-      *(volatile uint32_t *)s_abort = 1;
-      atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
-      // release the producer if it is waiting for this warp
-      for (uint32_t s = 0; s < p.n_stages; s++) mbar_arrive(&empty[s]);
-    }
+  if (dead && lane == 0) {
+    *(volatile uint32_t *)s_abort = 1;
+    atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
   }
 }
 
@@ -598,10 +590,7 @@ cudaError_t launch_ffn_stream(const MoeDispatch &d, void *scratch, int sm_count,
   const uint32_t P = d.n_tokens * d.slots;
   uint8_t *base = static_cast<uint8_t *>(scratch);
   // the layout is a function of the allocation-time maxima; only offsets matter here
-  static thread_local ScratchLayout L;
-  static thread_local uint32_t L_key[3] = {0, 0, 0};
-  (void)L_key;
-  L = scratch_layout(d.scratch_pairs, d.D, d.F);
+  const ScratchLayout L = scratch_layout(d.scratch_pairs, d.D, d.F);
   const uint32_t nt = pick_nt(d.dtype, d.D, d.F);
   const Plan pg = make_plan(d.dtype, d.D / 32, 0, nt), pd = make_plan(d.dtype, d.F / 32, 1, nt);
   uint32_t *n_passes = reinterpret_cast<uint32_t *>(base + L.npass);

@@ -136,6 +136,7 @@ MoeDispatch base_dispatch(mer_backend *b) {
   d.counters = b->d_counters;
   d.logits = b->d_logits;
   d.swiglu_limit = b->cfg.swiglu_limit;
+  d.scratch_pairs = b->max_pairs;
   return d;
 }
 
