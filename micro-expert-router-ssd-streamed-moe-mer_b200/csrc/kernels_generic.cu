@@ -128,29 +128,70 @@ __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uin
 
 __global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispatch d, uint32_t max_tokens) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
+  const RouterDev &r_ = r;
   const uint32_t E = r.num_experts, D = d.D;
   const uint32_t token = blockIdx.y;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float *x = d.x + (size_t)token * D;
-  const uint32_t e = blockIdx.x * ROUTER_ROWS + warp;
-  if (e < E) {
-    const float *w = r.w + (size_t)e * D;
-    float acc = 0.0f;
-    if ((D & 3u) == 0) {
-      const float4 *w4 = reinterpret_cast<const float4 *>(w);
-      const float4 *x4 = reinterpret_cast<const float4 *>(x);
-      for (uint32_t i = lane; i < D / 4; i += 32) {
-        float4 a = __ldg(w4 + i), b = __ldg(x4 + i);
-        acc = fmaf(a.x, b.x, acc);
-        acc = fmaf(a.y, b.y, acc);
-        acc = fmaf(a.z, b.z, acc);
-        acc = fmaf(a.w, b.w, acc);
+  const uint32_t e0 = blockIdx.x * ROUTER_ROWS;
+  if ((D & 1023u) == 0) {
+    // Eight rows per CTA; every warp takes one eighth of the columns of all eight rows, so each
+    // lane has 8 independent row loads in flight per activation vector and x is read once.
+    __shared__ float s_part[ROUTER_ROWS][ROUTER_ROWS + 1];  // [row][warp]
+    const uint32_t slice4 = D / 4 / ROUTER_ROWS;            // float4 per warp slice
+    const float4 *x4 = reinterpret_cast<const float4 *>(x) + warp * slice4;
+    float acc[ROUTER_ROWS];
+#pragma unroll
+    for (int r = 0; r < ROUTER_ROWS; r++) acc[r] = 0.0f;
+    for (uint32_t i = lane; i < slice4; i += 32) {
+      float4 b = __ldg(x4 + i);
+      float4 a[ROUTER_ROWS];
+#pragma unroll
+      for (int r = 0; r < ROUTER_ROWS; r++) {
+        uint32_t row = min(e0 + r, E - 1);
+        a[r] = __ldg(reinterpret_cast<const float4 *>((r_.w + (size_t)row * D)) + warp * slice4 + i);
       }
-    } else {
-      for (uint32_t i = lane; i < D; i += 32) acc = fmaf(__ldg(w + i), __ldg(x + i), acc);
+#pragma unroll
+      for (int r = 0; r < ROUTER_ROWS; r++) {
+        acc[r] = fmaf(a[r].x, b.x, acc[r]);
+        acc[r] = fmaf(a[r].y, b.y, acc[r]);
+        acc[r] = fmaf(a[r].z, b.z, acc[r]);
+        acc[r] = fmaf(a[r].w, b.w, acc[r]);
+      }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) d.logits[(size_t)token * E + e] = acc;
+#pragma unroll
+    for (int r = 0; r < ROUTER_ROWS; r++) {
+      float v = warp_sum(acc[r]);
+      if (lane == 0) s_part[r][warp] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < ROUTER_ROWS && e0 + threadIdx.x < E) {
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < ROUTER_ROWS; w++) v += s_part[threadIdx.x][w];
+      d.logits[(size_t)token * E + e0 + threadIdx.x] = v;
+    }
+  } else {
+    const uint32_t e = e0 + warp;
+    if (e < E) {
+      const float *w = r.w + (size_t)e * D;
+      float acc = 0.0f;
+      if ((D & 3u) == 0) {
+        const float4 *w4 = reinterpret_cast<const float4 *>(w);
+        const float4 *x4 = reinterpret_cast<const float4 *>(x);
+        for (uint32_t i = lane; i < D / 4; i += 32) {
+          float4 a = __ldg(w4 + i), b = __ldg(x4 + i);
+          acc = fmaf(a.x, b.x, acc);
+          acc = fmaf(a.y, b.y, acc);
+          acc = fmaf(a.z, b.z, acc);
+          acc = fmaf(a.w, b.w, acc);
+        }
+      } else {
+        for (uint32_t i = lane; i < D; i += 32) acc = fmaf(__ldg(w + i), __ldg(x + i), acc);
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) d.logits[(size_t)token * E + e] = acc;
+    }
   }
   __shared__ uint32_t s_flag;
   __syncthreads();

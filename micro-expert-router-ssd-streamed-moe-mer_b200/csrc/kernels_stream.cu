@@ -23,11 +23,13 @@
 
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "../../include/mer_b200.h"
 
 namespace {
 
-constexpr int CONSUMER_WARPS = 8;
+constexpr int CONSUMER_WARPS = 16;
 constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;  // + one producer warp
 constexpr int ROWCHUNKS = 32;                       // row segments per stage: 2 M-tiles x 16 row slots
 constexpr int KSPLIT_WARPS = CONSUMER_WARPS / 2;    // warps that split the K range of one M-tile
@@ -87,11 +89,33 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
                "l"(src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                        uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// D = A * B + C with separate C so that a seed / zero needs no register moves.
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1, float c0, float c1, float c2, float c3) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
+}
+// Shared-memory loads on 32-bit shared addresses (no generic-address arithmetic in the block loop).
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float ldsf(uint32_t a) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
 
@@ -116,8 +140,13 @@ __device__ __forceinline__ void frag_slot(uint32_t j, uint32_t &pos, float &slot
   }
 }
 
-// One CTA per activation row: exact power-of-two scaling so that max |a| lands in [256, 512),
-// f16 hi/lo split in fragment order, and the per-block accumulator seed.
+// Activation rows -> MMA B fragments.  Exact power-of-two scaling so that max |a| lands in
+// [256, 512), f16 hi/lo split in fragment order, and the per-block accumulator seed.
+// grid = (rows, ceil(K / 2048)); every thread converts two groups of four consecutive elements.
+constexpr uint32_t PREP_CHUNK = 2048;
+
+__device__ __forceinline__ float nan_max(float a, float b) { return (b > a || b != b) ? b : a; }  // NaN sticks
+
 template <int DT>
 __global__ void __launch_bounds__(256) k_act_prep(const float *__restrict__ a, uint32_t K, const uint32_t *__restrict__ amax_bits,
                                                   uint16_t *__restrict__ frag, float *__restrict__ init,
@@ -125,95 +154,102 @@ __global__ void __launch_bounds__(256) k_act_prep(const float *__restrict__ a, u
   const uint32_t row = blockIdx.x;
   const float *src = a + (size_t)row * K;
   __shared__ float s_red[8];
-  __shared__ float s_scale;
   float mx;
   if (amax_bits) {
     mx = __uint_as_float(amax_bits[row]);
   } else {
     mx = 0.0f;
-    for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) {
-      float v = fabsf(src[i]);
-      mx = (v > mx || v != v) ? v : mx;  // NaN sticks
+    const float4 *src4 = reinterpret_cast<const float4 *>(src);
+#pragma unroll 4
+    for (uint32_t i = threadIdx.x; i < K / 4; i += 256) {
+      float4 v = __ldg(src4 + i);
+      mx = nan_max(nan_max(nan_max(nan_max(mx, fabsf(v.x)), fabsf(v.y)), fabsf(v.z)), fabsf(v.w));
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float other = __shfl_xor_sync(0xffffffffu, mx, o);
-      mx = (other > mx || other != other) ? other : mx;
-    }
+    for (int o = 16; o > 0; o >>= 1) mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = mx;
     __syncthreads();
-    if (threadIdx.x == 0) {
-      for (int w = 1; w < 8; w++) mx = (s_red[w] > mx || s_red[w] != s_red[w]) ? s_red[w] : mx;
-      s_red[0] = mx;
-    }
-    __syncthreads();
     mx = s_red[0];
+#pragma unroll
+    for (int w = 1; w < 8; w++) mx = nan_max(mx, s_red[w]);
   }
-  if (threadIdx.x == 0) {
-    float s = 1.0f;
-    if (mx > 0.0f && isfinite(mx)) {
-      int e;
-      frexpf(mx, &e);             // mx = m * 2^e, m in [0.5, 1)
-      s = ldexpf(1.0f, 9 - e);    // mx * s in [256, 512)
-    } else if (mx != mx || isinf(mx)) {
-      s = mx;  // non-finite activations poison the row, as they would in fp32
-    }
-    s_scale = s;
-    unscale[row] = POW2_24 / s;
+  float s = 1.0f;
+  if (mx > 0.0f && isfinite(mx)) {
+    int e;
+    frexpf(mx, &e);           // mx = m * 2^e, m in [0.5, 1)
+    s = ldexpf(1.0f, 9 - e);  // mx * s in [256, 512)
+  } else if (mx != mx || isinf(mx)) {
+    s = mx;  // non-finite activations poison the row, as they would in fp32
   }
-  __syncthreads();
-  const float s = s_scale;
+  if (blockIdx.y == 0 && threadIdx.x == 0) unscale[row] = POW2_24 / s;
   const uint32_t KB = K / 32;
   const float zp = DT == MER_DTYPE_Q4_0 ? 8.0f : 128.0f;
   uint16_t *hi_dst = frag + (size_t)row * 2 * K;
   uint16_t *lo_dst = hi_dst + K;
-  // one warp per block: lane j handles element j
-  for (uint32_t kb = threadIdx.x >> 5; kb < KB; kb += blockDim.x >> 5) {
-    uint32_t j = threadIdx.x & 31;
-    float v = src[kb * 32 + j] * s;  // exact (power of two) unless it overflows
+#pragma unroll
+  for (int half = 0; half < 2; half++) {
+    const uint32_t e0 = blockIdx.y * PREP_CHUNK + half * (PREP_CHUNK / 2) + threadIdx.x * 4;  // first of 4 elements
+    const bool live = e0 < K;
+    float4 v = live ? __ldg(reinterpret_cast<const float4 *>(src + e0)) : make_float4(0, 0, 0, 0);
+    v.x *= s, v.y *= s, v.z *= s, v.w *= s;  // exact (power of two) unless it overflows
+    const uint32_t kb = e0 >> 5, j0 = e0 & 31u;
     uint32_t pos;
     float ss;
-    frag_slot<DT>(j, pos, ss);
-    float vs = v * ss;
-    __half h = __float2half_rn(vs);
-    __half l = __float2half_rn(vs - __half2float(h));
-    hi_dst[kb * 32 + pos] = __half_as_ushort(h);
-    lo_dst[kb * 32 + pos] = __half_as_ushort(l);
-    float sum = v;
+    frag_slot<DT>(j0, pos, ss);  // the four elements land at pos + {0, 2, 1, 3}
+    float vs[4] = {v.x * ss, v.z * ss, v.y * ss, v.w * ss};
+    uint16_t hi[4], lo[4];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (j == 0) init[(size_t)row * KB + kb] = -zp * sum * (1.0f / POW2_24);
+    for (int i = 0; i < 4; i++) {
+      __half h = __float2half_rn(vs[i]);
+      hi[i] = __half_as_ushort(h);
+      lo[i] = __half_as_ushort(__float2half_rn(vs[i] - __half2float(h)));
+    }
+    if (live) {
+      *reinterpret_cast<uint2 *>(hi_dst + kb * 32 + pos) = make_uint2(hi[0] | (uint32_t)hi[1] << 16, hi[2] | (uint32_t)hi[3] << 16);
+      *reinterpret_cast<uint2 *>(lo_dst + kb * 32 + pos) = make_uint2(lo[0] | (uint32_t)lo[1] << 16, lo[2] | (uint32_t)lo[3] << 16);
+    }
+    float sum = (v.x + v.y) + (v.z + v.w);  // eight consecutive lanes hold one block
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (live && (threadIdx.x & 7) == 0) init[(size_t)row * KB + kb] = -zp * sum * (1.0f / POW2_24);
   }
 }
 
 // ------------------------------------------------------------------------ weight unpacking
 // Eight weights of one row of one block -> four f16x2 registers holding the integer fields as
-// subnormals: {MMA0.k(2t,2t+1), MMA0.k(2t+8,2t+9), MMA1.k(2t,2t+1), MMA1.k(2t+8,2t+9)}.
-template <int DT>
-__device__ __forceinline__ void unpack_row(const uint8_t *blk, uint32_t t, uint32_t (&r)[4]) {
+// subnormals: {MMA0.k(2t,2t+1), MMA0.k(2t+8,2t+9), MMA1.k(2t,2t+1), MMA1.k(2t+8,2t+9)}, plus the
+// block scale.  `ba` is the shared address of the block start, `toff` = 4t (Q4_0) or 8t (Q8_0).
+// Row segments start 16-byte aligned and blocks are 18 / 34 bytes, so the quants of odd blocks are
+// word aligned and those of even blocks sit two bytes past a word: ODD is uniform per warp.
+template <int DT, bool ODD>
+__device__ __forceinline__ void load_unpack(uint32_t ba, uint32_t toff, uint32_t (&r)[4], float &scale) {
+  scale = __half2float(__ushort_as_half((unsigned short)lds16(ba)));
   if (DT == MER_DTYPE_Q4_0) {
-    // bytes 2 + 4t .. 2 + 4t + 3: low nibbles = elements 4t..4t+3, high nibbles = 16 + the same
-    const uint8_t *p = blk + 2 + 4 * t;
-    uint32_t mis = (uint32_t)(size_t)p & 3u;  // 0 or 2
-    const uint32_t *w = reinterpret_cast<const uint32_t *>(p - mis);
-    uint32_t v = __funnelshift_r(w[0], w[1], mis * 8);
+    uint32_t v;
+    if (ODD) {
+      v = lds32(ba + 2 + toff);
+    } else {
+      uint32_t w0 = lds32(ba + toff), w1 = lds32(ba + toff + 4);
+      v = __funnelshift_r(w0, w1, 16);
+    }
     uint32_t v8 = v >> 8;
-    r[0] = v & 0x000F000Fu;
-    r[2] = v & 0x00F000F0u;
-    r[1] = v8 & 0x000F000Fu;
+    r[0] = v & 0x000F000Fu;   // low nibbles of bytes 0, 2  -> elements 4t, 4t+2
+    r[1] = v8 & 0x000F000Fu;  // low nibbles of bytes 1, 3  -> elements 4t+1, 4t+3
+    r[2] = v & 0x00F000F0u;   // high nibbles               -> elements 16 + ... (x16, undone on the activation side)
     r[3] = v8 & 0x00F000F0u;
   } else {
-    const uint8_t *p = blk + 2 + 8 * t;
-    uint32_t mis = (uint32_t)(size_t)p & 3u;
-    const uint32_t *w = reinterpret_cast<const uint32_t *>(p - mis);
-    uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
-    uint32_t lo = __funnelshift_r(w0, w1, mis * 8), hi = __funnelshift_r(w1, w2, mis * 8);
-    lo ^= 0x80808080u;  // int8 -> biased unsigned byte (q + 128)
-    hi ^= 0x80808080u;
-    r[0] = lo & 0x00FF00FFu;
-    r[1] = (lo >> 8) & 0x00FF00FFu;
-    r[2] = hi & 0x00FF00FFu;
-    r[3] = (hi >> 8) & 0x00FF00FFu;
+    uint32_t lo, hi;
+    if (ODD) {
+      lo = lds32(ba + 2 + toff), hi = lds32(ba + 6 + toff);
+    } else {
+      uint32_t w0 = lds32(ba + toff), w1 = lds32(ba + toff + 4), w2 = lds32(ba + toff + 8);
+      lo = __funnelshift_r(w0, w1, 16), hi = __funnelshift_r(w1, w2, 16);
+    }
+    // int8 -> biased unsigned byte (q + 128) in the low mantissa bits
+    r[0] = (lo ^ 0x80808080u) & 0x00FF00FFu;
+    r[1] = ((lo >> 8) ^ 0x00808080u) & 0x00FF00FFu;
+    r[2] = (hi ^ 0x80808080u) & 0x00FF00FFu;
+    r[3] = ((hi >> 8) ^ 0x00808080u) & 0x00FF00FFu;
   }
 }
 
@@ -236,8 +272,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   uint64_t *empty = full + p.n_stages;                   // [n_stages]
   uint64_t *actbar = empty + p.n_stages;                 // [1]
   uint32_t *s_abort = reinterpret_cast<uint32_t *>(actbar + 1);
-  float *s_red = reinterpret_cast<float *>(smem + 256);                     // [8 warps][NT][4][32]
-  float *s_init = s_red + CONSUMER_WARPS * NT * 128;                        // [kb_split][TP]
+  float *s_red = reinterpret_cast<float *>(smem + 256);                     // [2][CONSUMER_WARPS][NT][4][32]
+  float *s_init = s_red + 2 * CONSUMER_WARPS * NT * 128;                    // [TP][kb_split]
   uint8_t *s_frag = reinterpret_cast<uint8_t *>(s_init + p.kb_split * TP);  // [TP*2][frag_stride]
   s_frag = reinterpret_cast<uint8_t *>(((size_t)s_frag + 127) & ~(size_t)127);
   uint8_t *s_stage = s_frag + (size_t)TP * 2 * p.frag_stride;               // [n_stages][32 * row_stride + 128]
@@ -257,16 +293,18 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   const uint32_t n_tiles = p.rows / (p.phase == 0 ? 16u : 32u);
   const uint32_t n_passes = *p.n_passes;
   const uint64_t n_items = (uint64_t)n_passes * p.n_ksplit * n_tiles;
-  const uint64_t item_beg = n_items * blockIdx.x / gridDim.x, item_end = n_items * (blockIdx.x + 1) / gridDim.x;
+  const uint32_t item_beg = (uint32_t)(n_items * blockIdx.x / gridDim.x), item_end = (uint32_t)(n_items * (blockIdx.x + 1) / gridDim.x);
   if (item_beg >= item_end) return;
   const size_t proj_bytes = (size_t)d.D * d.F / 32 * BB;
   const size_t row_bytes = (size_t)p.kb_total * BB;
 
-  auto decode = [&](uint64_t item, uint32_t &pp, uint32_t &ks, uint32_t &tile) {
-    tile = (uint32_t)(item % n_tiles);
-    uint64_t rest = item / n_tiles;
-    ks = (uint32_t)(rest % p.n_ksplit);
-    pp = (uint32_t)(rest / p.n_ksplit);
+  // items are ordered (pass, K split, tile); a CTA decodes its first item once and then steps
+  uint32_t tile = item_beg % n_tiles, ks = (item_beg / n_tiles) % p.n_ksplit, pp = item_beg / n_tiles / p.n_ksplit;
+  auto next_item = [&]() {
+    if (++tile == n_tiles) {
+      tile = 0;
+      if (++ks == p.n_ksplit) ks = 0, ++pp;
+    }
   };
   auto kb_range = [&](uint32_t ks, uint32_t &kb0, uint32_t &kbn) {
     kb0 = ks * p.kb_split;
@@ -277,9 +315,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
     // ------------------------------ producer warp: lane i copies row segment i of every stage
     uint32_t stage = 0, round = 0;
     bool ok = true;
-    for (uint64_t item = item_beg; item < item_end && ok; item++) {
-      uint32_t pp, ks, tile, kb0, kbn;
-      decode(item, pp, ks, tile);
+    for (uint32_t item = item_beg; item < item_end && ok; item++, next_item()) {
+      uint32_t kb0, kbn;
       kb_range(ks, kb0, kbn);
       uint32_t eid = d.group_expert[p.pass_group[pp]];
       const uint8_t *base = (eid < d.max_experts) ? d.expert_ptr[eid] : nullptr;
@@ -318,24 +355,53 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
 
   // ---------------------------------------------------------------------- consumer warps
   const uint32_t g = lane >> 2, t = lane & 3;
-  const uint32_t mtile = warp & 1, kpart = warp >> 1;  // M-tile of the stage, quarter of its K range
-  uint32_t stage = 0, round = 0, act_round = 0;
+  const uint32_t mtile = warp & 1, kpart = warp >> 1;  // M-tile of the stage, eighth of its K range
+  const uint32_t toff = (DT == MER_DTYPE_Q4_0 ? 4u : 8u) * t;
+  const uint32_t stage0 = smem_u32(s_stage) + (mtile * 16 + g) * p.row_stride;  // row g of this warp's M-tile, stage 0
+  const uint32_t row8 = 8 * p.row_stride;
+  const uint32_t frag0 = smem_u32(s_frag) + t * 16, init0 = smem_u32(s_init);
+  float *s_red2 = s_red;  // [2 buffers][CONSUMER_WARPS][NT][4][32]
+  uint32_t stage = 0, round = 0, act_round = 0, red_buf = 0;
   uint32_t cur_pp = MER_NONE, cur_ks = MER_NONE;
   // A warp whose bounded wait expired goes "dead": it stops computing and waiting but still walks
-  // the same loop structure, so the named barriers below always see all eight warps.
+  // the same loop structure, so the named barriers below always see all consumer warps.
   bool dead = false;
 
-  for (uint64_t item = item_beg; item < item_end; item++) {
-    uint32_t pp, ks, tile, kb0, kbn;
-    decode(item, pp, ks, tile);
+  uint32_t pstart = 0, pcount = 0, clean_from = 0;  // columns >= clean_from of the fragment arrays are zero
+  bool resident = false;
+  {  // the fragment and seed arrays start out zeroed so that unused columns contribute nothing
+    uint4 *z = reinterpret_cast<uint4 *>(s_init);
+    const uint32_t n16 = (uint32_t)((s_stage - reinterpret_cast<uint8_t *>(s_init)) / 16);
+    for (uint32_t i = threadIdx.x; i < n16; i += CONSUMER_WARPS * 32) z[i] = make_uint4(0, 0, 0, 0);
+    // generic-proxy stores, later overwritten by bulk copies (async proxy): fence here, and the
+    // consumer_sync of the first fragment load below orders them before the copy is issued
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+
+  for (uint32_t item = item_beg; item < item_end; item++, next_item()) {
+    uint32_t kb0, kbn;
     kb_range(ks, kb0, kbn);
-    const uint32_t grp = p.pass_group[pp], pstart = p.pass_start[pp], pcount = p.pass_count[pp];
-    const uint32_t eid = d.group_expert[grp];
-    const bool resident = eid < d.max_experts && d.expert_ptr[eid] != nullptr;
 
     if (pp != cur_pp || ks != cur_ks) {
       // new activation fragments: everyone is done with the old ones, then one thread issues the copies
+      if (pp != cur_pp) {
+        pstart = p.pass_start[pp], pcount = p.pass_count[pp];
+        const uint32_t eid = d.group_expert[p.pass_group[pp]];
+        resident = eid < d.max_experts && d.expert_ptr[eid] != nullptr;
+      }
       consumer_sync();
+      if (2 * pcount < clean_from) {
+        // columns that held a previous pass's tokens and stay unused now must read as zero
+        for (uint32_t c = 2 * pcount; c < clean_from; c++) {
+          uint4 *z = reinterpret_cast<uint4 *>(s_frag + (size_t)c * p.frag_stride);
+          for (uint32_t i = threadIdx.x; i < p.kb_split * 4; i += CONSUMER_WARPS * 32) z[i] = make_uint4(0, 0, 0, 0);
+        }
+        for (uint32_t c = pcount; c < clean_from / 2; c++)
+          for (uint32_t i = threadIdx.x; i < p.kb_split; i += CONSUMER_WARPS * 32) s_init[(size_t)c * p.kb_split + i] = 0.0f;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        consumer_sync();
+      }
+      clean_from = 2 * pcount;
       cur_pp = pp, cur_ks = ks;
       if (threadIdx.x == 0) {
         uint32_t bytes_each = kbn * 64;
@@ -367,41 +433,59 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       continue;
     }
 
+    // per-item loop invariants: where column g / token t of each N-tile lives (unused ones read zeros)
+    uint32_t fa[NT], ia[NT];
+#pragma unroll
+    for (int n = 0; n < NT; n++) {
+      fa[n] = frag0 + (n * 8 + g) * p.frag_stride;  // column g of N-tile n = (token n*4 + g/2, part g&1)
+      ia[n] = init0 + (n * 4 + t) * p.kb_split * 4;
+    }
     float acc[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; n++) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+    const uint32_t n_live = (pcount + 3) >> 2;  // N-tiles that hold tokens
+
+    // one block of both rows against every live N-tile; kb = block index within the K split
+    auto do_block = [&](uint32_t ba, uint32_t kb, auto odd_tag) {
+      constexpr bool ODD = decltype(odd_tag)::value;
+      uint32_t a_lo[4], a_hi[4];
+      float d_lo, d_hi;
+      load_unpack<DT, ODD>(ba, toff, a_lo, d_lo);
+      load_unpack<DT, ODD>(ba + row8, toff, a_hi, d_hi);
+#pragma unroll
+      for (int n = 0; n < NT; n++) {
+        if (n > 0 && (uint32_t)n >= n_live) break;  // uniform
+        const uint4 bf = lds128(fa[n] + kb * 64);
+        const float seed = ldsf(ia[n] + kb * 4);
+        float c1[4], c2[4];
+        mma_f16(c1, a_lo[0], a_hi[0], a_lo[1], a_hi[1], bf.x, bf.y, seed, 0.0f, seed, 0.0f);
+        mma_f16(c2, a_lo[2], a_hi[2], a_lo[3], a_hi[3], bf.z, bf.w, c1[0], c1[1], c1[2], c1[3]);
+        acc[n][0] = fmaf(d_lo, c2[0], acc[n][0]);
+        acc[n][1] = fmaf(d_lo, c2[1], acc[n][1]);
+        acc[n][2] = fmaf(d_hi, c2[2], acc[n][2]);
+        acc[n][3] = fmaf(d_hi, c2[3], acc[n][3]);
+      }
+    };
 
     for (uint32_t c0 = 0; c0 < kbn; c0 += p.kc) {
       const uint32_t nb = min(p.kc, kbn - c0);
       if (!dead && !mbar_wait(&full[stage], round & 1)) dead = true;
       dead = __any_sync(0xffffffffu, dead);
       if (!dead) {
-        const uint8_t *st = s_stage + (size_t)stage * stage_bytes + (size_t)(mtile * 16) * p.row_stride;
-        const uint8_t *row_lo = st + (size_t)g * p.row_stride, *row_hi = st + (size_t)(g + 8) * p.row_stride;
-        for (uint32_t b = kpart; b < nb; b += KSPLIT_WARPS) {
-          const uint8_t *blo = row_lo + b * BB, *bhi = row_hi + b * BB;
-          uint32_t a_lo[4], a_hi[4];
-          unpack_row<DT>(blo, t, a_lo);
-          unpack_row<DT>(bhi, t, a_hi);
-          float d_lo = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(blo)));
-          float d_hi = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(bhi)));
-          const uint32_t kb_local = c0 + b;
-#pragma unroll
-          for (int n = 0; n < NT; n++) {
-            // column g of this N-tile = (token n*4 + g/2, part g&1)
-            const uint32_t tokpart = n * 8 + g;
-            uint4 bf = make_uint4(0, 0, 0, 0);
-            if ((tokpart >> 1) < pcount)
-              bf = *reinterpret_cast<const uint4 *>(s_frag + (size_t)tokpart * p.frag_stride + kb_local * 64 + t * 16);
-            float c[4];
-            float seed = (n * 4 + t < pcount) ? s_init[(size_t)(n * 4 + t) * p.kb_split + kb_local] : 0.0f;
-            c[0] = seed, c[1] = 0.0f, c[2] = seed, c[3] = 0.0f;
-            mma_f16(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], bf.x, bf.y);
-            mma_f16(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], bf.z, bf.w);
-            acc[n][0] = fmaf(d_lo, c[0], acc[n][0]);
-            acc[n][1] = fmaf(d_lo, c[1], acc[n][1]);
-            acc[n][2] = fmaf(d_hi, c[2], acc[n][2]);
-            acc[n][3] = fmaf(d_hi, c[3], acc[n][3]);
+        uint32_t ba = stage0 + stage * stage_bytes + kpart * BB;
+        uint32_t kb = c0 + kpart;
+        // this warp's blocks kpart, kpart + 8, ... all have the parity of kpart; two per iteration
+        if (kpart & 1) {
+#pragma unroll 1
+          for (uint32_t b = kpart; b < nb; b += 2 * KSPLIT_WARPS, ba += 2 * KSPLIT_WARPS * BB, kb += 2 * KSPLIT_WARPS) {
+            do_block(ba, kb, std::true_type{});
+            if (b + KSPLIT_WARPS < nb) do_block(ba + KSPLIT_WARPS * BB, kb + KSPLIT_WARPS, std::true_type{});
+          }
+        } else {
+#pragma unroll 1
+          for (uint32_t b = kpart; b < nb; b += 2 * KSPLIT_WARPS, ba += 2 * KSPLIT_WARPS * BB, kb += 2 * KSPLIT_WARPS) {
+            do_block(ba, kb, std::false_type{});
+            if (b + KSPLIT_WARPS < nb) do_block(ba + KSPLIT_WARPS * BB, kb + KSPLIT_WARPS, std::false_type{});
           }
         }
       }
@@ -410,22 +494,26 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       if (++stage == p.n_stages) stage = 0, round++;
     }
 
-    // ---- item epilogue: sum the K-split partials of the four warps of each M-tile, then write
-    consumer_sync();  // s_red free (previous item's readers are done)
+    // ---- item epilogue: sum the K-split partials of the eight warps of each M-tile, then write.
+    // s_red is double buffered, so one barrier per item is enough: a buffer is rewritten two items
+    // later, after every warp has passed the barrier of the item in between.
+    float *red = s_red2 + (size_t)red_buf * CONSUMER_WARPS * NT * 128;
+    red_buf ^= 1;
 #pragma unroll
     for (int n = 0; n < NT; n++)
 #pragma unroll
-      for (int i = 0; i < 4; i++) s_red[((warp * NT + n) * 4 + i) * 32 + lane] = acc[n][i];
+      for (int i = 0; i < 4; i++) red[((warp * NT + n) * 4 + i) * 32 + lane] = acc[n][i];
     consumer_sync();
     if (warp < 2 && !dead) {  // warp m finishes M-tile m
 #pragma unroll
       for (int n = 0; n < NT; n++) {
+        if (n > 0 && (uint32_t)(n * 4) >= pcount) break;
         float v[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
           float s0 = 0.0f;
 #pragma unroll
-          for (int kp = 0; kp < KSPLIT_WARPS; kp++) s0 += s_red[(((kp * 2 + warp) * NT + n) * 4 + i) * 32 + lane];
+          for (int kp = 0; kp < KSPLIT_WARPS; kp++) s0 += red[(((kp * 2 + warp) * NT + n) * 4 + i) * 32 + lane];
           v[i] = s0;
         }
         const uint32_t tok = n * 4 + t;
@@ -462,22 +550,45 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
 }
 
 // Token passes: every group with tokens is cut into passes of at most tokens_per_pass pairs.
-__global__ void k_build_passes(MoeDispatch d, uint32_t tokens_per_pass, uint32_t *n_passes, uint32_t *pass_group,
-                               uint32_t *pass_start, uint32_t *pass_count, uint32_t *amax, uint32_t n_pairs) {
-  for (uint32_t i = threadIdx.x; i < n_pairs; i += blockDim.x) amax[i] = 0;
-  if (threadIdx.x == 0) {
-    uint32_t np = 0;
-    for (uint32_t g = 0; g < d.n_groups; g++) {
-      uint32_t beg = d.offsets[g], end = d.offsets[g + 1];
-      for (uint32_t s = beg; s < end; s += tokens_per_pass) {
-        pass_group[np] = g;
-        pass_start[np] = s;
-        pass_count[np] = min(tokens_per_pass, end - s);
-        np++;
-      }
+// Each thread owns a contiguous run of groups; a 256-entry scan gives every run its first pass.
+__global__ void __launch_bounds__(256) k_build_passes(MoeDispatch d, uint32_t tokens_per_pass, uint32_t *n_passes,
+                                                      uint32_t *pass_group, uint32_t *pass_start, uint32_t *pass_count,
+                                                      uint32_t *amax, uint32_t n_pairs) {
+  __shared__ uint32_t s_cnt[257];
+  for (uint32_t i = threadIdx.x; i < n_pairs; i += 256) amax[i] = 0;
+  const uint32_t per = (d.n_groups + 255) / 256;
+  const uint32_t g0 = threadIdx.x * per, g1 = min(g0 + per, d.n_groups);
+  uint32_t mine = 0;
+  for (uint32_t g = g0; g < g1; g++) mine += (d.offsets[g + 1] - d.offsets[g] + tokens_per_pass - 1) / tokens_per_pass;
+  s_cnt[threadIdx.x + 1] = mine;
+  if (threadIdx.x == 0) s_cnt[0] = 0;
+  __syncthreads();
+  if (threadIdx.x < 32) {  // inclusive scan of 256 counts by one warp, 8 per lane
+    uint32_t v[8], run = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) run += s_cnt[1 + threadIdx.x * 8 + i], v[i] = run;
+    uint32_t incl = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (threadIdx.x >= (uint32_t)o) incl += up;
     }
-    *n_passes = np;
+    uint32_t base = incl - run;
+#pragma unroll
+    for (int i = 0; i < 8; i++) s_cnt[1 + threadIdx.x * 8 + i] = base + v[i];
   }
+  __syncthreads();
+  uint32_t np = s_cnt[threadIdx.x];
+  for (uint32_t g = g0; g < g1; g++) {
+    uint32_t beg = d.offsets[g], end = d.offsets[g + 1];
+    for (uint32_t st = beg; st < end; st += tokens_per_pass) {
+      pass_group[np] = g;
+      pass_start[np] = st;
+      pass_count[np] = min(tokens_per_pass, end - st);
+      np++;
+    }
+  }
+  if (threadIdx.x == 0) *n_passes = s_cnt[256];
 }
 
 __global__ void k_reduce_ksplit(const float *__restrict__ part, float *__restrict__ y, size_t n, uint32_t n_ksplit) {
@@ -507,7 +618,7 @@ Plan make_plan(int dtype, uint32_t kb_total, int phase, uint32_t nt) {
   uint32_t kb_split = ((kb_total + n_ksplit - 1) / n_ksplit + 7) / 8 * 8;
   n_ksplit = (kb_total + kb_split - 1) / kb_split;
   uint32_t frag_stride = kb_split * 64 + 64;
-  size_t fixed = 256 + (size_t)CONSUMER_WARPS * nt * 128 * 4 + (size_t)kb_split * tp * 4 + 128 + (size_t)tp * 2 * frag_stride;
+  size_t fixed = 256 + (size_t)2 * CONSUMER_WARPS * nt * 128 * 4 + (size_t)kb_split * tp * 4 + 128 + (size_t)tp * 2 * frag_stride;
   for (uint32_t kc = 64; kc >= 8; kc -= 8) {
     if (kc > kb_split && kc != 8) continue;
     uint32_t chunk = kc * bb;
@@ -527,7 +638,7 @@ Plan make_plan(int dtype, uint32_t kb_total, int phase, uint32_t nt) {
 uint32_t pick_nt(int dtype, uint32_t D, uint32_t F) {
   // two N-tiles (8 tokens per pass) when both phases still fit three stages
   Plan a = make_plan(dtype, D / 32, 0, 2), b = make_plan(dtype, F / 32, 1, 2);
-  return (a.n_stages >= 3 && b.n_stages >= 3) ? 2u : 1u;
+  return (a.n_stages >= 3 && b.n_stages >= 3 && a.kc >= 32 && (b.kc >= 32 || b.kc >= b.kb_split)) ? 2u : 1u;
 }
 
 struct ScratchLayout {
@@ -603,9 +714,9 @@ cudaError_t launch_ffn_stream(const MoeDispatch &d, void *scratch, int sm_count,
   float *xinit = reinterpret_cast<float *>(base + L.xinit), *xun = reinterpret_cast<float *>(base + L.xun);
   float *hinit = reinterpret_cast<float *>(base + L.hinit), *hun = reinterpret_cast<float *>(base + L.hun);
   if (d.dtype == MER_DTYPE_Q4_0)
-    k_act_prep<MER_DTYPE_Q4_0><<<d.n_tokens, 256, 0, s>>>(d.x, d.D, nullptr, xfrag, xinit, xun);
+    k_act_prep<MER_DTYPE_Q4_0><<<dim3(d.n_tokens, (d.D + PREP_CHUNK - 1) / PREP_CHUNK), 256, 0, s>>>(d.x, d.D, nullptr, xfrag, xinit, xun);
   else
-    k_act_prep<MER_DTYPE_Q8_0><<<d.n_tokens, 256, 0, s>>>(d.x, d.D, nullptr, xfrag, xinit, xun);
+    k_act_prep<MER_DTYPE_Q8_0><<<dim3(d.n_tokens, (d.D + PREP_CHUNK - 1) / PREP_CHUNK), 256, 0, s>>>(d.x, d.D, nullptr, xfrag, xinit, xun);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
 
   StreamParams p{};
@@ -623,9 +734,9 @@ cudaError_t launch_ffn_stream(const MoeDispatch &d, void *scratch, int sm_count,
   if (ev_mid) cudaEventRecord(ev_mid, s);
   // activations of the down phase: h, scaled per pair by the max the gate/up epilogue collected
   if (d.dtype == MER_DTYPE_Q4_0)
-    k_act_prep<MER_DTYPE_Q4_0><<<P, 256, 0, s>>>(d.h, d.F, amax, hfrag, hinit, hun);
+    k_act_prep<MER_DTYPE_Q4_0><<<dim3(P, (d.F + PREP_CHUNK - 1) / PREP_CHUNK), 256, 0, s>>>(d.h, d.F, amax, hfrag, hinit, hun);
   else
-    k_act_prep<MER_DTYPE_Q8_0><<<P, 256, 0, s>>>(d.h, d.F, amax, hfrag, hinit, hun);
+    k_act_prep<MER_DTYPE_Q8_0><<<dim3(P, (d.F + PREP_CHUNK - 1) / PREP_CHUNK), 256, 0, s>>>(d.h, d.F, amax, hfrag, hinit, hun);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   // phase 1: down
   float *ypart = pd.n_ksplit > 1 ? reinterpret_cast<float *>(base + L.ypart) : d.y;
