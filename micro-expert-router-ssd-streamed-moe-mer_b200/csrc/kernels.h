@@ -46,6 +46,7 @@ struct MoeDispatch {
   float *logits;            // [n_tokens x E] scratch
   float swiglu_limit;       // <= 0 = off
   uint32_t scratch_pairs;   // pair capacity the streaming scratch was sized for
+  int packed;               // 1: slots hold the tile-major fragment layout (layout.cuh), 0: the flat block stream
 };
 
 // kernels_generic.cu
@@ -54,6 +55,10 @@ cudaError_t launch_groups_from_pairs(const MoeDispatch &d, cudaStream_t s, int *
 cudaError_t launch_ffn_generic(const MoeDispatch &d, cudaStream_t s, int *launches, cudaEvent_t ev_mid);
 cudaError_t launch_combine(const MoeDispatch &d, cudaStream_t s, int *launches);
 cudaError_t launch_dequant(int dtype, const uint8_t *src, float *dst, size_t n_weights, cudaStream_t s);
+// Dequantises projection `matrix` (0 gate, 1 up, 2 down) of a packed expert into row-major f32.
+cudaError_t launch_dequant_packed(int dtype, const uint8_t *expert, int matrix, uint32_t D, uint32_t F, float *dst, cudaStream_t s);
+// Flat gate||up||down block stream -> tile-major fragment layout (same bytes, permuted).
+cudaError_t launch_repack(int dtype, const uint8_t *flat, uint8_t *packed, uint32_t D, uint32_t F, cudaStream_t s);
 cudaError_t launch_raw_matvec(int dtype, const uint8_t *w, const float *x, float *y, size_t rows, size_t cols, cudaStream_t s);
 cudaError_t launch_f16_to_f32(const uint16_t *src, float *dst, size_t n, cudaStream_t s);
 cudaError_t launch_f32_to_f16(const float *src, uint16_t *dst, size_t n, cudaStream_t s);

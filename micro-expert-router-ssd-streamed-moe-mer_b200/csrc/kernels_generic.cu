@@ -10,6 +10,7 @@
 #include <math_constants.h>
 
 #include "../../include/mer_b200.h"
+#include "layout.cuh"
 
 namespace {
 
@@ -32,6 +33,23 @@ __device__ __forceinline__ float decode_weight(const uint8_t *__restrict__ base,
     int q = (int)(j < 16u ? (byte & 15u) : (byte >> 4)) - 8;
     return __fmul_rn(d, (float)q);
   }
+}
+
+// Weight (matrix, row, col) of a resident expert in either slot layout.
+template <int DT>
+__device__ __forceinline__ float weight_at(const MoeDispatch &d, const uint8_t *__restrict__ base, int matrix, uint32_t row,
+                                           uint32_t col) {
+  if (d.packed) {
+    PackedAddr a = packed_locate<DT>(d.D, d.F, matrix, row, col);
+    float sc = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(base + a.scale));
+    uint32_t byte = base[a.quant];
+    int q = DT == MER_DTYPE_Q8_0 ? (int)(int8_t)byte : (int)((col & 16u) ? (byte >> 4) : (byte & 15u)) - 8;
+    return __fmul_rn(sc, (float)q);
+  }
+  const size_t bb = DT == MER_DTYPE_Q8_0 ? MER_Q8_BLOCK_BYTES : MER_Q4_BLOCK_BYTES;
+  const size_t proj = ((size_t)d.D * d.F + 31) / 32 * bb;
+  const uint32_t K = matrix < 2 ? d.D : d.F;
+  return decode_weight<DT>(base + (size_t)matrix * proj, (size_t)row * K + col);
 }
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -417,9 +435,6 @@ __global__ void __launch_bounds__(256) k_gate_up_generic(MoeDispatch d) {
     for (uint32_t t = beg + lane; t < end; t += 32) d.h[(size_t)d.perm[t] * d.F + r] = 0.0f;
     return;
   }
-  const size_t bb = DT == MER_DTYPE_Q8_0 ? MER_Q8_BLOCK_BYTES : MER_Q4_BLOCK_BYTES;
-  const size_t proj = ((size_t)d.D * d.F + 31) / 32 * bb;
-  const uint8_t *gate = base, *up = base + proj;
   for (uint32_t t0 = beg; t0 < end; t0 += GEN_TG) {
     uint32_t pair[GEN_TG];
     const float *xs[GEN_TG];
@@ -431,8 +446,7 @@ __global__ void __launch_bounds__(256) k_gate_up_generic(MoeDispatch d) {
       ag[t] = au[t] = 0.0f;
     }
     for (uint32_t c = lane; c < d.D; c += 32) {
-      size_t flat = (size_t)r * d.D + c;
-      float wg = decode_weight<DT>(gate, flat), wu = decode_weight<DT>(up, flat);
+      float wg = weight_at<DT>(d, base, 0, r, c), wu = weight_at<DT>(d, base, 1, r, c);
 #pragma unroll
       for (int t = 0; t < GEN_TG; t++) {
         float xv = __ldg(xs[t] + c);
@@ -463,9 +477,6 @@ __global__ void __launch_bounds__(256) k_down_generic(MoeDispatch d) {
     for (uint32_t t = beg + lane; t < end; t += 32) d.y[(size_t)d.perm[t] * d.D + r] = 0.0f;
     return;
   }
-  const size_t bb = DT == MER_DTYPE_Q8_0 ? MER_Q8_BLOCK_BYTES : MER_Q4_BLOCK_BYTES;
-  const size_t proj = ((size_t)d.D * d.F + 31) / 32 * bb;
-  const uint8_t *down = base + 2 * proj;
   for (uint32_t t0 = beg; t0 < end; t0 += GEN_TG) {
     uint32_t pair[GEN_TG];
     const float *hs[GEN_TG];
@@ -477,7 +488,7 @@ __global__ void __launch_bounds__(256) k_down_generic(MoeDispatch d) {
       acc[t] = 0.0f;
     }
     for (uint32_t c = lane; c < d.F; c += 32) {
-      float w = decode_weight<DT>(down, (size_t)r * d.F + c);
+      float w = weight_at<DT>(d, base, 2, r, c);
 #pragma unroll
       for (int t = 0; t < GEN_TG; t++) acc[t] = fmaf(w, hs[t][c], acc[t]);
     }
@@ -511,6 +522,54 @@ __global__ void k_dequant(const uint8_t *__restrict__ src, float *__restrict__ d
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) dst[i] = decode_weight<DT>(src, i);
+}
+
+template <int DT>
+__global__ void k_dequant_packed(const uint8_t *__restrict__ expert, int matrix, uint32_t D, uint32_t F, float *__restrict__ dst) {
+  const uint32_t rows = matrix < 2 ? F : D, cols = matrix < 2 ? D : F;
+  size_t n = (size_t)rows * cols;
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    uint32_t row = (uint32_t)(i / cols), col = (uint32_t)(i % cols);
+    PackedAddr a = packed_locate<DT>(D, F, matrix, row, col);
+    float sc = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(expert + a.scale));
+    uint32_t byte = expert[a.quant];
+    int q = DT == MER_DTYPE_Q8_0 ? (int)(int8_t)byte : (int)((col & 16u) ? (byte >> 4) : (byte & 15u)) - 8;
+    dst[i] = __fmul_rn(sc, (float)q);
+  }
+}
+
+// One thread per source block: copies its scale and its quant bytes to their packed places.
+template <int DT>
+__global__ void k_repack(const uint8_t *__restrict__ flat, uint8_t *__restrict__ packed, uint32_t D, uint32_t F) {
+  constexpr uint32_t BB = DT == MER_DTYPE_Q8_0 ? MER_Q8_BLOCK_BYTES : MER_Q4_BLOCK_BYTES;
+  const size_t per_matrix = (size_t)D * F / 32;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < 3 * per_matrix; i += stride) {
+    const int matrix = (int)(i / per_matrix);
+    const size_t blk = i % per_matrix;
+    const uint32_t K = matrix < 2 ? D : F;
+    const uint32_t row = (uint32_t)(blk / (K / 32)), kb = (uint32_t)(blk % (K / 32));
+    const uint16_t *src = reinterpret_cast<const uint16_t *>(flat + i * BB);  // blocks are 2-byte aligned
+    PackedAddr a0 = packed_locate<DT>(D, F, matrix, row, kb * 32);
+    *reinterpret_cast<uint16_t *>(packed + a0.scale) = src[0];
+    if (DT == MER_DTYPE_Q4_0) {
+#pragma unroll
+      for (uint32_t t = 0; t < 4; t++) {  // quant bytes 4t..4t+3 hold elements 4t.. (low) and 16+4t.. (high)
+        PackedAddr a = packed_locate<DT>(D, F, matrix, row, kb * 32 + 4 * t);
+        *reinterpret_cast<uint32_t *>(packed + a.quant) = (uint32_t)src[1 + 2 * t] | ((uint32_t)src[2 + 2 * t] << 16);
+      }
+    } else {
+#pragma unroll
+      for (uint32_t t = 0; t < 4; t++) {
+        PackedAddr a = packed_locate<DT>(D, F, matrix, row, kb * 32 + 8 * t);
+        uint2 v;
+        v.x = (uint32_t)src[1 + 4 * t] | ((uint32_t)src[2 + 4 * t] << 16);
+        v.y = (uint32_t)src[3 + 4 * t] | ((uint32_t)src[4 + 4 * t] << 16);
+        *reinterpret_cast<uint2 *>(packed + a.quant) = v;
+      }
+    }
+  }
 }
 
 // Raw block-stream matvec for the qualification cases: one warp per row.
@@ -590,6 +649,22 @@ cudaError_t launch_dequant(int dtype, const uint8_t *src, float *dst, size_t n, 
     k_dequant<MER_DTYPE_Q8_0><<<blocks, 256, 0, s>>>(src, dst, n);
   else
     k_dequant<MER_DTYPE_Q4_0><<<blocks, 256, 0, s>>>(src, dst, n);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dequant_packed(int dtype, const uint8_t *expert, int matrix, uint32_t D, uint32_t F, float *dst, cudaStream_t s) {
+  if (dtype == MER_DTYPE_Q8_0)
+    k_dequant_packed<MER_DTYPE_Q8_0><<<148 * 8, 256, 0, s>>>(expert, matrix, D, F, dst);
+  else
+    k_dequant_packed<MER_DTYPE_Q4_0><<<148 * 8, 256, 0, s>>>(expert, matrix, D, F, dst);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_repack(int dtype, const uint8_t *flat, uint8_t *packed, uint32_t D, uint32_t F, cudaStream_t s) {
+  if (dtype == MER_DTYPE_Q8_0)
+    k_repack<MER_DTYPE_Q8_0><<<148 * 8, 256, 0, s>>>(flat, packed, D, F);
+  else
+    k_repack<MER_DTYPE_Q4_0><<<148 * 8, 256, 0, s>>>(flat, packed, D, F);
   return cudaGetLastError();
 }
 

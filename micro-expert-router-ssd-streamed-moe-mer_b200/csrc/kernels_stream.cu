@@ -1,9 +1,10 @@
 // Streaming expert FFN for decode-sized token groups (a few tokens per expert): HBM-bound.
 //
 // Data flow per projection phase (gate/up, then down):
-//   * Raw Q4_0 / Q8_0 row segments are copied global -> shared memory by bulk async copies
-//     (cp.async.bulk, completion on an mbarrier) through a multi-stage ring: every byte of an
-//     expert is read from HBM once, 16-byte aligned and fully coalesced.
+//   * Experts are resident in the tile-major fragment layout of layout.cuh (the reference's bytes,
+//     permuted at admission).  A stage of the ring is two contiguous 16-row tile chunks, each moved
+//     global -> shared memory by ONE bulk async copy (cp.async.bulk, completion on an mbarrier):
+//     every byte of an expert is read from HBM once, as a linear stream.
 //   * Warps unpack the integer part of the weights straight into f16 mma.sync A fragments.  A
 //     4-bit or 8-bit field masked into the low mantissa bits of an f16 IS the subnormal value
 //     q * 2^-24 (q * 2^-20 for a field at bits 4..7), so unpacking is one LOP3 per two weights and
@@ -31,7 +32,6 @@ namespace {
 
 constexpr int CONSUMER_WARPS = 16;
 constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;  // + one producer warp
-constexpr int ROWCHUNKS = 32;                       // row segments per stage: 2 M-tiles x 16 row slots
 constexpr int KSPLIT_WARPS = CONSUMER_WARPS / 2;    // warps that split the K range of one M-tile
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr float POW2_24 = 16777216.0f;
@@ -49,7 +49,7 @@ struct StreamParams {
   uint32_t n_ksplit;
   uint32_t kc;               // blocks per pipeline stage
   uint32_t n_stages;
-  uint32_t row_stride;       // bytes between row segments in a stage (padded against bank conflicts)
+  uint32_t chunk_stride;     // bytes between the two 16-row tile chunks of a stage (kc * 16 * block bytes)
   uint32_t frag_stride;      // bytes between (token, part) fragment arrays in shared memory
   uint32_t tokens_per_pass;  // 4 * NT
   const uint32_t *n_passes;  // device scalar
@@ -102,14 +102,9 @@ __device__ __forceinline__ uint32_t lds32(uint32_t a) {
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
   return v;
 }
-__device__ __forceinline__ uint32_t lds16(uint32_t a) {
-  uint16_t v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ float ldsf(uint32_t a) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
   return v;
 }
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
@@ -216,42 +211,23 @@ __global__ void __launch_bounds__(256) k_act_prep(const float *__restrict__ a, u
 }
 
 // ------------------------------------------------------------------------ weight unpacking
-// Eight weights of one row of one block -> four f16x2 registers holding the integer fields as
-// subnormals: {MMA0.k(2t,2t+1), MMA0.k(2t+8,2t+9), MMA1.k(2t,2t+1), MMA1.k(2t+8,2t+9)}, plus the
-// block scale.  `ba` is the shared address of the block start, `toff` = 4t (Q4_0) or 8t (Q8_0).
-// Row segments start 16-byte aligned and blocks are 18 / 34 bytes, so the quants of odd blocks are
-// word aligned and those of even blocks sit two bytes past a word: ODD is uniform per warp.
-template <int DT, bool ODD>
-__device__ __forceinline__ void load_unpack(uint32_t ba, uint32_t toff, uint32_t (&r)[4], float &scale) {
-  scale = __half2float(__ushort_as_half((unsigned short)lds16(ba)));
-  if (DT == MER_DTYPE_Q4_0) {
-    uint32_t v;
-    if (ODD) {
-      v = lds32(ba + 2 + toff);
-    } else {
-      uint32_t w0 = lds32(ba + toff), w1 = lds32(ba + toff + 4);
-      v = __funnelshift_r(w0, w1, 16);
-    }
-    uint32_t v8 = v >> 8;
-    r[0] = v & 0x000F000Fu;   // low nibbles of bytes 0, 2  -> elements 4t, 4t+2
-    r[1] = v8 & 0x000F000Fu;  // low nibbles of bytes 1, 3  -> elements 4t+1, 4t+3
-    r[2] = v & 0x00F000F0u;   // high nibbles               -> elements 16 + ... (x16, undone on the activation side)
-    r[3] = v8 & 0x00F000F0u;
-  } else {
-    uint32_t lo, hi;
-    if (ODD) {
-      lo = lds32(ba + 2 + toff), hi = lds32(ba + 6 + toff);
-    } else {
-      uint32_t w0 = lds32(ba + toff), w1 = lds32(ba + toff + 4), w2 = lds32(ba + toff + 8);
-      lo = __funnelshift_r(w0, w1, 16), hi = __funnelshift_r(w1, w2, 16);
-    }
-    // int8 -> biased unsigned byte (q + 128) in the low mantissa bits
-    r[0] = (lo ^ 0x80808080u) & 0x00FF00FFu;
-    r[1] = ((lo >> 8) ^ 0x00808080u) & 0x00FF00FFu;
-    r[2] = (hi ^ 0x80808080u) & 0x00FF00FFu;
-    r[3] = ((hi >> 8) ^ 0x00808080u) & 0x00FF00FFu;
-  }
+// Eight weights of one row slot of one block -> four f16x2 registers holding the integer fields as
+// subnormals: {MMA0.k(2t,2t+1), MMA0.k(2t+8,2t+9), MMA1.k(2t,2t+1), MMA1.k(2t+8,2t+9)}.
+__device__ __forceinline__ void unpack_q4(uint32_t v, uint32_t (&r)[4]) {
+  const uint32_t v8 = v >> 8;
+  r[0] = v & 0x000F000Fu;   // low nibbles of bytes 0, 2  -> elements 4t, 4t+2
+  r[1] = v8 & 0x000F000Fu;  // low nibbles of bytes 1, 3  -> elements 4t+1, 4t+3
+  r[2] = v & 0x00F000F0u;   // high nibbles -> elements 16 + ... (x16, undone on the activation side)
+  r[3] = v8 & 0x00F000F0u;
 }
+__device__ __forceinline__ void unpack_q8(uint32_t lo, uint32_t hi, uint32_t (&r)[4]) {
+  // int8 -> biased unsigned byte (q + 128) in the low mantissa bits
+  r[0] = (lo ^ 0x80808080u) & 0x00FF00FFu;
+  r[1] = ((lo >> 8) ^ 0x00808080u) & 0x00FF00FFu;
+  r[2] = (hi ^ 0x80808080u) & 0x00FF00FFu;
+  r[3] = ((hi >> 8) ^ 0x00808080u) & 0x00FF00FFu;
+}
+__device__ __forceinline__ float2 h2_to_f2(uint32_t v) { return __half22float2(*reinterpret_cast<const __half2 *>(&v)); }
 
 template <int DT>
 struct BlockBytes {
@@ -276,8 +252,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   float *s_init = s_red + 2 * CONSUMER_WARPS * NT * 128;                    // [TP][kb_split]
   uint8_t *s_frag = reinterpret_cast<uint8_t *>(s_init + p.kb_split * TP);  // [TP*2][frag_stride]
   s_frag = reinterpret_cast<uint8_t *>(((size_t)s_frag + 127) & ~(size_t)127);
-  uint8_t *s_stage = s_frag + (size_t)TP * 2 * p.frag_stride;               // [n_stages][32 * row_stride + 128]
-  const uint32_t stage_bytes = ROWCHUNKS * p.row_stride + 128;
+  uint8_t *s_stage = s_frag + (size_t)TP * 2 * p.frag_stride;               // [n_stages][2 tiles][chunk_stride]
+  const uint32_t stage_bytes = 2 * p.chunk_stride;
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < p.n_stages; s++) {
@@ -296,7 +272,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   const uint32_t item_beg = (uint32_t)(n_items * blockIdx.x / gridDim.x), item_end = (uint32_t)(n_items * (blockIdx.x + 1) / gridDim.x);
   if (item_beg >= item_end) return;
   const size_t proj_bytes = (size_t)d.D * d.F / 32 * BB;
-  const size_t row_bytes = (size_t)p.kb_total * BB;
+  const size_t tile_bytes = (size_t)p.kb_total * 16 * BB;  // one packed 16-row tile, all of K
 
   // items are ordered (pass, K split, tile); a CTA decodes its first item once and then steps
   uint32_t tile = item_beg % n_tiles, ks = (item_beg / n_tiles) % p.n_ksplit, pp = item_beg / n_tiles / p.n_ksplit;
@@ -312,7 +288,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   };
 
   if (warp == CONSUMER_WARPS) {
-    // ------------------------------ producer warp: lane i copies row segment i of every stage
+    // ------------------------------ producer warp: lanes 0 and 1 each copy one tile chunk per stage
     uint32_t stage = 0, round = 0;
     bool ok = true;
     for (uint32_t item = item_beg; item < item_end && ok; item++, next_item()) {
@@ -321,24 +297,19 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       uint32_t eid = d.group_expert[p.pass_group[pp]];
       const uint8_t *base = (eid < d.max_experts) ? d.expert_ptr[eid] : nullptr;
       if (!base) continue;  // consumers skip the same item
-      const uint8_t *src;
-      if (p.phase == 0) {
-        uint32_t m = lane >> 4, r = lane & 15;
-        uint32_t row = tile * 16 + m * 8 + (r & 7);
-        src = base + (r >= 8 ? proj_bytes : 0) + (size_t)row * row_bytes;
-      } else {
-        src = base + 2 * proj_bytes + (size_t)(tile * 32 + lane) * row_bytes;
-      }
+      // item tile -> packed tiles 2*tile and 2*tile + 1 of the phase's region; lanes 0 and 1 copy one each
+      const uint8_t *src = base + (p.phase == 0 ? 0 : 2 * proj_bytes) + (size_t)(2 * tile + (lane & 1)) * tile_bytes;
       for (uint32_t c0 = 0; c0 < kbn && ok; c0 += p.kc) {
         uint32_t nb = min(p.kc, kbn - c0);
         if (round > 0) ok = mbar_wait(&empty[stage], (round - 1) & 1);
         if (*(volatile uint32_t *)s_abort) ok = false;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (lane == 0) mbar_expect_tx(&full[stage], ROWCHUNKS * nb * BB);
+        if (lane == 0) mbar_expect_tx(&full[stage], 2 * nb * 16 * BB);
         __syncwarp();
-        bulk_g2s(s_stage + (size_t)stage * stage_bytes + lane * p.row_stride, src + (size_t)(kb0 + c0) * BB, nb * BB,
-                 &full[stage]);
+        if (lane < 2)
+          bulk_g2s(s_stage + (size_t)stage * stage_bytes + lane * p.chunk_stride, src + (size_t)(kb0 + c0) * 16 * BB, nb * 16 * BB,
+                   &full[stage]);
         if (++stage == p.n_stages) stage = 0, round++;
       }
     }
@@ -356,9 +327,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   // ---------------------------------------------------------------------- consumer warps
   const uint32_t g = lane >> 2, t = lane & 3;
   const uint32_t mtile = warp & 1, kpart = warp >> 1;  // M-tile of the stage, eighth of its K range
-  const uint32_t toff = (DT == MER_DTYPE_Q4_0 ? 4u : 8u) * t;
-  const uint32_t stage0 = smem_u32(s_stage) + (mtile * 16 + g) * p.row_stride;  // row g of this warp's M-tile, stage 0
-  const uint32_t row8 = 8 * p.row_stride;
+  const uint32_t stage0 = smem_u32(s_stage) + mtile * p.chunk_stride;  // this warp's tile chunk in stage 0
   const uint32_t frag0 = smem_u32(s_frag) + t * 16, init0 = smem_u32(s_init);
   float *s_red2 = s_red;  // [2 buffers][CONSUMER_WARPS][NT][4][32]
   uint32_t stage = 0, round = 0, act_round = 0, red_buf = 0;
@@ -445,25 +414,41 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
     for (int n = 0; n < NT; n++) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
     const uint32_t n_live = (pcount + 3) >> 2;  // N-tiles that hold tokens
 
-    // one block of both rows against every live N-tile; kb = block index within the K split
-    auto do_block = [&](uint32_t ba, uint32_t kb, auto odd_tag) {
-      constexpr bool ODD = decltype(odd_tag)::value;
-      uint32_t a_lo[4], a_hi[4];
-      float d_lo, d_hi;
-      load_unpack<DT, ODD>(ba, toff, a_lo, d_lo);
-      load_unpack<DT, ODD>(ba + row8, toff, a_hi, d_hi);
+    // two adjacent blocks (kb, kb + 1; kb even) of both row slots against every live N-tile.
+    // rec = shared address of the pair's first record in this warp's tile chunk.
+    auto do_pair = [&](uint32_t rec, uint32_t kb) {
+      uint32_t a0[4], a0h[4], a1[4], a1h[4];  // block kb: slots g / g+8; block kb+1: slots g / g+8
+      float2 d0, d1;                          // {scale slot g, scale slot g+8} of each block
+      if (DT == MER_DTYPE_Q4_0) {
+        const uint4 w = lds128(rec + lane * 16);
+        const uint2 sc = lds64(rec + 512 + g * 8);
+        unpack_q4(w.x, a0), unpack_q4(w.y, a0h), unpack_q4(w.z, a1), unpack_q4(w.w, a1h);
+        d0 = h2_to_f2(sc.x), d1 = h2_to_f2(sc.y);
+      } else {
+        const uint4 w0 = lds128(rec + lane * 16), w1 = lds128(rec + 544 + lane * 16);
+        const uint32_t sc0 = lds32(rec + 512 + g * 4), sc1 = lds32(rec + 544 + 512 + g * 4);
+        unpack_q8(w0.x, w0.y, a0), unpack_q8(w0.z, w0.w, a0h), unpack_q8(w1.x, w1.y, a1), unpack_q8(w1.z, w1.w, a1h);
+        d0 = h2_to_f2(sc0), d1 = h2_to_f2(sc1);
+      }
 #pragma unroll
       for (int n = 0; n < NT; n++) {
         if (n > 0 && (uint32_t)n >= n_live) break;  // uniform
-        const uint4 bf = lds128(fa[n] + kb * 64);
-        const float seed = ldsf(ia[n] + kb * 4);
-        float c1[4], c2[4];
-        mma_f16(c1, a_lo[0], a_hi[0], a_lo[1], a_hi[1], bf.x, bf.y, seed, 0.0f, seed, 0.0f);
-        mma_f16(c2, a_lo[2], a_hi[2], a_lo[3], a_hi[3], bf.z, bf.w, c1[0], c1[1], c1[2], c1[3]);
-        acc[n][0] = fmaf(d_lo, c2[0], acc[n][0]);
-        acc[n][1] = fmaf(d_lo, c2[1], acc[n][1]);
-        acc[n][2] = fmaf(d_hi, c2[2], acc[n][2]);
-        acc[n][3] = fmaf(d_hi, c2[3], acc[n][3]);
+        const uint4 bf0 = lds128(fa[n] + kb * 64), bf1 = lds128(fa[n] + kb * 64 + 64);
+        const uint2 sd = lds64(ia[n] + kb * 4);
+        const float seed0 = __uint_as_float(sd.x), seed1 = __uint_as_float(sd.y);
+        float c1[4], c2[4], e1[4], e2[4];
+        mma_f16(c1, a0[0], a0h[0], a0[1], a0h[1], bf0.x, bf0.y, seed0, 0.0f, seed0, 0.0f);
+        mma_f16(e1, a1[0], a1h[0], a1[1], a1h[1], bf1.x, bf1.y, seed1, 0.0f, seed1, 0.0f);
+        mma_f16(c2, a0[2], a0h[2], a0[3], a0h[3], bf0.z, bf0.w, c1[0], c1[1], c1[2], c1[3]);
+        mma_f16(e2, a1[2], a1h[2], a1[3], a1h[3], bf1.z, bf1.w, e1[0], e1[1], e1[2], e1[3]);
+        acc[n][0] = fmaf(d0.x, c2[0], acc[n][0]);
+        acc[n][1] = fmaf(d0.x, c2[1], acc[n][1]);
+        acc[n][2] = fmaf(d0.y, c2[2], acc[n][2]);
+        acc[n][3] = fmaf(d0.y, c2[3], acc[n][3]);
+        acc[n][0] = fmaf(d1.x, e2[0], acc[n][0]);
+        acc[n][1] = fmaf(d1.x, e2[1], acc[n][1]);
+        acc[n][2] = fmaf(d1.y, e2[2], acc[n][2]);
+        acc[n][3] = fmaf(d1.y, e2[3], acc[n][3]);
       }
     };
 
@@ -472,21 +457,15 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       if (!dead && !mbar_wait(&full[stage], round & 1)) dead = true;
       dead = __any_sync(0xffffffffu, dead);
       if (!dead) {
-        uint32_t ba = stage0 + stage * stage_bytes + kpart * BB;
-        uint32_t kb = c0 + kpart;
-        // this warp's blocks kpart, kpart + 8, ... all have the parity of kpart; two per iteration
-        if (kpart & 1) {
+        constexpr uint32_t PAIR_BYTES = 2 * 16 * BB;  // 576 (Q4_0) / 1088 (Q8_0)
+        const uint32_t np = nb >> 1;                  // block pairs in this chunk
+        uint32_t rec = stage0 + stage * stage_bytes + kpart * PAIR_BYTES;
+        uint32_t kb = c0 + 2 * kpart;
+        // this warp's pairs kpart, kpart + 8, ...; two pairs per iteration keep independent chains in flight
 #pragma unroll 1
-          for (uint32_t b = kpart; b < nb; b += 2 * KSPLIT_WARPS, ba += 2 * KSPLIT_WARPS * BB, kb += 2 * KSPLIT_WARPS) {
-            do_block(ba, kb, std::true_type{});
-            if (b + KSPLIT_WARPS < nb) do_block(ba + KSPLIT_WARPS * BB, kb + KSPLIT_WARPS, std::true_type{});
-          }
-        } else {
-#pragma unroll 1
-          for (uint32_t b = kpart; b < nb; b += 2 * KSPLIT_WARPS, ba += 2 * KSPLIT_WARPS * BB, kb += 2 * KSPLIT_WARPS) {
-            do_block(ba, kb, std::false_type{});
-            if (b + KSPLIT_WARPS < nb) do_block(ba + KSPLIT_WARPS * BB, kb + KSPLIT_WARPS, std::false_type{});
-          }
+        for (uint32_t pr = kpart; pr < np; pr += 2 * KSPLIT_WARPS, rec += 2 * KSPLIT_WARPS * PAIR_BYTES, kb += 4 * KSPLIT_WARPS) {
+          do_pair(rec, kb);
+          if (pr + KSPLIT_WARPS < np) do_pair(rec + KSPLIT_WARPS * PAIR_BYTES, kb + 2 * KSPLIT_WARPS);
         }
       }
       __syncwarp();
@@ -600,7 +579,7 @@ __global__ void k_reduce_ksplit(const float *__restrict__ part, float *__restric
 }
 
 struct Plan {
-  uint32_t nt, kc, n_stages, row_stride, frag_stride, kb_split, n_ksplit;
+  uint32_t nt, kc, n_stages, chunk_stride, frag_stride, kb_split, n_ksplit;
   size_t smem;
 };
 
@@ -621,15 +600,12 @@ Plan make_plan(int dtype, uint32_t kb_total, int phase, uint32_t nt) {
   size_t fixed = 256 + (size_t)2 * CONSUMER_WARPS * nt * 128 * 4 + (size_t)kb_split * tp * 4 + 128 + (size_t)tp * 2 * frag_stride;
   for (uint32_t kc = 64; kc >= 8; kc -= 8) {
     if (kc > kb_split && kc != 8) continue;
-    uint32_t chunk = kc * bb;
-    uint32_t want = dtype == MER_DTYPE_Q4_0 ? 16u : 32u;  // row stride mod 128 that spreads 8 rows over the banks
-    uint32_t row_stride = chunk + ((want + 128 - chunk % 128) % 128);
-    if (row_stride < chunk + 16) row_stride += 128;  // slack for the aligned over-read of the last words
-    size_t stage = (size_t)ROWCHUNKS * row_stride + 128;
+    uint32_t chunk = kc * 16 * bb;  // one tile chunk; a stage holds two
+    size_t stage = 2 * (size_t)chunk;
     if (fixed + 3 * stage > SMEM_LIMIT) continue;
     uint32_t n_stages = (uint32_t)((SMEM_LIMIT - fixed) / stage);
     if (n_stages > 6) n_stages = 6;
-    best = Plan{nt, kc, n_stages, row_stride, frag_stride, kb_split, n_ksplit, fixed + n_stages * stage};
+    best = Plan{nt, kc, n_stages, chunk, frag_stride, kb_split, n_ksplit, fixed + n_stages * stage};
     break;
   }
   return best;
@@ -726,7 +702,7 @@ cudaError_t launch_ffn_stream(const MoeDispatch &d, void *scratch, int sm_count,
   // phase 0: gate/up
   p.phase = 0, p.afrag = xfrag, p.ainit = xinit, p.aunscale = xun, p.act_per_pair = 0;
   p.rows = d.F, p.kb_total = d.D / 32, p.kb_split = pg.kb_split, p.n_ksplit = pg.n_ksplit, p.kc = pg.kc;
-  p.n_stages = pg.n_stages, p.row_stride = pg.row_stride, p.frag_stride = pg.frag_stride;
+  p.n_stages = pg.n_stages, p.chunk_stride = pg.chunk_stride, p.frag_stride = pg.frag_stride;
   p.out = d.h, p.amax = amax;
   e = d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, pg.smem, sm_count, s)
                                 : launch_phase<MER_DTYPE_Q8_0>(p, nt, pg.smem, sm_count, s);
@@ -742,7 +718,7 @@ cudaError_t launch_ffn_stream(const MoeDispatch &d, void *scratch, int sm_count,
   float *ypart = pd.n_ksplit > 1 ? reinterpret_cast<float *>(base + L.ypart) : d.y;
   p.phase = 1, p.afrag = hfrag, p.ainit = hinit, p.aunscale = hun, p.act_per_pair = 1;
   p.rows = d.D, p.kb_total = d.F / 32, p.kb_split = pd.kb_split, p.n_ksplit = pd.n_ksplit, p.kc = pd.kc;
-  p.n_stages = pd.n_stages, p.row_stride = pd.row_stride, p.frag_stride = pd.frag_stride;
+  p.n_stages = pd.n_stages, p.chunk_stride = pd.chunk_stride, p.frag_stride = pd.frag_stride;
   p.out = ypart, p.amax = nullptr;
   e = d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, pd.smem, sm_count, s)
                                 : launch_phase<MER_DTYPE_Q8_0>(p, nt, pd.smem, sm_count, s);

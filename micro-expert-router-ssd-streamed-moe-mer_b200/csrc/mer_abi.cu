@@ -75,6 +75,8 @@ struct mer_backend {
   uint32_t *h_u32 = nullptr;  // pinned [max_pairs + 1]: ids up/down, status
   float *h_f32 = nullptr;     // pinned [max_pairs]
   float *d_dequant = nullptr;
+  bool packed = false;          // slots hold the tile-major fragment layout (block-aligned shapes)
+  uint8_t *d_raw_stage = nullptr;  // device copy of one flat blob, source of the repack at admission
 
   std::unordered_map<uint32_t, RouterEntry> routers;
   int kernel_path = 0;
@@ -137,6 +139,7 @@ MoeDispatch base_dispatch(mer_backend *b) {
   d.logits = b->d_logits;
   d.swiglu_limit = b->cfg.swiglu_limit;
   d.scratch_pairs = b->max_pairs;
+  d.packed = b->packed ? 1 : 0;
   return d;
 }
 
@@ -241,7 +244,7 @@ void free_all(mer_backend *b) {
   b->routers.clear();
   F(b->arena), F(b->d_expert_ptr), F(b->d_x), F(b->d_out), F(b->d_h), F(b->d_y), F(b->d_pair_weight), F(b->d_logits);
   F(b->d_pair_expert), F(b->d_group_expert), F(b->d_offsets), F(b->d_perm), F(b->d_status), F(b->d_counters);
-  F(b->d_f16), F(b->d_stream_scratch), F(b->d_dequant);
+  F(b->d_f16), F(b->d_stream_scratch), F(b->d_dequant), F(b->d_raw_stage);
   H(b->h_expert_ptr), H(b->h_stage[0]), H(b->h_stage[1]), H(b->h_hdr), H(b->h_u32), H(b->h_f32);
   if (b->ev_compute_done) cudaEventDestroy(b->ev_compute_done);
   if (b->ev_copy_done) cudaEventDestroy(b->ev_copy_done);
@@ -325,16 +328,20 @@ int admit_impl(mer_backend *b, uint32_t id, uint64_t generation, const void *blo
   CU(MER_ERR_UPLOAD, "cudaStreamWaitEvent", cudaStreamWaitEvent(b->copy, b->ev_compute_done, 0));
   uint8_t *slot_base = b->arena + si * b->slot_stride;
   uint8_t *payload = slot_base + SLOT_HEADER_BYTES;
+  uint8_t *landing = b->packed ? b->d_raw_stage : payload;  // packed slots: land flat bytes in staging, then permute
   const uint8_t *src = static_cast<const uint8_t *>(blob);
   if (from_device) {
-    CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(D2D)", cudaMemcpyAsync(payload, src, b->expert_bytes, cudaMemcpyDeviceToDevice, b->copy));
+    if (b->packed)
+      landing = const_cast<uint8_t *>(src);  // permute straight out of the caller's device buffer
+    else
+      CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(D2D)", cudaMemcpyAsync(payload, src, b->expert_bytes, cudaMemcpyDeviceToDevice, b->copy));
   } else {
     cudaPointerAttributes attr{};
     bool pinned = cudaPointerGetAttributes(&attr, blob) == cudaSuccess && attr.type == cudaMemoryTypeHost;
     cudaGetLastError();
     if (pinned) {
       CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(H2D pinned)",
-         cudaMemcpyAsync(payload, src, b->expert_bytes, cudaMemcpyHostToDevice, b->copy));
+         cudaMemcpyAsync(landing, src, b->expert_bytes, cudaMemcpyHostToDevice, b->copy));
     } else {
       int which = 0;
       for (size_t off = 0; off < b->expert_bytes; off += STAGE_BYTES, which ^= 1) {
@@ -342,11 +349,14 @@ int admit_impl(mer_backend *b, uint32_t id, uint64_t generation, const void *blo
         CU(MER_ERR_UPLOAD, "cudaEventSynchronize(stage)", cudaEventSynchronize(b->ev_stage[which]));
         memcpy(b->h_stage[which], src + off, n);
         CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(H2D staged)",
-           cudaMemcpyAsync(payload + off, b->h_stage[which], n, cudaMemcpyHostToDevice, b->copy));
+           cudaMemcpyAsync(landing + off, b->h_stage[which], n, cudaMemcpyHostToDevice, b->copy));
         CU(MER_ERR_UPLOAD, "cudaEventRecord(stage)", cudaEventRecord(b->ev_stage[which], b->copy));
       }
     }
   }
+  if (b->packed)
+    CU(MER_ERR_UPLOAD, "repack kernel",
+       launch_repack(b->cfg.dtype, landing, payload, (uint32_t)b->cfg.d_model, (uint32_t)b->cfg.d_ff, b->copy));
   SlotHeader *hdr = b->h_hdr + si;
   hdr->epoch = generation;
   hdr->expert_id = id;
@@ -518,6 +528,8 @@ MER_EXPORT int mer_backend_create(const mer_backend_cfg *cfg, mer_backend **out)
   CB(cudaHostAlloc((void **)&b->h_u32, (P + 1) * 4, cudaHostAllocDefault));
   CB(cudaHostAlloc((void **)&b->h_f32, P * 4, cudaHostAllocDefault));
   if (stream_ffn_supported(cfg->dtype, (uint32_t)D, (uint32_t)F)) {
+    b->packed = true;
+    CB(cudaMalloc((void **)&b->d_raw_stage, b->expert_bytes));
     size_t sb = stream_ffn_scratch_bytes((uint32_t)P, (uint32_t)D, (uint32_t)F);
     if (sb) {
       CB(cudaMalloc(&b->d_stream_scratch, sb));
@@ -878,9 +890,15 @@ MER_EXPORT int mer_dequant_projection_f32(mer_backend *b, uint32_t expert_id, in
   if (rc) return rc;
   size_t n = (size_t)b->cfg.d_model * b->cfg.d_ff;
   if (!b->d_dequant) CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(dequant)", cudaMalloc((void **)&b->d_dequant, n * 4));
-  const uint8_t *src = b->h_expert_ptr[expert_id] + (size_t)projection * (b->expert_bytes / 3);
   CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, b->compute));
-  CU(MER_ERR_SUBMISSION, "dequant kernel", launch_dequant(b->cfg.dtype, src, b->d_dequant, n, b->compute));
+  if (b->packed) {
+    CU(MER_ERR_SUBMISSION, "dequant kernel",
+       launch_dequant_packed(b->cfg.dtype, b->h_expert_ptr[expert_id], projection, (uint32_t)b->cfg.d_model, (uint32_t)b->cfg.d_ff,
+                             b->d_dequant, b->compute));
+  } else {
+    const uint8_t *src = b->h_expert_ptr[expert_id] + (size_t)projection * (b->expert_bytes / 3);
+    CU(MER_ERR_SUBMISSION, "dequant kernel", launch_dequant(b->cfg.dtype, src, b->d_dequant, n, b->compute));
+  }
   CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(out)", cudaMemcpyAsync(out, b->d_dequant, n * 4, cudaMemcpyDeviceToHost, b->compute));
   CU(MER_ERR_READBACK_MAP, "cudaStreamSynchronize", cudaStreamSynchronize(b->compute));
   b->ctr.kernel_launches++;
