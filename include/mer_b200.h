@@ -220,6 +220,23 @@ int mer_qualification_matvec(mer_backend *b, int32_t dtype, const void *weights,
                              const float *input, size_t rows, size_t columns, size_t w_block_off,
                              float *out);
 
+/* ---- no-allocation variant (no counterpart in the reference) ----
+ * One expert's SwiGLU FFN for up to MER_NOALLOC_MAX_TOKENS rows, for callers that cannot let a
+ * library allocate device memory: no backend handle, no cudaMalloc/cudaFree, no allocating library
+ * call.  d_expert_blob is the flat gate||up||down block stream in device memory; d_x is
+ * [n_tokens x d_model] f32 and d_out [n_tokens x d_model] f32, both device pointers; work is enqueued
+ * on `stream` of the CURRENT device and not synchronised.  The silu(gate)*up intermediate lives in a
+ * fixed array inside the library (about 0.5 MiB, held by every GPU that loads the library until the
+ * process exits), so: sizes beyond the maxima below are refused with MER_ERR_VALIDATION_DISPATCH and a
+ * message in `err`; all calls on one GPU share that array, so two calls that overlap on the GPU (two
+ * streams, two threads) race - serialise them; the first call on a device looks the array's address
+ * up, so make that first call outside any stream capture.  Runs the generic fp32 kernels. */
+#define MER_NOALLOC_MAX_TOKENS 8
+#define MER_NOALLOC_MAX_DIM 16384
+int mer_expert_forward_noalloc(int32_t dtype, uint64_t d_model, uint64_t d_ff, const void *d_expert_blob,
+                               const float *d_x, size_t n_tokens, float *d_out, float swiglu_limit,
+                               void *stream, char *err, size_t err_len);
+
 /* ---- per-stage device timing: StageTimings (stage_timing.rs:6-29) with the reference's stage
  * names, measured with CUDA events on the stream each layer call is enqueued on. ---- */
 typedef struct mer_stage_timings {

@@ -228,3 +228,17 @@ class Backend:
         out = np.empty(self.d_model * self.d_ff, np.float32)
         self._check(self.lib.mer_dequant_projection_f32(self.h, expert_id, projection, _ptr(out)))
         return out
+
+
+NOALLOC_MAX_TOKENS, NOALLOC_MAX_DIM = 8, 16384
+
+
+def expert_forward_noalloc(dtype, d_model, d_ff, d_expert_blob, d_x, n_tokens, d_out, swiglu_limit=0.0, stream=0):
+    """mer_expert_forward_noalloc: device pointers (ints) in and out, nothing allocated, asynchronous on
+    `stream` of the current device.  All calls on a GPU share one fixed scratch array inside the library,
+    so the caller must not let two of them overlap."""
+    msg = C.create_string_buffer(256)
+    rc = capi.load_library().mer_expert_forward_noalloc(dtype, d_model, d_ff, C.c_void_p(d_expert_blob), C.c_void_p(d_x),
+                                                        n_tokens, C.c_void_p(d_out), swiglu_limit, C.c_void_p(stream), msg, 256)
+    if rc != 0:
+        raise GpuExpertDispatchError(0, capi.EXPERT_NONE, rc, msg.value.decode(errors="replace"))

@@ -76,6 +76,7 @@ ABI_SYMBOLS = {
     "mer_qualification_matvec": (C.c_int, [_vp, C.c_int32, _vp, _sz, _vp, _sz, _sz, _sz, _vp]),
     "mer_stage_timing_enable": (C.c_int, [_vp, _i32]),
     "mer_stage_timings_read": (C.c_int, [_vp, C.POINTER(MerStageTimings)]),
+    "mer_expert_forward_noalloc": (C.c_int, [C.c_int32, _u64, _u64, _vp, _vp, _sz, _vp, C.c_float, _vp, C.c_char_p, _sz]),
     "mer_last_error": (C.c_int, [_vp, C.POINTER(MerErrorInfo)]),
     "mer_snapshot": (C.c_int, [_vp, C.POINTER(MerCounters)]),
     "mer_set_kernel_path": (C.c_int, [_vp, _i32]),
