@@ -46,6 +46,8 @@ struct MoeDispatch {
   float *logits;            // [n_tokens x E] scratch
   float swiglu_limit;       // <= 0 = off
   uint32_t scratch_pairs;   // pair capacity the streaming scratch was sized for
+  uint32_t max_group_tokens;  // upper bound on the pairs of any one group in this dispatch
+  uint32_t active_groups_hint;  // expected number of non-empty groups (shapes the work split)
   int packed;               // 1: slots hold the tile-major fragment layout (layout.cuh), 0: the flat block stream
 };
 

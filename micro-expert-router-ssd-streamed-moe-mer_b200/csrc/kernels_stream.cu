@@ -32,7 +32,6 @@ namespace {
 
 constexpr int CONSUMER_WARPS = 16;
 constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;  // + one producer warp
-constexpr int KSPLIT_WARPS = CONSUMER_WARPS / 2;    // warps that split the K range of one M-tile
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr float POW2_24 = 16777216.0f;
 
@@ -49,7 +48,10 @@ struct StreamParams {
   uint32_t n_ksplit;
   uint32_t kc;               // blocks per pipeline stage
   uint32_t n_stages;
-  uint32_t chunk_stride;     // bytes between the two 16-row tile chunks of a stage (kc * 16 * block bytes)
+  uint32_t chunk_stride;     // bytes between the 16-row tile chunks of a stage (kc * 16 * block bytes)
+  uint32_t mt;               // packed tiles per item (= per stage); the 16 consumer warps form mt groups
+  uint32_t kp;               // warps that split the K range of one tile (mt * kp == 16)
+  uint32_t frag_cols;        // fragment arrays held in shared memory: 2 * min(4 * NT, most tokens of any group)
   uint32_t frag_stride;      // bytes between (token, part) fragment arrays in shared memory
   uint32_t tokens_per_pass;  // 4 * NT
   const uint32_t *n_passes;  // device scalar
@@ -252,8 +254,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   float *s_init = s_red + 2 * CONSUMER_WARPS * NT * 128;                    // [TP][kb_split]
   uint8_t *s_frag = reinterpret_cast<uint8_t *>(s_init + p.kb_split * TP);  // [TP*2][frag_stride]
   s_frag = reinterpret_cast<uint8_t *>(((size_t)s_frag + 127) & ~(size_t)127);
-  uint8_t *s_stage = s_frag + (size_t)TP * 2 * p.frag_stride;               // [n_stages][2 tiles][chunk_stride]
-  const uint32_t stage_bytes = 2 * p.chunk_stride;
+  uint8_t *s_stage = s_frag + (size_t)p.frag_cols * p.frag_stride;          // [n_stages][mt tiles][chunk_stride]
+  const uint32_t stage_bytes = p.mt * p.chunk_stride;
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < p.n_stages; s++) {
@@ -266,7 +268,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   }
   __syncthreads();
 
-  const uint32_t n_tiles = p.rows / (p.phase == 0 ? 16u : 32u);
+  const uint32_t n_tiles = p.rows / ((p.phase == 0 ? 8u : 16u) * p.mt);  // items per (pass, K split)
   const uint32_t n_passes = *p.n_passes;
   const uint64_t n_items = (uint64_t)n_passes * p.n_ksplit * n_tiles;
   const uint32_t item_beg = (uint32_t)(n_items * blockIdx.x / gridDim.x), item_end = (uint32_t)(n_items * (blockIdx.x + 1) / gridDim.x);
@@ -288,7 +290,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   };
 
   if (warp == CONSUMER_WARPS) {
-    // ------------------------------ producer warp: lanes 0 and 1 each copy one tile chunk per stage
+    // ------------------------------ producer warp: lane m copies the chunk of tile m of every stage
     uint32_t stage = 0, round = 0;
     bool ok = true;
     for (uint32_t item = item_beg; item < item_end && ok; item++, next_item()) {
@@ -297,17 +299,17 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       uint32_t eid = d.group_expert[p.pass_group[pp]];
       const uint8_t *base = (eid < d.max_experts) ? d.expert_ptr[eid] : nullptr;
       if (!base) continue;  // consumers skip the same item
-      // item tile -> packed tiles 2*tile and 2*tile + 1 of the phase's region; lanes 0 and 1 copy one each
-      const uint8_t *src = base + (p.phase == 0 ? 0 : 2 * proj_bytes) + (size_t)(2 * tile + (lane & 1)) * tile_bytes;
+      // item -> packed tiles mt*tile .. mt*tile + mt - 1 of the phase's region; lane m copies tile m's chunk
+      const uint8_t *src = base + (p.phase == 0 ? 0 : 2 * proj_bytes) + (size_t)(p.mt * tile + (lane % p.mt)) * tile_bytes;
       for (uint32_t c0 = 0; c0 < kbn && ok; c0 += p.kc) {
         uint32_t nb = min(p.kc, kbn - c0);
         if (round > 0) ok = mbar_wait(&empty[stage], (round - 1) & 1);
         if (*(volatile uint32_t *)s_abort) ok = false;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (lane == 0) mbar_expect_tx(&full[stage], 2 * nb * 16 * BB);
+        if (lane == 0) mbar_expect_tx(&full[stage], p.mt * nb * 16 * BB);
         __syncwarp();
-        if (lane < 2)
+        if (lane < p.mt)
           bulk_g2s(s_stage + (size_t)stage * stage_bytes + lane * p.chunk_stride, src + (size_t)(kb0 + c0) * 16 * BB, nb * 16 * BB,
                    &full[stage]);
         if (++stage == p.n_stages) stage = 0, round++;
@@ -326,26 +328,21 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
 
   // ---------------------------------------------------------------------- consumer warps
   const uint32_t g = lane >> 2, t = lane & 3;
-  const uint32_t mtile = warp & 1, kpart = warp >> 1;  // M-tile of the stage, eighth of its K range
+  const uint32_t KP = p.kp;
+  const uint32_t mtile = warp % p.mt, kpart = warp / p.mt;  // tile of the stage, share of its K range
   const uint32_t stage0 = smem_u32(s_stage) + mtile * p.chunk_stride;  // this warp's tile chunk in stage 0
   const uint32_t frag0 = smem_u32(s_frag) + t * 16, init0 = smem_u32(s_init);
-  float *s_red2 = s_red;  // [2 buffers][CONSUMER_WARPS][NT][4][32]
   uint32_t stage = 0, round = 0, act_round = 0, red_buf = 0;
   uint32_t cur_pp = MER_NONE, cur_ks = MER_NONE;
   // A warp whose bounded wait expired goes "dead": it stops computing and waiting but still walks
   // the same loop structure, so the named barriers below always see all consumer warps.
   bool dead = false;
 
-  uint32_t pstart = 0, pcount = 0, clean_from = 0;  // columns >= clean_from of the fragment arrays are zero
+  // Fragment columns and seeds of tokens beyond a pass's count hold stale data (or lie past the
+  // arrays when the dispatch has few tokens per group).  That is harmless: an MMA output column
+  // depends on its own B column only, and the columns of absent tokens are never written out.
+  uint32_t pstart = 0, pcount = 0;
   bool resident = false;
-  {  // the fragment and seed arrays start out zeroed so that unused columns contribute nothing
-    uint4 *z = reinterpret_cast<uint4 *>(s_init);
-    const uint32_t n16 = (uint32_t)((s_stage - reinterpret_cast<uint8_t *>(s_init)) / 16);
-    for (uint32_t i = threadIdx.x; i < n16; i += CONSUMER_WARPS * 32) z[i] = make_uint4(0, 0, 0, 0);
-    // generic-proxy stores, later overwritten by bulk copies (async proxy): fence here, and the
-    // consumer_sync of the first fragment load below orders them before the copy is issued
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
 
   for (uint32_t item = item_beg; item < item_end; item++, next_item()) {
     uint32_t kb0, kbn;
@@ -359,18 +356,6 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
         resident = eid < d.max_experts && d.expert_ptr[eid] != nullptr;
       }
       consumer_sync();
-      if (2 * pcount < clean_from) {
-        // columns that held a previous pass's tokens and stay unused now must read as zero
-        for (uint32_t c = 2 * pcount; c < clean_from; c++) {
-          uint4 *z = reinterpret_cast<uint4 *>(s_frag + (size_t)c * p.frag_stride);
-          for (uint32_t i = threadIdx.x; i < p.kb_split * 4; i += CONSUMER_WARPS * 32) z[i] = make_uint4(0, 0, 0, 0);
-        }
-        for (uint32_t c = pcount; c < clean_from / 2; c++)
-          for (uint32_t i = threadIdx.x; i < p.kb_split; i += CONSUMER_WARPS * 32) s_init[(size_t)c * p.kb_split + i] = 0.0f;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        consumer_sync();
-      }
-      clean_from = 2 * pcount;
       cur_pp = pp, cur_ks = ks;
       if (threadIdx.x == 0) {
         uint32_t bytes_each = kbn * 64;
@@ -391,7 +376,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
     if (!resident) {
       if (threadIdx.x == 0) atomicOr(d.status, MER_DEVSTAT_RESIDENCY_MISS);
       // fail closed: zero outputs for this tile
-      const uint32_t rows_here = p.phase == 0 ? 16u : 32u;
+      const uint32_t rows_here = (p.phase == 0 ? 8u : 16u) * p.mt;
       for (uint32_t i = threadIdx.x; i < rows_here * pcount; i += CONSUMER_WARPS * 32) {
         uint32_t pair = d.perm[pstart + i / rows_here], row = tile * rows_here + i % rows_here;
         if (p.phase == 0)
@@ -461,11 +446,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
         const uint32_t np = nb >> 1;                  // block pairs in this chunk
         uint32_t rec = stage0 + stage * stage_bytes + kpart * PAIR_BYTES;
         uint32_t kb = c0 + 2 * kpart;
-        // this warp's pairs kpart, kpart + 8, ...; two pairs per iteration keep independent chains in flight
+        // this warp's pairs kpart, kpart + KP, ...; two pairs per iteration keep independent chains in flight
 #pragma unroll 1
-        for (uint32_t pr = kpart; pr < np; pr += 2 * KSPLIT_WARPS, rec += 2 * KSPLIT_WARPS * PAIR_BYTES, kb += 4 * KSPLIT_WARPS) {
+        for (uint32_t pr = kpart; pr < np; pr += 2 * KP, rec += 2 * KP * PAIR_BYTES, kb += 4 * KP) {
           do_pair(rec, kb);
-          if (pr + KSPLIT_WARPS < np) do_pair(rec + KSPLIT_WARPS * PAIR_BYTES, kb + 2 * KSPLIT_WARPS);
+          if (pr + KP < np) do_pair(rec + KP * PAIR_BYTES, kb + 2 * KP);
         }
       }
       __syncwarp();
@@ -473,41 +458,52 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       if (++stage == p.n_stages) stage = 0, round++;
     }
 
-    // ---- item epilogue: sum the K-split partials of the eight warps of each M-tile, then write.
-    // s_red is double buffered, so one barrier per item is enough: a buffer is rewritten two items
-    // later, after every warp has passed the barrier of the item in between.
-    float *red = s_red2 + (size_t)red_buf * CONSUMER_WARPS * NT * 128;
-    red_buf ^= 1;
+    // ---- item epilogue: the KP warps of a tile sum their K-split partials, warp kpart == 0 writes.
+    // s_red is double buffered, so one named barrier (per tile group) per item is enough: a buffer
+    // is rewritten two items later, after every warp of the group passed the barrier in between.
+    float v[NT][4];
+    if (KP > 1) {
+      float *red = s_red + (size_t)red_buf * CONSUMER_WARPS * NT * 128;
+      red_buf ^= 1;
 #pragma unroll
-    for (int n = 0; n < NT; n++)
+      for (int n = 0; n < NT; n++)
 #pragma unroll
-      for (int i = 0; i < 4; i++) red[((warp * NT + n) * 4 + i) * 32 + lane] = acc[n][i];
-    consumer_sync();
-    if (warp < 2 && !dead) {  // warp m finishes M-tile m
+        for (int i = 0; i < 4; i++) red[((warp * NT + n) * 4 + i) * 32 + lane] = acc[n][i];
+      asm volatile("bar.sync %0, %1;" ::"r"(2 + mtile), "r"(KP * 32) : "memory");
+      if (kpart == 0) {
+#pragma unroll
+        for (int n = 0; n < NT; n++)
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            float s0 = 0.0f;
+            for (uint32_t k2 = 0; k2 < KP; k2++) s0 += red[(((k2 * p.mt + mtile) * NT + n) * 4 + i) * 32 + lane];
+            v[n][i] = s0;
+          }
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < NT; n++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) v[n][i] = acc[n][i];
+    }
+    if (kpart == 0 && !dead) {
+      const uint32_t ptile = p.mt * tile + mtile;  // packed tile index within the phase's region
 #pragma unroll
       for (int n = 0; n < NT; n++) {
-        if (n > 0 && (uint32_t)(n * 4) >= pcount) break;
-        float v[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          float s0 = 0.0f;
-#pragma unroll
-          for (int kp = 0; kp < KSPLIT_WARPS; kp++) s0 += red[(((kp * 2 + warp) * NT + n) * 4 + i) * 32 + lane];
-          v[i] = s0;
-        }
+        if (n > 0 && (uint32_t)n >= n_live) break;
         const uint32_t tok = n * 4 + t;
         const bool valid = tok < pcount;
         const uint32_t pair = valid ? d.perm[pstart + tok] : 0;
         const uint32_t a = p.act_per_pair ? pair : pair / d.slots;
         const float un = valid ? p.aunscale[a] : 0.0f;
-        const float r_lo = (v[0] + v[1]) * un, r_hi = (v[2] + v[3]) * un;  // rows g and g+8 of the M-tile
+        const float r_lo = (v[n][0] + v[n][1]) * un, r_hi = (v[n][2] + v[n][3]) * un;  // row slots g and g+8
         if (p.phase == 0) {
-          // rows 0..7 of an M-tile are gate rows, rows 8..15 the matching up rows
+          // slots 0..7 of a gate/up tile are gate rows, slots 8..15 the matching up rows
           float gate = r_lo;
           if (d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit) && gate == gate)
             gate = fminf(fmaxf(gate, -d.swiglu_limit), d.swiglu_limit);
           const float hval = silu_f(gate) * r_hi;
-          if (valid) p.out[(size_t)pair * d.F + tile * 16 + warp * 8 + g] = hval;
+          if (valid) p.out[(size_t)pair * d.F + ptile * 8 + g] = hval;
           const float ah = fabsf(hval);
           uint32_t bits = !valid ? 0u : (ah != ah) ? 0x7fc00000u : __float_as_uint(ah);
           // max over the 8 rows held by the lanes that share t (all lanes take part in the shuffles)
@@ -515,7 +511,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
           for (int o = 4; o < 32; o <<= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
           if (valid && g == 0) atomicMax(p.amax + pair, bits);
         } else if (valid) {
-          float *yo = p.out + ((size_t)ks * d.n_tokens * d.slots + pair) * d.D + tile * 32 + warp * 16;
+          float *yo = p.out + ((size_t)ks * d.n_tokens * d.slots + pair) * d.D + ptile * 16;
           yo[g] = r_lo;
           yo[g + 8] = r_hi;
         }
@@ -579,42 +575,55 @@ __global__ void k_reduce_ksplit(const float *__restrict__ part, float *__restric
 }
 
 struct Plan {
-  uint32_t nt, kc, n_stages, chunk_stride, frag_stride, kb_split, n_ksplit;
+  uint32_t nt, kc, n_stages, chunk_stride, frag_stride, kb_split, n_ksplit, mt, kp, frag_cols;
   size_t smem;
 };
 
 constexpr size_t SMEM_LIMIT = 227 * 1024;
 
-// Chooses the K split, stage depth and stage size for one phase so that everything fits in
-// shared memory with at least three stages in flight.
-Plan make_plan(int dtype, uint32_t kb_total, int phase, uint32_t nt) {
+// Shapes one phase: tile-group shape (mt tiles x kp K-split warps), K split, stage size and depth.
+//  * items must stay fine enough to balance over the CTAs: mt is the largest of {16, 8, 4, 2} that still
+//    leaves about ten items per CTA for the expected number of active experts;
+//  * a stage holds `ppw` block pairs per warp (4 if at least four stages then fit, else 2, else 1);
+//  * fragment arrays are sized by the most tokens any group can hold in this dispatch.
+Plan make_plan(int dtype, uint32_t kb_total, uint32_t packed_tiles, int phase, uint32_t nt, uint32_t max_group_tokens,
+               uint32_t active_groups, int n_ctas) {
   const uint32_t bb = dtype == MER_DTYPE_Q4_0 ? MER_Q4_BLOCK_BYTES : MER_Q8_BLOCK_BYTES;
   const uint32_t tp = 4 * nt;
-  Plan best{};
+  Plan pl{};
   // the K split applies to the down phase only (gate/up needs whole rows before SiLU)
   uint32_t max_split_blocks = phase == 0 ? kb_total : 64u;
   uint32_t n_ksplit = (kb_total + max_split_blocks - 1) / max_split_blocks;
   uint32_t kb_split = ((kb_total + n_ksplit - 1) / n_ksplit + 7) / 8 * 8;
   n_ksplit = (kb_total + kb_split - 1) / kb_split;
-  uint32_t frag_stride = kb_split * 64 + 64;
-  size_t fixed = 256 + (size_t)2 * CONSUMER_WARPS * nt * 128 * 4 + (size_t)kb_split * tp * 4 + 128 + (size_t)tp * 2 * frag_stride;
-  for (uint32_t kc = 64; kc >= 8; kc -= 8) {
-    if (kc > kb_split && kc != 8) continue;
-    uint32_t chunk = kc * 16 * bb;  // one tile chunk; a stage holds two
-    size_t stage = 2 * (size_t)chunk;
-    if (fixed + 3 * stage > SMEM_LIMIT) continue;
-    uint32_t n_stages = (uint32_t)((SMEM_LIMIT - fixed) / stage);
-    if (n_stages > 6) n_stages = 6;
-    best = Plan{nt, kc, n_stages, chunk, frag_stride, kb_split, n_ksplit, fixed + n_stages * stage};
-    break;
+  uint32_t mt = 2;
+  for (uint32_t cand = 16; cand > 2; cand >>= 1) {
+    uint64_t items = (uint64_t)active_groups * n_ksplit * (packed_tiles / cand);
+    if (packed_tiles % cand == 0 && items >= (uint64_t)10 * n_ctas && kb_split / 2 >= 4 * (CONSUMER_WARPS / cand)) {
+      mt = cand;
+      break;
+    }
   }
-  return best;
-}
-
-uint32_t pick_nt(int dtype, uint32_t D, uint32_t F) {
-  // two N-tiles (8 tokens per pass) when both phases still fit three stages
-  Plan a = make_plan(dtype, D / 32, 0, 2), b = make_plan(dtype, F / 32, 1, 2);
-  return (a.n_stages >= 3 && b.n_stages >= 3 && a.kc >= 32 && (b.kc >= 32 || b.kc >= b.kb_split)) ? 2u : 1u;
+  const uint32_t kp = CONSUMER_WARPS / mt;
+  const uint32_t frag_cols = 2 * (max_group_tokens < tp ? max_group_tokens : tp);
+  const uint32_t frag_stride = kb_split * 64 + 64;
+  const size_t fixed = 256 + (size_t)2 * CONSUMER_WARPS * nt * 128 * 4 + (size_t)kb_split * tp * 4 + 128 + (size_t)frag_cols * frag_stride;
+  if (fixed >= SMEM_LIMIT) return pl;
+  const size_t avail = SMEM_LIMIT - fixed;
+  for (uint32_t ppw = 4; ppw >= 1; ppw >>= 1) {
+    uint32_t kc = 2 * kp * ppw;
+    if (kc > kb_split) kc = kb_split;  // the whole K split fits one stage
+    if (kc % 8) kc = (kc + 7) / 8 * 8;
+    const uint32_t chunk = kc * 16 * bb;
+    const size_t stage = (size_t)mt * chunk;
+    uint32_t n_stages = (uint32_t)(avail / stage);
+    if (n_stages > 8) n_stages = 8;
+    if (n_stages >= 4 || (ppw == 1 && n_stages >= 2)) {
+      pl = Plan{nt, kc, n_stages, chunk, frag_stride, kb_split, n_ksplit, mt, kp, frag_cols, fixed + n_stages * stage};
+      break;
+    }
+  }
+  return pl;
 }
 
 struct ScratchLayout {
@@ -666,8 +675,8 @@ cudaError_t launch_phase(const StreamParams &p, uint32_t nt, size_t smem, int gr
 bool stream_ffn_supported(int dtype, uint32_t D, uint32_t F) {
   if (dtype != MER_DTYPE_Q4_0 && dtype != MER_DTYPE_Q8_0) return false;
   if (D == 0 || F == 0 || D % 256 != 0 || F % 256 != 0) return false;  // 16-byte aligned rows, whole tiles
-  Plan a = make_plan(dtype, D / 32, 0, 1), b = make_plan(dtype, F / 32, 1, 1);
-  return a.n_stages >= 3 && b.n_stages >= 3;
+  Plan a = make_plan(dtype, D / 32, F / 8, 0, 1, 4, 1, 148), b = make_plan(dtype, F / 32, D / 16, 1, 1, 4, 1, 148);
+  return a.n_stages >= 2 && b.n_stages >= 2;
 }
 
 size_t stream_ffn_scratch_bytes(uint32_t max_pairs, uint32_t D, uint32_t F) { return scratch_layout(max_pairs, D, F).total; }
@@ -678,8 +687,14 @@ cudaError_t launch_ffn_stream(const MoeDispatch &d, void *scratch, int sm_count,
   uint8_t *base = static_cast<uint8_t *>(scratch);
   // the layout is a function of the allocation-time maxima; only offsets matter here
   const ScratchLayout L = scratch_layout(d.scratch_pairs, d.D, d.F);
-  const uint32_t nt = pick_nt(d.dtype, d.D, d.F);
-  const Plan pg = make_plan(d.dtype, d.D / 32, 0, nt), pd = make_plan(d.dtype, d.F / 32, 1, nt);
+  const uint32_t mgt = d.max_group_tokens ? d.max_group_tokens : P, act = d.active_groups_hint ? d.active_groups_hint : 1;
+  uint32_t nt = mgt > 4 ? 2u : 1u;
+  Plan pg = make_plan(d.dtype, d.D / 32, d.F / 8, 0, nt, mgt, act, sm_count), pd = make_plan(d.dtype, d.F / 32, d.D / 16, 1, nt, mgt, act, sm_count);
+  if (nt == 2 && (pg.n_stages < 3 || pd.n_stages < 3)) {  // eight tokens per pass do not fit: four per pass
+    nt = 1;
+    pg = make_plan(d.dtype, d.D / 32, d.F / 8, 0, nt, mgt, act, sm_count), pd = make_plan(d.dtype, d.F / 32, d.D / 16, 1, nt, mgt, act, sm_count);
+  }
+  if (pg.n_stages < 2 || pd.n_stages < 2) return cudaErrorInvalidConfiguration;
   uint32_t *n_passes = reinterpret_cast<uint32_t *>(base + L.npass);
   uint32_t *pgroup = reinterpret_cast<uint32_t *>(base + L.pgroup), *pstart = reinterpret_cast<uint32_t *>(base + L.pstart),
            *pcount = reinterpret_cast<uint32_t *>(base + L.pcount), *amax = reinterpret_cast<uint32_t *>(base + L.amax);
@@ -703,6 +718,7 @@ cudaError_t launch_ffn_stream(const MoeDispatch &d, void *scratch, int sm_count,
   p.phase = 0, p.afrag = xfrag, p.ainit = xinit, p.aunscale = xun, p.act_per_pair = 0;
   p.rows = d.F, p.kb_total = d.D / 32, p.kb_split = pg.kb_split, p.n_ksplit = pg.n_ksplit, p.kc = pg.kc;
   p.n_stages = pg.n_stages, p.chunk_stride = pg.chunk_stride, p.frag_stride = pg.frag_stride;
+  p.mt = pg.mt, p.kp = pg.kp, p.frag_cols = pg.frag_cols;
   p.out = d.h, p.amax = amax;
   e = d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, pg.smem, sm_count, s)
                                 : launch_phase<MER_DTYPE_Q8_0>(p, nt, pg.smem, sm_count, s);
@@ -719,6 +735,7 @@ cudaError_t launch_ffn_stream(const MoeDispatch &d, void *scratch, int sm_count,
   p.phase = 1, p.afrag = hfrag, p.ainit = hinit, p.aunscale = hun, p.act_per_pair = 1;
   p.rows = d.D, p.kb_total = d.F / 32, p.kb_split = pd.kb_split, p.n_ksplit = pd.n_ksplit, p.kc = pd.kc;
   p.n_stages = pd.n_stages, p.chunk_stride = pd.chunk_stride, p.frag_stride = pd.frag_stride;
+  p.mt = pd.mt, p.kp = pd.kp, p.frag_cols = pd.frag_cols;
   p.out = ypart, p.amax = nullptr;
   e = d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, pd.smem, sm_count, s)
                                 : launch_phase<MER_DTYPE_Q8_0>(p, nt, pd.smem, sm_count, s);

@@ -460,7 +460,8 @@ def test_full_size_qwen3_layer_properties_and_spot_check():
         out64, ids, w = b.moe_layer_forward(0, x)
         out8, _, _ = b.moe_layer_forward(0, x[:8])
         out1, _, _ = b.moe_layer_forward(0, x[:1])
-    assert (out8.view(np.uint32) == out64[:8].view(np.uint32)).all() and (out1.view(np.uint32) == out64[:1].view(np.uint32)).all()
+    # the work split (and so the fp32 summation tree) is chosen per batch size: equal up to rounding
+    assert rel_rms_err(out8, out64[:8]) <= 1e-5 and rel_rms_err(out1, out64[:1]) <= 1e-5
     assert np.isfinite(out64).all() and len(np.unique(ids)) > 100  # ~125.9 of 128 experts expected at B=64
     ref, rids, rw, gaps = oracle.moe_layer_forward(cfg.dtype, oracle.LinearGate(W, E, D, k), blobs, x[:4], F, n_threads=4)
     assert (ids[:4] == rids).all()
