@@ -71,6 +71,9 @@ typedef enum mer_status {
 #define MER_SCORE_SOFTMAX 0
 #define MER_SCORE_SIGMOID 1
 
+/* mer_backend_cfg.flags */
+#define MER_FLAG_NO_GRAPHS 0x1u /* mer_moe_layer_forward_device: always launch kernel by kernel (no CUDA graph replay) */
+
 /* mer_expert_admit flags. */
 #define MER_ADMIT_ANCHOR 0x1u /* Anchor Core entry: never evicted (expert_cache.rs:798-828) */
 #define MER_ADMIT_ASYNC 0x2u  /* return once the side-stream copy is enqueued */
@@ -88,7 +91,7 @@ typedef struct mer_backend_cfg {
   uint32_t max_tokens;          /* largest token batch of one layer call */
   uint32_t max_top_k;           /* largest top_k (+1 if a shared expert is used) */
   float swiglu_limit;           /* GPT-OSS gate clamp; <= 0 or non-finite = off (inference.rs:86-112) */
-  uint32_t flags;               /* reserved, 0 */
+  uint32_t flags;               /* MER_FLAG_* */
   uint32_t reserved;
 } mer_backend_cfg;
 
@@ -204,7 +207,11 @@ int mer_moe_step_weighted_into(mer_backend *b, uint32_t layer, const float *x,
 int mer_moe_layer_forward(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens,
                           float *out, uint32_t *ids, float *weights);
 
-/* ---- compute, device buffers, asynchronous on `stream` (a cudaStream_t) ---- */
+/* ---- compute, device buffers, asynchronous on `stream` (a cudaStream_t) ----
+ * The launch sequence of a call is captured into a CUDA graph the first time a (layer, n_tokens,
+ * pointers, stream) combination is seen and replayed afterwards (one cudaGraphLaunch per call), so
+ * the first call with new arguments must not itself be inside a stream capture.  The backend's
+ * workspace is shared: calls on different streams must not overlap. */
 int mer_moe_layer_forward_device(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens,
                                  float *d_out, uint32_t *d_ids, float *d_weights, void *stream);
 

@@ -74,229 +74,176 @@ __device__ __forceinline__ bool better(int ka, uint32_t ia, int kb, uint32_t ib)
 }
 
 // ---------------------------------------------------------------------------------------
-// Router: logits = W x (one warp per expert row), then the last CTA of each token scores,
-// applies the group filter and picks top-k (LinearGate::route_with_scratch, gating.rs:395-476);
-// the last CTA overall groups the (token, slot) pairs by expert.
+// Router.  One CTA computes the logits of 8 experts for a tile of 4 tokens (every warp takes an
+// eighth of the columns of all 8 rows, so W is read once per token tile and each lane has many
+// independent loads in flight).  The last CTA to finish a token tile scores, filters and picks
+// top-k for its tokens, one warp per token (LinearGate::route_with_scratch, gating.rs:395-476);
+// the last tile overall groups the (token, slot) pairs by expert.
 // ---------------------------------------------------------------------------------------
 constexpr int ROUTER_THREADS = 256;
-constexpr int ROUTER_ROWS = ROUTER_THREADS / 32;
-constexpr uint32_t SMALL_P = 4096;  // stable grouping below this many pairs
+constexpr int ROUTER_ROWS = ROUTER_THREADS / 32;  // expert rows per CTA
+constexpr int ROUTER_TT = 4;                      // tokens per CTA
+constexpr uint32_t SMALL_P = 4096;                // pair keys staged in shared memory below this many pairs
+constexpr uint32_t STABLE_G = 512;                // stable (token, slot)-ordered grouping up to this many groups
 
+// Runs in one CTA after every token has been routed: groups pairs by expert.
 __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uint32_t *s_u32) {
-  // Runs in one CTA after every token has been routed.
   const uint32_t P = d.n_tokens * d.slots;
   const uint32_t G = d.n_groups;
-  const uint32_t tid = threadIdx.x, nt = blockDim.x;
-  uint32_t *s_cnt = s_u32;          // [G]
-  uint32_t *s_off = s_u32 + G;      // [G + 1]
-  uint32_t *s_key = s_u32 + 2 * G + 1;  // [min(P, SMALL_P)]
-  for (uint32_t g = tid; g < G; g += nt) {
-    s_cnt[g] = 0;
-    d.group_expert[g] = (g < r.num_experts) ? r.id_base + g : r.shared_expert_id;
-  }
-  __syncthreads();
-  auto key_of = [&](uint32_t p) -> uint32_t {
+  const uint32_t tid = threadIdx.x, nt = blockDim.x, warp = tid >> 5, lane = tid & 31;
+  uint32_t *s_off = s_u32;                    // [G + 1]
+  uint32_t *s_cnt = s_u32 + G + 1;            // [8 warps][G] (stable path) or [G]
+  const bool stable = G <= STABLE_G;
+  uint32_t *s_key = s_cnt + (stable ? ROUTER_ROWS * G : G);  // [min(P, SMALL_P)]
+  const bool staged = P <= SMALL_P;
+  auto key_global = [&](uint32_t p) -> uint32_t {
     uint32_t e = __ldcg(d.pair_expert + p);
     if (e == MER_NONE) return MER_NONE;
     if ((p % d.slots) >= r.top_k) return r.num_experts;  // shared-expert slot
     return e - r.id_base;
   };
-  if (P <= SMALL_P) {
-    for (uint32_t p = tid; p < P; p += nt) s_key[p] = key_of(p);
+  auto key_of = [&](uint32_t p) -> uint32_t { return staged ? s_key[p] : key_global(p); };
+  for (uint32_t g = tid; g < G; g += nt) d.group_expert[g] = (g < r.num_experts) ? r.id_base + g : r.shared_expert_id;
+  for (uint32_t i = tid; i < (stable ? ROUTER_ROWS * G : G); i += nt) s_cnt[i] = 0;
+  if (staged)
+    for (uint32_t p = tid; p < P; p += nt) s_key[p] = key_global(p);
+  __syncthreads();
+  if (stable) {
+    // every warp owns a contiguous run of pairs, so (warp, position in run) order = (token, slot) order
+    const uint32_t chunk = ((P + ROUTER_ROWS - 1) / ROUTER_ROWS + 31) / 32 * 32;
+    const uint32_t p0 = warp * chunk, p1 = min(P, p0 + chunk);
+    for (uint32_t p = p0 + lane; p < p1; p += 32) {
+      uint32_t k = key_of(p);
+      if (k != MER_NONE) atomicAdd(&s_cnt[warp * G + k], 1u);
+    }
     __syncthreads();
-    for (uint32_t g = tid; g < G; g += nt) {
-      uint32_t c = 0;
-      for (uint32_t p = 0; p < P; p++) c += (s_key[p] == g);
-      s_cnt[g] = c;
+    for (uint32_t g = tid; g < G; g += nt) {  // per group: exclusive scan over the warps, total into s_off
+      uint32_t run = 0;
+      for (uint32_t w = 0; w < ROUTER_ROWS; w++) {
+        uint32_t c = s_cnt[w * G + g];
+        s_cnt[w * G + g] = run;
+        run += c;
+      }
+      s_off[g] = run;
+    }
+    __syncthreads();
+    if (warp == 0) {  // exclusive scan of the group totals
+      const uint32_t per = (G + 31) / 32;
+      uint32_t run = 0;
+      for (uint32_t i = 0; i < per; i++) {
+        uint32_t g = lane * per + i;
+        if (g < G) run += s_off[g];
+      }
+      uint32_t incl = run;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= (uint32_t)o) incl += up;
+      }
+      uint32_t base = incl - run;
+      for (uint32_t i = 0; i < per; i++) {
+        uint32_t g = lane * per + i;
+        if (g < G) {
+          uint32_t c = s_off[g];
+          s_off[g] = base;
+          base += c;
+        }
+      }
+      if (lane == 31) s_off[G] = incl;
+    }
+    __syncthreads();
+    for (uint32_t pb = p0; pb < p1; pb += 32) {
+      const uint32_t p = pb + lane;
+      const uint32_t k = p < p1 ? key_of(p) : MER_NONE;
+      const uint32_t same = __match_any_sync(0xffffffffu, k);
+      if (k != MER_NONE) {
+        const uint32_t rank = __popc(same & ((1u << lane) - 1));
+        d.perm[s_off[k] + s_cnt[warp * G + k] + rank] = p;
+      }
+      __syncwarp();
+      if (k != MER_NONE && (same & ((1u << lane) - 1)) == 0) s_cnt[warp * G + k] += __popc(same);
+      __syncwarp();
     }
   } else {
     for (uint32_t p = tid; p < P; p += nt) {
       uint32_t k = key_of(p);
       if (k != MER_NONE) atomicAdd(&s_cnt[k], 1u);
     }
-  }
-  __syncthreads();
-  if (tid == 0) {
-    uint32_t acc = 0;
-    for (uint32_t g = 0; g < G; g++) {
-      s_off[g] = acc;
-      acc += s_cnt[g];
+    __syncthreads();
+    if (tid == 0) {
+      uint32_t acc = 0;
+      for (uint32_t g = 0; g < G; g++) {
+        s_off[g] = acc;
+        acc += s_cnt[g];
+        s_cnt[g] = 0;
+      }
+      s_off[G] = acc;
     }
-    s_off[G] = acc;
-  }
-  __syncthreads();
-  for (uint32_t g = tid; g <= G; g += nt) d.offsets[g] = s_off[g];
-  if (P <= SMALL_P) {
-    // stable: pairs of a group keep (token, slot) order
-    for (uint32_t g = tid; g < G; g += nt) {
-      uint32_t o = s_off[g];
-      if (s_cnt[g] == 0) continue;
-      for (uint32_t p = 0; p < P; p++)
-        if (s_key[p] == g) d.perm[o++] = p;
-    }
-  } else {
-    for (uint32_t g = tid; g < G; g += nt) s_cnt[g] = 0;
     __syncthreads();
     for (uint32_t p = tid; p < P; p += nt) {
       uint32_t k = key_of(p);
       if (k != MER_NONE) d.perm[s_off[k] + atomicAdd(&s_cnt[k], 1u)] = p;
     }
   }
+  __syncthreads();
+  for (uint32_t g = tid; g <= G; g += nt) d.offsets[g] = s_off[g];
 }
 
-__global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispatch d, uint32_t max_tokens) {
-  extern __shared__ __align__(16) uint8_t smem_raw[];
-  const RouterDev &r_ = r;
-  const uint32_t E = r.num_experts, D = d.D;
-  const uint32_t token = blockIdx.y;
-  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const float *x = d.x + (size_t)token * D;
-  const uint32_t e0 = blockIdx.x * ROUTER_ROWS;
-  if ((D & 1023u) == 0) {
-    // Eight rows per CTA; every warp takes one eighth of the columns of all eight rows, so each
-    // lane has 8 independent row loads in flight per activation vector and x is read once.
-    __shared__ float s_part[ROUTER_ROWS][ROUTER_ROWS + 1];  // [row][warp]
-    const uint32_t slice4 = D / 4 / ROUTER_ROWS;            // float4 per warp slice
-    const float4 *x4 = reinterpret_cast<const float4 *>(x) + warp * slice4;
-    float acc[ROUTER_ROWS];
-#pragma unroll
-    for (int r = 0; r < ROUTER_ROWS; r++) acc[r] = 0.0f;
-    for (uint32_t i = lane; i < slice4; i += 32) {
-      float4 b = __ldg(x4 + i);
-      float4 a[ROUTER_ROWS];
-#pragma unroll
-      for (int r = 0; r < ROUTER_ROWS; r++) {
-        uint32_t row = min(e0 + r, E - 1);
-        a[r] = __ldg(reinterpret_cast<const float4 *>((r_.w + (size_t)row * D)) + warp * slice4 + i);
-      }
-#pragma unroll
-      for (int r = 0; r < ROUTER_ROWS; r++) {
-        acc[r] = fmaf(a[r].x, b.x, acc[r]);
-        acc[r] = fmaf(a[r].y, b.y, acc[r]);
-        acc[r] = fmaf(a[r].z, b.z, acc[r]);
-        acc[r] = fmaf(a[r].w, b.w, acc[r]);
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < ROUTER_ROWS; r++) {
-      float v = warp_sum(acc[r]);
-      if (lane == 0) s_part[r][warp] = v;
-    }
-    __syncthreads();
-    if (threadIdx.x < ROUTER_ROWS && e0 + threadIdx.x < E) {
-      float v = 0.0f;
-#pragma unroll
-      for (int w = 0; w < ROUTER_ROWS; w++) v += s_part[threadIdx.x][w];
-      d.logits[(size_t)token * E + e0 + threadIdx.x] = v;
-    }
-  } else {
-    const uint32_t e = e0 + warp;
-    if (e < E) {
-      const float *w = r.w + (size_t)e * D;
-      float acc = 0.0f;
-      if ((D & 3u) == 0) {
-        const float4 *w4 = reinterpret_cast<const float4 *>(w);
-        const float4 *x4 = reinterpret_cast<const float4 *>(x);
-        for (uint32_t i = lane; i < D / 4; i += 32) {
-          float4 a = __ldg(w4 + i), b = __ldg(x4 + i);
-          acc = fmaf(a.x, b.x, acc);
-          acc = fmaf(a.y, b.y, acc);
-          acc = fmaf(a.z, b.z, acc);
-          acc = fmaf(a.w, b.w, acc);
-        }
-      } else {
-        for (uint32_t i = lane; i < D; i += 32) acc = fmaf(__ldg(w + i), __ldg(x + i), acc);
-      }
-      acc = warp_sum(acc);
-      if (lane == 0) d.logits[(size_t)token * E + e] = acc;
-    }
-  }
-  __shared__ uint32_t s_flag;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    uint32_t prev = atomicAdd(&d.counters[token], 1u);
-    s_flag = (prev == gridDim.x - 1);
-  }
-  __syncthreads();
-  if (!s_flag) return;
-  __threadfence();
-
-  // ---- this CTA saw the last logit of the token: score, filter, select ----
-  float *s_score = reinterpret_cast<float *>(smem_raw);  // [E] scores (become mixing weights)
-  float *s_sel = s_score + E;                             // [E] selection scores
-  uint8_t *s_ok = reinterpret_cast<uint8_t *>(s_sel + E);  // [E] allowed & not yet taken
-  __shared__ float s_red[2];
-  __shared__ uint32_t s_groups[64];
-  __shared__ float s_gscore[64];
-  const uint32_t tid = threadIdx.x, nt = blockDim.x;
-  for (uint32_t i = tid; i < E; i += nt) {
-    float v = __ldcg(d.logits + (size_t)token * E + i);
-    if (r.logit_bias) v += r.logit_bias[i];
-    s_score[i] = v;
-  }
-  if (tid == 0) d.counters[token] = 0;  // re-arm for the next launch
-  __syncthreads();
+// Scoring, group filter, top-k and mixing weights of one token by one warp.
+// s_score / s_sel / s_ok are this warp's shared arrays of E entries; logits are already in s_score.
+__device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t token, float *s_score, float *s_sel,
+                            uint8_t *s_ok, uint32_t *s_groups, float *s_gscore) {
+  const uint32_t E = r.num_experts, lane = threadIdx.x & 31;
+  if (r.logit_bias)
+    for (uint32_t i = lane; i < E; i += 32) s_score[i] += r.logit_bias[i];
+  __syncwarp();
   if (r.scoring == MER_SCORE_SOFTMAX) {
     // softmax_inplace (transformer.rs:2747-2819)
-    if (warp == 0) {
-      float mx = -CUDART_INF_F;
-      int nan = 0;
-      for (uint32_t i = lane; i < E; i += 32) {
-        float v = s_score[i];
-        if (v != v)
-          nan = 1;
-        else if (v > mx)
-          mx = v;
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        nan |= __shfl_xor_sync(0xffffffffu, nan, o);
-      }
-      if (lane == 0) {
-        s_red[0] = mx;
-        s_red[1] = (nan || !isfinite(mx)) ? 1.0f : 0.0f;
-      }
+    float mx = -CUDART_INF_F;
+    int nan = 0;
+    for (uint32_t i = lane; i < E; i += 32) {
+      float v = s_score[i];
+      if (v != v)
+        nan = 1;
+      else if (v > mx)
+        mx = v;
     }
-    __syncthreads();
-    if (s_red[1] != 0.0f) {
-      for (uint32_t i = tid; i < E; i += nt) s_score[i] = 1.0f / (float)E;
-      if (tid == 0) atomicOr(d.status, MER_DEVSTAT_NONFINITE_ROUTER);
-      __syncthreads();
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      nan |= __shfl_xor_sync(0xffffffffu, nan, o);
+    }
+    if (nan || !isfinite(mx)) {
+      for (uint32_t i = lane; i < E; i += 32) s_score[i] = 1.0f / (float)E;
+      if (lane == 0) atomicOr(d.status, MER_DEVSTAT_NONFINITE_ROUTER);
     } else {
-      float mx = s_red[0];
-      for (uint32_t i = tid; i < E; i += nt) s_score[i] = expf(s_score[i] - mx);
-      __syncthreads();
-      if (tid == 0) {  // the reference sums left to right; keep that order
-        float sum = 0.0f;
+      for (uint32_t i = lane; i < E; i += 32) s_score[i] = expf(s_score[i] - mx);
+      __syncwarp();
+      float sum = 0.0f;
+      if (lane == 0)  // the reference sums left to right; keep that order
         for (uint32_t i = 0; i < E; i++) sum += s_score[i];
-        s_red[0] = sum;
-      }
-      __syncthreads();
-      float sum = s_red[0];
+      sum = __shfl_sync(0xffffffffu, sum, 0);
       if (sum > 0.0f)
-        for (uint32_t i = tid; i < E; i += nt) s_score[i] = s_score[i] / sum;
-      __syncthreads();
+        for (uint32_t i = lane; i < E; i += 32) s_score[i] = s_score[i] / sum;
     }
   } else {
-    for (uint32_t i = tid; i < E; i += nt) s_score[i] = 1.0f / (1.0f + expf(-s_score[i]));
-    __syncthreads();
+    for (uint32_t i = lane; i < E; i += 32) s_score[i] = 1.0f / (1.0f + expf(-s_score[i]));
   }
-  for (uint32_t i = tid; i < E; i += nt) {
+  __syncwarp();
+  for (uint32_t i = lane; i < E; i += 32) {
     s_sel[i] = r.correction_bias ? s_score[i] + r.correction_bias[i] : s_score[i];
     s_ok[i] = 1;
   }
-  __syncthreads();
+  __syncwarp();
   // group_filter_shape + select_top_groups (gating.rs:335-376)
-  uint32_t ng = r.n_group < 1 ? 1 : r.n_group;
-  bool grouped = ng > 1 && r.topk_group > 0 && r.topk_group < ng && (E % ng) == 0 && ng <= 64;
+  const uint32_t ng = r.n_group < 1 ? 1 : r.n_group;
+  const bool grouped = ng > 1 && r.topk_group > 0 && r.topk_group < ng && (E % ng) == 0 && ng <= 64;
   if (grouped) {
-    uint32_t gs = E / ng;
-    if (tid < ng) {
+    const uint32_t gs = E / ng;
+    for (uint32_t gi = lane; gi < ng; gi += 32) {
       float top1 = -CUDART_INF_F, top2 = -CUDART_INF_F;
       for (uint32_t i = 0; i < gs; i++) {
-        float s = s_sel[tid * gs + i];
+        float s = s_sel[gi * gs + i];
         if (s > top1) {
           top2 = top1;
           top1 = s;
@@ -304,10 +251,10 @@ __global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispa
           top2 = s;
         }
       }
-      s_gscore[tid] = top1 + (isfinite(top2) ? top2 : 0.0f);
+      s_gscore[gi] = top1 + (isfinite(top2) ? top2 : 0.0f);
     }
-    __syncthreads();
-    if (tid == 0) {
+    __syncwarp();
+    if (lane == 0) {
       uint64_t taken = 0;
       for (uint32_t n = 0; n < r.topk_group; n++) {
         int bk = 0;
@@ -321,71 +268,176 @@ __global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispa
         s_groups[n] = bi;
       }
     }
-    __syncthreads();
-    for (uint32_t i = tid; i < E; i += nt) {
+    __syncwarp();
+    for (uint32_t i = lane; i < E; i += 32) {
       bool ok = false;
       for (uint32_t n = 0; n < r.topk_group; n++) ok |= (s_groups[n] == i / gs);
       s_ok[i] = ok;
     }
-    __syncthreads();
+    __syncwarp();
   }
   // top-k by (selection desc, id asc), non-finite skipped (gating.rs:315-333, 429-441)
-  if (warp == 0) {
-    const uint32_t S = d.slots, k = r.top_k;
-    uint32_t my_id = MER_NONE;  // lane i keeps the i-th pick
-    uint32_t n_sel = 0;
-    for (uint32_t n = 0; n < k; n++) {
-      int bk = 0;
-      uint32_t bi = MER_NONE;
-      for (uint32_t i = lane; i < E; i += 32) {
-        float s = s_sel[i];
-        if (!s_ok[i] || !isfinite(s)) continue;
-        int key = total_key(s);
-        if (bi == MER_NONE || key > bk) bk = key, bi = i;  // ascending scan keeps the lowest id on ties
+  const uint32_t S = d.slots, k = r.top_k;
+  uint32_t my_id = MER_NONE;  // lane i keeps the i-th pick
+  uint32_t n_sel = 0;
+  for (uint32_t n = 0; n < k; n++) {
+    int bk = 0;
+    uint32_t bi = MER_NONE;
+    for (uint32_t i = lane; i < E; i += 32) {
+      float s = s_sel[i];
+      if (!s_ok[i] || !isfinite(s)) continue;
+      int key = total_key(s);
+      if (bi == MER_NONE || key > bk) bk = key, bi = i;  // ascending scan keeps the lowest id on ties
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      int ok = __shfl_xor_sync(0xffffffffu, bk, o);
+      uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi != MER_NONE && (bi == MER_NONE || better(ok, oi, bk, bi))) bk = ok, bi = oi;
+    }
+    if (bi == MER_NONE) break;
+    if (lane == 0) s_ok[bi] = 0;
+    if (lane == (n & 31)) my_id = bi;
+    n_sel++;
+    __syncwarp();
+  }
+  // mixing weights = unbiased scores; renormalise; scale (gating.rs:443-474)
+  float w = (lane < n_sel && my_id != MER_NONE) ? s_score[my_id] : 0.0f;
+  if (r.normalise) {
+    float sum = 0.0f;
+    for (uint32_t i = 0; i < n_sel; i++) sum += __shfl_sync(0xffffffffu, w, i);  // slot order
+    if (isfinite(sum) && sum > 0.0f) w = w / sum;
+  }
+  if (r.scaling != 1.0f && isfinite(r.scaling)) w = w * r.scaling;
+  if (lane < k) {
+    bool have = lane < n_sel;
+    d.pair_expert[(size_t)token * S + lane] = have ? r.id_base + my_id : MER_NONE;
+    d.pair_weight[(size_t)token * S + lane] = have ? w : 0.0f;
+  }
+  if (lane == 0) {
+    if (n_sel < k) atomicOr(d.status, MER_DEVSTAT_SHORT_SELECTION);
+    if (S > k) {
+      d.pair_expert[(size_t)token * S + k] = r.shared_expert_id;
+      d.pair_weight[(size_t)token * S + k] = 1.0f;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispatch d, uint32_t max_tokens) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  const uint32_t E = r.num_experts, D = d.D;
+  const uint32_t tile = blockIdx.y, t0 = tile * ROUTER_TT;
+  const uint32_t n_here = min((uint32_t)ROUTER_TT, d.n_tokens - t0);
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t e0 = blockIdx.x * ROUTER_ROWS;
+  __shared__ float s_part[ROUTER_ROWS][ROUTER_TT][ROUTER_ROWS + 1];  // [row][token][warp]
+  __shared__ float s_logit[ROUTER_TT][ROUTER_ROWS];                  // used when one CTA covers all experts
+  const bool single = gridDim.x == 1;
+
+  if ((D & 1023u) == 0) {
+    const uint32_t slice4 = D / 4 / ROUTER_ROWS;  // float4 per warp slice
+    float acc[ROUTER_ROWS][ROUTER_TT];
+#pragma unroll
+    for (int rr = 0; rr < ROUTER_ROWS; rr++)
+#pragma unroll
+      for (int tt = 0; tt < ROUTER_TT; tt++) acc[rr][tt] = 0.0f;
+    for (uint32_t i = lane; i < slice4; i += 32) {
+      float4 b[ROUTER_TT], a[ROUTER_ROWS];
+#pragma unroll
+      for (int tt = 0; tt < ROUTER_TT; tt++) {
+        const uint32_t tok = t0 + min((uint32_t)tt, n_here - 1);
+        b[tt] = __ldg(reinterpret_cast<const float4 *>(d.x + (size_t)tok * D) + warp * slice4 + i);
       }
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        int ok = __shfl_xor_sync(0xffffffffu, bk, o);
-        uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (oi != MER_NONE && (bi == MER_NONE || better(ok, oi, bk, bi))) bk = ok, bi = oi;
+      for (int rr = 0; rr < ROUTER_ROWS; rr++) {
+        const uint32_t row = min(e0 + rr, E - 1);
+        a[rr] = __ldg(reinterpret_cast<const float4 *>(r.w + (size_t)row * D) + warp * slice4 + i);
       }
-      if (bi == MER_NONE) break;
-      if (lane == 0) s_ok[bi] = 0;
-      if (lane == (n & 31)) my_id = bi;
-      n_sel++;
-      __syncwarp();
+#pragma unroll
+      for (int rr = 0; rr < ROUTER_ROWS; rr++)
+#pragma unroll
+        for (int tt = 0; tt < ROUTER_TT; tt++) {
+          acc[rr][tt] = fmaf(a[rr].x, b[tt].x, acc[rr][tt]);
+          acc[rr][tt] = fmaf(a[rr].y, b[tt].y, acc[rr][tt]);
+          acc[rr][tt] = fmaf(a[rr].z, b[tt].z, acc[rr][tt]);
+          acc[rr][tt] = fmaf(a[rr].w, b[tt].w, acc[rr][tt]);
+        }
     }
-    // mixing weights = unbiased scores; renormalise; scale (gating.rs:443-474)
-    float w = (lane < n_sel && my_id != MER_NONE) ? s_score[my_id] : 0.0f;
-    if (r.normalise) {
-      float sum = 0.0f;
-      for (uint32_t i = 0; i < n_sel; i++) sum += __shfl_sync(0xffffffffu, w, i);  // slot order
-      if (isfinite(sum) && sum > 0.0f) w = w / sum;
+#pragma unroll
+    for (int rr = 0; rr < ROUTER_ROWS; rr++)
+#pragma unroll
+      for (int tt = 0; tt < ROUTER_TT; tt++) {
+        float v = warp_sum(acc[rr][tt]);
+        if (lane == 0) s_part[rr][tt][warp] = v;
+      }
+    __syncthreads();
+    if (threadIdx.x < ROUTER_ROWS * ROUTER_TT) {
+      const uint32_t rr = threadIdx.x / ROUTER_TT, tt = threadIdx.x % ROUTER_TT;
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < ROUTER_ROWS; w++) v += s_part[rr][tt][w];
+      if (single)
+        s_logit[tt][rr] = v;
+      else if (e0 + rr < E && tt < n_here)
+        d.logits[(size_t)(t0 + tt) * E + e0 + rr] = v;
     }
-    if (r.scaling != 1.0f && isfinite(r.scaling)) w = w * r.scaling;
-    if (lane < k) {
-      bool have = lane < n_sel;
-      d.pair_expert[(size_t)token * S + lane] = have ? r.id_base + my_id : MER_NONE;
-      d.pair_weight[(size_t)token * S + lane] = have ? w : 0.0f;
-    }
-    if (lane == 0) {
-      if (n_sel < k) atomicOr(d.status, MER_DEVSTAT_SHORT_SELECTION);
-      if (S > k) {
-        d.pair_expert[(size_t)token * S + k] = r.shared_expert_id;
-        d.pair_weight[(size_t)token * S + k] = 1.0f;
+  } else {
+    // any d_model: warp = expert row, tokens one after the other
+    const uint32_t e = e0 + warp;
+    for (uint32_t tt = 0; tt < n_here; tt++) {
+      float acc = 0.0f;
+      if (e < E) {
+        const float *w = r.w + (size_t)e * D, *x = d.x + (size_t)(t0 + tt) * D;
+        for (uint32_t i = lane; i < D; i += 32) acc = fmaf(__ldg(w + i), __ldg(x + i), acc);
+        acc = warp_sum(acc);
+      }
+      if (lane == 0 && e < E) {
+        if (single)
+          s_logit[tt][warp] = acc;
+        else
+          d.logits[(size_t)(t0 + tt) * E + e] = acc;
       }
     }
   }
+  __shared__ uint32_t s_flag;
   __syncthreads();
-  if (tid == 0) {
+  if (!single) {
+    if (threadIdx.x == 0) {
+      __threadfence();
+      uint32_t prev = atomicAdd(&d.counters[tile], 1u);
+      s_flag = (prev == gridDim.x - 1);
+      if (s_flag) d.counters[tile] = 0;  // re-arm for the next launch
+    }
+    __syncthreads();
+    if (!s_flag) return;
     __threadfence();
-    uint32_t prev = atomicAdd(&d.counters[max_tokens], 1u);
-    s_flag = (prev == d.n_tokens - 1);
-    if (s_flag) d.counters[max_tokens] = 0;
+  }
+
+  // ---- this CTA holds the last logits of the token tile: one warp routes one token ----
+  __shared__ uint32_t s_groups[ROUTER_TT][64];
+  __shared__ float s_gscore[ROUTER_TT][64];
+  if (warp < n_here) {
+    float *s_score = reinterpret_cast<float *>(smem_raw) + (size_t)warp * 2 * E;  // [E] scores (become mixing weights)
+    float *s_sel = s_score + E;                                                    // [E] selection scores
+    uint8_t *s_ok = smem_raw + (size_t)ROUTER_TT * 2 * E * 4 + (size_t)warp * E;    // [E] allowed & not yet taken
+    const uint32_t token = t0 + warp;
+    for (uint32_t i = lane; i < E; i += 32) s_score[i] = single ? s_logit[warp][i] : __ldcg(d.logits + (size_t)token * E + i);
+    __syncwarp();
+    route_token(r, d, token, s_score, s_sel, s_ok, s_groups[warp], s_gscore[warp]);
   }
   __syncthreads();
-  if (!s_flag) return;
-  __threadfence();
+  const uint32_t n_tiles = gridDim.y;
+  if (n_tiles > 1) {
+    if (threadIdx.x == 0) {
+      __threadfence();
+      uint32_t prev = atomicAdd(&d.counters[max_tokens], 1u);
+      s_flag = (prev == n_tiles - 1);
+      if (s_flag) d.counters[max_tokens] = 0;
+    }
+    __syncthreads();
+    if (!s_flag) return;
+    __threadfence();
+  }
   build_groups_layer(r, d, reinterpret_cast<uint32_t *>(smem_raw));
 }
 
@@ -598,17 +650,17 @@ __global__ void k_f32_to_f16(const float *__restrict__ src, uint16_t *__restrict
 
 cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max_tokens, cudaStream_t s,
                           int *launches) {
-  const uint32_t E = r.num_experts;
+  const uint32_t E = r.num_experts, G = d.n_groups;
   const uint32_t P = d.n_tokens * d.slots;
-  size_t smem_topk = (size_t)E * 9;
-  size_t smem_grp = (size_t)(2 * d.n_groups + 1 + (P <= SMALL_P ? P : 0)) * 4;
+  size_t smem_topk = (size_t)ROUTER_TT * E * 9;
+  size_t smem_grp = (size_t)(G + 1 + (G <= STABLE_G ? ROUTER_ROWS * G : G) + (P <= SMALL_P ? P : 0)) * 4;
   size_t smem = smem_topk > smem_grp ? smem_topk : smem_grp;
   smem = (smem + 15) & ~(size_t)15;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k_router, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  dim3 grid((E + ROUTER_ROWS - 1) / ROUTER_ROWS, d.n_tokens);
+  dim3 grid((E + ROUTER_ROWS - 1) / ROUTER_ROWS, (d.n_tokens + ROUTER_TT - 1) / ROUTER_TT);
   k_router<<<grid, ROUTER_THREADS, smem, s>>>(r, d, max_tokens);
   if (launches) (*launches)++;
   return cudaGetLastError();

@@ -32,16 +32,15 @@ namespace {
 
 constexpr int CONSUMER_WARPS = 16;
 constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;  // + one producer warp
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr uint32_t SPIN_LIMIT = 1u << 16;  // polls per bounded wait; a poll suspends for tens of microseconds
+constexpr uint32_t HEADER_BYTES = 1024;  // mbarriers and per-pass token tables at the start of shared memory
 constexpr float POW2_24 = 16777216.0f;
 
 struct StreamParams {
   MoeDispatch d;
   int phase;                 // 0 = gate/up (+SiLU*mul), 1 = down
-  const uint16_t *afrag;     // [n_act][2 parts][kb_total][32] f16, fragment order
-  const float *ainit;        // [n_act][kb_total]  -zp * 2^-24 * sum of the block's scaled activations
-  const float *aunscale;     // [n_act]  2^24 / s  (s = the activation's power-of-two scale)
-  uint32_t act_per_pair;     // 1: activations indexed by pair (down); 0: by token = pair / slots (gate/up)
+  const float *act;          // activations, row-major fp32: x [n_tokens x D] (gate/up) or h [P x F] (down)
+  uint32_t act_per_pair;     // 1: rows indexed by pair (down); 0: by token = pair / slots (gate/up)
   uint32_t rows;             // output rows of the projection (F for gate/up, D for down)
   uint32_t kb_total;         // 32-weight blocks per row
   uint32_t kb_split;         // blocks per K split (kb_total when n_ksplit == 1)
@@ -116,7 +115,6 @@ __device__ __forceinline__ uint4 lds128(uint32_t a) {
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 
 // ------------------------------------------------------------------- activation fragments
 // Position of block element j in the per-block fragment order, and the extra exact scale of
@@ -137,80 +135,7 @@ __device__ __forceinline__ void frag_slot(uint32_t j, uint32_t &pos, float &slot
   }
 }
 
-// Activation rows -> MMA B fragments.  Exact power-of-two scaling so that max |a| lands in
-// [256, 512), f16 hi/lo split in fragment order, and the per-block accumulator seed.
-// grid = (rows, ceil(K / 2048)); every thread converts two groups of four consecutive elements.
-constexpr uint32_t PREP_CHUNK = 2048;
-
 __device__ __forceinline__ float nan_max(float a, float b) { return (b > a || b != b) ? b : a; }  // NaN sticks
-
-template <int DT>
-__global__ void __launch_bounds__(256) k_act_prep(const float *__restrict__ a, uint32_t K, const uint32_t *__restrict__ amax_bits,
-                                                  uint16_t *__restrict__ frag, float *__restrict__ init,
-                                                  float *__restrict__ unscale) {
-  const uint32_t row = blockIdx.x;
-  const float *src = a + (size_t)row * K;
-  __shared__ float s_red[8];
-  float mx;
-  if (amax_bits) {
-    mx = __uint_as_float(amax_bits[row]);
-  } else {
-    mx = 0.0f;
-    const float4 *src4 = reinterpret_cast<const float4 *>(src);
-#pragma unroll 4
-    for (uint32_t i = threadIdx.x; i < K / 4; i += 256) {
-      float4 v = __ldg(src4 + i);
-      mx = nan_max(nan_max(nan_max(nan_max(mx, fabsf(v.x)), fabsf(v.y)), fabsf(v.z)), fabsf(v.w));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = mx;
-    __syncthreads();
-    mx = s_red[0];
-#pragma unroll
-    for (int w = 1; w < 8; w++) mx = nan_max(mx, s_red[w]);
-  }
-  float s = 1.0f;
-  if (mx > 0.0f && isfinite(mx)) {
-    int e;
-    frexpf(mx, &e);           // mx = m * 2^e, m in [0.5, 1)
-    s = ldexpf(1.0f, 9 - e);  // mx * s in [256, 512)
-  } else if (mx != mx || isinf(mx)) {
-    s = mx;  // non-finite activations poison the row, as they would in fp32
-  }
-  if (blockIdx.y == 0 && threadIdx.x == 0) unscale[row] = POW2_24 / s;
-  const uint32_t KB = K / 32;
-  const float zp = DT == MER_DTYPE_Q4_0 ? 8.0f : 128.0f;
-  uint16_t *hi_dst = frag + (size_t)row * 2 * K;
-  uint16_t *lo_dst = hi_dst + K;
-#pragma unroll
-  for (int half = 0; half < 2; half++) {
-    const uint32_t e0 = blockIdx.y * PREP_CHUNK + half * (PREP_CHUNK / 2) + threadIdx.x * 4;  // first of 4 elements
-    const bool live = e0 < K;
-    float4 v = live ? __ldg(reinterpret_cast<const float4 *>(src + e0)) : make_float4(0, 0, 0, 0);
-    v.x *= s, v.y *= s, v.z *= s, v.w *= s;  // exact (power of two) unless it overflows
-    const uint32_t kb = e0 >> 5, j0 = e0 & 31u;
-    uint32_t pos;
-    float ss;
-    frag_slot<DT>(j0, pos, ss);  // the four elements land at pos + {0, 2, 1, 3}
-    float vs[4] = {v.x * ss, v.z * ss, v.y * ss, v.w * ss};
-    uint16_t hi[4], lo[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      __half h = __float2half_rn(vs[i]);
-      hi[i] = __half_as_ushort(h);
-      lo[i] = __half_as_ushort(__float2half_rn(vs[i] - __half2float(h)));
-    }
-    if (live) {
-      *reinterpret_cast<uint2 *>(hi_dst + kb * 32 + pos) = make_uint2(hi[0] | (uint32_t)hi[1] << 16, hi[2] | (uint32_t)hi[3] << 16);
-      *reinterpret_cast<uint2 *>(lo_dst + kb * 32 + pos) = make_uint2(lo[0] | (uint32_t)lo[1] << 16, lo[2] | (uint32_t)lo[3] << 16);
-    }
-    float sum = (v.x + v.y) + (v.z + v.w);  // eight consecutive lanes hold one block
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (live && (threadIdx.x & 7) == 0) init[(size_t)row * KB + kb] = -zp * sum * (1.0f / POW2_24);
-  }
-}
 
 // ------------------------------------------------------------------------ weight unpacking
 // Eight weights of one row slot of one block -> four f16x2 registers holding the integer fields as
@@ -248,9 +173,12 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   // shared memory carve-up
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);  // [n_stages]
   uint64_t *empty = full + p.n_stages;                   // [n_stages]
-  uint64_t *actbar = empty + p.n_stages;                 // [1]
-  uint32_t *s_abort = reinterpret_cast<uint32_t *>(actbar + 1);
-  float *s_red = reinterpret_cast<float *>(smem + 256);                     // [2][CONSUMER_WARPS][NT][4][32]
+  uint32_t *s_abort = reinterpret_cast<uint32_t *>(empty + p.n_stages);
+  uint32_t *s_pair = reinterpret_cast<uint32_t *>(smem + 160);  // [TP] pair index of each token of the current pass
+  float *s_un = reinterpret_cast<float *>(smem + 192);          // [TP] its 2^24 / scale
+  uint32_t *s_amax = reinterpret_cast<uint32_t *>(smem + 224);  // [TP] max |activation| of its row, as float bits
+  float *s_scale = reinterpret_cast<float *>(smem + 768);       // [TP] the row's power-of-two scale
+  float *s_red = reinterpret_cast<float *>(smem + HEADER_BYTES);            // [2][CONSUMER_WARPS][NT][4][32]
   float *s_init = s_red + 2 * CONSUMER_WARPS * NT * 128;                    // [TP][kb_split]
   uint8_t *s_frag = reinterpret_cast<uint8_t *>(s_init + p.kb_split * TP);  // [TP*2][frag_stride]
   s_frag = reinterpret_cast<uint8_t *>(((size_t)s_frag + 127) & ~(size_t)127);
@@ -262,7 +190,6 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], CONSUMER_WARPS);
     }
-    mbar_init(actbar, 1);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -332,7 +259,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   const uint32_t mtile = warp % p.mt, kpart = warp / p.mt;  // tile of the stage, share of its K range
   const uint32_t stage0 = smem_u32(s_stage) + mtile * p.chunk_stride;  // this warp's tile chunk in stage 0
   const uint32_t frag0 = smem_u32(s_frag) + t * 16, init0 = smem_u32(s_init);
-  uint32_t stage = 0, round = 0, act_round = 0, red_buf = 0;
+  uint32_t stage = 0, round = 0, n_done = 0;  // n_done: resident items finished by this CTA
   uint32_t cur_pp = MER_NONE, cur_ks = MER_NONE;
   // A warp whose bounded wait expired goes "dead": it stops computing and waiting but still walks
   // the same loop structure, so the named barriers below always see all consumer warps.
@@ -349,7 +276,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
     kb_range(ks, kb0, kbn);
 
     if (pp != cur_pp || ks != cur_ks) {
-      // new activation fragments: everyone is done with the old ones, then one thread issues the copies
+      // new activation fragments: first, everyone must be done with the old ones
       if (pp != cur_pp) {
         pstart = p.pass_start[pp], pcount = p.pass_count[pp];
         const uint32_t eid = d.group_expert[p.pass_group[pp]];
@@ -357,21 +284,86 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       }
       consumer_sync();
       cur_pp = pp, cur_ks = ks;
-      if (threadIdx.x == 0) {
-        uint32_t bytes_each = kbn * 64;
-        mbar_expect_tx(actbar, pcount * (2 * bytes_each + kbn * 4));
-        for (uint32_t i = 0; i < pcount; i++) {
-          uint32_t pair = d.perm[pstart + i];
-          uint32_t a = p.act_per_pair ? pair : pair / d.slots;
-          const uint16_t *fsrc = p.afrag + (size_t)a * 2 * p.kb_total * 32;
-          bulk_g2s(s_frag + (size_t)(2 * i) * p.frag_stride, fsrc + (size_t)kb0 * 32, bytes_each, actbar);
-          bulk_g2s(s_frag + (size_t)(2 * i + 1) * p.frag_stride, fsrc + (size_t)(p.kb_total + kb0) * 32, bytes_each, actbar);
-          bulk_g2s(s_init + (size_t)i * p.kb_split, p.ainit + (size_t)a * p.kb_total + kb0, kbn * 4, actbar);
+      // The pass's activation rows become MMA B fragments here, in shared memory: an exact power-of-two
+      // scaling that puts max |a| of the row in [256, 512), an f16 hi/lo split in fragment order, and the
+      // per-block accumulator seed -zp * 2^-24 * sum(block).  Warps share the rows: 16 / pcount per row.
+      const uint32_t K = p.kb_total * 32;
+      if (threadIdx.x < TP) {
+        uint32_t pair = 0, mx = 0;
+        if (threadIdx.x < pcount) {
+          pair = d.perm[pstart + threadIdx.x];
+          if (p.phase == 1) mx = p.amax[pair];  // collected by the gate/up epilogue
+        }
+        s_pair[threadIdx.x] = pair;
+        s_amax[threadIdx.x] = mx;
+      }
+      consumer_sync();
+      const uint32_t wpt = CONSUMER_WARPS / pcount;  // warps per row (pcount <= 8)
+      const uint32_t my_tok = warp / wpt, my_sub = warp % wpt;
+      const bool has_row = my_tok < pcount;
+      const float *row = nullptr;
+      if (has_row) {
+        const uint32_t pair = s_pair[my_tok];
+        row = p.act + (size_t)(p.act_per_pair ? pair : pair / d.slots) * K;
+      }
+      if (p.phase == 0) {  // the row maximum is not known yet: one pass over the row
+        float mx = 0.0f;
+        if (has_row) {
+          const float4 *r4 = reinterpret_cast<const float4 *>(row);
+          for (uint32_t i = my_sub * 32 + lane; i < K / 4; i += wpt * 32) {
+            const float4 v = __ldg(r4 + i);
+            mx = nan_max(nan_max(nan_max(nan_max(mx, fabsf(v.x)), fabsf(v.y)), fabsf(v.z)), fabsf(v.w));
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (has_row && lane == 0) atomicMax(&s_amax[my_tok], (mx != mx) ? 0x7fc00000u : __float_as_uint(mx));
+        consumer_sync();
+      }
+      if (threadIdx.x < TP) {
+        const float mx = __uint_as_float(s_amax[threadIdx.x]);
+        float sc = 1.0f;
+        if (mx > 0.0f && isfinite(mx)) {
+          int e;
+          frexpf(mx, &e);            // mx = m * 2^e, m in [0.5, 1)
+          sc = ldexpf(1.0f, 9 - e);  // mx * sc in [256, 512)
+        } else if (mx != mx || isinf(mx)) {
+          sc = mx;  // non-finite activations poison the row, as they would in fp32
+        }
+        s_scale[threadIdx.x] = sc;
+        s_un[threadIdx.x] = POW2_24 / sc;
+      }
+      consumer_sync();
+      if (has_row) {
+        const float sc = s_scale[my_tok];
+        const float zp = DT == MER_DTYPE_Q4_0 ? 8.0f : 128.0f;
+        uint8_t *hi_dst = s_frag + (size_t)(2 * my_tok) * p.frag_stride, *lo_dst = hi_dst + p.frag_stride;
+        float *seed_dst = s_init + (size_t)my_tok * p.kb_split;
+        // float4 groups of this K split: 8 per block; a warp converts 4 blocks per step
+        for (uint32_t q = my_sub * 32 + lane; q < kbn * 8; q += wpt * 32) {
+          float4 v = __ldg(reinterpret_cast<const float4 *>(row + (size_t)kb0 * 32) + q);
+          v.x *= sc, v.y *= sc, v.z *= sc, v.w *= sc;  // exact (power of two) unless it overflows
+          const uint32_t kbl = q >> 3, j0 = (q & 7u) * 4;
+          uint32_t pos;
+          float ss;
+          frag_slot<DT>(j0, pos, ss);  // the four elements land at pos + {0, 2, 1, 3}
+          const float vs[4] = {v.x * ss, v.z * ss, v.y * ss, v.w * ss};
+          uint32_t hi[4], lo[4];
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const __half h = __float2half_rn(vs[i]);
+            hi[i] = __half_as_ushort(h);
+            lo[i] = __half_as_ushort(__float2half_rn(vs[i] - __half2float(h)));
+          }
+          *reinterpret_cast<uint2 *>(hi_dst + kbl * 64 + pos * 2) = make_uint2(hi[0] | hi[1] << 16, hi[2] | hi[3] << 16);
+          *reinterpret_cast<uint2 *>(lo_dst + kbl * 64 + pos * 2) = make_uint2(lo[0] | lo[1] << 16, lo[2] | lo[3] << 16);
+          float sum = (v.x + v.y) + (v.z + v.w);  // eight consecutive lanes hold one block
+#pragma unroll
+          for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+          if ((lane & 7) == 0) seed_dst[kbl] = -zp * sum * (1.0f / POW2_24);
         }
       }
-      if (!dead && !mbar_wait(actbar, act_round & 1)) dead = true;
-      dead = __any_sync(0xffffffffu, dead);
-      act_round++;
+      consumer_sync();  // fragments, seeds, s_pair, s_un visible to every warp
     }
     if (!resident) {
       if (threadIdx.x == 0) atomicOr(d.status, MER_DEVSTAT_RESIDENCY_MISS);
@@ -458,51 +450,59 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       if (++stage == p.n_stages) stage = 0, round++;
     }
 
-    // ---- item epilogue: the KP warps of a tile sum their K-split partials, warp kpart == 0 writes.
-    // s_red is double buffered, so one named barrier (per tile group) per item is enough: a buffer
-    // is rewritten two items later, after every warp of the group passed the barrier in between.
+    // ---- item epilogue.  The KP warps of a tile hand their K-split partials to ONE of them (the
+    // finisher, a role that rotates so the scalar epilogue work spreads over all warps) through
+    // double-buffered shared memory and one named barrier of the tile group (a sleeping wait: a
+    // polling wait here steals issue slots from the warps still computing).  A buffer is rewritten two
+    // items later, after every warp of the group - the previous finisher included - has passed the
+    // barrier of the item in between.
+    const uint32_t buf = n_done & 1;
+    const uint32_t finisher = KP > 1 ? (n_done % KP) : 0;
+    n_done++;
     float v[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; n++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) v[n][i] = acc[n][i];
     if (KP > 1) {
-      float *red = s_red + (size_t)red_buf * CONSUMER_WARPS * NT * 128;
-      red_buf ^= 1;
+      float *red = s_red + (size_t)buf * CONSUMER_WARPS * NT * 128;
+      if (kpart != finisher) {
 #pragma unroll
-      for (int n = 0; n < NT; n++)
+        for (int n = 0; n < NT; n++)
 #pragma unroll
-        for (int i = 0; i < 4; i++) red[((warp * NT + n) * 4 + i) * 32 + lane] = acc[n][i];
+          for (int i = 0; i < 4; i++) red[((warp * NT + n) * 4 + i) * 32 + lane] = acc[n][i];
+      }
       asm volatile("bar.sync %0, %1;" ::"r"(2 + mtile), "r"(KP * 32) : "memory");
-      if (kpart == 0) {
+      if (kpart == finisher) {
 #pragma unroll
         for (int n = 0; n < NT; n++)
 #pragma unroll
           for (int i = 0; i < 4; i++) {
             float s0 = 0.0f;
-            for (uint32_t k2 = 0; k2 < KP; k2++) s0 += red[(((k2 * p.mt + mtile) * NT + n) * 4 + i) * 32 + lane];
+            for (uint32_t k2 = 0; k2 < KP; k2++) {  // fixed order k2 = 0..KP-1, own partial from registers
+              float part = (k2 == kpart) ? acc[n][i] : red[(((k2 * p.mt + mtile) * NT + n) * 4 + i) * 32 + lane];
+              s0 += part;
+            }
             v[n][i] = s0;
           }
       }
-    } else {
-#pragma unroll
-      for (int n = 0; n < NT; n++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) v[n][i] = acc[n][i];
     }
-    if (kpart == 0 && !dead) {
+    if (kpart == finisher && !dead) {
       const uint32_t ptile = p.mt * tile + mtile;  // packed tile index within the phase's region
 #pragma unroll
       for (int n = 0; n < NT; n++) {
         if (n > 0 && (uint32_t)n >= n_live) break;
         const uint32_t tok = n * 4 + t;
         const bool valid = tok < pcount;
-        const uint32_t pair = valid ? d.perm[pstart + tok] : 0;
-        const uint32_t a = p.act_per_pair ? pair : pair / d.slots;
-        const float un = valid ? p.aunscale[a] : 0.0f;
+        const uint32_t pair = valid ? s_pair[tok] : 0;
+        const float un = valid ? s_un[tok] : 0.0f;
         const float r_lo = (v[n][0] + v[n][1]) * un, r_hi = (v[n][2] + v[n][3]) * un;  // row slots g and g+8
         if (p.phase == 0) {
           // slots 0..7 of a gate/up tile are gate rows, slots 8..15 the matching up rows
           float gate = r_lo;
           if (d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit) && gate == gate)
             gate = fminf(fmaxf(gate, -d.swiglu_limit), d.swiglu_limit);
-          const float hval = silu_f(gate) * r_hi;
+          const float hval = __fdividef(gate, 1.0f + __expf(-gate)) * r_hi;
           if (valid) p.out[(size_t)pair * d.F + ptile * 8 + g] = hval;
           const float ah = fabsf(hval);
           uint32_t bits = !valid ? 0u : (ah != ah) ? 0x7fc00000u : __float_as_uint(ah);
@@ -607,7 +607,7 @@ Plan make_plan(int dtype, uint32_t kb_total, uint32_t packed_tiles, int phase, u
   const uint32_t kp = CONSUMER_WARPS / mt;
   const uint32_t frag_cols = 2 * (max_group_tokens < tp ? max_group_tokens : tp);
   const uint32_t frag_stride = kb_split * 64 + 64;
-  const size_t fixed = 256 + (size_t)2 * CONSUMER_WARPS * nt * 128 * 4 + (size_t)kb_split * tp * 4 + 128 + (size_t)frag_cols * frag_stride;
+  const size_t fixed = HEADER_BYTES + (size_t)2 * CONSUMER_WARPS * nt * 128 * 4 + (size_t)kb_split * tp * 4 + 128 + (size_t)frag_cols * frag_stride;
   if (fixed >= SMEM_LIMIT) return pl;
   const size_t avail = SMEM_LIMIT - fixed;
   for (uint32_t ppw = 4; ppw >= 1; ppw >>= 1) {
@@ -627,7 +627,7 @@ Plan make_plan(int dtype, uint32_t kb_total, uint32_t packed_tiles, int phase, u
 }
 
 struct ScratchLayout {
-  size_t xfrag, xinit, xun, hfrag, hinit, hun, amax, npass, pgroup, pstart, pcount, ypart, total;
+  size_t amax, npass, pgroup, pstart, pcount, ypart, total;
 };
 
 ScratchLayout scratch_layout(uint32_t max_pairs, uint32_t D, uint32_t F) {
@@ -638,12 +638,6 @@ ScratchLayout scratch_layout(uint32_t max_pairs, uint32_t D, uint32_t F) {
     off += (bytes + 255) & ~(size_t)255;
     return o;
   };
-  L.xfrag = take((size_t)max_pairs * 2 * D * 2);
-  L.xinit = take((size_t)max_pairs * (D / 32) * 4);
-  L.xun = take((size_t)max_pairs * 4);
-  L.hfrag = take((size_t)max_pairs * 2 * F * 2);
-  L.hinit = take((size_t)max_pairs * (F / 32) * 4);
-  L.hun = take((size_t)max_pairs * 4);
   L.amax = take((size_t)max_pairs * 4);
   L.npass = take(256);
   L.pgroup = take((size_t)max_pairs * 4);
@@ -701,46 +695,32 @@ cudaError_t launch_ffn_stream(const MoeDispatch &d, void *scratch, int sm_count,
   cudaError_t e;
   k_build_passes<<<1, 256, 0, s>>>(d, 4 * nt, n_passes, pgroup, pstart, pcount, amax, P);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  uint16_t *xfrag = reinterpret_cast<uint16_t *>(base + L.xfrag), *hfrag = reinterpret_cast<uint16_t *>(base + L.hfrag);
-  float *xinit = reinterpret_cast<float *>(base + L.xinit), *xun = reinterpret_cast<float *>(base + L.xun);
-  float *hinit = reinterpret_cast<float *>(base + L.hinit), *hun = reinterpret_cast<float *>(base + L.hun);
-  if (d.dtype == MER_DTYPE_Q4_0)
-    k_act_prep<MER_DTYPE_Q4_0><<<dim3(d.n_tokens, (d.D + PREP_CHUNK - 1) / PREP_CHUNK), 256, 0, s>>>(d.x, d.D, nullptr, xfrag, xinit, xun);
-  else
-    k_act_prep<MER_DTYPE_Q8_0><<<dim3(d.n_tokens, (d.D + PREP_CHUNK - 1) / PREP_CHUNK), 256, 0, s>>>(d.x, d.D, nullptr, xfrag, xinit, xun);
-  if ((e = cudaGetLastError()) != cudaSuccess) return e;
-
   StreamParams p{};
   p.d = d;
   p.n_passes = n_passes, p.pass_group = pgroup, p.pass_start = pstart, p.pass_count = pcount;
   p.tokens_per_pass = 4 * nt;
-  // phase 0: gate/up
-  p.phase = 0, p.afrag = xfrag, p.ainit = xinit, p.aunscale = xun, p.act_per_pair = 0;
+  p.amax = amax;
+  // phase 0: gate/up, activations = x by token
+  p.phase = 0, p.act = d.x, p.act_per_pair = 0;
   p.rows = d.F, p.kb_total = d.D / 32, p.kb_split = pg.kb_split, p.n_ksplit = pg.n_ksplit, p.kc = pg.kc;
   p.n_stages = pg.n_stages, p.chunk_stride = pg.chunk_stride, p.frag_stride = pg.frag_stride;
   p.mt = pg.mt, p.kp = pg.kp, p.frag_cols = pg.frag_cols;
-  p.out = d.h, p.amax = amax;
+  p.out = d.h;
   e = d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, pg.smem, sm_count, s)
                                 : launch_phase<MER_DTYPE_Q8_0>(p, nt, pg.smem, sm_count, s);
   if (e != cudaSuccess) return e;
   if (ev_mid) cudaEventRecord(ev_mid, s);
-  // activations of the down phase: h, scaled per pair by the max the gate/up epilogue collected
-  if (d.dtype == MER_DTYPE_Q4_0)
-    k_act_prep<MER_DTYPE_Q4_0><<<dim3(P, (d.F + PREP_CHUNK - 1) / PREP_CHUNK), 256, 0, s>>>(d.h, d.F, amax, hfrag, hinit, hun);
-  else
-    k_act_prep<MER_DTYPE_Q8_0><<<dim3(P, (d.F + PREP_CHUNK - 1) / PREP_CHUNK), 256, 0, s>>>(d.h, d.F, amax, hfrag, hinit, hun);
-  if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  // phase 1: down
+  // phase 1: down, activations = h by pair, scaled by the row maxima the gate/up epilogue collected
   float *ypart = pd.n_ksplit > 1 ? reinterpret_cast<float *>(base + L.ypart) : d.y;
-  p.phase = 1, p.afrag = hfrag, p.ainit = hinit, p.aunscale = hun, p.act_per_pair = 1;
+  p.phase = 1, p.act = d.h, p.act_per_pair = 1;
   p.rows = d.D, p.kb_total = d.F / 32, p.kb_split = pd.kb_split, p.n_ksplit = pd.n_ksplit, p.kc = pd.kc;
   p.n_stages = pd.n_stages, p.chunk_stride = pd.chunk_stride, p.frag_stride = pd.frag_stride;
   p.mt = pd.mt, p.kp = pd.kp, p.frag_cols = pd.frag_cols;
-  p.out = ypart, p.amax = nullptr;
+  p.out = ypart;
   e = d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, pd.smem, sm_count, s)
                                 : launch_phase<MER_DTYPE_Q8_0>(p, nt, pd.smem, sm_count, s);
   if (e != cudaSuccess) return e;
-  int n = 5;
+  int n = 3;
   if (pd.n_ksplit > 1) {
     size_t cnt = (size_t)P * d.D;
     k_reduce_ksplit<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(ypart, d.y, cnt, pd.n_ksplit);

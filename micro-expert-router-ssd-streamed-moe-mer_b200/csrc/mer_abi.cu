@@ -80,6 +80,17 @@ struct mer_backend {
 
   std::unordered_map<uint32_t, RouterEntry> routers;
   int kernel_path = 0;
+  // captured launch sequences of mer_moe_layer_forward_device, replayed with one cudaGraphLaunch
+  struct GraphEntry {
+    uint32_t layer;
+    size_t n_tokens;
+    const void *x, *out, *ids, *w;
+    cudaStream_t stream;
+    cudaGraphExec_t exec;
+    int launches;
+  };
+  std::vector<GraphEntry> graphs;
+  bool graphs_ok = true;
   // stage timing: sets of 5 events {start, after router, mid FFN, after FFN, after combine}
   bool timing_on = false;
   std::vector<cudaEvent_t> timing_events;
@@ -199,6 +210,13 @@ void drain_timing(mer_backend *b) {
   b->timing_used = 0;
 }
 
+void drop_graphs(mer_backend *b) {
+  if (b->graphs.empty()) return;
+  cudaDeviceSynchronize();
+  for (auto &g : b->graphs) cudaGraphExecDestroy(g.exec);
+  b->graphs.clear();
+}
+
 int check_device_status(mer_backend *b, uint32_t status, uint32_t layer, uint32_t expert) {
   b->err.device_status = status;
   if (status & MER_DEVSTAT_RESIDENCY_MISS)
@@ -250,6 +268,8 @@ void free_all(mer_backend *b) {
   if (b->ev_copy_done) cudaEventDestroy(b->ev_copy_done);
   for (auto &e : b->ev_stage)
     if (e) cudaEventDestroy(e);
+  for (auto &g : b->graphs) cudaGraphExecDestroy(g.exec);
+  b->graphs.clear();
   for (auto &e : b->timing_events) cudaEventDestroy(e);
   b->timing_events.clear();
   if (b->compute) cudaStreamDestroy(b->compute);
@@ -622,6 +642,7 @@ MER_EXPORT int mer_router_install(mer_backend *b, uint32_t layer, const float *h
   CU(MER_ERR_UPLOAD, "cudaSetDevice", cudaSetDevice(b->cfg.device));
   RouterEntry &r = b->routers[layer];
   CU(MER_ERR_UPLOAD, "cudaStreamSynchronize", cudaStreamSynchronize(b->compute));
+  drop_graphs(b);
   if (r.d_w) cudaFree(r.d_w), r.d_w = nullptr;
   if (r.d_cbias) cudaFree(r.d_cbias), r.d_cbias = nullptr;
   if (r.d_lbias) cudaFree(r.d_lbias), r.d_lbias = nullptr;
@@ -654,7 +675,7 @@ MER_EXPORT int mer_router_install(mer_backend *b, uint32_t layer, const float *h
 namespace {
 // Enqueues router (+ optional FFN + combine) for device-resident x on stream s.
 int enqueue_layer(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out, bool run_ffn_too,
-                  cudaStream_t s, int *launches, MoeDispatch *out_d) {
+                  cudaStream_t s, int *launches, MoeDispatch *out_d, bool capturing = false) {
   const uint32_t expert = MER_NONE;
   auto it = b->routers.find(layer);
   if (it == b->routers.end()) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "no router installed for layer %u", layer);
@@ -670,8 +691,8 @@ int enqueue_layer(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tok
   d.x = d_x;
   d.out = d_out;
   CU(MER_ERR_SUBMISSION, "cudaMemsetAsync(status)", cudaMemsetAsync(b->d_status, 0, 4, s));
-  CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, s));
-  cudaEvent_t *ev = run_ffn_too ? next_timing_set(b) : nullptr;
+  if (!capturing) CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, s));
+  cudaEvent_t *ev = (run_ffn_too && !capturing) ? next_timing_set(b) : nullptr;
   if (ev) cudaEventRecord(ev[0], s);
   CU(MER_ERR_SUBMISSION, "router kernel", launch_router(r, d, b->cfg.max_tokens, s, launches));
   if (run_ffn_too) {
@@ -870,13 +891,66 @@ MER_EXPORT int mer_moe_layer_forward_device(mer_backend *b, uint32_t layer, cons
   CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int launches = 0;
-  MoeDispatch d;
-  int rc = enqueue_layer(b, layer, d_x, n_tokens, d_out, true, s, &launches, &d);
-  if (rc) return rc;
-  size_t P = n_tokens * d.slots;
-  // routing is exported as stored: [n_tokens x slots] global ids (slots = top_k + shared)
-  if (d_ids) CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(ids)", cudaMemcpyAsync(d_ids, b->d_pair_expert, P * 4, cudaMemcpyDeviceToDevice, s));
-  if (d_weights) CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(w)", cudaMemcpyAsync(d_weights, b->d_pair_weight, P * 4, cudaMemcpyDeviceToDevice, s));
+  size_t P = 0;
+  const bool use_graph = b->graphs_ok && !b->timing_on && !(b->cfg.flags & MER_FLAG_NO_GRAPHS);
+  bool replayed = false;
+  if (use_graph) {
+    auto it = b->routers.find(layer);
+    if (it == b->routers.end()) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "no router installed for layer %u", layer);
+    P = n_tokens * (it->second.dev.top_k + (it->second.dev.shared_expert_id != MER_NONE ? 1u : 0u));
+    CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, s));  // outside any capture
+    mer_backend::GraphEntry *hit = nullptr;
+    for (auto &g : b->graphs)
+      if (g.layer == layer && g.n_tokens == n_tokens && g.x == d_x && g.out == d_out && g.ids == d_ids && g.w == d_weights &&
+          g.stream == s)
+        hit = &g;
+    if (!hit) {
+      // first call with these arguments: capture the launch sequence once
+      if (b->graphs.size() >= 256) drop_graphs(b);
+      cudaGraph_t graph = nullptr;
+      cudaGraphExec_t exec = nullptr;
+      bool ok = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+      int rc = MER_OK;
+      if (ok) {
+        MoeDispatch d;
+        rc = enqueue_layer(b, layer, d_x, n_tokens, d_out, true, s, &launches, &d, true);
+        if (rc == MER_OK && d_ids) ok = cudaMemcpyAsync(d_ids, b->d_pair_expert, P * 4, cudaMemcpyDeviceToDevice, s) == cudaSuccess;
+        if (rc == MER_OK && ok && d_weights)
+          ok = cudaMemcpyAsync(d_weights, b->d_pair_weight, P * 4, cudaMemcpyDeviceToDevice, s) == cudaSuccess;
+        cudaError_t ce = cudaStreamEndCapture(s, &graph);
+        ok = ok && ce == cudaSuccess && graph != nullptr;
+      }
+      if (rc != MER_OK) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        return rc;
+      }
+      if (ok) ok = cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
+      if (graph) cudaGraphDestroy(graph);
+      if (ok) {
+        b->graphs.push_back({layer, n_tokens, d_x, d_out, d_ids, d_weights, s, exec, launches});
+        hit = &b->graphs.back();
+      } else {
+        cudaGetLastError();
+        b->graphs_ok = false;  // capture is not available here: plain launches from now on
+      }
+    }
+    if (hit) {
+      CU(MER_ERR_SUBMISSION, "cudaGraphLaunch", cudaGraphLaunch(hit->exec, s));
+      launches = hit->launches;
+      replayed = true;
+    }
+  }
+  if (!replayed) {
+    launches = 0;
+    MoeDispatch d;
+    int rc = enqueue_layer(b, layer, d_x, n_tokens, d_out, true, s, &launches, &d);
+    if (rc) return rc;
+    P = n_tokens * d.slots;
+    // routing is exported as stored: [n_tokens x slots] global ids (slots = top_k + shared)
+    if (d_ids) CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(ids)", cudaMemcpyAsync(d_ids, b->d_pair_expert, P * 4, cudaMemcpyDeviceToDevice, s));
+    if (d_weights) CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(w)", cudaMemcpyAsync(d_weights, b->d_pair_weight, P * 4, cudaMemcpyDeviceToDevice, s));
+  }
   b->ctr.kernel_launches += (uint64_t)launches;
   b->ctr.selected_routed_experts += P;
   b->ctr.gpu_dispatch_attempts += P;
@@ -982,5 +1056,6 @@ MER_EXPORT int mer_set_kernel_path(mer_backend *b, int path) {
   if (path == 2 && !b->d_stream_scratch)
     return fail(b, MER_ERR_INELIGIBLE, 0, MER_NONE, "streaming kernels need d_model and d_ff to be multiples of 256");
   b->kernel_path = path;
+  drop_graphs(b);
   return MER_OK;
 }
