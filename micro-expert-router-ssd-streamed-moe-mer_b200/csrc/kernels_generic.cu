@@ -564,7 +564,15 @@ __global__ void __launch_bounds__(256) k_combine(MoeDispatch d) {
     size_t p = (size_t)token * d.slots + s;
     float w = d.pair_weight[p];
     if (d.pair_expert[p] == MER_NONE || w == 0.0f) continue;
-    acc = __fadd_rn(acc, __fmul_rn(w, d.y[p * d.D + i]));
+    float yv;
+    if (d.y_parts && d.y_nparts > 1) {  // the streaming FFN left K-split partials: add them in split order
+      const size_t n = (size_t)d.n_tokens * d.slots * d.D;
+      yv = d.y_parts[p * d.D + i];
+      for (uint32_t k = 1; k < d.y_nparts; k++) yv += d.y_parts[(size_t)k * n + p * d.D + i];
+    } else {
+      yv = d.y[p * d.D + i];
+    }
+    acc = __fadd_rn(acc, __fmul_rn(w, yv));
   }
   d.out[(size_t)token * d.D + i] = acc;
 }

@@ -16,14 +16,20 @@
 //   * The per-block f16 scale d is applied in fp32 when a block's partial is folded into the row
 //     accumulator: acc += d * partial (the ordering of matmul_q4_0.wgsl:65-85 in the reference).
 //
-// Work is cut into items (token pass, K split, 16-row-slot tile pair); each persistent CTA takes a
-// contiguous item range, so a CTA reloads activation fragments only when its (pass, K split)
-// changes and no atomics or inter-CTA waits are needed.  Every mbarrier wait is bounded: on
-// expiry the CTA latches MER_DEVSTAT_TIMEOUT, drains its own copies in flight and returns.
+// Work is cut into items (token pass, K split, group of 16 tiles).  Each of the 16 consumer warps of
+// a CTA owns one 16-row tile of the item over the item's K range: no warp ever waits for another
+// one's partial sums (an earlier version split K across warps and lost a third of its time at the
+// hand-off barrier).  Load balance comes from splitting K across CTAs instead: partial sums go to
+// scratch and the next kernel adds them (k_h_finalize applies SiLU(gate)*up, the combine kernel sums
+// the down partials), always in the same order, so results are deterministic.  Each persistent CTA
+// takes a contiguous item range and rebuilds activation fragments only when its (pass, K split)
+// changes; no atomics on data, no inter-CTA waits.  Every mbarrier wait is bounded: on expiry the
+// warp stops computing, the CTA latches MER_DEVSTAT_TIMEOUT, drains its copies in flight and returns.
 #include "kernels.h"
 
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <type_traits>
 
 #include "../../include/mer_b200.h"
@@ -48,14 +54,13 @@ struct StreamParams {
   uint32_t kc;               // blocks per pipeline stage
   uint32_t n_stages;
   uint32_t chunk_stride;     // bytes between the 16-row tile chunks of a stage (kc * 16 * block bytes)
-  uint32_t mt;               // packed tiles per item (= per stage); the 16 consumer warps form mt groups
-  uint32_t kp;               // warps that split the K range of one tile (mt * kp == 16)
   uint32_t frag_cols;        // fragment arrays held in shared memory: 2 * min(4 * NT, most tokens of any group)
   uint32_t frag_stride;      // bytes between (token, part) fragment arrays in shared memory
   uint32_t tokens_per_pass;  // 4 * NT
   const uint32_t *n_passes;  // device scalar
   const uint32_t *pass_group, *pass_start, *pass_count;
-  float *out;                // phase 0: h [P x F];  phase 1: y partials [n_ksplit][P x D]
+  float *out;                // phase 0: h [P x F], or gate/up partials [n_ksplit][P][2][F] when K is split;
+                             // phase 1: y partials [n_ksplit][P x D]
   uint32_t *amax;            // phase 0: per-pair max |h| as float bits (for the down phase's scaling)
 };
 
@@ -178,12 +183,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   float *s_un = reinterpret_cast<float *>(smem + 192);          // [TP] its 2^24 / scale
   uint32_t *s_amax = reinterpret_cast<uint32_t *>(smem + 224);  // [TP] max |activation| of its row, as float bits
   float *s_scale = reinterpret_cast<float *>(smem + 768);       // [TP] the row's power-of-two scale
-  float *s_red = reinterpret_cast<float *>(smem + HEADER_BYTES);            // [2][CONSUMER_WARPS][NT][4][32]
-  float *s_init = s_red + 2 * CONSUMER_WARPS * NT * 128;                    // [TP][kb_split]
+  float *s_init = reinterpret_cast<float *>(smem + HEADER_BYTES);           // [TP][kb_split]
   uint8_t *s_frag = reinterpret_cast<uint8_t *>(s_init + p.kb_split * TP);  // [TP*2][frag_stride]
   s_frag = reinterpret_cast<uint8_t *>(((size_t)s_frag + 127) & ~(size_t)127);
-  uint8_t *s_stage = s_frag + (size_t)p.frag_cols * p.frag_stride;          // [n_stages][mt tiles][chunk_stride]
-  const uint32_t stage_bytes = p.mt * p.chunk_stride;
+  uint8_t *s_stage = s_frag + (size_t)p.frag_cols * p.frag_stride;          // [n_stages][16 tiles][chunk_stride]
+  const uint32_t stage_bytes = CONSUMER_WARPS * p.chunk_stride;
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < p.n_stages; s++) {
@@ -195,7 +199,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   }
   __syncthreads();
 
-  const uint32_t n_tiles = p.rows / ((p.phase == 0 ? 8u : 16u) * p.mt);  // items per (pass, K split)
+  const uint32_t n_tiles = p.rows / ((p.phase == 0 ? 8u : 16u) * CONSUMER_WARPS);  // items per (pass, K split)
   const uint32_t n_passes = *p.n_passes;
   const uint64_t n_items = (uint64_t)n_passes * p.n_ksplit * n_tiles;
   const uint32_t item_beg = (uint32_t)(n_items * blockIdx.x / gridDim.x), item_end = (uint32_t)(n_items * (blockIdx.x + 1) / gridDim.x);
@@ -226,17 +230,17 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       uint32_t eid = d.group_expert[p.pass_group[pp]];
       const uint8_t *base = (eid < d.max_experts) ? d.expert_ptr[eid] : nullptr;
       if (!base) continue;  // consumers skip the same item
-      // item -> packed tiles mt*tile .. mt*tile + mt - 1 of the phase's region; lane m copies tile m's chunk
-      const uint8_t *src = base + (p.phase == 0 ? 0 : 2 * proj_bytes) + (size_t)(p.mt * tile + (lane % p.mt)) * tile_bytes;
+      // item -> packed tiles 16*tile .. 16*tile + 15 of the phase's region; lane m < 16 copies tile m's chunk
+      const uint8_t *src = base + (p.phase == 0 ? 0 : 2 * proj_bytes) + (size_t)(CONSUMER_WARPS * tile + (lane & 15)) * tile_bytes;
       for (uint32_t c0 = 0; c0 < kbn && ok; c0 += p.kc) {
         uint32_t nb = min(p.kc, kbn - c0);
         if (round > 0) ok = mbar_wait(&empty[stage], (round - 1) & 1);
         if (*(volatile uint32_t *)s_abort) ok = false;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (lane == 0) mbar_expect_tx(&full[stage], p.mt * nb * 16 * BB);
+        if (lane == 0) mbar_expect_tx(&full[stage], CONSUMER_WARPS * nb * 16 * BB);
         __syncwarp();
-        if (lane < p.mt)
+        if (lane < CONSUMER_WARPS)
           bulk_g2s(s_stage + (size_t)stage * stage_bytes + lane * p.chunk_stride, src + (size_t)(kb0 + c0) * 16 * BB, nb * 16 * BB,
                    &full[stage]);
         if (++stage == p.n_stages) stage = 0, round++;
@@ -255,11 +259,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
 
   // ---------------------------------------------------------------------- consumer warps
   const uint32_t g = lane >> 2, t = lane & 3;
-  const uint32_t KP = p.kp;
-  const uint32_t mtile = warp % p.mt, kpart = warp / p.mt;  // tile of the stage, share of its K range
-  const uint32_t stage0 = smem_u32(s_stage) + mtile * p.chunk_stride;  // this warp's tile chunk in stage 0
+  const uint32_t stage0 = smem_u32(s_stage) + warp * p.chunk_stride;  // this warp's tile chunk in stage 0
   const uint32_t frag0 = smem_u32(s_frag) + t * 16, init0 = smem_u32(s_init);
-  uint32_t stage = 0, round = 0, n_done = 0;  // n_done: resident items finished by this CTA
+  uint32_t stage = 0, round = 0;
   uint32_t cur_pp = MER_NONE, cur_ks = MER_NONE;
   // A warp whose bounded wait expired goes "dead": it stops computing and waiting but still walks
   // the same loop structure, so the named barriers below always see all consumer warps.
@@ -365,16 +367,22 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       }
       consumer_sync();  // fragments, seeds, s_pair, s_un visible to every warp
     }
+    const size_t n_pairs = (size_t)d.n_tokens * d.slots;
+    const bool split_gate_up = p.phase == 0 && p.n_ksplit > 1;
     if (!resident) {
       if (threadIdx.x == 0) atomicOr(d.status, MER_DEVSTAT_RESIDENCY_MISS);
-      // fail closed: zero outputs for this tile
-      const uint32_t rows_here = (p.phase == 0 ? 8u : 16u) * p.mt;
+      // fail closed: zero outputs for this item
+      const uint32_t rows_here = (p.phase == 0 ? 8u : 16u) * CONSUMER_WARPS;
       for (uint32_t i = threadIdx.x; i < rows_here * pcount; i += CONSUMER_WARPS * 32) {
-        uint32_t pair = d.perm[pstart + i / rows_here], row = tile * rows_here + i % rows_here;
-        if (p.phase == 0)
+        const uint32_t pair = d.perm[pstart + i / rows_here], row = tile * rows_here + i % rows_here;
+        if (split_gate_up) {
+          float *gp = p.out + ((size_t)ks * n_pairs + pair) * 2 * d.F;
+          gp[row] = 0.0f, gp[d.F + row] = 0.0f;
+        } else if (p.phase == 0) {
           p.out[(size_t)pair * d.F + row] = 0.0f;
-        else
-          p.out[((size_t)ks * d.n_tokens * d.slots + pair) * d.D + row] = 0.0f;
+        } else {
+          p.out[((size_t)ks * n_pairs + pair) * d.D + row] = 0.0f;
+        }
       }
       continue;
     }
@@ -436,13 +444,13 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       if (!dead) {
         constexpr uint32_t PAIR_BYTES = 2 * 16 * BB;  // 576 (Q4_0) / 1088 (Q8_0)
         const uint32_t np = nb >> 1;                  // block pairs in this chunk
-        uint32_t rec = stage0 + stage * stage_bytes + kpart * PAIR_BYTES;
-        uint32_t kb = c0 + 2 * kpart;
-        // this warp's pairs kpart, kpart + KP, ...; two pairs per iteration keep independent chains in flight
+        uint32_t rec = stage0 + stage * stage_bytes;
+        uint32_t kb = c0;
+        // two pairs per iteration keep independent MMA chains in flight
 #pragma unroll 1
-        for (uint32_t pr = kpart; pr < np; pr += 2 * KP, rec += 2 * KP * PAIR_BYTES, kb += 4 * KP) {
+        for (uint32_t pr = 0; pr < np; pr += 2, rec += 2 * PAIR_BYTES, kb += 4) {
           do_pair(rec, kb);
-          if (pr + KP < np) do_pair(rec + KP * PAIR_BYTES, kb + 2 * KP);
+          if (pr + 1 < np) do_pair(rec + PAIR_BYTES, kb + 2);
         }
       }
       __syncwarp();
@@ -450,45 +458,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       if (++stage == p.n_stages) stage = 0, round++;
     }
 
-    // ---- item epilogue.  The KP warps of a tile hand their K-split partials to ONE of them (the
-    // finisher, a role that rotates so the scalar epilogue work spreads over all warps) through
-    // double-buffered shared memory and one named barrier of the tile group (a sleeping wait: a
-    // polling wait here steals issue slots from the warps still computing).  A buffer is rewritten two
-    // items later, after every warp of the group - the previous finisher included - has passed the
-    // barrier of the item in between.
-    const uint32_t buf = n_done & 1;
-    const uint32_t finisher = KP > 1 ? (n_done % KP) : 0;
-    n_done++;
-    float v[NT][4];
-#pragma unroll
-    for (int n = 0; n < NT; n++)
-#pragma unroll
-      for (int i = 0; i < 4; i++) v[n][i] = acc[n][i];
-    if (KP > 1) {
-      float *red = s_red + (size_t)buf * CONSUMER_WARPS * NT * 128;
-      if (kpart != finisher) {
-#pragma unroll
-        for (int n = 0; n < NT; n++)
-#pragma unroll
-          for (int i = 0; i < 4; i++) red[((warp * NT + n) * 4 + i) * 32 + lane] = acc[n][i];
-      }
-      asm volatile("bar.sync %0, %1;" ::"r"(2 + mtile), "r"(KP * 32) : "memory");
-      if (kpart == finisher) {
-#pragma unroll
-        for (int n = 0; n < NT; n++)
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            float s0 = 0.0f;
-            for (uint32_t k2 = 0; k2 < KP; k2++) {  // fixed order k2 = 0..KP-1, own partial from registers
-              float part = (k2 == kpart) ? acc[n][i] : red[(((k2 * p.mt + mtile) * NT + n) * 4 + i) * 32 + lane];
-              s0 += part;
-            }
-            v[n][i] = s0;
-          }
-      }
-    }
-    if (kpart == finisher && !dead) {
-      const uint32_t ptile = p.mt * tile + mtile;  // packed tile index within the phase's region
+    // ---- item epilogue: this warp's tile is complete over the item's K range; write it out
+    if (!dead) {
+      const uint32_t ptile = CONSUMER_WARPS * tile + warp;  // packed tile index within the phase's region
 #pragma unroll
       for (int n = 0; n < NT; n++) {
         if (n > 0 && (uint32_t)n >= n_live) break;
@@ -496,8 +468,15 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
         const bool valid = tok < pcount;
         const uint32_t pair = valid ? s_pair[tok] : 0;
         const float un = valid ? s_un[tok] : 0.0f;
-        const float r_lo = (v[n][0] + v[n][1]) * un, r_hi = (v[n][2] + v[n][3]) * un;  // row slots g and g+8
-        if (p.phase == 0) {
+        const float r_lo = (acc[n][0] + acc[n][1]) * un, r_hi = (acc[n][2] + acc[n][3]) * un;  // row slots g and g+8
+        if (split_gate_up) {
+          // K is split across CTAs: leave gate and up partial sums; k_h_finalize adds them and applies SiLU
+          if (valid) {
+            float *gp = p.out + ((size_t)ks * n_pairs + pair) * 2 * d.F + ptile * 8 + g;
+            gp[0] = r_lo;
+            gp[d.F] = r_hi;
+          }
+        } else if (p.phase == 0) {
           // slots 0..7 of a gate/up tile are gate rows, slots 8..15 the matching up rows
           float gate = r_lo;
           if (d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit) && gate == gate)
@@ -511,7 +490,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
           for (int o = 4; o < 32; o <<= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
           if (valid && g == 0) atomicMax(p.amax + pair, bits);
         } else if (valid) {
-          float *yo = p.out + ((size_t)ks * d.n_tokens * d.slots + pair) * d.D + ptile * 16;
+          float *yo = p.out + ((size_t)ks * n_pairs + pair) * d.D + ptile * 16;
           yo[g] = r_lo;
           yo[g + 8] = r_hi;
         }
@@ -566,6 +545,36 @@ __global__ void __launch_bounds__(256) k_build_passes(MoeDispatch d, uint32_t to
   if (threadIdx.x == 0) *n_passes = s_cnt[256];
 }
 
+// h = SiLU(clamp(sum of gate partials)) * (sum of up partials), partials added in K-split order, plus the
+// row maximum of |h| that the down phase scales its activations by.  grid = (pairs, ceil(F / 1024)).
+__global__ void __launch_bounds__(256) k_h_finalize(const float *__restrict__ parts, uint32_t n_ksplit, uint32_t n_pairs, uint32_t F,
+                                                    float limit, float *__restrict__ h, uint32_t *__restrict__ amax) {
+  const uint32_t pair = blockIdx.x;
+  const uint32_t f0 = blockIdx.y * 1024 + threadIdx.x * 4;
+  float mx = 0.0f;
+  if (f0 < F) {
+    float4 g = make_float4(0, 0, 0, 0), u = make_float4(0, 0, 0, 0);
+    for (uint32_t k = 0; k < n_ksplit; k++) {
+      const float *base = parts + ((size_t)k * n_pairs + pair) * 2 * F;
+      const float4 a = *reinterpret_cast<const float4 *>(base + f0), b = *reinterpret_cast<const float4 *>(base + F + f0);
+      g.x += a.x, g.y += a.y, g.z += a.z, g.w += a.w;
+      u.x += b.x, u.y += b.y, u.z += b.z, u.w += b.w;
+    }
+    float gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {u.x, u.y, u.z, u.w}, hv[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      float gate = gv[i];
+      if (limit > 0.0f && isfinite(limit) && gate == gate) gate = fminf(fmaxf(gate, -limit), limit);
+      hv[i] = __fdividef(gate, 1.0f + __expf(-gate)) * uv[i];
+      mx = nan_max(mx, fabsf(hv[i]));
+    }
+    *reinterpret_cast<float4 *>(h + (size_t)pair * F + f0) = make_float4(hv[0], hv[1], hv[2], hv[3]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((threadIdx.x & 31) == 0) atomicMax(amax + pair, (mx != mx) ? 0x7fc00000u : __float_as_uint(mx));
+}
+
 __global__ void k_reduce_ksplit(const float *__restrict__ part, float *__restrict__ y, size_t n, uint32_t n_ksplit) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -575,61 +584,70 @@ __global__ void k_reduce_ksplit(const float *__restrict__ part, float *__restric
 }
 
 struct Plan {
-  uint32_t nt, kc, n_stages, chunk_stride, frag_stride, kb_split, n_ksplit, mt, kp, frag_cols;
+  uint32_t nt, kc, n_stages, chunk_stride, frag_stride, kb_split, n_ksplit, frag_cols;
   size_t smem;
 };
 
 constexpr size_t SMEM_LIMIT = 227 * 1024;
+constexpr uint32_t MAX_KSPLIT = 64;
 
-// Shapes one phase: tile-group shape (mt tiles x kp K-split warps), K split, stage size and depth.
-//  * items must stay fine enough to balance over the CTAs: mt is the largest of {16, 8, 4, 2} that still
-//    leaves about ten items per CTA for the expected number of active experts;
-//  * a stage holds `ppw` block pairs per warp (4 if at least four stages then fit, else 2, else 1);
+// Shapes one phase.  An item is 16 tiles (one per warp) over one K split.
+//  * K split: the largest split (whole K, K/2, K/4, ... in multiples of 8 blocks, at least 16 blocks)
+//    that still leaves about eight items per CTA for the expected number of active experts, within
+//    `max_ksplit` (what the partial-sum scratch can hold);
+//  * a stage holds 4 block pairs per warp if at least three stages then fit, else 2, else 1;
 //  * fragment arrays are sized by the most tokens any group can hold in this dispatch.
-Plan make_plan(int dtype, uint32_t kb_total, uint32_t packed_tiles, int phase, uint32_t nt, uint32_t max_group_tokens,
-               uint32_t active_groups, int n_ctas) {
+Plan make_plan(int dtype, uint32_t kb_total, uint32_t packed_tiles, uint32_t nt, uint32_t max_group_tokens,
+               uint32_t active_groups, int n_ctas, uint32_t max_ksplit) {
   const uint32_t bb = dtype == MER_DTYPE_Q4_0 ? MER_Q4_BLOCK_BYTES : MER_Q8_BLOCK_BYTES;
   const uint32_t tp = 4 * nt;
   Plan pl{};
-  // the K split applies to the down phase only (gate/up needs whole rows before SiLU)
-  uint32_t max_split_blocks = phase == 0 ? kb_total : 64u;
-  uint32_t n_ksplit = (kb_total + max_split_blocks - 1) / max_split_blocks;
-  uint32_t kb_split = ((kb_total + n_ksplit - 1) / n_ksplit + 7) / 8 * 8;
-  n_ksplit = (kb_total + kb_split - 1) / kb_split;
-  uint32_t mt = 2;
-  for (uint32_t cand = 16; cand > 2; cand >>= 1) {
-    uint64_t items = (uint64_t)active_groups * n_ksplit * (packed_tiles / cand);
-    if (packed_tiles % cand == 0 && items >= (uint64_t)10 * n_ctas && kb_split / 2 >= 4 * (CONSUMER_WARPS / cand)) {
-      mt = cand;
-      break;
-    }
+  if (packed_tiles % CONSUMER_WARPS) return pl;
+  const uint64_t items_per_split = (uint64_t)active_groups * (packed_tiles / CONSUMER_WARPS);
+  uint32_t n_ksplit = 1, kb_split = kb_total;
+  if (max_ksplit > MAX_KSPLIT) max_ksplit = MAX_KSPLIT;
+  while (items_per_split * n_ksplit < (uint64_t)8 * n_ctas) {
+    const uint32_t next_split = ((kb_total + 2 * n_ksplit - 1) / (2 * n_ksplit) + 7) / 8 * 8;  // blocks per split if doubled
+    if (next_split < 16 || next_split >= kb_split) break;
+    const uint32_t next_n = (kb_total + next_split - 1) / next_split;
+    if (next_n > max_ksplit) break;
+    kb_split = next_split, n_ksplit = next_n;
   }
-  const uint32_t kp = CONSUMER_WARPS / mt;
-  const uint32_t frag_cols = 2 * (max_group_tokens < tp ? max_group_tokens : tp);
-  const uint32_t frag_stride = kb_split * 64 + 64;
-  const size_t fixed = HEADER_BYTES + (size_t)2 * CONSUMER_WARPS * nt * 128 * 4 + (size_t)kb_split * tp * 4 + 128 + (size_t)frag_cols * frag_stride;
-  if (fixed >= SMEM_LIMIT) return pl;
-  const size_t avail = SMEM_LIMIT - fixed;
-  for (uint32_t ppw = 4; ppw >= 1; ppw >>= 1) {
-    uint32_t kc = 2 * kp * ppw;
-    if (kc > kb_split) kc = kb_split;  // the whole K split fits one stage
-    if (kc % 8) kc = (kc + 7) / 8 * 8;
-    const uint32_t chunk = kc * 16 * bb;
-    const size_t stage = (size_t)mt * chunk;
-    uint32_t n_stages = (uint32_t)(avail / stage);
-    if (n_stages > 8) n_stages = 8;
-    if (n_stages >= 4 || (ppw == 1 && n_stages >= 2)) {
-      pl = Plan{nt, kc, n_stages, chunk, frag_stride, kb_split, n_ksplit, mt, kp, frag_cols, fixed + n_stages * stage};
-      break;
+  // shared memory also bounds a split: the fragment arrays of one split must leave room for the ring
+  for (;;) {
+    const uint32_t frag_cols = 2 * (max_group_tokens < tp ? max_group_tokens : tp);
+    const uint32_t frag_stride = kb_split * 64 + 64;
+    const size_t fixed = HEADER_BYTES + (size_t)kb_split * tp * 4 + 128 + (size_t)frag_cols * frag_stride;
+    if (fixed < SMEM_LIMIT) {
+      const size_t avail = SMEM_LIMIT - fixed;
+      for (uint32_t ppw = 4; ppw >= 1; ppw >>= 1) {
+        uint32_t kc = 2 * ppw;
+        if (kc > kb_split) kc = kb_split;
+        const uint32_t chunk = kc * 16 * bb;
+        const size_t stage = (size_t)CONSUMER_WARPS * chunk;
+        uint32_t n_stages = (uint32_t)(avail / stage);
+        if (n_stages > 8) n_stages = 8;
+        if (n_stages >= 3 || (ppw == 1 && n_stages >= 2)) {
+          pl = Plan{nt, kc, n_stages, chunk, frag_stride, kb_split, n_ksplit, frag_cols, fixed + n_stages * stage};
+          return pl;
+        }
+      }
     }
+    // does not fit: halve the split (more partial sums) if the scratch allows
+    const uint32_t next_split = ((kb_split + 1) / 2 + 7) / 8 * 8;
+    if (next_split >= kb_split || next_split < 8) return pl;
+    const uint32_t next_n = (kb_total + next_split - 1) / next_split;
+    if (next_n > max_ksplit) return pl;
+    kb_split = next_split, n_ksplit = next_n;
   }
-  return pl;
 }
 
 struct ScratchLayout {
-  size_t amax, npass, pgroup, pstart, pcount, ypart, total;
+  size_t amax, npass, pgroup, pstart, pcount, parts, parts_bytes, total;
 };
 
+// `parts` holds the K-split partial sums of whichever phase is running: gate/up partials
+// [n_ksplit][P][2][F], then (after k_h_finalize has consumed them) down partials [n_ksplit][P][D].
 ScratchLayout scratch_layout(uint32_t max_pairs, uint32_t D, uint32_t F) {
   ScratchLayout L{};
   size_t off = 0;
@@ -643,8 +661,15 @@ ScratchLayout scratch_layout(uint32_t max_pairs, uint32_t D, uint32_t F) {
   L.pgroup = take((size_t)max_pairs * 4);
   L.pstart = take((size_t)max_pairs * 4);
   L.pcount = take((size_t)max_pairs * 4);
-  uint32_t n_ksplit = (F / 32 + 63) / 64 + 1;
-  L.ypart = take((size_t)n_ksplit * max_pairs * D * 4);
+  // room for 8 splits of the largest batch, but never less than 64 splits of an 8-pair dispatch, capped at 1 GiB
+  const size_t per_pair = (size_t)(2 * F > D ? 2 * F : D) * 4;
+  size_t want = (size_t)8 * max_pairs * per_pair;
+  const size_t small = (size_t)MAX_KSPLIT * 8 * per_pair;
+  if (want < small) want = small;
+  if (want > ((size_t)1 << 30)) want = (size_t)1 << 30;
+  if (want < (size_t)max_pairs * per_pair) want = (size_t)max_pairs * per_pair;
+  L.parts_bytes = want;
+  L.parts = take(want);
   L.total = off;
   return L;
 }
@@ -668,33 +693,40 @@ cudaError_t launch_phase(const StreamParams &p, uint32_t nt, size_t smem, int gr
 
 bool stream_ffn_supported(int dtype, uint32_t D, uint32_t F) {
   if (dtype != MER_DTYPE_Q4_0 && dtype != MER_DTYPE_Q8_0) return false;
-  if (D == 0 || F == 0 || D % 256 != 0 || F % 256 != 0) return false;  // 16-byte aligned rows, whole tiles
-  Plan a = make_plan(dtype, D / 32, F / 8, 0, 1, 4, 1, 148), b = make_plan(dtype, F / 32, D / 16, 1, 1, 4, 1, 148);
+  if (D == 0 || F == 0 || D % 256 != 0 || F % 256 != 0) return false;  // 16-byte aligned rows, whole 16-tile groups
+  Plan a = make_plan(dtype, D / 32, F / 8, 1, 4, 1, 148, MAX_KSPLIT), b = make_plan(dtype, F / 32, D / 16, 1, 4, 1, 148, MAX_KSPLIT);
   return a.n_stages >= 2 && b.n_stages >= 2;
 }
 
 size_t stream_ffn_scratch_bytes(uint32_t max_pairs, uint32_t D, uint32_t F) { return scratch_layout(max_pairs, D, F).total; }
 
-cudaError_t launch_ffn_stream(const MoeDispatch &d, void *scratch, int sm_count, cudaStream_t s, int *launches,
-                              cudaEvent_t ev_mid) {
+cudaError_t launch_ffn_stream(MoeDispatch &d, void *scratch, int sm_count, cudaStream_t s, int *launches, cudaEvent_t ev_mid) {
   const uint32_t P = d.n_tokens * d.slots;
   uint8_t *base = static_cast<uint8_t *>(scratch);
   // the layout is a function of the allocation-time maxima; only offsets matter here
   const ScratchLayout L = scratch_layout(d.scratch_pairs, d.D, d.F);
   const uint32_t mgt = d.max_group_tokens ? d.max_group_tokens : P, act = d.active_groups_hint ? d.active_groups_hint : 1;
+  // how many K splits of partial sums the scratch can hold for this dispatch
+  const uint32_t cap_gu = (uint32_t)std::min<size_t>(MAX_KSPLIT, L.parts_bytes / ((size_t)P * 2 * d.F * 4));
+  const uint32_t cap_dn = (uint32_t)std::min<size_t>(MAX_KSPLIT, L.parts_bytes / ((size_t)P * d.D * 4));
   uint32_t nt = mgt > 4 ? 2u : 1u;
-  Plan pg = make_plan(d.dtype, d.D / 32, d.F / 8, 0, nt, mgt, act, sm_count), pd = make_plan(d.dtype, d.F / 32, d.D / 16, 1, nt, mgt, act, sm_count);
+  Plan pg = make_plan(d.dtype, d.D / 32, d.F / 8, nt, mgt, act, sm_count, cap_gu);
+  Plan pd = make_plan(d.dtype, d.F / 32, d.D / 16, nt, mgt, act, sm_count, cap_dn);
   if (nt == 2 && (pg.n_stages < 3 || pd.n_stages < 3)) {  // eight tokens per pass do not fit: four per pass
     nt = 1;
-    pg = make_plan(d.dtype, d.D / 32, d.F / 8, 0, nt, mgt, act, sm_count), pd = make_plan(d.dtype, d.F / 32, d.D / 16, 1, nt, mgt, act, sm_count);
+    pg = make_plan(d.dtype, d.D / 32, d.F / 8, nt, mgt, act, sm_count, cap_gu);
+    pd = make_plan(d.dtype, d.F / 32, d.D / 16, nt, mgt, act, sm_count, cap_dn);
   }
   if (pg.n_stages < 2 || pd.n_stages < 2) return cudaErrorInvalidConfiguration;
   uint32_t *n_passes = reinterpret_cast<uint32_t *>(base + L.npass);
   uint32_t *pgroup = reinterpret_cast<uint32_t *>(base + L.pgroup), *pstart = reinterpret_cast<uint32_t *>(base + L.pstart),
            *pcount = reinterpret_cast<uint32_t *>(base + L.pcount), *amax = reinterpret_cast<uint32_t *>(base + L.amax);
+  float *parts = reinterpret_cast<float *>(base + L.parts);
   cudaError_t e;
+  int n = 0;
   k_build_passes<<<1, 256, 0, s>>>(d, 4 * nt, n_passes, pgroup, pstart, pcount, amax, P);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  n++;
   StreamParams p{};
   p.d = d;
   p.n_passes = n_passes, p.pass_group = pgroup, p.pass_start = pstart, p.pass_count = pcount;
@@ -703,30 +735,39 @@ cudaError_t launch_ffn_stream(const MoeDispatch &d, void *scratch, int sm_count,
   // phase 0: gate/up, activations = x by token
   p.phase = 0, p.act = d.x, p.act_per_pair = 0;
   p.rows = d.F, p.kb_total = d.D / 32, p.kb_split = pg.kb_split, p.n_ksplit = pg.n_ksplit, p.kc = pg.kc;
-  p.n_stages = pg.n_stages, p.chunk_stride = pg.chunk_stride, p.frag_stride = pg.frag_stride;
-  p.mt = pg.mt, p.kp = pg.kp, p.frag_cols = pg.frag_cols;
-  p.out = d.h;
+  p.n_stages = pg.n_stages, p.chunk_stride = pg.chunk_stride, p.frag_stride = pg.frag_stride, p.frag_cols = pg.frag_cols;
+  p.out = pg.n_ksplit > 1 ? parts : d.h;
   e = d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, pg.smem, sm_count, s)
                                 : launch_phase<MER_DTYPE_Q8_0>(p, nt, pg.smem, sm_count, s);
   if (e != cudaSuccess) return e;
-  if (ev_mid) cudaEventRecord(ev_mid, s);
-  // phase 1: down, activations = h by pair, scaled by the row maxima the gate/up epilogue collected
-  float *ypart = pd.n_ksplit > 1 ? reinterpret_cast<float *>(base + L.ypart) : d.y;
-  p.phase = 1, p.act = d.h, p.act_per_pair = 1;
-  p.rows = d.D, p.kb_total = d.F / 32, p.kb_split = pd.kb_split, p.n_ksplit = pd.n_ksplit, p.kc = pd.kc;
-  p.n_stages = pd.n_stages, p.chunk_stride = pd.chunk_stride, p.frag_stride = pd.frag_stride;
-  p.mt = pd.mt, p.kp = pd.kp, p.frag_cols = pd.frag_cols;
-  p.out = ypart;
-  e = d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, pd.smem, sm_count, s)
-                                : launch_phase<MER_DTYPE_Q8_0>(p, nt, pd.smem, sm_count, s);
-  if (e != cudaSuccess) return e;
-  int n = 3;
-  if (pd.n_ksplit > 1) {
-    size_t cnt = (size_t)P * d.D;
-    k_reduce_ksplit<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(ypart, d.y, cnt, pd.n_ksplit);
+  n++;
+  if (pg.n_ksplit > 1) {
+    k_h_finalize<<<dim3(P, (d.F + 1023) / 1024), 256, 0, s>>>(parts, pg.n_ksplit, P, d.F, d.swiglu_limit, d.h, amax);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     n++;
   }
+  if (ev_mid) cudaEventRecord(ev_mid, s);
+  // phase 1: down, activations = h by pair, scaled by the row maxima collected above
+  p.phase = 1, p.act = d.h, p.act_per_pair = 1;
+  p.rows = d.D, p.kb_total = d.F / 32, p.kb_split = pd.kb_split, p.n_ksplit = pd.n_ksplit, p.kc = pd.kc;
+  p.n_stages = pd.n_stages, p.chunk_stride = pd.chunk_stride, p.frag_stride = pd.frag_stride, p.frag_cols = pd.frag_cols;
+  p.out = pd.n_ksplit > 1 ? parts : d.y;
+  e = d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, pd.smem, sm_count, s)
+                                : launch_phase<MER_DTYPE_Q8_0>(p, nt, pd.smem, sm_count, s);
+  if (e != cudaSuccess) return e;
+  n++;
+  // the per-pair outputs are the K-split partials until somebody adds them: the combine kernel does, or
+  // launch_reduce_parts for entry points that return per-pair outputs
+  d.y_parts = pd.n_ksplit > 1 ? parts : nullptr;
+  d.y_nparts = pd.n_ksplit;
   if (launches) *launches += n;
   return cudaSuccess;
+}
+
+cudaError_t launch_reduce_parts(const MoeDispatch &d, cudaStream_t s, int *launches) {
+  if (!d.y_parts || d.y_nparts <= 1) return cudaSuccess;
+  size_t cnt = (size_t)d.n_tokens * d.slots * d.D;
+  k_reduce_ksplit<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(d.y_parts, d.y, cnt, d.y_nparts);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
 }

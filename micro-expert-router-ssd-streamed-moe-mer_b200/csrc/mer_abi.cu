@@ -167,7 +167,8 @@ bool use_stream_path(mer_backend *b, const MoeDispatch &d) {
   return stream_ffn_supported(d.dtype, d.D, d.F) && b->d_stream_scratch != nullptr;
 }
 
-cudaError_t run_ffn(mer_backend *b, const MoeDispatch &d, cudaStream_t s, int *launches, cudaEvent_t ev_mid = nullptr) {
+cudaError_t run_ffn(mer_backend *b, MoeDispatch &d, cudaStream_t s, int *launches, cudaEvent_t ev_mid = nullptr) {
+  d.y_parts = nullptr, d.y_nparts = 1;
   if (use_stream_path(b, d)) return launch_ffn_stream(d, b->d_stream_scratch, b->sm_count, s, launches, ev_mid);
   return launch_ffn_generic(d, s, launches, ev_mid);
 }
@@ -403,7 +404,7 @@ int admit_impl(mer_backend *b, uint32_t id, uint64_t generation, const void *blo
 // Shared tail of the host entry points whose routing comes from the caller: upload ids and
 // weights, group, run the FFN.  `single_group` = all pairs run the same expert.
 int dispatch_given_routing(mer_backend *b, uint32_t layer, MoeDispatch &d, const uint32_t *ids, const float *weights,
-                           size_t n_pairs, bool single_group, int *launches) {
+                           size_t n_pairs, bool single_group, int *launches, bool combine_follows = false) {
   const uint32_t expert = n_pairs ? ids[0] : MER_NONE;
   memcpy(b->h_u32, ids, n_pairs * sizeof(uint32_t));
   for (size_t i = 0; i < n_pairs; i++) b->h_f32[i] = weights ? weights[i] : 1.0f;
@@ -418,6 +419,7 @@ int dispatch_given_routing(mer_backend *b, uint32_t layer, MoeDispatch &d, const
   CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, b->compute));
   CU(MER_ERR_SUBMISSION, "group kernel", launch_groups_from_pairs(d, b->compute, launches));
   CU(MER_ERR_SUBMISSION, "expert FFN kernels", run_ffn(b, d, b->compute, launches));
+  if (!combine_follows) CU(MER_ERR_SUBMISSION, "partial-sum kernel", launch_reduce_parts(d, b->compute, launches));
   return MER_OK;
 }
 
@@ -837,7 +839,7 @@ MER_EXPORT int mer_moe_step_weighted_into(mer_backend *b, uint32_t layer, const 
   d.x = b->d_x;
   d.out = b->d_out;
   int launches = 0;
-  rc = dispatch_given_routing(b, layer, d, expert_ids, weights, n_slots, false, &launches);
+  rc = dispatch_given_routing(b, layer, d, expert_ids, weights, n_slots, false, &launches, true);
   if (rc) return rc;
   CU(MER_ERR_SUBMISSION, "combine kernel", launch_combine(d, b->compute, &launches));
   CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(out)", cudaMemcpyAsync(out, b->d_out, D * 4, cudaMemcpyDeviceToHost, b->compute));
