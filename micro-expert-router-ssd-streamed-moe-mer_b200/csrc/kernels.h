@@ -48,6 +48,10 @@ struct MoeDispatch {
   uint32_t scratch_pairs;   // pair capacity the streaming scratch was sized for
   uint32_t max_group_tokens;  // upper bound on the pairs of any one group in this dispatch
   uint32_t active_groups_hint;  // expected number of non-empty groups (shapes the work split)
+  // token passes of the streaming FFN (null when the generic kernels run): groups cut into runs of at most
+  // tokens_per_pass pairs, built by the grouping kernels; amax = per-pair max |h| cell, zeroed there too
+  uint32_t *pass_group, *pass_start, *pass_count, *n_passes, *amax;
+  uint32_t tokens_per_pass;
   const float *y_parts;     // set by the streaming FFN: K-split partials [y_nparts][P x D] of the per-pair outputs,
   uint32_t y_nparts;        //   or null / 1 when `y` already holds them
   int packed;               // 1: slots hold the tile-major fragment layout (layout.cuh), 0: the flat block stream
@@ -71,4 +75,6 @@ cudaError_t launch_f32_to_f16(const float *src, uint16_t *dst, size_t n, cudaStr
 bool stream_ffn_supported(int dtype, uint32_t D, uint32_t F);
 size_t stream_ffn_scratch_bytes(uint32_t max_pairs, uint32_t D, uint32_t F);
 cudaError_t launch_ffn_stream(MoeDispatch &d, void *scratch, int sm_count, cudaStream_t s, int *launches, cudaEvent_t ev_mid);
+// Points d.pass_* / d.amax into the scratch and picks tokens_per_pass for this dispatch (call before grouping).
+void stream_bind(MoeDispatch &d, void *scratch, int sm_count);
 cudaError_t launch_reduce_parts(const MoeDispatch &d, cudaStream_t s, int *launches);

@@ -9,6 +9,8 @@
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
+#include <climits>
+
 #include "../../include/mer_b200.h"
 #include "layout.cuh"
 
@@ -85,6 +87,47 @@ constexpr int ROUTER_ROWS = ROUTER_THREADS / 32;  // expert rows per CTA
 constexpr int ROUTER_TT = 4;                      // tokens per CTA
 constexpr uint32_t SMALL_P = 4096;                // pair keys staged in shared memory below this many pairs
 constexpr uint32_t STABLE_G = 512;                // stable (token, slot)-ordered grouping up to this many groups
+
+// Cuts every group into passes of at most d.tokens_per_pass pairs (the unit the streaming FFN works
+// on) and clears the per-pair max cells.  One CTA of 256 threads; `off` = the group offsets.
+__device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
+  __shared__ uint32_t s_pcnt[257];
+  const uint32_t tpp = d.tokens_per_pass, P = d.n_tokens * d.slots;
+  for (uint32_t i = threadIdx.x; i < P; i += 256) d.amax[i] = 0;
+  const uint32_t per = (d.n_groups + 255) / 256;
+  const uint32_t g0 = threadIdx.x * per, g1 = min(g0 + per, d.n_groups);
+  uint32_t mine = 0;
+  for (uint32_t g = g0; g < g1; g++) mine += (off[g + 1] - off[g] + tpp - 1) / tpp;
+  s_pcnt[threadIdx.x + 1] = mine;
+  if (threadIdx.x == 0) s_pcnt[0] = 0;
+  __syncthreads();
+  if (threadIdx.x < 32) {  // inclusive scan of 256 counts by one warp, 8 per lane
+    uint32_t v[8], run = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) run += s_pcnt[1 + threadIdx.x * 8 + i], v[i] = run;
+    uint32_t incl = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (threadIdx.x >= (uint32_t)o) incl += up;
+    }
+    const uint32_t base = incl - run;
+#pragma unroll
+    for (int i = 0; i < 8; i++) s_pcnt[1 + threadIdx.x * 8 + i] = base + v[i];
+  }
+  __syncthreads();
+  uint32_t np = s_pcnt[threadIdx.x];
+  for (uint32_t g = g0; g < g1; g++) {
+    const uint32_t beg = off[g], end = off[g + 1];
+    for (uint32_t st = beg; st < end; st += tpp) {
+      d.pass_group[np] = g;
+      d.pass_start[np] = st;
+      d.pass_count[np] = min(tpp, end - st);
+      np++;
+    }
+  }
+  if (threadIdx.x == 0) *d.n_passes = s_pcnt[256];
+}
 
 // Runs in one CTA after every token has been routed: groups pairs by expert.
 __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uint32_t *s_u32) {
@@ -187,6 +230,7 @@ __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uin
   }
   __syncthreads();
   for (uint32_t g = tid; g <= G; g += nt) d.offsets[g] = s_off[g];
+  if (d.pass_group) build_passes_block(d, s_off);
 }
 
 // Scoring, group filter, top-k and mixing weights of one token by one warp.
@@ -289,12 +333,11 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
       int key = total_key(s);
       if (bi == MER_NONE || key > bk) bk = key, bi = i;  // ascending scan keeps the lowest id on ties
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      int ok = __shfl_xor_sync(0xffffffffu, bk, o);
-      uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (oi != MER_NONE && (bi == MER_NONE || better(ok, oi, bk, bi))) bk = ok, bi = oi;
-    }
+    // warp arg-max by (key desc, id asc): two warp reductions; lanes without a candidate bid the lowest key
+    const int my_key = bi == MER_NONE ? INT_MIN : bk;
+    const int top_key = __reduce_max_sync(0xffffffffu, my_key);
+    const uint32_t top_id = __reduce_min_sync(0xffffffffu, (bi != MER_NONE && my_key == top_key) ? bi : MER_NONE);
+    bk = top_key, bi = top_id;
     if (bi == MER_NONE) break;
     if (lane == 0) s_ok[bi] = 0;
     if (lane == (n & 31)) my_id = bi;
@@ -341,12 +384,13 @@ __global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispa
     for (int rr = 0; rr < ROUTER_ROWS; rr++)
 #pragma unroll
       for (int tt = 0; tt < ROUTER_TT; tt++) acc[rr][tt] = 0.0f;
+#pragma unroll 2
     for (uint32_t i = lane; i < slice4; i += 32) {
       float4 b[ROUTER_TT], a[ROUTER_ROWS];
 #pragma unroll
       for (int tt = 0; tt < ROUTER_TT; tt++) {
-        const uint32_t tok = t0 + min((uint32_t)tt, n_here - 1);
-        b[tt] = __ldg(reinterpret_cast<const float4 *>(d.x + (size_t)tok * D) + warp * slice4 + i);
+        b[tt] = make_float4(0, 0, 0, 0);
+        if ((uint32_t)tt < n_here) b[tt] = __ldg(reinterpret_cast<const float4 *>(d.x + (size_t)(t0 + tt) * D) + warp * slice4 + i);
       }
 #pragma unroll
       for (int rr = 0; rr < ROUTER_ROWS; rr++) {
@@ -460,6 +504,10 @@ __global__ void k_groups_from_pairs(MoeDispatch d, int single_group) {
       d.offsets[P] = P;
     }
   }
+  if (d.pass_group) {
+    __syncthreads();  // the offsets written above are read back by the whole block
+    build_passes_block(d, d.offsets);
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -568,6 +616,7 @@ __global__ void __launch_bounds__(256) k_combine(MoeDispatch d) {
     if (d.y_parts && d.y_nparts > 1) {  // the streaming FFN left K-split partials: add them in split order
       const size_t n = (size_t)d.n_tokens * d.slots * d.D;
       yv = d.y_parts[p * d.D + i];
+#pragma unroll 8
       for (uint32_t k = 1; k < d.y_nparts; k++) yv += d.y_parts[(size_t)k * n + p * d.D + i];
     } else {
       yv = d.y[p * d.D + i];

@@ -56,12 +56,8 @@ struct StreamParams {
   uint32_t chunk_stride;     // bytes between the 16-row tile chunks of a stage (kc * 16 * block bytes)
   uint32_t frag_cols;        // fragment arrays held in shared memory: 2 * min(4 * NT, most tokens of any group)
   uint32_t frag_stride;      // bytes between (token, part) fragment arrays in shared memory
-  uint32_t tokens_per_pass;  // 4 * NT
-  const uint32_t *n_passes;  // device scalar
-  const uint32_t *pass_group, *pass_start, *pass_count;
   float *out;                // phase 0: h [P x F], or gate/up partials [n_ksplit][P][2][F] when K is split;
                              // phase 1: y partials [n_ksplit][P x D]
-  uint32_t *amax;            // phase 0: per-pair max |h| as float bits (for the down phase's scaling)
 };
 
 // ----------------------------------------------------------------------------- PTX helpers
@@ -200,7 +196,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   __syncthreads();
 
   const uint32_t n_tiles = p.rows / ((p.phase == 0 ? 8u : 16u) * CONSUMER_WARPS);  // items per (pass, K split)
-  const uint32_t n_passes = *p.n_passes;
+  const uint32_t n_passes = *d.n_passes;
   const uint64_t n_items = (uint64_t)n_passes * p.n_ksplit * n_tiles;
   const uint32_t item_beg = (uint32_t)(n_items * blockIdx.x / gridDim.x), item_end = (uint32_t)(n_items * (blockIdx.x + 1) / gridDim.x);
   if (item_beg >= item_end) return;
@@ -227,7 +223,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
     for (uint32_t item = item_beg; item < item_end && ok; item++, next_item()) {
       uint32_t kb0, kbn;
       kb_range(ks, kb0, kbn);
-      uint32_t eid = d.group_expert[p.pass_group[pp]];
+      uint32_t eid = d.group_expert[d.pass_group[pp]];
       const uint8_t *base = (eid < d.max_experts) ? d.expert_ptr[eid] : nullptr;
       if (!base) continue;  // consumers skip the same item
       // item -> packed tiles 16*tile .. 16*tile + 15 of the phase's region; lane m < 16 copies tile m's chunk
@@ -280,8 +276,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
     if (pp != cur_pp || ks != cur_ks) {
       // new activation fragments: first, everyone must be done with the old ones
       if (pp != cur_pp) {
-        pstart = p.pass_start[pp], pcount = p.pass_count[pp];
-        const uint32_t eid = d.group_expert[p.pass_group[pp]];
+        pstart = d.pass_start[pp], pcount = d.pass_count[pp];
+        const uint32_t eid = d.group_expert[d.pass_group[pp]];
         resident = eid < d.max_experts && d.expert_ptr[eid] != nullptr;
       }
       consumer_sync();
@@ -294,7 +290,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
         uint32_t pair = 0, mx = 0;
         if (threadIdx.x < pcount) {
           pair = d.perm[pstart + threadIdx.x];
-          if (p.phase == 1) mx = p.amax[pair];  // collected by the gate/up epilogue
+          if (p.phase == 1) mx = d.amax[pair];  // collected by the gate/up epilogue
         }
         s_pair[threadIdx.x] = pair;
         s_amax[threadIdx.x] = mx;
@@ -488,7 +484,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
           // max over the 8 rows held by the lanes that share t (all lanes take part in the shuffles)
 #pragma unroll
           for (int o = 4; o < 32; o <<= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
-          if (valid && g == 0) atomicMax(p.amax + pair, bits);
+          if (valid && g == 0) atomicMax(d.amax + pair, bits);
         } else if (valid) {
           float *yo = p.out + ((size_t)ks * n_pairs + pair) * d.D + ptile * 16;
           yo[g] = r_lo;
@@ -503,48 +499,6 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   }
 }
 
-// Token passes: every group with tokens is cut into passes of at most tokens_per_pass pairs.
-// Each thread owns a contiguous run of groups; a 256-entry scan gives every run its first pass.
-__global__ void __launch_bounds__(256) k_build_passes(MoeDispatch d, uint32_t tokens_per_pass, uint32_t *n_passes,
-                                                      uint32_t *pass_group, uint32_t *pass_start, uint32_t *pass_count,
-                                                      uint32_t *amax, uint32_t n_pairs) {
-  __shared__ uint32_t s_cnt[257];
-  for (uint32_t i = threadIdx.x; i < n_pairs; i += 256) amax[i] = 0;
-  const uint32_t per = (d.n_groups + 255) / 256;
-  const uint32_t g0 = threadIdx.x * per, g1 = min(g0 + per, d.n_groups);
-  uint32_t mine = 0;
-  for (uint32_t g = g0; g < g1; g++) mine += (d.offsets[g + 1] - d.offsets[g] + tokens_per_pass - 1) / tokens_per_pass;
-  s_cnt[threadIdx.x + 1] = mine;
-  if (threadIdx.x == 0) s_cnt[0] = 0;
-  __syncthreads();
-  if (threadIdx.x < 32) {  // inclusive scan of 256 counts by one warp, 8 per lane
-    uint32_t v[8], run = 0;
-#pragma unroll
-    for (int i = 0; i < 8; i++) run += s_cnt[1 + threadIdx.x * 8 + i], v[i] = run;
-    uint32_t incl = run;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
-      if (threadIdx.x >= (uint32_t)o) incl += up;
-    }
-    uint32_t base = incl - run;
-#pragma unroll
-    for (int i = 0; i < 8; i++) s_cnt[1 + threadIdx.x * 8 + i] = base + v[i];
-  }
-  __syncthreads();
-  uint32_t np = s_cnt[threadIdx.x];
-  for (uint32_t g = g0; g < g1; g++) {
-    uint32_t beg = d.offsets[g], end = d.offsets[g + 1];
-    for (uint32_t st = beg; st < end; st += tokens_per_pass) {
-      pass_group[np] = g;
-      pass_start[np] = st;
-      pass_count[np] = min(tokens_per_pass, end - st);
-      np++;
-    }
-  }
-  if (threadIdx.x == 0) *n_passes = s_cnt[256];
-}
-
 // h = SiLU(clamp(sum of gate partials)) * (sum of up partials), partials added in K-split order, plus the
 // row maximum of |h| that the down phase scales its activations by.  grid = (pairs, ceil(F / 1024)).
 __global__ void __launch_bounds__(256) k_h_finalize(const float *__restrict__ parts, uint32_t n_ksplit, uint32_t n_pairs, uint32_t F,
@@ -554,6 +508,7 @@ __global__ void __launch_bounds__(256) k_h_finalize(const float *__restrict__ pa
   float mx = 0.0f;
   if (f0 < F) {
     float4 g = make_float4(0, 0, 0, 0), u = make_float4(0, 0, 0, 0);
+#pragma unroll 4
     for (uint32_t k = 0; k < n_ksplit; k++) {
       const float *base = parts + ((size_t)k * n_pairs + pair) * 2 * F;
       const float4 a = *reinterpret_cast<const float4 *>(base + f0), b = *reinterpret_cast<const float4 *>(base + F + f0);
@@ -700,38 +655,56 @@ bool stream_ffn_supported(int dtype, uint32_t D, uint32_t F) {
 
 size_t stream_ffn_scratch_bytes(uint32_t max_pairs, uint32_t D, uint32_t F) { return scratch_layout(max_pairs, D, F).total; }
 
-cudaError_t launch_ffn_stream(MoeDispatch &d, void *scratch, int sm_count, cudaStream_t s, int *launches, cudaEvent_t ev_mid) {
+namespace {
+struct Plans {
+  uint32_t nt;
+  Plan gate_up, down;
+};
+// Token-pass width and both phase plans of a dispatch (pure function of its shape and hints).
+Plans plan_dispatch(const MoeDispatch &d, int sm_count) {
   const uint32_t P = d.n_tokens * d.slots;
-  uint8_t *base = static_cast<uint8_t *>(scratch);
-  // the layout is a function of the allocation-time maxima; only offsets matter here
   const ScratchLayout L = scratch_layout(d.scratch_pairs, d.D, d.F);
   const uint32_t mgt = d.max_group_tokens ? d.max_group_tokens : P, act = d.active_groups_hint ? d.active_groups_hint : 1;
   // how many K splits of partial sums the scratch can hold for this dispatch
   const uint32_t cap_gu = (uint32_t)std::min<size_t>(MAX_KSPLIT, L.parts_bytes / ((size_t)P * 2 * d.F * 4));
   const uint32_t cap_dn = (uint32_t)std::min<size_t>(MAX_KSPLIT, L.parts_bytes / ((size_t)P * d.D * 4));
-  uint32_t nt = mgt > 4 ? 2u : 1u;
-  Plan pg = make_plan(d.dtype, d.D / 32, d.F / 8, nt, mgt, act, sm_count, cap_gu);
-  Plan pd = make_plan(d.dtype, d.F / 32, d.D / 16, nt, mgt, act, sm_count, cap_dn);
-  if (nt == 2 && (pg.n_stages < 3 || pd.n_stages < 3)) {  // eight tokens per pass do not fit: four per pass
-    nt = 1;
-    pg = make_plan(d.dtype, d.D / 32, d.F / 8, nt, mgt, act, sm_count, cap_gu);
-    pd = make_plan(d.dtype, d.F / 32, d.D / 16, nt, mgt, act, sm_count, cap_dn);
+  Plans pl{};
+  pl.nt = mgt > 4 ? 2u : 1u;
+  pl.gate_up = make_plan(d.dtype, d.D / 32, d.F / 8, pl.nt, mgt, act, sm_count, cap_gu);
+  pl.down = make_plan(d.dtype, d.F / 32, d.D / 16, pl.nt, mgt, act, sm_count, cap_dn);
+  if (pl.nt == 2 && (pl.gate_up.n_stages < 3 || pl.down.n_stages < 3)) {  // eight tokens per pass do not fit: four per pass
+    pl.nt = 1;
+    pl.gate_up = make_plan(d.dtype, d.D / 32, d.F / 8, pl.nt, mgt, act, sm_count, cap_gu);
+    pl.down = make_plan(d.dtype, d.F / 32, d.D / 16, pl.nt, mgt, act, sm_count, cap_dn);
   }
-  if (pg.n_stages < 2 || pd.n_stages < 2) return cudaErrorInvalidConfiguration;
-  uint32_t *n_passes = reinterpret_cast<uint32_t *>(base + L.npass);
-  uint32_t *pgroup = reinterpret_cast<uint32_t *>(base + L.pgroup), *pstart = reinterpret_cast<uint32_t *>(base + L.pstart),
-           *pcount = reinterpret_cast<uint32_t *>(base + L.pcount), *amax = reinterpret_cast<uint32_t *>(base + L.amax);
+  return pl;
+}
+}  // namespace
+
+void stream_bind(MoeDispatch &d, void *scratch, int sm_count) {
+  uint8_t *base = static_cast<uint8_t *>(scratch);
+  const ScratchLayout L = scratch_layout(d.scratch_pairs, d.D, d.F);
+  d.n_passes = reinterpret_cast<uint32_t *>(base + L.npass);
+  d.pass_group = reinterpret_cast<uint32_t *>(base + L.pgroup);
+  d.pass_start = reinterpret_cast<uint32_t *>(base + L.pstart);
+  d.pass_count = reinterpret_cast<uint32_t *>(base + L.pcount);
+  d.amax = reinterpret_cast<uint32_t *>(base + L.amax);
+  d.tokens_per_pass = 4 * plan_dispatch(d, sm_count).nt;
+}
+
+cudaError_t launch_ffn_stream(MoeDispatch &d, void *scratch, int sm_count, cudaStream_t s, int *launches, cudaEvent_t ev_mid) {
+  const uint32_t P = d.n_tokens * d.slots;
+  uint8_t *base = static_cast<uint8_t *>(scratch);
+  const ScratchLayout L = scratch_layout(d.scratch_pairs, d.D, d.F);
+  const Plans pl = plan_dispatch(d, sm_count);
+  const Plan &pg = pl.gate_up, &pd = pl.down;
+  const uint32_t nt = pl.nt;
+  if (pg.n_stages < 2 || pd.n_stages < 2 || !d.pass_group || d.tokens_per_pass != 4 * nt) return cudaErrorInvalidConfiguration;
   float *parts = reinterpret_cast<float *>(base + L.parts);
   cudaError_t e;
   int n = 0;
-  k_build_passes<<<1, 256, 0, s>>>(d, 4 * nt, n_passes, pgroup, pstart, pcount, amax, P);
-  if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  n++;
   StreamParams p{};
   p.d = d;
-  p.n_passes = n_passes, p.pass_group = pgroup, p.pass_start = pstart, p.pass_count = pcount;
-  p.tokens_per_pass = 4 * nt;
-  p.amax = amax;
   // phase 0: gate/up, activations = x by token
   p.phase = 0, p.act = d.x, p.act_per_pair = 0;
   p.rows = d.F, p.kb_total = d.D / 32, p.kb_split = pg.kb_split, p.n_ksplit = pg.n_ksplit, p.kc = pg.kc;
@@ -742,7 +715,7 @@ cudaError_t launch_ffn_stream(MoeDispatch &d, void *scratch, int sm_count, cudaS
   if (e != cudaSuccess) return e;
   n++;
   if (pg.n_ksplit > 1) {
-    k_h_finalize<<<dim3(P, (d.F + 1023) / 1024), 256, 0, s>>>(parts, pg.n_ksplit, P, d.F, d.swiglu_limit, d.h, amax);
+    k_h_finalize<<<dim3(P, (d.F + 1023) / 1024), 256, 0, s>>>(parts, pg.n_ksplit, P, d.F, d.swiglu_limit, d.h, d.amax);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     n++;
   }

@@ -416,6 +416,7 @@ int dispatch_given_routing(mer_backend *b, uint32_t layer, MoeDispatch &d, const
   d.n_groups = single_group ? 1u : (uint32_t)n_pairs;
   d.max_group_tokens = single_group ? (uint32_t)n_pairs : 1u;
   d.active_groups_hint = d.n_groups;
+  if (use_stream_path(b, d)) stream_bind(d, b->d_stream_scratch, b->sm_count);
   CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, b->compute));
   CU(MER_ERR_SUBMISSION, "group kernel", launch_groups_from_pairs(d, b->compute, launches));
   CU(MER_ERR_SUBMISSION, "expert FFN kernels", run_ffn(b, d, b->compute, launches));
@@ -690,6 +691,7 @@ int enqueue_layer(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tok
   d.n_groups = r.num_experts + (r.shared_expert_id != MER_NONE ? 1u : 0u);
   d.max_group_tokens = d.n_tokens;  // a token reaches an expert at most once
   d.active_groups_hint = std::min(d.n_groups, d.n_tokens * d.slots);
+  if (run_ffn_too && use_stream_path(b, d)) stream_bind(d, b->d_stream_scratch, b->sm_count);
   d.x = d_x;
   d.out = d_out;
   CU(MER_ERR_SUBMISSION, "cudaMemsetAsync(status)", cudaMemsetAsync(b->d_status, 0, 4, s));
