@@ -37,6 +37,13 @@ WORKLOADS = {  # name -> (config, default batch, default layers)
     "cfg4": ("cfg4-deepseek-v3-q4_0", 16, 1),
 }
 DTYPE_NAME = {0: "q4_0", 1: "q8_0"}
+PARALLELISM_NOTE = {
+    "replicas": "{n} replicas, tokens data-parallel, no data-path collective",
+    "ep-peer": "expert-parallel over {n} GPUs (experts split contiguously, tokens data-parallel), dispatch and combine by the "
+               "library's kernels through peer memory over NVLink",
+    "ep-collective": "expert-parallel over {n} GPUs (experts split contiguously, tokens data-parallel), NCCL all-gather of "
+                     "tokens+routing and reduce-scatter of partial outputs",
+}
 
 
 def parse_args():
@@ -51,6 +58,9 @@ def parse_args():
     ap.add_argument("--kernel-path", type=int, default=0, help="0 auto, 1 generic, 2 streaming")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="bound on the CPU baseline leg")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--parallelism", default="auto", choices=["auto", "replicas", "ep-peer", "ep-collective"],
+                    help="N > 1: expert-parallel with the exchange through peer memory (default) or through NCCL "
+                         "collectives, or independent token-parallel replicas")
     return ap.parse_args()
 
 
@@ -148,6 +158,12 @@ def main():
     cfg_name, def_batch, def_layers = WORKLOADS[args.workload]
     B = args.batch or def_batch
     R = args.layers or def_layers
+    mode = args.parallelism
+    if mode == "auto":
+        mode = "ep-peer" if world > 1 else "replicas"
+    if world == 1:
+        mode = "replicas"
+    ep_mode = mode.startswith("ep-")
     import mer_b200  # noqa: F401  (registers the package alias)
     synth = importlib.import_module("mer_b200.synth")
     cfg = synth.CONFIGS[cfg_name]
@@ -157,7 +173,7 @@ def main():
             "data": "synthetic"}
     config = {"workload": workload, "weights": DTYPE_NAME[cfg.dtype], "batch_per_gpu": B, "resident_layers": R,
               "l2": f"steps rotate over {R} distinct resident layers; one step streams more expert bytes than L2 holds" if R > 1
-              else "single layer", "parallelism": "single GPU" if args.gpus == 1 else f"{args.gpus} replicas, tokens data-parallel, no data-path collective"}
+              else "single layer", "parallelism": "single GPU" if args.gpus == 1 else PARALLELISM_NOTE[mode].format(n=args.gpus)}
 
     if args.impl == "reference":
         if rank != 0:
@@ -187,8 +203,11 @@ def main():
     n_exp = cfg.num_experts + (1 if cfg.shared else 0)
     exp_bytes = mer_b200.expert_bytes(cfg.dtype, cfg.d_model, cfg.d_ff)
     stride = (256 + exp_bytes + 4095) // 4096 * 4096
-    be = mer_b200.Backend(cfg.dtype, cfg.d_model, cfg.d_ff, stride * n_exp * R, (R + 1) * cfg.num_experts + R, max_tokens=B,
-                          max_top_k=slots, device=local_rank)
+    epm = importlib.import_module("mer_b200.expert_parallel")
+    mine = set(epm.local_expert_range(rank, world, cfg.num_experts)) if ep_mode else set(range(cfg.num_experts))
+    n_local = len(mine) + (1 if cfg.shared else 0)
+    be = mer_b200.Backend(cfg.dtype, cfg.d_model, cfg.d_ff, stride * n_local * R, (R + 1) * cfg.num_experts + R,
+                          max_tokens=B * world if ep_mode else B, max_top_k=slots, device=local_rank)
     if args.kernel_path:
         be.set_kernel_path(args.kernel_path)
     layers = build_layers(synth, cfg, R)
@@ -196,7 +215,8 @@ def main():
     xs_host = []
     for l, (blobs, shared, W) in enumerate(layers):
         for e, blob in enumerate(blobs):
-            be.admit(l * cfg.num_experts + e, 1, blob, wait=False)
+            if e in mine:
+                be.admit(l * cfg.num_experts + e, 1, blob, wait=False)
         shared_id = 0xFFFFFFFF
         if shared is not None:
             shared_id = R * cfg.num_experts + l
@@ -214,16 +234,36 @@ def main():
     xs = [torch.from_numpy(x).to(dev) for x in xs_host]
     out = torch.empty(B, cfg.d_model, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
-    for l in range(R):  # routing per layer -> distinct experts hit -> algorithmic bytes
-        _, ids, _ = be.moe_layer_forward(l, xs_host[l])
-        distinct = len(np.unique(ids[ids != 0xFFFFFFFF])) + (1 if cfg.shared else 0)
+    for l in range(R):  # routing per layer -> distinct (local) experts hit -> algorithmic bytes of this rank
+        if ep_mode:
+            x_all = np.concatenate([synth.make_activations(B, cfg.d_model, cfg.seed, r * R + l) for r in range(world)])
+            ids, _ = be.route(l, x_all)
+            hit = [e for e in np.unique(ids[ids != 0xFFFFFFFF]) if int(e) in mine]
+            distinct = len(hit) + (1 if cfg.shared else 0)
+        else:
+            _, ids, _ = be.moe_layer_forward(l, xs_host[l])
+            distinct = len(np.unique(ids[ids != 0xFFFFFFFF])) + (1 if cfg.shared else 0)
         hit_bytes.append(distinct * exp_bytes)
     router_bytes = cfg.num_experts * cfg.d_model * 4
     io_bytes = 2 * B * cfg.d_model * 4 + B * cfg.top_k * 8
 
-    def step(i):
+    ep = None
+    if ep_mode:
+        ep = epm.ExpertParallel(be, rank, world, cfg.num_experts, B)
+        if mode == "ep-peer":
+            ep.attach()
+            dist.barrier()
+
+    def step(i, x=None, o=None):
         l = i % R
-        be.moe_layer_forward_device(l, xs[l].data_ptr(), B, out.data_ptr(), stream)
+        x = xs[l] if x is None else x
+        o = out if o is None else o
+        if mode == "ep-peer":
+            ep.layer_forward_peer(l, x.data_ptr(), B, o.data_ptr(), stream)
+        elif mode == "ep-collective":
+            ep.layer_forward_collective(l, x, o, slots)
+        else:
+            be.moe_layer_forward_device(l, x.data_ptr(), B, o.data_ptr(), stream)
 
     def barrier():
         torch.cuda.synchronize()
@@ -247,25 +287,41 @@ def main():
     barrier()
     ms_total = e0.elapsed_time(e1)
     launches = be.snapshot()["kernel_launches"] - launches0
-    be.synchronize()  # surfaces a latched device status, if any
+    if ep_mode:
+        ep.check(0, stream)  # surfaces a latched device status (a peer that never answered, a missing expert)
+    else:
+        be.synchronize()
 
     # stage timing pass (same steps, events around each stage) for the roofline of the dominant kernel
-    be.stage_timing_enable(True)
-    for i in range(args.steps):
-        step(i)
-    torch.cuda.synchronize()
-    st = be.stage_timings()
-    be.stage_timing_enable(False)
+    st = None
+    if not ep_mode:
+        be.stage_timing_enable(True)
+        for i in range(args.steps):
+            step(i)
+        torch.cuda.synchronize()
+        st = be.stage_timings()
+        be.stage_timing_enable(False)
 
-    # end to end: host buffers through the public host entry point
+    # end to end: host buffers in, host buffers out, copies inside the timed region
     pinned_in = [torch.from_numpy(x).pin_memory() for x in xs_host]
     pinned_out = torch.empty(B, cfg.d_model).pin_memory()
+    x_dev = torch.empty(B, cfg.d_model, device=dev)
+
+    def e2e_step(i):
+        if ep_mode:  # pinned host rows -> device, the expert-parallel layer, result back to pinned host memory
+            x_dev.copy_(pinned_in[i % R], non_blocking=True)
+            step(i, x_dev, out)
+            pinned_out.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        else:  # the library's host entry point does the same copies itself
+            be.moe_layer_forward(i % R, pinned_in[i % R].numpy(), return_routing=False, out=pinned_out.numpy())
+
     for i in range(3):
-        be.moe_layer_forward(i % R, pinned_in[i % R].numpy(), return_routing=False, out=pinned_out.numpy())
+        e2e_step(i)
     barrier()
     t0 = time.perf_counter()
     for i in range(args.steps):
-        be.moe_layer_forward(i % R, pinned_in[i % R].numpy(), return_routing=False, out=pinned_out.numpy())
+        e2e_step(i)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else None
@@ -286,17 +342,24 @@ def main():
     layer_bytes = mean_hit + router_bytes + io_bytes
     hbm_gbs = layer_bytes * steps / (ms_total * 1e-3) / 1e9
     peak, peak_kind = measured_peak()
-    n = max(st["samples"], 1)
-    gu_ms, dn_ms = st["expert_gate_up_kernel_ms"] / n, st["expert_down_kernel_ms"] / n
-    fused = dn_ms == 0.0
-    kernel_bytes = (mean_hit if fused else mean_hit * 2 / 3) + B * cfg.d_model * 4
-    achieved = kernel_bytes / (gu_ms * 1e-3) / 1e9 if gu_ms > 0 else None
-    kname = "expert_ffn (gate/up + SiLU*mul + down)" if fused else "expert_gate_up (gate/up dequant-matvec + SiLU*mul)"
-    roofline = {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak if achieved else None, "peak_source": f"of {peak_kind}",
-                "traffic": ncu_traffic(f"{args.workload}-b{B}"), "algorithmic_bytes_per_launch": kernel_bytes,
-                "avg_launch_ms": gu_ms, "frac_of_8tbs": achieved / 8000.0 if achieved else None}
-    stages = {k: v / n for k, v in st.items() if k != "samples"}
+    if st is not None:
+        n = max(st["samples"], 1)
+        gu_ms, dn_ms = st["expert_gate_up_kernel_ms"] / n, st["expert_down_kernel_ms"] / n
+        fused = dn_ms == 0.0
+        kernel_bytes = (mean_hit if fused else mean_hit * 2 / 3) + B * cfg.d_model * 4
+        achieved = kernel_bytes / (gu_ms * 1e-3) / 1e9 if gu_ms > 0 else None
+        kname = "expert_ffn (gate/up + SiLU*mul + down)" if fused else "expert_gate_up (gate/up dequant-matvec + SiLU*mul)"
+        roofline = {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak if achieved else None, "peak_source": f"of {peak_kind}",
+                    "traffic": ncu_traffic(f"{args.workload}-b{B}"), "algorithmic_bytes_per_launch": kernel_bytes,
+                    "avg_launch_ms": gu_ms, "frac_of_8tbs": achieved / 8000.0 if achieved else None}
+        stages = {k: v / n for k, v in st.items() if k != "samples"}
+    else:
+        # expert-parallel step: no per-stage timers; the whole step of rank 0 against the bytes its experts stream
+        roofline = {"bound": "hbm", "kernel": "whole expert-parallel step of one rank (router, exchange, local experts, combine)",
+                    "achieved": hbm_gbs, "peak": peak, "unit": "GB/s", "frac": hbm_gbs / peak, "peak_source": f"of {peak_kind}",
+                    "traffic": None, "algorithmic_bytes_per_launch": layer_bytes, "avg_launch_ms": ms_total / steps}
+        stages = None
     line = dict(base, value=value, ms_per_step=ms_total / steps, config=config, clocks=clocks,
                 e2e={"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * cfg.d_model * 4,
                      "d2h_bytes_per_step": B * cfg.d_model * 4},

@@ -259,6 +259,54 @@ int mer_stage_timing_enable(mer_backend *b, int on);
 /* Waits for the recorded events and returns the accumulated per-stage times. */
 int mer_stage_timings_read(mer_backend *b, mer_stage_timings *out);
 
+/* ---- expert parallelism: one backend per GPU, the experts of every layer split contiguously over
+ * the ranks (rank j owns the local indices [j*ceil(E/world), (j+1)*ceil(E/world))), a shared expert
+ * replicated on every rank and run for the rank's own tokens.  Stands in for the reference's only
+ * multi-node expert placement, ShardRouter / RouteExperts (distributed.rs, docs/distributed.md:16-50:
+ * router node computes top-k, fans out per shard, sums weighted outputs; a shard that times out
+ * contributes zero and is counted).  Here a peer that does not answer within wait_ms latches
+ * MER_DEVSTAT_TIMEOUT and the call fails with MER_ERR_TIMEOUT at the next mer_stream_check.
+ * The backend's max_tokens must cover world * max_tokens_per_rank; a rank admits only its own
+ * experts (plus the shared expert). ---- */
+#define MER_EP_MAX_WORLD 16
+#define MER_EP_HANDLE_BYTES 64
+typedef struct mer_ep_cfg {
+  uint32_t rank, world;
+  uint32_t experts_per_layer;   /* routed experts per layer (E) */
+  uint32_t max_tokens_per_rank; /* every rank brings the same number of tokens to a step, at most this many */
+  uint32_t wait_ms;             /* limit of every device-side wait on a peer; 0 = 2000 */
+  uint32_t reserved;
+} mer_ep_cfg;
+/* Allocates this rank's exchange buffer (tokens, routing, per-pair expert outputs, arrival flags). */
+int mer_ep_init(mer_backend *b, const mer_ep_cfg *cfg);
+size_t mer_ep_exchange_bytes(mer_backend *b);
+/* One process per GPU: export the exchange buffer as a 64-byte CUDA IPC handle; after the host has
+ * exchanged the handles of all ranks (rank order), attach maps the peers' buffers. */
+int mer_ep_export_handle(mer_backend *b, void *handle_out);
+int mer_ep_attach_handles(mer_backend *b, const void *handles, size_t n_handles);
+/* One process driving several GPUs with peer access enabled: pass the buffers directly. */
+void *mer_ep_exchange_buffer(mer_backend *b);
+int mer_ep_attach_pointers(mer_backend *b, void *const *exchange_buffers, size_t n);
+/* LinearGate::route for n_tokens device rows: ids [n x slots] global ids, weights [n x slots]
+ * (slots = top_k + shared); asynchronous on `stream`. */
+int mer_router_route_device(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens,
+                            uint32_t *d_ids, float *d_weights, void *stream);
+/* Collectives run by the host (all-gather of x / ids / weights in rank order, reduce-scatter of the
+ * partial outputs): runs the experts of this rank over the tokens of all ranks and writes
+ * d_out_partial [n_tokens_all x d_model] = sum over the local pairs of weight * expert(x). */
+int mer_ep_local_experts_forward_device(mer_backend *b, uint32_t layer, const float *d_x_all,
+                                        const uint32_t *d_ids_all, const float *d_weights_all,
+                                        size_t n_tokens_all, size_t tokens_per_rank,
+                                        float *d_out_partial, void *stream);
+/* The whole layer for this rank's n_tokens rows with the exchange done by the kernels through peer
+ * memory: route, publish, pull the tokens that hit a local expert, run the local experts, pull every
+ * pair's output from its owner and sum in slot order (same order as a single GPU).  Every rank must
+ * make the same sequence of calls with the same n_tokens. */
+int mer_ep_layer_forward_device(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens,
+                                float *d_out, void *stream);
+/* Synchronises `stream` and turns the device status word into a typed error (for _device calls). */
+int mer_stream_check(mer_backend *b, uint32_t layer, void *stream);
+
 /* ---- introspection ---- */
 int mer_last_error(mer_backend *b, mer_error_info *out);
 int mer_snapshot(mer_backend *b, mer_counters *out);

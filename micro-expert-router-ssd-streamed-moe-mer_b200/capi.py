@@ -40,6 +40,11 @@ class MerCounters(C.Structure):
         return {n: int(getattr(self, n)) for n, _ in self._fields_}
 
 
+class MerEpCfg(C.Structure):
+    _fields_ = [("rank", C.c_uint32), ("world", C.c_uint32), ("experts_per_layer", C.c_uint32),
+                ("max_tokens_per_rank", C.c_uint32), ("wait_ms", C.c_uint32), ("reserved", C.c_uint32)]
+
+
 class MerStageTimings(C.Structure):
     _fields_ = [("samples", C.c_uint64), ("router_gate_ms", C.c_double), ("expert_gate_up_kernel_ms", C.c_double),
                 ("expert_down_kernel_ms", C.c_double), ("moe_weighted_combination_ms", C.c_double),
@@ -80,6 +85,16 @@ ABI_SYMBOLS = {
     "mer_last_error": (C.c_int, [_vp, C.POINTER(MerErrorInfo)]),
     "mer_snapshot": (C.c_int, [_vp, C.POINTER(MerCounters)]),
     "mer_set_kernel_path": (C.c_int, [_vp, _i32]),
+    "mer_ep_init": (C.c_int, [_vp, C.POINTER(MerEpCfg)]),
+    "mer_ep_exchange_bytes": (_sz, [_vp]),
+    "mer_ep_export_handle": (C.c_int, [_vp, _vp]),
+    "mer_ep_attach_handles": (C.c_int, [_vp, _vp, _sz]),
+    "mer_ep_exchange_buffer": (_vp, [_vp]),
+    "mer_ep_attach_pointers": (C.c_int, [_vp, C.POINTER(_vp), _sz]),
+    "mer_router_route_device": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _vp, _vp]),
+    "mer_ep_local_experts_forward_device": (C.c_int, [_vp, _u32, _vp, _vp, _vp, _sz, _sz, _vp, _vp]),
+    "mer_ep_layer_forward_device": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _vp]),
+    "mer_stream_check": (C.c_int, [_vp, _u32, _vp]),
 }
 
 _lib = None

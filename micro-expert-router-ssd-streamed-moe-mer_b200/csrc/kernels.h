@@ -57,7 +57,32 @@ struct MoeDispatch {
   int packed;               // 1: slots hold the tile-major fragment layout (layout.cuh), 0: the flat block stream
 };
 
+// Expert-parallel view of one rank: where every rank's exchange buffer is mapped and how experts
+// and tokens are partitioned.  Offsets are the same on every rank.
+#define MER_EP_MAX_WORLD 16
+struct EpDev {
+  uint8_t *peer[MER_EP_MAX_WORLD];  // exchange buffer of rank j as mapped here (own buffer at [rank])
+  uint32_t rank, world;
+  uint32_t experts_per_rank;  // rank j owns the local expert indices [j*epr, (j+1)*epr) of every layer
+  uint32_t top_k;             // slots >= top_k are the shared expert (runs on the token's own rank)
+  uint32_t id_base;           // layer * experts_per_layer of the layer in flight
+  uint32_t tokens_per_rank;   // tokens every rank contributes to the step in flight
+  size_t off_flags, off_x, off_ids, off_y;  // byte offsets inside an exchange buffer
+  uint64_t wait_ns;           // limit of every wait on a peer
+};
+
+// kernels_ep.cu
+cudaError_t launch_ep_filter(const EpDev &ep, const uint32_t *ids_all, const float *w_all, uint32_t n_pairs, uint32_t slots,
+                             uint32_t *pair_expert, float *pair_weight, cudaStream_t s, int *launches);
+cudaError_t launch_ep_signal(const EpDev &ep, uint32_t epoch, cudaStream_t s, int *launches);
+cudaError_t launch_ep_gather(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, float *x_all, uint32_t *pair_expert,
+                             float *pair_weight, uint32_t *status, cudaStream_t s, int *launches);
+cudaError_t launch_ep_combine(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, const uint32_t *ids, const float *w,
+                              float *out, uint32_t *status, cudaStream_t s, int *launches);
+
 // kernels_generic.cu
+// Groups pairs by expert for a whole layer whose routing is already in d.pair_expert (+ pass table).
+cudaError_t launch_groups_layer(const RouterDev &r, const MoeDispatch &d, cudaStream_t s, int *launches);
 cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max_tokens, cudaStream_t s, int *launches);
 cudaError_t launch_groups_from_pairs(const MoeDispatch &d, cudaStream_t s, int *launches);
 cudaError_t launch_ffn_generic(const MoeDispatch &d, cudaStream_t s, int *launches, cudaEvent_t ev_mid);

@@ -1,0 +1,170 @@
+// Expert-parallel kernels: one process per GPU, experts of every layer partitioned contiguously
+// over the ranks.  Two ways to move tokens:
+//   (1) the host runs the collectives (all-gather of x and routing, reduce-scatter of partial
+//       outputs) and this file only filters the gathered routing down to the local experts;
+//   (2) the ranks exchange through peer memory: every rank publishes its tokens, routing and
+//       per-pair expert outputs in an exchange buffer the other ranks have mapped; a rank pulls
+//       the rows it needs with plain peer loads (no TMA, no multicast) after a flag barrier.
+// Every wait on a peer is bounded by wall-clock time; on expiry the kernel latches
+// MER_DEVSTAT_TIMEOUT and carries on without the peer's data (the host then fails the call).
+#include "../../include/mer_b200.h"
+#include "kernels.h"
+
+namespace {
+
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ uint32_t ld_flag(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Waits until flag >= epoch (epochs grow monotonically; compared as signed distance so that a
+// wrap after 2^31 steps is harmless).  Returns false when the time limit ran out.
+__device__ bool wait_flag(const uint32_t *flag, uint32_t epoch, uint64_t limit_ns) {
+  if ((int32_t)(ld_flag(flag) - epoch) >= 0) return true;
+  const uint64_t t0 = global_ns();
+  for (;;) {
+    for (int i = 0; i < 64; i++) {
+      if ((int32_t)(ld_flag(flag) - epoch) >= 0) return true;
+      __nanosleep(200);
+    }
+    if (global_ns() - t0 > limit_ns) return false;
+  }
+}
+
+__device__ __forceinline__ bool pair_is_local(const EpDev &ep, uint32_t e, uint32_t slot, uint32_t src_rank) {
+  if (e == MER_NONE) return false;
+  if (slot >= ep.top_k) return src_rank == ep.rank;  // shared expert: replicated, runs where the token lives
+  return (e - ep.id_base) / ep.experts_per_rank == ep.rank;
+}
+
+// (1) Routing gathered by the host: keep the pairs whose expert lives here, blank the rest.
+__global__ void k_ep_filter(EpDev ep, const uint32_t *__restrict__ ids_all, const float *__restrict__ w_all, uint32_t n_pairs,
+                            uint32_t slots, uint32_t *__restrict__ pair_expert, float *__restrict__ pair_weight) {
+  const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= n_pairs) return;
+  const uint32_t token = p / slots, slot = p % slots;
+  const uint32_t e = ids_all[p];
+  const bool local = pair_is_local(ep, e, slot, token / ep.tokens_per_rank);
+  pair_expert[p] = local ? e : MER_NONE;
+  pair_weight[p] = local ? w_all[p] : 0.0f;
+}
+
+// (2a) Tells every peer that this rank's exchange buffer holds the data of `epoch`.
+// Runs after the kernels that wrote the data (stream order), so the data is in this GPU's memory.
+__global__ void k_ep_signal(EpDev ep, uint32_t epoch) {
+  const uint32_t j = threadIdx.x;
+  if (j >= ep.world) return;
+  __threadfence_system();
+  uint32_t *flag = reinterpret_cast<uint32_t *>(ep.peer[j] + ep.off_flags) + ep.rank;
+  asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+}
+
+// (2b) Pulls the tokens of every rank that hit a local expert: routing (filtered) for all tokens,
+// x rows only for tokens with at least one local pair.  One CTA per (source rank, token).
+__global__ void __launch_bounds__(256) k_ep_gather(EpDev ep, uint32_t epoch, uint32_t D, uint32_t slots, float *__restrict__ x_all,
+                                                   uint32_t *__restrict__ pair_expert, float *__restrict__ pair_weight,
+                                                   uint32_t *status) {
+  const uint32_t src = blockIdx.y, t = blockIdx.x;
+  __shared__ int s_ok, s_any;
+  if (threadIdx.x == 0) {
+    const uint32_t *flags = reinterpret_cast<const uint32_t *>(ep.peer[ep.rank] + ep.off_flags);
+    s_ok = wait_flag(flags + src, epoch, ep.wait_ns);
+    if (!s_ok) atomicOr(status, MER_DEVSTAT_TIMEOUT);
+    __threadfence_system();  // the peer's data is read only after its flag was seen
+    s_any = 0;
+  }
+  __syncthreads();
+  const uint32_t tg = src * ep.tokens_per_rank + t;  // global token index
+  if (!s_ok) {
+    if (threadIdx.x < slots) pair_expert[tg * slots + threadIdx.x] = MER_NONE, pair_weight[tg * slots + threadIdx.x] = 0.0f;
+    return;
+  }
+  const uint8_t *base = ep.peer[src];
+  if (threadIdx.x < slots) {
+    const uint32_t e = __ldcg(reinterpret_cast<const uint32_t *>(base + ep.off_ids) + t * slots + threadIdx.x);
+    const bool local = pair_is_local(ep, e, threadIdx.x, src);
+    pair_expert[tg * slots + threadIdx.x] = local ? e : MER_NONE;
+    pair_weight[tg * slots + threadIdx.x] = local ? 1.0f : 0.0f;
+    if (local) s_any = 1;
+  }
+  __syncthreads();
+  if (!s_any) return;
+  const float4 *srcx = reinterpret_cast<const float4 *>(base + ep.off_x) + (size_t)t * (D / 4);
+  float4 *dst = reinterpret_cast<float4 *>(x_all) + (size_t)tg * (D / 4);
+  for (uint32_t i = threadIdx.x; i < D / 4; i += blockDim.x) dst[i] = __ldcg(srcx + i);
+}
+
+// (2c) out[t] = sum over slots, in slot order, of weight * y, where y of a pair is read from the
+// exchange buffer of the rank that owns the pair's expert (same order and rounding as k_combine).
+__global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, uint32_t epoch, uint32_t D, uint32_t slots,
+                                                    const uint32_t *__restrict__ ids, const float *__restrict__ w,
+                                                    float *__restrict__ out, uint32_t *status) {
+  const uint32_t t = blockIdx.y;
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  __shared__ int s_ok;
+  if (threadIdx.x < 32) {
+    // lanes share the ranks to wait for
+    const uint32_t *flags = reinterpret_cast<const uint32_t *>(ep.peer[ep.rank] + ep.off_flags);
+    int ok = 1;
+    for (uint32_t j = threadIdx.x; j < ep.world; j += 32) ok &= (int)wait_flag(flags + j, epoch, ep.wait_ns);
+    ok = __all_sync(0xffffffffu, ok);
+    __threadfence_system();
+    if (threadIdx.x == 0) {
+      s_ok = ok;
+      if (!ok) atomicOr(status, MER_DEVSTAT_TIMEOUT);
+    }
+  }
+  __syncthreads();
+  if (i >= D) return;
+  float acc = 0.0f;
+  if (s_ok) {
+    const uint32_t tg = ep.rank * ep.tokens_per_rank + t;
+    for (uint32_t s = 0; s < slots; s++) {
+      const uint32_t e = ids[t * slots + s];
+      const float wt = w[t * slots + s];
+      if (e == MER_NONE || wt == 0.0f) continue;
+      const uint32_t owner = s >= ep.top_k ? ep.rank : (e - ep.id_base) / ep.experts_per_rank;
+      const float *y = reinterpret_cast<const float *>(ep.peer[owner] + ep.off_y) + ((size_t)tg * slots + s) * D;
+      acc = __fadd_rn(acc, __fmul_rn(wt, __ldcg(y + i)));
+    }
+  }
+  out[(size_t)t * D + i] = acc;
+}
+
+}  // namespace
+
+cudaError_t launch_ep_filter(const EpDev &ep, const uint32_t *ids_all, const float *w_all, uint32_t n_pairs, uint32_t slots,
+                             uint32_t *pair_expert, float *pair_weight, cudaStream_t s, int *launches) {
+  k_ep_filter<<<(n_pairs + 255) / 256, 256, 0, s>>>(ep, ids_all, w_all, n_pairs, slots, pair_expert, pair_weight);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_signal(const EpDev &ep, uint32_t epoch, cudaStream_t s, int *launches) {
+  k_ep_signal<<<1, 64, 0, s>>>(ep, epoch);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_gather(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, float *x_all, uint32_t *pair_expert,
+                             float *pair_weight, uint32_t *status, cudaStream_t s, int *launches) {
+  dim3 grid(ep.tokens_per_rank, ep.world);
+  k_ep_gather<<<grid, 256, 0, s>>>(ep, epoch, D, slots, x_all, pair_expert, pair_weight, status);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_combine(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, const uint32_t *ids, const float *w,
+                              float *out, uint32_t *status, cudaStream_t s, int *launches) {
+  dim3 grid((D + 255) / 256, ep.tokens_per_rank);
+  k_ep_combine<<<grid, 256, 0, s>>>(ep, epoch, D, slots, ids, w, out, status);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
+}

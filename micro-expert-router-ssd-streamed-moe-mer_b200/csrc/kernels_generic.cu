@@ -485,6 +485,12 @@ __global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispa
   build_groups_layer(r, d, reinterpret_cast<uint32_t *>(smem_raw));
 }
 
+// Routing of a whole layer supplied by the caller (pair_expert already filled): group by expert.
+__global__ void __launch_bounds__(ROUTER_THREADS) k_groups_layer(RouterDev r, MoeDispatch d) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  build_groups_layer(r, d, reinterpret_cast<uint32_t *>(smem_raw));
+}
+
 // Routing supplied by the caller: mode 0 = every pair is its own group, mode 1 = one group.
 __global__ void k_groups_from_pairs(MoeDispatch d, int single_group) {
   const uint32_t P = d.n_tokens * d.slots;
@@ -719,6 +725,19 @@ cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max
   }
   dim3 grid((E + ROUTER_ROWS - 1) / ROUTER_ROWS, (d.n_tokens + ROUTER_TT - 1) / ROUTER_TT);
   k_router<<<grid, ROUTER_THREADS, smem, s>>>(r, d, max_tokens);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_groups_layer(const RouterDev &r, const MoeDispatch &d, cudaStream_t s, int *launches) {
+  const uint32_t G = d.n_groups, P = d.n_tokens * d.slots;
+  size_t smem = (size_t)(G + 1 + (G <= STABLE_G ? ROUTER_ROWS * G : G) + (P <= SMALL_P ? P : 0)) * 4;
+  smem = (smem + 15) & ~(size_t)15;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k_groups_layer, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  k_groups_layer<<<1, ROUTER_THREADS, smem, s>>>(r, d);
   if (launches) (*launches)++;
   return cudaGetLastError();
 }

@@ -80,6 +80,15 @@ struct mer_backend {
 
   std::unordered_map<uint32_t, RouterEntry> routers;
   int kernel_path = 0;
+
+  // expert parallel (mer_ep_*): exchange buffer mapped by the peers, peers' buffers mapped here
+  bool ep_on = false, ep_attached = false;
+  EpDev ep{};
+  mer_ep_cfg ep_cfg{};
+  uint8_t *ep_buf = nullptr;
+  size_t ep_bytes = 0, ep_off_w = 0;
+  uint32_t ep_epoch = 0;
+  void *ep_opened[MER_EP_MAX_WORLD] = {};  // mappings opened from IPC handles (closed at destroy)
   // captured launch sequences of mer_moe_layer_forward_device, replayed with one cudaGraphLaunch
   struct GraphEntry {
     uint32_t layer;
@@ -273,6 +282,9 @@ void free_all(mer_backend *b) {
   b->graphs.clear();
   for (auto &e : b->timing_events) cudaEventDestroy(e);
   b->timing_events.clear();
+  for (auto &p : b->ep_opened)
+    if (p) cudaIpcCloseMemHandle(p), p = nullptr;
+  F(b->ep_buf);
   if (b->compute) cudaStreamDestroy(b->compute);
   if (b->copy) cudaStreamDestroy(b->copy);
 }
@@ -960,6 +972,242 @@ MER_EXPORT int mer_moe_layer_forward_device(mer_backend *b, uint32_t layer, cons
   b->ctr.gpu_dispatch_attempts += P;
   b->ctr.gpu_dispatch_successes += P;
   return MER_OK;
+}
+
+// ------------------------------------------------------------------------ expert parallel
+
+namespace {
+size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+// Dispatch over the tokens of all ranks whose routing (filtered to the local experts) is already in the workspace.
+int ep_run_local_experts(mer_backend *b, uint32_t layer, const RouterDev &r, MoeDispatch &d, cudaStream_t s, int *launches) {
+  const uint32_t expert = MER_NONE;
+  const uint32_t shared = r.shared_expert_id != MER_NONE ? 1u : 0u;
+  d.slots = r.top_k + shared;
+  d.n_groups = r.num_experts + shared;
+  d.max_group_tokens = d.n_tokens;
+  d.active_groups_hint = std::min(b->ep.experts_per_rank + shared, d.n_tokens * d.slots);
+  if (use_stream_path(b, d)) stream_bind(d, b->d_stream_scratch, b->sm_count);
+  CU(MER_ERR_SUBMISSION, "group kernel", launch_groups_layer(r, d, s, launches));
+  CU(MER_ERR_SUBMISSION, "expert FFN kernels", run_ffn(b, d, s, launches));
+  return MER_OK;
+}
+}  // namespace
+
+MER_EXPORT int mer_ep_init(mer_backend *b, const mer_ep_cfg *cfg) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t layer = 0, expert = MER_NONE;
+  if (!cfg) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null cfg");
+  if (cfg->world == 0 || cfg->world > MER_EP_MAX_WORLD || cfg->rank >= cfg->world || cfg->experts_per_layer == 0 ||
+      cfg->max_tokens_per_rank == 0)
+    return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "rank %u of %u, %u experts per layer, %u tokens per rank", cfg->rank,
+                cfg->world, cfg->experts_per_layer, cfg->max_tokens_per_rank);
+  if ((uint64_t)cfg->max_tokens_per_rank * cfg->world > b->cfg.max_tokens)
+    return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert,
+                "the backend's max_tokens (%u) must cover the tokens of all ranks (%u x %u)", b->cfg.max_tokens,
+                cfg->max_tokens_per_rank, cfg->world);
+  std::lock_guard<std::mutex> lock(b->mu);
+  if (b->ep_on) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "expert parallelism is already initialised");
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  const size_t D = b->cfg.d_model, S = b->cfg.max_top_k, Bm = cfg->max_tokens_per_rank, T = Bm * cfg->world;
+  EpDev &ep = b->ep;
+  ep = EpDev{};
+  ep.rank = cfg->rank, ep.world = cfg->world;
+  ep.experts_per_rank = (cfg->experts_per_layer + cfg->world - 1) / cfg->world;
+  ep.wait_ns = (uint64_t)(cfg->wait_ms ? cfg->wait_ms : 2000u) * 1000000ull;
+  ep.off_flags = 0;
+  ep.off_x = 256;
+  ep.off_ids = ep.off_x + round256(Bm * D * 4);
+  b->ep_off_w = ep.off_ids + round256(Bm * S * 4);
+  ep.off_y = b->ep_off_w + round256(Bm * S * 4);
+  b->ep_bytes = ep.off_y + round256(T * S * D * 4);
+  CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(exchange buffer)", cudaMalloc((void **)&b->ep_buf, b->ep_bytes));
+  CU(MER_ERR_SUBMISSION, "cudaMemset(exchange buffer)", cudaMemset(b->ep_buf, 0, 256));
+  ep.peer[ep.rank] = b->ep_buf;
+  b->ep_cfg = *cfg;
+  b->ep_on = true;
+  b->ep_attached = cfg->world == 1;
+  b->ep_epoch = 0;
+  return MER_OK;
+}
+
+MER_EXPORT size_t mer_ep_exchange_bytes(mer_backend *b) { return b && b->ep_on ? b->ep_bytes : 0; }
+
+MER_EXPORT int mer_ep_export_handle(mer_backend *b, void *handle_out) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t layer = 0, expert = MER_NONE;
+  if (!handle_out) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null handle buffer");
+  std::lock_guard<std::mutex> lock(b->mu);
+  if (!b->ep_on) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "mer_ep_init has not been called");
+  static_assert(sizeof(cudaIpcMemHandle_t) == MER_EP_HANDLE_BYTES, "handle size");
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  cudaIpcMemHandle_t h;
+  CU(MER_ERR_SUBMISSION, "cudaIpcGetMemHandle", cudaIpcGetMemHandle(&h, b->ep_buf));
+  memcpy(handle_out, &h, sizeof h);
+  return MER_OK;
+}
+
+MER_EXPORT int mer_ep_attach_handles(mer_backend *b, const void *handles, size_t n_handles) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t layer = 0, expert = MER_NONE;
+  std::lock_guard<std::mutex> lock(b->mu);
+  if (!b->ep_on || !handles || n_handles != b->ep.world)
+    return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "expected the %u handles of an initialised group", b->ep_on ? b->ep.world : 0);
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  for (uint32_t j = 0; j < b->ep.world; j++) {
+    if (j == b->ep.rank || b->ep_opened[j]) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, (const uint8_t *)handles + (size_t)j * MER_EP_HANDLE_BYTES, sizeof h);
+    void *p = nullptr;
+    CU(MER_ERR_SUBMISSION, "cudaIpcOpenMemHandle", cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    b->ep_opened[j] = p;
+    b->ep.peer[j] = (uint8_t *)p;
+  }
+  b->ep_attached = true;
+  return MER_OK;
+}
+
+MER_EXPORT int mer_ep_attach_pointers(mer_backend *b, void *const *exchange_buffers, size_t n) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t layer = 0, expert = MER_NONE;
+  std::lock_guard<std::mutex> lock(b->mu);
+  if (!b->ep_on || !exchange_buffers || n != b->ep.world)
+    return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "expected the %u buffers of an initialised group", b->ep_on ? b->ep.world : 0);
+  for (uint32_t j = 0; j < b->ep.world; j++) {
+    if (j == b->ep.rank) continue;
+    if (!exchange_buffers[j]) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null exchange buffer for rank %u", j);
+    b->ep.peer[j] = (uint8_t *)exchange_buffers[j];
+  }
+  b->ep_attached = true;
+  return MER_OK;
+}
+
+MER_EXPORT void *mer_ep_exchange_buffer(mer_backend *b) { return b && b->ep_on ? b->ep_buf : nullptr; }
+
+MER_EXPORT int mer_router_route_device(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, uint32_t *d_ids,
+                                       float *d_weights, void *stream) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t expert = MER_NONE;
+  if (!d_x || !d_ids || !d_weights) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer");
+  std::lock_guard<std::mutex> lock(b->mu);
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int launches = 0;
+  MoeDispatch d;
+  int rc = enqueue_layer(b, layer, d_x, n_tokens, b->d_out, false, s, &launches, &d);
+  if (rc) return rc;
+  const size_t P = n_tokens * d.slots;
+  CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(ids)", cudaMemcpyAsync(d_ids, b->d_pair_expert, P * 4, cudaMemcpyDeviceToDevice, s));
+  CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(w)", cudaMemcpyAsync(d_weights, b->d_pair_weight, P * 4, cudaMemcpyDeviceToDevice, s));
+  b->ctr.kernel_launches += (uint64_t)launches;
+  return MER_OK;
+}
+
+MER_EXPORT int mer_ep_local_experts_forward_device(mer_backend *b, uint32_t layer, const float *d_x_all, const uint32_t *d_ids_all,
+                                                   const float *d_weights_all, size_t n_tokens_all, size_t tokens_per_rank,
+                                                   float *d_out_partial, void *stream) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t expert = MER_NONE;
+  if (!d_x_all || !d_ids_all || !d_weights_all || !d_out_partial) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer");
+  std::lock_guard<std::mutex> lock(b->mu);
+  if (!b->ep_on) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "mer_ep_init has not been called");
+  auto it = b->routers.find(layer);
+  if (it == b->routers.end()) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "no router installed for layer %u", layer);
+  const RouterDev &r = it->second.dev;
+  if (n_tokens_all == 0 || n_tokens_all > b->cfg.max_tokens || tokens_per_rank == 0 || n_tokens_all != tokens_per_rank * b->ep.world)
+    return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "%zu tokens in all, %zu per rank, %u ranks, at most %u", n_tokens_all,
+                tokens_per_rank, b->ep.world, b->cfg.max_tokens);
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int launches = 0;
+  EpDev ep = b->ep;
+  ep.top_k = r.top_k, ep.id_base = r.id_base, ep.tokens_per_rank = (uint32_t)tokens_per_rank;
+  MoeDispatch d = base_dispatch(b);
+  d.n_tokens = (uint32_t)n_tokens_all;
+  d.x = d_x_all;
+  d.out = d_out_partial;
+  const uint32_t slots = r.top_k + (r.shared_expert_id != MER_NONE ? 1u : 0u);
+  CU(MER_ERR_SUBMISSION, "cudaMemsetAsync(status)", cudaMemsetAsync(b->d_status, 0, 4, s));
+  CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, s));
+  CU(MER_ERR_SUBMISSION, "filter kernel",
+     launch_ep_filter(ep, d_ids_all, d_weights_all, d.n_tokens * slots, slots, d.pair_expert, d.pair_weight, s, &launches));
+  int rc = ep_run_local_experts(b, layer, r, d, s, &launches);
+  if (rc) return rc;
+  CU(MER_ERR_SUBMISSION, "combine kernel", launch_combine(d, s, &launches));
+  b->ctr.kernel_launches += (uint64_t)launches;
+  return MER_OK;
+}
+
+MER_EXPORT int mer_ep_layer_forward_device(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out,
+                                           void *stream) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t expert = MER_NONE;
+  if (!d_x || !d_out) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer");
+  std::lock_guard<std::mutex> lock(b->mu);
+  if (!b->ep_on || !b->ep_attached)
+    return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "the expert-parallel group is not initialised and attached");
+  auto it = b->routers.find(layer);
+  if (it == b->routers.end()) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "no router installed for layer %u", layer);
+  const RouterDev &r = it->second.dev;
+  if (n_tokens == 0 || n_tokens > b->ep_cfg.max_tokens_per_rank)
+    return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "n_tokens %zu outside 1..=%u per rank", n_tokens, b->ep_cfg.max_tokens_per_rank);
+  if ((b->cfg.d_model & 3) != 0) return fail(b, MER_ERR_INELIGIBLE, layer, expert, "d_model must be a multiple of 4");
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int launches = 0;
+  const size_t D = b->cfg.d_model;
+  const uint32_t shared = r.shared_expert_id != MER_NONE ? 1u : 0u, slots = r.top_k + shared;
+  EpDev ep = b->ep;
+  ep.top_k = r.top_k, ep.id_base = r.id_base, ep.tokens_per_rank = (uint32_t)n_tokens;
+  float *x_pub = reinterpret_cast<float *>(b->ep_buf + ep.off_x);
+  uint32_t *ids_pub = reinterpret_cast<uint32_t *>(b->ep_buf + ep.off_ids);
+  float *w_own = reinterpret_cast<float *>(b->ep_buf + b->ep_off_w);
+  float *y_pub = reinterpret_cast<float *>(b->ep_buf + ep.off_y);
+  const uint32_t e1 = ++b->ep_epoch, e2 = ++b->ep_epoch;
+
+  CU(MER_ERR_SUBMISSION, "cudaMemsetAsync(status)", cudaMemsetAsync(b->d_status, 0, 4, s));
+  CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, s));
+  // publish this rank's tokens and their routing
+  CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(x)", cudaMemcpyAsync(x_pub, d_x, n_tokens * D * 4, cudaMemcpyDeviceToDevice, s));
+  MoeDispatch dr = base_dispatch(b);
+  dr.n_tokens = (uint32_t)n_tokens;
+  dr.slots = slots;
+  dr.n_groups = r.num_experts + shared;
+  dr.x = x_pub;
+  dr.pair_expert = ids_pub;
+  dr.pair_weight = w_own;
+  CU(MER_ERR_SUBMISSION, "router kernel", launch_router(r, dr, b->cfg.max_tokens, s, &launches));
+  CU(MER_ERR_SUBMISSION, "signal kernel", launch_ep_signal(ep, e1, s, &launches));
+  // pull the tokens that hit a local expert, run the local experts over them
+  MoeDispatch d = base_dispatch(b);
+  d.n_tokens = (uint32_t)(n_tokens * ep.world);
+  d.x = b->d_x;
+  d.y = y_pub;
+  d.out = d_out;
+  CU(MER_ERR_SUBMISSION, "gather kernel",
+     launch_ep_gather(ep, e1, (uint32_t)D, slots, b->d_x, d.pair_expert, d.pair_weight, b->d_status, s, &launches));
+  int rc = ep_run_local_experts(b, layer, r, d, s, &launches);
+  if (rc) return rc;
+  CU(MER_ERR_SUBMISSION, "partial-sum kernel", launch_reduce_parts(d, s, &launches));
+  CU(MER_ERR_SUBMISSION, "signal kernel", launch_ep_signal(ep, e2, s, &launches));
+  // weighted sum in slot order, every pair's output read from the rank that owns its expert
+  CU(MER_ERR_SUBMISSION, "combine kernel",
+     launch_ep_combine(ep, e2, (uint32_t)D, slots, ids_pub, w_own, d_out, b->d_status, s, &launches));
+  b->ctr.kernel_launches += (uint64_t)launches;
+  b->ctr.selected_routed_experts += n_tokens * slots;
+  return MER_OK;
+}
+
+MER_EXPORT int mer_stream_check(mer_backend *b, uint32_t layer, void *stream) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t expert = MER_NONE;
+  std::lock_guard<std::mutex> lock(b->mu);
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(status)",
+     cudaMemcpyAsync(b->h_u32 + b->max_pairs, b->d_status, 4, cudaMemcpyDeviceToHost, s));
+  CU(MER_ERR_READBACK_MAP, "cudaStreamSynchronize", cudaStreamSynchronize(s));
+  return check_device_status(b, b->h_u32[b->max_pairs], layer, expert);
 }
 
 MER_EXPORT int mer_dequant_projection_f32(mer_backend *b, uint32_t expert_id, int projection, float *out) {
