@@ -54,6 +54,7 @@ struct MoeDispatch {
   uint32_t tokens_per_pass;
   const float *y_parts;     // set by the streaming FFN: K-split partials [y_nparts][P x D] of the per-pair outputs,
   uint32_t y_nparts;        //   or null / 1 when `y` already holds them
+  uint32_t gemm_bn;         // > 0: the tcgen05 GEMM path runs this dispatch with passes of gemm_bn tokens
   int packed;               // 1: slots hold the tile-major fragment layout (layout.cuh), 0: the flat block stream
 };
 
@@ -103,3 +104,12 @@ cudaError_t launch_ffn_stream(MoeDispatch &d, void *scratch, int sm_count, cudaS
 // Points d.pass_* / d.amax into the scratch and picks tokens_per_pass for this dispatch (call before grouping).
 void stream_bind(MoeDispatch &d, void *scratch, int sm_count);
 cudaError_t launch_reduce_parts(const MoeDispatch &d, cudaStream_t s, int *launches);
+
+// kernels_gemm.cu: tcgen05 / TMEM grouped GEMM for groups of a dozen tokens and more.
+bool gemm_ffn_supported(int dtype, uint32_t D, uint32_t F);
+size_t gemm_ffn_scratch_bytes(uint32_t max_tokens, uint32_t max_pairs, uint32_t D, uint32_t F);
+// Tokens per pass (16..128) for this dispatch, or 0 when its groups are too small for the GEMM path.
+uint32_t gemm_pick_bn(const MoeDispatch &d, uint32_t min_mean_tokens);
+void gemm_bind(MoeDispatch &d, void *stream_scratch, int sm_count, uint32_t bn);
+cudaError_t launch_ffn_gemm(MoeDispatch &d, void *gemm_scratch, size_t gemm_scratch_bytes, uint32_t max_tokens, int sm_count,
+                            cudaStream_t s, int *launches, cudaEvent_t ev_mid);

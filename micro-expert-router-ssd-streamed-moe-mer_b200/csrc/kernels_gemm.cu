@@ -1,0 +1,549 @@
+// Grouped expert FFN for token groups of a dozen tokens and more (prefill, expert-parallel decode):
+// tcgen05 tensor-core GEMM per (expert, 128 weight rows, up to 128 tokens) with TMEM accumulators.
+//
+//   D[128 weight rows x N tokens] += A[128 x 64] * B[N x 64]^T      per 64-column chunk of K
+//
+//   * A is produced on the fly: the packed Q4_0 / Q8_0 tile chunks of layout.cuh are streamed
+//     global -> shared by bulk async copies (every weight byte crosses HBM once per token tile) and
+//     eight warps dequantise them into two f16 operand tiles, hi = f16(d*q) and lo = d*q - hi (exact:
+//     an 11-bit scale times an 8-bit integer has at most 19 significant bits), written in the
+//     K-major no-swizzle core-matrix layout the MMA reads.
+//   * B is the activation tile as f16 hi + lo parts (22 significant bits after an exact power-of-two
+//     per-row scaling), laid out in the same core-matrix order by k_gemm_act_image and fetched with
+//     one bulk copy per chunk.
+//   * Three MMAs per 16 columns of K (hi*hi, hi*lo, lo*hi; lo*lo is below fp32 resolution) accumulate
+//     in fp32 in TMEM, so the result matches the fp32 reference to ~1e-6 instead of f16's 1e-3.
+//   * Warp roles: 0 = copy producer, 1 = MMA issuer (one elected lane) and TMEM owner, 2..5 = epilogue
+//     (tcgen05.ld, un-scaling, SiLU(gate)*up or plain store), 6..13 = dequantisers.  Two accumulator
+//     buffers let the epilogue of one item overlap the MMAs of the next.
+// Every wait is bounded; on expiry the CTA latches MER_DEVSTAT_TIMEOUT, stops issuing work, waits
+// (bounded) for its copies and MMAs in flight, frees its TMEM and returns.
+#include <cuda_fp16.h>
+
+#include "../../include/mer_b200.h"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace {
+
+constexpr int G_WARPS = 14, G_THREADS = G_WARPS * 32;
+constexpr int W_PRODUCER = 0, W_MMA = 1, W_EPI0 = 2, W_DQ0 = 6;
+constexpr int EPI_WARPS = 4, DQ_WARPS = 8;
+constexpr uint32_t A_LBO = 2080;         // bytes between K core matrices of A: 16 row groups x 128 B + 32 B skew (bank spread)
+constexpr uint32_t A_TERM = 8 * A_LBO;   // one operand tile: 8 core-matrix columns = 64 values of K
+constexpr uint32_t G_HEADER = 1024;
+constexpr uint32_t TMEM_COLS = 256;      // two accumulator buffers of up to 128 columns
+constexpr uint32_t MAX_RING = 4;
+constexpr float POW2_SCALE_TARGET = 9;   // activations are scaled so that the row maximum lies in [256, 512)
+
+struct GemmParams {
+  MoeDispatch d;
+  int phase;               // 0 = gate/up (+SiLU*mul), 1 = down
+  const uint8_t *act_img;  // [pass][K / 64] images of {hi, lo} activation tiles
+  const float *unscale;    // [pass][bn] 1 / scale of each token row
+  uint32_t rows;           // F (gate/up) or D (down)
+  uint32_t kb_total;       // 32-value blocks per weight row
+  uint32_t bn;             // token columns per pass (16, 32, 64 or 128)
+  uint32_t b_lbo;          // bytes between K core matrices of B: bn * 16 + 32
+  uint32_t n_raw, n_a, n_b;  // ring depths
+  float *out;              // phase 0: h [P x F]; phase 1: y [P x D]
+};
+
+// ------------------------------------------------------------------------------ tcgen05 PTX
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// K-major, no swizzle: 8-row x 16-byte core matrices; LBO = step between core matrices along K,
+// SBO = step between 8-row groups.  Bits: start >> 4 [0,14), LBO >> 4 [16,30), SBO >> 4 [32,46), version 1 [46,48).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
+}
+// f16 x f16 -> f32, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t instr_desc(uint32_t n) { return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      "tcgen05.wait::ld.sync.aligned;\n"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+        "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) {
+  asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+
+// Two integers held as the f16 values 1024 + b (b in the low mantissa bits) -> hi = f16(d * (b - zp)),
+// lo = d * (b - zp) - hi.  Every step is exact except the rounding that defines hi.
+__device__ __forceinline__ void dq2(uint32_t biased, __half2 zp1024, __half2 d2, uint32_t &hi, uint32_t &lo) {
+  const __half2 q = __hsub2(bits_h2(biased), zp1024);
+  const __half2 h = __hmul2(d2, q);
+  hi = h2_bits(h);
+  lo = h2_bits(__hfma2(d2, q, __hneg2(h)));
+}
+
+struct Ring {
+  uint32_t stage = 0, round = 0, n;
+  __device__ explicit Ring(uint32_t n_) : n(n_) {}
+  __device__ void advance() {
+    if (++stage == n) stage = 0, round++;
+  }
+};
+
+template <int DT>
+__global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr uint32_t BB = DT == MER_DTYPE_Q4_0 ? MER_Q4_BLOCK_BYTES : MER_Q8_BLOCK_BYTES;
+  constexpr uint32_t TCB = 2 * 16 * BB;  // bytes of one packed tile's 64-column chunk (576 / 1088)
+  constexpr uint32_t RAW_BYTES = 8 * TCB;
+  const MoeDispatch &d = p.d;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const uint32_t m_tiles = p.rows / (p.phase == 0 ? 64u : 128u);  // 8 packed tiles each
+  const uint32_t n_chunks = p.kb_total / 2;
+  const uint32_t n_passes = *d.n_passes;
+  const uint64_t n_items = (uint64_t)n_passes * m_tiles;
+  const uint32_t item_beg = (uint32_t)(n_items * blockIdx.x / gridDim.x), item_end = (uint32_t)(n_items * (blockIdx.x + 1) / gridDim.x);
+  if (item_beg >= item_end) return;
+
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
+  uint64_t *raw_full = bars, *raw_empty = bars + 4, *a_full = bars + 8, *a_empty = bars + 12, *b_full = bars + 16,
+           *b_empty = bars + 20, *acc_full = bars + 24, *acc_empty = bars + 26, *drain = bars + 28;
+  uint32_t *s_tmem = reinterpret_cast<uint32_t *>(smem + 256);
+  volatile uint32_t *s_abort = reinterpret_cast<volatile uint32_t *>(smem + 260);
+  uint8_t *s_raw = smem + G_HEADER;
+  uint8_t *s_a = s_raw + p.n_raw * RAW_BYTES;
+  uint8_t *s_b = s_a + p.n_a * 2 * A_TERM;
+  const uint32_t b_term = 8 * p.b_lbo, b_stage = 2 * b_term;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < MAX_RING; s++) {
+      mbar_init(&raw_full[s], 1), mbar_init(&raw_empty[s], DQ_WARPS);
+      mbar_init(&a_full[s], DQ_WARPS), mbar_init(&a_empty[s], 1);
+      mbar_init(&b_full[s], 1), mbar_init(&b_empty[s], 1);
+    }
+    for (uint32_t s = 0; s < 2; s++) mbar_init(&acc_full[s], 1), mbar_init(&acc_empty[s], EPI_WARPS);
+    mbar_init(drain, 1);
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == W_MMA) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  const size_t proj_bytes = (size_t)d.D * d.F / 32 * BB;
+  const size_t tile_bytes = (size_t)p.kb_total * 16 * BB;
+  const size_t region = p.phase == 0 ? 0 : 2 * proj_bytes;
+  auto expert_base = [&](uint32_t pass) -> const uint8_t * {
+    const uint32_t eid = d.group_expert[d.pass_group[pass]];
+    return eid < d.max_experts ? d.expert_ptr[eid] : nullptr;
+  };
+  bool ok = true;
+
+  if (warp == W_PRODUCER) {
+    // ------------------------------------------------------------------------ copy producer
+    Ring raw(p.n_raw), rb(p.n_b);
+    for (uint32_t item = item_beg; item < item_end && ok; item++) {
+      const uint32_t pass = item / m_tiles, mt = item % m_tiles;
+      const uint8_t *base = expert_base(pass);
+      if (!base) continue;
+      const uint8_t *wsrc = base + region + (size_t)(mt * 8 + (lane & 7)) * tile_bytes;
+      const uint8_t *bsrc = p.act_img + (size_t)pass * n_chunks * b_stage;
+      for (uint32_t c = 0; c < n_chunks && ok; c++) {
+        if (raw.round > 0) ok = mbar_wait(&raw_empty[raw.stage], (raw.round - 1) & 1);
+        if (ok && rb.round > 0) ok = mbar_wait(&b_empty[rb.stage], (rb.round - 1) & 1);
+        if (*s_abort) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_expect_tx(&raw_full[raw.stage], RAW_BYTES);
+          mbar_expect_tx(&b_full[rb.stage], b_stage);
+        }
+        __syncwarp();
+        if (lane < 8) bulk_g2s(s_raw + raw.stage * RAW_BYTES + lane * TCB, wsrc + (size_t)c * TCB, TCB, &raw_full[raw.stage]);
+        if (lane == 8) bulk_g2s(s_b + (size_t)rb.stage * b_stage, bsrc + (size_t)c * b_stage, b_stage, &b_full[rb.stage]);
+        raw.advance(), rb.advance();
+      }
+    }
+    if (!ok) {
+      if (lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
+      // copies already in flight get a bounded chance to land before the CTA's shared memory is released
+      for (uint32_t s = 0; s < p.n_raw; s++) (void)mbar_wait(&raw_full[s], 0), (void)mbar_wait(&raw_full[s], 1);
+      for (uint32_t s = 0; s < p.n_b; s++) (void)mbar_wait(&b_full[s], 0), (void)mbar_wait(&b_full[s], 1);
+    }
+  } else if (warp == W_MMA) {
+    // -------------------------------------------------------------------------- MMA issuer
+    Ring ra(p.n_a), rb(p.n_b);
+    const uint32_t idesc = instr_desc(p.bn);
+    uint32_t used = 0;  // items issued so far: buffer = used & 1, its k-th use has k = used >> 1
+    for (uint32_t item = item_beg; item < item_end && ok; item++) {
+      const uint32_t pass = item / m_tiles;
+      if (!expert_base(pass)) continue;
+      const uint32_t buf = used & 1, use = used >> 1;
+      used++;
+      if (lane == 0) {
+        if (use > 0) ok = mbar_wait(&acc_empty[buf], (use - 1) & 1);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * 128;
+        for (uint32_t c = 0; c < n_chunks && ok; c++) {
+          ok = mbar_wait(&a_full[ra.stage], ra.round & 1) && mbar_wait(&b_full[rb.stage], rb.round & 1);
+          if (*s_abort) ok = false;
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_hi = smem_u32(s_a) + ra.stage * 2 * A_TERM, a_lo = a_hi + A_TERM;
+          const uint32_t b_hi = smem_u32(s_b) + rb.stage * b_stage, b_lo = b_hi + b_term;
+#pragma unroll
+          for (uint32_t j = 0; j < 4; j++) {  // 16 values of K per instruction = two core-matrix columns
+            const uint64_t dah = smem_desc(a_hi + j * 2 * A_LBO, A_LBO, 128), dal = smem_desc(a_lo + j * 2 * A_LBO, A_LBO, 128);
+            const uint64_t dbh = smem_desc(b_hi + j * 2 * p.b_lbo, p.b_lbo, 128), dbl = smem_desc(b_lo + j * 2 * p.b_lbo, p.b_lbo, 128);
+            tc_mma(d_tmem, dah, dbh, idesc, (c | j) != 0);
+            tc_mma(d_tmem, dah, dbl, idesc, 1);
+            tc_mma(d_tmem, dal, dbh, idesc, 1);
+          }
+          tc_commit(&a_empty[ra.stage]);
+          tc_commit(&b_empty[rb.stage]);
+          ra.advance(), rb.advance();
+        }
+        if (ok) tc_commit(&acc_full[buf]);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+    }
+    if (lane == 0) {
+      if (!ok) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
+      // nothing may still be writing TMEM when it is freed
+      tc_commit(drain);
+      (void)mbar_wait(drain, 0);
+    }
+    __syncwarp();
+  } else if (warp >= W_DQ0) {
+    // ------------------------------------------------------------------------ dequantisers
+    Ring raw(p.n_raw), ra(p.n_a);
+    const uint32_t T = warp - W_DQ0;  // packed tile of the item handled by this warp
+    const uint32_t g = lane >> 2, t = lane & 3;
+    const __half2 zp = DT == MER_DTYPE_Q4_0 ? __floats2half2_rn(1032.0f, 1032.0f) : __floats2half2_rn(1152.0f, 1152.0f);
+    for (uint32_t item = item_beg; item < item_end && ok; item++) {
+      const uint32_t pass = item / m_tiles;
+      if (!expert_base(pass)) continue;
+      for (uint32_t c = 0; c < n_chunks && ok; c++) {
+        ok = mbar_wait(&raw_full[raw.stage], raw.round & 1);
+        if (ok && ra.round > 0) ok = mbar_wait(&a_empty[ra.stage], (ra.round - 1) & 1);
+        if (*s_abort) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const uint32_t src = smem_u32(s_raw) + raw.stage * RAW_BYTES + T * TCB;
+        const uint32_t hi0 = smem_u32(s_a) + ra.stage * 2 * A_TERM + (2 * T) * 128 + g * 16;  // row T*16 + g; +128 = row + 8
+        if (DT == MER_DTYPE_Q8_0) {
+#pragma unroll
+          for (uint32_t b = 0; b < 2; b++) {
+            const uint4 w = lds128(src + b * 544 + lane * 16);
+            const uint32_t sc = lds32(src + b * 544 + 512 + g * 4);
+            const __half2 dl = __half2half2(__low2half(bits_h2(sc))), dh = __half2half2(__high2half(bits_h2(sc)));
+            const uint32_t dst = hi0 + (b * 4 + t) * A_LBO;
+            const uint32_t words[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
+            uint32_t hi[8], lo[8];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+              const __half2 dd = i < 2 ? dl : dh;
+              dq2(__byte_perm(words[i], 0x64646464u, 0x4140), zp, dd, hi[2 * i], lo[2 * i]);
+              dq2(__byte_perm(words[i], 0x64646464u, 0x4342), zp, dd, hi[2 * i + 1], lo[2 * i + 1]);
+            }
+            sts128(dst, hi[0], hi[1], hi[2], hi[3]);
+            sts128(dst + A_TERM, lo[0], lo[1], lo[2], lo[3]);
+            sts128(dst + 128, hi[4], hi[5], hi[6], hi[7]);
+            sts128(dst + 128 + A_TERM, lo[4], lo[5], lo[6], lo[7]);
+          }
+        } else {
+          // one block-pair record: words = (slot g, blk 0), (slot g+8, blk 0), (slot g, blk 1), (slot g+8, blk 1);
+          // byte i of a word holds values 4t+i (low nibble) and 16+4t+i (high nibble) of its block
+          const uint4 w = lds128(src + lane * 16);
+          const uint2 sc = lds64(src + 512 + g * 8);
+          const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const uint32_t blk = i >> 1, half = i & 1;
+            const uint32_t sbits = blk == 0 ? sc.x : sc.y;
+            const __half2 dd = __half2half2(half == 0 ? __low2half(bits_h2(sbits)) : __high2half(bits_h2(sbits)));
+            const uint32_t lows = words[i] & 0x0F0F0F0Fu, highs = (words[i] >> 4) & 0x0F0F0F0Fu;
+            uint32_t h0, l0, h1, l1;
+            // values 4t..4t+3 sit in core-matrix column blk*4 + t/2, at byte (t & 1) * 8 of the row's 16 bytes
+            const uint32_t dst = hi0 + half * 128 + (blk * 4 + (t >> 1)) * A_LBO + (t & 1) * 8;
+            dq2(__byte_perm(lows, 0x64646464u, 0x4140), zp, dd, h0, l0);
+            dq2(__byte_perm(lows, 0x64646464u, 0x4342), zp, dd, h1, l1);
+            sts64(dst, h0, h1);
+            sts64(dst + A_TERM, l0, l1);
+            dq2(__byte_perm(highs, 0x64646464u, 0x4140), zp, dd, h0, l0);
+            dq2(__byte_perm(highs, 0x64646464u, 0x4342), zp, dd, h1, l1);
+            sts64(dst + 2 * A_LBO, h0, h1);  // values 16 + 4t.. : two core-matrix columns further
+            sts64(dst + 2 * A_LBO + A_TERM, l0, l1);
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA's reads
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&a_full[ra.stage]);
+          mbar_arrive(&raw_empty[raw.stage]);
+        }
+        raw.advance(), ra.advance();
+      }
+    }
+    if (!ok && lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
+  } else {
+    // ---------------------------------------------------------------------------- epilogue
+    const uint32_t q = warp & 3;  // a warp reads the TMEM lanes 32 * (warp % 4) ..
+    const uint32_t row = q * 32 + lane;  // row of the item's 128-row tile
+    uint32_t used = 0;
+    for (uint32_t item = item_beg; item < item_end && ok; item++) {
+      const uint32_t pass = item / m_tiles, mt = item % m_tiles;
+      const uint32_t pstart = d.pass_start[pass], pcount = d.pass_count[pass];
+      const bool resident = expert_base(pass) != nullptr;
+      uint32_t buf = 0;
+      if (resident) {
+        buf = used & 1;
+        ok = mbar_wait(&acc_full[buf], (used >> 1) & 1);
+        used++;
+        if (*s_abort) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+      } else if (warp == W_EPI0 && lane == 0) {
+        atomicOr(d.status, MER_DEVSTAT_RESIDENCY_MISS);  // fail closed: zeros below
+      }
+      for (uint32_t c0 = 0; c0 < pcount; c0 += 16) {
+        uint32_t v[16];
+        if (resident) {
+          tc_ld16(tmem_base + ((q * 32u) << 16) + buf * 128 + c0, v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; i++) v[i] = 0;
+        }
+        // lanes 0..15 fetch the pair index and un-scale factor of the chunk's columns
+        uint32_t my_pair = 0;
+        float my_un = 0.0f;
+        if (lane < 16 && c0 + lane < pcount) {
+          my_pair = d.perm[pstart + c0 + lane];
+          my_un = p.unscale[(size_t)pass * p.bn + c0 + lane];
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+          const uint32_t pair = __shfl_sync(0xffffffffu, my_pair, i);
+          const float un = __shfl_sync(0xffffffffu, my_un, i);
+          const bool valid = c0 + i < pcount;  // uniform
+          const float val = __uint_as_float(v[i]) * un;
+          if (p.phase == 0) {
+            // rows come in packed tiles of 16: slots 0..7 gate rows, 8..15 the matching up rows
+            const float up = __shfl_down_sync(0xffffffffu, val, 8);
+            const bool is_gate = (lane & 8) == 0;
+            float gate = val;
+            if (d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit) && gate == gate) gate = fminf(fmaxf(gate, -d.swiglu_limit), d.swiglu_limit);
+            const float hval = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+            const float ah = fabsf(hval);
+            uint32_t bits = (!valid || !is_gate) ? 0u : (ah != ah) ? 0x7fc00000u : __float_as_uint(ah);
+            bits = __reduce_max_sync(0xffffffffu, bits);
+            if (valid) {
+              if (is_gate) p.out[(size_t)pair * d.F + (mt * 8 + (row >> 4)) * 8 + (lane & 7)] = hval;
+              if (lane == 0) atomicMax(d.amax + pair, bits);
+            }
+          } else if (valid) {
+            p.out[(size_t)pair * d.D + mt * 128 + row] = val;
+          }
+        }
+      }
+      if (resident) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      }
+    }
+    if (!ok && lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == W_MMA) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// Per-token row maximum of |x| (the gate/up activations' scale source).  One warp per token.
+__global__ void __launch_bounds__(256) k_row_amax(const float *__restrict__ x, uint32_t n_tokens, uint32_t K, uint32_t *__restrict__ amax) {
+  const uint32_t tok = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (tok >= n_tokens) return;
+  const float4 *r4 = reinterpret_cast<const float4 *>(x + (size_t)tok * K);
+  float mx = 0.0f;
+  bool nan = false;
+  for (uint32_t i = lane; i < K / 4; i += 32) {
+    const float4 v = __ldg(r4 + i);
+    nan |= (v.x != v.x) | (v.y != v.y) | (v.z != v.z) | (v.w != v.w);
+    mx = fmaxf(fmaxf(fmaxf(fmaxf(mx, fabsf(v.x)), fabsf(v.y)), fabsf(v.z)), fabsf(v.w));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  nan = __any_sync(0xffffffffu, nan);
+  if (lane == 0) amax[tok] = nan ? 0x7fc00000u : __float_as_uint(mx);
+}
+
+// Builds, for every token pass, the activation operand images the GEMM kernel copies chunk by
+// chunk: per 64 columns of K, {hi tile, lo tile}, each 8 core-matrix columns of [bn/8 row groups]
+// [8 rows][16 B] (+32 B skew), rows = the pass's tokens.  grid = (pass capacity, K / 64).
+__global__ void __launch_bounds__(256) k_gemm_act_image(MoeDispatch d, int phase, const float *__restrict__ act, uint32_t K, uint32_t bn,
+                                                        uint32_t b_lbo, const uint32_t *__restrict__ amax_tok, uint8_t *__restrict__ img,
+                                                        float *__restrict__ unscale) {
+  const uint32_t pass = blockIdx.x, chunk = blockIdx.y;
+  if (pass >= *d.n_passes) return;
+  const uint32_t pstart = d.pass_start[pass], pcount = d.pass_count[pass];
+  const uint32_t n_chunks = K / 64;
+  uint8_t *dst0 = img + ((size_t)pass * n_chunks + chunk) * 16 * b_lbo;
+  for (uint32_t idx = threadIdx.x; idx < bn * 8; idx += blockDim.x) {
+    const uint32_t j = idx % bn, k8 = idx / bn;
+    uint4 hi = make_uint4(0, 0, 0, 0), lo = make_uint4(0, 0, 0, 0);
+    float un = 0.0f;
+    if (j < pcount) {
+      const uint32_t pair = d.perm[pstart + j];
+      const uint32_t rowi = phase == 0 ? pair / d.slots : pair;
+      const float mx = __uint_as_float(phase == 0 ? amax_tok[rowi] : d.amax[pair]);
+      float sc = 1.0f;
+      if (mx > 0.0f && isfinite(mx)) {
+        int e;
+        frexpf(mx, &e);
+        sc = ldexpf(1.0f, (int)POW2_SCALE_TARGET - e);  // mx * sc in [256, 512)
+      } else if (mx != mx || isinf(mx)) {
+        sc = mx;  // non-finite activations poison the row, as they would in fp32
+      }
+      un = 1.0f / sc;
+      const float4 *src = reinterpret_cast<const float4 *>(act + (size_t)rowi * K + chunk * 64 + k8 * 8);
+      const float4 a = __ldg(src), b = __ldg(src + 1);
+      const float vs[8] = {a.x * sc, a.y * sc, a.z * sc, a.w * sc, b.x * sc, b.y * sc, b.z * sc, b.w * sc};
+      uint32_t h[4], l[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const __half2 hh = __floats2half2_rn(vs[2 * i], vs[2 * i + 1]);
+        const float2 back = __half22float2(hh);
+        h[i] = h2_bits(hh);
+        l[i] = h2_bits(__floats2half2_rn(vs[2 * i] - back.x, vs[2 * i + 1] - back.y));
+      }
+      hi = make_uint4(h[0], h[1], h[2], h[3]), lo = make_uint4(l[0], l[1], l[2], l[3]);
+    }
+    uint8_t *dst = dst0 + (size_t)k8 * b_lbo + (j >> 3) * 128 + (j & 7) * 16;
+    *reinterpret_cast<uint4 *>(dst) = hi;
+    *reinterpret_cast<uint4 *>(dst + 8 * b_lbo) = lo;
+    if (chunk == 0 && k8 == 0) unscale[(size_t)pass * bn + j] = un;
+  }
+}
+
+struct GemmPlan {
+  uint32_t n_raw, n_a, n_b, b_lbo;
+  size_t smem;
+};
+
+GemmPlan gemm_plan(int dtype, uint32_t bn) {
+  const uint32_t tcb = 2 * 16 * (dtype == MER_DTYPE_Q4_0 ? MER_Q4_BLOCK_BYTES : MER_Q8_BLOCK_BYTES);
+  GemmPlan pl{};
+  pl.b_lbo = bn * 16 + 32;
+  pl.n_raw = 4, pl.n_a = 2, pl.n_b = 3;
+  pl.smem = G_HEADER + (size_t)pl.n_raw * 8 * tcb + (size_t)pl.n_a * 2 * A_TERM + (size_t)pl.n_b * 16 * pl.b_lbo;
+  return pl;
+}
+
+struct GemmScratch {
+  uint32_t *amax_tok;
+  float *unscale;
+  uint8_t *img;
+  size_t img_bytes;
+};
+
+GemmScratch gemm_scratch(void *scratch, size_t scratch_bytes, uint32_t max_tokens, uint32_t max_pairs) {
+  GemmScratch g{};
+  uint8_t *p = reinterpret_cast<uint8_t *>(scratch);
+  g.amax_tok = reinterpret_cast<uint32_t *>(p);
+  size_t off = ((size_t)max_tokens * 4 + 255) & ~(size_t)255;
+  g.unscale = reinterpret_cast<float *>(p + off);
+  off += ((size_t)3 * max_pairs * 4 + 128 * 4 + 255) & ~(size_t)255;
+  g.img = p + off;
+  g.img_bytes = scratch_bytes > off ? scratch_bytes - off : 0;
+  return g;
+}
+
+}  // namespace
+
+bool gemm_ffn_supported(int dtype, uint32_t D, uint32_t F) {
+  return (dtype == MER_DTYPE_Q4_0 || dtype == MER_DTYPE_Q8_0) && D % 256 == 0 && F % 256 == 0;
+}
+
+// Activation images: rows padded to whole passes (at most 3 x max_pairs rows), 4 bytes per value plus the skew.
+size_t gemm_ffn_scratch_bytes(uint32_t max_tokens, uint32_t max_pairs, uint32_t D, uint32_t F) {
+  const size_t kmax = D > F ? D : F;
+  const size_t rows = (size_t)3 * max_pairs + 128;
+  return (((size_t)max_tokens * 4 + 255) & ~(size_t)255) + ((rows * 4 + 255) & ~(size_t)255) + rows * kmax * 4 + (rows / 16 + 1) * (kmax / 64) * 512 +
+         4096;
+}
+
+// Tokens per pass for a dispatch: about 1.5 x the mean group size, within what the image scratch holds.
+// Returns 0 when the dispatch is better served by the streaming kernels.
+uint32_t gemm_pick_bn(const MoeDispatch &d, uint32_t min_mean_tokens) {
+  const uint64_t P = (uint64_t)d.n_tokens * d.slots;
+  const uint32_t groups = d.active_groups_hint ? d.active_groups_hint : 1;
+  const uint64_t mean = P / groups;
+  if (mean < min_mean_tokens) return 0;
+  uint32_t bn = mean <= 12 ? 16 : mean <= 24 ? 32 : mean <= 56 ? 64 : 128;
+  const uint64_t gmax = d.n_groups < P ? d.n_groups : P;
+  while (bn > 16 && P + gmax * (bn - 1) > (uint64_t)3 * d.scratch_pairs) bn >>= 1;
+  if (P + gmax * (bn - 1) > (uint64_t)3 * d.scratch_pairs + 128) return 0;
+  return bn;
+}
+
+void gemm_bind(MoeDispatch &d, void *stream_scratch, int sm_count, uint32_t bn) {
+  stream_bind(d, stream_scratch, sm_count);  // pass tables and the per-pair max cells live in the streaming scratch
+  d.tokens_per_pass = bn;
+}
+
+cudaError_t launch_ffn_gemm(MoeDispatch &d, void *gemm_scratch_ptr, size_t gemm_scratch_bytes, uint32_t max_tokens, int sm_count,
+                            cudaStream_t s, int *launches, cudaEvent_t ev_mid) {
+  const uint32_t bn = d.tokens_per_pass;
+  const GemmPlan pl = gemm_plan(d.dtype, bn);
+  const GemmScratch gs = gemm_scratch(gemm_scratch_ptr, gemm_scratch_bytes, max_tokens, d.scratch_pairs);
+  const uint32_t P = d.n_tokens * d.slots;
+  const uint32_t gmax = d.n_groups < P ? d.n_groups : P;
+  const uint32_t pass_cap = P / bn + gmax;  // upper bound on the number of passes
+  auto kern = d.dtype == MER_DTYPE_Q4_0 ? k_ffn_gemm<MER_DTYPE_Q4_0> : k_ffn_gemm<MER_DTYPE_Q8_0>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+  if (e != cudaSuccess) return e;
+
+  k_row_amax<<<(d.n_tokens + 7) / 8, 256, 0, s>>>(d.x, d.n_tokens, d.D, gs.amax_tok);
+  for (int phase = 0; phase < 2; phase++) {
+    const uint32_t K = phase == 0 ? d.D : d.F;
+    const float *act = phase == 0 ? d.x : d.h;
+    k_gemm_act_image<<<dim3(pass_cap, K / 64), 256, 0, s>>>(d, phase, act, K, bn, pl.b_lbo, gs.amax_tok, gs.img, gs.unscale);
+    GemmParams p{};
+    p.d = d, p.phase = phase, p.act_img = gs.img, p.unscale = gs.unscale;
+    p.rows = phase == 0 ? d.F : d.D;
+    p.kb_total = K / 32;
+    p.bn = bn, p.b_lbo = pl.b_lbo, p.n_raw = pl.n_raw, p.n_a = pl.n_a, p.n_b = pl.n_b;
+    p.out = phase == 0 ? d.h : d.y;
+    kern<<<sm_count, G_THREADS, pl.smem, s>>>(p);
+    if (phase == 0 && ev_mid) cudaEventRecord(ev_mid, s);
+  }
+  d.y_parts = nullptr, d.y_nparts = 1;
+  if (launches) (*launches) += 5;
+  return cudaGetLastError();
+}

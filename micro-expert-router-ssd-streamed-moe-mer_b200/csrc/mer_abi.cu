@@ -71,6 +71,8 @@ struct mer_backend {
   uint32_t *d_status = nullptr, *d_counters = nullptr;
   uint16_t *d_f16 = nullptr;
   void *d_stream_scratch = nullptr;
+  void *d_gemm_scratch = nullptr;  // activation operand images of the tensor-core GEMM path
+  size_t gemm_scratch_bytes = 0;
   uint32_t max_groups = 0, max_router_experts = 0;
   uint32_t *h_u32 = nullptr;  // pinned [max_pairs + 1]: ids up/down, status
   float *h_f32 = nullptr;     // pinned [max_pairs]
@@ -176,8 +178,28 @@ bool use_stream_path(mer_backend *b, const MoeDispatch &d) {
   return stream_ffn_supported(d.dtype, d.D, d.F) && b->d_stream_scratch != nullptr;
 }
 
+constexpr uint32_t GEMM_MIN_MEAN_TOKENS = 12;  // mean tokens per expert from which the tcgen05 GEMM path takes over
+
+// Chooses the kernel family of a dispatch and binds its scratch (call before the grouping kernel, which
+// cuts the groups into passes of d.tokens_per_pass).
+void bind_ffn(mer_backend *b, MoeDispatch &d) {
+  d.gemm_bn = 0;
+  if (!use_stream_path(b, d)) return;
+  if (b->d_gemm_scratch && b->kernel_path != 2) {
+    const uint32_t bn = gemm_pick_bn(d, b->kernel_path == 3 ? 1u : GEMM_MIN_MEAN_TOKENS);
+    if (bn) {
+      gemm_bind(d, b->d_stream_scratch, b->sm_count, bn);
+      d.gemm_bn = bn;
+      return;
+    }
+  }
+  stream_bind(d, b->d_stream_scratch, b->sm_count);
+}
+
 cudaError_t run_ffn(mer_backend *b, MoeDispatch &d, cudaStream_t s, int *launches, cudaEvent_t ev_mid = nullptr) {
   d.y_parts = nullptr, d.y_nparts = 1;
+  if (d.gemm_bn)
+    return launch_ffn_gemm(d, b->d_gemm_scratch, b->gemm_scratch_bytes, b->cfg.max_tokens, b->sm_count, s, launches, ev_mid);
   if (use_stream_path(b, d)) return launch_ffn_stream(d, b->d_stream_scratch, b->sm_count, s, launches, ev_mid);
   return launch_ffn_generic(d, s, launches, ev_mid);
 }
@@ -272,7 +294,7 @@ void free_all(mer_backend *b) {
   b->routers.clear();
   F(b->arena), F(b->d_expert_ptr), F(b->d_x), F(b->d_out), F(b->d_h), F(b->d_y), F(b->d_pair_weight), F(b->d_logits);
   F(b->d_pair_expert), F(b->d_group_expert), F(b->d_offsets), F(b->d_perm), F(b->d_status), F(b->d_counters);
-  F(b->d_f16), F(b->d_stream_scratch), F(b->d_dequant), F(b->d_raw_stage);
+  F(b->d_f16), F(b->d_stream_scratch), F(b->d_gemm_scratch), F(b->d_dequant), F(b->d_raw_stage);
   H(b->h_expert_ptr), H(b->h_stage[0]), H(b->h_stage[1]), H(b->h_hdr), H(b->h_u32), H(b->h_f32);
   if (b->ev_compute_done) cudaEventDestroy(b->ev_compute_done);
   if (b->ev_copy_done) cudaEventDestroy(b->ev_copy_done);
@@ -428,7 +450,7 @@ int dispatch_given_routing(mer_backend *b, uint32_t layer, MoeDispatch &d, const
   d.n_groups = single_group ? 1u : (uint32_t)n_pairs;
   d.max_group_tokens = single_group ? (uint32_t)n_pairs : 1u;
   d.active_groups_hint = d.n_groups;
-  if (use_stream_path(b, d)) stream_bind(d, b->d_stream_scratch, b->sm_count);
+  bind_ffn(b, d);
   CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, b->compute));
   CU(MER_ERR_SUBMISSION, "group kernel", launch_groups_from_pairs(d, b->compute, launches));
   CU(MER_ERR_SUBMISSION, "expert FFN kernels", run_ffn(b, d, b->compute, launches));
@@ -572,6 +594,10 @@ MER_EXPORT int mer_backend_create(const mer_backend_cfg *cfg, mer_backend **out)
       CB(cudaMalloc(&b->d_stream_scratch, sb));
       CB(cudaMemset(b->d_stream_scratch, 0, sb));
     }
+    if (sb && T >= GEMM_MIN_MEAN_TOKENS && gemm_ffn_supported(cfg->dtype, (uint32_t)D, (uint32_t)F)) {
+      b->gemm_scratch_bytes = gemm_ffn_scratch_bytes((uint32_t)T, (uint32_t)P, (uint32_t)D, (uint32_t)F);
+      CB(cudaMalloc(&b->d_gemm_scratch, b->gemm_scratch_bytes));
+    }
   }
   CB(cudaDeviceSynchronize());
 #undef CB
@@ -703,7 +729,7 @@ int enqueue_layer(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tok
   d.n_groups = r.num_experts + (r.shared_expert_id != MER_NONE ? 1u : 0u);
   d.max_group_tokens = d.n_tokens;  // a token reaches an expert at most once
   d.active_groups_hint = std::min(d.n_groups, d.n_tokens * d.slots);
-  if (run_ffn_too && use_stream_path(b, d)) stream_bind(d, b->d_stream_scratch, b->sm_count);
+  if (run_ffn_too) bind_ffn(b, d);
   d.x = d_x;
   d.out = d_out;
   CU(MER_ERR_SUBMISSION, "cudaMemsetAsync(status)", cudaMemsetAsync(b->d_status, 0, 4, s));
@@ -987,7 +1013,7 @@ int ep_run_local_experts(mer_backend *b, uint32_t layer, const RouterDev &r, Moe
   d.n_groups = r.num_experts + shared;
   d.max_group_tokens = d.n_tokens;
   d.active_groups_hint = std::min(b->ep.experts_per_rank + shared, d.n_tokens * d.slots);
-  if (use_stream_path(b, d)) stream_bind(d, b->d_stream_scratch, b->sm_count);
+  bind_ffn(b, d);
   CU(MER_ERR_SUBMISSION, "group kernel", launch_groups_layer(r, d, s, launches));
   CU(MER_ERR_SUBMISSION, "expert FFN kernels", run_ffn(b, d, s, launches));
   return MER_OK;
@@ -1303,10 +1329,13 @@ MER_EXPORT int mer_snapshot(mer_backend *b, mer_counters *out) {
 }
 
 MER_EXPORT int mer_set_kernel_path(mer_backend *b, int path) {
-  if (!b || path < 0 || path > 2) return MER_ERR_INVALID_ARGUMENT;
+  if (!b || path < 0 || path > 3) return MER_ERR_INVALID_ARGUMENT;
   std::lock_guard<std::mutex> lock(b->mu);
   if (path == 2 && !b->d_stream_scratch)
     return fail(b, MER_ERR_INELIGIBLE, 0, MER_NONE, "streaming kernels need d_model and d_ff to be multiples of 256");
+  if (path == 3 && !b->d_gemm_scratch)
+    return fail(b, MER_ERR_INELIGIBLE, 0, MER_NONE,
+                "the GEMM kernels need d_model and d_ff to be multiples of 256 and a backend of at least %u tokens", GEMM_MIN_MEAN_TOKENS);
   b->kernel_path = path;
   drop_graphs(b);
   return MER_OK;
