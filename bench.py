@@ -34,8 +34,10 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {  # name -> (config, default batch, default layers)
     "cfg0": ("cfg0-mixtral-q4_0", 1, 4),
     "cfg1": ("cfg1-qwen3-q8_0", 64, 4),
+    "cfg3": ("cfg3-qwen3-prefill-q8_0", 2048, 2),  # prefill: ~128 tokens per expert, Zipf(1.0) skew -> tcgen05 GEMM path
     "cfg4": ("cfg4-deepseek-v3-q4_0", 16, 1),
 }
+ZIPF = {"cfg3": 1.0}  # routing-locality skew added to the router logits of a workload
 DTYPE_NAME = {0: "q4_0", 1: "q8_0"}
 PARALLELISM_NOTE = {
     "replicas": "{n} replicas, tokens data-parallel, no data-path collective",
@@ -108,6 +110,14 @@ def measured_peak():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def measured_tensor_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
 
 
 def ncu_traffic(key):
@@ -223,6 +233,8 @@ def main():
             be.admit(shared_id, 1, shared, wait=False)
         gate = mer_b200.LinearGate.with_routing(W, cfg.num_experts, cfg.d_model, cfg.top_k, cfg.scoring, True, None, cfg.n_group,
                                                 cfg.topk_group, cfg.scaling)
+        if args.workload in ZIPF:
+            gate.logit_bias = synth.zipf_logit_bias(cfg.num_experts, ZIPF[args.workload], cfg.seed, l, strength=0.25)
         be.install_router(l, gate, shared_id)
         xs_host.append(synth.make_activations(B, cfg.d_model, cfg.seed, rank * R + l))
     be.synchronize()
@@ -354,6 +366,18 @@ def main():
                     "traffic": ncu_traffic(f"{args.workload}-b{B}"), "algorithmic_bytes_per_launch": kernel_bytes,
                     "avg_launch_ms": gu_ms, "frac_of_8tbs": achieved / 8000.0 if achieved else None}
         stages = {k: v / n for k, v in st.items() if k != "samples"}
+        if B * slots >= 12 * n_exp and not fused and gu_ms > 0:
+            # a dozen tokens per expert and more: the tcgen05 GEMM kernels run, bounded by the tensor pipe.
+            # Algorithmic FLOPs of the gate/up launch: every (token, slot) pair through two [F x D] projections.
+            tpeak, tkind = measured_tensor_peak()
+            flops = 2.0 * B * slots * 2 * cfg.d_model * cfg.d_ff
+            tf = flops / (gu_ms * 1e-3) / 1e12
+            roofline = {"bound": "tensor", "kernel": "expert_gate_up (grouped dequant GEMM, tcgen05, + SiLU*mul)", "achieved": tf,
+                        "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak, "peak_source": f"of {tkind}",
+                        "traffic": ncu_traffic(f"{args.workload}-b{B}"), "algorithmic_flops_per_launch": flops,
+                        "avg_launch_ms": gu_ms,
+                        "note": "each algorithmic product is issued as three f16 MMAs (hi*hi, hi*lo, lo*hi) to hold the fp32 "
+                                "parity bar, so the tensor pipe does 3x these FLOPs"}
     else:
         # expert-parallel step: no per-stage timers; the whole step of rank 0 against the bytes its experts stream
         roofline = {"bound": "hbm", "kernel": "whole expert-parallel step of one rank (router, exchange, local experts, combine)",

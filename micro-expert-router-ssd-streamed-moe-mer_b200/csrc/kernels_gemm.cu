@@ -1,20 +1,23 @@
 // Grouped expert FFN for token groups of a dozen tokens and more (prefill, expert-parallel decode):
 // tcgen05 tensor-core GEMM per (expert, 128 weight rows, up to 128 tokens) with TMEM accumulators.
 //
-//   D[128 weight rows x N tokens] += A[128 x 64] * B[N x 64]^T      per 64-column chunk of K
+//   D[128 weight rows x N tokens] += A[128 x 32] * B[N x 32]^T      per 32-value block of K
 //
-//   * A is produced on the fly: the packed Q4_0 / Q8_0 tile chunks of layout.cuh are streamed
-//     global -> shared by bulk async copies (every weight byte crosses HBM once per token tile) and
-//     eight warps dequantise them into two f16 operand tiles, hi = f16(d*q) and lo = d*q - hi (exact:
-//     an 11-bit scale times an 8-bit integer has at most 19 significant bits), written in the
-//     K-major no-swizzle core-matrix layout the MMA reads.
+//   * A never touches shared memory as an operand: the packed Q4_0 / Q8_0 tile chunks of layout.cuh
+//     are streamed global -> shared by bulk async copies (every weight byte crosses HBM once per token
+//     tile), eight warps dequantise them block by block into two f16 operands, hi = f16(d*q) and
+//     lo = d*q - hi (exact: an 11-bit scale times an 8-bit integer has at most 19 significant bits),
+//     and store them straight into TENSOR MEMORY (tcgen05.st; a thread owns one weight row), from
+//     where the MMA reads its A operand.  Eight A stages live in TMEM beside the two accumulators, so
+//     the dequant -> MMA -> release loop is covered without spending shared memory on it.
 //   * B is the activation tile as f16 hi + lo parts (22 significant bits after an exact power-of-two
-//     per-row scaling), laid out in the same core-matrix order by k_gemm_act_image and fetched with
-//     one bulk copy per chunk.
-//   * Three MMAs per 16 columns of K (hi*hi, hi*lo, lo*hi; lo*lo is below fp32 resolution) accumulate
+//     per-row scaling), laid out in the K-major no-swizzle core-matrix order by k_gemm_act_image and
+//     fetched with one bulk copy per 64 values of K into a five-stage shared-memory ring.
+//   * Three MMAs per 16 values of K (hi*hi, hi*lo, lo*hi; lo*lo is below fp32 resolution) accumulate
 //     in fp32 in TMEM, so the result matches the fp32 reference to ~1e-6 instead of f16's 1e-3.
 //   * Warp roles: 0 = copy producer, 1 = MMA issuer (one elected lane) and TMEM owner, 2..5 = epilogue
-//     (tcgen05.ld, un-scaling, SiLU(gate)*up or plain store), 6..13 = dequantisers.  Two accumulator
+//     (tcgen05.ld, un-scaling, SiLU(gate)*up or plain store), 6..13 = dequantisers (a warp reaches the
+//     32 TMEM lanes of its quarter; the two warps of a quarter take alternate blocks).  Two accumulator
 //     buffers let the epilogue of one item overlap the MMAs of the next.
 // Every wait is bounded; on expiry the CTA latches MER_DEVSTAT_TIMEOUT, stops issuing work, waits
 // (bounded) for its copies and MMAs in flight, frees its TMEM and returns.
@@ -29,11 +32,15 @@ namespace {
 constexpr int G_WARPS = 14, G_THREADS = G_WARPS * 32;
 constexpr int W_PRODUCER = 0, W_MMA = 1, W_EPI0 = 2, W_DQ0 = 6;
 constexpr int EPI_WARPS = 4, DQ_WARPS = 8;
-constexpr uint32_t A_LBO = 2080;         // bytes between K core matrices of A: 16 row groups x 128 B + 32 B skew (bank spread)
-constexpr uint32_t A_TERM = 8 * A_LBO;   // one operand tile: 8 core-matrix columns = 64 values of K
+constexpr uint32_t RAW_BLOCKS = 4;       // blocks of K per weight stage (per packed tile: one bulk copy)
 constexpr uint32_t G_HEADER = 1024;
-constexpr uint32_t TMEM_COLS = 256;      // two accumulator buffers of up to 128 columns
-constexpr uint32_t MAX_RING = 4;
+constexpr uint32_t TMEM_COLS = 512;      // [0, 256): two accumulator buffers of up to 128 columns; [256, 512): A stages
+constexpr uint32_t TMEM_A0 = 256, A_STAGES = 8, A_STAGE_COLS = 32;  // a stage = one block: 16 columns hi + 16 columns lo
+constexpr uint32_t MAX_RING = 8;
+// The MMA issuer synchronises once per GROUP blocks of K: it waits for a whole group of A stages, issues the
+// group's MMAs and commits ONE barrier, done[], that releases both the group's A stages and the activation stages
+// it read (a wait or a commit per block cost more issue time than the block's MMAs take to run).
+constexpr uint32_t GROUP = 4, DONE_RING = 4;
 constexpr float POW2_SCALE_TARGET = 9;   // activations are scaled so that the row maximum lies in [256, 512)
 
 struct GemmParams {
@@ -45,7 +52,7 @@ struct GemmParams {
   uint32_t kb_total;       // 32-value blocks per weight row
   uint32_t bn;             // token columns per pass (16, 32, 64 or 128)
   uint32_t b_lbo;          // bytes between K core matrices of B: bn * 16 + 32
-  uint32_t n_raw, n_a, n_b;  // ring depths
+  uint32_t n_raw, n_b;     // ring depths (weights, activations)
   float *out;              // phase 0: h [P x F]; phase 1: y [P x D]
 };
 
@@ -62,11 +69,24 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
 }
 // f16 x f16 -> f32, both operands K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t instr_desc(uint32_t n) { return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+// A operand read from tensor memory (lane = row, a 32-bit column = two consecutive values of K), B through a descriptor.
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
-      "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u)
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// 32 columns of this thread's TMEM lane (lane = 32 * (warp % 4) + lane id).
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      "tcgen05.wait::st.sync.aligned;\n" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+      "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
+      "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]),
+      "r"(v[31])
       : "memory");
 }
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
@@ -78,13 +98,6 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
-  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
-}
-__device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) {
-  asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(x), "r"(y) : "memory");
-}
-
 __device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
 __device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
 
@@ -109,33 +122,34 @@ template <int DT>
 __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr uint32_t BB = DT == MER_DTYPE_Q4_0 ? MER_Q4_BLOCK_BYTES : MER_Q8_BLOCK_BYTES;
-  constexpr uint32_t TCB = 2 * 16 * BB;  // bytes of one packed tile's 64-column chunk (576 / 1088)
-  constexpr uint32_t RAW_BYTES = 8 * TCB;
+  constexpr uint32_t TILE_RAW = RAW_BLOCKS * 16 * BB;  // bytes of RAW_BLOCKS blocks of one packed tile (2304 / 4352)
+  constexpr uint32_t RAW_BYTES = 8 * TILE_RAW;
   const MoeDispatch &d = p.d;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const uint32_t m_tiles = p.rows / (p.phase == 0 ? 64u : 128u);  // 8 packed tiles each
   const uint32_t n_chunks = p.kb_total / 2;
   const uint32_t n_passes = *d.n_passes;
-  const uint64_t n_items = (uint64_t)n_passes * m_tiles;
-  const uint32_t item_beg = (uint32_t)(n_items * blockIdx.x / gridDim.x), item_end = (uint32_t)(n_items * (blockIdx.x + 1) / gridDim.x);
-  if (item_beg >= item_end) return;
+  // Items (pass, 128-row tile) are dealt round-robin: the CTAs running at any moment work on a dozen
+  // neighbouring passes, so the activation images they all re-read stay in L2.
+  const uint32_t n_items = n_passes * m_tiles;
+  const uint32_t item_beg = blockIdx.x, item_step = gridDim.x;
+  if (item_beg >= n_items) return;
 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
-  uint64_t *raw_full = bars, *raw_empty = bars + 4, *a_full = bars + 8, *a_empty = bars + 12, *b_full = bars + 16,
-           *b_empty = bars + 20, *acc_full = bars + 24, *acc_empty = bars + 26, *drain = bars + 28;
-  uint32_t *s_tmem = reinterpret_cast<uint32_t *>(smem + 256);
-  volatile uint32_t *s_abort = reinterpret_cast<volatile uint32_t *>(smem + 260);
+  uint64_t *raw_full = bars, *raw_empty = bars + 8, *a_full = bars + 16, *done = bars + 24, *b_full = bars + 32,
+           *acc_full = bars + 48, *acc_empty = bars + 50, *drain = bars + 52;
+  uint32_t *s_tmem = reinterpret_cast<uint32_t *>(smem + 512);
+  volatile uint32_t *s_abort = reinterpret_cast<volatile uint32_t *>(smem + 516);
   uint8_t *s_raw = smem + G_HEADER;
-  uint8_t *s_a = s_raw + p.n_raw * RAW_BYTES;
-  uint8_t *s_b = s_a + p.n_a * 2 * A_TERM;
+  uint8_t *s_b = s_raw + p.n_raw * RAW_BYTES;
   const uint32_t b_term = 8 * p.b_lbo, b_stage = 2 * b_term;
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < MAX_RING; s++) {
       mbar_init(&raw_full[s], 1), mbar_init(&raw_empty[s], DQ_WARPS);
-      mbar_init(&a_full[s], DQ_WARPS), mbar_init(&a_empty[s], 1);
-      mbar_init(&b_full[s], 1), mbar_init(&b_empty[s], 1);
+      mbar_init(&a_full[s], GROUP * (DQ_WARPS / 2)), mbar_init(&done[s], 1);
+      mbar_init(&b_full[s], 1);
     }
     for (uint32_t s = 0; s < 2; s++) mbar_init(&acc_full[s], 1), mbar_init(&acc_empty[s], EPI_WARPS);
     mbar_init(drain, 1);
@@ -162,27 +176,38 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
 
   if (warp == W_PRODUCER) {
     // ------------------------------------------------------------------------ copy producer
+    // weights: one stage = RAW_BLOCKS blocks of the item's 8 packed tiles (8 copies); activations: one stage = 2 blocks
     Ring raw(p.n_raw), rb(p.n_b);
-    for (uint32_t item = item_beg; item < item_end && ok; item++) {
+    uint32_t gchunk = 0;  // 64-value activation chunks issued so far, over all items
+    for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
       const uint32_t pass = item / m_tiles, mt = item % m_tiles;
       const uint8_t *base = expert_base(pass);
       if (!base) continue;
       const uint8_t *wsrc = base + region + (size_t)(mt * 8 + (lane & 7)) * tile_bytes;
       const uint8_t *bsrc = p.act_img + (size_t)pass * n_chunks * b_stage;
-      for (uint32_t c = 0; c < n_chunks && ok; c++) {
-        if (raw.round > 0) ok = mbar_wait(&raw_empty[raw.stage], (raw.round - 1) & 1);
-        if (ok && rb.round > 0) ok = mbar_wait(&b_empty[rb.stage], (rb.round - 1) & 1);
+      for (uint32_t st = 0; st < p.kb_total && ok; st += 2) {
+        const bool new_raw = (st % RAW_BLOCKS) == 0;
+        if (new_raw && raw.round > 0) ok = mbar_wait(&raw_empty[raw.stage], (raw.round - 1) & 1);
+        if (ok && gchunk >= p.n_b) {
+          // the slot's previous chunk was read by the MMAs of group (gchunk - n_b) / 2
+          const uint32_t sp = (gchunk - p.n_b) / (GROUP / 2);
+          ok = mbar_wait(&done[sp % DONE_RING], (sp / DONE_RING) & 1);
+        }
+        gchunk++;
         if (*s_abort) ok = false;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (lane == 0) {
-          mbar_expect_tx(&raw_full[raw.stage], RAW_BYTES);
+          if (new_raw) mbar_expect_tx(&raw_full[raw.stage], RAW_BYTES);
           mbar_expect_tx(&b_full[rb.stage], b_stage);
         }
         __syncwarp();
-        if (lane < 8) bulk_g2s(s_raw + raw.stage * RAW_BYTES + lane * TCB, wsrc + (size_t)c * TCB, TCB, &raw_full[raw.stage]);
-        if (lane == 8) bulk_g2s(s_b + (size_t)rb.stage * b_stage, bsrc + (size_t)c * b_stage, b_stage, &b_full[rb.stage]);
-        raw.advance(), rb.advance();
+        if (new_raw && lane < 8)
+          bulk_g2s(s_raw + raw.stage * RAW_BYTES + lane * TILE_RAW, wsrc + (size_t)(st / RAW_BLOCKS) * TILE_RAW, TILE_RAW,
+                   &raw_full[raw.stage]);
+        if (lane == 8) bulk_g2s(s_b + (size_t)rb.stage * b_stage, bsrc + (size_t)(st / 2) * b_stage, b_stage, &b_full[rb.stage]);
+        if (new_raw) raw.advance();
+        rb.advance();
       }
     }
     if (!ok) {
@@ -193,10 +218,12 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     }
   } else if (warp == W_MMA) {
     // -------------------------------------------------------------------------- MMA issuer
-    Ring ra(p.n_a), rb(p.n_b);
+    // one step = one 32-value block of K: two instructions of 16 values for each of the three operand pairings
+    Ring rb(p.n_b);
     const uint32_t idesc = instr_desc(p.bn);
     uint32_t used = 0;  // items issued so far: buffer = used & 1, its k-th use has k = used >> 1
-    for (uint32_t item = item_beg; item < item_end && ok; item++) {
+    uint32_t grp = 0;   // groups of GROUP blocks issued so far, over all items
+    for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
       const uint32_t pass = item / m_tiles;
       if (!expert_base(pass)) continue;
       const uint32_t buf = used & 1, use = used >> 1;
@@ -205,28 +232,37 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
         if (use > 0) ok = mbar_wait(&acc_empty[buf], (use - 1) & 1);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * 128;
-        for (uint32_t c = 0; c < n_chunks && ok; c++) {
-          ok = mbar_wait(&a_full[ra.stage], ra.round & 1) && mbar_wait(&b_full[rb.stage], rb.round & 1);
+        for (uint32_t st = 0; st < p.kb_total && ok; st += GROUP, grp++) {
+          const uint32_t ag = grp & 1;  // the group's A stages: ag * GROUP ..
+          ok = mbar_wait(&a_full[ag], (grp >> 1) & 1);
           if (*s_abort) ok = false;
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_hi = smem_u32(s_a) + ra.stage * 2 * A_TERM, a_lo = a_hi + A_TERM;
-          const uint32_t b_hi = smem_u32(s_b) + rb.stage * b_stage, b_lo = b_hi + b_term;
 #pragma unroll
-          for (uint32_t j = 0; j < 4; j++) {  // 16 values of K per instruction = two core-matrix columns
-            const uint64_t dah = smem_desc(a_hi + j * 2 * A_LBO, A_LBO, 128), dal = smem_desc(a_lo + j * 2 * A_LBO, A_LBO, 128);
-            const uint64_t dbh = smem_desc(b_hi + j * 2 * p.b_lbo, p.b_lbo, 128), dbl = smem_desc(b_lo + j * 2 * p.b_lbo, p.b_lbo, 128);
-            tc_mma(d_tmem, dah, dbh, idesc, (c | j) != 0);
-            tc_mma(d_tmem, dah, dbl, idesc, 1);
-            tc_mma(d_tmem, dal, dbh, idesc, 1);
+          for (uint32_t b4 = 0; b4 < GROUP; b4++) {
+            if (!(b4 & 1)) {
+              ok = mbar_wait(&b_full[rb.stage], rb.round & 1);
+              if (!ok) break;
+              tc_fence_after();
+            }
+            const uint32_t a_hi = tmem_base + TMEM_A0 + (ag * GROUP + b4) * A_STAGE_COLS, a_lo = a_hi + 16;
+            const uint32_t b_hi = smem_u32(s_b) + rb.stage * b_stage + (b4 & 1) * 4 * p.b_lbo, b_lo = b_hi + b_term;
+#pragma unroll
+            for (uint32_t j = 0; j < 2; j++) {  // 16 values of K per instruction: 8 TMEM columns of A, two core-matrix columns of B
+              const uint64_t dbh = smem_desc(b_hi + j * 2 * p.b_lbo, p.b_lbo, 128), dbl = smem_desc(b_lo + j * 2 * p.b_lbo, p.b_lbo, 128);
+              tc_mma_ts(d_tmem, a_hi + j * 8, dbh, idesc, (st | b4 | j) != 0);
+              tc_mma_ts(d_tmem, a_hi + j * 8, dbl, idesc, 1);
+              tc_mma_ts(d_tmem, a_lo + j * 8, dbh, idesc, 1);
+            }
+            if (b4 & 1) rb.advance();
           }
-          tc_commit(&a_empty[ra.stage]);
-          tc_commit(&b_empty[rb.stage]);
-          ra.advance(), rb.advance();
+          if (!ok) break;
+          tc_commit(&done[grp % DONE_RING]);
         }
         if (ok) tc_commit(&acc_full[buf]);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
+      grp = __shfl_sync(0xffffffffu, grp, 0);
     }
     if (lane == 0) {
       if (!ok) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
@@ -237,73 +273,72 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     __syncwarp();
   } else if (warp >= W_DQ0) {
     // ------------------------------------------------------------------------ dequantisers
-    Ring raw(p.n_raw), ra(p.n_a);
-    const uint32_t T = warp - W_DQ0;  // packed tile of the item handled by this warp
-    const uint32_t g = lane >> 2, t = lane & 3;
+    // A thread owns one weight row of the item: TMEM lane 32 * (warp % 4) + lane, i.e. packed tile 2q + lane / 16,
+    // row slot lane % 16.  Per block it reads the row's 32 quants from the tile chunk in shared memory and stores
+    // 16 columns of hi and 16 of lo.  The two warps of a quarter take alternate blocks.
+    Ring raw(p.n_raw);
+    uint32_t gblk = 0;  // blocks of K seen so far, over all items (A stage = gblk % A_STAGES)
+    const uint32_t q = warp & 3, mine = (warp - W_DQ0) >> 2;
+    const uint32_t T = 2 * q + (lane >> 4), g = lane & 7, half = (lane >> 3) & 1;
     const __half2 zp = DT == MER_DTYPE_Q4_0 ? __floats2half2_rn(1032.0f, 1032.0f) : __floats2half2_rn(1152.0f, 1152.0f);
-    for (uint32_t item = item_beg; item < item_end && ok; item++) {
+    for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
       const uint32_t pass = item / m_tiles;
       if (!expert_base(pass)) continue;
-      for (uint32_t c = 0; c < n_chunks && ok; c++) {
-        ok = mbar_wait(&raw_full[raw.stage], raw.round & 1);
-        if (ok && ra.round > 0) ok = mbar_wait(&a_empty[ra.stage], (ra.round - 1) & 1);
-        if (*s_abort) ok = false;
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        const uint32_t src = smem_u32(s_raw) + raw.stage * RAW_BYTES + T * TCB;
-        const uint32_t hi0 = smem_u32(s_a) + ra.stage * 2 * A_TERM + (2 * T) * 128 + g * 16;  // row T*16 + g; +128 = row + 8
-        if (DT == MER_DTYPE_Q8_0) {
+      for (uint32_t st = 0; st < p.kb_total && ok; st++) {
+        const uint32_t sub = st % RAW_BLOCKS;
+        if ((st & 1) == mine) {
+          // raw stages are shared by both warps of the quarter: a warp enters a stage at its first own block
+          if (sub == mine) ok = mbar_wait(&raw_full[raw.stage], raw.round & 1);
+          if (ok && gblk >= A_STAGES) {
+            // the stage was last read by the MMAs of group gblk / GROUP - 2
+            const uint32_t sp = gblk / GROUP - A_STAGES / GROUP;
+            ok = mbar_wait(&done[sp % DONE_RING], (sp / DONE_RING) & 1);
+          }
+          if (*s_abort) ok = false;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t tile_src = smem_u32(s_raw) + raw.stage * RAW_BYTES + T * TILE_RAW;
+          uint32_t v[32];  // [0, 16): hi, values (2c, 2c+1) of the block in column c; [16, 32): lo
+          if (DT == MER_DTYPE_Q8_0) {
+            const uint32_t src = tile_src + sub * 544;
+            const uint32_t sc2 = lds32(src + 512 + g * 4);
+            const __half2 dd = __half2half2(half ? __high2half(bits_h2(sc2)) : __low2half(bits_h2(sc2)));
 #pragma unroll
-          for (uint32_t b = 0; b < 2; b++) {
-            const uint4 w = lds128(src + b * 544 + lane * 16);
-            const uint32_t sc = lds32(src + b * 544 + 512 + g * 4);
-            const __half2 dl = __half2half2(__low2half(bits_h2(sc))), dh = __half2half2(__high2half(bits_h2(sc)));
-            const uint32_t dst = hi0 + (b * 4 + t) * A_LBO;
-            const uint32_t words[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
-            uint32_t hi[8], lo[8];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-              const __half2 dd = i < 2 ? dl : dh;
-              dq2(__byte_perm(words[i], 0x64646464u, 0x4140), zp, dd, hi[2 * i], lo[2 * i]);
-              dq2(__byte_perm(words[i], 0x64646464u, 0x4342), zp, dd, hi[2 * i + 1], lo[2 * i + 1]);
+            for (int t = 0; t < 4; t++) {  // values 8t .. 8t+7
+              const uint2 w = lds64(src + (g * 4 + t) * 16 + half * 8);
+              const uint32_t w0 = w.x ^ 0x80808080u, w1 = w.y ^ 0x80808080u;
+              dq2(__byte_perm(w0, 0x64646464u, 0x4140), zp, dd, v[4 * t + 0], v[16 + 4 * t + 0]);
+              dq2(__byte_perm(w0, 0x64646464u, 0x4342), zp, dd, v[4 * t + 1], v[16 + 4 * t + 1]);
+              dq2(__byte_perm(w1, 0x64646464u, 0x4140), zp, dd, v[4 * t + 2], v[16 + 4 * t + 2]);
+              dq2(__byte_perm(w1, 0x64646464u, 0x4342), zp, dd, v[4 * t + 3], v[16 + 4 * t + 3]);
             }
-            sts128(dst, hi[0], hi[1], hi[2], hi[3]);
-            sts128(dst + A_TERM, lo[0], lo[1], lo[2], lo[3]);
-            sts128(dst + 128, hi[4], hi[5], hi[6], hi[7]);
-            sts128(dst + 128 + A_TERM, lo[4], lo[5], lo[6], lo[7]);
-          }
-        } else {
-          // one block-pair record: words = (slot g, blk 0), (slot g+8, blk 0), (slot g, blk 1), (slot g+8, blk 1);
-          // byte i of a word holds values 4t+i (low nibble) and 16+4t+i (high nibble) of its block
-          const uint4 w = lds128(src + lane * 16);
-          const uint2 sc = lds64(src + 512 + g * 8);
-          const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+          } else {
+            // block-pair record: 16 bytes per (g, t) = words (slot g, blk 0), (slot g+8, blk 0), (slot g, blk 1), (slot g+8, blk 1);
+            // byte i of a word holds values 4t+i (low nibble) and 16+4t+i (high nibble) of its block
+            const uint32_t src = tile_src + (sub >> 1) * 576, blk = sub & 1;
+            const uint32_t sc2 = lds32(src + 512 + g * 8 + blk * 4);
+            const __half2 dd = __half2half2(half ? __high2half(bits_h2(sc2)) : __low2half(bits_h2(sc2)));
 #pragma unroll
-          for (int i = 0; i < 4; i++) {
-            const uint32_t blk = i >> 1, half = i & 1;
-            const uint32_t sbits = blk == 0 ? sc.x : sc.y;
-            const __half2 dd = __half2half2(half == 0 ? __low2half(bits_h2(sbits)) : __high2half(bits_h2(sbits)));
-            const uint32_t lows = words[i] & 0x0F0F0F0Fu, highs = (words[i] >> 4) & 0x0F0F0F0Fu;
-            uint32_t h0, l0, h1, l1;
-            // values 4t..4t+3 sit in core-matrix column blk*4 + t/2, at byte (t & 1) * 8 of the row's 16 bytes
-            const uint32_t dst = hi0 + half * 128 + (blk * 4 + (t >> 1)) * A_LBO + (t & 1) * 8;
-            dq2(__byte_perm(lows, 0x64646464u, 0x4140), zp, dd, h0, l0);
-            dq2(__byte_perm(lows, 0x64646464u, 0x4342), zp, dd, h1, l1);
-            sts64(dst, h0, h1);
-            sts64(dst + A_TERM, l0, l1);
-            dq2(__byte_perm(highs, 0x64646464u, 0x4140), zp, dd, h0, l0);
-            dq2(__byte_perm(highs, 0x64646464u, 0x4342), zp, dd, h1, l1);
-            sts64(dst + 2 * A_LBO, h0, h1);  // values 16 + 4t.. : two core-matrix columns further
-            sts64(dst + 2 * A_LBO + A_TERM, l0, l1);
+            for (int t = 0; t < 4; t++) {
+              const uint32_t w = lds32(src + (g * 4 + t) * 16 + (blk * 2 + half) * 4);
+              const uint32_t lows = w & 0x0F0F0F0Fu, highs = (w >> 4) & 0x0F0F0F0Fu;
+              dq2(__byte_perm(lows, 0x64646464u, 0x4140), zp, dd, v[2 * t + 0], v[16 + 2 * t + 0]);
+              dq2(__byte_perm(lows, 0x64646464u, 0x4342), zp, dd, v[2 * t + 1], v[16 + 2 * t + 1]);
+              dq2(__byte_perm(highs, 0x64646464u, 0x4140), zp, dd, v[8 + 2 * t + 0], v[24 + 2 * t + 0]);
+              dq2(__byte_perm(highs, 0x64646464u, 0x4342), zp, dd, v[8 + 2 * t + 1], v[24 + 2 * t + 1]);
+            }
+          }
+          tc_st32(tmem_base + ((q * 32u) << 16) + TMEM_A0 + (gblk % A_STAGES) * A_STAGE_COLS, v);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(&a_full[(gblk / GROUP) & 1]);
+            if (sub + 2 >= RAW_BLOCKS) mbar_arrive(&raw_empty[raw.stage]);  // this warp's last block of the stage
           }
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA's reads
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&a_full[ra.stage]);
-          mbar_arrive(&raw_empty[raw.stage]);
-        }
-        raw.advance(), ra.advance();
+        gblk++;
+        if (sub == RAW_BLOCKS - 1) raw.advance();
       }
     }
     if (!ok && lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
@@ -312,7 +347,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     const uint32_t q = warp & 3;  // a warp reads the TMEM lanes 32 * (warp % 4) ..
     const uint32_t row = q * 32 + lane;  // row of the item's 128-row tile
     uint32_t used = 0;
-    for (uint32_t item = item_beg; item < item_end && ok; item++) {
+    for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
       const uint32_t pass = item / m_tiles, mt = item % m_tiles;
       const uint32_t pstart = d.pass_start[pass], pcount = d.pass_count[pass];
       const bool resident = expert_base(pass) != nullptr;
@@ -452,16 +487,16 @@ __global__ void __launch_bounds__(256) k_gemm_act_image(MoeDispatch d, int phase
 }
 
 struct GemmPlan {
-  uint32_t n_raw, n_a, n_b, b_lbo;
+  uint32_t n_raw, n_b, b_lbo;
   size_t smem;
 };
 
 GemmPlan gemm_plan(int dtype, uint32_t bn) {
-  const uint32_t tcb = 2 * 16 * (dtype == MER_DTYPE_Q4_0 ? MER_Q4_BLOCK_BYTES : MER_Q8_BLOCK_BYTES);
+  const uint32_t tile_raw = RAW_BLOCKS * 16 * (dtype == MER_DTYPE_Q4_0 ? MER_Q4_BLOCK_BYTES : MER_Q8_BLOCK_BYTES);
   GemmPlan pl{};
   pl.b_lbo = bn * 16 + 32;
-  pl.n_raw = 4, pl.n_a = 2, pl.n_b = 3;
-  pl.smem = G_HEADER + (size_t)pl.n_raw * 8 * tcb + (size_t)pl.n_a * 2 * A_TERM + (size_t)pl.n_b * 16 * pl.b_lbo;
+  pl.n_raw = 3, pl.n_b = 5;
+  pl.smem = G_HEADER + (size_t)pl.n_raw * 8 * tile_raw + (size_t)pl.n_b * 16 * pl.b_lbo;
   return pl;
 }
 
@@ -538,7 +573,7 @@ cudaError_t launch_ffn_gemm(MoeDispatch &d, void *gemm_scratch_ptr, size_t gemm_
     p.d = d, p.phase = phase, p.act_img = gs.img, p.unscale = gs.unscale;
     p.rows = phase == 0 ? d.F : d.D;
     p.kb_total = K / 32;
-    p.bn = bn, p.b_lbo = pl.b_lbo, p.n_raw = pl.n_raw, p.n_a = pl.n_a, p.n_b = pl.n_b;
+    p.bn = bn, p.b_lbo = pl.b_lbo, p.n_raw = pl.n_raw, p.n_b = pl.n_b;
     p.out = phase == 0 ? d.h : d.y;
     kern<<<sm_count, G_THREADS, pl.smem, s>>>(p);
     if (phase == 0 && ev_mid) cudaEventRecord(ev_mid, s);
