@@ -38,6 +38,8 @@ struct MoeDispatch {
   uint32_t *group_expert;   // [n_groups]
   uint32_t *offsets;        // [n_groups + 1]
   uint32_t *perm;           // [P]
+  uint32_t *group_count;    // [n_groups] zero between dispatches: per-group pair counts of the grid-wide grouping,
+  uint32_t *group_cursor;   //   and its scatter cursors (both null: always group in one CTA)
   float *h;                 // [P x F]   silu(gate) * up
   float *y;                 // [P x D]   per-pair expert outputs
   float *out;               // [n_tokens x D]

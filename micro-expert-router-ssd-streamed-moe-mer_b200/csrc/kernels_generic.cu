@@ -86,7 +86,8 @@ constexpr int ROUTER_THREADS = 256;
 constexpr int ROUTER_ROWS = ROUTER_THREADS / 32;  // expert rows per CTA
 constexpr int ROUTER_TT = 4;                      // tokens per CTA
 constexpr uint32_t SMALL_P = 4096;                // pair keys staged in shared memory below this many pairs
-constexpr uint32_t STABLE_G = 512;                // stable (token, slot)-ordered grouping up to this many groups
+constexpr uint32_t STABLE_G = 512;
+constexpr uint32_t GRID_GROUPING_PAIRS = 8192;    // from this many pairs the grouping runs grid-wide (count / scan / scatter)                // stable (token, slot)-ordered grouping up to this many groups
 
 // Cuts every group into passes of at most d.tokens_per_pass pairs (the unit the streaming FFN works
 // on) and clears the per-pair max cells.  One CTA of 256 threads; `off` = the group offsets.
@@ -127,6 +128,68 @@ __device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
     }
   }
   if (threadIdx.x == 0) *d.n_passes = s_pcnt[256];
+}
+
+// Group of pair p: local expert index, the shared-expert group, or MER_NONE for an unfilled / foreign slot.
+__device__ __forceinline__ uint32_t pair_group_key(const RouterDev &r, const MoeDispatch &d, uint32_t p) {
+  const uint32_t e = __ldcg(d.pair_expert + p);
+  if (e == MER_NONE) return MER_NONE;
+  if ((p % d.slots) >= r.top_k) return r.num_experts;  // shared-expert slot
+  return e - r.id_base;
+}
+
+// Grouping of a large dispatch in three grid-wide steps (count, scan, scatter) instead of one CTA.  The order of
+// the pairs inside a group is whatever the atomics give; every pair's result is independent of its position.
+__global__ void __launch_bounds__(256) k_group_count(RouterDev r, MoeDispatch d) {
+  const uint32_t P = d.n_tokens * d.slots;
+  for (uint32_t p = blockIdx.x * blockDim.x + threadIdx.x; p < P; p += gridDim.x * blockDim.x) {
+    const uint32_t k = pair_group_key(r, d, p);
+    if (k != MER_NONE) atomicAdd(d.group_count + k, 1u);
+  }
+}
+__global__ void __launch_bounds__(256) k_group_scan(RouterDev r, MoeDispatch d) {
+  const uint32_t G = d.n_groups;
+  for (uint32_t g = threadIdx.x; g < G; g += blockDim.x) d.group_expert[g] = (g < r.num_experts) ? r.id_base + g : r.shared_expert_id;
+  // the counts go through shared memory in slabs: one thread adds them up, everybody loads and stores
+  __shared__ uint32_t s_cnt[1024];
+  __shared__ uint32_t s_run;
+  if (threadIdx.x == 0) s_run = 0;
+  for (uint32_t g0 = 0; g0 < G; g0 += 1024) {
+    const uint32_t n = min(1024u, G - g0);
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+      s_cnt[i] = d.group_count[g0 + i];
+      d.group_count[g0 + i] = 0;  // zero again for the next dispatch's count
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t acc = s_run;
+      for (uint32_t i = 0; i < n; i++) {
+        const uint32_t c = s_cnt[i];
+        s_cnt[i] = acc;
+        acc += c;
+      }
+      s_run = acc;
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) d.offsets[g0 + i] = s_cnt[i];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) d.offsets[G] = s_run;
+  __threadfence_block();
+  __syncthreads();
+  if (d.pass_group) build_passes_block(d, d.offsets);
+}
+__global__ void __launch_bounds__(256) k_group_scatter(RouterDev r, MoeDispatch d) {
+  const uint32_t P = d.n_tokens * d.slots;
+  for (uint32_t p = blockIdx.x * blockDim.x + threadIdx.x; p < P; p += gridDim.x * blockDim.x) {
+    const uint32_t k = pair_group_key(r, d, p);
+    if (k != MER_NONE) d.perm[d.offsets[k] + atomicAdd(d.group_cursor + k, 1u)] = p;
+  }
+}
+// Clears the scatter cursors after use, so that group_count / group_cursor are zero between dispatches.
+__global__ void k_group_clear(MoeDispatch d) {
+  for (uint32_t g = threadIdx.x; g < d.n_groups; g += blockDim.x) d.group_cursor[g] = 0;
 }
 
 // Runs in one CTA after every token has been routed: groups pairs by expert.
@@ -366,7 +429,74 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
   }
 }
 
-__global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispatch d, uint32_t max_tokens) {
+// Router logits of a large batch as a tiled fp32 GEMM: logits[t][e] = x[t] . w[e].  A CTA of 128 threads computes
+// 32 tokens x 64 experts through shared memory in K chunks of 64 (the next chunk's global loads are in flight while
+// the current one is multiplied), a thread 4 tokens x 4 experts (8 shared loads per 64 FMAs).  k_router then runs
+// with `pre` set and only scores / selects.
+constexpr int RL_TT = 32, RL_TE = 64, RL_KC = 64, RL_LD = 68, RL_THREADS = 128;  // row stride 68 floats: conflict-free 128-bit loads
+__global__ void __launch_bounds__(RL_THREADS) k_router_logits_tiled(RouterDev r, MoeDispatch d) {
+  __shared__ __align__(16) float xs[RL_TT][RL_LD];
+  __shared__ __align__(16) float ws[RL_TE][RL_LD];
+  const uint32_t E = r.num_experts, D = d.D, T = d.n_tokens;
+  const uint32_t t0 = blockIdx.y * RL_TT, e0 = blockIdx.x * RL_TE;
+  const uint32_t tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+  const uint32_t lr = tid >> 4, lc = (tid & 15) * 4;  // this thread's float4 of an 8-row x 64-column slab
+  const float *xrow[4], *wrow[8];
+#pragma unroll
+  for (int i = 0; i < 4; i++) xrow[i] = d.x + (size_t)min(t0 + 8 * i + lr, T - 1) * D + lc;
+#pragma unroll
+  for (int j = 0; j < 8; j++) wrow[j] = r.w + (size_t)min(e0 + 8 * j + lr, E - 1) * D + lc;
+  float4 xv[4], wv[8];
+#pragma unroll
+  for (int i = 0; i < 4; i++) xv[i] = __ldg(reinterpret_cast<const float4 *>(xrow[i]));
+#pragma unroll
+  for (int j = 0; j < 8; j++) wv[j] = __ldg(reinterpret_cast<const float4 *>(wrow[j]));
+  for (uint32_t k0 = 0; k0 < D; k0 += RL_KC) {
+    __syncthreads();  // the previous chunk has been consumed
+#pragma unroll
+    for (int i = 0; i < 4; i++) *reinterpret_cast<float4 *>(&xs[8 * i + lr][lc]) = xv[i];
+#pragma unroll
+    for (int j = 0; j < 8; j++) *reinterpret_cast<float4 *>(&ws[8 * j + lr][lc]) = wv[j];
+    __syncthreads();
+    if (k0 + RL_KC < D) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) xv[i] = __ldg(reinterpret_cast<const float4 *>(xrow[i] + k0 + RL_KC));
+#pragma unroll
+      for (int j = 0; j < 8; j++) wv[j] = __ldg(reinterpret_cast<const float4 *>(wrow[j] + k0 + RL_KC));
+    }
+#pragma unroll 4
+    for (int k = 0; k < RL_KC; k += 4) {
+      float4 a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) a[i] = *reinterpret_cast<const float4 *>(&xs[ty * 4 + i][k]);
+#pragma unroll
+      for (int j = 0; j < 4; j++) b[j] = *reinterpret_cast<const float4 *>(&ws[tx + 16 * j][k]);
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
+          acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
+          acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
+          acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+        }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const uint32_t t = t0 + ty * 4 + i, e = e0 + tx + 16 * j;
+      if (t < T && e < E) d.logits[(size_t)t * E + e] = acc[i][j];
+    }
+}
+
+__global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispatch d, uint32_t max_tokens, int pre, int group_here) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const uint32_t E = r.num_experts, D = d.D;
   const uint32_t tile = blockIdx.y, t0 = tile * ROUTER_TT;
@@ -375,9 +505,11 @@ __global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispa
   const uint32_t e0 = blockIdx.x * ROUTER_ROWS;
   __shared__ float s_part[ROUTER_ROWS][ROUTER_TT][ROUTER_ROWS + 1];  // [row][token][warp]
   __shared__ float s_logit[ROUTER_TT][ROUTER_ROWS];                  // used when one CTA covers all experts
-  const bool single = gridDim.x == 1;
+  const bool single = gridDim.x == 1 && !pre;
 
-  if ((D & 1023u) == 0) {
+  if (pre) {
+    // logits are already in d.logits (k_router_logits_tiled)
+  } else if ((D & 1023u) == 0) {
     const uint32_t slice4 = D / 4 / ROUTER_ROWS;  // float4 per warp slice
     float acc[ROUTER_ROWS][ROUTER_TT];
 #pragma unroll
@@ -445,7 +577,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispa
   }
   __shared__ uint32_t s_flag;
   __syncthreads();
-  if (!single) {
+  if (!single && !pre) {
     if (threadIdx.x == 0) {
       __threadfence();
       uint32_t prev = atomicAdd(&d.counters[tile], 1u);
@@ -469,6 +601,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispa
     __syncwarp();
     route_token(r, d, token, s_score, s_sel, s_ok, s_groups[warp], s_gscore[warp]);
   }
+  if (!group_here) return;  // a large dispatch is grouped by the grid-wide kernels that follow
   __syncthreads();
   const uint32_t n_tiles = gridDim.y;
   if (n_tiles > 1) {
@@ -723,9 +856,24 @@ cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max
     cudaError_t e = cudaFuncSetAttribute(k_router, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  dim3 grid((E + ROUTER_ROWS - 1) / ROUTER_ROWS, (d.n_tokens + ROUTER_TT - 1) / ROUTER_TT);
-  k_router<<<grid, ROUTER_THREADS, smem, s>>>(r, d, max_tokens);
+  const bool tiled = d.n_tokens >= 128 && (d.D % RL_KC) == 0;  // large batches: logits as a tiled GEMM first
+  if (tiled) {
+    dim3 lgrid((E + RL_TE - 1) / RL_TE, (d.n_tokens + RL_TT - 1) / RL_TT);
+    k_router_logits_tiled<<<lgrid, RL_THREADS, 0, s>>>(r, d);
+    if (launches) (*launches)++;
+  }
+  dim3 grid(tiled ? 1 : (E + ROUTER_ROWS - 1) / ROUTER_ROWS, (d.n_tokens + ROUTER_TT - 1) / ROUTER_TT);
+  const bool grid_grouping = P >= GRID_GROUPING_PAIRS && d.group_count != nullptr;
+  k_router<<<grid, ROUTER_THREADS, smem, s>>>(r, d, max_tokens, tiled ? 1 : 0, grid_grouping ? 0 : 1);
   if (launches) (*launches)++;
+  if (grid_grouping) {
+    const unsigned blocks = (P + 1023) / 1024;
+    k_group_count<<<blocks, 256, 0, s>>>(r, d);
+    k_group_scan<<<1, 256, 0, s>>>(r, d);
+    k_group_scatter<<<blocks, 256, 0, s>>>(r, d);
+    k_group_clear<<<1, 256, 0, s>>>(d);
+    if (launches) (*launches) += 4;
+  }
   return cudaGetLastError();
 }
 

@@ -68,7 +68,7 @@ struct mer_backend {
   uint32_t max_pairs = 0;
   float *d_x = nullptr, *d_out = nullptr, *d_h = nullptr, *d_y = nullptr, *d_pair_weight = nullptr, *d_logits = nullptr;
   uint32_t *d_pair_expert = nullptr, *d_group_expert = nullptr, *d_offsets = nullptr, *d_perm = nullptr;
-  uint32_t *d_status = nullptr, *d_counters = nullptr;
+  uint32_t *d_status = nullptr, *d_counters = nullptr, *d_group_count = nullptr;  // d_group_count: [2 x max_groups]
   uint16_t *d_f16 = nullptr;
   void *d_stream_scratch = nullptr;
   void *d_gemm_scratch = nullptr;  // activation operand images of the tensor-core GEMM path
@@ -154,6 +154,8 @@ MoeDispatch base_dispatch(mer_backend *b) {
   d.group_expert = b->d_group_expert;
   d.offsets = b->d_offsets;
   d.perm = b->d_perm;
+  d.group_count = b->d_group_count;
+  d.group_cursor = b->d_group_count ? b->d_group_count + b->max_groups : nullptr;
   d.h = b->d_h;
   d.y = b->d_y;
   d.status = b->d_status;
@@ -293,7 +295,7 @@ void free_all(mer_backend *b) {
   }
   b->routers.clear();
   F(b->arena), F(b->d_expert_ptr), F(b->d_x), F(b->d_out), F(b->d_h), F(b->d_y), F(b->d_pair_weight), F(b->d_logits);
-  F(b->d_pair_expert), F(b->d_group_expert), F(b->d_offsets), F(b->d_perm), F(b->d_status), F(b->d_counters);
+  F(b->d_pair_expert), F(b->d_group_expert), F(b->d_offsets), F(b->d_perm), F(b->d_status), F(b->d_counters), F(b->d_group_count);
   F(b->d_f16), F(b->d_stream_scratch), F(b->d_gemm_scratch), F(b->d_dequant), F(b->d_raw_stage);
   H(b->h_expert_ptr), H(b->h_stage[0]), H(b->h_stage[1]), H(b->h_hdr), H(b->h_u32), H(b->h_f32);
   if (b->ev_compute_done) cudaEventDestroy(b->ev_compute_done);
@@ -577,6 +579,8 @@ MER_EXPORT int mer_backend_create(const mer_backend_cfg *cfg, mer_backend **out)
   CB(cudaMalloc((void **)&b->d_pair_expert, P * 4));
   CB(cudaMalloc((void **)&b->d_group_expert, (size_t)b->max_groups * 4));
   CB(cudaMalloc((void **)&b->d_offsets, ((size_t)b->max_groups + 1) * 4));
+  CB(cudaMalloc((void **)&b->d_group_count, (size_t)b->max_groups * 2 * 4));
+  CB(cudaMemset(b->d_group_count, 0, (size_t)b->max_groups * 2 * 4));
   CB(cudaMalloc((void **)&b->d_perm, P * 4));
   CB(cudaMalloc((void **)&b->d_logits, T * b->max_router_experts * 4));
   CB(cudaMalloc((void **)&b->d_status, 4));

@@ -219,11 +219,18 @@ def test_router_nonfinite_scores():
         assert e.value.kind == Kind.Numerical
 
 
-@pytest.mark.parametrize("cfg", ["softmax-128x8", "sigmoid-groups-256x8", "softmax-8x2"])
+@pytest.mark.parametrize("cfg", ["softmax-128x8", "sigmoid-groups-256x8", "softmax-8x2", "softmax-128x8-large-batch",
+                                 "softmax-10x3-ragged-large-batch"])
 def test_router_matches_oracle_on_random_inputs(cfg):
     rng = np.random.default_rng(17)
     if cfg == "softmax-128x8":
         E, D, k, B = 128, 2048, 8, 64
+        args = dict()
+    elif cfg == "softmax-128x8-large-batch":  # 128 tokens and more: logits come from the tiled GEMM kernel
+        E, D, k, B = 128, 1024, 8, 300
+        args = dict()
+    elif cfg == "softmax-10x3-ragged-large-batch":  # expert and token counts that do not fill the tiles
+        E, D, k, B = 10, 96, 3, 131
         args = dict()
     elif cfg == "softmax-8x2":
         E, D, k, B = 8, 4096, 2, 16
