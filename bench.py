@@ -162,6 +162,9 @@ def cpu_layer_rate(oracle, cfg, layer, x, threads, seconds, steps=None, warmup=1
 
 def main():
     args = parse_args()
+    # Libraries (NCCL's version banner, for one) write to stdout; the JSON line must be the only thing there.
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -198,7 +201,8 @@ def main():
                     cpu_baseline={"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
                     e2e={"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                     note="the reference is Rust and cannot be built here; this is the C restatement of its CPU kernels (oracle/)")
-        print(json.dumps(line))
+        json_out.write(json.dumps(line) + "\n")
+        json_out.flush()
         return
 
     import torch
@@ -397,7 +401,8 @@ def main():
         threads = os.cpu_count() or 1
         rate, ms, sample = cpu_layer_rate(oracle, cfg, keep_for_cpu, x_cpu, threads, args.cpu_seconds)
         line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
-    print(json.dumps(line))
+    json_out.write(json.dumps(line) + "\n")
+    json_out.flush()
     if world > 1:
         dist.destroy_process_group()
 

@@ -50,6 +50,7 @@ struct MoeDispatch {
   uint32_t scratch_pairs;   // pair capacity the streaming scratch was sized for
   uint32_t max_group_tokens;  // upper bound on the pairs of any one group in this dispatch
   uint32_t active_groups_hint;  // expected number of non-empty groups (shapes the work split)
+  uint32_t expected_pairs;      // expected number of pairs that reach a group (0 = all of them; fewer under expert parallelism)
   // token passes of the streaming FFN (null when the generic kernels run): groups cut into runs of at most
   // tokens_per_pass pairs, built by the grouping kernels; amax = per-pair max |h| cell, zeroed there too
   uint32_t *pass_group, *pass_start, *pass_count, *n_passes, *amax;

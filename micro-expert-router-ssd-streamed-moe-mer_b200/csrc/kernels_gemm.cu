@@ -538,7 +538,7 @@ size_t gemm_ffn_scratch_bytes(uint32_t max_tokens, uint32_t max_pairs, uint32_t 
 uint32_t gemm_pick_bn(const MoeDispatch &d, uint32_t min_mean_tokens) {
   const uint64_t P = (uint64_t)d.n_tokens * d.slots;
   const uint32_t groups = d.active_groups_hint ? d.active_groups_hint : 1;
-  const uint64_t mean = P / groups;
+  const uint64_t mean = (d.expected_pairs ? d.expected_pairs : P) / groups;
   if (mean < min_mean_tokens) return 0;
   uint32_t bn = mean <= 12 ? 16 : mean <= 24 ? 32 : mean <= 56 ? 64 : 128;
   const uint64_t gmax = d.n_groups < P ? d.n_groups : P;

@@ -1017,6 +1017,8 @@ int ep_run_local_experts(mer_backend *b, uint32_t layer, const RouterDev &r, Moe
   d.n_groups = r.num_experts + shared;
   d.max_group_tokens = d.n_tokens;
   d.active_groups_hint = std::min(b->ep.experts_per_rank + shared, d.n_tokens * d.slots);
+  // of all ranks' pairs, about one in `world` lands on a local expert (the shared expert takes the rank's own tokens)
+  d.expected_pairs = std::max<uint32_t>(1u, d.n_tokens * d.slots / b->ep.world);
   bind_ffn(b, d);
   CU(MER_ERR_SUBMISSION, "group kernel", launch_groups_layer(r, d, s, launches));
   CU(MER_ERR_SUBMISSION, "expert FFN kernels", run_ffn(b, d, s, launches));
