@@ -38,7 +38,8 @@
 namespace {
 
 constexpr int CONSUMER_WARPS = 16;
-constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;  // + one producer warp
+constexpr int PRODUCER_WARPS = 2;  // each issues the bulk copies of half a stage's tiles: one warp alone was busy ~90 % of the time
+constexpr int THREADS = (CONSUMER_WARPS + PRODUCER_WARPS) * 32;
 constexpr uint32_t HEADER_BYTES = 1024;  // mbarriers and per-pass token tables at the start of shared memory
 constexpr float POW2_24 = 16777216.0f;
 
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < p.n_stages; s++) {
-      mbar_init(&full[s], 1);
+      mbar_init(&full[s], PRODUCER_WARPS);
       mbar_init(&empty[s], CONSUMER_WARPS);
     }
     *s_abort = 0;
@@ -169,8 +170,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
     kbn = min(p.kb_split, p.kb_total - kb0);
   };
 
-  if (warp == CONSUMER_WARPS) {
-    // ------------------------------ producer warp: lane m copies the chunk of tile m of every stage
+  if (warp >= CONSUMER_WARPS) {
+    // ------------------------------ producer warps: warp h, lane m < 8 copies the chunk of tile 8h + m of every stage
+    constexpr uint32_t TILES_PER_PRODUCER = CONSUMER_WARPS / PRODUCER_WARPS;
+    const uint32_t my_tile = (warp - CONSUMER_WARPS) * TILES_PER_PRODUCER + (lane % TILES_PER_PRODUCER);
     uint32_t stage = 0, round = 0;
     bool ok = true;
     for (uint32_t item = item_beg; item < item_end && ok; item++, next_item()) {
@@ -180,17 +183,17 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
       const uint8_t *base = (eid < d.max_experts) ? d.expert_ptr[eid] : nullptr;
       if (!base) continue;  // consumers skip the same item
       // item -> packed tiles 16*tile .. 16*tile + 15 of the phase's region; lane m < 16 copies tile m's chunk
-      const uint8_t *src = base + (p.phase == 0 ? 0 : 2 * proj_bytes) + (size_t)(CONSUMER_WARPS * tile + (lane & 15)) * tile_bytes;
+      const uint8_t *src = base + (p.phase == 0 ? 0 : 2 * proj_bytes) + (size_t)(CONSUMER_WARPS * tile + my_tile) * tile_bytes;
       for (uint32_t c0 = 0; c0 < kbn && ok; c0 += p.kc) {
         uint32_t nb = min(p.kc, kbn - c0);
         if (round > 0) ok = mbar_wait(&empty[stage], (round - 1) & 1);
         if (*(volatile uint32_t *)s_abort) ok = false;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (lane == 0) mbar_expect_tx(&full[stage], CONSUMER_WARPS * nb * 16 * BB);
+        if (lane == 0) mbar_expect_tx(&full[stage], TILES_PER_PRODUCER * nb * 16 * BB);
         __syncwarp();
-        if (lane < CONSUMER_WARPS)
-          bulk_g2s(s_stage + (size_t)stage * stage_bytes + lane * p.chunk_stride, src + (size_t)(kb0 + c0) * 16 * BB, nb * 16 * BB,
+        if (lane < TILES_PER_PRODUCER)
+          bulk_g2s(s_stage + (size_t)stage * stage_bytes + my_tile * p.chunk_stride, src + (size_t)(kb0 + c0) * 16 * BB, nb * 16 * BB,
                    &full[stage]);
         if (++stage == p.n_stages) stage = 0, round++;
       }

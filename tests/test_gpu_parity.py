@@ -183,6 +183,25 @@ def test_nan_activation_propagates():
         assert np.isnan(b.expert_forward_f32(0, 0, x)).all()
 
 
+@pytest.mark.parametrize("dtype", [oracle.Q8_0, oracle.Q4_0])
+def test_streaming_kernels_clamp_and_nan_rows_when_k_is_split(dtype):
+    # 64 blocks of K and few work items: the gate/up phase splits K across CTAs, so SiLU(gate)*up (with the clamp)
+    # is applied to the summed partials by the finalize kernel
+    D, F, n = 2048, 512, 5
+    blob = random_blob(dtype, D, F, 19)
+    x = synth.make_activations(n, D, 19) * 6.0
+    x[3, 100] = np.nan
+    with backend(dtype, D, F, max_tokens=8, swiglu_limit=0.3) as b:
+        b.admit(0, 1, blob)
+        b.set_kernel_path(2)
+        got = b.expert_forward_f32(0, 0, x)
+    assert np.isnan(got[3]).all()
+    for t in (0, 1, 2, 4):
+        ref = oracle.expert_forward(dtype, blob, x[t], D, F, swiglu_limit=0.3)
+        assert rel_rms_err(got[t], ref) <= FFN_TOL
+        assert rel_rms_err(oracle.expert_forward(dtype, blob, x[t], D, F), ref) > 0.01  # the clamp matters here
+
+
 # ------------------------------------------------------------------------------- router
 
 def _golden_gate(c):
