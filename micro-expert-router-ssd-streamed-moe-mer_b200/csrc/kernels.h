@@ -57,6 +57,8 @@ struct MoeDispatch {
   uint32_t tokens_per_pass;
   const float *y_parts;     // set by the streaming FFN: K-split partials [y_nparts][P x D] of the per-pair outputs,
   uint32_t y_nparts;        //   or null / 1 when `y` already holds them
+  int fuse_combine;         // in: a weighted combine into `out` follows the expert FFN; the FFN launch may do it itself
+  int combined;             // out: it did (launch_combine then does nothing)
   uint32_t gemm_bn;         // > 0: the tcgen05 GEMM path runs this dispatch with passes of gemm_bn tokens
   int packed;               // 1: slots hold the tile-major fragment layout (layout.cuh), 0: the flat block stream
 };

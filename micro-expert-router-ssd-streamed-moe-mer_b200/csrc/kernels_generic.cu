@@ -127,7 +127,10 @@ __device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
       np++;
     }
   }
-  if (threadIdx.x == 0) *d.n_passes = s_pcnt[256];
+  if (threadIdx.x == 0) {
+    d.n_passes[0] = s_pcnt[256];
+    d.n_passes[1] = d.n_passes[2] = 0;  // arrival counters of the streaming kernels' grid-wide barriers
+  }
 }
 
 // Group of pair p: local expert index, the shared-expert group, or MER_NONE for an unfilled / foreign slot.
@@ -912,6 +915,7 @@ cudaError_t launch_ffn_generic(const MoeDispatch &d, cudaStream_t s, int *launch
 }
 
 cudaError_t launch_combine(const MoeDispatch &d, cudaStream_t s, int *launches) {
+  if (d.combined) return cudaSuccess;  // the expert FFN launch already did it
   dim3 grid((d.D + 255) / 256, d.n_tokens);
   k_combine<<<grid, 256, 0, s>>>(d);
   if (launches) (*launches)++;

@@ -43,6 +43,8 @@ constexpr int THREADS = (CONSUMER_WARPS + PRODUCER_WARPS) * 32;
 constexpr uint32_t HEADER_BYTES = 1024;  // mbarriers and per-pass token tables at the start of shared memory
 constexpr float POW2_24 = 16777216.0f;
 
+constexpr int TAIL_NONE = 0, TAIL_FINALIZE = 1, TAIL_COMBINE = 2;
+
 struct StreamParams {
   MoeDispatch d;
   int phase;                 // 0 = gate/up (+SiLU*mul), 1 = down
@@ -59,6 +61,10 @@ struct StreamParams {
   uint32_t frag_stride;      // bytes between (token, part) fragment arrays in shared memory
   float *out;                // phase 0: h [P x F], or gate/up partials [n_ksplit][P][2][F] when K is split;
                              // phase 1: y partials [n_ksplit][P x D]
+  int tail;                  // work done by the whole grid after a grid-wide barrier (cooperative launch):
+                             // TAIL_FINALIZE (phase 0, K split): h = SiLU(sum gate) * sum up and the row maxima;
+                             // TAIL_COMBINE (phase 1): out[token] = weighted sum of its pairs' outputs in slot order
+  uint32_t *grid_counter;    // arrival counter of that barrier, zeroed by the grouping kernel
 };
 
 // D = A * B + C with separate C so that a seed / zero needs no register moves.
@@ -118,7 +124,7 @@ struct BlockBytes {
 
 // --------------------------------------------------------------------------- main kernel
 template <int DT, int NT>
-__global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
+__device__ __forceinline__ void ffn_stream_body(const StreamParams &p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr uint32_t BB = BlockBytes<DT>::value;
   constexpr uint32_t TP = 4 * NT;
@@ -455,6 +461,104 @@ __global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
   }
 }
 
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Grid-wide barrier of a cooperative launch: every CTA arrives once; waits are bounded by wall-clock time.
+__device__ bool grid_barrier(uint32_t *counter, uint32_t *status) {
+  __shared__ int s_ok;
+  __syncthreads();  // this CTA's stores are issued
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(counter, 1u);
+    const uint64_t t0 = global_ns();
+    bool ok = true;
+    while (*(volatile uint32_t *)counter < gridDim.x) {
+      __nanosleep(64);
+      if (global_ns() - t0 > 2000000000ull) {
+        ok = false;
+        break;
+      }
+    }
+    __threadfence();
+    if (!ok) atomicOr(status, MER_DEVSTAT_TIMEOUT);
+    s_ok = ok;
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+// After all CTAs have left their partial sums: the same arithmetic as k_h_finalize / k_combine, spread over the grid.
+__device__ void ffn_stream_tail(const StreamParams &p) {
+  const MoeDispatch &d = p.d;
+  if (!grid_barrier(p.grid_counter, d.status)) return;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t P = d.n_tokens * d.slots;
+  if (p.tail == TAIL_FINALIZE) {
+    const float *parts = p.out;
+    const uint32_t F = d.F, fchunks = (F + 127) / 128;
+    const uint32_t gw = blockIdx.x * (THREADS / 32) + warp, nw = gridDim.x * (THREADS / 32);
+    for (uint32_t u = gw; u < P * fchunks; u += nw) {  // a warp: 128 consecutive values of one pair's row
+      const uint32_t pair = u / fchunks, f0 = (u % fchunks) * 128 + lane * 4;
+      float mx = 0.0f;
+      if (f0 < F) {
+        float4 g = make_float4(0, 0, 0, 0), up = make_float4(0, 0, 0, 0);
+        for (uint32_t k = 0; k < p.n_ksplit; k++) {
+          const float *base = parts + ((size_t)k * P + pair) * 2 * F;
+          const float4 a = __ldcg(reinterpret_cast<const float4 *>(base + f0)), b = __ldcg(reinterpret_cast<const float4 *>(base + F + f0));
+          g.x += a.x, g.y += a.y, g.z += a.z, g.w += a.w;
+          up.x += b.x, up.y += b.y, up.z += b.z, up.w += b.w;
+        }
+        const float gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {up.x, up.y, up.z, up.w};
+        float hv[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          float gate = gv[i];
+          if (d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit) && gate == gate) gate = fminf(fmaxf(gate, -d.swiglu_limit), d.swiglu_limit);
+          hv[i] = __fdividef(gate, 1.0f + __expf(-gate)) * uv[i];
+          mx = nan_max(mx, fabsf(hv[i]));
+        }
+        *reinterpret_cast<float4 *>(d.h + (size_t)pair * F + f0) = make_float4(hv[0], hv[1], hv[2], hv[3]);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if (lane == 0) atomicMax(d.amax + pair, (mx != mx) ? 0x7fc00000u : __float_as_uint(mx));
+    }
+  } else if (p.tail == TAIL_COMBINE) {
+    const uint32_t D4 = d.D / 4;
+    const float4 *yp = reinterpret_cast<const float4 *>(p.n_ksplit > 1 ? p.out : d.y);
+    const size_t part4 = (size_t)P * D4;
+    for (uint32_t e = blockIdx.x * THREADS + threadIdx.x; e < d.n_tokens * D4; e += gridDim.x * THREADS) {
+      const uint32_t token = e / D4, i4 = e % D4;
+      float4 acc = make_float4(0, 0, 0, 0);
+      for (uint32_t sl = 0; sl < d.slots; sl++) {
+        const size_t pr = (size_t)token * d.slots + sl;
+        const float w = d.pair_weight[pr];
+        if (d.pair_expert[pr] == MER_NONE || w == 0.0f) continue;
+        float4 yv = __ldcg(yp + pr * D4 + i4);
+        for (uint32_t k = 1; k < p.n_ksplit; k++) {
+          const float4 t = __ldcg(yp + (size_t)k * part4 + pr * D4 + i4);
+          yv.x += t.x, yv.y += t.y, yv.z += t.z, yv.w += t.w;
+        }
+        acc.x = __fadd_rn(acc.x, __fmul_rn(w, yv.x));
+        acc.y = __fadd_rn(acc.y, __fmul_rn(w, yv.y));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(w, yv.z));
+        acc.w = __fadd_rn(acc.w, __fmul_rn(w, yv.w));
+      }
+      reinterpret_cast<float4 *>(d.out)[(size_t)token * D4 + i4] = acc;
+    }
+  }
+}
+
+template <int DT, int NT>
+__global__ void __launch_bounds__(THREADS, 1) k_ffn_stream(StreamParams p) {
+  ffn_stream_body<DT, NT>(p);
+  if (p.tail != TAIL_NONE) ffn_stream_tail(p);
+}
+
 // h = SiLU(clamp(sum of gate partials)) * (sum of up partials), partials added in K-split order, plus the
 // row maximum of |h| that the down phase scales its activations by.  grid = (pairs, ceil(F / 1024)).
 __global__ void __launch_bounds__(256) k_h_finalize(const float *__restrict__ parts, uint32_t n_ksplit, uint32_t n_pairs, uint32_t F,
@@ -499,7 +603,7 @@ struct Plan {
   size_t smem;
 };
 
-constexpr size_t SMEM_LIMIT = 227 * 1024;
+constexpr size_t SMEM_LIMIT = 226 * 1024;  // 227 KB per CTA less the kernel's static shared memory
 constexpr uint32_t MAX_KSPLIT = 64;
 
 // Shapes one phase.  An item is 16 tiles (one per warp) over one K split.
@@ -587,16 +691,16 @@ ScratchLayout scratch_layout(uint32_t max_pairs, uint32_t D, uint32_t F) {
 
 template <int DT>
 cudaError_t launch_phase(const StreamParams &p, uint32_t nt, size_t smem, int grid, cudaStream_t s) {
-  cudaError_t e;
-  if (nt == 2) {
-    e = cudaFuncSetAttribute(k_ffn_stream<DT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    k_ffn_stream<DT, 2><<<grid, THREADS, smem, s>>>(p);
-  } else {
-    e = cudaFuncSetAttribute(k_ffn_stream<DT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    k_ffn_stream<DT, 1><<<grid, THREADS, smem, s>>>(p);
+  void (*kern)(StreamParams) = nt == 2 ? k_ffn_stream<DT, 2> : k_ffn_stream<DT, 1>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  if (p.tail != TAIL_NONE) {
+    // the tail waits for every CTA of the grid: a cooperative launch guarantees that they are all resident
+    StreamParams q = p;
+    void *args[] = {&q};
+    return cudaLaunchCooperativeKernel((const void *)kern, dim3(grid), dim3(THREADS), args, smem, s);
   }
+  kern<<<grid, THREADS, smem, s>>>(p);
   return cudaGetLastError();
 }
 
@@ -666,23 +770,42 @@ cudaError_t launch_ffn_stream(MoeDispatch &d, void *scratch, int sm_count, cudaS
   p.rows = d.F, p.kb_total = d.D / 32, p.kb_split = pg.kb_split, p.n_ksplit = pg.n_ksplit, p.kc = pg.kc;
   p.n_stages = pg.n_stages, p.chunk_stride = pg.chunk_stride, p.frag_stride = pg.frag_stride, p.frag_cols = pg.frag_cols;
   p.out = pg.n_ksplit > 1 ? parts : d.h;
-  e = d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, pg.smem, sm_count, s)
-                                : launch_phase<MER_DTYPE_Q8_0>(p, nt, pg.smem, sm_count, s);
+  auto launch = [&](size_t smem) {
+    return d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, smem, sm_count, s)
+                                     : launch_phase<MER_DTYPE_Q8_0>(p, nt, smem, sm_count, s);
+  };
+  // K split: the partial sums are finished (SiLU(gate) * up, row maxima) by the same launch after a grid-wide barrier;
+  // where a cooperative launch is refused, by a second kernel
+  p.tail = pg.n_ksplit > 1 ? TAIL_FINALIZE : TAIL_NONE, p.grid_counter = d.n_passes + 1;
+  e = launch(pg.smem);
+  if (e != cudaSuccess && p.tail != TAIL_NONE) {
+    cudaGetLastError();
+    p.tail = TAIL_NONE;
+    e = launch(pg.smem);
+    if (e == cudaSuccess) {
+      k_h_finalize<<<dim3(P, (d.F + 1023) / 1024), 256, 0, s>>>(parts, pg.n_ksplit, P, d.F, d.swiglu_limit, d.h, d.amax);
+      e = cudaGetLastError();
+      n++;
+    }
+  }
   if (e != cudaSuccess) return e;
   n++;
-  if (pg.n_ksplit > 1) {
-    k_h_finalize<<<dim3(P, (d.F + 1023) / 1024), 256, 0, s>>>(parts, pg.n_ksplit, P, d.F, d.swiglu_limit, d.h, d.amax);
-    if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    n++;
-  }
   if (ev_mid) cudaEventRecord(ev_mid, s);
   // phase 1: down, activations = h by pair, scaled by the row maxima collected above
   p.phase = 1, p.act = d.h, p.act_per_pair = 1;
   p.rows = d.D, p.kb_total = d.F / 32, p.kb_split = pd.kb_split, p.n_ksplit = pd.n_ksplit, p.kc = pd.kc;
   p.n_stages = pd.n_stages, p.chunk_stride = pd.chunk_stride, p.frag_stride = pd.frag_stride, p.frag_cols = pd.frag_cols;
   p.out = pd.n_ksplit > 1 ? parts : d.y;
-  e = d.dtype == MER_DTYPE_Q4_0 ? launch_phase<MER_DTYPE_Q4_0>(p, nt, pd.smem, sm_count, s)
-                                : launch_phase<MER_DTYPE_Q8_0>(p, nt, pd.smem, sm_count, s);
+  // the weighted combine of the layer rides on the same launch when the caller asked for it
+  p.tail = d.fuse_combine ? TAIL_COMBINE : TAIL_NONE, p.grid_counter = d.n_passes + 2;
+  d.combined = 0;
+  e = launch(pd.smem);
+  if (e == cudaSuccess && p.tail == TAIL_COMBINE) d.combined = 1;
+  if (e != cudaSuccess && p.tail != TAIL_NONE) {
+    cudaGetLastError();
+    p.tail = TAIL_NONE;
+    e = launch(pd.smem);
+  }
   if (e != cudaSuccess) return e;
   n++;
   // the per-pair outputs are the K-split partials until somebody adds them: the combine kernel does, or

@@ -200,6 +200,7 @@ void bind_ffn(mer_backend *b, MoeDispatch &d) {
 
 cudaError_t run_ffn(mer_backend *b, MoeDispatch &d, cudaStream_t s, int *launches, cudaEvent_t ev_mid = nullptr) {
   d.y_parts = nullptr, d.y_nparts = 1;
+  d.combined = 0;
   if (d.gemm_bn)
     return launch_ffn_gemm(d, b->d_gemm_scratch, b->gemm_scratch_bytes, b->cfg.max_tokens, b->sm_count, s, launches, ev_mid);
   if (use_stream_path(b, d)) return launch_ffn_stream(d, b->d_stream_scratch, b->sm_count, s, launches, ev_mid);
@@ -455,6 +456,7 @@ int dispatch_given_routing(mer_backend *b, uint32_t layer, MoeDispatch &d, const
   bind_ffn(b, d);
   CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, b->compute));
   CU(MER_ERR_SUBMISSION, "group kernel", launch_groups_from_pairs(d, b->compute, launches));
+  d.fuse_combine = combine_follows ? 1 : 0;
   CU(MER_ERR_SUBMISSION, "expert FFN kernels", run_ffn(b, d, b->compute, launches));
   if (!combine_follows) CU(MER_ERR_SUBMISSION, "partial-sum kernel", launch_reduce_parts(d, b->compute, launches));
   return MER_OK;
@@ -743,6 +745,7 @@ int enqueue_layer(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tok
   CU(MER_ERR_SUBMISSION, "router kernel", launch_router(r, d, b->cfg.max_tokens, s, launches));
   if (run_ffn_too) {
     if (ev) cudaEventRecord(ev[1], s);
+    d.fuse_combine = 1;
     CU(MER_ERR_SUBMISSION, "expert FFN kernels", run_ffn(b, d, s, launches, ev ? ev[2] : nullptr));
     if (ev) cudaEventRecord(ev[3], s);
     CU(MER_ERR_SUBMISSION, "combine kernel", launch_combine(d, s, launches));
