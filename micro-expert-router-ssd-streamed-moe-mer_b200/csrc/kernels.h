@@ -9,6 +9,7 @@
 #define MER_Q4_BLOCK_BYTES 18
 #define MER_Q8_BLOCK_BYTES 34
 #define MER_NONE 0xFFFFFFFFu
+#define MER_MAX_CTAS1 257  /* per-phase stride of MoeDispatch::item_bounds: up to 256 CTAs + 1 */
 
 // Router parameters resident on the device (one per installed layer).
 struct RouterDev {
@@ -55,6 +56,11 @@ struct MoeDispatch {
   // tokens_per_pass pairs, built by the grouping kernels; amax = per-pair max |h| cell, zeroed there too
   uint32_t *pass_group, *pass_start, *pass_count, *n_passes, *amax;
   uint32_t tokens_per_pass;
+  // Work split of the streaming kernels, built with the passes: item_bounds[phase * MER_MAX_CTAS1 + b] = first item of
+  // CTA b in that phase (b = 0 .. n_ctas), items weighted by the tokens of their pass (null: the GEMM path).
+  uint32_t *item_bounds;
+  uint32_t items_per_pass[2];  // items per pass in the gate/up and the down phase (K splits x tile groups)
+  uint32_t n_ctas;
   const float *y_parts;     // set by the streaming FFN: K-split partials [y_nparts][P x D] of the per-pair outputs,
   uint32_t y_nparts;        //   or null / 1 when `y` already holds them
   int fuse_combine;         // in: a weighted combine into `out` follows the expert FFN; the FFN launch may do it itself

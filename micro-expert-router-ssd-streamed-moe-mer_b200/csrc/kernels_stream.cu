@@ -158,7 +158,9 @@ __device__ __forceinline__ void ffn_stream_body(const StreamParams &p) {
   const uint32_t n_tiles = p.rows / ((p.phase == 0 ? 8u : 16u) * CONSUMER_WARPS);  // items per (pass, K split)
   const uint32_t n_passes = *d.n_passes;
   const uint64_t n_items = (uint64_t)n_passes * p.n_ksplit * n_tiles;
-  const uint32_t item_beg = (uint32_t)(n_items * blockIdx.x / gridDim.x), item_end = (uint32_t)(n_items * (blockIdx.x + 1) / gridDim.x);
+  // the grouping kernel cut the item list into one contiguous range per CTA, balanced by the tokens of the passes
+  const uint32_t *bounds = d.item_bounds + p.phase * MER_MAX_CTAS1 + blockIdx.x;
+  const uint32_t item_beg = min((uint32_t)n_items, bounds[0]), item_end = min((uint32_t)n_items, bounds[1]);
   if (item_beg >= item_end) return;
   const size_t proj_bytes = (size_t)d.D * d.F / 32 * BB;
   const size_t tile_bytes = (size_t)p.kb_total * 16 * BB;  // one packed 16-row tile, all of K
@@ -658,7 +660,7 @@ Plan make_plan(int dtype, uint32_t kb_total, uint32_t packed_tiles, uint32_t nt,
 }
 
 struct ScratchLayout {
-  size_t amax, npass, pgroup, pstart, pcount, parts, parts_bytes, total;
+  size_t amax, npass, pgroup, pstart, pcount, bounds, parts, parts_bytes, total;
 };
 
 // `parts` holds the K-split partial sums of whichever phase is running: gate/up partials
@@ -676,6 +678,7 @@ ScratchLayout scratch_layout(uint32_t max_pairs, uint32_t D, uint32_t F) {
   L.pgroup = take((size_t)max_pairs * 4);
   L.pstart = take((size_t)max_pairs * 4);
   L.pcount = take((size_t)max_pairs * 4);
+  L.bounds = take((size_t)2 * MER_MAX_CTAS1 * 4);
   // room for 8 splits of the largest batch, but never less than 64 splits of an 8-pair dispatch, capped at 1 GiB
   const size_t per_pair = (size_t)(2 * F > D ? 2 * F : D) * 4;
   size_t want = (size_t)8 * max_pairs * per_pair;
@@ -742,6 +745,7 @@ Plans plan_dispatch(const MoeDispatch &d, int sm_count) {
 }  // namespace
 
 void stream_bind(MoeDispatch &d, void *scratch, int sm_count) {
+  if (sm_count > MER_MAX_CTAS1 - 1) sm_count = MER_MAX_CTAS1 - 1;
   uint8_t *base = static_cast<uint8_t *>(scratch);
   const ScratchLayout L = scratch_layout(d.scratch_pairs, d.D, d.F);
   d.n_passes = reinterpret_cast<uint32_t *>(base + L.npass);
@@ -749,10 +753,16 @@ void stream_bind(MoeDispatch &d, void *scratch, int sm_count) {
   d.pass_start = reinterpret_cast<uint32_t *>(base + L.pstart);
   d.pass_count = reinterpret_cast<uint32_t *>(base + L.pcount);
   d.amax = reinterpret_cast<uint32_t *>(base + L.amax);
-  d.tokens_per_pass = 4 * plan_dispatch(d, sm_count).nt;
+  const Plans pl = plan_dispatch(d, sm_count);
+  d.tokens_per_pass = 4 * pl.nt;
+  d.item_bounds = reinterpret_cast<uint32_t *>(base + L.bounds);
+  d.items_per_pass[0] = pl.gate_up.n_ksplit * (d.F / 8 / CONSUMER_WARPS);
+  d.items_per_pass[1] = pl.down.n_ksplit * (d.D / 16 / CONSUMER_WARPS);
+  d.n_ctas = (uint32_t)sm_count;
 }
 
 cudaError_t launch_ffn_stream(MoeDispatch &d, void *scratch, int sm_count, cudaStream_t s, int *launches, cudaEvent_t ev_mid) {
+  if (sm_count > MER_MAX_CTAS1 - 1) sm_count = MER_MAX_CTAS1 - 1;  // the per-CTA work split holds at most 256 ranges
   const uint32_t P = d.n_tokens * d.slots;
   uint8_t *base = static_cast<uint8_t *>(scratch);
   const ScratchLayout L = scratch_layout(d.scratch_pairs, d.D, d.F);
