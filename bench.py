@@ -370,8 +370,8 @@ def main():
                     "traffic": ncu_traffic(f"{args.workload}-b{B}"), "algorithmic_bytes_per_launch": kernel_bytes,
                     "avg_launch_ms": gu_ms, "frac_of_8tbs": achieved / 8000.0 if achieved else None}
         stages = {k: v / n for k, v in st.items() if k != "samples"}
-        if B * slots >= 12 * n_exp and not fused and gu_ms > 0:
-            # a dozen tokens per expert and more: the tcgen05 GEMM kernels run, bounded by the tensor pipe.
+        if B * slots >= 32 * n_exp and not fused and gu_ms > 0:
+            # a mean of 32 tokens per expert and more: the tcgen05 GEMM kernels run, bounded by the tensor pipe.
             # Algorithmic FLOPs of the gate/up launch: every (token, slot) pair through two [F x D] projections.
             tpeak, tkind = measured_tensor_peak()
             flops = 2.0 * B * slots * 2 * cfg.d_model * cfg.d_ff

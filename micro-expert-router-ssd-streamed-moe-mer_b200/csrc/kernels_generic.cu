@@ -926,7 +926,7 @@ cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max
     cudaError_t e = cudaFuncSetAttribute(k_router, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  const bool tiled = d.n_tokens >= 128 && (d.D % RL_KC) == 0;  // large batches: logits as a tiled GEMM first
+  const bool tiled = d.n_tokens >= 1024 && (d.D % RL_KC) == 0;  // large batches: logits as a tiled GEMM first (below: too few tiles to fill the SMs)
   if (tiled) {
     dim3 lgrid((E + RL_TE - 1) / RL_TE, (d.n_tokens + RL_TT - 1) / RL_TT);
     k_router_logits_tiled<<<lgrid, RL_THREADS, 0, s>>>(r, d);

@@ -43,7 +43,7 @@ def test_one_expert_many_tokens_matches_oracle(dtype, D, F, n_tokens):
 
 
 def test_automatic_selection_takes_the_gemm_path_for_large_groups():
-    dtype, E, D, F, k, B = oracle.Q8_0, 8, 512, 256, 2, 96  # 192 pairs over 8 experts: 24 tokens per expert
+    dtype, E, D, F, k, B = oracle.Q8_0, 8, 512, 256, 2, 160  # 320 pairs over 8 experts: 40 tokens per expert
     blobs = [synth.make_expert_blob(dtype, D, F, 82, 0, e) for e in range(E)]
     W = synth.make_router(E, D, 82)
     x = synth.make_activations(B, D, 82)

@@ -245,11 +245,11 @@ def test_router_matches_oracle_on_random_inputs(cfg):
     if cfg == "softmax-128x8":
         E, D, k, B = 128, 2048, 8, 64
         args = dict()
-    elif cfg == "softmax-128x8-large-batch":  # 128 tokens and more: logits come from the tiled GEMM kernel
-        E, D, k, B = 128, 1024, 8, 300
+    elif cfg == "softmax-128x8-large-batch":  # 1024 tokens and more: logits come from the tiled GEMM kernel
+        E, D, k, B = 128, 512, 8, 1100
         args = dict()
     elif cfg == "softmax-10x3-ragged-large-batch":  # expert and token counts that do not fill the tiles
-        E, D, k, B = 10, 96, 3, 131
+        E, D, k, B = 10, 128, 3, 1027
         args = dict()
     elif cfg == "softmax-8x2":
         E, D, k, B = 8, 4096, 2, 16
