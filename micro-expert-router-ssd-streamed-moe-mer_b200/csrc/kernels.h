@@ -65,6 +65,7 @@ struct MoeDispatch {
   uint32_t y_nparts;        //   or null / 1 when `y` already holds them
   int fuse_combine;         // in: a weighted combine into `out` follows the expert FFN; the FFN launch may do it itself
   int combined;             // out: it did (launch_combine then does nothing)
+  int fuse_reduce;          // in: the caller wants final per-pair outputs in `y` for the grouped pairs (no K-split partials left)
   uint32_t gemm_bn;         // > 0: the tcgen05 GEMM path runs this dispatch with passes of gemm_bn tokens
   int packed;               // 1: slots hold the tile-major fragment layout (layout.cuh), 0: the flat block stream
 };
@@ -86,7 +87,6 @@ struct EpDev {
 // kernels_ep.cu
 cudaError_t launch_ep_filter(const EpDev &ep, const uint32_t *ids_all, const float *w_all, uint32_t n_pairs, uint32_t slots,
                              uint32_t *pair_expert, float *pair_weight, cudaStream_t s, int *launches);
-cudaError_t launch_ep_signal(const EpDev &ep, uint32_t epoch, cudaStream_t s, int *launches);
 cudaError_t launch_ep_gather(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, float *x_all, uint32_t *pair_expert,
                              float *pair_weight, uint32_t *status, cudaStream_t s, int *launches);
 cudaError_t launch_ep_combine(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, const uint32_t *ids, const float *w,
@@ -95,7 +95,9 @@ cudaError_t launch_ep_combine(const EpDev &ep, uint32_t epoch, uint32_t D, uint3
 // kernels_generic.cu
 // Groups pairs by expert for a whole layer whose routing is already in d.pair_expert (+ pass table).
 cudaError_t launch_groups_layer(const RouterDev &r, const MoeDispatch &d, cudaStream_t s, int *launches);
-cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max_tokens, cudaStream_t s, int *launches);
+// group = false: route only (the caller groups later, e.g. after gathering other ranks' tokens)
+cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max_tokens, cudaStream_t s, int *launches,
+                          bool group = true);
 cudaError_t launch_groups_from_pairs(const MoeDispatch &d, cudaStream_t s, int *launches);
 cudaError_t launch_ffn_generic(const MoeDispatch &d, cudaStream_t s, int *launches, cudaEvent_t ev_mid);
 cudaError_t launch_combine(const MoeDispatch &d, cudaStream_t s, int *launches);

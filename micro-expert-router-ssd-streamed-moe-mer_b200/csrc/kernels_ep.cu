@@ -4,7 +4,9 @@
 //       outputs) and this file only filters the gathered routing down to the local experts;
 //   (2) the ranks exchange through peer memory: every rank publishes its tokens, routing and
 //       per-pair expert outputs in an exchange buffer the other ranks have mapped; a rank pulls
-//       the rows it needs with plain peer loads (no TMA, no multicast) after a flag barrier.
+//       the rows it needs with plain peer loads (no TMA, no multicast) after a flag barrier (the
+//       first CTA of the gather / combine kernel raises this rank's flag on every peer, all CTAs
+//       wait for the flags of the ranks they read).
 // Every wait on a peer is bounded by wall-clock time; on expiry the kernel latches
 // MER_DEVSTAT_TIMEOUT and carries on without the peer's data (the host then fails the call).
 #include "../../include/mer_b200.h"
@@ -56,9 +58,9 @@ __global__ void k_ep_filter(EpDev ep, const uint32_t *__restrict__ ids_all, cons
   pair_weight[p] = local ? w_all[p] : 0.0f;
 }
 
-// (2a) Tells every peer that this rank's exchange buffer holds the data of `epoch`.
-// Runs after the kernels that wrote the data (stream order), so the data is in this GPU's memory.
-__global__ void k_ep_signal(EpDev ep, uint32_t epoch) {
+// (2a) Tells every peer that this rank's exchange buffer holds the data of `epoch`.  Called by the first CTA of the
+// kernel that follows the kernels which wrote the data (stream order: the data is in this GPU's memory by then).
+__device__ __forceinline__ void ep_signal(const EpDev &ep, uint32_t epoch) {
   const uint32_t j = threadIdx.x;
   if (j >= ep.world) return;
   __threadfence_system();
@@ -73,6 +75,7 @@ __global__ void __launch_bounds__(256) k_ep_gather(EpDev ep, uint32_t epoch, uin
                                                    uint32_t *status) {
   const uint32_t src = blockIdx.y, t = blockIdx.x;
   __shared__ int s_ok, s_any;
+  if (blockIdx.x == 0 && blockIdx.y == 0) ep_signal(ep, epoch);  // this rank's tokens and routing are published
   if (threadIdx.x == 0) {
     const uint32_t *flags = reinterpret_cast<const uint32_t *>(ep.peer[ep.rank] + ep.off_flags);
     s_ok = wait_flag(flags + src, epoch, ep.wait_ns);
@@ -103,12 +106,15 @@ __global__ void __launch_bounds__(256) k_ep_gather(EpDev ep, uint32_t epoch, uin
 
 // (2c) out[t] = sum over slots, in slot order, of weight * y, where y of a pair is read from the
 // exchange buffer of the rank that owns the pair's expert (same order and rounding as k_combine).
+// One CTA per token, a thread four consecutive values.
 __global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, uint32_t epoch, uint32_t D, uint32_t slots,
                                                     const uint32_t *__restrict__ ids, const float *__restrict__ w,
                                                     float *__restrict__ out, uint32_t *status) {
-  const uint32_t t = blockIdx.y;
-  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t t = blockIdx.x;
   __shared__ int s_ok;
+  __shared__ const float *s_row[64];
+  __shared__ float s_w[64];
+  if (blockIdx.x == 0) ep_signal(ep, epoch);  // this rank's expert outputs are published
   if (threadIdx.x < 32) {
     // lanes share the ranks to wait for
     const uint32_t *flags = reinterpret_cast<const uint32_t *>(ep.peer[ep.rank] + ep.off_flags);
@@ -121,21 +127,37 @@ __global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, uint32_t epoch, ui
       if (!ok) atomicOr(status, MER_DEVSTAT_TIMEOUT);
     }
   }
-  __syncthreads();
-  if (i >= D) return;
-  float acc = 0.0f;
-  if (s_ok) {
-    const uint32_t tg = ep.rank * ep.tokens_per_rank + t;
-    for (uint32_t s = 0; s < slots; s++) {
-      const uint32_t e = ids[t * slots + s];
-      const float wt = w[t * slots + s];
-      if (e == MER_NONE || wt == 0.0f) continue;
-      const uint32_t owner = s >= ep.top_k ? ep.rank : (e - ep.id_base) / ep.experts_per_rank;
-      const float *y = reinterpret_cast<const float *>(ep.peer[owner] + ep.off_y) + ((size_t)tg * slots + s) * D;
-      acc = __fadd_rn(acc, __fmul_rn(wt, __ldcg(y + i)));
+  // where each slot's row lives (null = skipped slot), resolved once per token
+  const uint32_t tg = ep.rank * ep.tokens_per_rank + t;
+  if (threadIdx.x >= 32 && threadIdx.x < 32 + slots && threadIdx.x < 96) {
+    const uint32_t sl = threadIdx.x - 32;
+    const uint32_t e = ids[t * slots + sl];
+    const float wt = w[t * slots + sl];
+    const float *row = nullptr;
+    if (e != MER_NONE && wt != 0.0f) {
+      const uint32_t owner = sl >= ep.top_k ? ep.rank : (e - ep.id_base) / ep.experts_per_rank;
+      row = reinterpret_cast<const float *>(ep.peer[owner] + ep.off_y) + ((size_t)tg * slots + sl) * D;
     }
+    s_row[sl] = row;
+    s_w[sl] = wt;
   }
-  out[(size_t)t * D + i] = acc;
+  __syncthreads();
+  for (uint32_t i4 = threadIdx.x; i4 < D / 4; i4 += blockDim.x) {
+    float4 acc = make_float4(0, 0, 0, 0);
+    if (s_ok) {
+      for (uint32_t sl = 0; sl < slots; sl++) {
+        const float *row = s_row[sl];
+        if (!row) continue;
+        const float wt = s_w[sl];
+        const float4 y = __ldcg(reinterpret_cast<const float4 *>(row) + i4);
+        acc.x = __fadd_rn(acc.x, __fmul_rn(wt, y.x));
+        acc.y = __fadd_rn(acc.y, __fmul_rn(wt, y.y));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(wt, y.z));
+        acc.w = __fadd_rn(acc.w, __fmul_rn(wt, y.w));
+      }
+    }
+    reinterpret_cast<float4 *>(out)[(size_t)t * (D / 4) + i4] = acc;
+  }
 }
 
 }  // namespace
@@ -143,12 +165,6 @@ __global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, uint32_t epoch, ui
 cudaError_t launch_ep_filter(const EpDev &ep, const uint32_t *ids_all, const float *w_all, uint32_t n_pairs, uint32_t slots,
                              uint32_t *pair_expert, float *pair_weight, cudaStream_t s, int *launches) {
   k_ep_filter<<<(n_pairs + 255) / 256, 256, 0, s>>>(ep, ids_all, w_all, n_pairs, slots, pair_expert, pair_weight);
-  if (launches) (*launches)++;
-  return cudaGetLastError();
-}
-
-cudaError_t launch_ep_signal(const EpDev &ep, uint32_t epoch, cudaStream_t s, int *launches) {
-  k_ep_signal<<<1, 64, 0, s>>>(ep, epoch);
   if (launches) (*launches)++;
   return cudaGetLastError();
 }
@@ -163,8 +179,7 @@ cudaError_t launch_ep_gather(const EpDev &ep, uint32_t epoch, uint32_t D, uint32
 
 cudaError_t launch_ep_combine(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, const uint32_t *ids, const float *w,
                               float *out, uint32_t *status, cudaStream_t s, int *launches) {
-  dim3 grid((D + 255) / 256, ep.tokens_per_rank);
-  k_ep_combine<<<grid, 256, 0, s>>>(ep, epoch, D, slots, ids, w, out, status);
+  k_ep_combine<<<ep.tokens_per_rank, 256, 0, s>>>(ep, epoch, D, slots, ids, w, out, status);
   if (launches) (*launches)++;
   return cudaGetLastError();
 }

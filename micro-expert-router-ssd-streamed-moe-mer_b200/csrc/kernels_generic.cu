@@ -915,7 +915,7 @@ __global__ void k_f32_to_f16(const float *__restrict__ src, uint16_t *__restrict
 }  // namespace
 
 cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max_tokens, cudaStream_t s,
-                          int *launches) {
+                          int *launches, bool group) {
   const uint32_t E = r.num_experts, G = d.n_groups;
   const uint32_t P = d.n_tokens * d.slots;
   size_t smem_topk = (size_t)ROUTER_TT * E * 9;
@@ -933,8 +933,8 @@ cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max
     if (launches) (*launches)++;
   }
   dim3 grid(tiled ? 1 : (E + ROUTER_ROWS - 1) / ROUTER_ROWS, (d.n_tokens + ROUTER_TT - 1) / ROUTER_TT);
-  const bool grid_grouping = P >= GRID_GROUPING_PAIRS && d.group_count != nullptr;
-  k_router<<<grid, ROUTER_THREADS, smem, s>>>(r, d, max_tokens, tiled ? 1 : 0, grid_grouping ? 0 : 1);
+  const bool grid_grouping = group && P >= GRID_GROUPING_PAIRS && d.group_count != nullptr;
+  k_router<<<grid, ROUTER_THREADS, smem, s>>>(r, d, max_tokens, tiled ? 1 : 0, (group && !grid_grouping) ? 1 : 0);
   if (launches) (*launches)++;
   if (grid_grouping) {
     const unsigned blocks = (P + 1023) / 1024;

@@ -43,7 +43,7 @@ constexpr int THREADS = (CONSUMER_WARPS + PRODUCER_WARPS) * 32;
 constexpr uint32_t HEADER_BYTES = 1024;  // mbarriers and per-pass token tables at the start of shared memory
 constexpr float POW2_24 = 16777216.0f;
 
-constexpr int TAIL_NONE = 0, TAIL_FINALIZE = 1, TAIL_COMBINE = 2;
+constexpr int TAIL_NONE = 0, TAIL_FINALIZE = 1, TAIL_COMBINE = 2, TAIL_REDUCE = 3;
 
 struct StreamParams {
   MoeDispatch d;
@@ -63,7 +63,8 @@ struct StreamParams {
                              // phase 1: y partials [n_ksplit][P x D]
   int tail;                  // work done by the whole grid after a grid-wide barrier (cooperative launch):
                              // TAIL_FINALIZE (phase 0, K split): h = SiLU(sum gate) * sum up and the row maxima;
-                             // TAIL_COMBINE (phase 1): out[token] = weighted sum of its pairs' outputs in slot order
+                             // TAIL_COMBINE (phase 1): out[token] = weighted sum of its pairs' outputs in slot order;
+                             // TAIL_REDUCE (phase 1, K split): y[pair] = sum of its partials, grouped pairs only
   uint32_t *grid_counter;    // arrival counter of that barrier, zeroed by the grouping kernel
 };
 
@@ -552,6 +553,21 @@ __device__ void ffn_stream_tail(const StreamParams &p) {
       }
       reinterpret_cast<float4 *>(d.out)[(size_t)token * D4 + i4] = acc;
     }
+  } else if (p.tail == TAIL_REDUCE) {
+    // per-pair outputs of the pairs that ran here (under expert parallelism: a fraction of all pairs)
+    const uint32_t D4 = d.D / 4, n_here = d.offsets[d.n_groups];
+    const float4 *yp = reinterpret_cast<const float4 *>(p.out);
+    const size_t part4 = (size_t)P * D4;
+    for (uint32_t e = blockIdx.x * THREADS + threadIdx.x; e < n_here * D4; e += gridDim.x * THREADS) {
+      const size_t pr = d.perm[e / D4];
+      const uint32_t i4 = e % D4;
+      float4 yv = __ldcg(yp + pr * D4 + i4);
+      for (uint32_t k = 1; k < p.n_ksplit; k++) {
+        const float4 t = __ldcg(yp + (size_t)k * part4 + pr * D4 + i4);
+        yv.x += t.x, yv.y += t.y, yv.z += t.z, yv.w += t.w;
+      }
+      reinterpret_cast<float4 *>(d.y)[pr * D4 + i4] = yv;
+    }
   }
 }
 
@@ -807,10 +823,13 @@ cudaError_t launch_ffn_stream(MoeDispatch &d, void *scratch, int sm_count, cudaS
   p.n_stages = pd.n_stages, p.chunk_stride = pd.chunk_stride, p.frag_stride = pd.frag_stride, p.frag_cols = pd.frag_cols;
   p.out = pd.n_ksplit > 1 ? parts : d.y;
   // the weighted combine of the layer rides on the same launch when the caller asked for it
-  p.tail = d.fuse_combine ? TAIL_COMBINE : TAIL_NONE, p.grid_counter = d.n_passes + 2;
+  p.tail = d.fuse_combine ? TAIL_COMBINE : (d.fuse_reduce && pd.n_ksplit > 1) ? TAIL_REDUCE : TAIL_NONE;
+  p.grid_counter = d.n_passes + 2;
   d.combined = 0;
+  bool reduced = false;
   e = launch(pd.smem);
   if (e == cudaSuccess && p.tail == TAIL_COMBINE) d.combined = 1;
+  if (e == cudaSuccess && p.tail == TAIL_REDUCE) reduced = true;
   if (e != cudaSuccess && p.tail != TAIL_NONE) {
     cudaGetLastError();
     p.tail = TAIL_NONE;
@@ -820,7 +839,7 @@ cudaError_t launch_ffn_stream(MoeDispatch &d, void *scratch, int sm_count, cudaS
   n++;
   // the per-pair outputs are the K-split partials until somebody adds them: the combine kernel does, or
   // launch_reduce_parts for entry points that return per-pair outputs
-  d.y_parts = pd.n_ksplit > 1 ? parts : nullptr;
+  d.y_parts = (pd.n_ksplit > 1 && !reduced) ? parts : nullptr;
   d.y_nparts = pd.n_ksplit;
   if (launches) *launches += n;
   return cudaSuccess;

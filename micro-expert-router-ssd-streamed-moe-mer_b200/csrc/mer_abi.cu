@@ -1212,8 +1212,7 @@ MER_EXPORT int mer_ep_layer_forward_device(mer_backend *b, uint32_t layer, const
   dr.x = x_pub;
   dr.pair_expert = ids_pub;
   dr.pair_weight = w_own;
-  CU(MER_ERR_SUBMISSION, "router kernel", launch_router(r, dr, b->cfg.max_tokens, s, &launches));
-  CU(MER_ERR_SUBMISSION, "signal kernel", launch_ep_signal(ep, e1, s, &launches));
+  CU(MER_ERR_SUBMISSION, "router kernel", launch_router(r, dr, b->cfg.max_tokens, s, &launches, false));
   // pull the tokens that hit a local expert, run the local experts over them
   MoeDispatch d = base_dispatch(b);
   d.n_tokens = (uint32_t)(n_tokens * ep.world);
@@ -1222,10 +1221,10 @@ MER_EXPORT int mer_ep_layer_forward_device(mer_backend *b, uint32_t layer, const
   d.out = d_out;
   CU(MER_ERR_SUBMISSION, "gather kernel",
      launch_ep_gather(ep, e1, (uint32_t)D, slots, b->d_x, d.pair_expert, d.pair_weight, b->d_status, s, &launches));
+  d.fuse_reduce = 1;  // the peers read final per-pair outputs, and only those of the local experts exist
   int rc = ep_run_local_experts(b, layer, r, d, s, &launches);
   if (rc) return rc;
   CU(MER_ERR_SUBMISSION, "partial-sum kernel", launch_reduce_parts(d, s, &launches));
-  CU(MER_ERR_SUBMISSION, "signal kernel", launch_ep_signal(ep, e2, s, &launches));
   // weighted sum in slot order, every pair's output read from the rank that owns its expert
   CU(MER_ERR_SUBMISSION, "combine kernel",
      launch_ep_combine(ep, e2, (uint32_t)D, slots, ids_pub, w_own, d_out, b->d_status, s, &launches));
