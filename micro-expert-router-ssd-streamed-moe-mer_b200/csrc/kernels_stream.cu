@@ -639,12 +639,29 @@ Plan make_plan(int dtype, uint32_t kb_total, uint32_t packed_tiles, uint32_t nt,
   const uint64_t items_per_split = (uint64_t)active_groups * (packed_tiles / CONSUMER_WARPS);
   uint32_t n_ksplit = 1, kb_split = kb_total;
   if (max_ksplit > MAX_KSPLIT) max_ksplit = MAX_KSPLIT;
-  while (items_per_split * n_ksplit < (uint64_t)8 * n_ctas) {
-    const uint32_t next_split = ((kb_total + 2 * n_ksplit - 1) / (2 * n_ksplit) + 7) / 8 * 8;  // blocks per split if doubled
-    if (next_split < 16 || next_split >= kb_split) break;
-    const uint32_t next_n = (kb_total + next_split - 1) / next_split;
-    if (next_n > max_ksplit) break;
-    kb_split = next_split, n_ksplit = next_n;
+  // Pick the K split that minimises the busiest CTA's estimated time, in units of one block step (16 tiles x one
+  // block of K).  A CTA gets ceil(items / CTAs) items of kb_split block steps each, pays a fixed cost per item
+  // (epilogue) and one activation-fragment rebuild per (pass, K split) unit its contiguous range touches; a rebuild
+  // measures about 4 us, i.e. ~10 block steps of Q8_0 or ~20 of Q4_0 at the rate one SM streams.
+  {
+    const double rebuild = dtype == MER_DTYPE_Q4_0 ? 20.0 : 10.0, per_item = 2.0;
+    const uint32_t tile_groups = packed_tiles / CONSUMER_WARPS;
+    double best = 1e30;
+    uint32_t seen_split = 0;
+    for (uint32_t n = 1; n <= max_ksplit; n++) {
+      uint32_t split = ((kb_total + n - 1) / n + 7) / 8 * 8;
+      if (split > kb_total) split = kb_total;
+      if (n > 1 && split < 16) break;
+      if (split == seen_split) continue;  // same split as a smaller n
+      seen_split = split;
+      const uint32_t nn = (kb_total + split - 1) / split;
+      if (nn > max_ksplit) continue;
+      const uint64_t items = items_per_split * nn;
+      const double per_cta = (double)((items + n_ctas - 1) / n_ctas);
+      const double units = (per_cta - 1.0) / tile_groups + 1.0;
+      const double cost = per_cta * (split + per_item) + units * rebuild + 0.5 * nn;  // last term: partial sums, and ties go to fewer splits
+      if (cost < best) best = cost, kb_split = split, n_ksplit = nn;
+    }
   }
   // shared memory also bounds a split: the fragment arrays of one split must leave room for the ring
   for (;;) {
