@@ -220,7 +220,6 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     // -------------------------------------------------------------------------- MMA issuer
     // one step = one 32-value block of K: two instructions of 16 values for each of the three operand pairings
     Ring rb(p.n_b);
-    const uint32_t idesc = instr_desc(p.bn);
     uint32_t used = 0;  // items issued so far: buffer = used & 1, its k-th use has k = used >> 1
     uint32_t grp = 0;   // groups of GROUP blocks issued so far, over all items
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
@@ -228,6 +227,9 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
       if (!expert_base(pass)) continue;
       const uint32_t buf = used & 1, use = used >> 1;
       used++;
+      // the MMA is as wide as the pass has tokens (rounded up to 16 columns): a ragged last pass of a group costs
+      // its share, not a full tile
+      const uint32_t idesc = instr_desc(min(p.bn, (d.pass_count[pass] + 15u) & ~15u));
       if (lane == 0) {
         if (use > 0) ok = mbar_wait(&acc_empty[buf], (use - 1) & 1);
         tc_fence_after();
