@@ -135,6 +135,40 @@ def test_a_missing_local_expert_is_a_typed_residency_miss():
         b.close()
 
 
+def test_a_peer_that_never_answers_runs_the_bounded_wait_out():
+    # failure detection without a fault: rank 0 of a world of two whose "peer" is never driven.  Both exchange-buffer
+    # slots point at rank 0's own buffer, so nothing ever raises rank 1's flag: the gather and combine kernels give
+    # up after wait_ms, latch the timeout bit and return; the call fails typed and the backend stays usable.
+    import ctypes as C
+    dtype, E, D, F, k, B, layer = oracle.Q8_0, 8, 256, 256, 2, 3, 0
+    blobs = [synth.make_expert_blob(dtype, D, F, 65, 0, e) for e in range(E)]
+    W = synth.make_router(E, D, 65)
+    x = synth.make_activations(B, D, 65)
+    stride = (256 + mer_b200.expert_bytes(dtype, D, F) + 4095) // 4096 * 4096
+    b = mer_b200.Backend(dtype, D, F, stride * (E + 1), E, max_tokens=2 * B, max_top_k=k)
+    try:
+        for e in range(E):
+            b.admit(e, 1, blobs[e])
+        mer_b200.LinearGate(W, E, D, k).bind(b, layer)
+        ep = ExpertParallel(b, 0, 2, E, B, wait_ms=200)
+        own = b.lib.mer_ep_exchange_buffer(b.h)
+        bufs = (C.c_void_p * 2)(own, own)
+        b._check(b.lib.mer_ep_attach_pointers(b.h, bufs, 2))
+        dev = torch.device("cuda:0")
+        xd = torch.from_numpy(x).to(dev)
+        out = torch.empty(B, D, dtype=torch.float32, device=dev)
+        ep.layer_forward_peer(layer, xd.data_ptr(), B, out.data_ptr())
+        with pytest.raises(mer_b200.GpuExpertDispatchError) as e:
+            ep.check(layer)
+        assert e.value.kind == Kind.Timeout
+        # the context is intact: the plain single-GPU entry point still answers, and correctly
+        got, _, _ = b.moe_layer_forward(layer, x)
+        ref, _, _, _ = oracle.moe_layer_forward(dtype, oracle.LinearGate(W, E, D, k), blobs, x, F, n_threads=2)
+        assert rel_rms_err(got, ref) <= FFN_TOL
+    finally:
+        b.close()
+
+
 def test_ep_argument_validation():
     dtype, E, D, F, k, B = oracle.Q8_0, 8, 256, 256, 2, 4
     blobs = [synth.make_expert_blob(dtype, D, F, 64, 0, e) for e in range(E)]
