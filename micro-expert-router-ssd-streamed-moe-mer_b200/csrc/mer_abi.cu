@@ -907,6 +907,71 @@ MER_EXPORT int mer_moe_layer_forward(mer_backend *b, uint32_t layer, const float
   if (n_tokens == 0 || n_tokens > b->cfg.max_tokens)
     return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "n_tokens %zu outside 1..=%u", n_tokens, b->cfg.max_tokens);
   const size_t D = b->cfg.d_model;
+  // Pinned host buffers and no routing wanted back: upload, layer, read-back and the status word are captured once
+  // per (layer, n_tokens, x, out) and replayed as one graph launch (the call stays synchronous).
+  if (!ids && !weights && b->graphs_ok && !b->timing_on && !(b->cfg.flags & MER_FLAG_NO_GRAPHS) && b->routers.count(layer)) {
+    cudaPointerAttributes ax{}, ao{};
+    const bool pinned = cudaPointerGetAttributes(&ax, x) == cudaSuccess && ax.type == cudaMemoryTypeHost &&
+                        cudaPointerGetAttributes(&ao, out) == cudaSuccess && ao.type == cudaMemoryTypeHost;
+    cudaGetLastError();
+    if (pinned) {
+      cudaStream_t s = b->compute;
+      const void *host_tag = reinterpret_cast<const void *>(uintptr_t(1));  // marks host-entry graphs in the cache
+      CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, s));
+      mer_backend::GraphEntry *hit = nullptr;
+      for (auto &g : b->graphs)
+        if (g.layer == layer && g.n_tokens == n_tokens && g.x == x && g.out == out && g.ids == host_tag && g.stream == s) hit = &g;
+      if (!hit) {
+        if (b->graphs.size() >= 256) drop_graphs(b);
+        cudaGraph_t graph = nullptr;
+        cudaGraphExec_t exec = nullptr;
+        int launches = 0, rc = MER_OK;
+        bool ok = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+        if (ok) {
+          ok = cudaMemcpyAsync(b->d_x, x, n_tokens * D * 4, cudaMemcpyHostToDevice, s) == cudaSuccess;
+          MoeDispatch d;
+          if (ok) rc = enqueue_layer(b, layer, b->d_x, n_tokens, b->d_out, true, s, &launches, &d, true);
+          if (ok && rc == MER_OK) ok = cudaMemcpyAsync(out, b->d_out, n_tokens * D * 4, cudaMemcpyDeviceToHost, s) == cudaSuccess;
+          if (ok && rc == MER_OK)
+            ok = cudaMemcpyAsync(b->h_u32 + b->max_pairs, b->d_status, 4, cudaMemcpyDeviceToHost, s) == cudaSuccess;
+          cudaError_t ce = cudaStreamEndCapture(s, &graph);
+          ok = ok && ce == cudaSuccess && graph != nullptr;
+        }
+        if (rc != MER_OK) {
+          if (graph) cudaGraphDestroy(graph);
+          cudaGetLastError();
+          return rc;
+        }
+        if (ok) ok = cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
+        if (graph) cudaGraphDestroy(graph);
+        if (ok) {
+          b->graphs.push_back({layer, n_tokens, x, out, host_tag, nullptr, s, exec, launches});
+          hit = &b->graphs.back();
+        } else {
+          cudaGetLastError();
+          b->graphs_ok = false;  // capture is not available here: plain launches from now on
+        }
+      }
+      if (hit) {
+        const RouterDev &r = b->routers[layer].dev;
+        const size_t P = n_tokens * (r.top_k + (r.shared_expert_id != MER_NONE ? 1u : 0u));
+        CU(MER_ERR_SUBMISSION, "cudaGraphLaunch", cudaGraphLaunch(hit->exec, s));
+        CU(MER_ERR_READBACK_MAP, "cudaStreamSynchronize", cudaStreamSynchronize(s));
+        b->ctr.kernel_launches += (uint64_t)hit->launches;
+        b->ctr.selected_routed_experts += P;
+        b->ctr.gpu_dispatch_attempts += P;
+        b->ctr.hidden_upload_bytes += n_tokens * D * 4;
+        b->ctr.readback_bytes += n_tokens * D * 4;
+        int rc = check_device_status(b, b->h_u32[b->max_pairs], layer, expert);
+        if (rc && rc != MER_ERR_NUMERICAL) {
+          b->ctr.gpu_dispatch_failures += P;
+          return rc;
+        }
+        b->ctr.gpu_dispatch_successes += P;
+        return rc;
+      }
+    }
+  }
   CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(x)", cudaMemcpyAsync(b->d_x, x, n_tokens * D * 4, cudaMemcpyHostToDevice, b->compute));
   int launches = 0;
   MoeDispatch d;

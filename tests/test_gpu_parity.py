@@ -327,6 +327,40 @@ def test_layer_forward_is_invariant_to_batching_and_token_order():
             assert (step.view(np.uint32) == full[t].view(np.uint32)).all()
 
 
+def test_host_entry_with_pinned_buffers_equals_the_pageable_path():
+    # pinned x / out and no routing wanted back: the library replays one captured graph per (layer, n, x, out)
+    torch = pytest.importorskip("torch")
+    dtype, E, D, F, k, B = oracle.Q8_0, 16, 256, 256, 4, 9
+    blobs = [random_blob(dtype, D, F, 35, e) for e in range(E)]
+    W = synth.make_router(E, D, 35)
+    x = synth.make_activations(B, D, 35)
+    xp = torch.from_numpy(x.copy()).pin_memory()
+    op = torch.empty(B, D).pin_memory()
+    with backend(dtype, D, F, n_experts=E, max_tokens=16, max_top_k=k) as b:
+        for e in range(E):
+            b.admit(e, 1, blobs[e])
+        mer_b200.LinearGate(W, E, D, k).bind(b, 0)
+        plain, _, _ = b.moe_layer_forward(0, x)
+        before = b.snapshot()
+        for rep in range(3):  # first call captures, the others replay
+            op.zero_()
+            b.moe_layer_forward(0, xp.numpy(), return_routing=False, out=op.numpy())
+            assert (op.numpy().view(np.uint32) == plain.view(np.uint32)).all()
+        after = b.snapshot()
+        assert after["gpu_dispatch_successes"] - before["gpu_dispatch_successes"] == 3 * B * k
+        xp[2, 7] = 5.0  # new data in the same pinned buffer is picked up by the replay
+        b.moe_layer_forward(0, xp.numpy(), return_routing=False, out=op.numpy())
+        x2 = x.copy()
+        x2[2, 7] = 5.0
+        plain2, _, _ = b.moe_layer_forward(0, x2)
+        assert (op.numpy().view(np.uint32) == plain2.view(np.uint32)).all()
+        b.retire(3, 1)  # a missing expert is still reported through the replayed graph
+        with pytest.raises(mer_b200.GpuExpertDispatchError) as e:
+            for t in range(4):
+                b.moe_layer_forward(0, xp.numpy(), return_routing=False, out=op.numpy())
+        assert e.value.kind == Kind.ResidencyMiss
+
+
 def test_shared_expert_and_deepseek_routing():
     # sigmoid + groups + scaling 2.5 + always-on shared expert (transformer.rs:2094-2238, model.rs:2758-2763)
     dtype, E, D, F, k, B = oracle.Q4_0, 32, 256, 128, 4, 7
