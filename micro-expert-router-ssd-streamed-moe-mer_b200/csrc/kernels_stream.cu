@@ -139,7 +139,6 @@ __device__ __forceinline__ void ffn_stream_body(const StreamParams &p) {
   uint32_t *s_pair = reinterpret_cast<uint32_t *>(smem + 160);  // [TP] pair index of each token of the current pass
   float *s_un = reinterpret_cast<float *>(smem + 192);          // [TP] its 2^24 / scale
   uint32_t *s_amax = reinterpret_cast<uint32_t *>(smem + 224);  // [TP] max |activation| of its row, as float bits
-  float *s_scale = reinterpret_cast<float *>(smem + 768);       // [TP] the row's power-of-two scale
   float *s_init = reinterpret_cast<float *>(smem + HEADER_BYTES);           // [TP][kb_split]
   uint8_t *s_frag = reinterpret_cast<uint8_t *>(s_init + p.kb_split * TP);  // [TP*2][frag_stride]
   s_frag = reinterpret_cast<uint8_t *>(((size_t)s_frag + 127) & ~(size_t)127);
@@ -245,30 +244,26 @@ __device__ __forceinline__ void ffn_stream_body(const StreamParams &p) {
         const uint32_t eid = d.group_expert[d.pass_group[pp]];
         resident = eid < d.max_experts && d.expert_ptr[eid] != nullptr;
       }
+      if (threadIdx.x < TP) s_amax[threadIdx.x] = 0;  // nobody reads it before the barrier below
       consumer_sync();
       cur_pp = pp, cur_ks = ks;
       // The pass's activation rows become MMA B fragments here, in shared memory: an exact power-of-two
       // scaling that puts max |a| of the row in [256, 512), an f16 hi/lo split in fragment order, and the
-      // per-block accumulator seed -zp * 2^-24 * sum(block).  Warps share the rows: 16 / pcount per row.
+      // per-block accumulator seed -zp * 2^-24 * sum(block).  Warps share the rows: 16 / pcount per row; every
+      // warp looks up its own row, so the only barriers are the one above, one for the row maxima (gate/up
+      // phase) and the final one.
       const uint32_t K = p.kb_total * 32;
-      if (threadIdx.x < TP) {
-        uint32_t pair = 0, mx = 0;
-        if (threadIdx.x < pcount) {
-          pair = d.perm[pstart + threadIdx.x];
-          if (p.phase == 1) mx = d.amax[pair];  // collected by the gate/up epilogue
-        }
-        s_pair[threadIdx.x] = pair;
-        s_amax[threadIdx.x] = mx;
-      }
-      consumer_sync();
       const uint32_t wpt = CONSUMER_WARPS / pcount;  // warps per row (pcount <= 8)
       const uint32_t my_tok = warp / wpt, my_sub = warp % wpt;
       const bool has_row = my_tok < pcount;
       const float *row = nullptr;
+      uint32_t my_pair = 0;
       if (has_row) {
-        const uint32_t pair = s_pair[my_tok];
-        row = p.act + (size_t)(p.act_per_pair ? pair : pair / d.slots) * K;
+        my_pair = d.perm[pstart + my_tok];
+        row = p.act + (size_t)(p.act_per_pair ? my_pair : my_pair / d.slots) * K;
       }
+      if (threadIdx.x < TP) s_pair[threadIdx.x] = threadIdx.x < pcount ? d.perm[pstart + threadIdx.x] : 0u;  // for the epilogues
+      float row_max = 0.0f;
       if (p.phase == 0) {  // the row maximum is not known yet: one pass over the row
         float mx = 0.0f;
         if (has_row) {
@@ -282,23 +277,21 @@ __device__ __forceinline__ void ffn_stream_body(const StreamParams &p) {
         for (int o = 16; o > 0; o >>= 1) mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         if (has_row && lane == 0) atomicMax(&s_amax[my_tok], (mx != mx) ? 0x7fc00000u : __float_as_uint(mx));
         consumer_sync();
+        if (has_row) row_max = __uint_as_float(s_amax[my_tok]);
+      } else if (has_row) {
+        row_max = __uint_as_float(d.amax[my_pair]);  // collected by the gate/up epilogue or its finalize step
       }
-      if (threadIdx.x < TP) {
-        const float mx = __uint_as_float(s_amax[threadIdx.x]);
-        float sc = 1.0f;
-        if (mx > 0.0f && isfinite(mx)) {
-          int e;
-          frexpf(mx, &e);            // mx = m * 2^e, m in [0.5, 1)
-          sc = ldexpf(1.0f, 9 - e);  // mx * sc in [256, 512)
-        } else if (mx != mx || isinf(mx)) {
-          sc = mx;  // non-finite activations poison the row, as they would in fp32
-        }
-        s_scale[threadIdx.x] = sc;
-        s_un[threadIdx.x] = POW2_24 / sc;
+      float row_scale = 1.0f;
+      if (row_max > 0.0f && isfinite(row_max)) {
+        int e;
+        frexpf(row_max, &e);               // row_max = m * 2^e, m in [0.5, 1)
+        row_scale = ldexpf(1.0f, 9 - e);   // row_max * scale in [256, 512)
+      } else if (row_max != row_max || isinf(row_max)) {
+        row_scale = row_max;  // non-finite activations poison the row, as they would in fp32
       }
-      consumer_sync();
+      if (has_row && my_sub == 0 && lane == 0) s_un[my_tok] = POW2_24 / row_scale;
       if (has_row) {
-        const float sc = s_scale[my_tok];
+        const float sc = row_scale;
         const float zp = DT == MER_DTYPE_Q4_0 ? 8.0f : 128.0f;
         uint8_t *hi_dst = s_frag + (size_t)(2 * my_tok) * p.frag_stride, *lo_dst = hi_dst + p.frag_stride;
         float *seed_dst = s_init + (size_t)my_tok * p.kb_split;
