@@ -112,3 +112,38 @@ def test_swiglu_limit_and_nonfinite_rows_on_the_gemm_path():
     for t in (0, 6, 23):
         ref = oracle.expert_forward(dtype, blob, x[t], D, F, oracle.FWD_AUTHORITATIVE, swiglu_limit=0.5)
         assert rel_rms_err(got[t], ref) <= FFN_TOL
+
+
+def test_full_size_prefill_properties_and_spot_check():
+    # BASELINE config 3 at full size: 2048 tokens, D=2048, F=768, E=128, k=8, Q8_0, Zipf-skewed routing.  Size-independent
+    # properties: token-order invariance (bit-exact per token), agreement of the two kernel families, linearity in
+    # the routing weights; plus an oracle spot check on a few tokens.
+    cfg = synth.CONFIGS["cfg3-qwen3-prefill-q8_0"]
+    E, D, F, k, B = cfg.num_experts, cfg.d_model, cfg.d_ff, cfg.top_k, 2048
+    blobs = [synth.make_expert_blob(cfg.dtype, D, F, cfg.seed, 0, e) for e in range(E)]
+    W = synth.make_router(E, D, cfg.seed)
+    bias = synth.zipf_logit_bias(E, 1.0, cfg.seed, 0, strength=0.25)
+    x = synth.make_activations(B, D, cfg.seed)
+    gate = mer_b200.LinearGate(W, E, D, k)
+    gate.logit_bias = bias
+    perm = np.random.default_rng(3).permutation(B)
+    with backend(cfg.dtype, D, F, E, max_experts=E, max_tokens=B, max_top_k=k) as b:
+        for e in range(E):
+            b.admit(e, 1, blobs[e])
+        gate.bind(b, 0)
+        out, ids, w = b.moe_layer_forward(0, x)          # automatic selection: the GEMM kernels at 128 tokens per expert
+        shuffled, sids, _ = b.moe_layer_forward(0, x[perm])
+        b.set_kernel_path(2)
+        streamed, ids2, _ = b.moe_layer_forward(0, x)
+    assert np.isfinite(out).all()
+    counts = np.bincount(ids.ravel(), minlength=E)
+    assert counts.max() > 2 * counts.mean() > 0 and counts.sum() == B * k  # skewed, every pair accounted for
+    assert (sids == ids[perm]).all()
+    assert rel_rms_err(shuffled, out[perm]) <= 1e-5   # passes are cut differently: equal up to fp32 summation order
+    assert (ids2 == ids).all()
+    worst = max(rel_rms_err(out[t], streamed[t]) for t in range(B))
+    assert worst <= 1e-4, worst
+    og = oracle.LinearGate(W, E, D, k, logit_bias=bias)
+    ref, rids, rw, _ = oracle.moe_layer_forward(cfg.dtype, og, blobs, x[:4], F, n_threads=4)
+    assert (ids[:4] == rids).all()
+    assert rel_rms_err(out[:4], ref) <= FFN_TOL
