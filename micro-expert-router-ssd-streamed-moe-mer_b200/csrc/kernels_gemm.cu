@@ -77,6 +77,14 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
       "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
+// The same, always accumulating (no predicate to set up: the issuing thread's instruction count is what limits it).
+__device__ __forceinline__ void tc_mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.eq.b32 p, 0, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%4, %4, %4, %4}, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b), "r"(idesc), "r"(0u)
+      : "memory");
+}
 // 32 columns of this thread's TMEM lane (lane = 32 * (warp % 4) + lane id).
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
   asm volatile(
@@ -234,6 +242,10 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
         if (use > 0) ok = mbar_wait(&acc_empty[buf], (use - 1) & 1);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * 128;
+        // B descriptors differ only in their start-address field: one base, then 64-bit adds of (byte offset >> 4).
+        // (The ring lies well inside the 256 KB the 14-bit field spans, so the adds never carry out of it.)
+        const uint64_t b_desc0 = smem_desc(smem_u32(s_b), p.b_lbo, 128);
+        const uint32_t stage16 = b_stage >> 4, half16 = (4 * p.b_lbo) >> 4, j16 = (2 * p.b_lbo) >> 4, lo16 = b_term >> 4;
         for (uint32_t st = 0; st < p.kb_total && ok; st += GROUP, grp++) {
           const uint32_t ag = grp & 1;  // the group's A stages: ag * GROUP ..
           ok = mbar_wait(&a_full[ag], (grp >> 1) & 1);
@@ -248,13 +260,16 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
               tc_fence_after();
             }
             const uint32_t a_hi = tmem_base + TMEM_A0 + (ag * GROUP + b4) * A_STAGE_COLS, a_lo = a_hi + 16;
-            const uint32_t b_hi = smem_u32(s_b) + rb.stage * b_stage + (b4 & 1) * 4 * p.b_lbo, b_lo = b_hi + b_term;
+            const uint64_t b_blk = b_desc0 + (uint64_t)(rb.stage * stage16 + (b4 & 1) * half16);
 #pragma unroll
             for (uint32_t j = 0; j < 2; j++) {  // 16 values of K per instruction: 8 TMEM columns of A, two core-matrix columns of B
-              const uint64_t dbh = smem_desc(b_hi + j * 2 * p.b_lbo, p.b_lbo, 128), dbl = smem_desc(b_lo + j * 2 * p.b_lbo, p.b_lbo, 128);
-              tc_mma_ts(d_tmem, a_hi + j * 8, dbh, idesc, (st | b4 | j) != 0);
-              tc_mma_ts(d_tmem, a_hi + j * 8, dbl, idesc, 1);
-              tc_mma_ts(d_tmem, a_lo + j * 8, dbh, idesc, 1);
+              const uint64_t dbh = b_blk + (uint64_t)(j * j16), dbl = dbh + lo16;
+              if (b4 == 0 && j == 0)
+                tc_mma_ts(d_tmem, a_hi, dbh, idesc, st != 0);  // the item's first MMA overwrites the accumulator
+              else
+                tc_mma_ts_acc(d_tmem, a_hi + j * 8, dbh, idesc);
+              tc_mma_ts_acc(d_tmem, a_hi + j * 8, dbl, idesc);
+              tc_mma_ts_acc(d_tmem, a_lo + j * 8, dbh, idesc);
             }
             if (b4 & 1) rb.advance();
           }
