@@ -14,7 +14,7 @@ layers so that no step finds its weights in L2.  Prints ONE JSON line (rank 0).
   cpu_baseline  the CPU restatement of the reference's path timed on this host's cores (rank 0, N=1)
 
 `--impl reference` times the CPU path only (the reference itself is Rust and cannot be built here;
-the oracle port stands in for it, see DESIGN.md).
+the oracle port stands in for it).
 """
 import argparse
 import importlib

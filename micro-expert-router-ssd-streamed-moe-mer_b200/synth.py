@@ -33,7 +33,7 @@ class MoeShape:
 
 
 CONFIGS = {
-    # BASELINE configs 0..4 (shapes only; batch sizes are chosen by the caller)
+    # the five benchmark configurations (shapes only; batch sizes are chosen by the caller)
     "cfg0-mixtral-q4_0": MoeShape("cfg0-mixtral-q4_0", Q4_0, 4096, 14336, 8, 2, seed=0),
     "cfg1-qwen3-q8_0": MoeShape("cfg1-qwen3-q8_0", Q8_0, 2048, 768, 128, 8, seed=1),
     "cfg2-mixtral-stack-q4_0": MoeShape("cfg2-mixtral-stack-q4_0", Q4_0, 4096, 14336, 8, 2, seed=0, layers=32),

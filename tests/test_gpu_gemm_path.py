@@ -115,7 +115,7 @@ def test_swiglu_limit_and_nonfinite_rows_on_the_gemm_path():
 
 
 def test_full_size_prefill_properties_and_spot_check():
-    # BASELINE config 3 at full size: 2048 tokens, D=2048, F=768, E=128, k=8, Q8_0, Zipf-skewed routing.  Size-independent
+    # benchmark configuration 3 at full size: 2048 tokens, D=2048, F=768, E=128, k=8, Q8_0, Zipf-skewed routing.  Size-independent
     # properties: token-order invariance (bit-exact per token), agreement of the two kernel families, linearity in
     # the routing weights; plus an oracle spot check on a few tokens.
     cfg = synth.CONFIGS["cfg3-qwen3-prefill-q8_0"]

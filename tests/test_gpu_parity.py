@@ -507,7 +507,7 @@ def test_concurrent_callers_get_bit_equal_results():
 # ------------------------------------------------------------- full-size configurations
 
 def test_full_size_qwen3_layer_properties_and_spot_check():
-    # BASELINE config 1 at full size: D=2048, F=768, E=128, k=8, Q8_0, seed 1, batches 1/8/64
+    # benchmark configuration 1 at full size: D=2048, F=768, E=128, k=8, Q8_0, seed 1, batches 1/8/64
     cfg = synth.CONFIGS["cfg1-qwen3-q8_0"]
     E, D, F, k = cfg.num_experts, cfg.d_model, cfg.d_ff, cfg.top_k
     blobs = [synth.make_expert_blob(cfg.dtype, D, F, cfg.seed, 0, e) for e in range(E)]
@@ -529,7 +529,7 @@ def test_full_size_qwen3_layer_properties_and_spot_check():
 
 
 def test_full_size_mixtral_expert_spot_check():
-    # BASELINE config 0 at full size: D=4096, F=14336, Q4_0, seed 0; one expert, batch 1 and 4
+    # benchmark configuration 0 at full size: D=4096, F=14336, Q4_0, seed 0; one expert, batch 1 and 4
     cfg = synth.CONFIGS["cfg0-mixtral-q4_0"]
     D, F = cfg.d_model, cfg.d_ff
     blob = synth.make_expert_blob(cfg.dtype, D, F, cfg.seed, 0, 0)
