@@ -34,10 +34,11 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {  # name -> (config, default batch, default layers)
     "cfg0": ("cfg0-mixtral-q4_0", 1, 4),
     "cfg1": ("cfg1-qwen3-q8_0", 64, 4),
+    "cfg2": ("cfg2-mixtral-stack-q4_0", 16, 32),   # 32 layers x 8 experts resident (25 GB of HBM slots), Zipf(1.1) skew
     "cfg3": ("cfg3-qwen3-prefill-q8_0", 2048, 2),  # prefill: ~128 tokens per expert, Zipf(1.0) skew -> tcgen05 GEMM path
     "cfg4": ("cfg4-deepseek-v3-q4_0", 16, 1),
 }
-ZIPF = {"cfg3": 1.0}  # routing-locality skew added to the router logits of a workload
+ZIPF = {"cfg2": 1.1, "cfg3": 1.0}  # routing-locality skew added to the router logits of a workload
 DTYPE_NAME = {0: "q4_0", 1: "q8_0"}
 PARALLELISM_NOTE = {
     "replicas": "{n} replicas, tokens data-parallel, no data-path collective",
@@ -54,7 +55,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))  # cfg2: weights of 2 layers repeat over the 32
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--kernel-path", type=int, default=0, help="0 auto, 1 generic, 2 streaming")
@@ -129,11 +130,18 @@ def ncu_traffic(key):
         return None
 
 
-def build_layers(synth, cfg, n_layers):
+def build_layers(synth, cfg, n_layers, distinct_weight_layers=None):
+    """Per layer: expert blobs, shared-expert blob, router.  With distinct_weight_layers = m the expert weights of
+    layer l are those of layer l % m (a deep resident stack without minutes of host-side generation); routers and
+    activations stay distinct per layer."""
     layers = []
+    m = distinct_weight_layers or n_layers
     for l in range(n_layers):
-        blobs = [synth.make_expert_blob(cfg.dtype, cfg.d_model, cfg.d_ff, cfg.seed, l, e) for e in range(cfg.num_experts)]
-        shared = synth.make_expert_blob(cfg.dtype, cfg.d_model, cfg.d_ff, cfg.seed, l, cfg.num_experts) if cfg.shared else None
+        if l < m:
+            blobs = [synth.make_expert_blob(cfg.dtype, cfg.d_model, cfg.d_ff, cfg.seed, l, e) for e in range(cfg.num_experts)]
+            shared = synth.make_expert_blob(cfg.dtype, cfg.d_model, cfg.d_ff, cfg.seed, l, cfg.num_experts) if cfg.shared else None
+        else:
+            blobs, shared = layers[l % m][0], layers[l % m][1]
         layers.append((blobs, shared, synth.make_router(cfg.num_experts, cfg.d_model, cfg.seed, l)))
     return layers
 
@@ -224,7 +232,7 @@ def main():
                           max_tokens=B * world if ep_mode else B, max_top_k=slots, device=local_rank)
     if args.kernel_path:
         be.set_kernel_path(args.kernel_path)
-    layers = build_layers(synth, cfg, R)
+    layers = build_layers(synth, cfg, R, distinct_weight_layers=2 if args.workload == "cfg2" else None)
     hit_bytes = []
     xs_host = []
     for l, (blobs, shared, W) in enumerate(layers):
