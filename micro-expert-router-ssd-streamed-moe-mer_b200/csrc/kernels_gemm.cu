@@ -41,6 +41,7 @@ constexpr uint32_t MAX_RING = 8;
 // group's MMAs and commits ONE barrier, done[], that releases both the group's A stages and the activation stages
 // it read (a wait or a commit per block cost more issue time than the block's MMAs take to run).
 constexpr uint32_t GROUP = 4, DONE_RING = 4;
+static_assert(GROUP == RAW_BLOCKS, "a weight stage holds exactly one group of blocks");
 constexpr float POW2_SCALE_TARGET = 9;   // activations are scaled so that the row maximum lies in [256, 512)
 
 struct GemmParams {
@@ -89,14 +90,14 @@ __device__ __forceinline__ void tc_mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, 
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
-      "tcgen05.wait::st.sync.aligned;\n" ::"r"(taddr),
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
       "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
       "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
       "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]),
       "r"(v[31])
       : "memory");
 }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < MAX_RING; s++) {
       mbar_init(&raw_full[s], 1), mbar_init(&raw_empty[s], DQ_WARPS);
-      mbar_init(&a_full[s], GROUP * (DQ_WARPS / 2)), mbar_init(&done[s], 1);
+      mbar_init(&a_full[s], DQ_WARPS), mbar_init(&done[s], 1);  // one arrival per dequantiser warp and group
       mbar_init(&b_full[s], 1);
     }
     for (uint32_t s = 0; s < 2; s++) mbar_init(&acc_full[s], 1), mbar_init(&acc_empty[s], EPI_WARPS);
@@ -301,21 +302,22 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
       const uint32_t pass = item / m_tiles;
       if (!expert_base(pass)) continue;
-      for (uint32_t st = 0; st < p.kb_total && ok; st++) {
-        const uint32_t sub = st % RAW_BLOCKS;
-        if ((st & 1) == mine) {
-          // raw stages are shared by both warps of the quarter: a warp enters a stage at its first own block
-          if (sub == mine) ok = mbar_wait(&raw_full[raw.stage], raw.round & 1);
-          if (ok && gblk >= A_STAGES) {
-            // the stage was last read by the MMAs of group gblk / GROUP - 2
-            const uint32_t sp = gblk / GROUP - A_STAGES / GROUP;
-            ok = mbar_wait(&done[sp % DONE_RING], (sp / DONE_RING) & 1);
-          }
-          if (*s_abort) ok = false;
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t tile_src = smem_u32(s_raw) + raw.stage * RAW_BYTES + T * TILE_RAW;
+      // one group (= one weight stage) at a time: this warp's two blocks of it, one wait on each side
+      for (uint32_t st0 = 0; st0 < p.kb_total && ok; st0 += GROUP, gblk += GROUP) {
+        ok = mbar_wait(&raw_full[raw.stage], raw.round & 1);
+        if (ok && gblk >= A_STAGES) {
+          // the group's A stages were last read by the MMAs of group gblk / GROUP - 2
+          const uint32_t sp = gblk / GROUP - A_STAGES / GROUP;
+          ok = mbar_wait(&done[sp % DONE_RING], (sp / DONE_RING) & 1);
+        }
+        if (*s_abort) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tile_src = smem_u32(s_raw) + raw.stage * RAW_BYTES + T * TILE_RAW;
+#pragma unroll
+        for (uint32_t hb = 0; hb < GROUP / 2; hb++) {
+          const uint32_t sub = mine + 2 * hb;  // block of the group handled here
           uint32_t v[32];  // [0, 16): hi, values (2c, 2c+1) of the block in column c; [16, 32): lo
           if (DT == MER_DTYPE_Q8_0) {
             const uint32_t src = tile_src + sub * 544;
@@ -346,16 +348,16 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
               dq2(__byte_perm(highs, 0x64646464u, 0x4342), zp, dd, v[8 + 2 * t + 1], v[24 + 2 * t + 1]);
             }
           }
-          tc_st32(tmem_base + ((q * 32u) << 16) + TMEM_A0 + (gblk % A_STAGES) * A_STAGE_COLS, v);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) {
-            mbar_arrive(&a_full[(gblk / GROUP) & 1]);
-            if (sub + 2 >= RAW_BLOCKS) mbar_arrive(&raw_empty[raw.stage]);  // this warp's last block of the stage
-          }
+          tc_st32(tmem_base + ((q * 32u) << 16) + TMEM_A0 + ((gblk + sub) % A_STAGES) * A_STAGE_COLS, v);
         }
-        gblk++;
-        if (sub == RAW_BLOCKS - 1) raw.advance();
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&a_full[(gblk / GROUP) & 1]);
+          mbar_arrive(&raw_empty[raw.stage]);
+        }
+        raw.advance();
       }
     }
     if (!ok && lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
