@@ -244,6 +244,17 @@ int mer_expert_forward_noalloc(int32_t dtype, uint64_t d_model, uint64_t d_ff, c
                                const float *d_x, size_t n_tokens, float *d_out, float swiglu_limit,
                                void *stream, char *err, size_t err_len);
 
+/* ---- pipelined host entry: mer_moe_layer_forward for callers that keep several independent token batches in
+ * flight (a serving loop over micro-batches; the reference's engine overlaps SSD reads with compute the same way,
+ * engine.rs:5174-5643, and has no device boundary to pipeline).  x and out must be pinned host memory and stay
+ * untouched until the wait.  submit() enqueues upload (copy stream), layer (compute stream) and read-back (its own
+ * stream) and returns; wait() blocks until out holds the result and returns the call's typed status.  A slot
+ * (0 .. MER_ASYNC_SLOTS-1) carries one call at a time; calls on different slots overlap. ---- */
+#define MER_ASYNC_SLOTS 4
+int mer_moe_layer_forward_submit(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens,
+                                 float *out, uint32_t slot);
+int mer_moe_layer_forward_wait(mer_backend *b, uint32_t slot);
+
 /* ---- per-stage device timing: StageTimings (stage_timing.rs:6-29) with the reference's stage
  * names, measured with CUDA events on the stream each layer call is enqueued on. ---- */
 typedef struct mer_stage_timings {

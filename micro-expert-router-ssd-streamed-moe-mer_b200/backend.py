@@ -210,6 +210,15 @@ class Backend:
         self._check(self.lib.mer_moe_layer_forward(self.h, layer, _ptr(x), x.shape[0], _ptr(out), _ptr(ids), _ptr(w)))
         return (out, ids, w) if return_routing else out
 
+    def moe_layer_forward_submit(self, layer, x_pinned, out_pinned, slot):
+        """Pipelined host entry: enqueue upload, layer and read-back for pinned numpy views; returns at once."""
+        assert x_pinned.dtype == np.float32 and out_pinned.dtype == np.float32 and x_pinned.flags.c_contiguous
+        n = x_pinned.size // self.d_model
+        self._check(self.lib.mer_moe_layer_forward_submit(self.h, layer, _ptr(x_pinned), n, _ptr(out_pinned), slot))
+
+    def moe_layer_forward_wait(self, slot):
+        self._check(self.lib.mer_moe_layer_forward_wait(self.h, slot))
+
     def moe_layer_forward_device(self, layer, d_x, n_tokens, d_out, stream=0, d_ids=0, d_weights=0):
         """Device pointers (ints) in, asynchronous on `stream` (a cudaStream_t as int)."""
         self._check(self.lib.mer_moe_layer_forward_device(self.h, layer, C.c_void_p(d_x), n_tokens, C.c_void_p(d_out),

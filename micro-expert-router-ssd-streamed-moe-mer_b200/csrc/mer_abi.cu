@@ -83,6 +83,18 @@ struct mer_backend {
   std::unordered_map<uint32_t, RouterEntry> routers;
   int kernel_path = 0;
 
+  // pipelined host entry (mer_moe_layer_forward_submit / _wait): per slot its own device x / out and status copy
+  struct AsyncSlot {
+    float *d_x = nullptr, *d_out = nullptr;
+    uint32_t *d_status = nullptr, *h_status = nullptr;
+    cudaEvent_t ev_in = nullptr, ev_compute = nullptr, ev_out = nullptr;
+    bool in_flight = false;
+    uint32_t layer = 0;
+    size_t pairs = 0;
+  };
+  AsyncSlot aslots[MER_ASYNC_SLOTS];
+  cudaStream_t d2h = nullptr;
+
   // expert parallel (mer_ep_*): exchange buffer mapped by the peers, peers' buffers mapped here
   bool ep_on = false, ep_attached = false;
   EpDev ep{};
@@ -308,6 +320,13 @@ void free_all(mer_backend *b) {
   b->graphs.clear();
   for (auto &e : b->timing_events) cudaEventDestroy(e);
   b->timing_events.clear();
+  for (auto &a : b->aslots) {
+    F(a.d_x), F(a.d_out), F(a.d_status), H(a.h_status);
+    if (a.ev_in) cudaEventDestroy(a.ev_in);
+    if (a.ev_compute) cudaEventDestroy(a.ev_compute);
+    if (a.ev_out) cudaEventDestroy(a.ev_out);
+  }
+  if (b->d2h) cudaStreamDestroy(b->d2h);
   for (auto &p : b->ep_opened)
     if (p) cudaIpcCloseMemHandle(p), p = nullptr;
   F(b->ep_buf);
@@ -997,6 +1016,11 @@ MER_EXPORT int mer_moe_layer_forward(mer_backend *b, uint32_t layer, const float
   return rc;
 }
 
+namespace {
+int layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out, uint32_t *d_ids,
+                                float *d_weights, cudaStream_t s);
+}
+
 MER_EXPORT int mer_moe_layer_forward_device(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out,
                                             uint32_t *d_ids, float *d_weights, void *stream) {
   if (!b) return MER_ERR_INVALID_ARGUMENT;
@@ -1004,7 +1028,13 @@ MER_EXPORT int mer_moe_layer_forward_device(mer_backend *b, uint32_t layer, cons
   if (!d_x || !d_out) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer");
   std::lock_guard<std::mutex> lock(b->mu);
   CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return layer_forward_device_locked(b, layer, d_x, n_tokens, d_out, d_ids, d_weights, static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+int layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out, uint32_t *d_ids,
+                                float *d_weights, cudaStream_t s) {
+  const uint32_t expert = MER_NONE;
   int launches = 0;
   size_t P = 0;
   const bool use_graph = b->graphs_ok && !b->timing_on && !(b->cfg.flags & MER_FLAG_NO_GRAPHS);
@@ -1071,6 +1101,84 @@ MER_EXPORT int mer_moe_layer_forward_device(mer_backend *b, uint32_t layer, cons
   b->ctr.gpu_dispatch_attempts += P;
   b->ctr.gpu_dispatch_successes += P;
   return MER_OK;
+}
+}  // namespace
+
+// ---- pipelined host entry: upload, layer and read-back of consecutive calls overlap (one slot per call in flight)
+MER_EXPORT int mer_moe_layer_forward_submit(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens, float *out, uint32_t slot) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t expert = MER_NONE;
+  if (!x || !out || slot >= MER_ASYNC_SLOTS) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer or slot >= %d", MER_ASYNC_SLOTS);
+  std::lock_guard<std::mutex> lock(b->mu);
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  if (n_tokens == 0 || n_tokens > b->cfg.max_tokens)
+    return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "n_tokens %zu outside 1..=%u", n_tokens, b->cfg.max_tokens);
+  auto it = b->routers.find(layer);
+  if (it == b->routers.end()) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "no router installed for layer %u", layer);
+  mer_backend::AsyncSlot &a = b->aslots[slot];
+  if (a.in_flight) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "slot %u is still in flight: wait for it first", slot);
+  cudaPointerAttributes ax{}, ao{};
+  const bool pinned = cudaPointerGetAttributes(&ax, x) == cudaSuccess && ax.type == cudaMemoryTypeHost &&
+                      cudaPointerGetAttributes(&ao, out) == cudaSuccess && ao.type == cudaMemoryTypeHost;
+  cudaGetLastError();
+  if (!pinned) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "the pipelined entry point needs pinned host buffers");
+  const size_t D = b->cfg.d_model, bytes = n_tokens * D * 4;
+  if (!a.d_x) {
+    const size_t cap = (size_t)b->cfg.max_tokens * D * 4;
+    CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(slot x)", cudaMalloc((void **)&a.d_x, cap));
+    CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(slot out)", cudaMalloc((void **)&a.d_out, cap));
+    CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(slot status)", cudaMalloc((void **)&a.d_status, 4));
+    CU(MER_ERR_PHYSICAL_CAPACITY, "cudaHostAlloc(slot status)", cudaHostAlloc((void **)&a.h_status, 4, cudaHostAllocDefault));
+    CU(MER_ERR_SUBMISSION, "cudaEventCreate", cudaEventCreateWithFlags(&a.ev_in, cudaEventDisableTiming));
+    CU(MER_ERR_SUBMISSION, "cudaEventCreate", cudaEventCreateWithFlags(&a.ev_compute, cudaEventDisableTiming));
+    CU(MER_ERR_SUBMISSION, "cudaEventCreate", cudaEventCreateWithFlags(&a.ev_out, cudaEventDisableTiming));
+    if (!b->d2h) CU(MER_ERR_SUBMISSION, "cudaStreamCreate", cudaStreamCreateWithFlags(&b->d2h, cudaStreamNonBlocking));
+  }
+  // upload on the copy stream (the slot's previous layer call, waited for by the caller, is long done)
+  CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(x)", cudaMemcpyAsync(a.d_x, x, bytes, cudaMemcpyHostToDevice, b->copy));
+  CU(MER_ERR_SUBMISSION, "cudaEventRecord", cudaEventRecord(a.ev_in, b->copy));
+  // the layer on the compute stream, then a copy of the status word it leaves (the next call resets the shared one)
+  CU(MER_ERR_SUBMISSION, "cudaStreamWaitEvent", cudaStreamWaitEvent(b->compute, a.ev_in, 0));
+  int rc = layer_forward_device_locked(b, layer, a.d_x, n_tokens, a.d_out, nullptr, nullptr, b->compute);
+  if (rc) return rc;
+  CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(status)", cudaMemcpyAsync(a.d_status, b->d_status, 4, cudaMemcpyDeviceToDevice, b->compute));
+  CU(MER_ERR_SUBMISSION, "cudaEventRecord", cudaEventRecord(a.ev_compute, b->compute));
+  // read-back on its own stream
+  CU(MER_ERR_SUBMISSION, "cudaStreamWaitEvent", cudaStreamWaitEvent(b->d2h, a.ev_compute, 0));
+  CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(out)", cudaMemcpyAsync(out, a.d_out, bytes, cudaMemcpyDeviceToHost, b->d2h));
+  CU(MER_ERR_READBACK_MAP, "cudaMemcpyAsync(status)", cudaMemcpyAsync(a.h_status, a.d_status, 4, cudaMemcpyDeviceToHost, b->d2h));
+  CU(MER_ERR_SUBMISSION, "cudaEventRecord", cudaEventRecord(a.ev_out, b->d2h));
+  a.in_flight = true;
+  a.layer = layer;
+  a.pairs = n_tokens * (it->second.dev.top_k + (it->second.dev.shared_expert_id != MER_NONE ? 1u : 0u));
+  b->ctr.hidden_upload_bytes += bytes;
+  b->ctr.readback_bytes += bytes;
+  return MER_OK;
+}
+
+MER_EXPORT int mer_moe_layer_forward_wait(mer_backend *b, uint32_t slot) {
+  if (!b || slot >= MER_ASYNC_SLOTS) return MER_ERR_INVALID_ARGUMENT;
+  cudaEvent_t ev;
+  uint32_t layer;
+  {
+    std::lock_guard<std::mutex> lock(b->mu);
+    mer_backend::AsyncSlot &a = b->aslots[slot];
+    if (!a.in_flight) return fail(b, MER_ERR_INVALID_ARGUMENT, 0, MER_NONE, "slot %u has nothing in flight", slot);
+    ev = a.ev_out, layer = a.layer;
+  }
+  const uint32_t expert = MER_NONE;
+  cudaError_t e = cudaEventSynchronize(ev);  // outside the lock: other threads may submit meanwhile
+  std::lock_guard<std::mutex> lock(b->mu);
+  mer_backend::AsyncSlot &a = b->aslots[slot];
+  a.in_flight = false;
+  if (e != cudaSuccess) return cuda_fail(b, MER_ERR_READBACK_MAP, layer, expert, "cudaEventSynchronize", e);
+  int rc = check_device_status(b, *a.h_status, layer, expert);
+  if (rc && rc != MER_ERR_NUMERICAL) {
+    // the call was counted as a success when it was enqueued: move it
+    b->ctr.gpu_dispatch_successes -= a.pairs;
+    b->ctr.gpu_dispatch_failures += a.pairs;
+  }
+  return rc;
 }
 
 // ------------------------------------------------------------------------ expert parallel

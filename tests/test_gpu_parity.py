@@ -361,6 +361,50 @@ def test_host_entry_with_pinned_buffers_equals_the_pageable_path():
         assert e.value.kind == Kind.ResidencyMiss
 
 
+def test_pipelined_host_entry_matches_the_synchronous_one():
+    # submit / wait: several independent batches in flight, every result equal to the synchronous entry point's
+    torch = pytest.importorskip("torch")
+    dtype, E, D, F, k, B = oracle.Q8_0, 16, 256, 256, 4, 7
+    blobs = [random_blob(dtype, D, F, 36, e) for e in range(E)]
+    W = synth.make_router(E, D, 36)
+    xs = [synth.make_activations(B, D, 36, i) for i in range(10)]
+    with backend(dtype, D, F, n_experts=E, max_tokens=8, max_top_k=k) as b:
+        for e in range(E):
+            b.admit(e, 1, blobs[e])
+        mer_b200.LinearGate(W, E, D, k).bind(b, 0)
+        refs = [b.moe_layer_forward(0, x)[0] for x in xs]
+        pin_x = [torch.from_numpy(x.copy()).pin_memory() for x in xs]
+        pin_o = [torch.zeros(B, D).pin_memory() for _ in range(4)]
+        depth, got = 3, {}
+        for i in range(len(xs) + depth):
+            if i >= depth:
+                j = i - depth
+                b.moe_layer_forward_wait(j % 4)
+                got[j] = pin_o[j % 4].numpy().copy()
+            if i < len(xs):
+                b.moe_layer_forward_submit(0, pin_x[i].numpy(), pin_o[i % 4].numpy(), i % 4)
+        for j, ref in enumerate(refs):
+            assert (got[j].view(np.uint32) == ref.view(np.uint32)).all(), j
+        with pytest.raises(mer_b200.GpuExpertDispatchError) as e:  # pageable memory is refused, nothing is enqueued
+            b.moe_layer_forward_submit(0, xs[0], np.empty((B, D), np.float32), 0)
+        assert e.value.kind == Kind.InvalidArgument
+        b.moe_layer_forward_submit(0, pin_x[0].numpy(), pin_o[0].numpy(), 0)
+        with pytest.raises(mer_b200.GpuExpertDispatchError):  # one call per slot
+            b.moe_layer_forward_submit(0, pin_x[1].numpy(), pin_o[1].numpy(), 0)
+        b.moe_layer_forward_wait(0)
+        b.retire(5, 1)  # a missing expert surfaces at the wait of the call that needed it
+        failures = 0
+        for i in range(4):
+            b.moe_layer_forward_submit(0, pin_x[i].numpy(), pin_o[i].numpy(), i)
+        for i in range(4):
+            try:
+                b.moe_layer_forward_wait(i)
+            except mer_b200.GpuExpertDispatchError as err:
+                assert err.kind == Kind.ResidencyMiss
+                failures += 1
+        assert failures >= 1
+
+
 def test_shared_expert_and_deepseek_routing():
     # sigmoid + groups + scaling 2.5 + always-on shared expert (transformer.rs:2094-2238, model.rs:2758-2763)
     dtype, E, D, F, k, B = oracle.Q4_0, 32, 256, 128, 4, 7
