@@ -344,7 +344,7 @@ def main():
     for i in range(3):
         e2e_step(i)
     barrier()
-    if ep_mode:
+    if mode == "ep-collective":
         t0 = time.perf_counter()
         for i in range(args.steps):
             e2e_step(i)
@@ -355,8 +355,9 @@ def main():
         # result back to pinned memory; upload, layer and read-back of neighbouring steps overlap (three in flight)
         depth = 3
         outs = [torch.empty(B, cfg.d_model).pin_memory() for _ in range(depth)]
+        submit = ep.layer_forward_peer_submit if mode == "ep-peer" else be.moe_layer_forward_submit
         for i in range(depth):  # warm the slots (allocations, graph capture)
-            be.moe_layer_forward_submit(i % R, pinned_in[i % R].numpy(), outs[i].numpy(), i)
+            submit(i % R, pinned_in[i % R].numpy(), outs[i].numpy(), i)
         for i in range(depth):
             be.moe_layer_forward_wait(i)
         barrier()
@@ -365,7 +366,7 @@ def main():
             if i >= depth:
                 be.moe_layer_forward_wait(i % depth)
             if i < args.steps:
-                be.moe_layer_forward_submit(i % R, pinned_in[i % R].numpy(), outs[i % depth].numpy(), i % depth)
+                submit(i % R, pinned_in[i % R].numpy(), outs[i % depth].numpy(), i % depth)
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else None

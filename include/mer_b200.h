@@ -254,6 +254,10 @@ int mer_expert_forward_noalloc(int32_t dtype, uint64_t d_model, uint64_t d_ff, c
 int mer_moe_layer_forward_submit(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens,
                                  float *out, uint32_t slot);
 int mer_moe_layer_forward_wait(mer_backend *b, uint32_t slot);
+/* The same for the expert-parallel layer of this rank's tokens (mer_ep_layer_forward_device in the middle); every
+ * rank must submit the same sequence of calls.  Waited for with mer_moe_layer_forward_wait. */
+int mer_ep_layer_forward_submit(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens,
+                                float *out, uint32_t slot);
 
 /* ---- per-stage device timing: StageTimings (stage_timing.rs:6-29) with the reference's stage
  * names, measured with CUDA events on the stream each layer call is enqueued on. ---- */

@@ -97,6 +97,7 @@ ABI_SYMBOLS = {
     "mer_stream_check": (C.c_int, [_vp, _u32, _vp]),
     "mer_moe_layer_forward_submit": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _u32]),
     "mer_moe_layer_forward_wait": (C.c_int, [_vp, _u32]),
+    "mer_ep_layer_forward_submit": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _u32]),
 }
 
 _lib = None

@@ -1105,7 +1105,10 @@ int layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *d_x
 }  // namespace
 
 // ---- pipelined host entry: upload, layer and read-back of consecutive calls overlap (one slot per call in flight)
-MER_EXPORT int mer_moe_layer_forward_submit(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens, float *out, uint32_t slot) {
+namespace {
+int ep_layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out, cudaStream_t s);
+
+int submit_impl(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens, float *out, uint32_t slot, bool ep) {
   if (!b) return MER_ERR_INVALID_ARGUMENT;
   const uint32_t expert = MER_NONE;
   if (!x || !out || slot >= MER_ASYNC_SLOTS) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer or slot >= %d", MER_ASYNC_SLOTS);
@@ -1139,7 +1142,8 @@ MER_EXPORT int mer_moe_layer_forward_submit(mer_backend *b, uint32_t layer, cons
   CU(MER_ERR_SUBMISSION, "cudaEventRecord", cudaEventRecord(a.ev_in, b->copy));
   // the layer on the compute stream, then a copy of the status word it leaves (the next call resets the shared one)
   CU(MER_ERR_SUBMISSION, "cudaStreamWaitEvent", cudaStreamWaitEvent(b->compute, a.ev_in, 0));
-  int rc = layer_forward_device_locked(b, layer, a.d_x, n_tokens, a.d_out, nullptr, nullptr, b->compute);
+  int rc = ep ? ep_layer_forward_device_locked(b, layer, a.d_x, n_tokens, a.d_out, b->compute)
+              : layer_forward_device_locked(b, layer, a.d_x, n_tokens, a.d_out, nullptr, nullptr, b->compute);
   if (rc) return rc;
   CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(status)", cudaMemcpyAsync(a.d_status, b->d_status, 4, cudaMemcpyDeviceToDevice, b->compute));
   CU(MER_ERR_SUBMISSION, "cudaEventRecord", cudaEventRecord(a.ev_compute, b->compute));
@@ -1154,6 +1158,15 @@ MER_EXPORT int mer_moe_layer_forward_submit(mer_backend *b, uint32_t layer, cons
   b->ctr.hidden_upload_bytes += bytes;
   b->ctr.readback_bytes += bytes;
   return MER_OK;
+}
+}  // namespace
+
+MER_EXPORT int mer_moe_layer_forward_submit(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens, float *out, uint32_t slot) {
+  return submit_impl(b, layer, x, n_tokens, out, slot, false);
+}
+
+MER_EXPORT int mer_ep_layer_forward_submit(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens, float *out, uint32_t slot) {
+  return submit_impl(b, layer, x, n_tokens, out, slot, true);
 }
 
 MER_EXPORT int mer_moe_layer_forward_wait(mer_backend *b, uint32_t slot) {
@@ -1175,7 +1188,7 @@ MER_EXPORT int mer_moe_layer_forward_wait(mer_backend *b, uint32_t slot) {
   int rc = check_device_status(b, *a.h_status, layer, expert);
   if (rc && rc != MER_ERR_NUMERICAL) {
     // the call was counted as a success when it was enqueued: move it
-    b->ctr.gpu_dispatch_successes -= a.pairs;
+    if (b->ctr.gpu_dispatch_successes >= a.pairs) b->ctr.gpu_dispatch_successes -= a.pairs;
     b->ctr.gpu_dispatch_failures += a.pairs;
   }
   return rc;
@@ -1353,6 +1366,12 @@ MER_EXPORT int mer_ep_layer_forward_device(mer_backend *b, uint32_t layer, const
   const uint32_t expert = MER_NONE;
   if (!d_x || !d_out) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null pointer");
   std::lock_guard<std::mutex> lock(b->mu);
+  return ep_layer_forward_device_locked(b, layer, d_x, n_tokens, d_out, static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+int ep_layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out, cudaStream_t s) {
+  const uint32_t expert = MER_NONE;
   if (!b->ep_on || !b->ep_attached)
     return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "the expert-parallel group is not initialised and attached");
   auto it = b->routers.find(layer);
@@ -1362,7 +1381,6 @@ MER_EXPORT int mer_ep_layer_forward_device(mer_backend *b, uint32_t layer, const
     return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "n_tokens %zu outside 1..=%u per rank", n_tokens, b->ep_cfg.max_tokens_per_rank);
   if ((b->cfg.d_model & 3) != 0) return fail(b, MER_ERR_INELIGIBLE, layer, expert, "d_model must be a multiple of 4");
   CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
   int launches = 0;
   const size_t D = b->cfg.d_model;
   const uint32_t shared = r.shared_expert_id != MER_NONE ? 1u : 0u, slots = r.top_k + shared;
@@ -1404,7 +1422,7 @@ MER_EXPORT int mer_ep_layer_forward_device(mer_backend *b, uint32_t layer, const
   b->ctr.kernel_launches += (uint64_t)launches;
   b->ctr.selected_routed_experts += n_tokens * slots;
   return MER_OK;
-}
+}}  // namespace
 
 MER_EXPORT int mer_stream_check(mer_backend *b, uint32_t layer, void *stream) {
   if (!b) return MER_ERR_INVALID_ARGUMENT;

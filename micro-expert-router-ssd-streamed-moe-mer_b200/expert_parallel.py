@@ -75,6 +75,15 @@ class ExpertParallel:
         self.b._check(self.b.lib.mer_ep_layer_forward_device(self.b.h, layer, C.c_void_p(d_x), n_tokens, C.c_void_p(d_out),
                                                              C.c_void_p(stream)))
 
+    def layer_forward_peer_submit(self, layer, x_pinned, out_pinned, slot):
+        """Pipelined host form of layer_forward_peer: pinned numpy views in and out, returns at once."""
+        n = x_pinned.size // self.b.d_model
+        self.b._check(self.b.lib.mer_ep_layer_forward_submit(
+            self.b.h, layer, x_pinned.ctypes.data_as(C.c_void_p), n, out_pinned.ctypes.data_as(C.c_void_p), slot))
+
+    def wait(self, slot):
+        self.b._check(self.b.lib.mer_moe_layer_forward_wait(self.b.h, slot))
+
     # -- collective mode --------------------------------------------------------------------
     def _buffers(self, n_tokens, slots, device):
         import torch

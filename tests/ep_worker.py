@@ -78,6 +78,15 @@ def main():
             for _ in range(4):
                 ep.layer_forward_peer(layer, x.data_ptr(), B, out.data_ptr(), stream)
                 ep.check(layer, stream)
+            first = out.cpu().numpy().copy()
+            # the pipelined host form: pinned rows in, pinned rows out, three calls in flight
+            xp = torch.from_numpy(x_all[rank * B:(rank + 1) * B].copy()).pin_memory()
+            ops = [torch.zeros(B, D).pin_memory() for _ in range(3)]
+            for i in range(3):
+                ep.layer_forward_peer_submit(layer, xp.numpy(), ops[i].numpy(), i)
+            for i in range(3):
+                ep.wait(i)
+                assert (ops[i].numpy().view(np.uint32) == first.view(np.uint32)).all(), f"rank {rank}: pipelined call {i} differs"
         else:
             for _ in range(2):
                 ep.layer_forward_collective(layer, x, out, k)
