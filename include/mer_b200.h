@@ -171,6 +171,117 @@ int mer_expert_retire(mer_backend *b, uint32_t expert_id, uint64_t generation);
 /* contains_generation (expert_cache.rs:909): 1 if (id, generation) is resident, else 0. */
 int mer_expert_contains_generation(mer_backend *b, uint32_t expert_id, uint64_t generation);
 
+/* ---- logical VRAM tier: GpuExpertCache (expert_cache.rs:734-1350), the host-side policy that decides which
+ * experts are admitted to the GPU.  Pure bookkeeping: no CUDA call, usable without a device.  Two byte-budgeted
+ * regions are cut from `capacity_bytes` by `anchor_ratio` (clamped to [0, 1]; expert_cache.rs:798-828): the Anchor
+ * Core, whose entries are never evicted, and the LRU Edge, which admits foreground demand and evicts least recently
+ * used.  Generations start at 1, grow monotonically, are allocated before any eviction and are never reused; the
+ * physical slots of mer_expert_admit are keyed by (expert_id, generation), so a stale physical copy is detected
+ * with mer_gpu_cache_contains_generation exactly as backend/mod.rs:3884-3912 does.  The payload itself stays with
+ * the caller; `payload_tag` is an opaque 64-bit identity stored with the admission (the reference keeps an
+ * Arc<GpuResident>).  Calls that may evict report the evicted ids (up to max_evicted; *n_evicted is the true count)
+ * so that the caller retires their physical slots. ---- */
+typedef struct mer_gpu_cache mer_gpu_cache;
+
+#define MER_REGION_NONE 0
+#define MER_REGION_ANCHOR 1
+#define MER_REGION_LRU 2
+/* GpuLookup (expert_cache.rs:629-646) */
+#define MER_LOOKUP_MISS 0
+#define MER_LOOKUP_ANCHOR_HIT 1
+#define MER_LOOKUP_LRU_HIT 2
+/* GpuHotPromotionOutcome (expert_cache.rs:667-702); the first three change state and count as promotions */
+#define MER_HOT_MOVED_LRU_TO_ANCHOR 0
+#define MER_HOT_INSTALLED_ANCHOR 1
+#define MER_HOT_INSTALLED_LRU 2
+#define MER_HOT_ALREADY_ANCHOR 3
+#define MER_HOT_ALREADY_LRU_ANCHOR_FULL 4
+#define MER_HOT_PAYLOAD_REQUIRED 5
+#define MER_HOT_NO_CAPACITY 6
+#define MER_HOT_GENERATION_EXHAUSTED 7
+/* GpuDemandAdmissionPreflight / demand_admit_lru results and GpuDemandAdmissionError (expert_cache.rs:649-665) */
+#define MER_DEMAND_ALREADY_ADMITTED 0 /* preflight: AlreadyAdmitted; demand_admit_lru: Ok(false) */
+#define MER_DEMAND_NEEDS_PAYLOAD 1    /* preflight only */
+#define MER_DEMAND_ADMITTED 2         /* demand_admit_lru: Ok(true) */
+#define MER_DEMAND_ERR_EMPTY_PAYLOAD (-1)
+#define MER_DEMAND_ERR_EXCEEDS_LRU_CAPACITY (-2)
+#define MER_DEMAND_ERR_GENERATION_EXHAUSTED (-3)
+
+/* GpuAdmission (expert_cache.rs:600-623) */
+typedef struct mer_gpu_admission {
+  uint32_t expert_id;
+  uint32_t region; /* MER_REGION_* */
+  uint64_t generation;
+  uint64_t bytes;
+  uint64_t payload_tag;
+} mer_gpu_admission;
+
+typedef struct mer_gpu_cache_stats {
+  uint64_t anchor_capacity_bytes, lru_capacity_bytes;
+  uint64_t anchor_used_bytes, lru_used_bytes, used_bytes; /* used_bytes = logical admitted bytes (expert_cache.rs:835) */
+  uint64_t anchor_len, lru_len;
+  uint64_t promotions, hits, misses; /* mer_promotions_total, mer_gpu_cache_hits_total, mer_gpu_cache_misses_total */
+  uint64_t next_generation;
+  uint64_t promote_after_hits;
+  uint64_t pending_promotions, rearmed_promotions;
+} mer_gpu_cache_stats;
+
+/* GpuExpertCache::new (expert_cache.rs:798-828) */
+int mer_gpu_cache_create(uint64_t capacity_bytes, float anchor_ratio, uint64_t promote_after_hits, mer_gpu_cache **out);
+void mer_gpu_cache_destroy(mer_gpu_cache *c);
+/* get (expert_cache.rs:864-879): the only call that counts a hit or a miss and refreshes LRU recency. Returns MER_LOOKUP_*. */
+int mer_gpu_cache_get(mer_gpu_cache *c, uint32_t expert_id, mer_gpu_admission *out);
+/* current_admission / contains / contains_generation (expert_cache.rs:884-912): no counters, no recency. Return 1 / 0. */
+int mer_gpu_cache_current_admission(mer_gpu_cache *c, uint32_t expert_id, mer_gpu_admission *out);
+int mer_gpu_cache_contains(mer_gpu_cache *c, uint32_t expert_id);
+int mer_gpu_cache_contains_generation(mer_gpu_cache *c, uint32_t expert_id, uint64_t generation);
+/* should_promote / claim_promotion / cancel_promotion (expert_cache.rs:918-952): one claim per threshold edge
+ * (ram_hits == promote_after_hits) and one more after every logical eviction of the id; never two pending. */
+int mer_gpu_cache_should_promote(mer_gpu_cache *c, uint64_t ram_hits);
+int mer_gpu_cache_claim_promotion(mer_gpu_cache *c, uint32_t expert_id, uint64_t ram_hits);
+void mer_gpu_cache_cancel_promotion(mer_gpu_cache *c, uint32_t expert_id);
+/* promote_hot_existing / promote_hot_sync (expert_cache.rs:962-1046). Return MER_HOT_*. */
+int mer_gpu_cache_promote_hot_existing(mer_gpu_cache *c, uint32_t expert_id);
+int mer_gpu_cache_promote_hot_sync(mer_gpu_cache *c, uint32_t expert_id, uint64_t bytes, uint64_t payload_tag, uint32_t *evicted,
+                                   size_t max_evicted, size_t *n_evicted, uint64_t *generation);
+/* promote_sync (expert_cache.rs:1116-1192): warm-up admission, Anchor first when it fits, else LRU with eviction. 1 / 0. */
+int mer_gpu_cache_promote_sync(mer_gpu_cache *c, uint32_t expert_id, uint64_t bytes, uint64_t payload_tag, uint32_t *evicted,
+                               size_t max_evicted, size_t *n_evicted, uint64_t *generation);
+/* try_promote_lru_no_evict (expert_cache.rs:1208-1249): speculative, never evicts, never uses the Anchor Core. 1 / 0. */
+int mer_gpu_cache_try_promote_lru_no_evict(mer_gpu_cache *c, uint32_t expert_id, uint64_t bytes, uint64_t payload_tag,
+                                           uint64_t *generation);
+/* demand_admission_preflight (expert_cache.rs:1251-1270): side-effect free. Returns MER_DEMAND_*. */
+int mer_gpu_cache_demand_admission_preflight(mer_gpu_cache *c, uint32_t expert_id, uint64_t payload_bytes);
+/* demand_admit_lru (expert_cache.rs:1281-1340): foreground demand enters the LRU Edge; the generation is allocated
+ * before victims are evicted; the Anchor Core is never touched; an existing admission changes nothing. MER_DEMAND_*. */
+int mer_gpu_cache_demand_admit_lru(mer_gpu_cache *c, uint32_t expert_id, uint64_t bytes, uint64_t payload_tag, uint32_t *evicted,
+                                   size_t max_evicted, size_t *n_evicted, uint64_t *generation);
+/* Drops (expert_id, generation) from whichever region holds it (the host retired the expert). 1 if it was current. */
+int mer_gpu_cache_remove(mer_gpu_cache *c, uint32_t expert_id, uint64_t generation);
+int mer_gpu_cache_stats_read(mer_gpu_cache *c, mer_gpu_cache_stats *out);
+/* Moves the generation counter forward (never back): lets a host resume a numbering, and tests reach exhaustion. */
+int mer_gpu_cache_set_next_generation(mer_gpu_cache *c, uint64_t next_generation);
+/* bit 0: a promotion request is pending for the id; bit 1: the id may claim one more after its eviction. */
+int mer_gpu_cache_marker_state(mer_gpu_cache *c, uint32_t expert_id);
+
+/* ---- the logical tier driving the physical one: Engine::ensure_gpu_admission / the GPU arm of moe_step_inner
+ * (engine.rs:2382-2429, 5494-5643) followed by GpuBackend's lazy upload keyed by (id, generation)
+ * (backend/mod.rs:3856-4018).  Both calls leave `cache` and the backend's slots consistent: ids the policy evicts are
+ * retired from their slots before the new payload is uploaded.  Flags as mer_expert_admit (MER_ADMIT_ASYNC). ---- */
+/* Foreground demand for `expert_id`: preflight, demand_admit_lru, retire the victims, upload under the new generation.
+ * An id that is already admitted logically but has no physical copy of its current generation is uploaded again under
+ * that generation.  *generation receives the current generation.  Oversized payload: MER_ERR_PHYSICAL_CAPACITY. */
+int mer_expert_demand_admit(mer_backend *b, mer_gpu_cache *cache, uint32_t expert_id, const void *host_blob, size_t bytes,
+                            uint32_t flags, uint64_t *generation);
+/* Threshold-driven promotion (the background promotion task of engine.rs install_gpu_cache): moves an LRU admission
+ * into the Anchor Core, or installs an absent expert (host_blob required then).  Returns MER_OK and the
+ * MER_HOT_* outcome in *outcome; the slot of an anchored expert is never evicted. */
+int mer_expert_hot_promote(mer_backend *b, mer_gpu_cache *cache, uint32_t expert_id, const void *host_blob, size_t bytes,
+                           uint32_t flags, int *outcome);
+/* Routing feedback for hosts whose router runs on the device: counts one mer_gpu_cache_get per id (hits, misses, LRU
+ * recency; `cache` may be NULL) and refreshes the physical slots' recency. */
+int mer_expert_touch(mer_backend *b, mer_gpu_cache *cache, const uint32_t *expert_ids, size_t n);
+
 /* ---- router: LinearGate::new / with_routing (gating.rs:149-238). ---- */
 int mer_router_install(mer_backend *b, uint32_t layer, const float *host_weights /*[E x D]*/,
                        const mer_router_cfg *cfg);

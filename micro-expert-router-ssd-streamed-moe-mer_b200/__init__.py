@@ -11,11 +11,14 @@ from .capi import (ABI_SYMBOLS, DTYPE_Q4_0, DTYPE_Q8_0, EXPERT_NONE, LIB_PATH, S
                    MerCounters, MerErrorInfo, load_library)
 from .backend import (Backend, GpuExpertBatchDispatchOutcome, GpuExpertDispatchError, GpuExpertDispatchErrorKind,
                       expert_bytes, expert_forward_noalloc, routed_expert_gpu_compatibility)
+from .expert_cache import (GpuAdmission, GpuDemandAdmissionError, GpuDemandAdmissionPreflight, GpuExpertCache,
+                           GpuHotPromotionOutcome, GpuLookup)
 from .gating import LinearGate, RoutingDecision, ScoringFunc
 
 __all__ = [
     "ABI_SYMBOLS", "Backend", "DTYPE_Q4_0", "DTYPE_Q8_0", "EXPERT_NONE", "GpuExpertBatchDispatchOutcome",
-    "GpuExpertDispatchError", "GpuExpertDispatchErrorKind", "LIB_PATH", "LinearGate", "MerCounters", "MerErrorInfo",
+    "GpuAdmission", "GpuDemandAdmissionError", "GpuDemandAdmissionPreflight", "GpuExpertCache",
+    "GpuExpertDispatchError", "GpuExpertDispatchErrorKind", "GpuHotPromotionOutcome", "GpuLookup", "LIB_PATH", "LinearGate", "MerCounters", "MerErrorInfo",
     "RoutingDecision", "SCORE_SIGMOID", "SCORE_SOFTMAX", "ScoringFunc", "expert_bytes", "expert_forward_noalloc",
     "load_library",
     "routed_expert_gpu_compatibility",

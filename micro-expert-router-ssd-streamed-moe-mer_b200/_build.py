@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmer_b200.so")
-SOURCES = ["mer_abi.cu", "kernels_generic.cu", "kernels_stream.cu", "kernels_ep.cu", "kernels_gemm.cu", "noalloc.cu"]
+SOURCES = ["mer_abi.cu", "kernels_generic.cu", "kernels_stream.cu", "kernels_ep.cu", "kernels_gemm.cu", "noalloc.cu", "vram_tier.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
               "-Xcompiler", "-fPIC,-fvisibility=hidden,-O3", "-cudart", "static"]
 
@@ -31,7 +31,7 @@ def build(force=False, verbose=False):
         flags += ["-Xptxas", "-v"]
     procs = []
     for src in SOURCES:
-        obj = os.path.join(HERE, "build", src.replace(".cu", ".o"))
+        obj = os.path.join(HERE, "build", os.path.splitext(src)[0] + ".o")
         objs.append(obj)
         procs.append(subprocess.Popen([_nvcc()] + flags + ["-c", os.path.join(CSRC, src), "-o", obj]))
     for p in procs:

@@ -40,6 +40,21 @@ class MerCounters(C.Structure):
         return {n: int(getattr(self, n)) for n, _ in self._fields_}
 
 
+class MerGpuAdmission(C.Structure):
+    _fields_ = [("expert_id", C.c_uint32), ("region", C.c_uint32), ("generation", C.c_uint64), ("bytes", C.c_uint64),
+                ("payload_tag", C.c_uint64)]
+
+
+class MerGpuCacheStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in (
+        "anchor_capacity_bytes", "lru_capacity_bytes", "anchor_used_bytes", "lru_used_bytes", "used_bytes", "anchor_len",
+        "lru_len", "promotions", "hits", "misses", "next_generation", "promote_after_hits", "pending_promotions",
+        "rearmed_promotions")]
+
+    def as_dict(self):
+        return {n: int(getattr(self, n)) for n, _ in self._fields_}
+
+
 class MerEpCfg(C.Structure):
     _fields_ = [("rank", C.c_uint32), ("world", C.c_uint32), ("experts_per_layer", C.c_uint32),
                 ("max_tokens_per_rank", C.c_uint32), ("wait_ms", C.c_uint32), ("reserved", C.c_uint32)]
@@ -69,6 +84,28 @@ ABI_SYMBOLS = {
     "mer_expert_admit_device": (C.c_int, [_vp, _u32, _u64, _vp, _sz, _u32]),
     "mer_expert_retire": (C.c_int, [_vp, _u32, _u64]),
     "mer_expert_contains_generation": (C.c_int, [_vp, _u32, _u64]),
+    "mer_gpu_cache_create": (C.c_int, [_u64, C.c_float, _u64, C.POINTER(_vp)]),
+    "mer_gpu_cache_destroy": (None, [_vp]),
+    "mer_gpu_cache_get": (C.c_int, [_vp, _u32, C.POINTER(MerGpuAdmission)]),
+    "mer_gpu_cache_current_admission": (C.c_int, [_vp, _u32, C.POINTER(MerGpuAdmission)]),
+    "mer_gpu_cache_contains": (C.c_int, [_vp, _u32]),
+    "mer_gpu_cache_contains_generation": (C.c_int, [_vp, _u32, _u64]),
+    "mer_gpu_cache_should_promote": (C.c_int, [_vp, _u64]),
+    "mer_gpu_cache_claim_promotion": (C.c_int, [_vp, _u32, _u64]),
+    "mer_gpu_cache_cancel_promotion": (None, [_vp, _u32]),
+    "mer_gpu_cache_promote_hot_existing": (C.c_int, [_vp, _u32]),
+    "mer_gpu_cache_promote_hot_sync": (C.c_int, [_vp, _u32, _u64, _u64, _vp, _sz, C.POINTER(_sz), C.POINTER(_u64)]),
+    "mer_gpu_cache_promote_sync": (C.c_int, [_vp, _u32, _u64, _u64, _vp, _sz, C.POINTER(_sz), C.POINTER(_u64)]),
+    "mer_gpu_cache_try_promote_lru_no_evict": (C.c_int, [_vp, _u32, _u64, _u64, C.POINTER(_u64)]),
+    "mer_gpu_cache_demand_admission_preflight": (C.c_int, [_vp, _u32, _u64]),
+    "mer_gpu_cache_demand_admit_lru": (C.c_int, [_vp, _u32, _u64, _u64, _vp, _sz, C.POINTER(_sz), C.POINTER(_u64)]),
+    "mer_gpu_cache_remove": (C.c_int, [_vp, _u32, _u64]),
+    "mer_gpu_cache_stats_read": (C.c_int, [_vp, C.POINTER(MerGpuCacheStats)]),
+    "mer_gpu_cache_set_next_generation": (C.c_int, [_vp, _u64]),
+    "mer_gpu_cache_marker_state": (C.c_int, [_vp, _u32]),
+    "mer_expert_demand_admit": (C.c_int, [_vp, _vp, _u32, _vp, _sz, _u32, C.POINTER(_u64)]),
+    "mer_expert_hot_promote": (C.c_int, [_vp, _vp, _u32, _vp, _sz, _u32, C.POINTER(C.c_int)]),
+    "mer_expert_touch": (C.c_int, [_vp, _vp, _vp, _sz]),
     "mer_router_install": (C.c_int, [_vp, _u32, _vp, C.POINTER(MerRouterCfg)]),
     "mer_router_route": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _vp]),
     "mer_routed_expert_matmul": (C.c_int, [_vp, _u32, _u32, _vp, _sz, _sz, _vp]),

@@ -779,8 +779,7 @@ __global__ void __launch_bounds__(256) k_down_generic(MoeDispatch d) {
   if (beg == end) return;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t r = blockIdx.x * 8 + warp;
-  uint32_t eid = d.group_expert[g];
-  const uint8_t *base = (eid < d.max_experts) ? d.expert_ptr[eid] : nullptr;
+  const uint8_t *base = group_weights(d, g);  // latches the residency miss: the slot may have gone since gate/up ran
   if (r >= d.D) return;
   if (!base) {
     for (uint32_t t = beg + lane; t < end; t += 32) d.y[(size_t)d.perm[t] * d.D + r] = 0.0f;

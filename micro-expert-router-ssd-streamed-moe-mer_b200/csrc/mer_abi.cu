@@ -114,6 +114,14 @@ struct mer_backend {
   };
   std::vector<GraphEntry> graphs;
   bool graphs_ok = true;
+  // Streams other than `compute` that device entry points were last enqueued on, each with an event recorded after
+  // the call: an admission or a retire makes the copy stream wait for all of them before it touches a slot.
+  struct UserStream {
+    cudaStream_t stream;
+    cudaEvent_t done;
+    uint64_t last_use;
+  };
+  std::vector<UserStream> user_streams;
   // stage timing: sets of 5 events {start, after router, mid FFN, after FFN, after combine}
   bool timing_on = false;
   std::vector<cudaEvent_t> timing_events;
@@ -184,6 +192,50 @@ cudaError_t order_after_copies(mer_backend *b, cudaStream_t s) {
   if (!b->copy_pending) return cudaSuccess;
   cudaError_t e = cudaStreamWaitEvent(s, b->ev_copy_done, 0);
   if (e == cudaSuccess && s == b->compute) b->copy_pending = false;
+  return e;
+}
+
+constexpr size_t MAX_USER_STREAMS = 8;
+
+// Records that work reading the slot arena was just enqueued on caller stream `s`.
+cudaError_t note_stream_use(mer_backend *b, cudaStream_t s) {
+  if (s == b->compute) return cudaSuccess;  // ordered through ev_compute_done
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return cudaSuccess;  // a call captured into the caller's own graph: the caller orders its replays against admissions
+  }
+  mer_backend::UserStream *slot = nullptr;
+  for (auto &u : b->user_streams)
+    if (u.stream == s) slot = &u;
+  if (!slot) {
+    if (b->user_streams.size() < MAX_USER_STREAMS) {
+      cudaEvent_t ev;
+      cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+      if (e != cudaSuccess) return e;
+      b->user_streams.push_back({s, ev, 0});
+      slot = &b->user_streams.back();
+    } else {
+      // more distinct streams than tracked: the least recently used one is synchronised and its entry reused
+      slot = &b->user_streams[0];
+      for (auto &u : b->user_streams)
+        if (u.last_use < slot->last_use) slot = &u;
+      cudaError_t e = cudaEventSynchronize(slot->done);
+      if (e != cudaSuccess) return e;
+      slot->stream = s;
+    }
+  }
+  slot->last_use = ++b->tick;
+  return cudaEventRecord(slot->done, s);
+}
+
+// Before the copy stream overwrites, repacks or unmaps a slot: everything already enqueued that may read the arena
+// (the backend's compute stream and every tracked caller stream) must have finished.
+cudaError_t copy_waits_for_readers(mer_backend *b) {
+  cudaError_t e = cudaEventRecord(b->ev_compute_done, b->compute);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(b->copy, b->ev_compute_done, 0);
+  for (auto &u : b->user_streams)
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(b->copy, u.done, 0);
   return e;
 }
 
@@ -320,6 +372,8 @@ void free_all(mer_backend *b) {
   b->graphs.clear();
   for (auto &e : b->timing_events) cudaEventDestroy(e);
   b->timing_events.clear();
+  for (auto &u : b->user_streams) cudaEventDestroy(u.done);
+  b->user_streams.clear();
   for (auto &a : b->aslots) {
     F(a.d_x), F(a.d_out), F(a.d_status), H(a.h_status);
     if (a.ev_in) cudaEventDestroy(a.ev_in);
@@ -391,6 +445,9 @@ int admit_impl(mer_backend *b, uint32_t id, uint64_t generation, const void *blo
                 (unsigned long long)b->cfg.d_model, (unsigned long long)b->cfg.d_ff);
   std::lock_guard<std::mutex> lock(b->mu);
   CU(MER_ERR_UPLOAD, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  // A slot (the victim's table entry included) may still be read by layers already enqueued: every write of this
+  // admission, the eviction's table update first, is ordered after them.
+  CU(MER_ERR_UPLOAD, "order the copy stream after the readers", copy_waits_for_readers(b));
   size_t si;
   bool already;
   int rc = acquire_slot(b, id, generation, flags, &si, &already);
@@ -401,9 +458,6 @@ int admit_impl(mer_backend *b, uint32_t id, uint64_t generation, const void *blo
     if (flags & MER_ADMIT_ANCHOR) s.anchor = true;
     return MER_OK;
   }
-  // The slot may still be read by kernels already enqueued on the compute stream.
-  CU(MER_ERR_UPLOAD, "cudaEventRecord", cudaEventRecord(b->ev_compute_done, b->compute));
-  CU(MER_ERR_UPLOAD, "cudaStreamWaitEvent", cudaStreamWaitEvent(b->copy, b->ev_compute_done, 0));
   uint8_t *slot_base = b->arena + si * b->slot_stride;
   uint8_t *payload = slot_base + SLOT_HEADER_BYTES;
   uint8_t *landing = b->packed ? b->d_raw_stage : payload;  // packed slots: land flat bytes in staging, then permute
@@ -671,8 +725,7 @@ MER_EXPORT int mer_expert_retire(mer_backend *b, uint32_t expert_id, uint64_t ge
   auto it = b->id2slot.find(expert_id);
   if (it == b->id2slot.end() || b->slots[it->second].generation != generation) return MER_OK;  // not current: nothing to retire
   CU(MER_ERR_UPLOAD, "cudaSetDevice", cudaSetDevice(b->cfg.device));
-  CU(MER_ERR_UPLOAD, "cudaEventRecord", cudaEventRecord(b->ev_compute_done, b->compute));
-  CU(MER_ERR_UPLOAD, "cudaStreamWaitEvent", cudaStreamWaitEvent(b->copy, b->ev_compute_done, 0));
+  CU(MER_ERR_UPLOAD, "order the copy stream after the readers", copy_waits_for_readers(b));
   b->h_expert_ptr[expert_id] = nullptr;
   CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(table)",
      cudaMemcpyAsync((void *)(b->d_expert_ptr + expert_id), (void *)(b->h_expert_ptr + expert_id), sizeof(void *),
@@ -689,6 +742,141 @@ MER_EXPORT int mer_expert_contains_generation(mer_backend *b, uint32_t expert_id
   std::lock_guard<std::mutex> lock(b->mu);
   auto it = b->id2slot.find(expert_id);
   return it != b->id2slot.end() && b->slots[it->second].generation == generation;
+}
+
+// ---- the logical tier (vram_tier.cpp) driving the physical slots
+namespace {
+// Frees the physical slot of `id` whatever generation it holds (the policy evicted the id).  Caller holds b->mu.
+int retire_physical_locked(mer_backend *b, uint32_t id) {
+  const uint32_t layer = 0, expert = id;
+  auto it = b->id2slot.find(id);
+  if (it == b->id2slot.end()) return MER_OK;
+  CU(MER_ERR_UPLOAD, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  CU(MER_ERR_UPLOAD, "order the copy stream after the readers", copy_waits_for_readers(b));
+  b->h_expert_ptr[id] = nullptr;
+  CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(table)",
+     cudaMemcpyAsync((void *)(b->d_expert_ptr + id), (void *)(b->h_expert_ptr + id), sizeof(void *), cudaMemcpyHostToDevice, b->copy));
+  CU(MER_ERR_UPLOAD, "cudaEventRecord(copy)", cudaEventRecord(b->ev_copy_done, b->copy));
+  b->copy_pending = true;
+  b->slots[it->second] = Slot{};
+  b->id2slot.erase(it);
+  b->ctr.evictions++;
+  return MER_OK;
+}
+
+int retire_evicted(mer_backend *b, const uint32_t *ids, size_t n) {
+  std::lock_guard<std::mutex> lock(b->mu);
+  for (size_t i = 0; i < n; i++) {
+    int rc = retire_physical_locked(b, ids[i]);
+    if (rc) return rc;
+  }
+  return MER_OK;
+}
+
+bool physical_has(mer_backend *b, uint32_t id, uint64_t generation) {
+  std::lock_guard<std::mutex> lock(b->mu);
+  auto it = b->id2slot.find(id);
+  return it != b->id2slot.end() && b->slots[it->second].generation == generation;
+}
+}  // namespace
+
+MER_EXPORT int mer_expert_demand_admit(mer_backend *b, mer_gpu_cache *cache, uint32_t expert_id, const void *host_blob, size_t bytes,
+                                       uint32_t flags, uint64_t *generation) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t layer = 0, expert = expert_id;
+  if (!cache) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null cache");
+  if (expert_id >= b->cfg.max_experts)
+    return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "expert id %u outside the id space of %u", expert_id, b->cfg.max_experts);
+  if (host_blob && bytes < b->expert_bytes)
+    return fail(b, MER_ERR_UPLOAD, layer, expert, "blob has %zu bytes, need %zu", bytes, b->expert_bytes);
+  // The policy accounts the logical payload (the bytes a slot holds), not the caller's page padding.
+  const uint64_t logical = b->expert_bytes;
+  const int pre = mer_gpu_cache_demand_admission_preflight(cache, expert_id, logical);
+  if (pre == MER_DEMAND_ERR_EXCEEDS_LRU_CAPACITY)
+    return fail(b, MER_ERR_PHYSICAL_CAPACITY, layer, expert, "expert payload of %llu bytes exceeds the logical LRU capacity",
+                (unsigned long long)logical);
+  if (pre < 0) return fail(b, MER_ERR_UPLOAD, layer, expert, "empty expert payload");
+  mer_gpu_admission adm{};
+  if (pre == MER_DEMAND_ALREADY_ADMITTED) {
+    if (!mer_gpu_cache_current_admission(cache, expert_id, &adm))
+      return fail(b, MER_ERR_RESIDENCY_MISS, layer, expert, "the admission vanished between the preflight and the lookup");
+    if (generation) *generation = adm.generation;
+    if (physical_has(b, expert_id, adm.generation)) return MER_OK;
+    // admitted logically, no physical copy of that generation yet: the lazy upload of backend/mod.rs:3916-3990
+    if (!host_blob) return fail(b, MER_ERR_RESIDENCY_MISS, layer, expert, "admitted logically but not uploaded, and no payload was passed");
+    return admit_impl(b, expert_id, adm.generation, host_blob, bytes, flags | (adm.region == MER_REGION_ANCHOR ? MER_ADMIT_ANCHOR : 0u), false);
+  }
+  if (!host_blob) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "a new admission needs the expert payload");
+  uint32_t evicted[64];
+  size_t n_ev = 0;
+  uint64_t gen = 0;
+  const int rc = mer_gpu_cache_demand_admit_lru(cache, expert_id, logical, (uint64_t)(uintptr_t)host_blob, evicted, 64, &n_ev, &gen);
+  if (rc == MER_DEMAND_ERR_GENERATION_EXHAUSTED)
+    return fail(b, MER_ERR_RUNTIME_INVARIANT, layer, expert, "logical GPU admission generation space exhausted");
+  if (rc == MER_DEMAND_ERR_EXCEEDS_LRU_CAPACITY)
+    return fail(b, MER_ERR_PHYSICAL_CAPACITY, layer, expert, "expert payload exceeds the logical LRU capacity");
+  if (rc < 0) return fail(b, MER_ERR_UPLOAD, layer, expert, "empty expert payload");
+  if (rc == MER_DEMAND_ALREADY_ADMITTED) {  // another thread admitted it after the preflight: use that admission
+    mer_gpu_cache_current_admission(cache, expert_id, &adm);
+    gen = adm.generation;
+  }
+  if (generation) *generation = gen;
+  if (n_ev > 64)
+    return fail(b, MER_ERR_RUNTIME_INVARIANT, layer, expert, "one admission evicted %zu experts, more than this call can retire", n_ev);
+  int rr = retire_evicted(b, evicted, n_ev);
+  if (rr) return rr;
+  if (physical_has(b, expert_id, gen)) return MER_OK;
+  return admit_impl(b, expert_id, gen, host_blob, bytes, flags & ~MER_ADMIT_ANCHOR, false);
+}
+
+MER_EXPORT int mer_expert_hot_promote(mer_backend *b, mer_gpu_cache *cache, uint32_t expert_id, const void *host_blob, size_t bytes,
+                                      uint32_t flags, int *outcome) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t layer = 0, expert = expert_id;
+  if (!cache || !outcome) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null cache or outcome");
+  if (expert_id >= b->cfg.max_experts)
+    return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "expert id %u outside the id space of %u", expert_id, b->cfg.max_experts);
+  int o = mer_gpu_cache_promote_hot_existing(cache, expert_id);
+  uint32_t evicted[64];
+  size_t n_ev = 0;
+  uint64_t gen = 0;
+  if (o == MER_HOT_PAYLOAD_REQUIRED && host_blob) {
+    if (bytes < b->expert_bytes) {
+      mer_gpu_cache_cancel_promotion(cache, expert_id);
+      return fail(b, MER_ERR_UPLOAD, layer, expert, "blob has %zu bytes, need %zu", bytes, b->expert_bytes);
+    }
+    o = mer_gpu_cache_promote_hot_sync(cache, expert_id, b->expert_bytes, (uint64_t)(uintptr_t)host_blob, evicted, 64, &n_ev, &gen);
+  }
+  *outcome = o;
+  if (n_ev > 64) return fail(b, MER_ERR_RUNTIME_INVARIANT, layer, expert, "one promotion evicted %zu experts", n_ev);
+  int rr = retire_evicted(b, evicted, n_ev);
+  if (rr) return rr;
+  mer_gpu_admission adm{};
+  if (!mer_gpu_cache_current_admission(cache, expert_id, &adm)) return MER_OK;  // nothing admitted (payload required, no capacity ...)
+  const bool anchor = adm.region == MER_REGION_ANCHOR;
+  if (physical_has(b, expert_id, adm.generation)) {
+    std::lock_guard<std::mutex> lock(b->mu);
+    auto it = b->id2slot.find(expert_id);
+    if (it != b->id2slot.end()) b->slots[it->second].anchor = anchor;
+    return MER_OK;
+  }
+  if (!host_blob) return MER_OK;  // the physical upload stays lazy: the next demand for the id brings the payload
+  return admit_impl(b, expert_id, adm.generation, host_blob, bytes, (flags & ~MER_ADMIT_ANCHOR) | (anchor ? MER_ADMIT_ANCHOR : 0u), false);
+}
+
+MER_EXPORT int mer_expert_touch(mer_backend *b, mer_gpu_cache *cache, const uint32_t *expert_ids, size_t n) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  if (!expert_ids && n) return fail(b, MER_ERR_INVALID_ARGUMENT, 0, MER_NONE, "null ids");
+  for (size_t i = 0; i < n; i++) {
+    if (expert_ids[i] == MER_NONE) continue;
+    if (cache) (void)mer_gpu_cache_get(cache, expert_ids[i], nullptr);
+  }
+  std::lock_guard<std::mutex> lock(b->mu);
+  for (size_t i = 0; i < n; i++) {
+    auto it = b->id2slot.find(expert_ids[i]);
+    if (it != b->id2slot.end()) b->slots[it->second].last_use = ++b->tick;
+  }
+  return MER_OK;
 }
 
 MER_EXPORT int mer_router_install(mer_backend *b, uint32_t layer, const float *host_weights, const mer_router_cfg *cfg) {
@@ -1096,6 +1284,7 @@ int layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *d_x
     if (d_ids) CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(ids)", cudaMemcpyAsync(d_ids, b->d_pair_expert, P * 4, cudaMemcpyDeviceToDevice, s));
     if (d_weights) CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(w)", cudaMemcpyAsync(d_weights, b->d_pair_weight, P * 4, cudaMemcpyDeviceToDevice, s));
   }
+  CU(MER_ERR_SUBMISSION, "cudaEventRecord(stream use)", note_stream_use(b, s));
   b->ctr.kernel_launches += (uint64_t)launches;
   b->ctr.selected_routed_experts += P;
   b->ctr.gpu_dispatch_attempts += P;
@@ -1321,6 +1510,7 @@ MER_EXPORT int mer_router_route_device(mer_backend *b, uint32_t layer, const flo
   const size_t P = n_tokens * d.slots;
   CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(ids)", cudaMemcpyAsync(d_ids, b->d_pair_expert, P * 4, cudaMemcpyDeviceToDevice, s));
   CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(w)", cudaMemcpyAsync(d_weights, b->d_pair_weight, P * 4, cudaMemcpyDeviceToDevice, s));
+  CU(MER_ERR_SUBMISSION, "cudaEventRecord(stream use)", note_stream_use(b, s));
   b->ctr.kernel_launches += (uint64_t)launches;
   return MER_OK;
 }
@@ -1356,6 +1546,7 @@ MER_EXPORT int mer_ep_local_experts_forward_device(mer_backend *b, uint32_t laye
   int rc = ep_run_local_experts(b, layer, r, d, s, &launches);
   if (rc) return rc;
   CU(MER_ERR_SUBMISSION, "combine kernel", launch_combine(d, s, &launches));
+  CU(MER_ERR_SUBMISSION, "cudaEventRecord(stream use)", note_stream_use(b, s));
   b->ctr.kernel_launches += (uint64_t)launches;
   return MER_OK;
 }
@@ -1419,6 +1610,7 @@ int ep_layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *
   // weighted sum in slot order, every pair's output read from the rank that owns its expert
   CU(MER_ERR_SUBMISSION, "combine kernel",
      launch_ep_combine(ep, e2, (uint32_t)D, slots, ids_pub, w_own, d_out, b->d_status, s, &launches));
+  CU(MER_ERR_SUBMISSION, "cudaEventRecord(stream use)", note_stream_use(b, s));
   b->ctr.kernel_launches += (uint64_t)launches;
   b->ctr.selected_routed_experts += n_tokens * slots;
   return MER_OK;
