@@ -1,21 +1,27 @@
 #!/usr/bin/env python3
-"""Benchmark of the routed quantized SwiGLU expert-FFN path (one MoE layer per step).
+"""Benchmark of the routed quantized SwiGLU expert-FFN path.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1] [--batch B] [--impl reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload cfgN] [--batch B] [--layers L]
 
-A step is one pass of the whole hot path (router top-k -> permute -> gate/up + SiLU*mul -> down ->
-weighted combine) over one batch of synthetic tokens.  Steps rotate over `--layers` distinct resident
-layers so that no step finds its weights in L2.  Prints ONE JSON line (rank 0).
+The default workload is the largest configuration that fits one GPU and the only one defined at 1 / 2 / 4 / 8
+GPUs: the Qwen3-30B-A3B-shaped Q8_0 prefill (48 MoE layers x 128 experts resident, 30.8 GB; a 2048-token batch,
+top-8, Zipf(s=1.0) logit bias).  A STEP is the token batch through every resident layer once (router top-k ->
+permute -> gate/up + SiLU*mul -> down -> weighted combine, L times); `value` counts tokens x layers per second,
+i.e. tokens/s through one MoE layer.  At N > 1 the global batch stays 2048 tokens and every rank holds 128/N
+experts of each layer (strong scaling).  Prints ONE JSON line (rank 0).
 
-  value     tokens/s with inputs already in HBM (device pointers, mer_moe_layer_forward_device)
-  e2e       tokens/s through the host-buffer entry points (mer_moe_layer_forward_submit / _wait): every step
-            uploads its pinned host rows and reads its result back to pinned host memory inside the timed
-            region; three independent steps are in flight so that copies and compute overlap
-  roofline  dominant kernel: algorithmic bytes / its CUDA-event time, against the measured HBM peak
-  cpu_baseline  the CPU restatement of the reference's path timed on this host's cores (rank 0, N=1)
+  value      inputs already in HBM (device pointers), CUDA events around exactly K steps, max over ranks
+  e2e        the same steps through the host-buffer entry points: pinned host rows uploaded and results read back
+             inside the timed region (pipelined: three calls in flight); e2e_sync = the synchronous host call
+  roofline   dominant kernel (the gate/up launch): algorithmic FLOPs or bytes / its CUDA-event time against the
+             measured peak (MEASURED_PEAKS.json)
+  parity     rank 0 recomputes a few of its tokens with the CPU oracle outside the timed region; the run fails
+             when routing or outputs differ beyond the stated bar or a device status bit is latched
+  sweep      (N = 1) the other configurations at their stated decode batches, measured the same way
+  cpu_baseline  the CPU restatement of the reference's path on this host's cores (rank 0, N = 1)
 
-`--impl reference` times the CPU path only (the reference itself is Rust and cannot be built here;
-the oracle port stands in for it).
+`--impl reference` times the CPU path only (the reference itself is Rust and cannot be built here; the oracle
+port stands in for it).
 """
 import argparse
 import importlib
@@ -26,21 +32,30 @@ import subprocess
 import sys
 import threading
 import time
+from concurrent.futures import ThreadPoolExecutor
 
 import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-WORKLOADS = {  # name -> (config, default batch, default layers)
-    "cfg0": ("cfg0-mixtral-q4_0", 1, 4),
-    "cfg1": ("cfg1-qwen3-q8_0", 64, 4),
-    "cfg2": ("cfg2-mixtral-stack-q4_0", 16, 32),   # 32 layers x 8 experts resident (25 GB of HBM slots), Zipf(1.1) skew
-    "cfg3": ("cfg3-qwen3-prefill-q8_0", 2048, 2),  # prefill: ~128 tokens per expert, Zipf(1.0) skew -> tcgen05 GEMM path
-    "cfg4": ("cfg4-deepseek-v3-q4_0", 16, 1),
+WORKLOADS = {  # name -> (config, default batch, default resident layers, Zipf s or None)
+    "cfg0": ("cfg0-mixtral-q4_0", 1, 8, None),
+    "cfg1": ("cfg1-qwen3-q8_0", 64, 8, None),
+    "cfg2": ("cfg2-mixtral-stack-q4_0", 16, 32, 1.1),
+    "cfg3": ("cfg3-qwen3-prefill-q8_0", 2048, 48, 1.0),
+    "cfg4": ("cfg4-deepseek-v3-q4_0", 16, 1, None),
 }
-ZIPF = {"cfg2": 1.1, "cfg3": 1.0}  # routing-locality skew added to the router logits of a workload
+SWEEP = [  # (workload, batches) measured after the headline at N = 1; cfg1 / cfg0 reuse the resident cfg3 / cfg2 stacks
+    ("cfg1", (1, 8, 64)),
+    ("cfg2", (1, 4, 16, 64, 256)),
+    ("cfg0", (1, 16)),
+    ("cfg4", (16,)),
+]
 DTYPE_NAME = {0: "q4_0", 1: "q8_0"}
+GEMM_MEAN_TOKENS = 32  # mean tokens per expert from which the library's automatic selection runs the tcgen05 GEMM kernels
+PARITY_TOKENS = 4
+PARITY_BAR = 1e-3      # max-abs error of a token's output relative to the RMS of the oracle's output
 PARALLELISM_NOTE = {
     "replicas": "{n} replicas, tokens data-parallel, no data-path collective",
     "ep-peer": "expert-parallel over {n} GPUs (experts split contiguously, tokens data-parallel), dispatch and combine by the "
@@ -53,15 +68,18 @@ PARALLELISM_NOTE = {
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=400)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))  # cfg2: weights of 2 layers repeat over the 32
-    ap.add_argument("--batch", type=int, default=0)
-    ap.add_argument("--layers", type=int, default=0)
-    ap.add_argument("--kernel-path", type=int, default=0, help="0 auto, 1 generic, 2 streaming")
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0, help="tokens per step over all GPUs (cfg3) or per GPU (other workloads)")
+    ap.add_argument("--layers", type=int, default=0, help="resident layers a step runs through (default: the whole stack)")
+    ap.add_argument("--kernel-path", type=int, default=0, help="0 auto, 1 generic, 2 streaming, 3 GEMM")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="bound on the CPU baseline leg")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--zipf-strength", type=float, default=1.0)
     ap.add_argument("--parallelism", default="auto", choices=["auto", "replicas", "ep-peer", "ep-collective"],
                     help="N > 1: expert-parallel with the exchange through peer memory (default) or through NCCL "
                          "collectives, or independent token-parallel replicas")
@@ -100,26 +118,21 @@ class ClockSampler:
             self.proc.kill()
         sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
         mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        pw = [float(r[2]) for r in self.rows if len(r) >= 7 and r[2].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = sorted({n for r in self.rows if len(r) >= 7 for n, v in zip(names, r[3:7]) if v.lower().startswith("active")})
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": reasons}
+        busy = [s for s, p in zip(sm, pw) if p >= 0.5 * max(pw)] if pw else sm  # samples taken under load
+        return {"sm_mhz": statistics.median(busy or sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "power_w_max": max(pw) if pw else None, "reasons": reasons}
 
 
-def measured_peak():
+def measured_peaks():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
     except Exception:
-        return 6650.0, "fallback"
-
-
-def measured_tensor_peak():
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            return float(json.load(f)["bf16_tflops"]), "measured"
-    except Exception:
-        return 1590.0, "fallback"
+        return 6650.0, 1590.0, 1400.0, "fallback"
 
 
 def ncu_traffic(key):
@@ -131,42 +144,234 @@ def ncu_traffic(key):
         return None
 
 
-def build_layers(synth, cfg, n_layers, distinct_weight_layers=None):
-    """Per layer: expert blobs, shared-expert blob, router.  With distinct_weight_layers = m the expert weights of
-    layer l are those of layer l % m (a deep resident stack without minutes of host-side generation); routers and
-    activations stay distinct per layer."""
-    layers = []
-    m = distinct_weight_layers or n_layers
-    for l in range(n_layers):
-        if l < m:
-            blobs = [synth.make_expert_blob(cfg.dtype, cfg.d_model, cfg.d_ff, cfg.seed, l, e) for e in range(cfg.num_experts)]
-            shared = synth.make_expert_blob(cfg.dtype, cfg.d_model, cfg.d_ff, cfg.seed, l, cfg.num_experts) if cfg.shared else None
-        else:
-            blobs, shared = layers[l % m][0], layers[l % m][1]
-        layers.append((blobs, shared, synth.make_router(cfg.num_experts, cfg.d_model, cfg.seed, l)))
-    return layers
+def zipf_bias(synth, cfg, zipf_s, layer, strength):
+    return None if zipf_s is None else synth.zipf_logit_bias(cfg.num_experts, zipf_s, cfg.seed, layer, strength=strength)
 
 
-def cpu_layer_rate(oracle, cfg, layer, x, threads, seconds, steps=None, warmup=1):
-    """tokens/s of the CPU path on (a bounded sample of) the same step."""
-    blobs, shared, W = layer
-    gate = oracle.LinearGate(W, cfg.num_experts, cfg.d_model, cfg.top_k, scoring_func=cfg.scoring, n_group=cfg.n_group,
-                             topk_group=cfg.topk_group, routed_scaling_factor=cfg.scaling)
+def host_blobs(synth, cfg, layer, experts, threads):
+    """Expert blobs of one layer on the host (numpy generator), generated by a pool of threads."""
+    with ThreadPoolExecutor(max_workers=max(1, threads)) as pool:
+        return dict(zip(experts, pool.map(lambda e: synth.make_expert_blob(cfg.dtype, cfg.d_model, cfg.d_ff, cfg.seed, layer, e),
+                                          experts)))
+
+
+def oracle_gate(oracle, synth, cfg, layer, zipf_s, strength):
+    W = synth.make_router(cfg.num_experts, cfg.d_model, cfg.seed, layer)
+    return oracle.LinearGate(W, cfg.num_experts, cfg.d_model, cfg.top_k, scoring_func=cfg.scoring, n_group=cfg.n_group,
+                             topk_group=cfg.topk_group, routed_scaling_factor=cfg.scaling,
+                             logit_bias=zipf_bias(synth, cfg, zipf_s, layer, strength))
+
+
+def parity_check(oracle, synth, cfg, layer, zipf_s, strength, x_rows, got_rows, got_ids, threads):
+    """Recomputes the given token rows of `layer` with the CPU oracle.  Returns the `parity` object; raises SystemExit
+    when routing differs on a token that is not tie-ambiguous or an output exceeds the bar."""
+    gate = oracle_gate(oracle, synth, cfg, layer, zipf_s, strength)
+    routed = [gate.route(x, detail=True) for x in x_rows]
+    need = sorted({int(e) for ids, _, _, _ in routed for e in ids})
+    blobs = host_blobs(synth, cfg, layer, need + ([cfg.num_experts] if cfg.shared else []), threads)
+    filler = np.zeros(synth.expert_bytes(cfg.dtype, cfg.d_model, cfg.d_ff), np.uint8)  # experts no checked token is routed to
+    blob_list = [blobs.get(e, filler) for e in range(cfg.num_experts)]
+    ref, rids, _, gaps = oracle.moe_layer_forward(cfg.dtype, gate, blob_list, np.stack(x_rows), cfg.d_ff,
+                                                  shared_blob=blobs.get(cfg.num_experts) if cfg.shared else None, n_threads=threads)
+    worst, identical, checked = 0.0, True, 0
+    for t in range(len(x_rows)):
+        ids, _, scores, gap = routed[t]
+        sel = np.sort(scores[ids])
+        if gap < 1e-6 * float(np.abs(sel).max()) or (np.diff(sel) < 1e-6 * np.abs(sel[1:])).any():
+            continue  # scores tie within the logit summation noise: the choice or its order is ambiguous, not wrong
+        checked += 1
+        if got_ids is not None and [int(v) for v in got_ids[t]] != [int(v) for v in rids[t]]:
+            identical = False
+        rms = float(np.sqrt(np.mean(ref[t].astype(np.float64) ** 2))) + 1e-30
+        worst = max(worst, float(np.abs(got_rows[t].astype(np.float64) - ref[t]).max()) / rms)
+    par = {"tokens": checked, "max_rel_rms": worst, "topk_identical": identical, "bar": PARITY_BAR, "layer": layer}
+    if checked == 0 or not identical or not (worst <= PARITY_BAR):
+        raise SystemExit(f"bench.py: parity check against the CPU oracle failed: {par}")
+    return par
+
+
+def cpu_rate(oracle, synth, cfg, layer, zipf_s, strength, x, threads, seconds, steps=None, warmup=1):
+    """tokens/s of the CPU path on (a bounded sample of) one layer pass of the step."""
+    experts = list(range(cfg.num_experts + (1 if cfg.shared else 0)))
+    blobs = host_blobs(synth, cfg, layer, experts, threads)
+    gate = oracle_gate(oracle, synth, cfg, layer, zipf_s, strength)
+    blob_list = [blobs[e] for e in range(cfg.num_experts)]
+    shared = blobs.get(cfg.num_experts) if cfg.shared else None
+    run = lambda rows: oracle.moe_layer_forward_production(cfg.dtype, gate, blob_list, rows, cfg.d_ff, threads, shared_blob=shared)
     t0 = time.perf_counter()
-    oracle.moe_layer_forward_production(cfg.dtype, gate, blobs, x[:1], cfg.d_ff, threads, shared_blob=shared)
+    run(x[:1])
     per_token = time.perf_counter() - t0
     n_tok = int(max(1, min(x.shape[0], seconds / 4 / max(per_token, 1e-6))))
     sample = x[:n_tok]
     for _ in range(warmup):
-        oracle.moe_layer_forward_production(cfg.dtype, gate, blobs, sample, cfg.d_ff, threads, shared_blob=shared)
+        run(sample)
     reps, t0 = 0, time.perf_counter()
     while True:
-        oracle.moe_layer_forward_production(cfg.dtype, gate, blobs, sample, cfg.d_ff, threads, shared_blob=shared)
+        run(sample)
         reps += 1
         el = time.perf_counter() - t0
         if (steps is not None and reps >= steps) or (steps is None and (el > seconds / 2 or reps >= 50)):
             break
-    return n_tok * reps / el, el / reps * 1e3, f"{n_tok} of {x.shape[0]} tokens of one step, {reps} repetitions, {threads} threads"
+    return n_tok * reps / el, el / reps * 1e3, f"{n_tok} of {x.shape[0]} tokens of one layer pass, {reps} repetitions, {threads} threads"
+
+
+class Stack:
+    """A resident stack of MoE layers of one configuration on one backend."""
+
+    def __init__(self, mer_b200, synth, cfg, n_layers, max_tokens, device_index, mine=None, rank_tokens=None):
+        import torch
+        self.mer, self.synth, self.cfg, self.L = mer_b200, synth, cfg, n_layers
+        self.torch, self.dev = torch, torch.device("cuda", device_index)
+        self.mine = list(range(cfg.num_experts)) if mine is None else list(mine)
+        self.slots = cfg.top_k + (1 if cfg.shared else 0)
+        self.exp_bytes = mer_b200.expert_bytes(cfg.dtype, cfg.d_model, cfg.d_ff)
+        stride = (256 + self.exp_bytes + 4095) // 4096 * 4096
+        n_local = len(self.mine) + (1 if cfg.shared else 0)
+        self.be = mer_b200.Backend(cfg.dtype, cfg.d_model, cfg.d_ff, stride * n_local * n_layers,
+                                   (n_layers + 1) * cfg.num_experts + n_layers, max_tokens=max_tokens, max_top_k=self.slots,
+                                   device=device_index)
+        self.resident_bytes = self.exp_bytes * n_local * n_layers
+        # fill the slots: every layer's experts are generated in device memory (seed = the configuration's, layer = its index)
+        chunk = max(1, int((1 << 30) // (self.exp_bytes * 10)))  # the generator's 64-bit temporaries are ~10x the blob
+        for l in range(n_layers):
+            todo = [(e, l * cfg.num_experts + e) for e in self.mine]
+            if cfg.shared:
+                todo.append((cfg.num_experts, n_layers * cfg.num_experts + l))
+            for i in range(0, len(todo), chunk):
+                part = todo[i:i + chunk]
+                blobs = synth.make_expert_blobs_torch(cfg.dtype, cfg.d_model, cfg.d_ff, cfg.seed, l, [e for e, _ in part], self.dev)
+                torch.cuda.synchronize()  # the admission runs on the library's copy stream: the bytes must be there first
+                for j, (_, gid) in enumerate(part):
+                    self.be.admit_device(gid, 1, blobs[j].data_ptr(), self.exp_bytes, wait=False)
+                self.be.synchronize()  # the admission reads the generator's tensor: keep it alive until the copy stream is done
+                del blobs
+
+    def install_routers(self, zipf_s, strength):
+        m = self.mer
+        for l in range(self.L):
+            cfg = self.cfg
+            gate = m.LinearGate.with_routing(self.synth.make_router(cfg.num_experts, cfg.d_model, cfg.seed, l), cfg.num_experts,
+                                             cfg.d_model, cfg.top_k, cfg.scoring, True, None, cfg.n_group, cfg.topk_group, cfg.scaling)
+            gate.logit_bias = zipf_bias(self.synth, cfg, zipf_s, l, strength)
+            self.be.install_router(l, gate, self.L * cfg.num_experts + l if cfg.shared else 0xFFFFFFFF)
+
+    def close(self):
+        self.be.close()
+
+
+def cuda_time_ms(torch, fn):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1)
+
+
+def measure_point(stack, name, zipf_s, B, layers, passes, warm, peaks, x_seed_base=0):
+    """One single-GPU measurement: `passes` layer passes of a B-token batch rotating over `layers` resident layers.
+    Returns (entry dict, per-layer hit-expert bytes)."""
+    torch, be, cfg, synth = stack.torch, stack.be, stack.cfg, stack.synth
+    hbm_peak, tf_burst, tf_sustained, kind = peaks
+    xs_host = [synth.make_activations(B, cfg.d_model, cfg.seed, x_seed_base + i) for i in range(min(len(layers), 8))]
+    xs = [torch.from_numpy(x).to(stack.dev) for x in xs_host]
+    out = torch.empty(B, cfg.d_model, device=stack.dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    hit = []
+    for i, l in enumerate(layers):
+        _, ids, _ = be.moe_layer_forward(l, xs_host[i % len(xs)])
+        hit.append((len(np.unique(ids[ids != 0xFFFFFFFF])) + (1 if cfg.shared else 0)) * stack.exp_bytes)
+
+    def run(n):
+        for i in range(n):
+            be.moe_layer_forward_device(layers[i % len(layers)], xs[(i % len(layers)) % len(xs)].data_ptr(), B, out.data_ptr(), stream)
+
+    run(max(warm, 3))
+    ms = cuda_time_ms(torch, lambda: run(passes))
+    be.stream_check(layers[0], stream)
+    n_t = min(passes, 2048)
+    be.stage_timing_enable(True)
+    run(n_t)
+    torch.cuda.synchronize()
+    st = be.stage_timings()
+    be.stage_timing_enable(False)
+    n = max(st["samples"], 1)
+    gu_ms, dn_ms = st["expert_gate_up_kernel_ms"] / n, st["expert_down_kernel_ms"] / n
+    mean_hit = sum(hit[i % len(layers)] for i in range(passes)) / passes
+    layer_bytes = mean_hit + cfg.num_experts * cfg.d_model * 4 + 2 * B * cfg.d_model * 4 + B * cfg.top_k * 8
+    per_layer_ms = ms / passes
+    gemm = B * stack.slots >= GEMM_MEAN_TOKENS * (cfg.num_experts + (1 if cfg.shared else 0))
+    if gemm:
+        flops = 2.0 * B * stack.slots * 2 * cfg.d_model * cfg.d_ff
+        tf = flops / (gu_ms * 1e-3) / 1e12 if gu_ms > 0 else None
+        roof = {"bound": "tensor", "kernel": "expert_gate_up (grouped dequant GEMM, tcgen05, + SiLU*mul)", "achieved": tf, "peak": tf_burst,
+                "unit": "TFLOP/s", "frac": tf / tf_burst if tf else None, "peak_source": f"of {kind} (burst)",
+                "frac_of_sustained_peak": tf / tf_sustained if tf else None, "algorithmic_flops_per_launch": flops, "avg_launch_ms": gu_ms}
+    else:
+        fused = dn_ms == 0.0
+        kb = (mean_hit if fused else mean_hit * 2 / 3) + B * cfg.d_model * 4
+        ach = kb / (gu_ms * 1e-3) / 1e9 if gu_ms > 0 else None
+        roof = {"bound": "hbm", "kernel": "expert_gate_up (gate/up dequant-matvec + SiLU*mul)", "achieved": ach, "peak": hbm_peak,
+                "unit": "GB/s", "frac": ach / hbm_peak if ach else None, "peak_source": f"of {kind}",
+                "frac_of_8tbs": ach / 8000.0 if ach else None, "algorithmic_bytes_per_launch": kb, "avg_launch_ms": gu_ms}
+    layer_gbs = layer_bytes / (per_layer_ms * 1e-3) / 1e9
+    entry = {"workload": name, "batch": B, "layers_rotated": len(layers), "passes": passes, "tokens_per_s": B / (per_layer_ms * 1e-3),
+             "ms_per_layer": per_layer_ms, "roofline": roof,
+             "hbm": {"layer_algorithmic_bytes": layer_bytes, "achieved_gbs": layer_gbs, "frac_of_measured": layer_gbs / hbm_peak,
+                     "frac_of_8tbs": layer_gbs / 8000.0},
+             "stage_ms": {k: v / n for k, v in st.items() if k != "samples"}}
+    return entry, xs_host, xs, out
+
+
+def run_sweep(mer_b200, synth, oracle, args, qwen_stack, local_rank, peaks, threads):
+    """The other configurations at their stated decode batches.  cfg1 runs on the resident Qwen3 stack (same shapes
+    and seed as cfg3), cfg0 on the Mixtral stack of cfg2."""
+    import torch
+    entries = []
+
+    def point(stack, wl, zipf_s, B, n_rot):
+        cfg_name = WORKLOADS[wl][0]
+        layers = list(range(min(stack.L, n_rot)))
+        target_s = 0.15
+        probe, *_ = measure_point(stack, cfg_name, zipf_s, B, layers, 16, 3, peaks)
+        passes = int(min(4000, max(32, target_s / (probe["ms_per_layer"] * 1e-3))))
+        entry, xs_host, xs, out = measure_point(stack, cfg_name, zipf_s, B, layers, passes, 3, peaks)
+        # parity of this point: a few tokens of the first rotated layer against the oracle
+        stream = torch.cuda.current_stream().cuda_stream
+        ids_dev = torch.empty(B, stack.slots, dtype=torch.int32, device=stack.dev)
+        stack.be.moe_layer_forward_device(layers[0], xs[0].data_ptr(), B, out.data_ptr(), stream, d_ids=ids_dev.data_ptr())
+        stack.be.stream_check(layers[0], stream)
+        n = min(PARITY_TOKENS, B)
+        got = out[:n].cpu().numpy()
+        gids = ids_dev[:n, :stack.cfg.top_k].cpu().numpy().astype(np.int64) - layers[0] * stack.cfg.num_experts
+        entry["parity"] = parity_check(oracle, synth, stack.cfg, layers[0], zipf_s, args.zipf_strength, list(xs_host[0][:n]), got, gids,
+                                       threads)
+        entries.append(entry)
+
+    if qwen_stack is not None:
+        qwen_stack.install_routers(None, 0.0)
+        for B in dict(SWEEP)["cfg1"]:
+            point(qwen_stack, "cfg1", None, B, 8)
+        qwen_stack.close()
+    torch.cuda.empty_cache()
+    cfg2 = synth.CONFIGS[WORKLOADS["cfg2"][0]]
+    st = Stack(mer_b200, synth, cfg2, WORKLOADS["cfg2"][2], 256, local_rank)
+    st.install_routers(WORKLOADS["cfg2"][3], args.zipf_strength)
+    for B in dict(SWEEP)["cfg2"]:
+        point(st, "cfg2", WORKLOADS["cfg2"][3], B, 32)
+    st.install_routers(None, 0.0)
+    for B in dict(SWEEP)["cfg0"]:
+        point(st, "cfg0", None, B, 8)
+    st.close()
+    torch.cuda.empty_cache()
+    cfg4 = synth.CONFIGS[WORKLOADS["cfg4"][0]]
+    st = Stack(mer_b200, synth, cfg4, 1, 64, local_rank)
+    st.install_routers(None, 0.0)
+    for B in dict(SWEEP)["cfg4"]:
+        point(st, "cfg4", None, B, 1)
+    st.close()
+    return entries
 
 
 def main():
@@ -177,9 +382,13 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    cfg_name, def_batch, def_layers = WORKLOADS[args.workload]
-    B = args.batch or def_batch
-    R = args.layers or def_layers
+    cfg_name, def_batch, def_layers, zipf_s = WORKLOADS[args.workload]
+    strong = args.workload == "cfg3"  # a fixed global batch split over the ranks; the other workloads keep B per GPU
+    B_global = args.batch or def_batch
+    if strong and world > 1:
+        assert B_global % world == 0, "the global batch must divide by the number of GPUs"
+    B = B_global // world if strong else B_global  # tokens this rank brings to a step
+    L = args.layers or def_layers
     mode = args.parallelism
     if mode == "auto":
         mode = "ep-peer" if world > 1 else "replicas"
@@ -189,27 +398,35 @@ def main():
     import mer_b200  # noqa: F401  (registers the package alias)
     synth = importlib.import_module("mer_b200.synth")
     cfg = synth.CONFIGS[cfg_name]
-    workload = f"{cfg_name} decode batch {B}: 1 MoE layer/step, {cfg.num_experts} experts top-{cfg.top_k}, D={cfg.d_model} F={cfg.d_ff}"
+    threads = os.cpu_count() or 1
+    kind = "prefill" if B_global * cfg.top_k >= GEMM_MEAN_TOKENS * cfg.num_experts else "decode"
+    skew = f", Zipf(s={zipf_s}) logit bias x{args.zipf_strength:g}" if zipf_s is not None else ""
+    workload = (f"{cfg_name} {kind}: a {B_global}-token batch through {L} resident MoE layers per step "
+                f"({cfg.num_experts} experts top-{cfg.top_k}, D={cfg.d_model} F={cfg.d_ff}{skew}; weights and routers seeded per layer)")
     base = {"metric": "moe_layer_tokens_per_s", "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic"}
-    config = {"workload": workload, "weights": DTYPE_NAME[cfg.dtype], "batch_per_gpu": B, "resident_layers": R,
-              "l2": f"steps rotate over {R} distinct resident layers; one step streams more expert bytes than L2 holds" if R > 1
-              else "single layer", "parallelism": "single GPU" if args.gpus == 1 else PARALLELISM_NOTE[mode].format(n=args.gpus)}
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic"}
+    exp_bytes = synth.expert_bytes(cfg.dtype, cfg.d_model, cfg.d_ff)
+    config = {"workload": workload, "weights": DTYPE_NAME[cfg.dtype], "global_batch": B_global if strong else B * world,
+              "batch_per_gpu": B, "resident_layers": L, "layer_passes_per_step": L,
+              "resident_expert_gb": round(exp_bytes * (cfg.num_experts + (1 if cfg.shared else 0)) * L / 1e9, 2),
+              "value_counts": "tokens x layers per second = tokens/s through one MoE layer",
+              "l2": f"a step streams {L} distinct resident layers; every layer pass reads more expert bytes than L2 holds",
+              "parallelism": "single GPU" if args.gpus == 1 else PARALLELISM_NOTE[mode].format(n=args.gpus)}
 
     if args.impl == "reference":
         if rank != 0:
             return
         import oracle
         oracle.build()
-        threads = os.cpu_count() or 1
-        layer = build_layers(synth, cfg, 1)[0]
-        x = synth.make_activations(B, cfg.d_model, cfg.seed, 0)
-        rate, ms, sample = cpu_layer_rate(oracle, cfg, layer, x, threads, args.cpu_seconds * 4, steps=args.steps, warmup=args.warmup)
+        x = synth.make_activations(B_global, cfg.d_model, cfg.seed, 0)
+        rate, ms, sample = cpu_rate(oracle, synth, cfg, 0, zipf_s, args.zipf_strength, x, threads, args.cpu_seconds * 4,
+                                    steps=args.steps, warmup=max(1, min(args.warmup, 2)))
         line = dict(base, impl="reference", value=rate, ms_per_step=ms, config=config,
                     cpu_baseline={"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
                     e2e={"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-                    note="the reference is Rust and cannot be built here; this is the C restatement of its CPU kernels (oracle/)")
+                    note="the reference is Rust and cannot be built here; this is the C restatement of its CPU kernels (oracle/); "
+                         "each timed step is a bounded sample of one layer pass, ms_per_step is that sample's time")
         json_out.write(json.dumps(line) + "\n")
         json_out.flush()
         return
@@ -221,56 +438,26 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    import oracle
+    oracle.build()
+    peaks = measured_peaks()
+    hbm_peak, tf_burst, tf_sustained, peak_kind = peaks
 
-    slots = cfg.top_k + (1 if cfg.shared else 0)
-    n_exp = cfg.num_experts + (1 if cfg.shared else 0)
-    exp_bytes = mer_b200.expert_bytes(cfg.dtype, cfg.d_model, cfg.d_ff)
-    stride = (256 + exp_bytes + 4095) // 4096 * 4096
     epm = importlib.import_module("mer_b200.expert_parallel")
-    mine = set(epm.local_expert_range(rank, world, cfg.num_experts)) if ep_mode else set(range(cfg.num_experts))
-    n_local = len(mine) + (1 if cfg.shared else 0)
-    be = mer_b200.Backend(cfg.dtype, cfg.d_model, cfg.d_ff, stride * n_local * R, (R + 1) * cfg.num_experts + R,
-                          max_tokens=B * world if ep_mode else B, max_top_k=slots, device=local_rank)
+    mine = list(epm.local_expert_range(rank, world, cfg.num_experts)) if ep_mode else list(range(cfg.num_experts))
+    stack = Stack(mer_b200, synth, cfg, L, B * world if ep_mode else B, local_rank, mine=mine)
+    be, slots = stack.be, stack.slots
     if args.kernel_path:
         be.set_kernel_path(args.kernel_path)
-    layers = build_layers(synth, cfg, R, distinct_weight_layers=2 if args.workload == "cfg2" else None)
-    hit_bytes = []
-    xs_host = []
-    for l, (blobs, shared, W) in enumerate(layers):
-        for e, blob in enumerate(blobs):
-            if e in mine:
-                be.admit(l * cfg.num_experts + e, 1, blob, wait=False)
-        shared_id = 0xFFFFFFFF
-        if shared is not None:
-            shared_id = R * cfg.num_experts + l
-            be.admit(shared_id, 1, shared, wait=False)
-        gate = mer_b200.LinearGate.with_routing(W, cfg.num_experts, cfg.d_model, cfg.top_k, cfg.scoring, True, None, cfg.n_group,
-                                                cfg.topk_group, cfg.scaling)
-        if args.workload in ZIPF:
-            gate.logit_bias = synth.zipf_logit_bias(cfg.num_experts, ZIPF[args.workload], cfg.seed, l, strength=0.25)
-        be.install_router(l, gate, shared_id)
-        xs_host.append(synth.make_activations(B, cfg.d_model, cfg.seed, rank * R + l))
+    stack.install_routers(zipf_s, args.zipf_strength)
     be.synchronize()
-    keep_for_cpu = layers[0] if (rank == 0 and args.gpus == 1 and not args.no_cpu) else None
-    x_cpu = xs_host[0]
-    del layers
 
-    dev = torch.device("cuda", local_rank)
+    dev = stack.dev
+    n_x = min(L, 8)  # distinct activation batches, rotated over the layers
+    xs_host = [synth.make_activations(B, cfg.d_model, cfg.seed, rank * 64 + i) for i in range(n_x)]
     xs = [torch.from_numpy(x).to(dev) for x in xs_host]
     out = torch.empty(B, cfg.d_model, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
-    for l in range(R):  # routing per layer -> distinct (local) experts hit -> algorithmic bytes of this rank
-        if ep_mode:
-            x_all = np.concatenate([synth.make_activations(B, cfg.d_model, cfg.seed, r * R + l) for r in range(world)])
-            ids, _ = be.route(l, x_all)
-            hit = [e for e in np.unique(ids[ids != 0xFFFFFFFF]) if int(e) in mine]
-            distinct = len(hit) + (1 if cfg.shared else 0)
-        else:
-            _, ids, _ = be.moe_layer_forward(l, xs_host[l])
-            distinct = len(np.unique(ids[ids != 0xFFFFFFFF])) + (1 if cfg.shared else 0)
-        hit_bytes.append(distinct * exp_bytes)
-    router_bytes = cfg.num_experts * cfg.d_model * 4
-    io_bytes = 2 * B * cfg.d_model * 4 + B * cfg.top_k * 8
 
     ep = None
     if ep_mode:
@@ -279,10 +466,7 @@ def main():
             ep.attach()
             dist.barrier()
 
-    def step(i, x=None, o=None):
-        l = i % R
-        x = xs[l] if x is None else x
-        o = out if o is None else o
+    def layer_pass(l, x, o):
         if mode == "ep-peer":
             ep.layer_forward_peer(l, x.data_ptr(), B, o.data_ptr(), stream)
         elif mode == "ep-collective":
@@ -290,15 +474,40 @@ def main():
         else:
             be.moe_layer_forward_device(l, x.data_ptr(), B, o.data_ptr(), stream)
 
+    def step():
+        for l in range(L):
+            layer_pass(l, xs[l % n_x], out)
+
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
             torch.cuda.synchronize()
 
+    # ---- parity (outside the timed region): rank 0 recomputes a few of its own tokens of layer 0 with the oracle
+    parity = None
+    ids_dev = torch.empty(B, slots, dtype=torch.int32, device=dev)
+    if ep_mode:
+        layer_pass(0, xs[0], out)
+        ep.check(0, stream)
+        gids = None
+        if rank == 0:
+            rid, _ = be.route(0, xs_host[0][:PARITY_TOKENS])
+            gids = rid.astype(np.int64)
+    else:
+        be.moe_layer_forward_device(0, xs[0].data_ptr(), B, out.data_ptr(), stream, d_ids=ids_dev.data_ptr())
+        be.stream_check(0, stream)
+        gids = ids_dev[:PARITY_TOKENS, :cfg.top_k].cpu().numpy().astype(np.int64)  # layer 0: global id = local id
+    if rank == 0:
+        n = min(PARITY_TOKENS, B)
+        parity = parity_check(oracle, synth, cfg, 0, zipf_s, args.zipf_strength, list(xs_host[0][:n]), out[:n].cpu().numpy(),
+                              gids[:n], threads)
+    barrier()
+
+    # ---- the timed region: exactly K steps, CUDA events on the launching stream, max over ranks
     sampler = ClockSampler(local_rank)
-    for i in range(max(args.warmup, 3)):
-        step(i)
+    for _ in range(max(args.warmup, 3)):
+        step()
     barrier()
     if rank == 0:
         sampler.start()
@@ -306,130 +515,159 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    for i in range(args.steps):
-        step(i)
+    for _ in range(args.steps):
+        step()
     e1.record()
     barrier()
     ms_total = e0.elapsed_time(e1)
     launches = be.snapshot()["kernel_launches"] - launches0
+    # a latched device status (bounded wait expired, missing expert, non-finite router) fails the run here
     if ep_mode:
-        ep.check(0, stream)  # surfaces a latched device status (a peer that never answered, a missing expert)
+        ep.check(0, stream)
     else:
-        be.synchronize()
+        be.stream_check(0, stream)
 
-    # stage timing pass (same steps, events around each stage) for the roofline of the dominant kernel
+    # ---- stage timers (same steps, events around each stage) for the roofline of the dominant kernel
     st = None
+    hit_bytes = []
     if not ep_mode:
+        for l in range(L):
+            _, ids, _ = be.moe_layer_forward(l, xs_host[l % n_x])
+            hit_bytes.append((len(np.unique(ids[ids != 0xFFFFFFFF])) + (1 if cfg.shared else 0)) * exp_bytes)
         be.stage_timing_enable(True)
-        for i in range(args.steps):
-            step(i)
+        for _ in range(max(1, min(args.steps, 4000 // L))):
+            step()
         torch.cuda.synchronize()
         st = be.stage_timings()
         be.stage_timing_enable(False)
-
-    # end to end: host buffers in, host buffers out, copies inside the timed region
-    pinned_in = [torch.from_numpy(x).pin_memory() for x in xs_host]
-    pinned_out = torch.empty(B, cfg.d_model).pin_memory()
-    x_dev = torch.empty(B, cfg.d_model, device=dev)
-
-    def e2e_step(i):
-        if ep_mode:  # pinned host rows -> device, the expert-parallel layer, result back to pinned host memory
-            x_dev.copy_(pinned_in[i % R], non_blocking=True)
-            step(i, x_dev, out)
-            pinned_out.copy_(out, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-        else:  # the library's host entry point does the same copies itself
-            be.moe_layer_forward(i % R, pinned_in[i % R].numpy(), return_routing=False, out=pinned_out.numpy())
-
-    for i in range(3):
-        e2e_step(i)
-    barrier()
-    if mode == "ep-collective":
-        t0 = time.perf_counter()
-        for i in range(args.steps):
-            e2e_step(i)
-        torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
     else:
-        # independent token batches through the pipelined host entry: every step uploads its pinned rows and reads its
-        # result back to pinned memory; upload, layer and read-back of neighbouring steps overlap (three in flight)
+        for l in range(L):
+            x_all = np.concatenate([synth.make_activations(B, cfg.d_model, cfg.seed, r * 64 + (l % n_x)) for r in range(world)])
+            ids, _ = be.route(l, x_all)
+            hit = [e for e in np.unique(ids[ids != 0xFFFFFFFF]) if int(e) in set(mine)]
+            hit_bytes.append((len(hit) + (1 if cfg.shared else 0)) * exp_bytes)
+
+    # ---- end to end: host buffers in, host buffers out, copies inside the timed region
+    e2e_ms = e2e_sync_ms = None
+    if not args.no_e2e:
+        pinned_in = [torch.from_numpy(x).pin_memory() for x in xs_host]
         depth = 3
         outs = [torch.empty(B, cfg.d_model).pin_memory() for _ in range(depth)]
-        submit = ep.layer_forward_peer_submit if mode == "ep-peer" else be.moe_layer_forward_submit
-        for i in range(depth):  # warm the slots (allocations, graph capture)
-            submit(i % R, pinned_in[i % R].numpy(), outs[i].numpy(), i)
-        for i in range(depth):
-            be.moe_layer_forward_wait(i)
+        if mode == "ep-collective":
+            x_dev = torch.empty(B, cfg.d_model, device=dev)
+
+            def e2e_steps(k):
+                for _ in range(k):
+                    for l in range(L):
+                        x_dev.copy_(pinned_in[l % n_x], non_blocking=True)
+                        layer_pass(l, x_dev, out)
+                        outs[0].copy_(out, non_blocking=True)
+                        torch.cuda.current_stream().synchronize()
+        else:
+            submit = ep.layer_forward_peer_submit if mode == "ep-peer" else be.moe_layer_forward_submit
+
+            def e2e_steps(k):
+                # independent layer calls through the pipelined host entry: every call uploads its pinned rows and reads
+                # its result back to pinned memory; upload, layer and read-back of neighbouring calls overlap
+                n_calls = k * L
+                for i in range(n_calls + depth):
+                    if i >= depth:
+                        be.moe_layer_forward_wait(i % depth)
+                    if i < n_calls:
+                        l = i % L
+                        submit(l, pinned_in[l % n_x].numpy(), outs[i % depth].numpy(), i % depth)
+        e2e_steps(1)
         barrier()
         t0 = time.perf_counter()
-        for i in range(args.steps + depth):
-            if i >= depth:
-                be.moe_layer_forward_wait(i % depth)
-            if i < args.steps:
-                submit(i % R, pinned_in[i % R].numpy(), outs[i % depth].numpy(), i % depth)
+        e2e_steps(args.steps)
         torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+        if not ep_mode:
+            pin_out = outs[0]
+            for l in range(L):  # first call per (layer, buffers) captures its graph
+                be.moe_layer_forward(l, pinned_in[l % n_x].numpy(), return_routing=False, out=pin_out.numpy())
+            n_sync = max(1, min(args.steps, 5))
+            t0 = time.perf_counter()
+            for _ in range(n_sync):
+                for l in range(L):
+                    be.moe_layer_forward(l, pinned_in[l % n_x].numpy(), return_routing=False, out=pin_out.numpy())
+            e2e_sync_ms = (time.perf_counter() - t0) * 1e3 * args.steps / n_sync
     clocks = sampler.stop() if rank == 0 else None
 
-    times = torch.tensor([ms_total, e2e_s * 1e3], device=dev, dtype=torch.float64)
+    times = torch.tensor([ms_total, e2e_ms or 0.0, e2e_sync_ms or 0.0], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms = float(times[0]), float(times[1])
+    ms_total, e2e_ms, e2e_sync_ms = float(times[0]), float(times[1]) or None, float(times[2]) or None
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
     steps = args.steps
-    tokens = B * steps * world
-    value = tokens / (ms_total * 1e-3)
-    mean_hit = sum(hit_bytes[i % R] for i in range(steps)) / steps
+    tokens_global = (B_global if strong else B * world)
+    layer_tokens = tokens_global * L * steps  # tokens x layers over the timed region, all ranks
+    value = layer_tokens / (ms_total * 1e-3)
+    mean_hit = sum(hit_bytes) / len(hit_bytes)
+    router_bytes = cfg.num_experts * cfg.d_model * 4
+    io_bytes = 2 * B * cfg.d_model * 4 + B * cfg.top_k * 8
     layer_bytes = mean_hit + router_bytes + io_bytes
-    hbm_gbs = layer_bytes * steps / (ms_total * 1e-3) / 1e9
-    peak, peak_kind = measured_peak()
+    per_layer_ms = ms_total / (steps * L)
+    hbm_gbs = layer_bytes / (per_layer_ms * 1e-3) / 1e9
+    gemm = tokens_global * slots >= GEMM_MEAN_TOKENS * (cfg.num_experts + (1 if cfg.shared else 0))
+    traffic = ncu_traffic(f"{args.workload}-b{B_global}")
+    stages = None
     if st is not None:
         n = max(st["samples"], 1)
         gu_ms, dn_ms = st["expert_gate_up_kernel_ms"] / n, st["expert_down_kernel_ms"] / n
-        fused = dn_ms == 0.0
-        kernel_bytes = (mean_hit if fused else mean_hit * 2 / 3) + B * cfg.d_model * 4
-        achieved = kernel_bytes / (gu_ms * 1e-3) / 1e9 if gu_ms > 0 else None
-        kname = "expert_ffn (gate/up + SiLU*mul + down)" if fused else "expert_gate_up (gate/up dequant-matvec + SiLU*mul)"
-        roofline = {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": achieved / peak if achieved else None, "peak_source": f"of {peak_kind}",
-                    "traffic": ncu_traffic(f"{args.workload}-b{B}"), "algorithmic_bytes_per_launch": kernel_bytes,
-                    "avg_launch_ms": gu_ms, "frac_of_8tbs": achieved / 8000.0 if achieved else None}
         stages = {k: v / n for k, v in st.items() if k != "samples"}
-        if B * slots >= 32 * n_exp and not fused and gu_ms > 0:
-            # a mean of 32 tokens per expert and more: the tcgen05 GEMM kernels run, bounded by the tensor pipe.
+        if gemm and gu_ms > 0:
             # Algorithmic FLOPs of the gate/up launch: every (token, slot) pair through two [F x D] projections.
-            tpeak, tkind = measured_tensor_peak()
             flops = 2.0 * B * slots * 2 * cfg.d_model * cfg.d_ff
             tf = flops / (gu_ms * 1e-3) / 1e12
             roofline = {"bound": "tensor", "kernel": "expert_gate_up (grouped dequant GEMM, tcgen05, + SiLU*mul)", "achieved": tf,
-                        "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak, "peak_source": f"of {tkind}",
-                        "traffic": ncu_traffic(f"{args.workload}-b{B}"), "algorithmic_flops_per_launch": flops,
+                        "peak": tf_burst, "unit": "TFLOP/s", "frac": tf / tf_burst, "peak_source": f"of {peak_kind} (burst figure)",
+                        "frac_of_sustained_peak": tf / tf_sustained, "traffic": traffic, "algorithmic_flops_per_launch": flops,
                         "avg_launch_ms": gu_ms,
                         "note": "each algorithmic product is issued as three f16 MMAs (hi*hi, hi*lo, lo*hi) to hold the fp32 "
                                 "parity bar, so the tensor pipe does 3x these FLOPs"}
+        else:
+            fused = dn_ms == 0.0
+            kernel_bytes = (mean_hit if fused else mean_hit * 2 / 3) + B * cfg.d_model * 4
+            achieved = kernel_bytes / (gu_ms * 1e-3) / 1e9 if gu_ms > 0 else None
+            roofline = {"bound": "hbm", "kernel": "expert_gate_up (gate/up dequant-matvec + SiLU*mul)", "achieved": achieved, "peak": hbm_peak,
+                        "unit": "GB/s", "frac": achieved / hbm_peak if achieved else None, "peak_source": f"of {peak_kind}",
+                        "traffic": traffic, "algorithmic_bytes_per_launch": kernel_bytes, "avg_launch_ms": gu_ms,
+                        "frac_of_8tbs": achieved / 8000.0 if achieved else None}
+    elif gemm:
+        # expert-parallel step: no per-stage timers; rank 0's share of the layer's algorithmic FLOPs over its whole layer pass
+        flops = 2.0 * tokens_global * slots * 3 * cfg.d_model * cfg.d_ff / world
+        tf = flops / (per_layer_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": "whole expert-parallel layer pass of one rank (router, exchange, local experts, combine)",
+                    "achieved": tf, "peak": tf_burst, "unit": "TFLOP/s", "frac": tf / tf_burst, "peak_source": f"of {peak_kind} (burst figure)",
+                    "traffic": None, "algorithmic_flops_per_launch": flops, "avg_launch_ms": per_layer_ms}
     else:
-        # expert-parallel step: no per-stage timers; the whole step of rank 0 against the bytes its experts stream
-        roofline = {"bound": "hbm", "kernel": "whole expert-parallel step of one rank (router, exchange, local experts, combine)",
-                    "achieved": hbm_gbs, "peak": peak, "unit": "GB/s", "frac": hbm_gbs / peak, "peak_source": f"of {peak_kind}",
-                    "traffic": None, "algorithmic_bytes_per_launch": layer_bytes, "avg_launch_ms": ms_total / steps}
-        stages = None
-    line = dict(base, value=value, ms_per_step=ms_total / steps, config=config, clocks=clocks,
-                e2e={"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * cfg.d_model * 4,
-                     "d2h_bytes_per_step": B * cfg.d_model * 4},
-                gpu_launches=int(launches), roofline=roofline,
+        roofline = {"bound": "hbm", "kernel": "whole expert-parallel layer pass of one rank (router, exchange, local experts, combine)",
+                    "achieved": hbm_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": hbm_gbs / hbm_peak, "peak_source": f"of {peak_kind}",
+                    "traffic": None, "algorithmic_bytes_per_launch": layer_bytes, "avg_launch_ms": per_layer_ms}
+    step_bytes = B * cfg.d_model * 4 * L
+    line = dict(base, value=value, ms_per_step=ms_total / steps, ms_per_layer_pass=per_layer_ms, config=config, clocks=clocks,
+                gpu_launches=int(launches), roofline=roofline, parity=parity,
                 hbm={"layer_algorithmic_bytes": layer_bytes, "achieved_gbs_per_gpu": hbm_gbs,
-                     "frac_of_8tbs": hbm_gbs / 8000.0, "frac_of_measured": hbm_gbs / peak},
-                stage_ms=stages)
-    if keep_for_cpu is not None:
-        import oracle
-        oracle.build()
-        threads = os.cpu_count() or 1
-        rate, ms, sample = cpu_layer_rate(oracle, cfg, keep_for_cpu, x_cpu, threads, args.cpu_seconds)
+                     "frac_of_8tbs": hbm_gbs / 8000.0, "frac_of_measured": hbm_gbs / hbm_peak},
+                stage_ms=stages, timed_region_s=ms_total * 1e-3)
+    if e2e_ms:
+        line["e2e"] = {"value": layer_tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": step_bytes,
+                       "d2h_bytes_per_step": step_bytes, "mode": "pipelined host entry, three layer calls in flight"}
+    if e2e_sync_ms:
+        line["e2e_sync"] = {"value": layer_tokens / (e2e_sync_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": step_bytes,
+                            "d2h_bytes_per_step": step_bytes, "mode": "synchronous host entry (mer_moe_layer_forward), one call at a time"}
+    if rank == 0 and args.gpus == 1 and not args.no_cpu:
+        rate, ms, sample = cpu_rate(oracle, synth, cfg, 0, zipf_s, args.zipf_strength, xs_host[0], threads, args.cpu_seconds)
         line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
+    if rank == 0 and args.gpus == 1 and not args.no_sweep and args.workload == "cfg3":
+        line["sweep"] = run_sweep(mer_b200, synth, oracle, args, stack, local_rank, peaks, threads)
+    else:
+        stack.close()
     json_out.write(json.dumps(line) + "\n")
     json_out.flush()
     if world > 1:

@@ -163,7 +163,9 @@ int mer_backend_synchronize(mer_backend *b);
  * stale requester (MER_ERR_RESIDENCY_MISS); the same generation is a no-op. */
 int mer_expert_admit(mer_backend *b, uint32_t expert_id, uint64_t generation, const void *host_blob,
                      size_t bytes, uint32_t flags);
-/* Same, from a blob already in device memory (device-to-device copy on the copy stream). */
+/* Same, from a blob already in device memory (device-to-device copy or repack on the copy stream, which is not
+ * ordered after the caller's streams: the blob must be complete when the call is made, and must stay untouched
+ * until the admission has finished: mer_backend_synchronize, or a synchronous admit). */
 int mer_expert_admit_device(mer_backend *b, uint32_t expert_id, uint64_t generation,
                             const void *device_blob, size_t bytes, uint32_t flags);
 /* retire_key_if_present (backend/mod.rs:3893): frees the slot if (id, generation) is current. */

@@ -247,6 +247,10 @@ class Backend:
         self._check(self.lib.mer_moe_layer_forward_device(self.h, layer, C.c_void_p(d_x), n_tokens, C.c_void_p(d_out),
                                                           C.c_void_p(d_ids), C.c_void_p(d_weights), C.c_void_p(stream)))
 
+    def stream_check(self, layer, stream=0):
+        """Synchronises `stream` and raises the typed error the device status word holds, if any (for _device calls)."""
+        self._check(self.lib.mer_stream_check(self.h, layer, C.c_void_p(stream)))
+
     def qualification_matvec(self, weights, x, rows, columns, w_block_off=0, dtype=None):
         """GpuBackend::qualification_q4_0_matvec (backend/mod.rs:3532): raw block-stream matvec."""
         w = np.ascontiguousarray(weights, dtype=np.uint8)

@@ -3,7 +3,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libmer_b200.so")
+LIB_PATH = os.environ.get("MER_B200_LIB") or os.path.join(HERE, "libmer_b200.so")  # MER_B200_LIB: another build of the library
 
 DTYPE_Q4_0, DTYPE_Q8_0 = 0, 1
 SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1

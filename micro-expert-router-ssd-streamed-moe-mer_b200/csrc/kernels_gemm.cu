@@ -1,24 +1,26 @@
 // Grouped expert FFN for token groups of a dozen tokens and more (prefill, expert-parallel decode):
-// tcgen05 tensor-core GEMM per (expert, 128 weight rows, up to 128 tokens) with TMEM accumulators.
+// tcgen05 tensor-core GEMM per (expert, 256 weight rows, up to 128 tokens) with TMEM accumulators.
 //
-//   D[128 weight rows x N tokens] += A[128 x 32] * B[N x 32]^T      per 32-value block of K
+//   D[128 weight rows x N tokens] += A[128 x 32] * B[N x 32]^T      per 32-value block of K, for two row tiles
 //
 //   * A never touches shared memory as an operand: the packed Q4_0 / Q8_0 tile chunks of layout.cuh
-//     are streamed global -> shared by bulk async copies (every weight byte crosses HBM once per token
-//     tile), eight warps dequantise them block by block into two f16 operands, hi = f16(d*q) and
-//     lo = d*q - hi (exact: an 11-bit scale times an 8-bit integer has at most 19 significant bits),
-//     and store them straight into TENSOR MEMORY (tcgen05.st; a thread owns one weight row), from
-//     where the MMA reads its A operand.  Eight A stages live in TMEM beside the two accumulators, so
-//     the dequant -> MMA -> release loop is covered without spending shared memory on it.
+//     are streamed global -> shared by bulk async copies, eight warps dequantise them block by block into
+//     two f16 operands, hi = f16(d*q) and lo = d*q - hi (exact: an 11-bit scale times an 8-bit integer
+//     has at most 19 significant bits), and store them straight into TENSOR MEMORY (tcgen05.st; a thread
+//     owns one weight row), from where the MMA reads its A operand.  Eight A stages live in TMEM beside
+//     the two accumulators.
 //   * B is the activation tile as f16 hi + lo parts (22 significant bits after an exact power-of-two
 //     per-row scaling), laid out in the K-major no-swizzle core-matrix order by k_gemm_act_image and
-//     fetched with one bulk copy per 64 values of K into a five-stage shared-memory ring.
+//     fetched with one bulk copy per 64 values of K into a five-stage shared-memory ring.  B is 4 bytes per
+//     value against ~1 byte per weight, so it dominates what a CTA pulls from L2: an item therefore covers
+//     TWO 128-row tiles of the expert (one accumulator each) that share every activation stage, which
+//     halves the activation traffic per MMA.
 //   * Three MMAs per 16 values of K (hi*hi, hi*lo, lo*hi; lo*lo is below fp32 resolution) accumulate
 //     in fp32 in TMEM, so the result matches the fp32 reference to ~1e-6 instead of f16's 1e-3.
-//   * Warp roles: 0 = copy producer, 1 = MMA issuer (one elected lane) and TMEM owner, 2..5 = epilogue
-//     (tcgen05.ld, un-scaling, SiLU(gate)*up or plain store), 6..13 = dequantisers (a warp reaches the
-//     32 TMEM lanes of its quarter; the two warps of a quarter take alternate blocks).  Two accumulator
-//     buffers let the epilogue of one item overlap the MMAs of the next.
+//   * Warp roles: 0 = copy producer, 1 = MMA issuer (one elected lane) and TMEM owner, 2..9 = epilogue
+//     (four warps per accumulator: tcgen05.ld, un-scaling, SiLU(gate)*up or plain store), 10..17 =
+//     dequantisers (a warp reaches the 32 TMEM lanes of its quarter; the two warps of a quarter take
+//     alternate blocks).
 // Every wait is bounded; on expiry the CTA latches MER_DEVSTAT_TIMEOUT, stops issuing work, waits
 // (bounded) for its copies and MMAs in flight, frees its TMEM and returns.
 #include <cuda_fp16.h>
@@ -29,18 +31,21 @@
 
 namespace {
 
-constexpr int G_WARPS = 14, G_THREADS = G_WARPS * 32;
-constexpr int W_PRODUCER = 0, W_MMA = 1, W_EPI0 = 2, W_DQ0 = 6;
-constexpr int EPI_WARPS = 4, DQ_WARPS = 8;
+constexpr int G_WARPS = 18, G_THREADS = G_WARPS * 32;
+constexpr int W_PRODUCER = 0, W_MMA = 1, W_EPI0 = 2, W_DQ0 = 10;
+constexpr int EPI_WARPS = 4, DQ_WARPS = 8;  // EPI_WARPS per accumulator
 constexpr uint32_t RAW_BLOCKS = 4;       // blocks of K per weight stage (per packed tile: one bulk copy)
 constexpr uint32_t G_HEADER = 1024;
-constexpr uint32_t TMEM_COLS = 512;      // [0, 256): two accumulator buffers of up to 128 columns; [256, 512): A stages
+constexpr uint32_t TMEM_COLS = 512;      // [0, 256): the accumulators of an item's two row tiles, up to 128 columns each; [256, 512): A stages
 constexpr uint32_t TMEM_A0 = 256, A_STAGES = 8, A_STAGE_COLS = 32;  // a stage = one block: 16 columns hi + 16 columns lo
 constexpr uint32_t MAX_RING = 8;
-// The MMA issuer synchronises once per GROUP blocks of K: it waits for a whole group of A stages, issues the
-// group's MMAs and commits ONE barrier, done[], that releases both the group's A stages and the activation stages
-// it read (a wait or a commit per block cost more issue time than the block's MMAs take to run).
-constexpr uint32_t GROUP = 4, DONE_RING = 4;
+// The MMA issuer synchronises once per GROUP blocks of K of one row tile (a "sub-group"; sub-groups alternate
+// between the item's two row tiles, so A-stage half j always belongs to row tile j): it waits for the sub-group's
+// A stages, issues its MMAs and commits ONE barrier, done[], that releases those A stages and, after the second
+// row tile, the activation stages both read (a wait or a commit per block cost more issue time than the block's
+// MMAs take to run).  A waiter is never two phases behind a done[] barrier: the issuer leads the dequantisers by
+// at most two sub-groups and the producer by at most n_b / 2 + 1 groups of K, well inside the ring.
+constexpr uint32_t GROUP = 4, DONE_RING = 8;
 static_assert(GROUP == RAW_BLOCKS, "a weight stage holds exactly one group of blocks");
 constexpr float POW2_SCALE_TARGET = 9;   // activations are scaled so that the row maximum lies in [256, 512)
 
@@ -136,12 +141,12 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
   const MoeDispatch &d = p.d;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const uint32_t m_tiles = p.rows / (p.phase == 0 ? 64u : 128u);  // 8 packed tiles each
+  const uint32_t m_pairs = p.rows / (p.phase == 0 ? 128u : 256u);  // pairs of 128-row MMA tiles (8 packed tiles each)
   const uint32_t n_chunks = p.kb_total / 2;
   const uint32_t n_passes = *d.n_passes;
-  // Items (pass, 128-row tile) are dealt round-robin: the CTAs running at any moment work on a dozen
+  // Items (pass, pair of row tiles) are dealt round-robin: the CTAs running at any moment work on a dozen
   // neighbouring passes, so the activation images they all re-read stay in L2.
-  const uint32_t n_items = n_passes * m_tiles;
+  const uint32_t n_items = n_passes * m_pairs;
   const uint32_t item_beg = blockIdx.x, item_step = gridDim.x;
   if (item_beg >= n_items) return;
 
@@ -185,38 +190,43 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
 
   if (warp == W_PRODUCER) {
     // ------------------------------------------------------------------------ copy producer
-    // weights: one stage = RAW_BLOCKS blocks of the item's 8 packed tiles (8 copies); activations: one stage = 2 blocks
+    // weights: one stage = RAW_BLOCKS blocks of the 8 packed tiles of ONE row tile (8 copies); activations: one stage =
+    // 2 blocks of K, read by both row tiles.  Per group of K: weights of tile 0, first activation chunk, weights of tile 1,
+    // second activation chunk.
     Ring raw(p.n_raw), rb(p.n_b);
     uint32_t gchunk = 0;  // 64-value activation chunks issued so far, over all items
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
-      const uint32_t pass = item / m_tiles, mt = item % m_tiles;
+      const uint32_t pass = item / m_pairs, mp = item % m_pairs;
       const uint8_t *base = expert_base(pass);
       if (!base) continue;
-      const uint8_t *wsrc = base + region + (size_t)(mt * 8 + (lane & 7)) * tile_bytes;
+      const uint8_t *wsrc = base + region + (size_t)(mp * 16 + (lane & 7)) * tile_bytes;  // row tile 0; tile 1 = 8 packed tiles on
       const uint8_t *bsrc = p.act_img + (size_t)pass * n_chunks * b_stage;
-      for (uint32_t st = 0; st < p.kb_total && ok; st += 2) {
-        const bool new_raw = (st % RAW_BLOCKS) == 0;
-        if (new_raw && raw.round > 0) ok = mbar_wait(&raw_empty[raw.stage], (raw.round - 1) & 1);
-        if (ok && gchunk >= p.n_b) {
-          // the slot's previous chunk was read by the MMAs of group (gchunk - n_b) / 2
-          const uint32_t sp = (gchunk - p.n_b) / (GROUP / 2);
-          ok = mbar_wait(&done[sp % DONE_RING], (sp / DONE_RING) & 1);
+      for (uint32_t st = 0; st < p.kb_total && ok; st += GROUP) {
+#pragma unroll 1
+        for (uint32_t j = 0; j < 2 && ok; j++) {
+          if (raw.round > 0) ok = mbar_wait(&raw_empty[raw.stage], (raw.round - 1) & 1);
+          if (ok && gchunk >= p.n_b) {
+            // the slot's previous chunk was last read by the second sub-group of the group of K it belongs to
+            const uint32_t sp = 2 * ((gchunk - p.n_b) / 2) + 1;
+            ok = mbar_wait(&done[sp % DONE_RING], (sp / DONE_RING) & 1);
+          }
+          gchunk++;
+          if (*s_abort) ok = false;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          if (lane == 0) {
+            mbar_expect_tx(&raw_full[raw.stage], RAW_BYTES);
+            mbar_expect_tx(&b_full[rb.stage], b_stage);
+          }
+          __syncwarp();
+          if (lane < 8)
+            bulk_g2s(s_raw + raw.stage * RAW_BYTES + lane * TILE_RAW, wsrc + (size_t)j * 8 * tile_bytes + (size_t)(st / RAW_BLOCKS) * TILE_RAW,
+                     TILE_RAW, &raw_full[raw.stage]);
+          if (lane == 8)
+            bulk_g2s(s_b + (size_t)rb.stage * b_stage, bsrc + (size_t)(st / 2 + j) * b_stage, b_stage, &b_full[rb.stage]);
+          raw.advance();
+          rb.advance();
         }
-        gchunk++;
-        if (*s_abort) ok = false;
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (lane == 0) {
-          if (new_raw) mbar_expect_tx(&raw_full[raw.stage], RAW_BYTES);
-          mbar_expect_tx(&b_full[rb.stage], b_stage);
-        }
-        __syncwarp();
-        if (new_raw && lane < 8)
-          bulk_g2s(s_raw + raw.stage * RAW_BYTES + lane * TILE_RAW, wsrc + (size_t)(st / RAW_BLOCKS) * TILE_RAW, TILE_RAW,
-                   &raw_full[raw.stage]);
-        if (lane == 8) bulk_g2s(s_b + (size_t)rb.stage * b_stage, bsrc + (size_t)(st / 2) * b_stage, b_stage, &b_full[rb.stage]);
-        if (new_raw) raw.advance();
-        rb.advance();
       }
     }
     if (!ok) {
@@ -227,58 +237,64 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     }
   } else if (warp == W_MMA) {
     // -------------------------------------------------------------------------- MMA issuer
-    // one step = one 32-value block of K: two instructions of 16 values for each of the three operand pairings
+    // one step = one 32-value block of K of one row tile: two instructions of 16 values for each of the three operand pairings
     Ring rb(p.n_b);
-    uint32_t used = 0;  // items issued so far: buffer = used & 1, its k-th use has k = used >> 1
-    uint32_t grp = 0;   // groups of GROUP blocks issued so far, over all items
+    uint32_t n_done = 0;  // items issued so far
+    uint32_t grp = 0;     // sub-groups (GROUP blocks of one row tile) issued so far, over all items; grp & 1 = row tile
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
-      const uint32_t pass = item / m_tiles;
+      const uint32_t pass = item / m_pairs;
       if (!expert_base(pass)) continue;
-      const uint32_t buf = used & 1, use = used >> 1;
-      used++;
       // the MMA is as wide as the pass has tokens (rounded up to 16 columns): a ragged last pass of a group costs
       // its share, not a full tile
       const uint32_t idesc = instr_desc(min(p.bn, (d.pass_count[pass] + 15u) & ~15u));
       if (lane == 0) {
-        if (use > 0) ok = mbar_wait(&acc_empty[buf], (use - 1) & 1);
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * 128;
         // B descriptors differ only in their start-address field: one base, then 64-bit adds of (byte offset >> 4).
         // (The ring lies well inside the 256 KB the 14-bit field spans, so the adds never carry out of it.)
         const uint64_t b_desc0 = smem_desc(smem_u32(s_b), p.b_lbo, 128);
         const uint32_t stage16 = b_stage >> 4, half16 = (4 * p.b_lbo) >> 4, j16 = (2 * p.b_lbo) >> 4, lo16 = b_term >> 4;
-        for (uint32_t st = 0; st < p.kb_total && ok; st += GROUP, grp++) {
-          const uint32_t ag = grp & 1;  // the group's A stages: ag * GROUP ..
-          ok = mbar_wait(&a_full[ag], (grp >> 1) & 1);
-          if (*s_abort) ok = false;
-          if (!ok) break;
-          tc_fence_after();
-#pragma unroll
-          for (uint32_t b4 = 0; b4 < GROUP; b4++) {
-            if (!(b4 & 1)) {
-              ok = mbar_wait(&b_full[rb.stage], rb.round & 1);
+        for (uint32_t st = 0; st < p.kb_total && ok; st += GROUP) {
+          const bool last = st + GROUP >= p.kb_total;
+#pragma unroll 1
+          for (uint32_t rt = 0; rt < 2 && ok; rt++, grp++) {
+            const uint32_t d_tmem = tmem_base + rt * 128;
+            if (st == 0 && n_done > 0) {  // the previous item's epilogue has drained this accumulator
+              ok = mbar_wait(&acc_empty[rt], (n_done - 1) & 1);
               if (!ok) break;
-              tc_fence_after();
             }
-            const uint32_t a_hi = tmem_base + TMEM_A0 + (ag * GROUP + b4) * A_STAGE_COLS, a_lo = a_hi + 16;
-            const uint64_t b_blk = b_desc0 + (uint64_t)(rb.stage * stage16 + (b4 & 1) * half16);
+            ok = mbar_wait(&a_full[rt], (grp >> 1) & 1);
+            if (*s_abort) ok = false;
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll
-            for (uint32_t j = 0; j < 2; j++) {  // 16 values of K per instruction: 8 TMEM columns of A, two core-matrix columns of B
-              const uint64_t dbh = b_blk + (uint64_t)(j * j16), dbl = dbh + lo16;
-              if (b4 == 0 && j == 0)
-                tc_mma_ts(d_tmem, a_hi, dbh, idesc, st != 0);  // the item's first MMA overwrites the accumulator
-              else
-                tc_mma_ts_acc(d_tmem, a_hi + j * 8, dbh, idesc);
-              tc_mma_ts_acc(d_tmem, a_hi + j * 8, dbl, idesc);
-              tc_mma_ts_acc(d_tmem, a_lo + j * 8, dbh, idesc);
+            for (uint32_t b4 = 0; b4 < GROUP; b4++) {
+              uint32_t bs = rb.stage + (b4 >> 1), br = rb.round;  // the group's two activation stages, shared by both row tiles
+              if (bs >= p.n_b) bs -= p.n_b, br++;
+              if (rt == 0 && !(b4 & 1)) {
+                ok = mbar_wait(&b_full[bs], br & 1);
+                if (!ok) break;
+                tc_fence_after();
+              }
+              const uint32_t a_hi = tmem_base + TMEM_A0 + (rt * GROUP + b4) * A_STAGE_COLS, a_lo = a_hi + 16;
+              const uint64_t b_blk = b_desc0 + (uint64_t)(bs * stage16 + (b4 & 1) * half16);
+#pragma unroll
+              for (uint32_t j = 0; j < 2; j++) {  // 16 values of K per instruction: 8 TMEM columns of A, two core-matrix columns of B
+                const uint64_t dbh = b_blk + (uint64_t)(j * j16), dbl = dbh + lo16;
+                if (b4 == 0 && j == 0)
+                  tc_mma_ts(d_tmem, a_hi, dbh, idesc, st != 0);  // the item's first MMA of a row tile overwrites its accumulator
+                else
+                  tc_mma_ts_acc(d_tmem, a_hi + j * 8, dbh, idesc);
+                tc_mma_ts_acc(d_tmem, a_hi + j * 8, dbl, idesc);
+                tc_mma_ts_acc(d_tmem, a_lo + j * 8, dbh, idesc);
+              }
             }
-            if (b4 & 1) rb.advance();
+            if (!ok) break;
+            tc_commit(&done[grp % DONE_RING]);
+            if (last) tc_commit(&acc_full[rt]);
           }
-          if (!ok) break;
-          tc_commit(&done[grp % DONE_RING]);
+          rb.advance(), rb.advance();
         }
-        if (ok) tc_commit(&acc_full[buf]);
       }
+      n_done++;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       grp = __shfl_sync(0xffffffffu, grp, 0);
     }
@@ -300,13 +316,14 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     const uint32_t T = 2 * q + (lane >> 4), g = lane & 7, half = (lane >> 3) & 1;
     const __half2 zp = DT == MER_DTYPE_Q4_0 ? __floats2half2_rn(1032.0f, 1032.0f) : __floats2half2_rn(1152.0f, 1152.0f);
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
-      const uint32_t pass = item / m_tiles;
+      const uint32_t pass = item / m_pairs;
       if (!expert_base(pass)) continue;
-      // one group (= one weight stage) at a time: this warp's two blocks of it, one wait on each side
-      for (uint32_t st0 = 0; st0 < p.kb_total && ok; st0 += GROUP, gblk += GROUP) {
+      // one sub-group (= one weight stage of one row tile) at a time, the two row tiles alternating: this warp's two
+      // blocks of it, one wait on each side
+      for (uint32_t sg = 0; sg < 2 * (p.kb_total / GROUP) && ok; sg++, gblk += GROUP) {
         ok = mbar_wait(&raw_full[raw.stage], raw.round & 1);
         if (ok && gblk >= A_STAGES) {
-          // the group's A stages were last read by the MMAs of group gblk / GROUP - 2
+          // the sub-group's A stages were last read by the MMAs of sub-group gblk / GROUP - 2
           const uint32_t sp = gblk / GROUP - A_STAGES / GROUP;
           ok = mbar_wait(&done[sp % DONE_RING], (sp / DONE_RING) & 1);
         }
@@ -364,16 +381,15 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
   } else {
     // ---------------------------------------------------------------------------- epilogue
     const uint32_t q = warp & 3;  // a warp reads the TMEM lanes 32 * (warp % 4) ..
-    const uint32_t row = q * 32 + lane;  // row of the item's 128-row tile
+    const uint32_t row = q * 32 + lane;  // row of the 128-row tile
+    const uint32_t buf = (warp - W_EPI0) >> 2;  // which of the item's two row tiles (= accumulators) this warp drains
     uint32_t used = 0;
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
-      const uint32_t pass = item / m_tiles, mt = item % m_tiles;
+      const uint32_t pass = item / m_pairs, mt = 2 * (item % m_pairs) + buf;
       const uint32_t pstart = d.pass_start[pass], pcount = d.pass_count[pass];
       const bool resident = expert_base(pass) != nullptr;
-      uint32_t buf = 0;
       if (resident) {
-        buf = used & 1;
-        ok = mbar_wait(&acc_full[buf], (used >> 1) & 1);
+        ok = mbar_wait(&acc_full[buf], used & 1);
         used++;
         if (*s_abort) ok = false;
         ok = __all_sync(0xffffffffu, ok);

@@ -588,3 +588,21 @@ def test_full_size_mixtral_expert_spot_check():
     assert (w0.view(np.uint32) == oracle.dequant_stream(cfg.dtype, blob[2 * proj:], D * F).view(np.uint32)).all()
     ref = oracle.expert_forward(cfg.dtype, blob, x[0], D, F, oracle.FWD_SIMD8X4)
     assert rel_rms_err(got[0], ref) <= FFN_TOL
+
+
+@pytest.mark.parametrize("dtype", [oracle.Q4_0, oracle.Q8_0])
+def test_device_side_weight_generator_matches_the_host_generator(dtype):
+    # the benchmark fills deep resident stacks from the torch form of the generator; the oracle reads the numpy form
+    torch = pytest.importorskip("torch")
+    D, F = 256, 512
+    dev = synth.make_expert_blobs_torch(dtype, D, F, 9, 3, [0, 5, 130], torch.device("cuda", 0)).cpu().numpy()
+    for j, e in enumerate([0, 5, 130]):
+        assert (dev[j] == synth.make_expert_blob(dtype, D, F, 9, 3, e)).all()
+    x = synth.make_activations(2, D, 9)
+    with backend(dtype, D, F, max_tokens=4) as b:  # and admission from device memory gives the same expert
+        t = synth.make_expert_blobs_torch(dtype, D, F, 9, 3, [5], torch.device("cuda", 0))
+        torch.cuda.synchronize()
+        b.admit_device(2, 1, t[0].data_ptr(), t.shape[1])
+        got = b.expert_forward_f32(0, 2, x)
+    ref = oracle.expert_forward(dtype, synth.make_expert_blob(dtype, D, F, 9, 3, 5), x[1], D, F)
+    assert rel_rms_err(got[1], ref) <= FFN_TOL
