@@ -284,9 +284,73 @@ int mer_expert_hot_promote(mer_backend *b, mer_gpu_cache *cache, uint32_t expert
  * recency; `cache` may be NULL) and refreshes the physical slots' recency. */
 int mer_expert_touch(mer_backend *b, mer_gpu_cache *cache, const uint32_t *expert_ids, size_t n);
 
+/* ---- on-disk formats around the expert path: the Unified Tensor Header in front of an expert blob
+ * (tensor_header.rs:9-27: UTH1, 64 bytes; tensor_header.rs:256-283: UTH2, 128 bytes, one byte range per projection;
+ * both followed by zero padding up to block_align when flag bit 0 is set) and the dataset's metadata.json
+ * (main.rs:9096-9114).  Host-only parsing, no device needed. ---- */
+#define MER_UTH_KIND_NONE 0 /* legacy blob: no header, the payload is the whole buffer */
+#define MER_UTH_KIND_UTH1 1
+#define MER_UTH_KIND_UTH2 2
+typedef struct mer_uth_projection { /* ProjectionRange (tensor_header.rs:144-150); offsets relative to the payload */
+  uint32_t uth_dtype_id;            /* UthDtypeId (tensor_header.rs:75-89): 4 = Q4_0, 5 = Q8_0, ... */
+  uint32_t weights;
+  uint64_t offset, len;
+} mer_uth_projection;
+typedef struct mer_uth_info {
+  uint32_t kind;          /* MER_UTH_KIND_* */
+  uint32_t version;
+  uint32_t uth_dtype_id;  /* UTH1: the blob's dtype id; UTH2: 10 (mixed) */
+  int32_t dtype;          /* MER_DTYPE_* when this library runs it (UTH2: all three projections alike), else -1 */
+  uint32_t shape_rank, flags;
+  uint32_t shape[4];      /* UTH1: [d_ff, d_model, 3, 0] for a SwiGLU expert (tensor_header.rs:456) */
+  uint64_t d_model, d_ff;
+  uint64_t payload_offset, payload_bytes; /* where the weights start inside the buffer, and what is left from there */
+  mer_uth_projection proj[3];             /* UTH2: gate, up, down */
+} mer_uth_info;
+/* TensorHeader::strip / MixedExpertHeader::strip (tensor_header.rs:528-545, 376-391).  Best effort like the reference:
+ * a buffer without a valid header is reported as MER_UTH_KIND_NONE, never as an error. */
+int mer_uth_probe(const void *bytes, size_t len, size_t block_align, mer_uth_info *out);
+/* TensorHeader::for_swiglu_expert + write_padded (tensor_header.rs:419-470, 489-499): header + padding; *written = bytes
+ * needed (MER_ERR_PHYSICAL_CAPACITY when cap is smaller). */
+int mer_uth1_write(int32_t dtype, uint64_t d_model, uint64_t d_ff, size_t block_align, void *dst, size_t cap, size_t *written);
+/* MixedExpertHeader::to_bytes + write_padded (tensor_header.rs:256-295). */
+int mer_uth2_write(uint64_t d_model, uint64_t d_ff, const mer_uth_projection *proj /*[3]*/, size_t block_align, void *dst,
+                   size_t cap, size_t *written);
+typedef struct mer_dataset_info { /* the keys of metadata.json a loader needs; absent keys stay 0 / "" / -1 */
+  uint64_t format_version, num_experts, d_model, d_ff, expert_size, maximum_payload_bytes, block_align, experts_written;
+  uint64_t num_layers, experts_per_layer, top_k;
+  int32_t dtype; /* MER_DTYPE_* or -1 */
+  char dtype_name[16], q4_0_layout[32], conversion_mode[32];
+} mer_dataset_info;
+int mer_dataset_metadata_parse(const char *json, size_t len, mer_dataset_info *out);
+/* The loader: expert_<id>.bin (gguf_loader.rs:782) -> HBM slot.  Reads the file in chunks straight into the pinned
+ * staging buffers (no intermediate copy), strips a UTH1 / UTH2 header (UTH2: the three ranges are gathered into the
+ * gate||up||down order), checks dtype and shape against the backend, and admits under (expert_id, generation) like
+ * mer_expert_admit.  block_align = the dataset's (metadata.json; 4096 by default). */
+int mer_expert_admit_file(mer_backend *b, uint32_t expert_id, uint64_t generation, const char *path, size_t block_align,
+                          uint32_t flags);
+
 /* ---- router: LinearGate::new / with_routing (gating.rs:149-238). ---- */
 int mer_router_install(mer_backend *b, uint32_t layer, const float *host_weights /*[E x D]*/,
                        const mer_router_cfg *cfg);
+/* ---- the steps either side of the MoE block, per layer (optional; install after the layer's router):
+ *   rms_weight  pre-MoE RMSNorm (RmsNorm::forward_inplace, transformer.rs:52-95): router and experts read
+ *               xn = x * (1 / sqrt(mean(x^2) + rms_eps)) * rms_weight instead of x (moe_pre, transformer.rs:2493-2518);
+ *   shared_gate the shared expert's sigmoid gate vector (SharedExpert::gate_inp, transformer.rs:2101-2103, 2224-2237):
+ *               its output is mixed in with weight sigmoid(shared_gate . xn) instead of 1;
+ *   MER_LAYER_RESIDUAL  the combine writes out = (x + sum over routed slots) + shared expert, the order of
+ *               moe_accumulated_into + add_residual_into (transformer.rs:2559-2574, model.rs:2742-2763); out may alias x.
+ * The whole-layer entry points (mer_moe_layer_forward*, mer_ep_layer_forward*) honour them; entry points whose
+ * routing comes from the caller do not.  Both vectors are host pointers of d_model floats, or NULL. ---- */
+#define MER_LAYER_RESIDUAL 0x1u
+typedef struct mer_layer_cfg {
+  const float *rms_weight;
+  const float *shared_gate;
+  float rms_eps;
+  uint32_t flags;
+} mer_layer_cfg;
+int mer_layer_install(mer_backend *b, uint32_t layer, const mer_layer_cfg *cfg);
+
 /* LinearGate::route_with_scratch (gating.rs:395-476) for n_tokens rows of x (host).
  * ids/weights are [n_tokens x top_k]; unfilled slots get MER_EXPERT_NONE / 0. Ids are local. */
 int mer_router_route(mer_backend *b, uint32_t layer, const float *x, size_t n_tokens,

@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmer_b200.so")
-SOURCES = ["mer_abi.cu", "kernels_generic.cu", "kernels_stream.cu", "kernels_ep.cu", "kernels_gemm.cu", "noalloc.cu", "vram_tier.cpp"]
+SOURCES = ["mer_abi.cu", "kernels_generic.cu", "kernels_stream.cu", "kernels_ep.cu", "kernels_gemm.cu", "noalloc.cu", "vram_tier.cpp", "formats.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
               "-Xcompiler", "-fPIC,-fvisibility=hidden,-O3", "-cudart", "static"]
 

@@ -1,6 +1,7 @@
 """Mirror of the reference's routed-expert backend boundary (backend/mod.rs) over the C ABI."""
 import ctypes as C
 import enum
+import os
 
 import numpy as np
 
@@ -132,6 +133,12 @@ class Backend:
         flags = (capi.ADMIT_ANCHOR if anchor else 0) | (0 if wait else capi.ADMIT_ASYNC)
         self._check(self.lib.mer_expert_admit_device(self.h, expert_id, generation, C.c_void_p(device_ptr), nbytes, flags))
 
+    def admit_file(self, expert_id, generation, path, block_align=4096, anchor=False, wait=True):
+        """expert_<id>.bin -> HBM slot: strips a UTH1 / UTH2 header, checks dtype and shape, streams the payload through
+        the pinned staging buffers."""
+        flags = (capi.ADMIT_ANCHOR if anchor else 0) | (0 if wait else capi.ADMIT_ASYNC)
+        self._check(self.lib.mer_expert_admit_file(self.h, expert_id, generation, os.fsencode(path), block_align, flags))
+
     def retire(self, expert_id, generation):
         self._check(self.lib.mer_expert_retire(self.h, expert_id, generation))
 
@@ -172,6 +179,17 @@ class Backend:
                                 cb.ctypes.data if cb is not None else None, lb.ctypes.data if lb is not None else None)
         self._check(self.lib.mer_router_install(self.h, layer, _ptr(w), C.byref(cfg)))
         self._routers[layer] = gate
+
+    def install_layer(self, layer, rms_weight=None, rms_eps=1e-6, shared_gate=None, residual=False):
+        """The steps either side of the MoE block of `layer` (after install_router): pre-MoE RMSNorm
+        (transformer.rs:52-95), the shared expert's sigmoid gate vector (transformer.rs:2224-2237), residual add."""
+        rw = None if rms_weight is None else np.ascontiguousarray(rms_weight, dtype=np.float32)
+        sg = None if shared_gate is None else np.ascontiguousarray(shared_gate, dtype=np.float32)
+        assert rw is None or rw.size == self.d_model
+        assert sg is None or sg.size == self.d_model
+        cfg = capi.MerLayerCfg(rw.ctypes.data if rw is not None else None, sg.ctypes.data if sg is not None else None,
+                               float(rms_eps), capi.LAYER_RESIDUAL if residual else 0)
+        self._check(self.lib.mer_layer_install(self.h, layer, C.byref(cfg)))
 
     def route(self, layer, x):
         gate = self._routers[layer]

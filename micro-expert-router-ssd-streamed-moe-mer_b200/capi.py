@@ -9,6 +9,7 @@ DTYPE_Q4_0, DTYPE_Q8_0 = 0, 1
 SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
 EXPERT_NONE = 0xFFFFFFFF
 ADMIT_ANCHOR, ADMIT_ASYNC = 1, 2
+LAYER_RESIDUAL = 1
 
 
 class MerBackendCfg(C.Structure):
@@ -22,6 +23,26 @@ class MerRouterCfg(C.Structure):
                 ("normalise_topk", C.c_int32), ("n_group", C.c_uint32), ("topk_group", C.c_uint32),
                 ("routed_scaling_factor", C.c_float), ("shared_expert_id", C.c_uint32),
                 ("correction_bias", C.c_void_p), ("logit_bias", C.c_void_p)]
+
+
+class MerLayerCfg(C.Structure):
+    _fields_ = [("rms_weight", C.c_void_p), ("shared_gate", C.c_void_p), ("rms_eps", C.c_float), ("flags", C.c_uint32)]
+
+
+class MerUthProjection(C.Structure):
+    _fields_ = [("uth_dtype_id", C.c_uint32), ("weights", C.c_uint32), ("offset", C.c_uint64), ("len", C.c_uint64)]
+
+
+class MerUthInfo(C.Structure):
+    _fields_ = [("kind", C.c_uint32), ("version", C.c_uint32), ("uth_dtype_id", C.c_uint32), ("dtype", C.c_int32),
+                ("shape_rank", C.c_uint32), ("flags", C.c_uint32), ("shape", C.c_uint32 * 4), ("d_model", C.c_uint64),
+                ("d_ff", C.c_uint64), ("payload_offset", C.c_uint64), ("payload_bytes", C.c_uint64), ("proj", MerUthProjection * 3)]
+
+
+class MerDatasetInfo(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("format_version", "num_experts", "d_model", "d_ff", "expert_size", "maximum_payload_bytes",
+                                          "block_align", "experts_written", "num_layers", "experts_per_layer", "top_k")] + [
+        ("dtype", C.c_int32), ("dtype_name", C.c_char * 16), ("q4_0_layout", C.c_char * 32), ("conversion_mode", C.c_char * 32)]
 
 
 class MerErrorInfo(C.Structure):
@@ -106,7 +127,13 @@ ABI_SYMBOLS = {
     "mer_expert_demand_admit": (C.c_int, [_vp, _vp, _u32, _vp, _sz, _u32, C.POINTER(_u64)]),
     "mer_expert_hot_promote": (C.c_int, [_vp, _vp, _u32, _vp, _sz, _u32, C.POINTER(C.c_int)]),
     "mer_expert_touch": (C.c_int, [_vp, _vp, _vp, _sz]),
+    "mer_uth_probe": (C.c_int, [_vp, _sz, _sz, C.POINTER(MerUthInfo)]),
+    "mer_uth1_write": (C.c_int, [C.c_int32, _u64, _u64, _sz, _vp, _sz, C.POINTER(_sz)]),
+    "mer_uth2_write": (C.c_int, [_u64, _u64, C.POINTER(MerUthProjection), _sz, _vp, _sz, C.POINTER(_sz)]),
+    "mer_dataset_metadata_parse": (C.c_int, [C.c_char_p, _sz, C.POINTER(MerDatasetInfo)]),
+    "mer_expert_admit_file": (C.c_int, [_vp, _u32, _u64, C.c_char_p, _sz, _u32]),
     "mer_router_install": (C.c_int, [_vp, _u32, _vp, C.POINTER(MerRouterCfg)]),
+    "mer_layer_install": (C.c_int, [_vp, _u32, C.POINTER(MerLayerCfg)]),
     "mer_router_route": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _vp]),
     "mer_routed_expert_matmul": (C.c_int, [_vp, _u32, _u32, _vp, _sz, _sz, _vp]),
     "mer_routed_expert_matmul_batch": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _sz, _sz, _vp]),

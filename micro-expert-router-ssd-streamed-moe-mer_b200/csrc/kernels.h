@@ -22,6 +22,7 @@ struct RouterDev {
   float scaling;
   uint32_t shared_expert_id;  // global id or MER_NONE
   uint32_t id_base;           // layer * num_experts
+  const float *shared_scale;  // [n_tokens] mixing weight of the shared expert (its sigmoid gate scalar), or null = 1
 };
 
 // One MoE dispatch: P = n_tokens * slots pairs (token, slot); pair p belongs to token p / slots.
@@ -68,6 +69,10 @@ struct MoeDispatch {
   int fuse_reduce;          // in: the caller wants final per-pair outputs in `y` for the grouped pairs (no K-split partials left)
   uint32_t gemm_bn;         // > 0: the tcgen05 GEMM path runs this dispatch with passes of gemm_bn tokens
   int packed;               // 1: slots hold the tile-major fragment layout (layout.cuh), 0: the flat block stream
+  // Residual stream: when set, the combine writes out = (residual + sum over the routed slots) + shared-expert slot,
+  // in that order (add_residual after the routed sum, then the shared expert: model.rs:2742-2763).
+  const float *residual;    // [n_tokens x D] or null
+  uint32_t routed_slots;    // slots below this index are routed experts (used with `residual`)
 };
 
 // Expert-parallel view of one rank: where every rank's exchange buffer is mapped and how experts
@@ -90,7 +95,7 @@ cudaError_t launch_ep_filter(const EpDev &ep, const uint32_t *ids_all, const flo
 cudaError_t launch_ep_gather(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, float *x_all, uint32_t *pair_expert,
                              float *pair_weight, uint32_t *status, cudaStream_t s, int *launches);
 cudaError_t launch_ep_combine(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, const uint32_t *ids, const float *w,
-                              float *out, uint32_t *status, cudaStream_t s, int *launches);
+                              const float *residual, float *out, uint32_t *status, cudaStream_t s, int *launches);
 
 // kernels_generic.cu
 // Groups pairs by expert for a whole layer whose routing is already in d.pair_expert (+ pass table).
@@ -101,6 +106,10 @@ cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max
 cudaError_t launch_groups_from_pairs(const MoeDispatch &d, cudaStream_t s, int *launches);
 cudaError_t launch_ffn_generic(const MoeDispatch &d, cudaStream_t s, int *launches, cudaEvent_t ev_mid);
 cudaError_t launch_combine(const MoeDispatch &d, cudaStream_t s, int *launches);
+// Pre-MoE steps on n_tokens rows of x: RMSNorm (rms_weight != null: xn = x * rsqrt(mean(x^2) + eps) * weight) and the
+// shared expert's gate scalar (shared_gate != null: scale[t] = sigmoid(shared_gate . xn[t])).
+cudaError_t launch_pre_moe(const float *x, uint32_t n_tokens, uint32_t D, const float *rms_weight, float eps, const float *shared_gate,
+                           float *xn, float *shared_scale, cudaStream_t s, int *launches);
 cudaError_t launch_dequant(int dtype, const uint8_t *src, float *dst, size_t n_weights, cudaStream_t s);
 // Dequantises projection `matrix` (0 gate, 1 up, 2 down) of a packed expert into row-major f32.
 cudaError_t launch_dequant_packed(int dtype, const uint8_t *expert, int matrix, uint32_t D, uint32_t F, float *dst, cudaStream_t s);

@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(256) k_ep_gather(EpDev ep, uint32_t epoch, uin
 // One CTA per token, a thread four consecutive values.
 __global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, uint32_t epoch, uint32_t D, uint32_t slots,
                                                     const uint32_t *__restrict__ ids, const float *__restrict__ w,
-                                                    float *__restrict__ out, uint32_t *status) {
+                                                    const float *__restrict__ residual, float *__restrict__ out, uint32_t *status) {
   const uint32_t t = blockIdx.x;
   __shared__ int s_ok;
   __shared__ const float *s_row[64];
@@ -145,7 +145,12 @@ __global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, uint32_t epoch, ui
   for (uint32_t i4 = threadIdx.x; i4 < D / 4; i4 += blockDim.x) {
     float4 acc = make_float4(0, 0, 0, 0);
     if (s_ok) {
-      for (uint32_t sl = 0; sl < slots; sl++) {
+      for (uint32_t sl = 0; sl <= slots; sl++) {
+        if (residual && sl == min(ep.top_k, slots)) {  // hidden + routed sum, before the shared expert's slot
+          const float4 r = __ldg(reinterpret_cast<const float4 *>(residual) + (size_t)t * (D / 4) + i4);
+          acc.x = __fadd_rn(r.x, acc.x), acc.y = __fadd_rn(r.y, acc.y), acc.z = __fadd_rn(r.z, acc.z), acc.w = __fadd_rn(r.w, acc.w);
+        }
+        if (sl == slots) break;
         const float *row = s_row[sl];
         if (!row) continue;
         const float wt = s_w[sl];
@@ -178,8 +183,8 @@ cudaError_t launch_ep_gather(const EpDev &ep, uint32_t epoch, uint32_t D, uint32
 }
 
 cudaError_t launch_ep_combine(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, const uint32_t *ids, const float *w,
-                              float *out, uint32_t *status, cudaStream_t s, int *launches) {
-  k_ep_combine<<<ep.tokens_per_rank, 256, 0, s>>>(ep, epoch, D, slots, ids, w, out, status);
+                              const float *residual, float *out, uint32_t *status, cudaStream_t s, int *launches) {
+  k_ep_combine<<<ep.tokens_per_rank, 256, 0, s>>>(ep, epoch, D, slots, ids, w, residual, out, status);
   if (launches) (*launches)++;
   return cudaGetLastError();
 }

@@ -17,16 +17,19 @@
 //     halves the activation traffic per MMA.
 //   * Three MMAs per 16 values of K (hi*hi, hi*lo, lo*hi; lo*lo is below fp32 resolution) accumulate
 //     in fp32 in TMEM, so the result matches the fp32 reference to ~1e-6 instead of f16's 1e-3.
-//   * Warp roles: 0 = copy producer, 1 = MMA issuer (one elected lane) and TMEM owner, 2..9 = epilogue
-//     (four warps per accumulator: tcgen05.ld, un-scaling, SiLU(gate)*up or plain store), 10..17 =
-//     dequantisers (a warp reaches the 32 TMEM lanes of its quarter; the two warps of a quarter take
-//     alternate blocks).
+//   * Warp roles: 0 = producer of the activation stages, 1 = MMA issuer (one elected lane) and TMEM owner,
+//     2..9 = epilogue (four warps per accumulator: tcgen05.ld, un-scaling, SiLU(gate)*up or plain store),
+//     10..17 = dequantisers (a warp reaches the 32 TMEM lanes of its quarter; the two warps of a quarter
+//     take alternate blocks).  Each dequantiser warp also issues the bulk copy of one of the eight packed
+//     tiles of every weight stage: issuing a bulk copy occupies a thread for ~100 cycles, and one producer
+//     warp issuing all ten copies of a group was what the whole pipeline waited for (clock64 probes).
 // Every wait is bounded; on expiry the CTA latches MER_DEVSTAT_TIMEOUT, stops issuing work, waits
 // (bounded) for its copies and MMAs in flight, frees its TMEM and returns.
 #include <cuda_fp16.h>
 
 #include "../../include/mer_b200.h"
 #include "kernels.h"
+#include "layout.cuh"
 #include "ptx.cuh"
 
 namespace {
@@ -161,7 +164,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < MAX_RING; s++) {
-      mbar_init(&raw_full[s], 1), mbar_init(&raw_empty[s], DQ_WARPS);
+      mbar_init(&raw_full[s], DQ_WARPS), mbar_init(&raw_empty[s], DQ_WARPS);  // one copy per dequantiser warp and stage
       mbar_init(&a_full[s], DQ_WARPS), mbar_init(&done[s], 1);  // one arrival per dequantiser warp and group
       mbar_init(&b_full[s], 1);
     }
@@ -190,49 +193,33 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
 
   if (warp == W_PRODUCER) {
     // ------------------------------------------------------------------------ copy producer
-    // weights: one stage = RAW_BLOCKS blocks of the 8 packed tiles of ONE row tile (8 copies); activations: one stage =
-    // 2 blocks of K, read by both row tiles.  Per group of K: weights of tile 0, first activation chunk, weights of tile 1,
-    // second activation chunk.
-    Ring raw(p.n_raw), rb(p.n_b);
+    // activations: one stage = 2 blocks of K (one bulk copy), read by both row tiles of the item
+    Ring rb(p.n_b);
     uint32_t gchunk = 0;  // 64-value activation chunks issued so far, over all items
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
-      const uint32_t pass = item / m_pairs, mp = item % m_pairs;
-      const uint8_t *base = expert_base(pass);
-      if (!base) continue;
-      const uint8_t *wsrc = base + region + (size_t)(mp * 16 + (lane & 7)) * tile_bytes;  // row tile 0; tile 1 = 8 packed tiles on
+      const uint32_t pass = item / m_pairs;
+      if (!expert_base(pass)) continue;
       const uint8_t *bsrc = p.act_img + (size_t)pass * n_chunks * b_stage;
-      for (uint32_t st = 0; st < p.kb_total && ok; st += GROUP) {
-#pragma unroll 1
-        for (uint32_t j = 0; j < 2 && ok; j++) {
-          if (raw.round > 0) ok = mbar_wait(&raw_empty[raw.stage], (raw.round - 1) & 1);
-          if (ok && gchunk >= p.n_b) {
-            // the slot's previous chunk was last read by the second sub-group of the group of K it belongs to
-            const uint32_t sp = 2 * ((gchunk - p.n_b) / 2) + 1;
-            ok = mbar_wait(&done[sp % DONE_RING], (sp / DONE_RING) & 1);
-          }
-          gchunk++;
-          if (*s_abort) ok = false;
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          if (lane == 0) {
-            mbar_expect_tx(&raw_full[raw.stage], RAW_BYTES);
-            mbar_expect_tx(&b_full[rb.stage], b_stage);
-          }
-          __syncwarp();
-          if (lane < 8)
-            bulk_g2s(s_raw + raw.stage * RAW_BYTES + lane * TILE_RAW, wsrc + (size_t)j * 8 * tile_bytes + (size_t)(st / RAW_BLOCKS) * TILE_RAW,
-                     TILE_RAW, &raw_full[raw.stage]);
-          if (lane == 8)
-            bulk_g2s(s_b + (size_t)rb.stage * b_stage, bsrc + (size_t)(st / 2 + j) * b_stage, b_stage, &b_full[rb.stage]);
-          raw.advance();
-          rb.advance();
+      for (uint32_t c = 0; c < n_chunks && ok; c++) {
+        if (gchunk >= p.n_b) {
+          // the slot's previous chunk was last read by the second sub-group of the group of K it belongs to
+          const uint32_t sp = 2 * ((gchunk - p.n_b) / 2) + 1;
+          ok = mbar_wait(&done[sp % DONE_RING], (sp / DONE_RING) & 1);
         }
+        gchunk++;
+        if (*s_abort) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_expect_tx(&b_full[rb.stage], b_stage);
+          bulk_g2s(s_b + (size_t)rb.stage * b_stage, bsrc + (size_t)c * b_stage, b_stage, &b_full[rb.stage]);
+        }
+        rb.advance();
       }
     }
     if (!ok) {
       if (lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
       // copies already in flight get a bounded chance to land before the CTA's shared memory is released
-      for (uint32_t s = 0; s < p.n_raw; s++) (void)mbar_wait(&raw_full[s], 0), (void)mbar_wait(&raw_full[s], 1);
       for (uint32_t s = 0; s < p.n_b; s++) (void)mbar_wait(&b_full[s], 0), (void)mbar_wait(&b_full[s], 1);
     }
   } else if (warp == W_MMA) {
@@ -315,13 +302,42 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     const uint32_t q = warp & 3, mine = (warp - W_DQ0) >> 2;
     const uint32_t T = 2 * q + (lane >> 4), g = lane & 7, half = (lane >> 3) & 1;
     const __half2 zp = DT == MER_DTYPE_Q4_0 ? __floats2half2_rn(1032.0f, 1032.0f) : __floats2half2_rn(1152.0f, 1152.0f);
+    // This warp copies packed tile `tw` of every weight stage.  The copies run n_raw sub-groups ahead of the
+    // dequantisation, walking the same sequence of (item, sub-group) with a cursor of their own.
+    const uint32_t tw = warp - W_DQ0, sg_per_item = 2 * (p.kb_total / GROUP);
+    uint32_t pf_item = item_beg, pf_sg = 0, n_issued = 0;
+    const uint8_t *pf_base = nullptr;
+    auto pf_seek = [&]() {  // the next item whose expert is resident
+      for (; pf_item < n_items; pf_item += item_step)
+        if ((pf_base = expert_base(pf_item / m_pairs)) != nullptr) break;
+    };
+    auto issue_copy = [&]() {  // sub-group number n_issued of this CTA goes to stage n_issued % n_raw
+      if (pf_item >= n_items) return;
+      if (lane == 0) {
+        const uint32_t stage = n_issued % p.n_raw, mp = pf_item % m_pairs, rt = pf_sg & 1, kg = pf_sg >> 1;
+        const uint8_t *src = pf_base + region + (size_t)(mp * 16 + rt * 8 + tw) * tile_bytes + (size_t)kg * TILE_RAW;
+        mbar_expect_tx(&raw_full[stage], TILE_RAW);
+        bulk_g2s(s_raw + stage * RAW_BYTES + tw * TILE_RAW, src, TILE_RAW, &raw_full[stage]);
+      }
+      n_issued++;
+      if (++pf_sg == sg_per_item) pf_sg = 0, pf_item += item_step, pf_seek();
+    };
+    pf_seek();
+    for (uint32_t i = 0; i < p.n_raw; i++) issue_copy();
+    uint32_t n_seen = 0;  // sub-groups dequantised so far
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
       const uint32_t pass = item / m_pairs;
       if (!expert_base(pass)) continue;
       // one sub-group (= one weight stage of one row tile) at a time, the two row tiles alternating: this warp's two
       // blocks of it, one wait on each side
-      for (uint32_t sg = 0; sg < 2 * (p.kb_total / GROUP) && ok; sg++, gblk += GROUP) {
-        ok = mbar_wait(&raw_full[raw.stage], raw.round & 1);
+      for (uint32_t sg = 0; sg < sg_per_item && ok; sg++, gblk += GROUP, n_seen++) {
+        if (n_seen >= 1) {
+          // refill the stage the previous sub-group emptied (every dequantiser warp has left it) with sub-group n_seen - 1 + n_raw
+          const uint32_t prev = n_seen - 1;
+          ok = mbar_wait(&raw_empty[prev % p.n_raw], (prev / p.n_raw) & 1);
+          if (ok) issue_copy();
+        }
+        if (ok) ok = mbar_wait(&raw_full[raw.stage], raw.round & 1);
         if (ok && gblk >= A_STAGES) {
           // the sub-group's A stages were last read by the MMAs of sub-group gblk / GROUP - 2
           const uint32_t sp = gblk / GROUP - A_STAGES / GROUP;
@@ -342,7 +358,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
             const __half2 dd = __half2half2(half ? __high2half(bits_h2(sc2)) : __low2half(bits_h2(sc2)));
 #pragma unroll
             for (int t = 0; t < 4; t++) {  // values 8t .. 8t+7
-              const uint2 w = lds64(src + (g * 4 + t) * 16 + half * 8);
+              const uint2 w = lds64(src + packed_piece(g, t) * 16 + half * 8);
               const uint32_t w0 = w.x ^ 0x80808080u, w1 = w.y ^ 0x80808080u;
               dq2(__byte_perm(w0, 0x64646464u, 0x4140), zp, dd, v[4 * t + 0], v[16 + 4 * t + 0]);
               dq2(__byte_perm(w0, 0x64646464u, 0x4342), zp, dd, v[4 * t + 1], v[16 + 4 * t + 1]);
@@ -357,7 +373,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
             const __half2 dd = __half2half2(half ? __high2half(bits_h2(sc2)) : __low2half(bits_h2(sc2)));
 #pragma unroll
             for (int t = 0; t < 4; t++) {
-              const uint32_t w = lds32(src + (g * 4 + t) * 16 + (blk * 2 + half) * 4);
+              const uint32_t w = lds32(src + packed_piece(g, t) * 16 + (blk * 2 + half) * 4);
               const uint32_t lows = w & 0x0F0F0F0Fu, highs = (w >> 4) & 0x0F0F0F0Fu;
               dq2(__byte_perm(lows, 0x64646464u, 0x4140), zp, dd, v[2 * t + 0], v[16 + 2 * t + 0]);
               dq2(__byte_perm(lows, 0x64646464u, 0x4342), zp, dd, v[2 * t + 1], v[16 + 2 * t + 1]);
@@ -377,7 +393,11 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
         raw.advance();
       }
     }
-    if (!ok && lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
+    if (!ok) {
+      if (lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
+      // weight copies already in flight get a bounded chance to land before the CTA's shared memory is released
+      for (uint32_t s = 0; s < p.n_raw; s++) (void)mbar_wait(&raw_full[s], 0), (void)mbar_wait(&raw_full[s], 1);
+    }
   } else {
     // ---------------------------------------------------------------------------- epilogue
     const uint32_t q = warp & 3;  // a warp reads the TMEM lanes 32 * (warp % 4) ..

@@ -494,7 +494,7 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
     if (n_sel < k) atomicOr(d.status, MER_DEVSTAT_SHORT_SELECTION);
     if (S > k) {
       d.pair_expert[(size_t)token * S + k] = r.shared_expert_id;
-      d.pair_weight[(size_t)token * S + k] = 1.0f;
+      d.pair_weight[(size_t)token * S + k] = r.shared_scale ? r.shared_scale[token] : 1.0f;
     }
   }
 }
@@ -817,6 +817,7 @@ __global__ void __launch_bounds__(256) k_combine(MoeDispatch d) {
   if (i >= d.D) return;
   float acc = 0.0f;
   for (uint32_t s = 0; s < d.slots; s++) {
+    if (d.residual && s == d.routed_slots) acc = __fadd_rn(d.residual[(size_t)token * d.D + i], acc);  // hidden + routed sum
     size_t p = (size_t)token * d.slots + s;
     float w = d.pair_weight[p];
     if (d.pair_expert[p] == MER_NONE || w == 0.0f) continue;
@@ -831,7 +832,53 @@ __global__ void __launch_bounds__(256) k_combine(MoeDispatch d) {
     }
     acc = __fadd_rn(acc, __fmul_rn(w, yv));
   }
+  if (d.residual && d.routed_slots >= d.slots) acc = __fadd_rn(d.residual[(size_t)token * d.D + i], acc);
   d.out[(size_t)token * d.D + i] = acc;
+}
+
+// RMSNorm of every token row and / or the shared expert's gate scalar (RmsNorm::forward_inplace, transformer.rs:62-74;
+// SharedExpert::forward, transformer.rs:2224-2231).  One CTA per token; sums are block tree reductions (the
+// reference adds left to right: rounding differs in the last bits only).
+__global__ void __launch_bounds__(256) k_pre_moe(const float *__restrict__ x, uint32_t D, const float *__restrict__ rms_weight, float eps,
+                                                 const float *__restrict__ shared_gate, float *__restrict__ xn,
+                                                 float *__restrict__ shared_scale) {
+  __shared__ float s_red[8];
+  __shared__ float s_bcast;
+  const uint32_t token = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float *row = x + (size_t)token * D;
+  auto block_sum = [&](float v) -> float {
+    v = warp_sum(v);
+    __syncthreads();  // s_red / s_bcast of a previous reduction have been read
+    if (lane == 0) s_red[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.0f;
+      for (int w = 0; w < 8; w++) t += s_red[w];
+      s_bcast = t;
+    }
+    __syncthreads();
+    return s_bcast;
+  };
+  float scale = 1.0f;
+  if (rms_weight) {
+    float sq = 0.0f;
+    for (uint32_t i = threadIdx.x; i < D; i += blockDim.x) sq = fmaf(row[i], row[i], sq);
+    sq = block_sum(sq);
+    scale = 1.0f / sqrtf(sq / (float)D + eps);
+  }
+  float dot = 0.0f;
+  for (uint32_t i = threadIdx.x; i < D; i += blockDim.x) {
+    float v = row[i];
+    if (rms_weight) {
+      v = __fmul_rn(__fmul_rn(v, scale), rms_weight[i]);  // x * scale * weight, rounded after each product
+      xn[(size_t)token * D + i] = v;
+    }
+    if (shared_gate) dot = fmaf(shared_gate[i], v, dot);
+  }
+  if (shared_gate) {
+    dot = block_sum(dot);
+    if (threadIdx.x == 0) shared_scale[token] = 1.0f / (1.0f + expf(-dot));
+  }
 }
 
 template <int DT>
@@ -984,6 +1031,14 @@ cudaError_t launch_combine(const MoeDispatch &d, cudaStream_t s, int *launches) 
   if (d.combined) return cudaSuccess;  // the expert FFN launch already did it
   dim3 grid((d.D + 255) / 256, d.n_tokens);
   k_combine<<<grid, 256, 0, s>>>(d);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pre_moe(const float *x, uint32_t n_tokens, uint32_t D, const float *rms_weight, float eps, const float *shared_gate,
+                           float *xn, float *shared_scale, cudaStream_t s, int *launches) {
+  if (!rms_weight && !shared_gate) return cudaSuccess;
+  k_pre_moe<<<n_tokens, 256, 0, s>>>(x, D, rms_weight, eps, shared_gate, xn, shared_scale);
   if (launches) (*launches)++;
   return cudaGetLastError();
 }

@@ -33,6 +33,7 @@
 #include <type_traits>
 
 #include "../../include/mer_b200.h"
+#include "layout.cuh"
 #include "ptx.cuh"
 
 namespace {
@@ -219,6 +220,7 @@ __device__ __forceinline__ void ffn_stream_body(const StreamParams &p) {
 
   // ---------------------------------------------------------------------- consumer warps
   const uint32_t g = lane >> 2, t = lane & 3;
+  const uint32_t piece16 = packed_piece(g, t) * 16;  // byte offset of this lane's 16-byte piece inside a block record
   const uint32_t stage0 = smem_u32(s_stage) + warp * p.chunk_stride;  // this warp's tile chunk in stage 0
   const uint32_t frag0 = smem_u32(s_frag) + t * 16, init0 = smem_u32(s_init);
   uint32_t stage = 0, round = 0;
@@ -359,12 +361,12 @@ __device__ __forceinline__ void ffn_stream_body(const StreamParams &p) {
       uint32_t a0[4], a0h[4], a1[4], a1h[4];  // block kb: slots g / g+8; block kb+1: slots g / g+8
       float2 d0, d1;                          // {scale slot g, scale slot g+8} of each block
       if (DT == MER_DTYPE_Q4_0) {
-        const uint4 w = lds128(rec + lane * 16);
+        const uint4 w = lds128(rec + piece16);
         const uint2 sc = lds64(rec + 512 + g * 8);
         unpack_q4(w.x, a0), unpack_q4(w.y, a0h), unpack_q4(w.z, a1), unpack_q4(w.w, a1h);
         d0 = h2_to_f2(sc.x), d1 = h2_to_f2(sc.y);
       } else {
-        const uint4 w0 = lds128(rec + lane * 16), w1 = lds128(rec + 544 + lane * 16);
+        const uint4 w0 = lds128(rec + piece16), w1 = lds128(rec + 544 + piece16);
         const uint32_t sc0 = lds32(rec + 512 + g * 4), sc1 = lds32(rec + 544 + 512 + g * 4);
         unpack_q8(w0.x, w0.y, a0), unpack_q8(w0.z, w0.w, a0h), unpack_q8(w1.x, w1.y, a1), unpack_q8(w1.z, w1.w, a1h);
         d0 = h2_to_f2(sc0), d1 = h2_to_f2(sc1);
@@ -530,7 +532,12 @@ __device__ void ffn_stream_tail(const StreamParams &p) {
     for (uint32_t e = blockIdx.x * THREADS + threadIdx.x; e < d.n_tokens * D4; e += gridDim.x * THREADS) {
       const uint32_t token = e / D4, i4 = e % D4;
       float4 acc = make_float4(0, 0, 0, 0);
+      auto add_residual = [&]() {  // hidden + routed sum, before the shared expert's slot (model.rs:2742-2763)
+        const float4 r = __ldg(reinterpret_cast<const float4 *>(d.residual) + (size_t)token * D4 + i4);
+        acc.x = __fadd_rn(r.x, acc.x), acc.y = __fadd_rn(r.y, acc.y), acc.z = __fadd_rn(r.z, acc.z), acc.w = __fadd_rn(r.w, acc.w);
+      };
       for (uint32_t sl = 0; sl < d.slots; sl++) {
+        if (d.residual && sl == d.routed_slots) add_residual();
         const size_t pr = (size_t)token * d.slots + sl;
         const float w = d.pair_weight[pr];
         if (d.pair_expert[pr] == MER_NONE || w == 0.0f) continue;
@@ -544,6 +551,7 @@ __device__ void ffn_stream_tail(const StreamParams &p) {
         acc.z = __fadd_rn(acc.z, __fmul_rn(w, yv.z));
         acc.w = __fadd_rn(acc.w, __fmul_rn(w, yv.w));
       }
+      if (d.residual && d.routed_slots >= d.slots) add_residual();
       reinterpret_cast<float4 *>(d.out)[(size_t)token * D4 + i4] = acc;
     }
   } else if (p.tail == TAIL_REDUCE) {

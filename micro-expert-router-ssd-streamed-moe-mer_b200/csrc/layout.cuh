@@ -16,6 +16,10 @@
 //                         (slot g, blk 2p+1), (slot g+8, blk 2p+1)                          (512 B)
 //        [g][4 x f16]   = scales in the same order                                          (64 B)
 //   (g = lane / 4 and t = lane % 4 are the mma.sync m16n8k16 fragment coordinates.)
+//   Inside a record the 16-byte piece of lane L = (g, t) sits at position g*4 + ((t + g/2) % 4), not at L: the
+//   streaming kernels read one piece per lane (any bijection is conflict-free for them), while the GEMM kernels'
+//   dequantisers read the four pieces of ONE row slot in four steps, all lanes at the same t; the rotation spreads the
+//   eight row slots of a step over all 32 banks of shared memory (without it: 8-way bank conflicts).
 //
 // Shapes whose rows are not multiples of 256 columns keep the reference's flat stream.
 #pragma once
@@ -28,6 +32,9 @@ struct PackedAddr {
   size_t quant;  // byte offset of the quant byte that holds the weight
   size_t scale;  // byte offset of the f16 block scale
 };
+
+// Position (in 16-byte pieces) of the piece of fragment lane (g, t) inside a block record.
+__host__ __device__ inline uint32_t packed_piece(uint32_t g, uint32_t t) { return g * 4u + ((t + (g >> 1)) & 3u); }
 
 // Location of weight (matrix, row, col) inside a packed expert. matrix: 0 gate, 1 up, 2 down.
 template <int DT>
@@ -47,12 +54,12 @@ __host__ __device__ inline PackedAddr packed_locate(uint32_t D, uint32_t F, int 
   if (DT == 0) {
     const size_t rec = tile_base + (size_t)(kb >> 1) * 576;
     const uint32_t bip = kb & 1u, jj = j & 15u, t = jj >> 2;
-    a.quant = rec + (size_t)(g * 4 + t) * 16 + bip * 8 + half * 4 + (jj & 3u);
+    a.quant = rec + (size_t)packed_piece(g, t) * 16 + bip * 8 + half * 4 + (jj & 3u);
     a.scale = rec + 512 + g * 8 + bip * 4 + half * 2;
   } else {
     const size_t rec = tile_base + (size_t)kb * 544;
     const uint32_t t = j >> 3;
-    a.quant = rec + (size_t)(g * 4 + t) * 16 + half * 8 + (j & 7u);
+    a.quant = rec + (size_t)packed_piece(g, t) * 16 + half * 8 + (j & 7u);
     a.scale = rec + 512 + g * 4 + half * 2;
   }
   return a;

@@ -8,6 +8,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <functional>
 #include <mutex>
 #include <new>
 #include <unordered_map>
@@ -41,6 +42,10 @@ struct Slot {
 struct RouterEntry {
   RouterDev dev{};
   float *d_w = nullptr, *d_cbias = nullptr, *d_lbias = nullptr;
+  // steps either side of the MoE block (mer_layer_install)
+  float *d_rms_w = nullptr, *d_shared_gate = nullptr;
+  float rms_eps = 0.0f;
+  uint32_t layer_flags = 0;
 };
 
 }  // namespace
@@ -69,6 +74,7 @@ struct mer_backend {
   float *d_x = nullptr, *d_out = nullptr, *d_h = nullptr, *d_y = nullptr, *d_pair_weight = nullptr, *d_logits = nullptr;
   uint32_t *d_pair_expert = nullptr, *d_group_expert = nullptr, *d_offsets = nullptr, *d_perm = nullptr;
   uint32_t *d_status = nullptr, *d_counters = nullptr, *d_group_count = nullptr;  // d_group_count: [2 x max_groups]
+  float *d_xn = nullptr, *d_shared_scale = nullptr;  // RMSNorm'ed rows [max_tokens x D] and shared-expert gate scalars (allocated on first mer_layer_install)
   uint16_t *d_f16 = nullptr;
   void *d_stream_scratch = nullptr;
   void *d_gemm_scratch = nullptr;  // activation operand images of the tensor-core GEMM path
@@ -184,6 +190,8 @@ MoeDispatch base_dispatch(mer_backend *b) {
   d.swiglu_limit = b->cfg.swiglu_limit;
   d.scratch_pairs = b->max_pairs;
   d.packed = b->packed ? 1 : 0;
+  d.residual = nullptr;
+  d.routed_slots = 0xFFFFFFFFu;
   return d;
 }
 
@@ -358,11 +366,13 @@ void free_all(mer_backend *b) {
     F(kv.second.d_w);
     F(kv.second.d_cbias);
     F(kv.second.d_lbias);
+    F(kv.second.d_rms_w);
+    F(kv.second.d_shared_gate);
   }
   b->routers.clear();
   F(b->arena), F(b->d_expert_ptr), F(b->d_x), F(b->d_out), F(b->d_h), F(b->d_y), F(b->d_pair_weight), F(b->d_logits);
   F(b->d_pair_expert), F(b->d_group_expert), F(b->d_offsets), F(b->d_perm), F(b->d_status), F(b->d_counters), F(b->d_group_count);
-  F(b->d_f16), F(b->d_stream_scratch), F(b->d_gemm_scratch), F(b->d_dequant), F(b->d_raw_stage);
+  F(b->d_f16), F(b->d_stream_scratch), F(b->d_gemm_scratch), F(b->d_dequant), F(b->d_raw_stage), F(b->d_xn), F(b->d_shared_scale);
   H(b->h_expert_ptr), H(b->h_stage[0]), H(b->h_stage[1]), H(b->h_hdr), H(b->h_u32), H(b->h_f32);
   if (b->ev_compute_done) cudaEventDestroy(b->ev_compute_done);
   if (b->ev_copy_done) cudaEventDestroy(b->ev_copy_done);
@@ -432,8 +442,11 @@ int acquire_slot(mer_backend *b, uint32_t id, uint64_t generation, uint32_t flag
   return MER_OK;
 }
 
+// Fills `dst` with bytes [off, off + n) of the expert's gate||up||down stream; false = the source ran short.
+using ChunkReader = std::function<bool(size_t off, size_t n, uint8_t *dst)>;
+
 int admit_impl(mer_backend *b, uint32_t id, uint64_t generation, const void *blob, size_t bytes, uint32_t flags,
-               bool from_device) {
+               bool from_device, const ChunkReader *reader = nullptr) {
   const uint32_t layer = 0, expert = id;
   if (!b || !blob) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null backend or blob");
   if (id >= b->cfg.max_experts)
@@ -469,7 +482,7 @@ int admit_impl(mer_backend *b, uint32_t id, uint64_t generation, const void *blo
       CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(D2D)", cudaMemcpyAsync(payload, src, b->expert_bytes, cudaMemcpyDeviceToDevice, b->copy));
   } else {
     cudaPointerAttributes attr{};
-    bool pinned = cudaPointerGetAttributes(&attr, blob) == cudaSuccess && attr.type == cudaMemoryTypeHost;
+    bool pinned = !reader && cudaPointerGetAttributes(&attr, blob) == cudaSuccess && attr.type == cudaMemoryTypeHost;
     cudaGetLastError();
     if (pinned) {
       CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(H2D pinned)",
@@ -479,7 +492,12 @@ int admit_impl(mer_backend *b, uint32_t id, uint64_t generation, const void *blo
       for (size_t off = 0; off < b->expert_bytes; off += STAGE_BYTES, which ^= 1) {
         size_t n = std::min(STAGE_BYTES, b->expert_bytes - off);
         CU(MER_ERR_UPLOAD, "cudaEventSynchronize(stage)", cudaEventSynchronize(b->ev_stage[which]));
-        memcpy(b->h_stage[which], src + off, n);
+        if (reader) {  // e.g. pread from an expert file, straight into the pinned staging buffer
+          if (!(*reader)(off, n, b->h_stage[which]))
+            return fail(b, MER_ERR_UPLOAD, layer, expert, "the expert source ended before byte %zu of %zu", off + n, b->expert_bytes);
+        } else {
+          memcpy(b->h_stage[which], src + off, n);
+        }
         CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(H2D staged)",
            cudaMemcpyAsync(landing + off, b->h_stage[which], n, cudaMemcpyHostToDevice, b->copy));
         CU(MER_ERR_UPLOAD, "cudaEventRecord(stage)", cudaEventRecord(b->ev_stage[which], b->copy));
@@ -718,6 +736,69 @@ MER_EXPORT int mer_expert_admit_device(mer_backend *b, uint32_t expert_id, uint6
   return admit_impl(b, expert_id, generation, device_blob, bytes, flags, true);
 }
 
+MER_EXPORT int mer_expert_admit_file(mer_backend *b, uint32_t expert_id, uint64_t generation, const char *path, size_t block_align,
+                                     uint32_t flags) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t layer = 0, expert = expert_id;
+  if (!path) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null path");
+  FILE *f = fopen(path, "rb");
+  if (!f) return fail(b, MER_ERR_UPLOAD, layer, expert, "cannot open %s", path);
+  struct Closer {
+    FILE *f;
+    ~Closer() { fclose(f); }
+  } closer{f};
+  if (fseeko(f, 0, SEEK_END) != 0) return fail(b, MER_ERR_UPLOAD, layer, expert, "cannot seek in %s", path);
+  const uint64_t file_bytes = (uint64_t)ftello(f);
+  // the header region: at most one block (a UTH header is padded to block_align)
+  std::vector<uint8_t> head(std::min<uint64_t>(file_bytes, std::max<size_t>(block_align, 128)));
+  if (fseeko(f, 0, SEEK_SET) != 0 || fread(head.data(), 1, head.size(), f) != head.size())
+    return fail(b, MER_ERR_UPLOAD, layer, expert, "cannot read the header region of %s", path);
+  mer_uth_info h{};
+  mer_uth_probe(head.data(), head.size(), block_align, &h);
+  uint64_t payload_off = 0;
+  uint64_t range_off[3], range_len[3];
+  const uint64_t proj = b->expert_bytes / 3;
+  if (h.kind == MER_UTH_KIND_NONE) {
+    // a legacy blob: the file is the payload (plus page padding)
+    for (int i = 0; i < 3; i++) range_off[i] = i * proj, range_len[i] = proj;
+  } else {
+    if (h.dtype != b->cfg.dtype)
+      return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "%s holds dtype id %u, the backend runs %s", path, h.uth_dtype_id,
+                  b->cfg.dtype == MER_DTYPE_Q4_0 ? "q4_0" : "q8_0");
+    if (h.d_model != b->cfg.d_model || h.d_ff != b->cfg.d_ff)
+      return fail(b, MER_ERR_VALIDATION_DISPATCH, layer, expert, "%s is %llux%llu, the backend %llux%llu", path, (unsigned long long)h.d_model,
+                  (unsigned long long)h.d_ff, (unsigned long long)b->cfg.d_model, (unsigned long long)b->cfg.d_ff);
+    payload_off = h.payload_offset;
+    if (h.kind == MER_UTH_KIND_UTH2) {
+      // the probe saw only the header region: validate the ranges against the real payload length
+      const uint64_t payload_len = file_bytes > payload_off ? file_bytes - payload_off : 0;
+      for (int i = 0; i < 3; i++) {
+        range_off[i] = h.proj[i].offset, range_len[i] = h.proj[i].len;
+        if (range_len[i] != proj || range_off[i] + range_len[i] > payload_len)
+          return fail(b, MER_ERR_UPLOAD, layer, expert, "%s: projection %d covers %llu bytes at %llu, need %llu inside %llu", path, i,
+                      (unsigned long long)range_len[i], (unsigned long long)range_off[i], (unsigned long long)proj,
+                      (unsigned long long)payload_len);
+      }
+    } else {
+      for (int i = 0; i < 3; i++) range_off[i] = i * proj, range_len[i] = proj;
+    }
+  }
+  uint64_t need = 0;
+  for (int i = 0; i < 3; i++) need = std::max(need, payload_off + range_off[i] + range_len[i]);
+  if (file_bytes < need)
+    return fail(b, MER_ERR_UPLOAD, layer, expert, "%s has %llu bytes, the expert needs %llu", path, (unsigned long long)file_bytes,
+                (unsigned long long)need);
+  ChunkReader reader = [&](size_t off, size_t n, uint8_t *dst) -> bool {
+    while (n) {  // canonical offset -> (projection, offset inside it) -> file offset
+      const size_t pi = off / proj, in = off % proj, take = std::min<size_t>(n, proj - in);
+      if (pi >= 3 || fseeko(f, (off_t)(payload_off + range_off[pi] + in), SEEK_SET) != 0 || fread(dst, 1, take, f) != take) return false;
+      off += take, dst += take, n -= take;
+    }
+    return true;
+  };
+  return admit_impl(b, expert_id, generation, head.data(), b->expert_bytes, flags, false, &reader);  // the file is read completely before this returns
+}
+
 MER_EXPORT int mer_expert_retire(mer_backend *b, uint32_t expert_id, uint64_t generation) {
   if (!b) return MER_ERR_INVALID_ARGUMENT;
   const uint32_t layer = 0, expert = expert_id;
@@ -927,6 +1008,37 @@ MER_EXPORT int mer_router_install(mer_backend *b, uint32_t layer, const float *h
   return MER_OK;
 }
 
+MER_EXPORT int mer_layer_install(mer_backend *b, uint32_t layer, const mer_layer_cfg *cfg) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t expert = MER_NONE;
+  if (!cfg) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "null layer cfg");
+  if (cfg->rms_weight && !(cfg->rms_eps >= 0.0f)) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "rms_eps must be >= 0");
+  std::lock_guard<std::mutex> lock(b->mu);
+  auto it = b->routers.find(layer);
+  if (it == b->routers.end()) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "install the layer's router first (layer %u)", layer);
+  CU(MER_ERR_UPLOAD, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  CU(MER_ERR_UPLOAD, "cudaStreamSynchronize", cudaStreamSynchronize(b->compute));
+  drop_graphs(b);
+  RouterEntry &r = it->second;
+  const size_t D = b->cfg.d_model;
+  if (r.d_rms_w) cudaFree(r.d_rms_w), r.d_rms_w = nullptr;
+  if (r.d_shared_gate) cudaFree(r.d_shared_gate), r.d_shared_gate = nullptr;
+  if (cfg->rms_weight) {
+    CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(rms weight)", cudaMalloc((void **)&r.d_rms_w, D * 4));
+    CU(MER_ERR_UPLOAD, "cudaMemcpy(rms weight)", cudaMemcpy(r.d_rms_w, cfg->rms_weight, D * 4, cudaMemcpyHostToDevice));
+    if (!b->d_xn) CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(normed rows)", cudaMalloc((void **)&b->d_xn, (size_t)b->cfg.max_tokens * D * 4));
+  }
+  if (cfg->shared_gate) {
+    CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(shared gate)", cudaMalloc((void **)&r.d_shared_gate, D * 4));
+    CU(MER_ERR_UPLOAD, "cudaMemcpy(shared gate)", cudaMemcpy(r.d_shared_gate, cfg->shared_gate, D * 4, cudaMemcpyHostToDevice));
+    if (!b->d_shared_scale)
+      CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(shared scale)", cudaMalloc((void **)&b->d_shared_scale, (size_t)b->cfg.max_tokens * 4));
+  }
+  r.rms_eps = cfg->rms_eps;
+  r.layer_flags = cfg->flags;
+  return MER_OK;
+}
+
 namespace {
 // Enqueues router (+ optional FFN + combine) for device-resident x on stream s.
 int enqueue_layer(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out, bool run_ffn_too,
@@ -950,7 +1062,20 @@ int enqueue_layer(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tok
   if (!capturing) CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, s));
   cudaEvent_t *ev = (run_ffn_too && !capturing) ? next_timing_set(b) : nullptr;
   if (ev) cudaEventRecord(ev[0], s);
-  CU(MER_ERR_SUBMISSION, "router kernel", launch_router(r, d, b->cfg.max_tokens, s, launches));
+  // optional steps in front of the block: RMSNorm of the rows (router and experts then read the normed rows) and the
+  // shared expert's gate scalar; behind it: the residual add in the combine
+  RouterDev rl = r;
+  const RouterEntry &re = it->second;
+  if (re.d_rms_w || re.d_shared_gate) {
+    const bool gated = re.d_shared_gate && r.shared_expert_id != MER_NONE;
+    CU(MER_ERR_SUBMISSION, "pre-MoE kernel",
+       launch_pre_moe(d_x, d.n_tokens, d.D, re.d_rms_w, re.rms_eps, gated ? re.d_shared_gate : nullptr, b->d_xn, b->d_shared_scale, s, launches));
+    if (re.d_rms_w) d.x = b->d_xn;
+    if (gated) rl.shared_scale = b->d_shared_scale;
+  }
+  if (re.layer_flags & MER_LAYER_RESIDUAL) d.residual = d_x, d.routed_slots = r.top_k;
+  const RouterDev &r2 = rl;
+  CU(MER_ERR_SUBMISSION, "router kernel", launch_router(r2, d, b->cfg.max_tokens, s, launches));
   if (run_ffn_too) {
     if (ev) cudaEventRecord(ev[1], s);
     d.fuse_combine = 1;
@@ -1585,8 +1710,16 @@ int ep_layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *
 
   CU(MER_ERR_SUBMISSION, "cudaMemsetAsync(status)", cudaMemsetAsync(b->d_status, 0, 4, s));
   CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, s));
-  // publish this rank's tokens and their routing
-  CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(x)", cudaMemcpyAsync(x_pub, d_x, n_tokens * D * 4, cudaMemcpyDeviceToDevice, s));
+  // publish this rank's tokens (RMSNorm'ed when the layer has a norm installed) and their routing
+  const RouterEntry &re = it->second;
+  RouterDev rl = r;
+  const bool gated = re.d_shared_gate && r.shared_expert_id != MER_NONE;
+  if (re.d_rms_w || gated)
+    CU(MER_ERR_SUBMISSION, "pre-MoE kernel",
+       launch_pre_moe(d_x, (uint32_t)n_tokens, (uint32_t)D, re.d_rms_w, re.rms_eps, gated ? re.d_shared_gate : nullptr, x_pub, b->d_shared_scale, s,
+                      &launches));
+  if (!re.d_rms_w) CU(MER_ERR_SUBMISSION, "cudaMemcpyAsync(x)", cudaMemcpyAsync(x_pub, d_x, n_tokens * D * 4, cudaMemcpyDeviceToDevice, s));
+  if (gated) rl.shared_scale = b->d_shared_scale;
   MoeDispatch dr = base_dispatch(b);
   dr.n_tokens = (uint32_t)n_tokens;
   dr.slots = slots;
@@ -1594,7 +1727,7 @@ int ep_layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *
   dr.x = x_pub;
   dr.pair_expert = ids_pub;
   dr.pair_weight = w_own;
-  CU(MER_ERR_SUBMISSION, "router kernel", launch_router(r, dr, b->cfg.max_tokens, s, &launches, false));
+  CU(MER_ERR_SUBMISSION, "router kernel", launch_router(rl, dr, b->cfg.max_tokens, s, &launches, false));
   // pull the tokens that hit a local expert, run the local experts over them
   MoeDispatch d = base_dispatch(b);
   d.n_tokens = (uint32_t)(n_tokens * ep.world);
@@ -1609,7 +1742,8 @@ int ep_layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *
   CU(MER_ERR_SUBMISSION, "partial-sum kernel", launch_reduce_parts(d, s, &launches));
   // weighted sum in slot order, every pair's output read from the rank that owns its expert
   CU(MER_ERR_SUBMISSION, "combine kernel",
-     launch_ep_combine(ep, e2, (uint32_t)D, slots, ids_pub, w_own, d_out, b->d_status, s, &launches));
+     launch_ep_combine(ep, e2, (uint32_t)D, slots, ids_pub, w_own, (re.layer_flags & MER_LAYER_RESIDUAL) ? d_x : nullptr, d_out, b->d_status, s,
+                       &launches));
   CU(MER_ERR_SUBMISSION, "cudaEventRecord(stream use)", note_stream_use(b, s));
   b->ctr.kernel_launches += (uint64_t)launches;
   b->ctr.selected_routed_experts += n_tokens * slots;

@@ -82,6 +82,12 @@ def lib():
         L.mer_oracle_route_stable.argtypes = [C.POINTER(_Gate), vp, vp, vp, C.POINTER(sz)]
         L.mer_oracle_combine.argtypes = [vp, vp, sz, sz, vp, i32]
         L.mer_oracle_accumulate_ordered_f16.argtypes = [vp, sz, vp, sz, sz, vp]
+        L.mer_oracle_rmsnorm.argtypes = [vp, vp, sz, f32, vp]
+        L.mer_oracle_rmsnorm.restype = None
+        L.mer_oracle_shared_gate_scale.argtypes = [vp, vp, sz]
+        L.mer_oracle_shared_gate_scale.restype = f32
+        L.mer_oracle_add_residual.argtypes = [vp, vp, sz, vp]
+        L.mer_oracle_add_residual.restype = None
         L.mer_oracle_synth_hidden_state.argtypes = [u64, sz, u64, vp]
         L.mer_oracle_randomized_q8_expert.argtypes = [sz, sz, u64, vp]
         L.mer_oracle_moe_layer_forward.argtypes = [i32, i32, C.POINTER(_Gate), vp, sz, vp, vp, sz, sz,
@@ -251,6 +257,50 @@ def combine(outputs, scores, skip_zero=False) -> np.ndarray:
     out = np.empty(d, np.float32)
     lib().mer_oracle_combine(_p(outputs), _p(scores), k, d, _p(out), int(skip_zero))
     return out
+
+
+def rmsnorm(x, weight, eps=1e-6) -> np.ndarray:
+    """RmsNorm::forward (transformer.rs:62-80)."""
+    x, weight = _f32(x), _f32(weight)
+    assert x.size == weight.size
+    y = np.empty_like(x)
+    lib().mer_oracle_rmsnorm(_p(x), _p(weight), x.size, C.c_float(eps), _p(y))
+    return y
+
+
+def shared_gate_scale(gate_inp, x) -> float:
+    """sigmoid(gate_inp . x): the shared expert's gate scalar (transformer.rs:2224-2231)."""
+    g, x = _f32(gate_inp), _f32(x)
+    assert g.size == x.size
+    return float(lib().mer_oracle_shared_gate_scale(_p(g), _p(x), x.size))
+
+
+def add_residual(a, b) -> np.ndarray:
+    a, b = _f32(a), _f32(b)
+    out = np.empty_like(a)
+    lib().mer_oracle_add_residual(_p(a), _p(b), a.size, _p(out))
+    return out
+
+
+def moe_block_forward(dtype, gate, expert_blobs, hidden, d_ff, rms_weight=None, eps=1e-6, shared_blob=None, shared_gate=None,
+                      residual=True, variant=FWD_AUTHORITATIVE, n_threads=1):
+    """The MoE block of a decoder layer, token by token (transformer.rs:2493-2574, model.rs:2742-2763):
+    normed = RMSNorm(hidden); routing and routed experts on normed; x = hidden + sum_slots w * y (slot order); then
+    x = x + scale * shared(normed) with scale = sigmoid(shared_gate . normed) when a gate vector is given.
+    Returns (out[B, D], ids[B, k], weights[B, k])."""
+    hidden = _f32(hidden).reshape(-1, gate.d_model)
+    normed = np.stack([rmsnorm(h, rms_weight, eps) for h in hidden]) if rms_weight is not None else hidden
+    moe, ids, w, _ = moe_layer_forward(dtype, gate, expert_blobs, normed, d_ff, variant=variant, n_threads=n_threads)
+    out = np.stack([add_residual(h, m) for h, m in zip(hidden, moe)]) if residual else moe
+    if shared_blob is not None:
+        rows = []
+        for t in range(hidden.shape[0]):
+            y = expert_forward(dtype, shared_blob, normed[t], gate.d_model, d_ff, variant=variant)
+            if shared_gate is not None:
+                y = (y * np.float32(shared_gate_scale(shared_gate, normed[t]))).astype(np.float32)
+            rows.append(add_residual(out[t], y))
+        out = np.stack(rows)
+    return out, ids, w
 
 
 def accumulate_ordered_f16(outputs_f16_bits, weights, d_model):

@@ -812,6 +812,30 @@ void mer_oracle_combine(const float *outputs, const float *scores, size_t k, siz
   }
 }
 
+/* ------------------------------------------- the steps either side of the MoE block */
+
+/* RmsNorm::forward_inplace, transformer.rs:62-74: sequential sum of squares, scale = 1 / sqrt(mean + eps),
+ * y = (x * scale) * weight (two roundings, in that order). */
+void mer_oracle_rmsnorm(const float *x, const float *weight, size_t n, float eps, float *y) {
+  float sq_sum = 0.0f;
+  for (size_t i = 0; i < n; i++) sq_sum += x[i] * x[i];
+  float mean_sq = sq_sum / (float)n;
+  float scale = 1.0f / sqrtf(mean_sq + eps);
+  for (size_t i = 0; i < n; i++) y[i] = x[i] * scale * weight[i];
+}
+
+/* SharedExpert::forward, transformer.rs:2224-2231: sigmoid of the sequential dot gate_inp . x. */
+float mer_oracle_shared_gate_scale(const float *gate_inp, const float *x, size_t n) {
+  float logit = 0.0f;
+  for (size_t i = 0; i < n; i++) logit += gate_inp[i] * x[i];
+  return 1.0f / (1.0f + expf(-logit));
+}
+
+/* add_residual_into, transformer.rs:2006-2011 */
+void mer_oracle_add_residual(const float *a, const float *b, size_t n, float *out) {
+  for (size_t i = 0; i < n; i++) out[i] = a[i] + b[i];
+}
+
 /* engine.rs:1651-1673 */
 int mer_oracle_accumulate_ordered_f16(const uint16_t *outputs, size_t outputs_len,
                                       const float *weights, size_t n_weights, size_t d_model,

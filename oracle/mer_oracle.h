@@ -133,6 +133,12 @@ int mer_oracle_route_stable(const mer_oracle_gate *gate, const float *x,
 void mer_oracle_combine(const float *outputs, const float *scores, size_t k,
                         size_t d, float *out, int skip_zero);
 
+/* RmsNorm::forward_inplace (transformer.rs:62-74), the shared expert's sigmoid gate scalar
+ * (transformer.rs:2224-2231) and add_residual_into (transformer.rs:2006-2011). */
+void mer_oracle_rmsnorm(const float *x, const float *weight, size_t n, float eps, float *y);
+float mer_oracle_shared_gate_scale(const float *gate_inp, const float *x, size_t n);
+void mer_oracle_add_residual(const float *a, const float *b, size_t n, float *out);
+
 /* accumulate_ordered_f16_outputs: engine.rs:1651-1673.  Returns 1 on success, 0 on length mismatch. */
 int mer_oracle_accumulate_ordered_f16(const uint16_t *outputs, size_t outputs_len,
                                       const float *weights, size_t n_weights,

@@ -109,4 +109,4 @@ def test_mixtral_shaped_layer_at_full_size():
         b.set_kernel_path(3)
         gemm_out, _, _ = b.moe_layer_forward(0, x)
         rms = np.sqrt(np.mean(stream_out.astype(np.float64) ** 2, axis=1, keepdims=True))
-        assert float((np.abs(stream_out - gemm_out) / rms).max()) <= 2e-4
+        assert float((np.abs(stream_out - gemm_out) / rms).max()) <= 5e-4

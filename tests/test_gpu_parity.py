@@ -606,3 +606,54 @@ def test_device_side_weight_generator_matches_the_host_generator(dtype):
         got = b.expert_forward_f32(0, 2, x)
     ref = oracle.expert_forward(dtype, synth.make_expert_blob(dtype, D, F, 9, 3, 5), x[1], D, F)
     assert rel_rms_err(got[1], ref) <= FFN_TOL
+
+
+@pytest.mark.parametrize("dtype,E,D,F,k,B", [(oracle.Q8_0, 8, 256, 256, 2, 11), (oracle.Q4_0, 6, 64, 96, 2, 5),
+                                             (oracle.Q8_0, 16, 512, 256, 4, 40)])
+@pytest.mark.parametrize("case", ["norm+residual", "norm+residual+gated-shared", "gated-shared", "residual+shared"])
+def test_moe_block_with_rmsnorm_residual_and_gated_shared_expert(dtype, E, D, F, k, B, case):
+    # moe_pre (RMSNorm -> router) ... moe_combine (+ residual) ... shared expert with its sigmoid gate scalar:
+    # transformer.rs:52-95, 2493-2574, 2224-2237, model.rs:2742-2763
+    rng = np.random.default_rng(91)
+    blobs = [random_blob(dtype, D, F, 91, e) for e in range(E + 1)]
+    W = synth.make_router(E, D, 91)
+    hidden = (synth.make_activations(B, D, 91) * 3.0 + 0.5).astype(np.float32)
+    norm = "norm" in case
+    shared = "shared" in case
+    gated = "gated" in case
+    residual = "residual" in case
+    rms_w = (1.0 + 0.1 * rng.standard_normal(D)).astype(np.float32) if norm else None
+    gate_vec = (0.05 * rng.standard_normal(D)).astype(np.float32) if gated else None
+    og = oracle.LinearGate(W, E, D, k)
+    ref, rids, rw = oracle.moe_block_forward(dtype, og, blobs[:E], hidden, F, rms_weight=rms_w, eps=1e-5,
+                                             shared_blob=blobs[E] if shared else None, shared_gate=gate_vec, residual=residual,
+                                             n_threads=8)
+    shared_id = 3 * E if shared else 0xFFFFFFFF
+    with backend(dtype, D, F, n_experts=E + 1, max_experts=4 * E, max_tokens=64, max_top_k=k + 1) as b:
+        for e in range(E):
+            b.admit(e, 1, blobs[e])
+        if shared:
+            b.admit(shared_id, 1, blobs[E])
+        mer_b200.LinearGate(W, E, D, k).bind(b, 0, shared_id)
+        b.install_layer(0, rms_weight=rms_w, rms_eps=1e-5, shared_gate=gate_vec, residual=residual)
+        for path in ([0, 1] if D % 256 == 0 else [0]):
+            b.set_kernel_path(path)
+            out, ids, w = b.moe_layer_forward(0, hidden)
+            assert (ids == rids).all()
+            assert np.abs(w - rw).max() <= 2e-6
+            # the bar is relative to the RMS of the block's contribution (the residual stream itself is exact)
+            contrib = ref - (hidden if residual else 0)
+            rms = np.sqrt(np.mean(contrib.astype(np.float64) ** 2))
+            assert float(np.abs(out.astype(np.float64) - ref).max() / rms) <= FFN_TOL, (case, path)
+        if gated:  # the gate scalar really scales the shared expert: without it the output differs
+            b.install_layer(0, rms_weight=rms_w, rms_eps=1e-5, shared_gate=None, residual=residual)
+            plain, _, _ = b.moe_layer_forward(0, hidden)
+            assert float(np.abs(plain - out).max()) > 1e-3
+        # in place: out aliases x on the device entry point
+        torch = pytest.importorskip("torch")
+        b.install_layer(0, rms_weight=rms_w, rms_eps=1e-5, shared_gate=gate_vec, residual=residual)
+        xd = torch.from_numpy(hidden.copy()).cuda()
+        b.moe_layer_forward_device(0, xd.data_ptr(), B, xd.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        b.stream_check(0, torch.cuda.current_stream().cuda_stream)
+        if residual or norm:
+            assert (xd.cpu().numpy().view(np.uint32) == out.view(np.uint32)).all()
