@@ -496,6 +496,19 @@ int mer_ep_local_experts_forward_device(mer_backend *b, uint32_t layer, const fl
  * make the same sequence of calls with the same n_tokens. */
 int mer_ep_layer_forward_device(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens,
                                 float *d_out, void *stream);
+/* ---- the same layer with NCCL all-to-all dispatch and combine (the library calls NCCL itself; it binds libnccl.so.2
+ * at run time, MER_ERR_INELIGIBLE when none can be loaded).  One rank obtains a 128-byte ncclUniqueId, the host hands
+ * it to every rank (any transport), every rank calls mer_ep_nccl_init after mer_ep_init (collective).  Per layer:
+ * route the rank's tokens, pack every (token, slot) pair into the send segment of the rank that owns its expert,
+ * all-gather the row counts, grouped ncclSend / ncclRecv of only the rows that hit a peer's experts (+ their expert
+ * ids), local experts over the received rows, the outputs back the same way, weighted sum in slot order.  The call
+ * synchronises `stream` once (the exchange is sized on the host from the counts) and is otherwise asynchronous.
+ * Stands in for RouteExperts(layer, expert_ids, hidden) -> ffn_out of the reference's shard protocol
+ * (proto/route_experts.proto, distributed.rs). ---- */
+#define MER_NCCL_ID_BYTES 128
+int mer_ep_nccl_unique_id(void *id_out /*[MER_NCCL_ID_BYTES]*/);
+int mer_ep_nccl_init(mer_backend *b, const void *unique_id);
+int mer_ep_layer_forward_a2a_device(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out, void *stream);
 /* Synchronises `stream` and turns the device status word into a typed error (for _device calls). */
 int mer_stream_check(mer_backend *b, uint32_t layer, void *stream);
 

@@ -158,6 +158,9 @@ ABI_SYMBOLS = {
     "mer_router_route_device": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _vp, _vp]),
     "mer_ep_local_experts_forward_device": (C.c_int, [_vp, _u32, _vp, _vp, _vp, _sz, _sz, _vp, _vp]),
     "mer_ep_layer_forward_device": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _vp]),
+    "mer_ep_nccl_unique_id": (C.c_int, [_vp]),
+    "mer_ep_nccl_init": (C.c_int, [_vp, _vp]),
+    "mer_ep_layer_forward_a2a_device": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _vp]),
     "mer_stream_check": (C.c_int, [_vp, _u32, _vp]),
     "mer_moe_layer_forward_submit": (C.c_int, [_vp, _u32, _vp, _sz, _vp, _u32]),
     "mer_moe_layer_forward_wait": (C.c_int, [_vp, _u32]),

@@ -97,6 +97,14 @@ cudaError_t launch_ep_gather(const EpDev &ep, uint32_t epoch, uint32_t D, uint32
 cudaError_t launch_ep_combine(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, const uint32_t *ids, const float *w,
                               const float *residual, float *out, uint32_t *status, cudaStream_t s, int *launches);
 
+// NCCL all-to-all mode: pack every pair into the send segment of its expert's owner (segment d = rows [d * seg_rows, ...),
+// cursors[d] counts its rows, pos[p] = row the pair went to); combine from the rows that came back.
+cudaError_t launch_a2a_pack(const EpDev &ep, uint32_t D, uint32_t slots, uint32_t n_pairs, uint32_t seg_rows, const float *x,
+                            const uint32_t *ids, uint32_t *cursors, float *send_x, uint32_t *send_meta, uint32_t *pos, cudaStream_t s,
+                            int *launches);
+cudaError_t launch_a2a_combine(uint32_t n_tokens, uint32_t D, uint32_t slots, uint32_t routed_slots, const uint32_t *pos, const float *w,
+                               const float *ret_y, const float *residual, float *out, cudaStream_t s, int *launches);
+
 // kernels_generic.cu
 // Groups pairs by expert for a whole layer whose routing is already in d.pair_expert (+ pass table).
 cudaError_t launch_groups_layer(const RouterDev &r, const MoeDispatch &d, cudaStream_t s, int *launches);

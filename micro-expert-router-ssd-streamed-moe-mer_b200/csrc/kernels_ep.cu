@@ -7,6 +7,10 @@
 //       the rows it needs with plain peer loads (no TMA, no multicast) after a flag barrier (the
 //       first CTA of the gather / combine kernel raises this rank's flag on every peer, all CTAs
 //       wait for the flags of the ranks they read).
+//   (3) NCCL all-to-all: every (token, slot) pair is packed into the send segment of the rank that owns its expert
+//       (k_a2a_pack), the library exchanges the segments with grouped ncclSend / ncclRecv, the owners run their
+//       experts over the rows they received and send the outputs back the same way; k_a2a_combine sums each
+//       token's pairs in slot order from the returned rows.
 // Every wait on a peer is bounded by wall-clock time; on expiry the kernel latches
 // MER_DEVSTAT_TIMEOUT and carries on without the peer's data (the host then fails the call).
 #include "../../include/mer_b200.h"
@@ -165,7 +169,74 @@ __global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, uint32_t epoch, ui
   }
 }
 
+// (3a) One warp per (token, slot) pair: claim the next row of the owner's send segment, copy the token's row and the
+// expert id there, remember where the pair went.  Segment d starts at row d * seg_rows.  The order of the pairs
+// inside a segment is whatever the atomics give; nothing depends on it.
+__global__ void __launch_bounds__(256) k_a2a_pack(EpDev ep, uint32_t D, uint32_t slots, uint32_t n_pairs, uint32_t seg_rows,
+                                                  const float *__restrict__ x, const uint32_t *__restrict__ ids,
+                                                  uint32_t *__restrict__ cursors, float *__restrict__ send_x,
+                                                  uint32_t *__restrict__ send_meta, uint32_t *__restrict__ pos) {
+  const uint32_t p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (p >= n_pairs) return;
+  const uint32_t token = p / slots, slot = p % slots;
+  const uint32_t e = ids[p];
+  if (e == MER_NONE) {
+    if (lane == 0) pos[p] = MER_NONE;
+    return;
+  }
+  const uint32_t dest = slot >= ep.top_k ? ep.rank : (e - ep.id_base) / ep.experts_per_rank;  // the shared expert runs at home
+  uint32_t row = 0;
+  if (lane == 0) row = dest * seg_rows + atomicAdd(cursors + dest, 1u);
+  row = __shfl_sync(0xffffffffu, row, 0);
+  if (lane == 0) pos[p] = row, send_meta[row] = e;
+  const float4 *src = reinterpret_cast<const float4 *>(x) + (size_t)token * (D / 4);
+  float4 *dst = reinterpret_cast<float4 *>(send_x) + (size_t)row * (D / 4);
+  for (uint32_t i = lane; i < D / 4; i += 32) dst[i] = __ldg(src + i);
+}
+
+// (3b) out[t] = sum over slots, in slot order, of weight * y, y of a pair = the row that came back for it
+// (same order and rounding as k_combine).  One CTA per token.
+__global__ void __launch_bounds__(256) k_a2a_combine(uint32_t D, uint32_t slots, uint32_t routed_slots, const uint32_t *__restrict__ pos,
+                                                     const float *__restrict__ w, const float *__restrict__ ret_y,
+                                                     const float *__restrict__ residual, float *__restrict__ out) {
+  const uint32_t t = blockIdx.x;
+  for (uint32_t i4 = threadIdx.x; i4 < D / 4; i4 += blockDim.x) {
+    float4 acc = make_float4(0, 0, 0, 0);
+    for (uint32_t sl = 0; sl <= slots; sl++) {
+      if (residual && sl == min(routed_slots, slots)) {  // hidden + routed sum, before the shared expert's slot
+        const float4 r = __ldg(reinterpret_cast<const float4 *>(residual) + (size_t)t * (D / 4) + i4);
+        acc.x = __fadd_rn(r.x, acc.x), acc.y = __fadd_rn(r.y, acc.y), acc.z = __fadd_rn(r.z, acc.z), acc.w = __fadd_rn(r.w, acc.w);
+      }
+      if (sl == slots) break;
+      const uint32_t row = pos[t * slots + sl];
+      const float wt = w[t * slots + sl];
+      if (row == MER_NONE || wt == 0.0f) continue;
+      const float4 y = __ldcg(reinterpret_cast<const float4 *>(ret_y) + (size_t)row * (D / 4) + i4);
+      acc.x = __fadd_rn(acc.x, __fmul_rn(wt, y.x));
+      acc.y = __fadd_rn(acc.y, __fmul_rn(wt, y.y));
+      acc.z = __fadd_rn(acc.z, __fmul_rn(wt, y.z));
+      acc.w = __fadd_rn(acc.w, __fmul_rn(wt, y.w));
+    }
+    reinterpret_cast<float4 *>(out)[(size_t)t * (D / 4) + i4] = acc;
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_a2a_pack(const EpDev &ep, uint32_t D, uint32_t slots, uint32_t n_pairs, uint32_t seg_rows, const float *x,
+                            const uint32_t *ids, uint32_t *cursors, float *send_x, uint32_t *send_meta, uint32_t *pos, cudaStream_t s,
+                            int *launches) {
+  k_a2a_pack<<<(n_pairs + 7) / 8, 256, 0, s>>>(ep, D, slots, n_pairs, seg_rows, x, ids, cursors, send_x, send_meta, pos);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_a2a_combine(uint32_t n_tokens, uint32_t D, uint32_t slots, uint32_t routed_slots, const uint32_t *pos, const float *w,
+                               const float *ret_y, const float *residual, float *out, cudaStream_t s, int *launches) {
+  k_a2a_combine<<<n_tokens, 256, 0, s>>>(D, slots, routed_slots, pos, w, ret_y, residual, out);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
+}
 
 cudaError_t launch_ep_filter(const EpDev &ep, const uint32_t *ids_all, const float *w_all, uint32_t n_pairs, uint32_t slots,
                              uint32_t *pair_expert, float *pair_weight, cudaStream_t s, int *launches) {

@@ -1,7 +1,7 @@
 // Grouped expert FFN for token groups of a dozen tokens and more (prefill, expert-parallel decode):
-// tcgen05 tensor-core GEMM per (expert, 256 weight rows, up to 128 tokens) with TMEM accumulators.
+// tcgen05 tensor-core GEMM per (expert, 128 weight rows, up to 128 tokens) with TMEM accumulators.
 //
-//   D[128 weight rows x N tokens] += A[128 x 32] * B[N x 32]^T      per 32-value block of K, for two row tiles
+//   D[128 weight rows x N tokens] += A[128 x 32] * B[N x 32]^T      per 32-value block of K
 //
 //   * A never touches shared memory as an operand: the packed Q4_0 / Q8_0 tile chunks of layout.cuh
 //     are streamed global -> shared by bulk async copies, eight warps dequantise them block by block into
@@ -11,14 +11,12 @@
 //     the two accumulators.
 //   * B is the activation tile as f16 hi + lo parts (22 significant bits after an exact power-of-two
 //     per-row scaling), laid out in the K-major no-swizzle core-matrix order by k_gemm_act_image and
-//     fetched with one bulk copy per 64 values of K into a five-stage shared-memory ring.  B is 4 bytes per
-//     value against ~1 byte per weight, so it dominates what a CTA pulls from L2: an item therefore covers
-//     TWO 128-row tiles of the expert (one accumulator each) that share every activation stage, which
-//     halves the activation traffic per MMA.
+//     fetched with one bulk copy per 64 values of K into a five-stage shared-memory ring.
 //   * Three MMAs per 16 values of K (hi*hi, hi*lo, lo*hi; lo*lo is below fp32 resolution) accumulate
 //     in fp32 in TMEM, so the result matches the fp32 reference to ~1e-6 instead of f16's 1e-3.
 //   * Warp roles: 0 = producer of the activation stages, 1 = MMA issuer (one elected lane) and TMEM owner,
-//     2..9 = epilogue (four warps per accumulator: tcgen05.ld, un-scaling, SiLU(gate)*up or plain store),
+//     2..9 = epilogue (four warps per accumulator buffer: tcgen05.ld, un-scaling, SiLU(gate)*up or plain store; two
+//     buffers let the epilogue of one item overlap the MMAs of the next two),
 //     10..17 = dequantisers (a warp reaches the 32 TMEM lanes of its quarter; the two warps of a quarter
 //     take alternate blocks).  Each dequantiser warp also issues the bulk copy of one of the eight packed
 //     tiles of every weight stage: issuing a bulk copy occupies a thread for ~100 cycles, and one producer
@@ -39,15 +37,14 @@ constexpr int W_PRODUCER = 0, W_MMA = 1, W_EPI0 = 2, W_DQ0 = 10;
 constexpr int EPI_WARPS = 4, DQ_WARPS = 8;  // EPI_WARPS per accumulator
 constexpr uint32_t RAW_BLOCKS = 4;       // blocks of K per weight stage (per packed tile: one bulk copy)
 constexpr uint32_t G_HEADER = 1024;
-constexpr uint32_t TMEM_COLS = 512;      // [0, 256): the accumulators of an item's two row tiles, up to 128 columns each; [256, 512): A stages
+constexpr uint32_t TMEM_COLS = 512;      // [0, 256): two accumulator buffers of up to 128 columns; [256, 512): A stages
 constexpr uint32_t TMEM_A0 = 256, A_STAGES = 8, A_STAGE_COLS = 32;  // a stage = one block: 16 columns hi + 16 columns lo
 constexpr uint32_t MAX_RING = 8;
-// The MMA issuer synchronises once per GROUP blocks of K of one row tile (a "sub-group"; sub-groups alternate
-// between the item's two row tiles, so A-stage half j always belongs to row tile j): it waits for the sub-group's
-// A stages, issues its MMAs and commits ONE barrier, done[], that releases those A stages and, after the second
-// row tile, the activation stages both read (a wait or a commit per block cost more issue time than the block's
-// MMAs take to run).  A waiter is never two phases behind a done[] barrier: the issuer leads the dequantisers by
-// at most two sub-groups and the producer by at most n_b / 2 + 1 groups of K, well inside the ring.
+// The MMA issuer synchronises once per GROUP blocks of K: it waits for a whole group of A stages, issues the
+// group's MMAs and commits ONE barrier, done[], that releases both the group's A stages and the activation stages
+// it read (a wait or a commit per block cost more issue time than the block's MMAs take to run).  A waiter is never
+// two phases behind a done[] barrier: the issuer leads the dequantisers by at most two groups and the producer by
+// at most n_b / 2 + 1, well inside the ring.
 constexpr uint32_t GROUP = 4, DONE_RING = 8;
 static_assert(GROUP == RAW_BLOCKS, "a weight stage holds exactly one group of blocks");
 constexpr float POW2_SCALE_TARGET = 9;   // activations are scaled so that the row maximum lies in [256, 512)
@@ -68,8 +65,19 @@ struct GemmParams {
 // ------------------------------------------------------------------------------ tcgen05 PTX
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// One lane of a converged warp.  The MMA warp runs its loops and waits with all 32 lanes, so that every address and
+// descriptor it computes is warp-uniform, and only the tcgen05.mma / tcgen05.commit instructions themselves are
+// issued by the elected lane (always the same one).  Running the whole loop inside `if (lane == 0)` instead made
+// every operand a per-thread value that had to be moved into uniform registers per instruction: ~85 cycles of issue
+// time per MMA, more than a 128-column MMA takes to execute.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void tc_commit(uint64_t *bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+  if (elect_one())
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // K-major, no swizzle: 8-row x 16-byte core matrices; LBO = step between core matrices along K,
 // SBO = step between 8-row groups.  Bits: start >> 4 [0,14), LBO >> 4 [16,30), SBO >> 4 [32,46), version 1 [46,48).
@@ -79,20 +87,17 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
 // f16 x f16 -> f32, both operands K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t instr_desc(uint32_t n) { return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
 // A operand read from tensor memory (lane = row, a 32-bit column = two consecutive values of K), B through a descriptor.
+// Called by the whole (converged) warp; the elected lane issues.
 __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
+  if (elect_one())
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
 }
-// The same, always accumulating (no predicate to set up: the issuing thread's instruction count is what limits it).
 __device__ __forceinline__ void tc_mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.eq.b32 p, 0, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%4, %4, %4, %4}, p;\n}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b), "r"(idesc), "r"(0u)
-      : "memory");
+  tc_mma_ts(d_tmem, a_tmem, b, idesc, 1u);
 }
 // 32 columns of this thread's TMEM lane (lane = 32 * (warp % 4) + lane id).
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
@@ -144,12 +149,12 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
   const MoeDispatch &d = p.d;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const uint32_t m_pairs = p.rows / (p.phase == 0 ? 128u : 256u);  // pairs of 128-row MMA tiles (8 packed tiles each)
-  const uint32_t n_chunks = p.kb_total / 2;
+  const uint32_t m_tiles = p.rows / (p.phase == 0 ? 64u : 128u);  // 128-row MMA tiles (8 packed tiles each)
+  const uint32_t n_chunks = p.kb_total / 2, n_groups = p.kb_total / GROUP;
   const uint32_t n_passes = *d.n_passes;
-  // Items (pass, pair of row tiles) are dealt round-robin: the CTAs running at any moment work on a dozen
+  // Items (pass, 128-row tile) are dealt round-robin: the CTAs running at any moment work on a dozen
   // neighbouring passes, so the activation images they all re-read stay in L2.
-  const uint32_t n_items = n_passes * m_pairs;
+  const uint32_t n_items = n_passes * m_tiles;
   const uint32_t item_beg = blockIdx.x, item_step = gridDim.x;
   if (item_beg >= n_items) return;
 
@@ -180,7 +185,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *s_tmem;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *s_tmem, 0);  // the same value in every lane, and visibly so
 
   const size_t proj_bytes = (size_t)d.D * d.F / 32 * BB;
   const size_t tile_bytes = (size_t)p.kb_total * 16 * BB;
@@ -192,18 +197,18 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
   bool ok = true;
 
   if (warp == W_PRODUCER) {
-    // ------------------------------------------------------------------------ copy producer
-    // activations: one stage = 2 blocks of K (one bulk copy), read by both row tiles of the item
+    // ------------------------------------------------------------------------ producer of the activation stages
+    // one stage = 2 blocks of K of the pass's activation image (one bulk copy)
     Ring rb(p.n_b);
     uint32_t gchunk = 0;  // 64-value activation chunks issued so far, over all items
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
-      const uint32_t pass = item / m_pairs;
+      const uint32_t pass = item / m_tiles;
       if (!expert_base(pass)) continue;
       const uint8_t *bsrc = p.act_img + (size_t)pass * n_chunks * b_stage;
       for (uint32_t c = 0; c < n_chunks && ok; c++) {
         if (gchunk >= p.n_b) {
-          // the slot's previous chunk was last read by the second sub-group of the group of K it belongs to
-          const uint32_t sp = 2 * ((gchunk - p.n_b) / 2) + 1;
+          // the slot's previous chunk was read by the MMAs of group (gchunk - n_b) / 2
+          const uint32_t sp = (gchunk - p.n_b) / (GROUP / 2);
           ok = mbar_wait(&done[sp % DONE_RING], (sp / DONE_RING) & 1);
         }
         gchunk++;
@@ -224,73 +229,63 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     }
   } else if (warp == W_MMA) {
     // -------------------------------------------------------------------------- MMA issuer
-    // one step = one 32-value block of K of one row tile: two instructions of 16 values for each of the three operand pairings
+    // The whole warp walks the loops and waits (every value it computes is warp-uniform); the elected lane issues.
+    // one step = one 32-value block of K: two instructions of 16 values for each of the three operand pairings
     Ring rb(p.n_b);
-    uint32_t n_done = 0;  // items issued so far
-    uint32_t grp = 0;     // sub-groups (GROUP blocks of one row tile) issued so far, over all items; grp & 1 = row tile
+    uint32_t n_done = 0;  // items issued so far: accumulator buffer = n_done & 1, its k-th use has k = n_done >> 1
+    uint32_t grp = 0;     // groups of GROUP blocks issued so far, over all items; A-stage half = grp & 1
+    // B descriptors differ only in their start-address field: one base, then 64-bit adds of (byte offset >> 4).
+    // (The ring lies well inside the 256 KB the 14-bit field spans, so the adds never carry out of it.)
+    const uint64_t b_desc0 = smem_desc(smem_u32(s_b), p.b_lbo, 128);
+    const uint32_t stage16 = b_stage >> 4, half16 = (4 * p.b_lbo) >> 4, j16 = (2 * p.b_lbo) >> 4, lo16 = b_term >> 4;
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
-      const uint32_t pass = item / m_pairs;
+      const uint32_t pass = item / m_tiles;
       if (!expert_base(pass)) continue;
+      const uint32_t buf = n_done & 1, use = n_done >> 1;
       // the MMA is as wide as the pass has tokens (rounded up to 16 columns): a ragged last pass of a group costs
       // its share, not a full tile
-      const uint32_t idesc = instr_desc(min(p.bn, (d.pass_count[pass] + 15u) & ~15u));
-      if (lane == 0) {
-        // B descriptors differ only in their start-address field: one base, then 64-bit adds of (byte offset >> 4).
-        // (The ring lies well inside the 256 KB the 14-bit field spans, so the adds never carry out of it.)
-        const uint64_t b_desc0 = smem_desc(smem_u32(s_b), p.b_lbo, 128);
-        const uint32_t stage16 = b_stage >> 4, half16 = (4 * p.b_lbo) >> 4, j16 = (2 * p.b_lbo) >> 4, lo16 = b_term >> 4;
-        for (uint32_t st = 0; st < p.kb_total && ok; st += GROUP) {
-          const bool last = st + GROUP >= p.kb_total;
-#pragma unroll 1
-          for (uint32_t rt = 0; rt < 2 && ok; rt++, grp++) {
-            const uint32_t d_tmem = tmem_base + rt * 128;
-            if (st == 0 && n_done > 0) {  // the previous item's epilogue has drained this accumulator
-              ok = mbar_wait(&acc_empty[rt], (n_done - 1) & 1);
-              if (!ok) break;
-            }
-            ok = mbar_wait(&a_full[rt], (grp >> 1) & 1);
-            if (*s_abort) ok = false;
+      const uint32_t idesc = instr_desc(min(p.bn, (__ldg(d.pass_count + pass) + 15u) & ~15u));
+      const uint32_t d_tmem = tmem_base + buf * 128;
+      for (uint32_t st = 0; st < p.kb_total && ok; st += GROUP, grp++) {
+        const uint32_t ag = grp & 1;
+        if (st == 0 && use > 0) ok = mbar_wait(&acc_empty[buf], (use - 1) & 1);  // the buffer's previous item has been drained
+        if (ok) ok = mbar_wait(&a_full[ag], (grp >> 1) & 1);
+        if (*s_abort) ok = false;
+        ok = __all_sync(0xffffffffu, ok);  // warp-uniform by construction; the vote also tells the compiler so
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (uint32_t b4 = 0; b4 < GROUP; b4++) {
+          if (!(b4 & 1)) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&b_full[rb.stage], rb.round & 1));
             if (!ok) break;
             tc_fence_after();
-#pragma unroll
-            for (uint32_t b4 = 0; b4 < GROUP; b4++) {
-              uint32_t bs = rb.stage + (b4 >> 1), br = rb.round;  // the group's two activation stages, shared by both row tiles
-              if (bs >= p.n_b) bs -= p.n_b, br++;
-              if (rt == 0 && !(b4 & 1)) {
-                ok = mbar_wait(&b_full[bs], br & 1);
-                if (!ok) break;
-                tc_fence_after();
-              }
-              const uint32_t a_hi = tmem_base + TMEM_A0 + (rt * GROUP + b4) * A_STAGE_COLS, a_lo = a_hi + 16;
-              const uint64_t b_blk = b_desc0 + (uint64_t)(bs * stage16 + (b4 & 1) * half16);
-#pragma unroll
-              for (uint32_t j = 0; j < 2; j++) {  // 16 values of K per instruction: 8 TMEM columns of A, two core-matrix columns of B
-                const uint64_t dbh = b_blk + (uint64_t)(j * j16), dbl = dbh + lo16;
-                if (b4 == 0 && j == 0)
-                  tc_mma_ts(d_tmem, a_hi, dbh, idesc, st != 0);  // the item's first MMA of a row tile overwrites its accumulator
-                else
-                  tc_mma_ts_acc(d_tmem, a_hi + j * 8, dbh, idesc);
-                tc_mma_ts_acc(d_tmem, a_hi + j * 8, dbl, idesc);
-                tc_mma_ts_acc(d_tmem, a_lo + j * 8, dbh, idesc);
-              }
-            }
-            if (!ok) break;
-            tc_commit(&done[grp % DONE_RING]);
-            if (last) tc_commit(&acc_full[rt]);
           }
-          rb.advance(), rb.advance();
+          const uint32_t a_hi = tmem_base + TMEM_A0 + (ag * GROUP + b4) * A_STAGE_COLS, a_lo = a_hi + 16;
+          const uint64_t b_blk = b_desc0 + (uint64_t)(rb.stage * stage16 + (b4 & 1) * half16);
+#pragma unroll
+          for (uint32_t j = 0; j < 2; j++) {  // 16 values of K per instruction: 8 TMEM columns of A, two core-matrix columns of B
+            const uint64_t dbh = b_blk + (uint64_t)(j * j16), dbl = dbh + lo16;
+            if (b4 == 0 && j == 0)
+              tc_mma_ts(d_tmem, a_hi, dbh, idesc, st != 0);  // the item's first MMA overwrites the accumulator
+            else
+              tc_mma_ts_acc(d_tmem, a_hi + j * 8, dbh, idesc);
+            tc_mma_ts_acc(d_tmem, a_hi + j * 8, dbl, idesc);
+            tc_mma_ts_acc(d_tmem, a_lo + j * 8, dbh, idesc);
+          }
+          if (b4 & 1) rb.advance();
         }
+        if (!ok) break;
+        tc_commit(&done[grp % DONE_RING]);
+        if (st + GROUP >= p.kb_total) tc_commit(&acc_full[buf]);
       }
       n_done++;
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      grp = __shfl_sync(0xffffffffu, grp, 0);
     }
-    if (lane == 0) {
-      if (!ok) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
-      // nothing may still be writing TMEM when it is freed
-      tc_commit(drain);
-      (void)mbar_wait(drain, 0);
-    }
+    if (!ok && lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
+    __syncwarp();
+    // nothing may still be writing TMEM when it is freed
+    tc_commit(drain);
+    (void)mbar_wait(drain, 0);
     __syncwarp();
   } else if (warp >= W_DQ0) {
     // ------------------------------------------------------------------------ dequantisers
@@ -302,44 +297,47 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     const uint32_t q = warp & 3, mine = (warp - W_DQ0) >> 2;
     const uint32_t T = 2 * q + (lane >> 4), g = lane & 7, half = (lane >> 3) & 1;
     const __half2 zp = DT == MER_DTYPE_Q4_0 ? __floats2half2_rn(1032.0f, 1032.0f) : __floats2half2_rn(1152.0f, 1152.0f);
-    // This warp copies packed tile `tw` of every weight stage.  The copies run n_raw sub-groups ahead of the
-    // dequantisation, walking the same sequence of (item, sub-group) with a cursor of their own.
-    const uint32_t tw = warp - W_DQ0, sg_per_item = 2 * (p.kb_total / GROUP);
-    uint32_t pf_item = item_beg, pf_sg = 0, n_issued = 0;
-    const uint8_t *pf_base = nullptr;
+    // This warp also copies packed tile `tw` of every weight stage.  The copies run n_raw groups ahead of the
+    // dequantisation, walking the same sequence of (item, group) with a cursor of their own.
+    const uint32_t tw = warp - W_DQ0;
+    uint32_t pf_item = item_beg, pf_g = 0, n_issued = 0;
+    const uint8_t *pf_src = nullptr;  // chunk 0 of this warp's packed tile in the cursor's item
     auto pf_seek = [&]() {  // the next item whose expert is resident
-      for (; pf_item < n_items; pf_item += item_step)
-        if ((pf_base = expert_base(pf_item / m_pairs)) != nullptr) break;
+      for (; pf_item < n_items; pf_item += item_step) {
+        const uint8_t *base = expert_base(pf_item / m_tiles);
+        if (base) {
+          pf_src = base + region + (size_t)((pf_item % m_tiles) * 8 + tw) * tile_bytes;
+          break;
+        }
+      }
     };
-    auto issue_copy = [&]() {  // sub-group number n_issued of this CTA goes to stage n_issued % n_raw
+    auto issue_copy = [&]() {  // group number n_issued of this CTA goes to stage n_issued % n_raw
       if (pf_item >= n_items) return;
       if (lane == 0) {
-        const uint32_t stage = n_issued % p.n_raw, mp = pf_item % m_pairs, rt = pf_sg & 1, kg = pf_sg >> 1;
-        const uint8_t *src = pf_base + region + (size_t)(mp * 16 + rt * 8 + tw) * tile_bytes + (size_t)kg * TILE_RAW;
+        const uint32_t stage = n_issued % p.n_raw;
         mbar_expect_tx(&raw_full[stage], TILE_RAW);
-        bulk_g2s(s_raw + stage * RAW_BYTES + tw * TILE_RAW, src, TILE_RAW, &raw_full[stage]);
+        bulk_g2s(s_raw + stage * RAW_BYTES + tw * TILE_RAW, pf_src + (size_t)pf_g * TILE_RAW, TILE_RAW, &raw_full[stage]);
       }
       n_issued++;
-      if (++pf_sg == sg_per_item) pf_sg = 0, pf_item += item_step, pf_seek();
+      if (++pf_g == n_groups) pf_g = 0, pf_item += item_step, pf_seek();
     };
     pf_seek();
     for (uint32_t i = 0; i < p.n_raw; i++) issue_copy();
-    uint32_t n_seen = 0;  // sub-groups dequantised so far
+    uint32_t n_seen = 0;  // groups dequantised so far
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
-      const uint32_t pass = item / m_pairs;
+      const uint32_t pass = item / m_tiles;
       if (!expert_base(pass)) continue;
-      // one sub-group (= one weight stage of one row tile) at a time, the two row tiles alternating: this warp's two
-      // blocks of it, one wait on each side
-      for (uint32_t sg = 0; sg < sg_per_item && ok; sg++, gblk += GROUP, n_seen++) {
+      // one group (= one weight stage) at a time: this warp's two blocks of it, one wait on each side
+      for (uint32_t gi = 0; gi < n_groups && ok; gi++, gblk += GROUP, n_seen++) {
         if (n_seen >= 1) {
-          // refill the stage the previous sub-group emptied (every dequantiser warp has left it) with sub-group n_seen - 1 + n_raw
+          // refill the stage the previous group emptied (every dequantiser warp has left it) with group n_seen - 1 + n_raw
           const uint32_t prev = n_seen - 1;
           ok = mbar_wait(&raw_empty[prev % p.n_raw], (prev / p.n_raw) & 1);
           if (ok) issue_copy();
         }
         if (ok) ok = mbar_wait(&raw_full[raw.stage], raw.round & 1);
         if (ok && gblk >= A_STAGES) {
-          // the sub-group's A stages were last read by the MMAs of sub-group gblk / GROUP - 2
+          // the group's A stages were last read by the MMAs of group gblk / GROUP - 2
           const uint32_t sp = gblk / GROUP - A_STAGES / GROUP;
           ok = mbar_wait(&done[sp % DONE_RING], (sp / DONE_RING) & 1);
         }
@@ -400,14 +398,32 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     }
   } else {
     // ---------------------------------------------------------------------------- epilogue
-    const uint32_t q = warp & 3;  // a warp reads the TMEM lanes 32 * (warp % 4) ..
-    const uint32_t row = q * 32 + lane;  // row of the 128-row tile
-    const uint32_t buf = (warp - W_EPI0) >> 2;  // which of the item's two row tiles (= accumulators) this warp drains
-    uint32_t used = 0;
+    // Two groups of four warps, one per accumulator buffer: group e drains the items whose running number is e mod 2,
+    // so the epilogues of two consecutive items may overlap each other as well as the MMAs that follow.
+    const uint32_t q = warp & 3;         // a warp reads the TMEM lanes 32 * (warp % 4) ..
+    const uint32_t row = q * 32 + lane;  // row of the item's 128-row tile
+    const uint32_t buf = (warp - W_EPI0) >> 2;
+    uint32_t n_item = 0, used = 0;  // resident items seen by the CTA; uses of this group's buffer
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
-      const uint32_t pass = item / m_pairs, mt = 2 * (item % m_pairs) + buf;
-      const uint32_t pstart = d.pass_start[pass], pcount = d.pass_count[pass];
+      const uint32_t pass = item / m_tiles, mt = item % m_tiles;
       const bool resident = expert_base(pass) != nullptr;
+      if (resident) {
+        if ((n_item++ & 1) != buf) continue;  // the other group's item
+      } else if (buf != 0) {
+        continue;  // items of missing experts are zero-filled by group 0
+      }
+      const uint32_t pstart = d.pass_start[pass], pcount = d.pass_count[pass];
+      // this lane's share of the pass's pair indices and un-scale factors (columns lane, lane + 32, ...): fetched before the
+      // accumulator is waited for, so that their latency hides behind the item's MMAs
+      uint32_t my_pair[4];
+      float my_un[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const uint32_t c = k * 32 + lane;
+        const bool have = c < pcount;
+        my_pair[k] = have ? __ldg(d.perm + pstart + c) : 0u;
+        my_un[k] = have ? __ldg(p.unscale + (size_t)pass * p.bn + c) : 0.0f;
+      }
       if (resident) {
         ok = mbar_wait(&acc_full[buf], used & 1);
         used++;
@@ -418,45 +434,47 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
       } else if (warp == W_EPI0 && lane == 0) {
         atomicOr(d.status, MER_DEVSTAT_RESIDENCY_MISS);  // fail closed: zeros below
       }
-      for (uint32_t c0 = 0; c0 < pcount; c0 += 16) {
-        uint32_t v[16];
-        if (resident) {
-          tc_ld16(tmem_base + ((q * 32u) << 16) + buf * 128 + c0, v);
-        } else {
 #pragma unroll
-          for (int i = 0; i < 16; i++) v[i] = 0;
-        }
-        // lanes 0..15 fetch the pair index and un-scale factor of the chunk's columns
-        uint32_t my_pair = 0;
-        float my_un = 0.0f;
-        if (lane < 16 && c0 + lane < pcount) {
-          my_pair = d.perm[pstart + c0 + lane];
-          my_un = p.unscale[(size_t)pass * p.bn + c0 + lane];
-        }
+      for (uint32_t k = 0; k < 4; k++) {  // 32 columns at a time
+        const uint32_t cbase = k * 32;
+        if (cbase >= pcount) break;  // uniform
+        uint32_t my_bits = 0;  // phase 0: lane i keeps the row-tile maximum of |h| of column cbase + i
 #pragma unroll
-        for (int i = 0; i < 16; i++) {
-          const uint32_t pair = __shfl_sync(0xffffffffu, my_pair, i);
-          const float un = __shfl_sync(0xffffffffu, my_un, i);
-          const bool valid = c0 + i < pcount;  // uniform
-          const float val = __uint_as_float(v[i]) * un;
-          if (p.phase == 0) {
-            // rows come in packed tiles of 16: slots 0..7 gate rows, 8..15 the matching up rows
-            const float up = __shfl_down_sync(0xffffffffu, val, 8);
-            const bool is_gate = (lane & 8) == 0;
-            float gate = val;
-            if (d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit) && gate == gate) gate = fminf(fmaxf(gate, -d.swiglu_limit), d.swiglu_limit);
-            const float hval = __fdividef(gate, 1.0f + __expf(-gate)) * up;
-            const float ah = fabsf(hval);
-            uint32_t bits = (!valid || !is_gate) ? 0u : (ah != ah) ? 0x7fc00000u : __float_as_uint(ah);
-            bits = __reduce_max_sync(0xffffffffu, bits);
-            if (valid) {
-              if (is_gate) p.out[(size_t)pair * d.F + (mt * 8 + (row >> 4)) * 8 + (lane & 7)] = hval;
-              if (lane == 0) atomicMax(d.amax + pair, bits);
+        for (uint32_t hh = 0; hh < 2; hh++) {
+          const uint32_t c0 = cbase + hh * 16;
+          if (c0 >= pcount) break;  // uniform
+          uint32_t v[16];
+          if (resident) {
+            tc_ld16(tmem_base + ((q * 32u) << 16) + buf * 128 + c0, v);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; i++) v[i] = 0;
+          }
+#pragma unroll
+          for (int i = 0; i < 16; i++) {
+            const uint32_t pair = __shfl_sync(0xffffffffu, my_pair[k], hh * 16 + i);
+            const float un = __shfl_sync(0xffffffffu, my_un[k], hh * 16 + i);
+            const bool valid = c0 + i < pcount;  // uniform
+            const float val = __uint_as_float(v[i]) * un;
+            if (p.phase == 0) {
+              // rows come in packed tiles of 16: slots 0..7 gate rows, 8..15 the matching up rows
+              const float up = __shfl_down_sync(0xffffffffu, val, 8);
+              const bool is_gate = (lane & 8) == 0;
+              float gate = val;
+              if (d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit) && gate == gate) gate = fminf(fmaxf(gate, -d.swiglu_limit), d.swiglu_limit);
+              const float hval = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+              const float ah = fabsf(hval);
+              uint32_t bits = (!valid || !is_gate) ? 0u : (ah != ah) ? 0x7fc00000u : __float_as_uint(ah);
+              bits = __reduce_max_sync(0xffffffffu, bits);
+              if (lane == hh * 16 + i) my_bits = bits;
+              if (valid && is_gate) p.out[(size_t)pair * d.F + (mt * 8 + (row >> 4)) * 8 + (lane & 7)] = hval;
+            } else if (valid) {
+              p.out[(size_t)pair * d.D + mt * 128 + row] = val;
             }
-          } else if (valid) {
-            p.out[(size_t)pair * d.D + mt * 128 + row] = val;
           }
         }
+        // one vector atomic for the 32 columns' maxima instead of one single-lane atomic per column
+        if (p.phase == 0 && cbase + lane < pcount) atomicMax(d.amax + my_pair[k], my_bits);
       }
       if (resident) {
         tc_fence_before();

@@ -204,7 +204,7 @@ __device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
 __device__ __forceinline__ uint32_t pair_group_key(const RouterDev &r, const MoeDispatch &d, uint32_t p) {
   const uint32_t e = __ldcg(d.pair_expert + p);
   if (e == MER_NONE) return MER_NONE;
-  if ((p % d.slots) >= r.top_k) return r.num_experts;  // shared-expert slot
+  if ((p % d.slots) >= r.top_k || e == r.shared_expert_id) return r.num_experts;  // shared-expert slot (or a dispatched row of it)
   return e - r.id_base;
 }
 
@@ -275,7 +275,7 @@ __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uin
   auto key_global = [&](uint32_t p) -> uint32_t {
     uint32_t e = __ldcg(d.pair_expert + p);
     if (e == MER_NONE) return MER_NONE;
-    if ((p % d.slots) >= r.top_k) return r.num_experts;  // shared-expert slot
+    if ((p % d.slots) >= r.top_k || e == r.shared_expert_id) return r.num_experts;  // shared-expert slot (or a dispatched row of it)
     return e - r.id_base;
   };
   auto key_of = [&](uint32_t p) -> uint32_t { return staged ? s_key[p] : key_global(p); };

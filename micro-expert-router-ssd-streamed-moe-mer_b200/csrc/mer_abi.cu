@@ -50,8 +50,11 @@ struct RouterEntry {
 
 }  // namespace
 
+struct mer_a2a_state;  // NCCL all-to-all mode (mer_abi_ep_nccl.inc)
+
 struct mer_backend {
   mer_backend_cfg cfg{};
+  mer_a2a_state *a2a = nullptr;
   int sm_count = 0;
   size_t expert_bytes = 0;
   cudaStream_t compute = nullptr, copy = nullptr;
@@ -275,7 +278,8 @@ cudaError_t run_ffn(mer_backend *b, MoeDispatch &d, cudaStream_t s, int *launche
   d.y_parts = nullptr, d.y_nparts = 1;
   d.combined = 0;
   if (d.gemm_bn)
-    return launch_ffn_gemm(d, b->d_gemm_scratch, b->gemm_scratch_bytes, b->cfg.max_tokens, b->sm_count, s, launches, ev_mid);
+    return launch_ffn_gemm(d, b->d_gemm_scratch, b->gemm_scratch_bytes, std::max(b->cfg.max_tokens, b->max_pairs), b->sm_count, s, launches,
+                           ev_mid);
   if (use_stream_path(b, d)) return launch_ffn_stream(d, b->d_stream_scratch, b->sm_count, s, launches, ev_mid);
   return launch_ffn_generic(d, s, launches, ev_mid);
 }
@@ -353,7 +357,10 @@ int require_resident(mer_backend *b, uint32_t layer, uint32_t id) {
   return MER_OK;
 }
 
+void a2a_free(mer_backend *b);  // mer_abi_ep_nccl.inc
+
 void free_all(mer_backend *b) {
+  a2a_free(b);
   auto F = [](auto *&p) {
     if (p) cudaFree((void *)p);
     p = nullptr;
@@ -693,7 +700,8 @@ MER_EXPORT int mer_backend_create(const mer_backend_cfg *cfg, mer_backend **out)
       CB(cudaMemset(b->d_stream_scratch, 0, sb));
     }
     if (sb && T >= 12 && gemm_ffn_supported(cfg->dtype, (uint32_t)D, (uint32_t)F)) {
-      b->gemm_scratch_bytes = gemm_ffn_scratch_bytes((uint32_t)T, (uint32_t)P, (uint32_t)D, (uint32_t)F);
+      // token rows of a dispatch may be (token, slot) pairs of other ranks (NCCL all-to-all mode): size per-row scratch by pairs
+      b->gemm_scratch_bytes = gemm_ffn_scratch_bytes((uint32_t)std::max(T, P), (uint32_t)P, (uint32_t)D, (uint32_t)F);
       CB(cudaMalloc(&b->d_gemm_scratch, b->gemm_scratch_bytes));
     }
   }
@@ -1866,3 +1874,5 @@ MER_EXPORT int mer_set_kernel_path(mer_backend *b, int path) {
   drop_graphs(b);
   return MER_OK;
 }
+
+#include "mer_abi_ep_nccl.inc"

@@ -7,6 +7,8 @@ GPUs of one NVSwitch box.  Two exchange modes over the same partition:
 
 * ``peer``       -- the library's kernels exchange through peer memory (exchange buffers mapped with
                     CUDA IPC): publish, flag, pull.  Summation stays in slot order.
+* ``a2a``        -- the library calls NCCL itself: all-to-all dispatch of only the rows that hit a peer's experts
+                    (grouped ncclSend / ncclRecv), local experts, all-to-all return, combine in slot order.
 * ``collective`` -- torch.distributed (NCCL) moves the data: all-gather of tokens and routing,
                     reduce-scatter of the partial outputs.
 
@@ -83,6 +85,24 @@ class ExpertParallel:
 
     def wait(self, slot):
         self.b._check(self.b.lib.mer_moe_layer_forward_wait(self.b.h, slot))
+
+    # -- NCCL all-to-all mode ---------------------------------------------------------------
+    def nccl_init(self, group=None):
+        """Rank 0 creates the ncclUniqueId, torch.distributed hands it round, every rank joins the library's own
+        NCCL communicator (collective)."""
+        import torch.distributed as dist
+        ident = [None]
+        if self.rank == 0:
+            buf = C.create_string_buffer(128)
+            self.b._check(self.b.lib.mer_ep_nccl_unique_id(buf))
+            ident[0] = buf.raw
+        if self.world > 1:
+            dist.broadcast_object_list(ident, src=0, group=group)
+        self.b._check(self.b.lib.mer_ep_nccl_init(self.b.h, ident[0]))
+
+    def layer_forward_a2a(self, layer, d_x, n_tokens, d_out, stream=0):
+        self.b._check(self.b.lib.mer_ep_layer_forward_a2a_device(self.b.h, layer, C.c_void_p(d_x), n_tokens, C.c_void_p(d_out),
+                                                                 C.c_void_p(stream)))
 
     # -- collective mode --------------------------------------------------------------------
     def _buffers(self, n_tokens, slots, device):

@@ -21,7 +21,7 @@ import oracle  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", choices=["collective", "peer", "cpu"], default="collective")
+    ap.add_argument("--mode", choices=["collective", "peer", "a2a", "cpu"], default="collective")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     cpu = args.mode == "cpu"
@@ -87,6 +87,11 @@ def main():
             for i in range(3):
                 ep.wait(i)
                 assert (ops[i].numpy().view(np.uint32) == first.view(np.uint32)).all(), f"rank {rank}: pipelined call {i} differs"
+        elif args.mode == "a2a":
+            ep.nccl_init()  # the library's own NCCL communicator: all-to-all dispatch and combine inside the library
+            for _ in range(3):
+                ep.layer_forward_a2a(layer, x.data_ptr(), B, out.data_ptr(), stream)
+                ep.check(layer, stream)
         else:
             for _ in range(2):
                 ep.layer_forward_collective(layer, x, out, k)

@@ -117,6 +117,39 @@ def test_peer_mode_world_of_one_equals_the_single_gpu_entry_point():
     assert rel_rms_err(got, single) <= 1e-5
 
 
+@pytest.mark.parametrize("shared", [False, True])
+def test_nccl_all_to_all_mode_world_of_one_equals_the_single_gpu_entry_point(shared):
+    # the library's own NCCL communicator with one rank: pack, count exchange, self send / recv, local experts over the
+    # dispatched rows (one row per pair), return, combine in slot order
+    dtype, E, D, F, k, B, layer = oracle.Q8_0, 16, 256, 512, 4, 16, 1
+    blobs = [synth.make_expert_blob(dtype, D, F, 63, 0, e) for e in range(E + 1)]
+    W = synth.make_router(E, D, 63)
+    x = synth.make_activations(B, D, 63)
+    b, ep = make_rank(dtype, E, D, F, k, 1, 0, blobs[:E], W, B, layer, shared_blob=blobs[E] if shared else None)
+    try:
+        ep.nccl_init()
+        dev = torch.device("cuda:0")
+        xd = torch.from_numpy(x).to(dev)
+        out = torch.empty(B, D, dtype=torch.float32, device=dev)
+        for _ in range(3):
+            ep.layer_forward_a2a(layer, xd.data_ptr(), B, out.data_ptr())
+            ep.check(layer)
+        got = out.cpu().numpy()
+        single, _, _ = b.moe_layer_forward(layer, x)
+        # a larger group: GEMM-sized dispatch of the received rows
+        b.set_kernel_path(3)
+        ep.layer_forward_a2a(layer, xd.data_ptr(), B, out.data_ptr())
+        ep.check(layer)
+        gemm = out.cpu().numpy()
+    finally:
+        b.close()
+    ref, _, _, _ = oracle.moe_layer_forward(dtype, oracle.LinearGate(W, E, D, k), blobs[:E], x, F, shared_blob=blobs[E] if shared else None,
+                                            n_threads=4)
+    assert rel_rms_err(got, ref) <= FFN_TOL
+    assert rel_rms_err(got, single) <= 1e-5
+    assert rel_rms_err(gemm, ref) <= FFN_TOL
+
+
 def test_a_missing_local_expert_is_a_typed_residency_miss():
     dtype, E, D, F, k, B, layer = oracle.Q8_0, 8, 256, 256, 8, 3, 0  # top-8 of 8: every expert is hit
     blobs = [synth.make_expert_blob(dtype, D, F, 63, 0, e) for e in range(E)]
@@ -189,7 +222,7 @@ def test_ep_argument_validation():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("mode", ["collective", "peer"])
+@pytest.mark.parametrize("mode", ["collective", "peer", "a2a"])
 def test_two_processes_two_gpus(mode):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
