@@ -62,6 +62,8 @@ PARALLELISM_NOTE = {
                "library's kernels through peer memory over NVLink",
     "ep-collective": "expert-parallel over {n} GPUs (experts split contiguously, tokens data-parallel), NCCL all-gather of "
                      "tokens+routing and reduce-scatter of partial outputs",
+    "ep-nccl": "expert-parallel over {n} GPUs (experts split contiguously, tokens data-parallel), NCCL all-to-all dispatch and "
+               "combine issued by the library (grouped ncclSend / ncclRecv of the rows that hit a peer's experts)",
 }
 
 
@@ -80,7 +82,7 @@ def parse_args():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--zipf-strength", type=float, default=1.0)
-    ap.add_argument("--parallelism", default="auto", choices=["auto", "replicas", "ep-peer", "ep-collective"],
+    ap.add_argument("--parallelism", default="auto", choices=["auto", "replicas", "ep-peer", "ep-collective", "ep-nccl"],
                     help="N > 1: expert-parallel with the exchange through peer memory (default) or through NCCL "
                          "collectives, or independent token-parallel replicas")
     return ap.parse_args()
@@ -465,10 +467,14 @@ def main():
         if mode == "ep-peer":
             ep.attach()
             dist.barrier()
+        elif mode == "ep-nccl":
+            ep.nccl_init()
 
     def layer_pass(l, x, o):
         if mode == "ep-peer":
             ep.layer_forward_peer(l, x.data_ptr(), B, o.data_ptr(), stream)
+        elif mode == "ep-nccl":
+            ep.layer_forward_a2a(l, x.data_ptr(), B, o.data_ptr(), stream)
         elif mode == "ep-collective":
             ep.layer_forward_collective(l, x, o, slots)
         else:
@@ -553,7 +559,7 @@ def main():
         pinned_in = [torch.from_numpy(x).pin_memory() for x in xs_host]
         depth = 3
         outs = [torch.empty(B, cfg.d_model).pin_memory() for _ in range(depth)]
-        if mode == "ep-collective":
+        if mode in ("ep-collective", "ep-nccl"):
             x_dev = torch.empty(B, cfg.d_model, device=dev)
 
             def e2e_steps(k):

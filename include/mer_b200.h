@@ -310,6 +310,8 @@ typedef struct mer_uth_info {
 /* TensorHeader::strip / MixedExpertHeader::strip (tensor_header.rs:528-545, 376-391).  Best effort like the reference:
  * a buffer without a valid header is reported as MER_UTH_KIND_NONE, never as an error. */
 int mer_uth_probe(const void *bytes, size_t len, size_t block_align, mer_uth_info *out);
+/* The same for a blob of `len` bytes of which only the first `have` (at least 128) are in memory: a file's header region. */
+int mer_uth_probe_prefix(const void *bytes, size_t have, uint64_t len, size_t block_align, mer_uth_info *out);
 /* TensorHeader::for_swiglu_expert + write_padded (tensor_header.rs:419-470, 489-499): header + padding; *written = bytes
  * needed (MER_ERR_PHYSICAL_CAPACITY when cap is smaller). */
 int mer_uth1_write(int32_t dtype, uint64_t d_model, uint64_t d_ff, size_t block_align, void *dst, size_t cap, size_t *written);

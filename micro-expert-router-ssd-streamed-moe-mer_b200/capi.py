@@ -128,6 +128,7 @@ ABI_SYMBOLS = {
     "mer_expert_hot_promote": (C.c_int, [_vp, _vp, _u32, _vp, _sz, _u32, C.POINTER(C.c_int)]),
     "mer_expert_touch": (C.c_int, [_vp, _vp, _vp, _sz]),
     "mer_uth_probe": (C.c_int, [_vp, _sz, _sz, C.POINTER(MerUthInfo)]),
+    "mer_uth_probe_prefix": (C.c_int, [_vp, _sz, _u64, _sz, C.POINTER(MerUthInfo)]),
     "mer_uth1_write": (C.c_int, [C.c_int32, _u64, _u64, _sz, _vp, _sz, C.POINTER(_sz)]),
     "mer_uth2_write": (C.c_int, [_u64, _u64, C.POINTER(MerUthProjection), _sz, _vp, _sz, C.POINTER(_sz)]),
     "mer_dataset_metadata_parse": (C.c_int, [C.c_char_p, _sz, C.POINTER(MerDatasetInfo)]),

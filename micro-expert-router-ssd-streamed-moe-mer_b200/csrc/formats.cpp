@@ -44,12 +44,17 @@ size_t padded_prefix(size_t header, uint32_t flags, size_t block_align) {
 // TensorHeader::strip / MixedExpertHeader::strip (tensor_header.rs:528-545, 376-391): a blob without a valid
 // header is a legacy blob and is returned unchanged (kind 0, payload = the whole buffer).
 MER_EXPORT int mer_uth_probe(const void *bytes_, size_t len, size_t block_align, mer_uth_info *out) {
-  if (!bytes_ || !out) return MER_ERR_INVALID_ARGUMENT;
+  return mer_uth_probe_prefix(bytes_, len, len, block_align, out);
+}
+
+// The same for a blob of `len` bytes of which only the first `have` are in memory (the header region of a file).
+MER_EXPORT int mer_uth_probe_prefix(const void *bytes_, size_t have, uint64_t len, size_t block_align, mer_uth_info *out) {
+  if (!bytes_ || !out || have > len) return MER_ERR_INVALID_ARGUMENT;
   const uint8_t *b = static_cast<const uint8_t *>(bytes_);
   memset(out, 0, sizeof *out);
   out->dtype = -1;
   out->payload_bytes = len;
-  if (len >= UTH1_BYTES && memcmp(b, "UTH1", 4) == 0) {
+  if (have >= UTH1_BYTES && memcmp(b, "UTH1", 4) == 0) {
     const uint16_t version = le16(b + 4);
     const uint8_t dt = b[6], rank = b[7];
     if (version == 0 || version > 1 || dt > UTH_DTYPE_LAST || rank == 0 || rank > 4) return MER_OK;  // not a header we know: legacy
@@ -70,7 +75,7 @@ MER_EXPORT int mer_uth_probe(const void *bytes_, size_t len, size_t block_align,
     out->payload_bytes = len - prefix;
     return MER_OK;
   }
-  if (len >= UTH2_BYTES && memcmp(b, "UTH2", 4) == 0) {
+  if (have >= UTH2_BYTES && memcmp(b, "UTH2", 4) == 0) {
     if (le16(b + 4) != 2 || le16(b + 6) != 3) return MER_OK;
     mer_uth_info h{};
     h.kind = MER_UTH_KIND_UTH2;

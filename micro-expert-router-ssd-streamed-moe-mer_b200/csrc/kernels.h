@@ -92,9 +92,10 @@ struct EpDev {
 // kernels_ep.cu
 cudaError_t launch_ep_filter(const EpDev &ep, const uint32_t *ids_all, const float *w_all, uint32_t n_pairs, uint32_t slots,
                              uint32_t *pair_expert, float *pair_weight, cudaStream_t s, int *launches);
-cudaError_t launch_ep_gather(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, float *x_all, uint32_t *pair_expert,
+// `epoch_counter`: device word, advanced by one by the signal kernel each of these launches starts with.
+cudaError_t launch_ep_gather(const EpDev &ep, uint32_t *epoch_counter, uint32_t D, uint32_t slots, float *x_all, uint32_t *pair_expert,
                              float *pair_weight, uint32_t *status, cudaStream_t s, int *launches);
-cudaError_t launch_ep_combine(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, const uint32_t *ids, const float *w,
+cudaError_t launch_ep_combine(const EpDev &ep, uint32_t *epoch_counter, uint32_t D, uint32_t slots, const uint32_t *ids, const float *w,
                               const float *residual, float *out, uint32_t *status, cudaStream_t s, int *launches);
 
 // NCCL all-to-all mode: pack every pair into the send segment of its expert's owner (segment d = rows [d * seg_rows, ...),

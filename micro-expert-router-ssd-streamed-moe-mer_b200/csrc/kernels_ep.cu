@@ -4,9 +4,9 @@
 //       outputs) and this file only filters the gathered routing down to the local experts;
 //   (2) the ranks exchange through peer memory: every rank publishes its tokens, routing and
 //       per-pair expert outputs in an exchange buffer the other ranks have mapped; a rank pulls
-//       the rows it needs with plain peer loads (no TMA, no multicast) after a flag barrier (the
-//       first CTA of the gather / combine kernel raises this rank's flag on every peer, all CTAs
-//       wait for the flags of the ranks they read).
+//       the rows it needs with plain peer loads (no TMA, no multicast) after a flag barrier (a
+//       one-CTA signal kernel raises this rank's flag on every peer, then all CTAs of the gather /
+//       combine kernel wait for the flags of the ranks they read).
 //   (3) NCCL all-to-all: every (token, slot) pair is packed into the send segment of the rank that owns its expert
 //       (k_a2a_pack), the library exchanges the segments with grouped ncclSend / ncclRecv, the owners run their
 //       experts over the rows they received and send the outputs back the same way; k_a2a_combine sums each
@@ -62,24 +62,29 @@ __global__ void k_ep_filter(EpDev ep, const uint32_t *__restrict__ ids_all, cons
   pair_weight[p] = local ? w_all[p] : 0.0f;
 }
 
-// (2a) Tells every peer that this rank's exchange buffer holds the data of `epoch`.  Called by the first CTA of the
-// kernel that follows the kernels which wrote the data (stream order: the data is in this GPU's memory by then).
-__device__ __forceinline__ void ep_signal(const EpDev &ep, uint32_t epoch) {
+// (2a) Tells every peer that this rank's exchange buffer holds the data of the next epoch.  A kernel of its own, launched
+// after the kernels that wrote the data (stream order: the data is in this GPU's memory by then) and before the kernel
+// whose CTAs wait for the peers' flags, so that no waiting CTA can ever stand in the way of the signal.  The epoch
+// counter lives in device memory (one step per signal), which lets the whole layer be replayed as a CUDA graph.
+__global__ void k_ep_signal(EpDev ep, uint32_t *epoch_counter) {
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) s_epoch = *epoch_counter = *epoch_counter + 1;
+  __syncthreads();
   const uint32_t j = threadIdx.x;
   if (j >= ep.world) return;
   __threadfence_system();
   uint32_t *flag = reinterpret_cast<uint32_t *>(ep.peer[j] + ep.off_flags) + ep.rank;
-  asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+  asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(flag), "r"(s_epoch) : "memory");
 }
 
 // (2b) Pulls the tokens of every rank that hit a local expert: routing (filtered) for all tokens,
 // x rows only for tokens with at least one local pair.  One CTA per (source rank, token).
-__global__ void __launch_bounds__(256) k_ep_gather(EpDev ep, uint32_t epoch, uint32_t D, uint32_t slots, float *__restrict__ x_all,
-                                                   uint32_t *__restrict__ pair_expert, float *__restrict__ pair_weight,
-                                                   uint32_t *status) {
+__global__ void __launch_bounds__(256) k_ep_gather(EpDev ep, const uint32_t *__restrict__ epoch_counter, uint32_t D, uint32_t slots,
+                                                   float *__restrict__ x_all, uint32_t *__restrict__ pair_expert,
+                                                   float *__restrict__ pair_weight, uint32_t *status) {
   const uint32_t src = blockIdx.y, t = blockIdx.x;
   __shared__ int s_ok, s_any;
-  if (blockIdx.x == 0 && blockIdx.y == 0) ep_signal(ep, epoch);  // this rank's tokens and routing are published
+  const uint32_t epoch = __ldcg(epoch_counter);  // set by the signal kernel in front of this one
   if (threadIdx.x == 0) {
     const uint32_t *flags = reinterpret_cast<const uint32_t *>(ep.peer[ep.rank] + ep.off_flags);
     s_ok = wait_flag(flags + src, epoch, ep.wait_ns);
@@ -111,14 +116,14 @@ __global__ void __launch_bounds__(256) k_ep_gather(EpDev ep, uint32_t epoch, uin
 // (2c) out[t] = sum over slots, in slot order, of weight * y, where y of a pair is read from the
 // exchange buffer of the rank that owns the pair's expert (same order and rounding as k_combine).
 // One CTA per token, a thread four consecutive values.
-__global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, uint32_t epoch, uint32_t D, uint32_t slots,
+__global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, const uint32_t *__restrict__ epoch_counter, uint32_t D, uint32_t slots,
                                                     const uint32_t *__restrict__ ids, const float *__restrict__ w,
                                                     const float *__restrict__ residual, float *__restrict__ out, uint32_t *status) {
   const uint32_t t = blockIdx.x;
   __shared__ int s_ok;
   __shared__ const float *s_row[64];
   __shared__ float s_w[64];
-  if (blockIdx.x == 0) ep_signal(ep, epoch);  // this rank's expert outputs are published
+  const uint32_t epoch = __ldcg(epoch_counter);  // set by the signal kernel in front of this one
   if (threadIdx.x < 32) {
     // lanes share the ranks to wait for
     const uint32_t *flags = reinterpret_cast<const uint32_t *>(ep.peer[ep.rank] + ep.off_flags);
@@ -245,17 +250,19 @@ cudaError_t launch_ep_filter(const EpDev &ep, const uint32_t *ids_all, const flo
   return cudaGetLastError();
 }
 
-cudaError_t launch_ep_gather(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, float *x_all, uint32_t *pair_expert,
+cudaError_t launch_ep_gather(const EpDev &ep, uint32_t *epoch_counter, uint32_t D, uint32_t slots, float *x_all, uint32_t *pair_expert,
                              float *pair_weight, uint32_t *status, cudaStream_t s, int *launches) {
+  k_ep_signal<<<1, 32, 0, s>>>(ep, epoch_counter);  // this rank's tokens and routing are published
   dim3 grid(ep.tokens_per_rank, ep.world);
-  k_ep_gather<<<grid, 256, 0, s>>>(ep, epoch, D, slots, x_all, pair_expert, pair_weight, status);
-  if (launches) (*launches)++;
+  k_ep_gather<<<grid, 256, 0, s>>>(ep, epoch_counter, D, slots, x_all, pair_expert, pair_weight, status);
+  if (launches) (*launches) += 2;
   return cudaGetLastError();
 }
 
-cudaError_t launch_ep_combine(const EpDev &ep, uint32_t epoch, uint32_t D, uint32_t slots, const uint32_t *ids, const float *w,
+cudaError_t launch_ep_combine(const EpDev &ep, uint32_t *epoch_counter, uint32_t D, uint32_t slots, const uint32_t *ids, const float *w,
                               const float *residual, float *out, uint32_t *status, cudaStream_t s, int *launches) {
-  k_ep_combine<<<ep.tokens_per_rank, 256, 0, s>>>(ep, epoch, D, slots, ids, w, residual, out, status);
-  if (launches) (*launches)++;
+  k_ep_signal<<<1, 32, 0, s>>>(ep, epoch_counter);  // this rank's expert outputs are published
+  k_ep_combine<<<ep.tokens_per_rank, 256, 0, s>>>(ep, epoch_counter, D, slots, ids, w, residual, out, status);
+  if (launches) (*launches) += 2;
   return cudaGetLastError();
 }

@@ -36,7 +36,7 @@ constexpr int G_WARPS = 18, G_THREADS = G_WARPS * 32;
 constexpr int W_PRODUCER = 0, W_MMA = 1, W_EPI0 = 2, W_DQ0 = 10;
 constexpr int EPI_WARPS = 4, DQ_WARPS = 8;  // EPI_WARPS per accumulator
 constexpr uint32_t RAW_BLOCKS = 4;       // blocks of K per weight stage (per packed tile: one bulk copy)
-constexpr uint32_t G_HEADER = 1024;
+constexpr uint32_t G_HEADER = 4096;      // mbarriers, TMEM base, and from byte 1024 the epilogue groups' per-pass tables
 constexpr uint32_t TMEM_COLS = 512;      // [0, 256): two accumulator buffers of up to 128 columns; [256, 512): A stages
 constexpr uint32_t TMEM_A0 = 256, A_STAGES = 8, A_STAGE_COLS = 32;  // a stage = one block: 16 columns hi + 16 columns lo
 constexpr uint32_t MAX_RING = 8;
@@ -111,12 +111,16 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32])
       : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+// 32 columns of this thread's TMEM lane (lane = 32 * (warp % 4) + lane id).
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
       "tcgen05.wait::ld.sync.aligned;\n"
       : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-        "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+        "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr)
       : "memory");
 }
@@ -402,9 +406,14 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     // so the epilogues of two consecutive items may overlap each other as well as the MMAs that follow.
     const uint32_t q = warp & 3;         // a warp reads the TMEM lanes 32 * (warp % 4) ..
     const uint32_t row = q * 32 + lane;  // row of the item's 128-row tile
-    const uint32_t buf = (warp - W_EPI0) >> 2;
+    const uint32_t buf = (warp - W_EPI0) >> 2, gw = (warp - W_EPI0) & 3;  // group, warp within the group
+    uint32_t *s_pair = reinterpret_cast<uint32_t *>(smem + 1024 + buf * 1024);
+    float *s_un = reinterpret_cast<float *>(smem + 1024 + buf * 1024 + 512);
     uint32_t n_item = 0, used = 0;  // resident items seen by the CTA; uses of this group's buffer
-    for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
+    // A group whose bounded wait expired goes "dead": it stops touching TMEM and waiting but keeps walking the items, so
+    // that the group's named barriers always see all four warps.
+    bool dead = false;
+    for (uint32_t item = item_beg; item < n_items; item += item_step) {
       const uint32_t pass = item / m_tiles, mt = item % m_tiles;
       const bool resident = expert_base(pass) != nullptr;
       if (resident) {
@@ -413,76 +422,72 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
         continue;  // items of missing experts are zero-filled by group 0
       }
       const uint32_t pstart = d.pass_start[pass], pcount = d.pass_count[pass];
-      // this lane's share of the pass's pair indices and un-scale factors (columns lane, lane + 32, ...): fetched before the
-      // accumulator is waited for, so that their latency hides behind the item's MMAs
-      uint32_t my_pair[4];
-      float my_un[4];
-#pragma unroll
-      for (int k = 0; k < 4; k++) {
-        const uint32_t c = k * 32 + lane;
+      // The pass's pair indices and un-scale factors go to shared memory (one column per thread of the group), fetched
+      // before the accumulator is waited for so that their latency hides behind the item's MMAs; the column loop then
+      // reads them as broadcasts.
+      {
+        const uint32_t c = gw * 32 + lane;
         const bool have = c < pcount;
-        my_pair[k] = have ? __ldg(d.perm + pstart + c) : 0u;
-        my_un[k] = have ? __ldg(p.unscale + (size_t)pass * p.bn + c) : 0.0f;
+        const uint32_t pr = have ? __ldg(d.perm + pstart + c) : 0u;
+        const float un = have ? __ldg(p.unscale + (size_t)pass * p.bn + c) : 0.0f;
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + buf) : "memory");  // the group has finished reading the previous item's tables
+        s_pair[c] = pr, s_un[c] = un;
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + buf) : "memory");
       }
-      if (resident) {
+      if (resident && !dead) {
         ok = mbar_wait(&acc_full[buf], used & 1);
         used++;
         if (*s_abort) ok = false;
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
+        if (!__all_sync(0xffffffffu, ok)) dead = true;
         tc_fence_after();
-      } else if (warp == W_EPI0 && lane == 0) {
+      } else if (!resident && warp == W_EPI0 && lane == 0) {
         atomicOr(d.status, MER_DEVSTAT_RESIDENCY_MISS);  // fail closed: zeros below
       }
+      const uint32_t acc_addr = tmem_base + ((q * 32u) << 16) + buf * 128;
+      const bool is_gate = (lane & 8) == 0;
+      const bool clamp = d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit);
+      for (uint32_t cbase = 0; cbase < pcount; cbase += 32) {  // 32 columns (tokens) at a time
+        uint32_t v[32];
+        if (resident && !dead) {
+          tc_ld32(acc_addr + cbase, v);
+        } else {
 #pragma unroll
-      for (uint32_t k = 0; k < 4; k++) {  // 32 columns at a time
-        const uint32_t cbase = k * 32;
-        if (cbase >= pcount) break;  // uniform
-        uint32_t my_bits = 0;  // phase 0: lane i keeps the row-tile maximum of |h| of column cbase + i
-#pragma unroll
-        for (uint32_t hh = 0; hh < 2; hh++) {
-          const uint32_t c0 = cbase + hh * 16;
-          if (c0 >= pcount) break;  // uniform
-          uint32_t v[16];
-          if (resident) {
-            tc_ld16(tmem_base + ((q * 32u) << 16) + buf * 128 + c0, v);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; i++) v[i] = 0;
-          }
-#pragma unroll
-          for (int i = 0; i < 16; i++) {
-            const uint32_t pair = __shfl_sync(0xffffffffu, my_pair[k], hh * 16 + i);
-            const float un = __shfl_sync(0xffffffffu, my_un[k], hh * 16 + i);
-            const bool valid = c0 + i < pcount;  // uniform
-            const float val = __uint_as_float(v[i]) * un;
-            if (p.phase == 0) {
-              // rows come in packed tiles of 16: slots 0..7 gate rows, 8..15 the matching up rows
-              const float up = __shfl_down_sync(0xffffffffu, val, 8);
-              const bool is_gate = (lane & 8) == 0;
-              float gate = val;
-              if (d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit) && gate == gate) gate = fminf(fmaxf(gate, -d.swiglu_limit), d.swiglu_limit);
-              const float hval = __fdividef(gate, 1.0f + __expf(-gate)) * up;
-              const float ah = fabsf(hval);
-              uint32_t bits = (!valid || !is_gate) ? 0u : (ah != ah) ? 0x7fc00000u : __float_as_uint(ah);
-              bits = __reduce_max_sync(0xffffffffu, bits);
-              if (lane == hh * 16 + i) my_bits = bits;
-              if (valid && is_gate) p.out[(size_t)pair * d.F + (mt * 8 + (row >> 4)) * 8 + (lane & 7)] = hval;
-            } else if (valid) {
-              p.out[(size_t)pair * d.D + mt * 128 + row] = val;
-            }
-          }
+          for (int i = 0; i < 32; i++) v[i] = 0;
         }
-        // one vector atomic for the 32 columns' maxima instead of one single-lane atomic per column
-        if (p.phase == 0 && cbase + lane < pcount) atomicMax(d.amax + my_pair[k], my_bits);
+        // the steps run column-batched (all multiplies, then all shuffles, ...): warp-synchronous operations are kept in
+        // program order, so a column-by-column loop would serialise on the latency of every single one
+        float val[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) val[i] = __uint_as_float(v[i]) * s_un[cbase + i];
+        if (p.phase == 0) {
+          // rows come in packed tiles of 16: slots 0..7 gate rows, 8..15 the matching up rows
+          float up[32];
+#pragma unroll
+          for (int i = 0; i < 32; i++) up[i] = __shfl_down_sync(0xffffffffu, val[i], 8);
+#pragma unroll
+          for (int i = 0; i < 32; i++) {
+            float gate = val[i];
+            if (clamp && gate == gate) gate = fminf(fmaxf(gate, -d.swiglu_limit), d.swiglu_limit);
+            val[i] = __fdividef(gate, 1.0f + __expf(-gate)) * up[i];
+          }
+          float *dst = p.out + (mt * 8 + (row >> 4)) * 8 + (lane & 7);
+#pragma unroll
+          for (int i = 0; i < 32; i++)
+            if (is_gate && cbase + i < pcount) dst[(size_t)s_pair[cbase + i] * d.F] = val[i];
+        } else {
+          float *dst = p.out + mt * 128 + row;
+#pragma unroll
+          for (int i = 0; i < 32; i++)
+            if (cbase + i < pcount) dst[(size_t)s_pair[cbase + i] * d.D] = val[i];
+        }
       }
-      if (resident) {
+      if (resident && !dead) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[buf]);
       }
     }
-    if (!ok && lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
+    if (dead && lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
   }
 
   tc_fence_before();
@@ -649,9 +654,14 @@ cudaError_t launch_ffn_gemm(MoeDispatch &d, void *gemm_scratch_ptr, size_t gemm_
     p.bn = bn, p.b_lbo = pl.b_lbo, p.n_raw = pl.n_raw, p.n_b = pl.n_b;
     p.out = phase == 0 ? d.h : d.y;
     kern<<<sm_count, G_THREADS, pl.smem, s>>>(p);
-    if (phase == 0 && ev_mid) cudaEventRecord(ev_mid, s);
+    if (phase == 0) {
+      // row maxima of h = SiLU(gate) * up, the scale source of the down phase's operand image (the GEMM epilogue does
+      // not collect them: a warp reduction per column sat on its critical path)
+      k_row_amax<<<(P + 7) / 8, 256, 0, s>>>(d.h, P, d.F, d.amax);
+      if (ev_mid) cudaEventRecord(ev_mid, s);
+    }
   }
   d.y_parts = nullptr, d.y_nparts = 1;
-  if (launches) (*launches) += 5;
+  if (launches) (*launches) += 6;
   return cudaGetLastError();
 }

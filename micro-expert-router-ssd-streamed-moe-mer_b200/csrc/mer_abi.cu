@@ -110,7 +110,6 @@ struct mer_backend {
   mer_ep_cfg ep_cfg{};
   uint8_t *ep_buf = nullptr;
   size_t ep_bytes = 0, ep_off_w = 0;
-  uint32_t ep_epoch = 0;
   void *ep_opened[MER_EP_MAX_WORLD] = {};  // mappings opened from IPC handles (closed at destroy)
   // captured launch sequences of mer_moe_layer_forward_device, replayed with one cudaGraphLaunch
   struct GraphEntry {
@@ -762,7 +761,7 @@ MER_EXPORT int mer_expert_admit_file(mer_backend *b, uint32_t expert_id, uint64_
   if (fseeko(f, 0, SEEK_SET) != 0 || fread(head.data(), 1, head.size(), f) != head.size())
     return fail(b, MER_ERR_UPLOAD, layer, expert, "cannot read the header region of %s", path);
   mer_uth_info h{};
-  mer_uth_probe(head.data(), head.size(), block_align, &h);
+  mer_uth_probe_prefix(head.data(), head.size(), file_bytes, block_align, &h);
   uint64_t payload_off = 0;
   uint64_t range_off[3], range_len[3];
   const uint64_t proj = b->expert_bytes / 3;
@@ -1571,7 +1570,6 @@ MER_EXPORT int mer_ep_init(mer_backend *b, const mer_ep_cfg *cfg) {
   b->ep_cfg = *cfg;
   b->ep_on = true;
   b->ep_attached = cfg->world == 1;
-  b->ep_epoch = 0;
   return MER_OK;
 }
 
@@ -1694,7 +1692,9 @@ MER_EXPORT int mer_ep_layer_forward_device(mer_backend *b, uint32_t layer, const
 }
 
 namespace {
-int ep_layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out, cudaStream_t s) {
+// Enqueues the launch sequence of one expert-parallel layer (peer-memory exchange) on stream s.
+int ep_enqueue(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out, cudaStream_t s, int *launches_out,
+               bool capturing) {
   const uint32_t expert = MER_NONE;
   if (!b->ep_on || !b->ep_attached)
     return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "the expert-parallel group is not initialised and attached");
@@ -1714,10 +1714,11 @@ int ep_layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *
   uint32_t *ids_pub = reinterpret_cast<uint32_t *>(b->ep_buf + ep.off_ids);
   float *w_own = reinterpret_cast<float *>(b->ep_buf + b->ep_off_w);
   float *y_pub = reinterpret_cast<float *>(b->ep_buf + ep.off_y);
-  const uint32_t e1 = ++b->ep_epoch, e2 = ++b->ep_epoch;
+  // the epoch the flags carry lives in device memory and advances by one per signal: the same launch sequence can be replayed
+  uint32_t *epoch_counter = reinterpret_cast<uint32_t *>(b->ep_buf + 128);
 
   CU(MER_ERR_SUBMISSION, "cudaMemsetAsync(status)", cudaMemsetAsync(b->d_status, 0, 4, s));
-  CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, s));
+  if (!capturing) CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, s));
   // publish this rank's tokens (RMSNorm'ed when the layer has a norm installed) and their routing
   const RouterEntry &re = it->second;
   RouterDev rl = r;
@@ -1743,18 +1744,71 @@ int ep_layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *
   d.y = y_pub;
   d.out = d_out;
   CU(MER_ERR_SUBMISSION, "gather kernel",
-     launch_ep_gather(ep, e1, (uint32_t)D, slots, b->d_x, d.pair_expert, d.pair_weight, b->d_status, s, &launches));
+     launch_ep_gather(ep, epoch_counter, (uint32_t)D, slots, b->d_x, d.pair_expert, d.pair_weight, b->d_status, s, &launches));
   d.fuse_reduce = 1;  // the peers read final per-pair outputs, and only those of the local experts exist
   int rc = ep_run_local_experts(b, layer, r, d, s, &launches);
   if (rc) return rc;
   CU(MER_ERR_SUBMISSION, "partial-sum kernel", launch_reduce_parts(d, s, &launches));
   // weighted sum in slot order, every pair's output read from the rank that owns its expert
   CU(MER_ERR_SUBMISSION, "combine kernel",
-     launch_ep_combine(ep, e2, (uint32_t)D, slots, ids_pub, w_own, (re.layer_flags & MER_LAYER_RESIDUAL) ? d_x : nullptr, d_out, b->d_status, s,
+     launch_ep_combine(ep, epoch_counter, (uint32_t)D, slots, ids_pub, w_own, (re.layer_flags & MER_LAYER_RESIDUAL) ? d_x : nullptr, d_out, b->d_status, s,
                        &launches));
+  *launches_out = launches;
+  return MER_OK;
+}
+
+int ep_layer_forward_device_locked(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens, float *d_out, cudaStream_t s) {
+  const uint32_t expert = MER_NONE;
+  int launches = 0;
+  const void *ep_tag = reinterpret_cast<const void *>(uintptr_t(2));  // marks expert-parallel graphs in the cache
+  bool replayed = false;
+  if (b->graphs_ok && !b->timing_on && !(b->cfg.flags & MER_FLAG_NO_GRAPHS) && b->ep_on && b->ep_attached) {
+    CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+    CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, s));  // outside any capture
+    mer_backend::GraphEntry *hit = nullptr;
+    for (auto &g : b->graphs)
+      if (g.layer == layer && g.n_tokens == n_tokens && g.x == d_x && g.out == d_out && g.ids == ep_tag && g.stream == s) hit = &g;
+    if (!hit) {
+      if (b->graphs.size() >= 256) drop_graphs(b);
+      cudaGraph_t graph = nullptr;
+      cudaGraphExec_t exec = nullptr;
+      int rc = MER_OK;
+      bool ok = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+      if (ok) {
+        rc = ep_enqueue(b, layer, d_x, n_tokens, d_out, s, &launches, true);
+        cudaError_t ce = cudaStreamEndCapture(s, &graph);
+        ok = ce == cudaSuccess && graph != nullptr;
+      }
+      if (rc != MER_OK) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        return rc;
+      }
+      if (ok) ok = cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
+      if (graph) cudaGraphDestroy(graph);
+      if (ok) {
+        b->graphs.push_back({layer, n_tokens, d_x, d_out, ep_tag, nullptr, s, exec, launches});
+        hit = &b->graphs.back();
+      } else {
+        cudaGetLastError();
+        b->graphs_ok = false;  // capture is not available here: plain launches from now on
+      }
+    }
+    if (hit) {
+      CU(MER_ERR_SUBMISSION, "cudaGraphLaunch", cudaGraphLaunch(hit->exec, s));
+      launches = hit->launches;
+      replayed = true;
+    }
+  }
+  if (!replayed) {
+    int rc = ep_enqueue(b, layer, d_x, n_tokens, d_out, s, &launches, false);
+    if (rc) return rc;
+  }
   CU(MER_ERR_SUBMISSION, "cudaEventRecord(stream use)", note_stream_use(b, s));
   b->ctr.kernel_launches += (uint64_t)launches;
-  b->ctr.selected_routed_experts += n_tokens * slots;
+  auto it = b->routers.find(layer);
+  if (it != b->routers.end())
+    b->ctr.selected_routed_experts += n_tokens * (it->second.dev.top_k + (it->second.dev.shared_expert_id != MER_NONE ? 1u : 0u));
   return MER_OK;
 }}  // namespace
 
