@@ -326,6 +326,110 @@ def measure_point(stack, name, zipf_s, B, layers, passes, warm, peaks, x_seed_ba
     return entry, xs_host, xs, out
 
 
+def run_vram_tier(mer_b200, synth, oracle, args, local_rank, threads, n_layers=8, slots_fraction=0.5, B=16, steps=160):
+    """The VRAM tier under miss traffic: a Mixtral-shaped stack whose experts do not all fit the slot arena.  The
+    expert payloads sit in pinned host memory; a step is one layer pass of B tokens whose routing (Zipf-skewed) was
+    computed beforehand, like the expert-id trace the reference's `run` replays (workload.rs:60-140).  Before layer
+    i is enqueued, the experts layer i + 1 needs are looked up in the logical tier (GpuExpertCache semantics: LRU
+    Edge demand admission, threshold promotion into the Anchor Core) and the missing ones are admitted on the copy
+    stream, so their H2D copies overlap layer i's kernels.  Reported: steps/s against the all-resident rate, the miss
+    rate, the H2D rate, and parity of a sampled step."""
+    import torch
+    cfg = synth.CONFIGS[WORKLOADS["cfg2"][0]]
+    E, D, F = cfg.num_experts, cfg.d_model, cfg.d_ff
+    eb = mer_b200.expert_bytes(cfg.dtype, D, F)
+    stride = (256 + eb + 4095) // 4096 * 4096
+    n_exp = n_layers * E
+    n_slots = max(4, int(n_exp * slots_fraction))
+    dev = torch.device("cuda", local_rank)
+    host = torch.empty((n_exp, eb), dtype=torch.uint8).pin_memory()  # the RAM tier: every expert's payload, pinned
+    for l in range(n_layers):
+        host[l * E:(l + 1) * E].copy_(synth.make_expert_blobs_torch(cfg.dtype, D, F, cfg.seed, l, list(range(E)), dev))
+    torch.cuda.synchronize()
+    host_np = host.numpy()
+    be = mer_b200.Backend(cfg.dtype, D, F, stride * n_slots, n_exp, max_tokens=B, max_top_k=cfg.top_k, device=local_rank)
+    cache = mer_b200.GpuExpertCache(n_slots * eb, 0.5, 16)  # anchor_ratio and promote_after_hits of `run --gpu` (main.rs:2190-2194)
+    for l in range(n_layers):
+        gate = mer_b200.LinearGate(synth.make_router(E, D, cfg.seed, l), E, D, cfg.top_k)
+        gate.logit_bias = zipf_bias(synth, cfg, WORKLOADS["cfg2"][3], l, args.zipf_strength)
+        be.install_router(l, gate)
+    xs_host = [synth.make_activations(B, D, cfg.seed, 500 + i) for i in range(16)]
+    xs = [torch.from_numpy(x).to(dev) for x in xs_host]
+    out = torch.empty(B, D, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    # the trace: which experts every step needs (routing needs no resident expert)
+    order = [(i * 5) % n_layers for i in range(steps)]  # layers in a scattered order: consecutive steps share no expert
+    need = []
+    for i, l in enumerate(order):
+        ids, _ = be.route(l, xs_host[i % len(xs)])
+        need.append(sorted({int(v) + l * E for v in ids.reshape(-1) if v != 0xFFFFFFFF}))
+    ram_hits = {}
+    stats = {"admissions": 0, "lookups": 0}
+
+    def ensure(i):
+        """Foreground demand for step i (engine.rs:2382-2429): lookup, admit what is missing, promote what got hot."""
+        for gid in need[i]:
+            stats["lookups"] += 1
+            kind, _ = cache.get(gid)
+            ram_hits[gid] = ram_hits.get(gid, 0) + 1
+            if kind == mer_b200.GpuLookup.Miss:
+                be.demand_admit(cache, gid, host_np[gid], wait=False, reader_wait=False)
+                stats["admissions"] += 1
+            elif not be.contains_generation(gid, cache.current_generation(gid)):
+                be.demand_admit(cache, gid, host_np[gid], wait=False, reader_wait=False)  # admitted logically, evicted physically
+                stats["admissions"] += 1
+            if cache.claim_promotion(gid, ram_hits[gid]):
+                be.hot_promote(cache, gid, host_np[gid], wait=False, reader_wait=False)
+
+    def run(n, check_step=None):
+        ensure(0)
+        got = None
+        for i in range(n):
+            be.moe_layer_forward_device(order[i], xs[i % len(xs)].data_ptr(), B, out.data_ptr(), stream)
+            if i + 1 < n:
+                # the next step's admissions ride the copy stream while this step's kernels run: the victims they evict are
+                # the least recently looked-up experts, this step's experts the most recent, so no slot this step reads is
+                # rewritten and the copies need not wait for it (MER_ADMIT_NO_READER_WAIT)
+                ensure(i + 1)
+            if check_step == i:
+                be.stream_check(order[i], stream)
+                got = out.cpu().numpy().copy()
+        be.stream_check(order[0], stream)
+        return got
+
+    run(min(steps, 2 * n_layers))  # warm: fills the arena, builds the graphs
+    m0, a0, l0 = cache.misses(), stats["admissions"], stats["lookups"]
+    up0 = be.snapshot()["expert_upload_bytes"]
+    t0 = time.perf_counter()
+    ms = cuda_time_ms(torch, lambda: run(steps))
+    wall = time.perf_counter() - t0
+    snap = be.snapshot()
+    misses, lookups = cache.misses() - m0, stats["lookups"] - l0
+    uploaded = snap["expert_upload_bytes"] - up0
+    # parity of one step that ran with admissions in flight
+    probe = steps // 2
+    got = run(probe + 1, check_step=probe)
+    lp = order[probe]
+    gate = oracle_gate(oracle, synth, cfg, lp, WORKLOADS["cfg2"][3], args.zipf_strength)
+    xr = xs_host[probe % len(xs)][:2]
+    ref, _, _, _ = oracle.moe_layer_forward(cfg.dtype, gate, [host_np[lp * E + e] for e in range(E)], xr, F, n_threads=threads)
+    worst = max(float(np.abs(got[t].astype(np.float64) - ref[t]).max() / (np.sqrt(np.mean(ref[t].astype(np.float64) ** 2)) + 1e-30))
+                for t in range(2))
+    par = {"tokens": 2, "max_rel_rms": worst, "bar": PARITY_BAR, "layer": lp}
+    if not worst <= PARITY_BAR:
+        raise SystemExit(f"bench.py: VRAM-tier step differs from the CPU oracle: {par}")
+    cs = cache.stats()
+    entry = {"workload": f"{cfg.name} VRAM tier under miss traffic: {n_layers} layers x {E} experts in pinned RAM, {n_slots} HBM slots "
+                         f"({slots_fraction:.0%} of the stack), decode batch {B}, admissions overlap the previous step's kernels",
+             "batch": B, "steps": steps, "steps_per_s": steps / (ms * 1e-3), "tokens_per_s": B * steps / (ms * 1e-3), "ms_per_step": ms / steps,
+             "wall_ms_per_step": wall * 1e3 / steps, "miss_rate": misses / max(lookups, 1), "expert_admissions": stats["admissions"] - a0,
+             "h2d_gbs": uploaded / (ms * 1e-3) / 1e9, "h2d_bytes": uploaded, "evictions": snap["evictions"],
+             "logical_tier": {k: cs[k] for k in ("anchor_len", "lru_len", "promotions", "hits", "misses")}, "parity": par}
+    be.close()
+    del host
+    return entry
+
+
 def run_sweep(mer_b200, synth, oracle, args, qwen_stack, local_rank, peaks, threads):
     """The other configurations at their stated decode batches.  cfg1 runs on the resident Qwen3 stack (same shapes
     and seed as cfg3), cfg0 on the Mixtral stack of cfg2."""
@@ -373,7 +477,67 @@ def run_sweep(mer_b200, synth, oracle, args, qwen_stack, local_rank, peaks, thre
     for B in dict(SWEEP)["cfg4"]:
         point(st, "cfg4", None, B, 1)
     st.close()
+    torch.cuda.empty_cache()
+    entries.append(run_vram_tier(mer_b200, synth, oracle, args, local_rank, threads))
     return entries
+
+
+def run_ep_point(mer_b200, synth, oracle, epm, args, wl, n_layers, B_rank, mode, rank, world, local_rank, passes, threads, peaks):
+    """One expert-parallel measurement of another configuration (all ranks call this together): B_rank tokens per rank
+    through `passes` layer passes rotating over n_layers resident layers, max over ranks of the CUDA-event time, and
+    rank 0's first tokens against the oracle."""
+    import torch
+    import torch.distributed as dist
+    cfg_name, _, _, zipf_s = WORKLOADS[wl]
+    cfg = synth.CONFIGS[cfg_name]
+    mine = list(epm.local_expert_range(rank, world, cfg.num_experts))
+    stack = Stack(mer_b200, synth, cfg, n_layers, B_rank * world, local_rank, mine=mine)
+    stack.install_routers(zipf_s, args.zipf_strength)
+    ep = epm.ExpertParallel(stack.be, rank, world, cfg.num_experts, B_rank)
+    if mode == "ep-nccl":
+        ep.nccl_init()
+    else:
+        ep.attach()
+    dist.barrier()
+    x_host = synth.make_activations(B_rank, cfg.d_model, cfg.seed, 900 + rank)
+    x = torch.from_numpy(x_host).to(stack.dev)
+    out = torch.empty(B_rank, cfg.d_model, device=stack.dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    fwd = ep.layer_forward_a2a if mode == "ep-nccl" else ep.layer_forward_peer
+
+    def run(n):
+        for i in range(n):
+            fwd(i % n_layers, x.data_ptr(), B_rank, out.data_ptr(), stream)
+
+    fwd(0, x.data_ptr(), B_rank, out.data_ptr(), stream)
+    ep.check(0, stream)
+    par = None
+    if rank == 0:
+        n = min(2, B_rank)
+        rid, _ = stack.be.route(0, x_host[:n])
+        par = parity_check(oracle, synth, cfg, 0, zipf_s, args.zipf_strength, list(x_host[:n]), out[:n].cpu().numpy(), rid.astype(np.int64),
+                           threads)
+    run(3)
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = cuda_time_ms(torch, lambda: run(passes))
+    ep.check(0, stream)
+    t = torch.tensor([ms], device=stack.dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    dist.barrier()
+    stack.close()
+    torch.cuda.empty_cache()
+    slots = cfg.top_k + (1 if cfg.shared else 0)
+    per_layer = ms / passes
+    entry = {"workload": cfg_name, "parallelism": mode, "n_gpus": world, "batch_per_gpu": B_rank, "resident_layers": n_layers,
+             "experts_per_gpu_per_layer": len(mine) + (1 if cfg.shared else 0),
+             "resident_expert_gb_per_gpu": round(stack.resident_bytes / 1e9, 2), "passes": passes, "ms_per_layer": per_layer,
+             "tokens_per_s": B_rank * world / (per_layer * 1e-3), "parity": par}
+    if B_rank * world * slots >= GEMM_MEAN_TOKENS * cfg.num_experts:
+        flops = 2.0 * B_rank * world * slots * 3 * cfg.d_model * cfg.d_ff
+        entry["algorithmic_tflops_all_gpus"] = flops / (per_layer * 1e-3) / 1e12
+    return entry
 
 
 def main():
@@ -604,7 +768,22 @@ def main():
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, e2e_ms, e2e_sync_ms = float(times[0]), float(times[1]) or None, float(times[2]) or None
+    ep_extra = None
+    if ep_mode and strong and not args.no_sweep:
+        # the other expert-parallel configuration: the DeepSeek-V3-shaped stack (256 routed experts split over the ranks, the
+        # shared expert replicated), a subset of its 58 layers resident, at a decode batch and at a 4096-token prefill
+        stack.close()
+        stack = None
+        torch.cuda.empty_cache()
+        ep_extra = []
+        for B_all, n_pass in ((16 * world, 60), (4096, 12)):
+            ep_extra.append(run_ep_point(mer_b200, synth, oracle, epm, args, "cfg4", 4, B_all // world, mode, rank, world, local_rank,
+                                         n_pass, threads, peaks))
     if rank != 0:
+        # every rank tears down in the same order (the library's communicator, then torch's): destroying a NCCL
+        # communicator waits for its peers, so two communicators destroyed in different orders wait for each other
+        if stack is not None:
+            stack.close()
         if world > 1:
             dist.destroy_process_group()
         return
@@ -667,13 +846,18 @@ def main():
     if e2e_sync_ms:
         line["e2e_sync"] = {"value": layer_tokens / (e2e_sync_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": step_bytes,
                             "d2h_bytes_per_step": step_bytes, "mode": "synchronous host entry (mer_moe_layer_forward), one call at a time"}
+    if ep_mode and stack is not None:
+        stack.close()  # before anything slow on this rank: the other ranks are waiting in the same teardown
+        stack = None
     if rank == 0 and args.gpus == 1 and not args.no_cpu:
         rate, ms, sample = cpu_rate(oracle, synth, cfg, 0, zipf_s, args.zipf_strength, xs_host[0], threads, args.cpu_seconds)
         line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
     if rank == 0 and args.gpus == 1 and not args.no_sweep and args.workload == "cfg3":
         line["sweep"] = run_sweep(mer_b200, synth, oracle, args, stack, local_rank, peaks, threads)
-    else:
+    elif stack is not None:
         stack.close()
+    if ep_extra is not None:
+        line["sweep"] = ep_extra
     json_out.write(json.dumps(line) + "\n")
     json_out.flush()
     if world > 1:

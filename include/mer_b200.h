@@ -77,6 +77,11 @@ typedef enum mer_status {
 /* mer_expert_admit flags. */
 #define MER_ADMIT_ANCHOR 0x1u /* Anchor Core entry: never evicted (expert_cache.rs:798-828) */
 #define MER_ADMIT_ASYNC 0x2u  /* return once the side-stream copy is enqueued */
+#define MER_ADMIT_NO_READER_WAIT 0x4u /* the copy stream does not wait for the layers in flight: the caller guarantees that none of
+                                         them reads the slot this admission (or the eviction it causes) rewrites.  That is the case
+                                         when every expert those layers may route to was looked up (mer_gpu_cache_get /
+                                         mer_expert_touch) after the eviction's victims: the admission's H2D copy then overlaps their
+                                         kernels instead of queueing behind them */
 
 typedef struct mer_backend mer_backend;
 
@@ -506,7 +511,10 @@ int mer_ep_layer_forward_device(mer_backend *b, uint32_t layer, const float *d_x
  * ids), local experts over the received rows, the outputs back the same way, weighted sum in slot order.  The call
  * synchronises `stream` once (the exchange is sized on the host from the counts) and is otherwise asynchronous.
  * Stands in for RouteExperts(layer, expert_ids, hidden) -> ffn_out of the reference's shard protocol
- * (proto/route_experts.proto, distributed.rs). ---- */
+ * (proto/route_experts.proto, distributed.rs).
+ * Teardown: mer_backend_destroy of a backend that joined the exchange destroys its communicator, which waits for the
+ * peers' (ncclCommDestroy): every rank must destroy its backend, and in the same order relative to any other NCCL
+ * communicator the host tears down, or the two teardowns wait for each other. ---- */
 #define MER_NCCL_ID_BYTES 128
 int mer_ep_nccl_unique_id(void *id_out /*[MER_NCCL_ID_BYTES]*/);
 int mer_ep_nccl_init(mer_backend *b, const void *unique_id);

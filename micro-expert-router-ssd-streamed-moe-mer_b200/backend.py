@@ -145,22 +145,24 @@ class Backend:
     def contains_generation(self, expert_id, generation):
         return bool(self.lib.mer_expert_contains_generation(self.h, expert_id, generation))
 
-    def demand_admit(self, cache, expert_id, blob, wait=True):
+    def demand_admit(self, cache, expert_id, blob, wait=True, reader_wait=True):
         """Foreground demand (engine.rs:2382-2429): logical admission into the LRU Edge of `cache`, victims retired,
         payload uploaded under the new generation.  Returns the expert's current generation."""
         blob = None if blob is None else np.ascontiguousarray(blob, dtype=np.uint8)
         gen = C.c_uint64(0)
-        self._check(self.lib.mer_expert_demand_admit(self.h, cache.h, expert_id, _ptr(blob), 0 if blob is None else blob.size,
-                                                     0 if wait else capi.ADMIT_ASYNC, C.byref(gen)))
+        flags = (0 if wait else capi.ADMIT_ASYNC) | (0 if reader_wait else capi.ADMIT_NO_READER_WAIT)
+        self._check(self.lib.mer_expert_demand_admit(self.h, cache.h, expert_id, _ptr(blob), 0 if blob is None else blob.size, flags,
+                                                     C.byref(gen)))
         return gen.value
 
-    def hot_promote(self, cache, expert_id, blob=None, wait=True):
+    def hot_promote(self, cache, expert_id, blob=None, wait=True, reader_wait=True):
         """Threshold-driven promotion into the Anchor Core; returns the GpuHotPromotionOutcome."""
         from .expert_cache import GpuHotPromotionOutcome
         blob = None if blob is None else np.ascontiguousarray(blob, dtype=np.uint8)
         out = C.c_int(0)
-        self._check(self.lib.mer_expert_hot_promote(self.h, cache.h, expert_id, _ptr(blob), 0 if blob is None else blob.size,
-                                                    0 if wait else capi.ADMIT_ASYNC, C.byref(out)))
+        flags = (0 if wait else capi.ADMIT_ASYNC) | (0 if reader_wait else capi.ADMIT_NO_READER_WAIT)
+        self._check(self.lib.mer_expert_hot_promote(self.h, cache.h, expert_id, _ptr(blob), 0 if blob is None else blob.size, flags,
+                                                    C.byref(out)))
         return GpuHotPromotionOutcome(out.value)
 
     def touch(self, cache, expert_ids):

@@ -8,7 +8,7 @@ LIB_PATH = os.environ.get("MER_B200_LIB") or os.path.join(HERE, "libmer_b200.so"
 DTYPE_Q4_0, DTYPE_Q8_0 = 0, 1
 SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
 EXPERT_NONE = 0xFFFFFFFF
-ADMIT_ANCHOR, ADMIT_ASYNC = 1, 2
+ADMIT_ANCHOR, ADMIT_ASYNC, ADMIT_NO_READER_WAIT = 1, 2, 4
 LAYER_RESIDUAL = 1
 
 

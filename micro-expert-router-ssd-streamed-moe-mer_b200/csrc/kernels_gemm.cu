@@ -40,11 +40,10 @@ constexpr uint32_t G_HEADER = 4096;      // mbarriers, TMEM base, and from byte 
 constexpr uint32_t TMEM_COLS = 512;      // [0, 256): two accumulator buffers of up to 128 columns; [256, 512): A stages
 constexpr uint32_t TMEM_A0 = 256, A_STAGES = 8, A_STAGE_COLS = 32;  // a stage = one block: 16 columns hi + 16 columns lo
 constexpr uint32_t MAX_RING = 8;
-// The MMA issuer synchronises once per GROUP blocks of K: it waits for a whole group of A stages, issues the
-// group's MMAs and commits ONE barrier, done[], that releases both the group's A stages and the activation stages
-// it read (a wait or a commit per block cost more issue time than the block's MMAs take to run).  A waiter is never
-// two phases behind a done[] barrier: the issuer leads the dequantisers by at most two groups and the producer by
-// at most n_b / 2 + 1, well inside the ring.
+// The MMA issuer synchronises with the dequantisers once per GROUP blocks of K: it waits for a whole group of A stages,
+// issues the group's MMAs and commits done[], which releases the group's A stages; each activation stage (two blocks)
+// is released by a commit of its own right after its MMAs, so that the producer can refill it half a group earlier.
+// A waiter is never two phases behind a done[] barrier: the issuer leads the dequantisers by at most two groups.
 constexpr uint32_t GROUP = 4, DONE_RING = 8;
 static_assert(GROUP == RAW_BLOCKS, "a weight stage holds exactly one group of blocks");
 constexpr float POW2_SCALE_TARGET = 9;   // activations are scaled so that the row maximum lies in [256, 512)
@@ -163,7 +162,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
   if (item_beg >= n_items) return;
 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
-  uint64_t *raw_full = bars, *raw_empty = bars + 8, *a_full = bars + 16, *done = bars + 24, *b_full = bars + 32,
+  uint64_t *raw_full = bars, *raw_empty = bars + 8, *a_full = bars + 16, *done = bars + 24, *b_full = bars + 32, *b_empty = bars + 40,
            *acc_full = bars + 48, *acc_empty = bars + 50, *drain = bars + 52;
   uint32_t *s_tmem = reinterpret_cast<uint32_t *>(smem + 512);
   volatile uint32_t *s_abort = reinterpret_cast<volatile uint32_t *>(smem + 516);
@@ -175,7 +174,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     for (uint32_t s = 0; s < MAX_RING; s++) {
       mbar_init(&raw_full[s], DQ_WARPS), mbar_init(&raw_empty[s], DQ_WARPS);  // one copy per dequantiser warp and stage
       mbar_init(&a_full[s], DQ_WARPS), mbar_init(&done[s], 1);  // one arrival per dequantiser warp and group
-      mbar_init(&b_full[s], 1);
+      mbar_init(&b_full[s], 1), mbar_init(&b_empty[s], 1);
     }
     for (uint32_t s = 0; s < 2; s++) mbar_init(&acc_full[s], 1), mbar_init(&acc_empty[s], EPI_WARPS);
     mbar_init(drain, 1);
@@ -204,18 +203,13 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     // ------------------------------------------------------------------------ producer of the activation stages
     // one stage = 2 blocks of K of the pass's activation image (one bulk copy)
     Ring rb(p.n_b);
-    uint32_t gchunk = 0;  // 64-value activation chunks issued so far, over all items
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
       const uint32_t pass = item / m_tiles;
       if (!expert_base(pass)) continue;
       const uint8_t *bsrc = p.act_img + (size_t)pass * n_chunks * b_stage;
       for (uint32_t c = 0; c < n_chunks && ok; c++) {
-        if (gchunk >= p.n_b) {
-          // the slot's previous chunk was read by the MMAs of group (gchunk - n_b) / 2
-          const uint32_t sp = (gchunk - p.n_b) / (GROUP / 2);
-          ok = mbar_wait(&done[sp % DONE_RING], (sp / DONE_RING) & 1);
-        }
-        gchunk++;
+        // the slot's previous chunk has been read: the MMA issuer commits b_empty right after the two blocks that use a stage
+        if (rb.round > 0) ok = mbar_wait(&b_empty[rb.stage], (rb.round - 1) & 1);
         if (*s_abort) ok = false;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -277,7 +271,10 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
             tc_mma_ts_acc(d_tmem, a_hi + j * 8, dbl, idesc);
             tc_mma_ts_acc(d_tmem, a_lo + j * 8, dbh, idesc);
           }
-          if (b4 & 1) rb.advance();
+          if (b4 & 1) {
+            tc_commit(&b_empty[rb.stage]);  // this activation stage is free as soon as the MMAs issued so far have run
+            rb.advance();
+          }
         }
         if (!ok) break;
         tc_commit(&done[grp % DONE_RING]);

@@ -466,7 +466,7 @@ int admit_impl(mer_backend *b, uint32_t id, uint64_t generation, const void *blo
   CU(MER_ERR_UPLOAD, "cudaSetDevice", cudaSetDevice(b->cfg.device));
   // A slot (the victim's table entry included) may still be read by layers already enqueued: every write of this
   // admission, the eviction's table update first, is ordered after them.
-  CU(MER_ERR_UPLOAD, "order the copy stream after the readers", copy_waits_for_readers(b));
+  if (!(flags & MER_ADMIT_NO_READER_WAIT)) CU(MER_ERR_UPLOAD, "order the copy stream after the readers", copy_waits_for_readers(b));
   size_t si;
   bool already;
   int rc = acquire_slot(b, id, generation, flags, &si, &already);
@@ -835,12 +835,12 @@ MER_EXPORT int mer_expert_contains_generation(mer_backend *b, uint32_t expert_id
 // ---- the logical tier (vram_tier.cpp) driving the physical slots
 namespace {
 // Frees the physical slot of `id` whatever generation it holds (the policy evicted the id).  Caller holds b->mu.
-int retire_physical_locked(mer_backend *b, uint32_t id) {
+int retire_physical_locked(mer_backend *b, uint32_t id, uint32_t flags) {
   const uint32_t layer = 0, expert = id;
   auto it = b->id2slot.find(id);
   if (it == b->id2slot.end()) return MER_OK;
   CU(MER_ERR_UPLOAD, "cudaSetDevice", cudaSetDevice(b->cfg.device));
-  CU(MER_ERR_UPLOAD, "order the copy stream after the readers", copy_waits_for_readers(b));
+  if (!(flags & MER_ADMIT_NO_READER_WAIT)) CU(MER_ERR_UPLOAD, "order the copy stream after the readers", copy_waits_for_readers(b));
   b->h_expert_ptr[id] = nullptr;
   CU(MER_ERR_UPLOAD, "cudaMemcpyAsync(table)",
      cudaMemcpyAsync((void *)(b->d_expert_ptr + id), (void *)(b->h_expert_ptr + id), sizeof(void *), cudaMemcpyHostToDevice, b->copy));
@@ -852,10 +852,10 @@ int retire_physical_locked(mer_backend *b, uint32_t id) {
   return MER_OK;
 }
 
-int retire_evicted(mer_backend *b, const uint32_t *ids, size_t n) {
+int retire_evicted(mer_backend *b, const uint32_t *ids, size_t n, uint32_t flags) {
   std::lock_guard<std::mutex> lock(b->mu);
   for (size_t i = 0; i < n; i++) {
-    int rc = retire_physical_locked(b, ids[i]);
+    int rc = retire_physical_locked(b, ids[i], flags);
     if (rc) return rc;
   }
   return MER_OK;
@@ -911,7 +911,7 @@ MER_EXPORT int mer_expert_demand_admit(mer_backend *b, mer_gpu_cache *cache, uin
   if (generation) *generation = gen;
   if (n_ev > 64)
     return fail(b, MER_ERR_RUNTIME_INVARIANT, layer, expert, "one admission evicted %zu experts, more than this call can retire", n_ev);
-  int rr = retire_evicted(b, evicted, n_ev);
+  int rr = retire_evicted(b, evicted, n_ev, flags);
   if (rr) return rr;
   if (physical_has(b, expert_id, gen)) return MER_OK;
   return admit_impl(b, expert_id, gen, host_blob, bytes, flags & ~MER_ADMIT_ANCHOR, false);
@@ -937,7 +937,7 @@ MER_EXPORT int mer_expert_hot_promote(mer_backend *b, mer_gpu_cache *cache, uint
   }
   *outcome = o;
   if (n_ev > 64) return fail(b, MER_ERR_RUNTIME_INVARIANT, layer, expert, "one promotion evicted %zu experts", n_ev);
-  int rr = retire_evicted(b, evicted, n_ev);
+  int rr = retire_evicted(b, evicted, n_ev, flags);
   if (rr) return rr;
   mer_gpu_admission adm{};
   if (!mer_gpu_cache_current_admission(cache, expert_id, &adm)) return MER_OK;  // nothing admitted (payload required, no capacity ...)
