@@ -32,8 +32,8 @@
 
 namespace {
 
-constexpr int G_WARPS = 18, G_THREADS = G_WARPS * 32;
-constexpr int W_PRODUCER = 0, W_MMA = 1, W_EPI0 = 2, W_DQ0 = 10;
+constexpr int G_WARPS = 19, G_THREADS = G_WARPS * 32;
+constexpr int W_PRODUCER = 0, W_MMA = 1, W_EPI0 = 2, W_DQ0 = 10, W_WEIGHTS = 18;
 constexpr int EPI_WARPS = 4, DQ_WARPS = 8;  // EPI_WARPS per accumulator
 constexpr uint32_t RAW_BLOCKS = 4;       // blocks of K per weight stage (per packed tile: one bulk copy)
 constexpr uint32_t G_HEADER = 4096;      // mbarriers, TMEM base, and from byte 1024 the epilogue groups' per-pass tables
@@ -65,18 +65,21 @@ struct GemmParams {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // One lane of a converged warp.  The MMA warp runs its loops and waits with all 32 lanes, so that every address and
-// descriptor it computes is warp-uniform, and only the tcgen05.mma / tcgen05.commit instructions themselves are
-// issued by the elected lane (always the same one).  Running the whole loop inside `if (lane == 0)` instead made
-// every operand a per-thread value that had to be moved into uniform registers per instruction: ~85 cycles of issue
-// time per MMA, more than a 128-column MMA takes to execute.
-__device__ __forceinline__ bool elect_one() {
+// descriptor it computes is warp-uniform; the lane elected ONCE at the start issues the tcgen05.mma / tcgen05.commit
+// instructions, as predicated instructions (no branch around them).  Measured on the way here: the whole loop inside
+// `if (lane == 0)` cost ~85 cycles of issue time per MMA, an elect.sync + branch around every single MMA ~65, either
+// of them more than a narrow MMA takes to execute.
+__device__ __forceinline__ uint32_t elect_one() {
   uint32_t pred;
   asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
-  return pred != 0;
+  return pred;
 }
-__device__ __forceinline__ void tc_commit(uint64_t *bar) {
-  if (elect_one())
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ void tc_commit(uint32_t leader, uint64_t *bar) {
+  asm volatile(
+      "{\n .reg .pred q;\n setp.ne.b32 q, %1, 0;\n"
+      " @q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" ::"r"(smem_u32(bar)),
+      "r"(leader)
+      : "memory");
 }
 // K-major, no swizzle: 8-row x 16-byte core matrices; LBO = step between core matrices along K,
 // SBO = step between 8-row groups.  Bits: start >> 4 [0,14), LBO >> 4 [16,30), SBO >> 4 [32,46), version 1 [46,48).
@@ -86,17 +89,16 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
 // f16 x f16 -> f32, both operands K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t instr_desc(uint32_t n) { return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
 // A operand read from tensor memory (lane = row, a 32-bit column = two consecutive values of K), B through a descriptor.
-// Called by the whole (converged) warp; the elected lane issues.
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  if (elect_one())
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
+// Called by the whole (converged) warp; only the lane with leader != 0 issues.
+__device__ __forceinline__ void tc_mma_ts(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p, q;\n setp.ne.b32 q, %5, 0;\n setp.ne.b32 p, %4, 0;\n"
+      " @q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate), "r"(leader)
+      : "memory");
 }
-__device__ __forceinline__ void tc_mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc) {
-  tc_mma_ts(d_tmem, a_tmem, b, idesc, 1u);
+__device__ __forceinline__ void tc_mma_ts_acc(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc) {
+  tc_mma_ts(leader, d_tmem, a_tmem, b, idesc, 1u);
 }
 // 32 columns of this thread's TMEM lane (lane = 32 * (warp % 4) + lane id).
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
@@ -172,7 +174,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < MAX_RING; s++) {
-      mbar_init(&raw_full[s], DQ_WARPS), mbar_init(&raw_empty[s], DQ_WARPS);  // one copy per dequantiser warp and stage
+      mbar_init(&raw_full[s], 1), mbar_init(&raw_empty[s], DQ_WARPS);  // filled by the weight producer, left by every dequantiser warp
       mbar_init(&a_full[s], DQ_WARPS), mbar_init(&done[s], 1);  // one arrival per dequantiser warp and group
       mbar_init(&b_full[s], 1), mbar_init(&b_empty[s], 1);
     }
@@ -188,7 +190,16 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *s_tmem, 0);  // the same value in every lane, and visibly so
+  // The CTA owns all 512 columns of its SM's tensor memory, so the allocation starts at lane 0, column 0.  Using the
+  // constant instead of the value read back lets every TMEM address below be computed in uniform registers: with the
+  // loaded value each MMA took ~57 cycles to issue, with the constant ~35.  Should the allocator ever answer otherwise,
+  // the kernel gives the columns back, latches the error status and leaves.
+  constexpr uint32_t tmem_base = 0;
+  if (*s_tmem != tmem_base) {
+    if (warp == W_MMA) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(*s_tmem), "r"(TMEM_COLS) : "memory");
+    if (threadIdx.x == 0) atomicOr(p.d.status, MER_DEVSTAT_TIMEOUT);
+    return;
+  }
 
   const size_t proj_bytes = (size_t)d.D * d.F / 32 * BB;
   const size_t tile_bytes = (size_t)p.kb_total * 16 * BB;
@@ -230,6 +241,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     // The whole warp walks the loops and waits (every value it computes is warp-uniform); the elected lane issues.
     // one step = one 32-value block of K: two instructions of 16 values for each of the three operand pairings
     Ring rb(p.n_b);
+    const uint32_t leader = elect_one();  // the warp is converged here; the same lane issues from now on
     uint32_t n_done = 0;  // items issued so far: accumulator buffer = n_done & 1, its k-th use has k = n_done >> 1
     uint32_t grp = 0;     // groups of GROUP blocks issued so far, over all items; A-stage half = grp & 1
     // B descriptors differ only in their start-address field: one base, then 64-bit adds of (byte offset >> 4).
@@ -265,29 +277,53 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
           for (uint32_t j = 0; j < 2; j++) {  // 16 values of K per instruction: 8 TMEM columns of A, two core-matrix columns of B
             const uint64_t dbh = b_blk + (uint64_t)(j * j16), dbl = dbh + lo16;
             if (b4 == 0 && j == 0)
-              tc_mma_ts(d_tmem, a_hi, dbh, idesc, st != 0);  // the item's first MMA overwrites the accumulator
+              tc_mma_ts(leader, d_tmem, a_hi, dbh, idesc, st != 0);  // the item's first MMA overwrites the accumulator
             else
-              tc_mma_ts_acc(d_tmem, a_hi + j * 8, dbh, idesc);
-            tc_mma_ts_acc(d_tmem, a_hi + j * 8, dbl, idesc);
-            tc_mma_ts_acc(d_tmem, a_lo + j * 8, dbh, idesc);
+              tc_mma_ts_acc(leader, d_tmem, a_hi + j * 8, dbh, idesc);
+            tc_mma_ts_acc(leader, d_tmem, a_hi + j * 8, dbl, idesc);
+            tc_mma_ts_acc(leader, d_tmem, a_lo + j * 8, dbh, idesc);
           }
           if (b4 & 1) {
-            tc_commit(&b_empty[rb.stage]);  // this activation stage is free as soon as the MMAs issued so far have run
+            tc_commit(leader, &b_empty[rb.stage]);  // this activation stage is free as soon as the MMAs issued so far have run
             rb.advance();
           }
         }
         if (!ok) break;
-        tc_commit(&done[grp % DONE_RING]);
-        if (st + GROUP >= p.kb_total) tc_commit(&acc_full[buf]);
+        tc_commit(leader, &done[grp % DONE_RING]);
+        if (st + GROUP >= p.kb_total) tc_commit(leader, &acc_full[buf]);
       }
       n_done++;
     }
     if (!ok && lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
     __syncwarp();
     // nothing may still be writing TMEM when it is freed
-    tc_commit(drain);
+    tc_commit(leader, drain);
     (void)mbar_wait(drain, 0);
     __syncwarp();
+  } else if (warp == W_WEIGHTS) {
+    // ------------------------------------------------------------------------ producer of the weight stages
+    // one stage = one group of RAW_BLOCKS blocks of the item's eight packed tiles; lane m < 8 copies tile m's chunk
+    Ring raw(p.n_raw);
+    for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
+      const uint8_t *base = expert_base(item / m_tiles);
+      if (!base) continue;
+      const uint8_t *src = base + region + (size_t)((item % m_tiles) * 8 + (lane & 7)) * tile_bytes;
+      for (uint32_t gi = 0; gi < n_groups && ok; gi++) {
+        if (raw.round > 0) ok = mbar_wait(&raw_empty[raw.stage], (raw.round - 1) & 1);  // every dequantiser warp has left the stage
+        if (*s_abort) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) mbar_expect_tx(&raw_full[raw.stage], RAW_BYTES);
+        __syncwarp();
+        if (lane < 8) bulk_g2s(s_raw + raw.stage * RAW_BYTES + lane * TILE_RAW, src + (size_t)gi * TILE_RAW, TILE_RAW, &raw_full[raw.stage]);
+        raw.advance();
+      }
+    }
+    if (!ok) {
+      if (lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
+      // weight copies already in flight get a bounded chance to land before the CTA's shared memory is released
+      for (uint32_t s = 0; s < p.n_raw; s++) (void)mbar_wait(&raw_full[s], 0), (void)mbar_wait(&raw_full[s], 1);
+    }
   } else if (warp >= W_DQ0) {
     // ------------------------------------------------------------------------ dequantisers
     // A thread owns one weight row of the item: TMEM lane 32 * (warp % 4) + lane, i.e. packed tile 2q + lane / 16,
@@ -298,45 +334,12 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     const uint32_t q = warp & 3, mine = (warp - W_DQ0) >> 2;
     const uint32_t T = 2 * q + (lane >> 4), g = lane & 7, half = (lane >> 3) & 1;
     const __half2 zp = DT == MER_DTYPE_Q4_0 ? __floats2half2_rn(1032.0f, 1032.0f) : __floats2half2_rn(1152.0f, 1152.0f);
-    // This warp also copies packed tile `tw` of every weight stage.  The copies run n_raw groups ahead of the
-    // dequantisation, walking the same sequence of (item, group) with a cursor of their own.
-    const uint32_t tw = warp - W_DQ0;
-    uint32_t pf_item = item_beg, pf_g = 0, n_issued = 0;
-    const uint8_t *pf_src = nullptr;  // chunk 0 of this warp's packed tile in the cursor's item
-    auto pf_seek = [&]() {  // the next item whose expert is resident
-      for (; pf_item < n_items; pf_item += item_step) {
-        const uint8_t *base = expert_base(pf_item / m_tiles);
-        if (base) {
-          pf_src = base + region + (size_t)((pf_item % m_tiles) * 8 + tw) * tile_bytes;
-          break;
-        }
-      }
-    };
-    auto issue_copy = [&]() {  // group number n_issued of this CTA goes to stage n_issued % n_raw
-      if (pf_item >= n_items) return;
-      if (lane == 0) {
-        const uint32_t stage = n_issued % p.n_raw;
-        mbar_expect_tx(&raw_full[stage], TILE_RAW);
-        bulk_g2s(s_raw + stage * RAW_BYTES + tw * TILE_RAW, pf_src + (size_t)pf_g * TILE_RAW, TILE_RAW, &raw_full[stage]);
-      }
-      n_issued++;
-      if (++pf_g == n_groups) pf_g = 0, pf_item += item_step, pf_seek();
-    };
-    pf_seek();
-    for (uint32_t i = 0; i < p.n_raw; i++) issue_copy();
-    uint32_t n_seen = 0;  // groups dequantised so far
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
       const uint32_t pass = item / m_tiles;
       if (!expert_base(pass)) continue;
       // one group (= one weight stage) at a time: this warp's two blocks of it, one wait on each side
-      for (uint32_t gi = 0; gi < n_groups && ok; gi++, gblk += GROUP, n_seen++) {
-        if (n_seen >= 1) {
-          // refill the stage the previous group emptied (every dequantiser warp has left it) with group n_seen - 1 + n_raw
-          const uint32_t prev = n_seen - 1;
-          ok = mbar_wait(&raw_empty[prev % p.n_raw], (prev / p.n_raw) & 1);
-          if (ok) issue_copy();
-        }
-        if (ok) ok = mbar_wait(&raw_full[raw.stage], raw.round & 1);
+      for (uint32_t gi = 0; gi < n_groups && ok; gi++, gblk += GROUP) {
+        ok = mbar_wait(&raw_full[raw.stage], raw.round & 1);
         if (ok && gblk >= A_STAGES) {
           // the group's A stages were last read by the MMAs of group gblk / GROUP - 2
           const uint32_t sp = gblk / GROUP - A_STAGES / GROUP;
@@ -392,11 +395,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
         raw.advance();
       }
     }
-    if (!ok) {
-      if (lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
-      // weight copies already in flight get a bounded chance to land before the CTA's shared memory is released
-      for (uint32_t s = 0; s < p.n_raw; s++) (void)mbar_wait(&raw_full[s], 0), (void)mbar_wait(&raw_full[s], 1);
-    }
+    if (!ok && lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
   } else {
     // ---------------------------------------------------------------------------- epilogue
     // Two groups of four warps, one per accumulator buffer: group e drains the items whose running number is e mod 2,
