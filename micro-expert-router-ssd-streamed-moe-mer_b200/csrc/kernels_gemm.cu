@@ -25,6 +25,8 @@
 // (bounded) for its copies and MMAs in flight, frees its TMEM and returns.
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "../../include/mer_b200.h"
 #include "kernels.h"
 #include "layout.cuh"
@@ -40,10 +42,9 @@ constexpr uint32_t G_HEADER = 4096;      // mbarriers, TMEM base, and from byte 
 constexpr uint32_t TMEM_COLS = 512;      // [0, 256): two accumulator buffers of up to 128 columns; [256, 512): A stages
 constexpr uint32_t TMEM_A0 = 256, A_STAGES = 8, A_STAGE_COLS = 32;  // a stage = one block: 16 columns hi + 16 columns lo
 constexpr uint32_t MAX_RING = 8;
-// The MMA issuer synchronises with the dequantisers once per GROUP blocks of K: it waits for a whole group of A stages,
-// issues the group's MMAs and commits done[], which releases the group's A stages; each activation stage (two blocks)
-// is released by a commit of its own right after its MMAs, so that the producer can refill it half a group earlier.
-// A waiter is never two phases behind a done[] barrier: the issuer leads the dequantisers by at most two groups.
+// The MMA issuer synchronises with its producers once per GROUP blocks of K: it waits for a whole group of A stages
+// (a_full) and for the group's activation stage (b_full), issues the group's MMAs and commits done[], which releases
+// both.  A waiter is never two phases behind a done[] barrier: the issuer leads its producers by at most two groups.
 constexpr uint32_t GROUP = 4, DONE_RING = 8;
 static_assert(GROUP == RAW_BLOCKS, "a weight stage holds exactly one group of blocks");
 constexpr float POW2_SCALE_TARGET = 9;   // activations are scaled so that the row maximum lies in [256, 512)
@@ -56,7 +57,7 @@ struct GemmParams {
   uint32_t rows;           // F (gate/up) or D (down)
   uint32_t kb_total;       // 32-value blocks per weight row
   uint32_t bn;             // token columns per pass (16, 32, 64 or 128)
-  uint32_t b_lbo;          // bytes between K core matrices of B: bn * 16 + 32
+  uint32_t b_lbo;          // bn * 16 + 32: a chunk slot of the activation ring and of the image array holds 16 of these
   uint32_t n_raw, n_b;     // ring depths (weights, activations)
   float *out;              // phase 0: h [P x F]; phase 1: y [P x D]
 };
@@ -87,7 +88,7 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
   return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
 }
 // f16 x f16 -> f32, both operands K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t instr_desc(uint32_t n) { return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t n) { return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
 // A operand read from tensor memory (lane = row, a 32-bit column = two consecutive values of K), B through a descriptor.
 // Called by the whole (converged) warp; only the lane with leader != 0 issues.
 __device__ __forceinline__ void tc_mma_ts(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
@@ -137,6 +138,17 @@ __device__ __forceinline__ void dq2(uint32_t biased, __half2 zp1024, __half2 d2,
   lo = h2_bits(__hfma2(d2, q, __hneg2(h)));
 }
 
+// Token columns a pass occupies in its activation image and in the accumulator: its count rounded up to 16, at most bn.
+__host__ __device__ constexpr uint32_t pass_width(uint32_t bn, uint32_t count) {
+  const uint32_t w = (count + 15u) & ~15u;
+  return w < bn ? w : bn;
+}
+// Bytes between two K core-matrix columns of a pass's image: the hi rows, then the lo rows, then a 32-byte skew.
+__host__ __device__ constexpr uint32_t pass_lbo(uint32_t width) { return 2u * width * 16u + 32u; }
+// A pass of at most MERGE_WIDTH columns multiplies W_hi by [x_hi | x_lo] in one instruction of twice its width
+// (two column sets of one accumulator buffer, added in the epilogue): two instructions per 16 values of K instead of three.
+constexpr uint32_t MERGE_WIDTH = 64;
+
 struct Ring {
   uint32_t stage = 0, round = 0, n;
   __device__ explicit Ring(uint32_t n_) : n(n_) {}
@@ -164,19 +176,19 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
   if (item_beg >= n_items) return;
 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
-  uint64_t *raw_full = bars, *raw_empty = bars + 8, *a_full = bars + 16, *done = bars + 24, *b_full = bars + 32, *b_empty = bars + 40,
+  uint64_t *raw_full = bars, *raw_empty = bars + 8, *a_full = bars + 16, *done = bars + 24, *b_full = bars + 32,
            *acc_full = bars + 48, *acc_empty = bars + 50, *drain = bars + 52;
   uint32_t *s_tmem = reinterpret_cast<uint32_t *>(smem + 512);
   volatile uint32_t *s_abort = reinterpret_cast<volatile uint32_t *>(smem + 516);
   uint8_t *s_raw = smem + G_HEADER;
   uint8_t *s_b = s_raw + p.n_raw * RAW_BYTES;
-  const uint32_t b_term = 8 * p.b_lbo, b_stage = 2 * b_term;
+  const uint32_t b_stage = 16 * p.b_lbo;  // ring slot and image slot of one 64-value chunk of K: what the widest pass needs
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < MAX_RING; s++) {
       mbar_init(&raw_full[s], 1), mbar_init(&raw_empty[s], DQ_WARPS);  // filled by the weight producer, left by every dequantiser warp
       mbar_init(&a_full[s], DQ_WARPS), mbar_init(&done[s], 1);  // one arrival per dequantiser warp and group
-      mbar_init(&b_full[s], 1), mbar_init(&b_empty[s], 1);
+      mbar_init(&b_full[s], 1);
     }
     for (uint32_t s = 0; s < 2; s++) mbar_init(&acc_full[s], 1), mbar_init(&acc_empty[s], EPI_WARPS);
     mbar_init(drain, 1);
@@ -212,22 +224,27 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
 
   if (warp == W_PRODUCER) {
     // ------------------------------------------------------------------------ producer of the activation stages
-    // one stage = 2 blocks of K of the pass's activation image (one bulk copy)
+    // one stage = one group of blocks of K of the pass's activation image: two chunks of 64 values, one bulk copy each.
+    // A stage is free again when the MMAs of the group that used it have run: the issuer's done[] commit says so.
     Ring rb(p.n_b);
+    uint32_t pg = 0;  // groups issued so far, over all items (the issuer counts the same way)
     for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
       const uint32_t pass = item / m_tiles;
       if (!expert_base(pass)) continue;
       const uint8_t *bsrc = p.act_img + (size_t)pass * n_chunks * b_stage;
-      for (uint32_t c = 0; c < n_chunks && ok; c++) {
-        // the slot's previous chunk has been read: the MMA issuer commits b_empty right after the two blocks that use a stage
-        if (rb.round > 0) ok = mbar_wait(&b_empty[rb.stage], (rb.round - 1) & 1);
+      const uint32_t bytes = 8 * pass_lbo(pass_width(p.bn, __ldg(d.pass_count + pass)));  // a narrow pass has a small image
+      for (uint32_t gi = 0; gi < n_groups && ok; gi++, pg++) {
+        if (pg >= p.n_b) {
+          const uint32_t sp = pg - p.n_b;
+          ok = mbar_wait(&done[sp % DONE_RING], (sp / DONE_RING) & 1);
+        }
         if (*s_abort) ok = false;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (lane == 0) {
-          mbar_expect_tx(&b_full[rb.stage], b_stage);
-          bulk_g2s(s_b + (size_t)rb.stage * b_stage, bsrc + (size_t)c * b_stage, b_stage, &b_full[rb.stage]);
-        }
+        if (lane == 0) mbar_expect_tx(&b_full[rb.stage], 2 * bytes);
+        __syncwarp();
+        if (lane < 2)
+          bulk_g2s(s_b + ((size_t)rb.stage * 2 + lane) * b_stage, bsrc + ((size_t)gi * 2 + lane) * b_stage, bytes, &b_full[rb.stage]);
         rb.advance();
       }
     }
@@ -246,53 +263,66 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     uint32_t grp = 0;     // groups of GROUP blocks issued so far, over all items; A-stage half = grp & 1
     // B descriptors differ only in their start-address field: one base, then 64-bit adds of (byte offset >> 4).
     // (The ring lies well inside the 256 KB the 14-bit field spans, so the adds never carry out of it.)
-    const uint64_t b_desc0 = smem_desc(smem_u32(s_b), p.b_lbo, 128);
-    const uint32_t stage16 = b_stage >> 4, half16 = (4 * p.b_lbo) >> 4, j16 = (2 * p.b_lbo) >> 4, lo16 = b_term >> 4;
-    for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
-      const uint32_t pass = item / m_tiles;
-      if (!expert_base(pass)) continue;
+    const uint32_t stage16 = b_stage >> 4;
+    // One item's K loop for a pass of WIDTH columns.  WIDTH is a template argument because everything the MMA instruction
+    // takes (descriptors, TMEM addresses) must sit in uniform registers: values derived from kernel parameters and
+    // constants are computed there directly, values derived from a loaded pass count had to be moved over per
+    // instruction (measured: +25 % issue time).
+    auto run_item = [&](auto width_tag) {
+      constexpr uint32_t width = decltype(width_tag)::value, lbo = pass_lbo(width);
+      constexpr bool merged = width <= MERGE_WIDTH;
+      constexpr uint32_t idesc = instr_desc(width), idesc2 = instr_desc(2 * width);
+      constexpr uint32_t half16 = (4 * lbo) >> 4, j16 = (2 * lbo) >> 4, lo16 = width;  // the lo rows follow the hi rows: width * 16 bytes
+      const uint64_t b_desc0 = smem_desc(smem_u32(s_b), lbo, 128);
       const uint32_t buf = n_done & 1, use = n_done >> 1;
-      // the MMA is as wide as the pass has tokens (rounded up to 16 columns): a ragged last pass of a group costs
-      // its share, not a full tile
-      const uint32_t idesc = instr_desc(min(p.bn, (__ldg(d.pass_count + pass) + 15u) & ~15u));
       const uint32_t d_tmem = tmem_base + buf * 128;
       for (uint32_t st = 0; st < p.kb_total && ok; st += GROUP, grp++) {
         const uint32_t ag = grp & 1;
         if (st == 0 && use > 0) ok = mbar_wait(&acc_empty[buf], (use - 1) & 1);  // the buffer's previous item has been drained
         if (ok) ok = mbar_wait(&a_full[ag], (grp >> 1) & 1);
+        if (ok) ok = mbar_wait(&b_full[rb.stage], rb.round & 1);
         if (*s_abort) ok = false;
         ok = __all_sync(0xffffffffu, ok);  // warp-uniform by construction; the vote also tells the compiler so
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (uint32_t b4 = 0; b4 < GROUP; b4++) {
-          if (!(b4 & 1)) {
-            ok = __all_sync(0xffffffffu, mbar_wait(&b_full[rb.stage], rb.round & 1));
-            if (!ok) break;
-            tc_fence_after();
-          }
           const uint32_t a_hi = tmem_base + TMEM_A0 + (ag * GROUP + b4) * A_STAGE_COLS, a_lo = a_hi + 16;
-          const uint64_t b_blk = b_desc0 + (uint64_t)(rb.stage * stage16 + (b4 & 1) * half16);
+          const uint64_t b_blk = b_desc0 + (uint64_t)((rb.stage * 2 + (b4 >> 1)) * stage16 + (b4 & 1) * half16);
 #pragma unroll
           for (uint32_t j = 0; j < 2; j++) {  // 16 values of K per instruction: 8 TMEM columns of A, two core-matrix columns of B
             const uint64_t dbh = b_blk + (uint64_t)(j * j16), dbl = dbh + lo16;
-            if (b4 == 0 && j == 0)
-              tc_mma_ts(leader, d_tmem, a_hi, dbh, idesc, st != 0);  // the item's first MMA overwrites the accumulator
-            else
-              tc_mma_ts_acc(leader, d_tmem, a_hi + j * 8, dbh, idesc);
-            tc_mma_ts_acc(leader, d_tmem, a_hi + j * 8, dbl, idesc);
+            const uint32_t acc = (b4 == 0 && j == 0) ? (st != 0) : 1u;  // the item's first MMA overwrites the accumulator
+            if (merged) {
+              tc_mma_ts(leader, d_tmem, a_hi + j * 8, dbh, idesc2, acc);  // columns [0, width): W_hi x_hi; [width, 2 width): W_hi x_lo
+            } else {
+              tc_mma_ts(leader, d_tmem, a_hi + j * 8, dbh, idesc, acc);
+              tc_mma_ts_acc(leader, d_tmem, a_hi + j * 8, dbl, idesc);
+            }
             tc_mma_ts_acc(leader, d_tmem, a_lo + j * 8, dbh, idesc);
           }
-          if (b4 & 1) {
-            tc_commit(leader, &b_empty[rb.stage]);  // this activation stage is free as soon as the MMAs issued so far have run
-            rb.advance();
-          }
         }
-        if (!ok) break;
-        tc_commit(leader, &done[grp % DONE_RING]);
+        rb.advance();
+        tc_commit(leader, &done[grp % DONE_RING]);  // frees the group's A stages and its activation stage
         if (st + GROUP >= p.kb_total) tc_commit(leader, &acc_full[buf]);
       }
       n_done++;
+    };
+    for (uint32_t item = item_beg; item < n_items && ok; item += item_step) {
+      const uint32_t pass = item / m_tiles;
+      if (!expert_base(pass)) continue;
+      // the MMA is as wide as the pass has tokens (rounded up to 16 columns): a ragged last pass of a group costs
+      // its share, not a full tile
+      switch (pass_width(p.bn, __ldg(d.pass_count + pass)) >> 4) {
+        case 1: run_item(std::integral_constant<uint32_t, 16>{}); break;
+        case 2: run_item(std::integral_constant<uint32_t, 32>{}); break;
+        case 3: run_item(std::integral_constant<uint32_t, 48>{}); break;
+        case 4: run_item(std::integral_constant<uint32_t, 64>{}); break;
+        case 5: run_item(std::integral_constant<uint32_t, 80>{}); break;
+        case 6: run_item(std::integral_constant<uint32_t, 96>{}); break;
+        case 7: run_item(std::integral_constant<uint32_t, 112>{}); break;
+        default: run_item(std::integral_constant<uint32_t, 128>{}); break;
+      }
     }
     if (!ok && lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
     __syncwarp();
@@ -440,21 +470,30 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
         atomicOr(d.status, MER_DEVSTAT_RESIDENCY_MISS);  // fail closed: zeros below
       }
       const uint32_t acc_addr = tmem_base + ((q * 32u) << 16) + buf * 128;
+      const uint32_t width = pass_width(p.bn, pcount);
+      const bool merged = width <= MERGE_WIDTH;
       const bool is_gate = (lane & 8) == 0;
       const bool clamp = d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit);
       for (uint32_t cbase = 0; cbase < pcount; cbase += 32) {  // 32 columns (tokens) at a time
         uint32_t v[32];
+        float val[32];
         if (resident && !dead) {
           tc_ld32(acc_addr + cbase, v);
+#pragma unroll
+          for (int i = 0; i < 32; i++) val[i] = __uint_as_float(v[i]);
+          if (merged) {  // the W_hi x_lo column set of the same tokens
+            tc_ld32(acc_addr + width + cbase, v);
+#pragma unroll
+            for (int i = 0; i < 32; i++) val[i] += __uint_as_float(v[i]);
+          }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; i++) v[i] = 0;
+          for (int i = 0; i < 32; i++) val[i] = 0.0f;
         }
         // the steps run column-batched (all multiplies, then all shuffles, ...): warp-synchronous operations are kept in
         // program order, so a column-by-column loop would serialise on the latency of every single one
-        float val[32];
 #pragma unroll
-        for (int i = 0; i < 32; i++) val[i] = __uint_as_float(v[i]) * s_un[cbase + i];
+        for (int i = 0; i < 32; i++) val[i] *= s_un[cbase + i];
         if (p.phase == 0) {
           // rows come in packed tiles of 16: slots 0..7 gate rows, 8..15 the matching up rows
           float up[32];
@@ -512,9 +551,11 @@ __global__ void __launch_bounds__(256) k_row_amax(const float *__restrict__ x, u
   if (lane == 0) amax[tok] = nan ? 0x7fc00000u : __float_as_uint(mx);
 }
 
-// Builds, for every token pass, the activation operand images the GEMM kernel copies chunk by
-// chunk: per 64 columns of K, {hi tile, lo tile}, each 8 core-matrix columns of [bn/8 row groups]
-// [8 rows][16 B] (+32 B skew), rows = the pass's tokens.  grid = (pass capacity, K / 64).
+// Builds, for every token pass, the activation operand images the GEMM kernel copies chunk by chunk.  A chunk is 64
+// values of K = 8 core-matrix columns; a column holds the pass's rows as 16-byte pieces, the f16 hi parts of all rows
+// first, then the lo parts (+32 B skew): [hi row 0 .. hi row w-1 | lo row 0 .. lo row w-1], w = the pass's width
+// (its token count rounded up to 16), so one descriptor of 2w rows covers [x_hi | x_lo] and a narrow pass is a small
+// image.  grid = (pass capacity, K / 64).
 __global__ void __launch_bounds__(256) k_gemm_act_image(MoeDispatch d, int phase, const float *__restrict__ act, uint32_t K, uint32_t bn,
                                                         uint32_t b_lbo, const uint32_t *__restrict__ amax_tok, uint8_t *__restrict__ img,
                                                         float *__restrict__ unscale) {
@@ -522,9 +563,10 @@ __global__ void __launch_bounds__(256) k_gemm_act_image(MoeDispatch d, int phase
   if (pass >= *d.n_passes) return;
   const uint32_t pstart = d.pass_start[pass], pcount = d.pass_count[pass];
   const uint32_t n_chunks = K / 64;
-  uint8_t *dst0 = img + ((size_t)pass * n_chunks + chunk) * 16 * b_lbo;
-  for (uint32_t idx = threadIdx.x; idx < bn * 8; idx += blockDim.x) {
-    const uint32_t j = idx % bn, k8 = idx / bn;
+  uint8_t *dst0 = img + ((size_t)pass * n_chunks + chunk) * 16 * b_lbo;  // slots are as large as the widest pass needs
+  const uint32_t width = pass_width(bn, pcount), lbo = pass_lbo(width);
+  for (uint32_t idx = threadIdx.x; idx < width * 8; idx += blockDim.x) {
+    const uint32_t j = idx % width, k8 = idx / width;
     uint4 hi = make_uint4(0, 0, 0, 0), lo = make_uint4(0, 0, 0, 0);
     float un = 0.0f;
     if (j < pcount) {
@@ -553,9 +595,9 @@ __global__ void __launch_bounds__(256) k_gemm_act_image(MoeDispatch d, int phase
       }
       hi = make_uint4(h[0], h[1], h[2], h[3]), lo = make_uint4(l[0], l[1], l[2], l[3]);
     }
-    uint8_t *dst = dst0 + (size_t)k8 * b_lbo + (j >> 3) * 128 + (j & 7) * 16;
+    uint8_t *dst = dst0 + (size_t)k8 * lbo + j * 16;
     *reinterpret_cast<uint4 *>(dst) = hi;
-    *reinterpret_cast<uint4 *>(dst + 8 * b_lbo) = lo;
+    *reinterpret_cast<uint4 *>(dst + width * 16) = lo;
     if (chunk == 0 && k8 == 0) unscale[(size_t)pass * bn + j] = un;
   }
 }
@@ -569,8 +611,8 @@ GemmPlan gemm_plan(int dtype, uint32_t bn) {
   const uint32_t tile_raw = RAW_BLOCKS * 16 * (dtype == MER_DTYPE_Q4_0 ? MER_Q4_BLOCK_BYTES : MER_Q8_BLOCK_BYTES);
   GemmPlan pl{};
   pl.b_lbo = bn * 16 + 32;
-  pl.n_raw = 3, pl.n_b = 5;
-  pl.smem = G_HEADER + (size_t)pl.n_raw * 8 * tile_raw + (size_t)pl.n_b * 16 * pl.b_lbo;
+  pl.n_raw = 4, pl.n_b = 2;  // weight stages (one group each); activation stages (one group = two chunk slots each)
+  pl.smem = G_HEADER + (size_t)pl.n_raw * 8 * tile_raw + (size_t)pl.n_b * 2 * 16 * pl.b_lbo;
   return pl;
 }
 
