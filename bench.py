@@ -53,7 +53,7 @@ SWEEP = [  # (workload, batches) measured after the headline at N = 1; cfg1 / cf
     ("cfg4", (16,)),
 ]
 DTYPE_NAME = {0: "q4_0", 1: "q8_0"}
-GEMM_MEAN_TOKENS = 32  # mean tokens per expert from which the library's automatic selection runs the tcgen05 GEMM kernels
+GEMM_MEAN_TOKENS = 12  # mean tokens per expert from which the library's automatic selection runs the tcgen05 GEMM kernels
 PARITY_TOKENS = 4
 PARITY_BAR = 1e-3      # max-abs error of a token's output relative to the RMS of the oracle's output
 PARALLELISM_NOTE = {

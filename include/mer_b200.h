@@ -526,7 +526,7 @@ int mer_stream_check(mer_backend *b, uint32_t layer, void *stream);
 int mer_last_error(mer_backend *b, mer_error_info *out);
 int mer_snapshot(mer_backend *b, mer_counters *out);
 /* Selects the kernel family: 0 = automatic (streaming kernels for a few tokens per expert, the
- * tcgen05 GEMM kernels from a mean of 32 tokens per expert), 1 = generic fp32 kernels (any shape),
+ * tcgen05 GEMM kernels from a mean of 12 tokens per expert), 1 = generic fp32 kernels (any shape),
  * 2 = streaming tensor-core kernels, 3 = tcgen05 GEMM kernels (2 and 3: block-aligned shapes).
  * For qualification runs. */
 int mer_set_kernel_path(mer_backend *b, int path);

@@ -254,8 +254,9 @@ bool use_stream_path(mer_backend *b, const MoeDispatch &d) {
   return stream_ffn_supported(d.dtype, d.D, d.F) && b->d_stream_scratch != nullptr;
 }
 
-constexpr uint32_t GEMM_MIN_MEAN_TOKENS = 32;  // mean tokens per expert from which the tcgen05 GEMM path takes over
-                                               // (measured: at a mean of 16 the streaming kernels are still ahead, at 32 level)
+constexpr uint32_t GEMM_MIN_MEAN_TOKENS = 12;  // mean tokens per expert from which the tcgen05 GEMM path takes over (measured:
+                                               // at a mean of 8-9 the streaming kernels are level or ahead, at 16 the GEMM kernels
+                                               // win by 5 % on Mixtral-sized and by 50 % on Qwen3-sized experts)
 
 // Chooses the kernel family of a dispatch and binds its scratch (call before the grouping kernel, which
 // cuts the groups into passes of d.tokens_per_pass).
