@@ -145,9 +145,12 @@ __host__ __device__ constexpr uint32_t pass_width(uint32_t bn, uint32_t count) {
 }
 // Bytes between two K core-matrix columns of a pass's image: the hi rows, then the lo rows, then a 32-byte skew.
 __host__ __device__ constexpr uint32_t pass_lbo(uint32_t width) { return 2u * width * 16u + 32u; }
-// A pass of at most MERGE_WIDTH columns multiplies W_hi by [x_hi | x_lo] in one instruction of twice its width
-// (two column sets of one accumulator buffer, added in the epilogue): two instructions per 16 values of K instead of three.
-constexpr uint32_t MERGE_WIDTH = 64;
+// The passes of a group of at most MERGE_TOKENS tokens (always a single pass) multiply W_hi by [x_hi | x_lo] in one
+// instruction of twice the pass's width (two column sets of one accumulator buffer, added in the epilogue): two
+// instructions per 16 values of K instead of three.  The rule looks at the group, not at the pass, so that the order
+// of a token's additions depends only on how many tokens its expert received, never on which pass it landed in:
+// results stay bit-identical from run to run although large dispatches are grouped with atomics.
+constexpr uint32_t MERGE_TOKENS = 64;
 
 struct Ring {
   uint32_t stage = 0, round = 0, n;
@@ -268,9 +271,9 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     // takes (descriptors, TMEM addresses) must sit in uniform registers: values derived from kernel parameters and
     // constants are computed there directly, values derived from a loaded pass count had to be moved over per
     // instruction (measured: +25 % issue time).
-    auto run_item = [&](auto width_tag) {
+    auto run_item = [&](auto width_tag, auto merged_tag) {
       constexpr uint32_t width = decltype(width_tag)::value, lbo = pass_lbo(width);
-      constexpr bool merged = width <= MERGE_WIDTH;
+      constexpr bool merged = decltype(merged_tag)::value;
       constexpr uint32_t idesc = instr_desc(width), idesc2 = instr_desc(2 * width);
       constexpr uint32_t half16 = (4 * lbo) >> 4, j16 = (2 * lbo) >> 4, lo16 = width;  // the lo rows follow the hi rows: width * 16 bytes
       const uint64_t b_desc0 = smem_desc(smem_u32(s_b), lbo, 128);
@@ -313,15 +316,29 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
       if (!expert_base(pass)) continue;
       // the MMA is as wide as the pass has tokens (rounded up to 16 columns): a ragged last pass of a group costs
       // its share, not a full tile
-      switch (pass_width(p.bn, __ldg(d.pass_count + pass)) >> 4) {
-        case 1: run_item(std::integral_constant<uint32_t, 16>{}); break;
-        case 2: run_item(std::integral_constant<uint32_t, 32>{}); break;
-        case 3: run_item(std::integral_constant<uint32_t, 48>{}); break;
-        case 4: run_item(std::integral_constant<uint32_t, 64>{}); break;
-        case 5: run_item(std::integral_constant<uint32_t, 80>{}); break;
-        case 6: run_item(std::integral_constant<uint32_t, 96>{}); break;
-        case 7: run_item(std::integral_constant<uint32_t, 112>{}); break;
-        default: run_item(std::integral_constant<uint32_t, 128>{}); break;
+      const uint32_t grp_id = __ldg(d.pass_group + pass);
+      const bool merged = __ldg(d.offsets + grp_id + 1) - __ldg(d.offsets + grp_id) <= MERGE_TOKENS;
+      const uint32_t w16 = pass_width(p.bn, __ldg(d.pass_count + pass)) >> 4;
+      using T = std::true_type;
+      using F = std::false_type;
+      if (merged) {
+        switch (w16) {
+          case 1: run_item(std::integral_constant<uint32_t, 16>{}, T{}); break;
+          case 2: run_item(std::integral_constant<uint32_t, 32>{}, T{}); break;
+          case 3: run_item(std::integral_constant<uint32_t, 48>{}, T{}); break;
+          default: run_item(std::integral_constant<uint32_t, 64>{}, T{}); break;
+        }
+      } else {
+        switch (w16) {
+          case 1: run_item(std::integral_constant<uint32_t, 16>{}, F{}); break;
+          case 2: run_item(std::integral_constant<uint32_t, 32>{}, F{}); break;
+          case 3: run_item(std::integral_constant<uint32_t, 48>{}, F{}); break;
+          case 4: run_item(std::integral_constant<uint32_t, 64>{}, F{}); break;
+          case 5: run_item(std::integral_constant<uint32_t, 80>{}, F{}); break;
+          case 6: run_item(std::integral_constant<uint32_t, 96>{}, F{}); break;
+          case 7: run_item(std::integral_constant<uint32_t, 112>{}, F{}); break;
+          default: run_item(std::integral_constant<uint32_t, 128>{}, F{}); break;
+        }
       }
     }
     if (!ok && lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
@@ -471,7 +488,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
       }
       const uint32_t acc_addr = tmem_base + ((q * 32u) << 16) + buf * 128;
       const uint32_t width = pass_width(p.bn, pcount);
-      const bool merged = width <= MERGE_WIDTH;
+      const uint32_t grp_id = d.pass_group[pass];
+      const bool merged = d.offsets[grp_id + 1] - d.offsets[grp_id] <= MERGE_TOKENS;
       const bool is_gate = (lane & 8) == 0;
       const bool clamp = d.swiglu_limit > 0.0f && isfinite(d.swiglu_limit);
       for (uint32_t cbase = 0; cbase < pcount; cbase += 32) {  // 32 columns (tokens) at a time

@@ -93,12 +93,14 @@ constexpr uint32_t GRID_GROUPING_PAIRS = 8192;    // from this many pairs the gr
 // on) and clears the per-pair max cells.  One CTA of 256 threads; `off` = the group offsets.
 __device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
   __shared__ uint32_t s_pcnt[257];
+  __shared__ uint8_t s_cost[1024];  // cost of each of the first 1024 passes (the weighted work split below)
   const uint32_t tpp = d.tokens_per_pass, P = d.n_tokens * d.slots;
+  const uint32_t tpp_shift = 31 - __clz(tpp);  // tokens per pass is a power of two (4 or 8; 16 .. 128 for the GEMM kernels)
   for (uint32_t i = threadIdx.x; i < P; i += 256) d.amax[i] = 0;
   const uint32_t per = (d.n_groups + 255) / 256;
   const uint32_t g0 = threadIdx.x * per, g1 = min(g0 + per, d.n_groups);
   uint32_t mine = 0;
-  for (uint32_t g = g0; g < g1; g++) mine += (off[g + 1] - off[g] + tpp - 1) / tpp;
+  for (uint32_t g = g0; g < g1; g++) mine += (off[g + 1] - off[g] + tpp - 1) >> tpp_shift;
   s_pcnt[threadIdx.x + 1] = mine;
   if (threadIdx.x == 0) s_pcnt[0] = 0;
   __syncthreads();
@@ -121,9 +123,11 @@ __device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
   for (uint32_t g = g0; g < g1; g++) {
     const uint32_t beg = off[g], end = off[g + 1];
     for (uint32_t st = beg; st < end; st += tpp) {
+      const uint32_t cnt = min(tpp, end - st);
       d.pass_group[np] = g;
       d.pass_start[np] = st;
-      d.pass_count[np] = min(tpp, end - st);
+      d.pass_count[np] = cnt;
+      if (np < 1024) s_cost[np] = cnt > 4 ? 13 : 10;
       np++;
     }
   }
@@ -136,7 +140,7 @@ __device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
   // more than four tokens multiplies two token tiles instead of one, which measures as ~1.3x the time: cost 13 vs 10.
   __shared__ uint32_t s_cum[1025];
   const uint32_t n_passes = s_pcnt[256], G = d.n_ctas;
-  __syncthreads();  // pass_count[] written above is read back below
+  __syncthreads();  // s_cost[] written above is read back below
   const bool weighted = n_passes <= 1024 && tpp == 8;
   if (weighted) {
     // inclusive scan of the pass costs: 4 per thread, then the same warp scan as above over the 256 partial sums
@@ -144,7 +148,7 @@ __device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
 #pragma unroll
     for (int i = 0; i < 4; i++) {
       const uint32_t q = threadIdx.x * 4 + i;
-      c[i] = q < n_passes ? (d.pass_count[q] > 4 ? 13u : 10u) : 0u;
+      c[i] = q < n_passes ? (uint32_t)s_cost[q] : 0u;
       run += c[i];
     }
     s_pcnt[threadIdx.x + 1] = run;
@@ -181,9 +185,25 @@ __device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
     uint32_t bound;
     if (!weighted) {
       bound = (uint32_t)(n_items * b / G);
+    } else if ((uint64_t)s_cum[n_passes] * ipp * G <= 0xFFFFFFFFull) {
+      // the usual case: everything fits 32 bits (64-bit divisions cost a few hundred cycles each, and this loop sits
+      // on the critical path of every decode layer)
+      const uint32_t total = s_cum[n_passes] * ipp, target = total * b / G;
+      uint32_t lo = 0, hi = n_passes;  // largest pass index with cum[pass] * ipp <= target
+      while (lo < hi) {
+        const uint32_t mid = (lo + hi + 1) >> 1;
+        if (s_cum[mid] * ipp <= target) lo = mid; else hi = mid - 1;
+      }
+      if (lo >= n_passes) {
+        bound = (uint32_t)n_items;
+      } else {
+        const uint32_t w = s_cum[lo + 1] - s_cum[lo];
+        const uint32_t rem = target - s_cum[lo] * ipp;
+        bound = lo * ipp + min(ipp, (rem + w - 1) / w);
+      }
     } else {
       const uint64_t total = (uint64_t)s_cum[n_passes] * ipp, target = total * b / G;
-      uint32_t lo = 0, hi = n_passes;  // largest pass index with cum[pass] * ipp <= target
+      uint32_t lo = 0, hi = n_passes;
       while (lo < hi) {
         const uint32_t mid = (lo + hi + 1) >> 1;
         if ((uint64_t)s_cum[mid] * ipp <= target) lo = mid; else hi = mid - 1;
@@ -371,8 +391,13 @@ __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uin
 __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t token, float *s_score, float *s_sel,
                             uint8_t *s_ok, uint32_t *s_groups, float *s_gscore) {
   const uint32_t E = r.num_experts, lane = threadIdx.x & 31;
+  constexpr int REG_E = 8;  // up to 32 * REG_E experts: selection keys live in registers
+  const bool small = E <= 32 * REG_E;
+  float cbias[REG_E];  // correction bias, fetched now so that its latency hides behind the scoring
+#pragma unroll
+  for (int j = 0; j < REG_E; j++) cbias[j] = (small && r.correction_bias && lane + 32 * j < E) ? __ldg(r.correction_bias + lane + 32 * j) : 0.0f;
   if (r.logit_bias)
-    for (uint32_t i = lane; i < E; i += 32) s_score[i] += r.logit_bias[i];
+    for (uint32_t i = lane; i < E; i += 32) s_score[i] += __ldg(r.logit_bias + i);
   __syncwarp();
   if (r.scoring == MER_SCORE_SOFTMAX) {
     // softmax_inplace (transformer.rs:2747-2819)
@@ -397,8 +422,18 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
       for (uint32_t i = lane; i < E; i += 32) s_score[i] = expf(s_score[i] - mx);
       __syncwarp();
       float sum = 0.0f;
-      if (lane == 0)  // the reference sums left to right; keep that order
-        for (uint32_t i = 0; i < E; i++) sum += s_score[i];
+      if (lane == 0) {  // the reference sums left to right; keep that order
+        if ((E & 3u) == 0) {
+          const float4 *s4 = reinterpret_cast<const float4 *>(s_score);  // E % 4 == 0 keeps every warp's array 16-byte aligned
+#pragma unroll 4
+          for (uint32_t i = 0; i < E / 4; i++) {
+            const float4 v = s4[i];
+            sum += v.x, sum += v.y, sum += v.z, sum += v.w;
+          }
+        } else {
+          for (uint32_t i = 0; i < E; i++) sum += s_score[i];
+        }
+      }
       sum = __shfl_sync(0xffffffffu, sum, 0);
       if (sum > 0.0f)
         for (uint32_t i = lane; i < E; i += 32) s_score[i] = s_score[i] / sum;
@@ -407,9 +442,17 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
     for (uint32_t i = lane; i < E; i += 32) s_score[i] = 1.0f / (1.0f + expf(-s_score[i]));
   }
   __syncwarp();
-  for (uint32_t i = lane; i < E; i += 32) {
-    s_sel[i] = r.correction_bias ? s_score[i] + r.correction_bias[i] : s_score[i];
-    s_ok[i] = 1;
+  if (small) {
+#pragma unroll
+    for (int j = 0; j < REG_E; j++) {
+      const uint32_t i = lane + 32 * j;
+      if (i < E) s_sel[i] = r.correction_bias ? s_score[i] + cbias[j] : s_score[i], s_ok[i] = 1;
+    }
+  } else {
+    for (uint32_t i = lane; i < E; i += 32) {
+      s_sel[i] = r.correction_bias ? s_score[i] + r.correction_bias[i] : s_score[i];
+      s_ok[i] = 1;
+    }
   }
   __syncwarp();
   // group_filter_shape + select_top_groups (gating.rs:335-376)
@@ -457,25 +500,53 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
   const uint32_t S = d.slots, k = r.top_k;
   uint32_t my_id = MER_NONE;  // lane i keeps the i-th pick
   uint32_t n_sel = 0;
-  for (uint32_t n = 0; n < k; n++) {
-    int bk = 0;
-    uint32_t bi = MER_NONE;
-    for (uint32_t i = lane; i < E; i += 32) {
-      float s = s_sel[i];
-      if (!s_ok[i] || !isfinite(s)) continue;
-      int key = total_key(s);
-      if (bi == MER_NONE || key > bk) bk = key, bi = i;  // ascending scan keeps the lowest id on ties
+  if (small) {
+    // keys in registers: lane l holds experts l, l + 32, ...; a taken or disallowed expert bids INT_MIN
+    int keys[REG_E];
+#pragma unroll
+    for (int j = 0; j < REG_E; j++) {
+      const uint32_t i = lane + 32 * j;
+      const float sv = i < E ? s_sel[i] : 0.0f;
+      keys[j] = (i < E && s_ok[i] && isfinite(sv)) ? total_key(sv) : INT_MIN;
     }
-    // warp arg-max by (key desc, id asc): two warp reductions; lanes without a candidate bid the lowest key
-    const int my_key = bi == MER_NONE ? INT_MIN : bk;
-    const int top_key = __reduce_max_sync(0xffffffffu, my_key);
-    const uint32_t top_id = __reduce_min_sync(0xffffffffu, (bi != MER_NONE && my_key == top_key) ? bi : MER_NONE);
-    bk = top_key, bi = top_id;
-    if (bi == MER_NONE) break;
-    if (lane == 0) s_ok[bi] = 0;
-    if (lane == (n & 31)) my_id = bi;
-    n_sel++;
-    __syncwarp();
+    for (uint32_t n = 0; n < k; n++) {
+      int bk = INT_MIN;
+      uint32_t bj = 0;
+#pragma unroll
+      for (int j = 0; j < REG_E; j++)
+        if (keys[j] > bk) bk = keys[j], bj = j;  // ascending j keeps the lowest id on ties
+      const int top_key = __reduce_max_sync(0xffffffffu, bk);
+      if (top_key == INT_MIN) break;  // nothing left to pick
+      const uint32_t top_id = __reduce_min_sync(0xffffffffu, bk == top_key ? lane + 32 * bj : MER_NONE);
+      if (lane == (top_id & 31u)) {
+#pragma unroll
+        for (int j = 0; j < REG_E; j++)
+          if ((uint32_t)j == (top_id >> 5)) keys[j] = INT_MIN;
+      }
+      if (lane == (n & 31)) my_id = top_id;
+      n_sel++;
+    }
+  } else {
+    for (uint32_t n = 0; n < k; n++) {
+      int bk = 0;
+      uint32_t bi = MER_NONE;
+      for (uint32_t i = lane; i < E; i += 32) {
+        float s = s_sel[i];
+        if (!s_ok[i] || !isfinite(s)) continue;
+        int key = total_key(s);
+        if (bi == MER_NONE || key > bk) bk = key, bi = i;  // ascending scan keeps the lowest id on ties
+      }
+      // warp arg-max by (key desc, id asc): two warp reductions; lanes without a candidate bid the lowest key
+      const int my_key = bi == MER_NONE ? INT_MIN : bk;
+      const int top_key = __reduce_max_sync(0xffffffffu, my_key);
+      const uint32_t top_id = __reduce_min_sync(0xffffffffu, (bi != MER_NONE && my_key == top_key) ? bi : MER_NONE);
+      bk = top_key, bi = top_id;
+      if (bi == MER_NONE) break;
+      if (lane == 0) s_ok[bi] = 0;
+      if (lane == (n & 31)) my_id = bi;
+      n_sel++;
+      __syncwarp();
+    }
   }
   // mixing weights = unbiased scores; renormalise; scale (gating.rs:443-474)
   float w = (lane < n_sel && my_id != MER_NONE) ? s_score[my_id] : 0.0f;

@@ -139,9 +139,8 @@ def test_full_size_prefill_properties_and_spot_check():
     counts = np.bincount(ids.ravel(), minlength=E)
     assert counts.max() > 2 * counts.mean() > 0 and counts.sum() == B * k  # skewed, every pair accounted for
     assert (sids == ids[perm]).all()
-    # passes are cut differently, and a narrow pass groups its three operand products differently from a wide one
-    # (two accumulator column sets added at the end): equal up to the order of the fp32 additions
-    assert rel_rms_err(shuffled, out[perm]) <= 1e-4
+    # passes are cut differently, but the order of a token's additions depends only on its expert's token count
+    assert rel_rms_err(shuffled, out[perm]) <= 1e-5
     assert (ids2 == ids).all()
     worst = max(rel_rms_err(out[t], streamed[t]) for t in range(B))
     assert worst <= 1e-4, worst
