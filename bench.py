@@ -58,11 +58,11 @@ PARITY_TOKENS = 4
 PARITY_BAR = 1e-3      # max-abs error of a token's output relative to the RMS of the oracle's output
 PARALLELISM_NOTE = {
     "replicas": "{n} replicas, tokens data-parallel, no data-path collective",
-    "ep-peer": "expert-parallel over {n} GPUs (experts split contiguously, tokens data-parallel), dispatch and combine by the "
+    "ep-peer": "expert-parallel over {n} GPUs ({e} experts per GPU and layer, {placement}; tokens data-parallel), dispatch and combine by the "
                "library's kernels through peer memory over NVLink",
-    "ep-collective": "expert-parallel over {n} GPUs (experts split contiguously, tokens data-parallel), NCCL all-gather of "
+    "ep-collective": "expert-parallel over {n} GPUs ({e} experts per GPU and layer, {placement}; tokens data-parallel), NCCL all-gather of "
                      "tokens+routing and reduce-scatter of partial outputs",
-    "ep-nccl": "expert-parallel over {n} GPUs (experts split contiguously, tokens data-parallel), NCCL all-to-all dispatch and "
+    "ep-nccl": "expert-parallel over {n} GPUs ({e} experts per GPU and layer, {placement}; tokens data-parallel), NCCL all-to-all dispatch and "
                "combine issued by the library (grouped ncclSend / ncclRecv of the rows that hit a peer's experts)",
 }
 
@@ -82,6 +82,9 @@ def parse_args():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--zipf-strength", type=float, default=1.0)
+    ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
+                    help="expert-parallel modes: experts placed by the token counts of a calibration batch (greedy, the same "
+                         "number of experts on every GPU), or rank j holds experts [j*E/N, (j+1)*E/N)")
     ap.add_argument("--parallelism", default="auto", choices=["auto", "replicas", "ep-peer", "ep-collective", "ep-nccl"],
                     help="N > 1: expert-parallel with the exchange through peer memory (default) or through NCCL "
                          "collectives, or independent token-parallel replicas")
@@ -148,6 +151,42 @@ def ncu_traffic(key):
 
 def zipf_bias(synth, cfg, zipf_s, layer, strength):
     return None if zipf_s is None else synth.zipf_logit_bias(cfg.num_experts, zipf_s, cfg.seed, layer, strength=strength)
+
+
+def calibration_counts(synth, cfg, layer, zipf_s, strength, n_tokens=2048):
+    """Tokens per routed expert of a calibration batch (its own seed, not a batch the benchmark times), by a numpy
+    restatement of the selection: enough to rank the experts by popularity, no parity claim."""
+    E, k = cfg.num_experts, cfg.top_k
+    x = synth.make_activations(n_tokens, cfg.d_model, cfg.seed, 7000 + layer)
+    logits = x @ synth.make_router(E, cfg.d_model, cfg.seed, layer).T
+    bias = zipf_bias(synth, cfg, zipf_s, layer, strength)
+    if bias is not None:
+        logits = logits + bias
+    sel = 1.0 / (1.0 + np.exp(-logits)) if cfg.scoring == 1 else logits  # softmax keeps the order of the logits
+    if cfg.n_group > 1 and 0 < cfg.topk_group < cfg.n_group:
+        g = sel.reshape(n_tokens, cfg.n_group, E // cfg.n_group)
+        gscore = np.sort(g, axis=2)[:, :, -2:].sum(axis=2)
+        keep = np.argsort(-gscore, axis=1)[:, :cfg.topk_group]
+        mask = np.zeros((n_tokens, cfg.n_group), bool)
+        np.put_along_axis(mask, keep, True, axis=1)
+        sel = np.where(np.repeat(mask, E // cfg.n_group, axis=1), sel, -np.inf)
+    top = np.argpartition(-sel, k - 1, axis=1)[:, :k]
+    return np.bincount(top.ravel(), minlength=E)
+
+
+def ep_placement(epm, synth, cfg, n_layers, zipf_s, strength, rank, world, policy):
+    """(owner table by global expert id or None, this rank's local expert indices per layer)."""
+    E = cfg.num_experts
+    if policy == "contiguous":
+        mine = list(epm.local_expert_range(rank, world, E))
+        return None, [mine] * n_layers
+    owner = np.zeros(n_layers * E, np.uint16)
+    mine = []
+    for l in range(n_layers):
+        o = epm.balanced_placement(calibration_counts(synth, cfg, l, zipf_s, strength), world)
+        owner[l * E:(l + 1) * E] = o
+        mine.append([e for e in range(E) if o[e] == rank])
+    return owner, mine
 
 
 def host_blobs(synth, cfg, layer, experts, threads):
@@ -224,19 +263,22 @@ class Stack:
         import torch
         self.mer, self.synth, self.cfg, self.L = mer_b200, synth, cfg, n_layers
         self.torch, self.dev = torch, torch.device("cuda", device_index)
-        self.mine = list(range(cfg.num_experts)) if mine is None else list(mine)
+        # the routed experts this backend holds: all, one list for every layer, or one list per layer
+        if mine is None:
+            mine = list(range(cfg.num_experts))
+        self.mine = [list(m) for m in mine] if len(mine) and isinstance(mine[0], (list, tuple, range)) else [list(mine)] * n_layers
         self.slots = cfg.top_k + (1 if cfg.shared else 0)
         self.exp_bytes = mer_b200.expert_bytes(cfg.dtype, cfg.d_model, cfg.d_ff)
         stride = (256 + self.exp_bytes + 4095) // 4096 * 4096
-        n_local = len(self.mine) + (1 if cfg.shared else 0)
-        self.be = mer_b200.Backend(cfg.dtype, cfg.d_model, cfg.d_ff, stride * n_local * n_layers,
+        n_slots = sum(len(m) for m in self.mine) + (n_layers if cfg.shared else 0)
+        self.be = mer_b200.Backend(cfg.dtype, cfg.d_model, cfg.d_ff, stride * n_slots,
                                    (n_layers + 1) * cfg.num_experts + n_layers, max_tokens=max_tokens, max_top_k=self.slots,
                                    device=device_index)
-        self.resident_bytes = self.exp_bytes * n_local * n_layers
+        self.resident_bytes = self.exp_bytes * n_slots
         # fill the slots: every layer's experts are generated in device memory (seed = the configuration's, layer = its index)
         chunk = max(1, int((1 << 30) // (self.exp_bytes * 10)))  # the generator's 64-bit temporaries are ~10x the blob
         for l in range(n_layers):
-            todo = [(e, l * cfg.num_experts + e) for e in self.mine]
+            todo = [(e, l * cfg.num_experts + e) for e in self.mine[l]]
             if cfg.shared:
                 todo.append((cfg.num_experts, n_layers * cfg.num_experts + l))
             for i in range(0, len(todo), chunk):
@@ -490,10 +532,12 @@ def run_ep_point(mer_b200, synth, oracle, epm, args, wl, n_layers, B_rank, mode,
     import torch.distributed as dist
     cfg_name, _, _, zipf_s = WORKLOADS[wl]
     cfg = synth.CONFIGS[cfg_name]
-    mine = list(epm.local_expert_range(rank, world, cfg.num_experts))
+    owner, mine = ep_placement(epm, synth, cfg, n_layers, zipf_s, args.zipf_strength, rank, world, args.placement)
     stack = Stack(mer_b200, synth, cfg, n_layers, B_rank * world, local_rank, mine=mine)
     stack.install_routers(zipf_s, args.zipf_strength)
     ep = epm.ExpertParallel(stack.be, rank, world, cfg.num_experts, B_rank)
+    if owner is not None:
+        ep.set_placement(owner)
     if mode == "ep-nccl":
         ep.nccl_init()
     else:
@@ -531,7 +575,7 @@ def run_ep_point(mer_b200, synth, oracle, epm, args, wl, n_layers, B_rank, mode,
     slots = cfg.top_k + (1 if cfg.shared else 0)
     per_layer = ms / passes
     entry = {"workload": cfg_name, "parallelism": mode, "n_gpus": world, "batch_per_gpu": B_rank, "resident_layers": n_layers,
-             "experts_per_gpu_per_layer": len(mine) + (1 if cfg.shared else 0),
+             "experts_per_gpu_per_layer": len(mine[0]) + (1 if cfg.shared else 0), "placement": args.placement,
              "resident_expert_gb_per_gpu": round(stack.resident_bytes / 1e9, 2), "passes": passes, "ms_per_layer": per_layer,
              "tokens_per_s": B_rank * world / (per_layer * 1e-3), "parity": par}
     if B_rank * world * slots >= GEMM_MEAN_TOKENS * cfg.num_experts:
@@ -578,7 +622,10 @@ def main():
               "resident_expert_gb": round(exp_bytes * (cfg.num_experts + (1 if cfg.shared else 0)) * L / 1e9, 2),
               "value_counts": "tokens x layers per second = tokens/s through one MoE layer",
               "l2": f"a step streams {L} distinct resident layers; every layer pass reads more expert bytes than L2 holds",
-              "parallelism": "single GPU" if args.gpus == 1 else PARALLELISM_NOTE[mode].format(n=args.gpus)}
+              "parallelism": "single GPU" if args.gpus == 1 else PARALLELISM_NOTE[mode].format(
+                  n=args.gpus, e=-(-cfg.num_experts // world),
+                  placement="placed by the token counts of a calibration batch, largest first onto the least loaded GPU" if args.placement == "balanced"
+                  else "rank j holds experts [j*E/N, (j+1)*E/N)")}
 
     if args.impl == "reference":
         if rank != 0:
@@ -610,7 +657,11 @@ def main():
     hbm_peak, tf_burst, tf_sustained, peak_kind = peaks
 
     epm = importlib.import_module("mer_b200.expert_parallel")
-    mine = list(epm.local_expert_range(rank, world, cfg.num_experts)) if ep_mode else list(range(cfg.num_experts))
+    owner = None
+    if ep_mode:
+        owner, mine = ep_placement(epm, synth, cfg, L, zipf_s, args.zipf_strength, rank, world, args.placement)
+    else:
+        mine = [list(range(cfg.num_experts))] * L
     stack = Stack(mer_b200, synth, cfg, L, B * world if ep_mode else B, local_rank, mine=mine)
     be, slots = stack.be, stack.slots
     if args.kernel_path:
@@ -628,6 +679,8 @@ def main():
     ep = None
     if ep_mode:
         ep = epm.ExpertParallel(be, rank, world, cfg.num_experts, B)
+        if owner is not None:
+            ep.set_placement(owner)
         if mode == "ep-peer":
             ep.attach()
             dist.barrier()
@@ -714,7 +767,8 @@ def main():
         for l in range(L):
             x_all = np.concatenate([synth.make_activations(B, cfg.d_model, cfg.seed, r * 64 + (l % n_x)) for r in range(world)])
             ids, _ = be.route(l, x_all)
-            hit = [e for e in np.unique(ids[ids != 0xFFFFFFFF]) if int(e) in set(mine)]
+            local = {l * cfg.num_experts + e for e in mine[l]}
+            hit = [e for e in np.unique(ids[ids != 0xFFFFFFFF]) if int(e) in local]
             hit_bytes.append((len(hit) + (1 if cfg.shared else 0)) * exp_bytes)
 
     # ---- end to end: host buffers in, host buffers out, copies inside the timed region

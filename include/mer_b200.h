@@ -479,6 +479,13 @@ typedef struct mer_ep_cfg {
 /* Allocates this rank's exchange buffer (tokens, routing, per-pair expert outputs, arrival flags). */
 int mer_ep_init(mer_backend *b, const mer_ep_cfg *cfg);
 size_t mer_ep_exchange_bytes(mer_backend *b);
+/* Expert placement.  By default rank j holds the local expert indices [j * ceil(E / N), (j + 1) * ceil(E / N)) of every
+ * layer.  A table owner[global expert id] = rank (n_ids entries from id 0; the same table on every rank) replaces that
+ * rule for every exchange mode, e.g. a placement balanced by measured expert popularity: the reference's ShardRouter
+ * maps experts to nodes by id % num_nodes (distributed.rs), which is as blind to popularity as the contiguous split.
+ * Which experts a rank admits is the host's side of the same table.  NULL / 0 restores the default.  Synchronises the
+ * device; call between steps, on every rank before the next layer call. */
+int mer_ep_set_placement(mer_backend *b, const uint16_t *owner, size_t n_ids);
 /* One process per GPU: export the exchange buffer as a 64-byte CUDA IPC handle; after the host has
  * exchanged the handles of all ranks (rank order), attach maps the peers' buffers. */
 int mer_ep_export_handle(mer_backend *b, void *handle_out);

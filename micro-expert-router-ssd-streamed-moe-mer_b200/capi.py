@@ -152,6 +152,7 @@ ABI_SYMBOLS = {
     "mer_set_kernel_path": (C.c_int, [_vp, _i32]),
     "mer_ep_init": (C.c_int, [_vp, C.POINTER(MerEpCfg)]),
     "mer_ep_exchange_bytes": (_sz, [_vp]),
+    "mer_ep_set_placement": (C.c_int, [_vp, _vp, _sz]),
     "mer_ep_export_handle": (C.c_int, [_vp, _vp]),
     "mer_ep_attach_handles": (C.c_int, [_vp, _vp, _sz]),
     "mer_ep_exchange_buffer": (_vp, [_vp]),

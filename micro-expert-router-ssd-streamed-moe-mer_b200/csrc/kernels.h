@@ -81,7 +81,8 @@ struct MoeDispatch {
 struct EpDev {
   uint8_t *peer[MER_EP_MAX_WORLD];  // exchange buffer of rank j as mapped here (own buffer at [rank])
   uint32_t rank, world;
-  uint32_t experts_per_rank;  // rank j owns the local expert indices [j*epr, (j+1)*epr) of every layer
+  uint32_t experts_per_rank;  // rank j owns the local expert indices [j*epr, (j+1)*epr) of every layer ...
+  const uint16_t *owner;      // ... unless a placement table is installed: owner[global expert id] (same on every rank)
   uint32_t top_k;             // slots >= top_k are the shared expert (runs on the token's own rank)
   uint32_t id_base;           // layer * experts_per_layer of the layer in flight
   uint32_t tokens_per_rank;   // tokens every rank contributes to the step in flight

@@ -44,10 +44,14 @@ __device__ bool wait_flag(const uint32_t *flag, uint32_t epoch, uint64_t limit_n
   }
 }
 
+// Rank that holds routed expert e of the layer in flight.
+__device__ __forceinline__ uint32_t expert_owner(const EpDev &ep, uint32_t e) {
+  return ep.owner ? (uint32_t)__ldg(ep.owner + e) : (e - ep.id_base) / ep.experts_per_rank;
+}
 __device__ __forceinline__ bool pair_is_local(const EpDev &ep, uint32_t e, uint32_t slot, uint32_t src_rank) {
   if (e == MER_NONE) return false;
   if (slot >= ep.top_k) return src_rank == ep.rank;  // shared expert: replicated, runs where the token lives
-  return (e - ep.id_base) / ep.experts_per_rank == ep.rank;
+  return expert_owner(ep, e) == ep.rank;
 }
 
 // (1) Routing gathered by the host: keep the pairs whose expert lives here, blank the rest.
@@ -144,7 +148,7 @@ __global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, const uint32_t *__
     const float wt = w[t * slots + sl];
     const float *row = nullptr;
     if (e != MER_NONE && wt != 0.0f) {
-      const uint32_t owner = sl >= ep.top_k ? ep.rank : (e - ep.id_base) / ep.experts_per_rank;
+      const uint32_t owner = sl >= ep.top_k ? ep.rank : expert_owner(ep, e);
       row = reinterpret_cast<const float *>(ep.peer[owner] + ep.off_y) + ((size_t)tg * slots + sl) * D;
     }
     s_row[sl] = row;
@@ -189,7 +193,7 @@ __global__ void __launch_bounds__(256) k_a2a_pack(EpDev ep, uint32_t D, uint32_t
     if (lane == 0) pos[p] = MER_NONE;
     return;
   }
-  const uint32_t dest = slot >= ep.top_k ? ep.rank : (e - ep.id_base) / ep.experts_per_rank;  // the shared expert runs at home
+  const uint32_t dest = slot >= ep.top_k ? ep.rank : expert_owner(ep, e);  // the shared expert runs at home
   uint32_t row = 0;
   if (lane == 0) row = dest * seg_rows + atomicAdd(cursors + dest, 1u);
   row = __shfl_sync(0xffffffffu, row, 0);

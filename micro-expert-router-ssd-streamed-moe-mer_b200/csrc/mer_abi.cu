@@ -110,6 +110,8 @@ struct mer_backend {
   mer_ep_cfg ep_cfg{};
   uint8_t *ep_buf = nullptr;
   size_t ep_bytes = 0, ep_off_w = 0;
+  uint16_t *d_ep_owner = nullptr;       // placement table [max_experts] (mer_ep_set_placement), device copy
+  std::vector<uint16_t> ep_owner_host;  // and host copy; empty = the contiguous rule
   void *ep_opened[MER_EP_MAX_WORLD] = {};  // mappings opened from IPC handles (closed at destroy)
   // captured launch sequences of mer_moe_layer_forward_device, replayed with one cudaGraphLaunch
   struct GraphEntry {
@@ -401,6 +403,7 @@ void free_all(mer_backend *b) {
   for (auto &p : b->ep_opened)
     if (p) cudaIpcCloseMemHandle(p), p = nullptr;
   F(b->ep_buf);
+  F(b->d_ep_owner);
   if (b->compute) cudaStreamDestroy(b->compute);
   if (b->copy) cudaStreamDestroy(b->copy);
 }
@@ -1521,6 +1524,14 @@ MER_EXPORT int mer_moe_layer_forward_wait(mer_backend *b, uint32_t slot) {
 namespace {
 size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
 
+// Routed experts of the layer that live on this rank.
+uint32_t ep_local_expert_count(const mer_backend *b, const RouterDev &r) {
+  if (b->ep_owner_host.empty()) return b->ep.experts_per_rank;
+  uint32_t n = 0;
+  for (uint32_t e = r.id_base; e < r.id_base + r.num_experts && e < b->ep_owner_host.size(); e++) n += b->ep_owner_host[e] == b->ep.rank;
+  return n;
+}
+
 // Dispatch over the tokens of all ranks whose routing (filtered to the local experts) is already in the workspace.
 int ep_run_local_experts(mer_backend *b, uint32_t layer, const RouterDev &r, MoeDispatch &d, cudaStream_t s, int *launches) {
   const uint32_t expert = MER_NONE;
@@ -1528,7 +1539,7 @@ int ep_run_local_experts(mer_backend *b, uint32_t layer, const RouterDev &r, Moe
   d.slots = r.top_k + shared;
   d.n_groups = r.num_experts + shared;
   d.max_group_tokens = d.n_tokens;
-  d.active_groups_hint = std::min(b->ep.experts_per_rank + shared, d.n_tokens * d.slots);
+  d.active_groups_hint = std::min(std::max(1u, ep_local_expert_count(b, r) + shared), d.n_tokens * d.slots);
   // of all ranks' pairs, about one in `world` lands on a local expert (the shared expert takes the rank's own tokens)
   d.expected_pairs = std::max<uint32_t>(1u, d.n_tokens * d.slots / b->ep.world);
   bind_ffn(b, d);
@@ -1575,6 +1586,35 @@ MER_EXPORT int mer_ep_init(mer_backend *b, const mer_ep_cfg *cfg) {
 }
 
 MER_EXPORT size_t mer_ep_exchange_bytes(mer_backend *b) { return b && b->ep_on ? b->ep_bytes : 0; }
+
+MER_EXPORT int mer_ep_set_placement(mer_backend *b, const uint16_t *owner, size_t n_ids) {
+  if (!b) return MER_ERR_INVALID_ARGUMENT;
+  const uint32_t layer = 0, expert = MER_NONE;
+  std::lock_guard<std::mutex> lock(b->mu);
+  if (!b->ep_on) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "mer_ep_init has not been called");
+  CU(MER_ERR_SUBMISSION, "cudaSetDevice", cudaSetDevice(b->cfg.device));
+  // layers in flight and captured layer graphs hold the old rule
+  CU(MER_ERR_SUBMISSION, "cudaDeviceSynchronize", cudaDeviceSynchronize());
+  drop_graphs(b);
+  if (!owner || n_ids == 0) {  // back to the contiguous rule
+    b->ep_owner_host.clear();
+    b->ep.owner = nullptr;
+    return MER_OK;
+  }
+  if (n_ids > b->cfg.max_experts)
+    return fail(b, MER_ERR_INVALID_ARGUMENT, layer, expert, "%zu ids, the backend's id space has %u", n_ids, b->cfg.max_experts);
+  for (size_t i = 0; i < n_ids; i++)
+    if (owner[i] >= b->ep.world) return fail(b, MER_ERR_INVALID_ARGUMENT, layer, (uint32_t)i, "owner %u of expert %zu outside the group of %u", owner[i], i, b->ep.world);
+  if (!b->d_ep_owner) CU(MER_ERR_PHYSICAL_CAPACITY, "cudaMalloc(placement table)", cudaMalloc((void **)&b->d_ep_owner, (size_t)b->cfg.max_experts * 2));
+  // ids beyond the table keep the contiguous rule's answer, so that every id the kernels may look up has an entry
+  std::vector<uint16_t> full(b->cfg.max_experts);
+  const uint32_t E = b->ep_cfg.experts_per_layer, epr = b->ep.experts_per_rank;
+  for (uint32_t i = 0; i < b->cfg.max_experts; i++) full[i] = i < n_ids ? owner[i] : (uint16_t)std::min((i % E) / epr, b->ep.world - 1);
+  CU(MER_ERR_UPLOAD, "cudaMemcpy(placement table)", cudaMemcpy(b->d_ep_owner, full.data(), full.size() * 2, cudaMemcpyHostToDevice));
+  b->ep_owner_host = std::move(full);
+  b->ep.owner = b->d_ep_owner;
+  return MER_OK;
+}
 
 MER_EXPORT int mer_ep_export_handle(mer_backend *b, void *handle_out) {
   if (!b) return MER_ERR_INVALID_ARGUMENT;

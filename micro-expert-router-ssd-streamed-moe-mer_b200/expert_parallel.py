@@ -1,4 +1,4 @@
-"""Expert-parallel execution of a MoE layer: one process per GPU, experts split contiguously by id.
+"""Expert-parallel execution of a MoE layer: one process per GPU, experts split contiguously by id or by a placement table.
 
 Stands in for the reference's expert sharding (`ShardRouter`, distributed.rs; docs/distributed.md:16-50:
 the router node computes the full top-k, fans out to the shards that own the experts, sums the
@@ -33,6 +33,22 @@ def expert_owner(local_index, world, experts_per_layer):
     return local_index // experts_per_rank(experts_per_layer, world)
 
 
+def balanced_placement(counts, world):
+    """Placement of one layer's experts by measured popularity: `counts[e]` = tokens expert e received in a
+    calibration batch.  Greedy (largest first, onto the least loaded rank that still has room), every rank gets
+    the same number of experts (ceil(E / world) at most).  Returns owner[e] as a list; deterministic, so every rank
+    that computes it from the same counts gets the same table."""
+    E = len(counts)
+    cap = experts_per_rank(E, world)
+    load, held, owner = [0] * world, [0] * world, [0] * E
+    for e in sorted(range(E), key=lambda i: (-int(counts[i]), i)):
+        r = min((j for j in range(world) if held[j] < cap), key=lambda j: (load[j], j))
+        owner[e] = r
+        load[r] += int(counts[e])
+        held[r] += 1
+    return owner
+
+
 def exchange_handles(handle_bytes, group=None):
     """All ranks' 64-byte handles in rank order (any torch.distributed backend)."""
     import torch.distributed as dist
@@ -58,6 +74,16 @@ class ExpertParallel:
 
     def owns(self, local_index):
         return expert_owner(local_index, self.world, self.experts_per_layer) == self.rank
+
+    def set_placement(self, owner_by_global_id):
+        """Installs owner[global expert id] = rank (the same table on every rank) in place of the contiguous rule;
+        None restores it.  The host admits the experts the table gives this rank."""
+        import numpy as np
+        if owner_by_global_id is None:
+            self.b._check(self.b.lib.mer_ep_set_placement(self.b.h, None, 0))
+            return
+        t = np.ascontiguousarray(owner_by_global_id, dtype=np.uint16)
+        self.b._check(self.b.lib.mer_ep_set_placement(self.b.h, t.ctypes.data_as(C.c_void_p), t.size))
 
     # -- peer mode ------------------------------------------------------------------------
     def export_handle(self):

@@ -22,6 +22,7 @@ import oracle  # noqa: E402
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--mode", choices=["collective", "peer", "a2a", "cpu"], default="collective")
+    ap.add_argument("--placement", choices=["contiguous", "table"], default="contiguous")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     cpu = args.mode == "cpu"
@@ -37,6 +38,11 @@ def main():
     og = oracle.LinearGate(W, E, D, k)
     ref, rids, rw, _ = oracle.moe_layer_forward(dtype, og, blobs, x_all, F, n_threads=2)
     mine = epm.local_expert_range(rank, world, E)
+    owner = None
+    if args.placement == "table":  # neither contiguous nor round-robin, uneven shares; by global expert id
+        owner = np.zeros((layer + 1) * E, np.uint16)
+        owner[layer * E:] = [(e * 7 + e // 3) % world for e in range(E)]
+        mine = [e for e in range(E) if owner[layer * E + e] == rank]
 
     # the handle exchange must return every rank's bytes in rank order, whatever the backend
     fake = bytes([rank]) * 64
@@ -69,6 +75,8 @@ def main():
             b.admit(layer * E + e, 1, blobs[e])
         mer_b200.LinearGate(W, E, D, k).bind(b, layer)
         ep = epm.ExpertParallel(b, rank, world, E, B)
+        if owner is not None:
+            ep.set_placement(owner)
         x = torch.from_numpy(x_all[rank * B:(rank + 1) * B]).to(dev)
         out = torch.empty(B, D, dtype=torch.float32, device=dev)
         stream = torch.cuda.current_stream().cuda_stream

@@ -6,7 +6,7 @@ import sys
 
 import pytest
 
-from mer_b200.expert_parallel import expert_owner, experts_per_rank, local_expert_range
+from mer_b200.expert_parallel import balanced_placement, expert_owner, experts_per_rank, local_expert_range
 
 
 def test_partition_is_contiguous_and_complete():
@@ -19,6 +19,24 @@ def test_partition_is_contiguous_and_complete():
             assert len(rng) <= epr
             seen += list(rng)
         assert seen == list(range(E))
+
+
+def test_balanced_placement_gives_every_rank_the_same_number_of_experts_and_levels_the_load():
+    import numpy as np
+    rng = np.random.default_rng(0)
+    for E, world in [(128, 2), (128, 4), (128, 8), (256, 8), (10, 4)]:
+        counts = (16384 / (rng.permutation(E) + 1.0)).astype(np.int64)  # Zipf(1.0) popularity, shuffled
+        owner = balanced_placement(counts, world)
+        assert len(owner) == E and set(owner) <= set(range(world))
+        held = np.bincount(owner, minlength=world)
+        assert held.max() <= experts_per_rank(E, world) and held.sum() == E
+        load = np.bincount(owner, weights=counts, minlength=world)
+        contiguous = np.array([counts[list(local_expert_range(r, world, E))].sum() for r in range(world)])
+        assert load.max() <= contiguous.max()
+        # never worse than 1.05 x the mean, or the busiest expert together with the least busy ones that fill its rank
+        cap = experts_per_rank(E, world)
+        assert load.max() <= max(counts.max() + np.sort(counts)[:cap - 1].sum(), 1.05 * counts.sum() / world)
+        assert balanced_placement(counts, world) == owner  # deterministic
 
 
 @pytest.mark.timeout(300)

@@ -27,9 +27,18 @@ def rel_rms_err(got, ref):
     return float(np.max(np.abs(np.asarray(got, np.float64) - ref)) / (np.sqrt(np.mean(ref ** 2)) + 1e-30))
 
 
-def make_rank(dtype, E, D, F, k, world, rank, blobs, W, B, layer, shared_blob=None, gate_kw=None, skip=()):
+def scattered_owner(E, world, layer):
+    """A placement table that is neither contiguous nor round-robin, with uneven shares: owner by global expert id."""
+    owner = np.zeros((layer + 1) * E, np.uint16)
+    owner[layer * E:] = [(e * 7 + e // 3) % world for e in range(E)]
+    return owner
+
+
+def make_rank(dtype, E, D, F, k, world, rank, blobs, W, B, layer, shared_blob=None, gate_kw=None, skip=(), owner=None):
     """A backend that holds only rank's experts of `layer` (+ the shared expert)."""
     mine = [e for e in local_expert_range(rank, world, E) if e not in skip]
+    if owner is not None:
+        mine = [e for e in range(E) if owner[layer * E + e] == rank and e not in skip]
     stride = (256 + mer_b200.expert_bytes(dtype, D, F) + 4095) // 4096 * 4096
     slots = k + (1 if shared_blob is not None else 0)
     b = mer_b200.Backend(dtype, D, F, stride * (len(mine) + 2), (layer + 1) * E + 1, max_tokens=B * world, max_top_k=slots)
@@ -41,12 +50,16 @@ def make_rank(dtype, E, D, F, k, world, rank, blobs, W, B, layer, shared_blob=No
         b.admit(shared_id, 1, shared_blob)
     gate = mer_b200.LinearGate.with_routing(W, E, D, k, *gate_kw) if gate_kw else mer_b200.LinearGate(W, E, D, k)
     gate.bind(b, layer, shared_expert_id=shared_id)
-    return b, ExpertParallel(b, rank, world, E, B)
+    ep = ExpertParallel(b, rank, world, E, B)
+    if owner is not None:
+        ep.set_placement(owner)
+    return b, ep
 
 
+@pytest.mark.parametrize("placement", ["contiguous", "table"])
 @pytest.mark.parametrize("world", [1, 2, 4])
 @pytest.mark.parametrize("case", ["q8-16x4", "q4-32x4-shared"])
-def test_collective_mode_ranks_in_turn_match_the_oracle(world, case):
+def test_collective_mode_ranks_in_turn_match_the_oracle(world, case, placement):
     if case == "q8-16x4":
         dtype, E, D, F, k, B, layer, shared, gate_kw, ogate_kw = oracle.Q8_0, 16, 256, 256, 4, 6, 1, False, None, {}
     else:
@@ -60,7 +73,9 @@ def test_collective_mode_ranks_in_turn_match_the_oracle(world, case):
     x_all = synth.make_activations(T, D, 61)
     slots = k + int(shared)
     dev = torch.device("cuda:0")
-    ranks = [make_rank(dtype, E, D, F, k, world, r, blobs, W, B, layer, blobs[E] if shared else None, gate_kw) for r in range(world)]
+    owner = scattered_owner(E, world, layer) if placement == "table" else None
+    ranks = [make_rank(dtype, E, D, F, k, world, r, blobs, W, B, layer, blobs[E] if shared else None, gate_kw, owner=owner)
+             for r in range(world)]
     try:
         # every rank routes its own tokens; "all-gather" = concatenation in rank order
         ids_parts, w_parts = [], []
@@ -222,12 +237,13 @@ def test_ep_argument_validation():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("placement", ["contiguous", "table"])
 @pytest.mark.parametrize("mode", ["collective", "peer", "a2a"])
-def test_two_processes_two_gpus(mode):
+def test_two_processes_two_gpus(mode, placement):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29631", os.path.join(root, "tests", "ep_worker.py"), "--mode", mode]
+           "--master-port", "29631", os.path.join(root, "tests", "ep_worker.py"), "--mode", mode, "--placement", placement]
     r = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "EP-WORKER-OK" in r.stdout
