@@ -158,20 +158,30 @@ __global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, const uint32_t *__
   for (uint32_t i4 = threadIdx.x; i4 < D / 4; i4 += blockDim.x) {
     float4 acc = make_float4(0, 0, 0, 0);
     if (s_ok) {
-      for (uint32_t sl = 0; sl <= slots; sl++) {
-        if (residual && sl == min(ep.top_k, slots)) {  // hidden + routed sum, before the shared expert's slot
-          const float4 r = __ldg(reinterpret_cast<const float4 *>(residual) + (size_t)t * (D / 4) + i4);
-          acc.x = __fadd_rn(r.x, acc.x), acc.y = __fadd_rn(r.y, acc.y), acc.z = __fadd_rn(r.z, acc.z), acc.w = __fadd_rn(r.w, acc.w);
+      // eight slots at a time: all their (mostly remote) loads are issued before the first one is consumed; the sum
+      // itself stays in slot order
+      for (uint32_t s0 = 0; s0 <= slots; s0 += 8) {
+        float4 y[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const float *row = s0 + j < slots ? s_row[s0 + j] : nullptr;
+          y[j] = row ? __ldcg(reinterpret_cast<const float4 *>(row) + i4) : make_float4(0, 0, 0, 0);
         }
-        if (sl == slots) break;
-        const float *row = s_row[sl];
-        if (!row) continue;
-        const float wt = s_w[sl];
-        const float4 y = __ldcg(reinterpret_cast<const float4 *>(row) + i4);
-        acc.x = __fadd_rn(acc.x, __fmul_rn(wt, y.x));
-        acc.y = __fadd_rn(acc.y, __fmul_rn(wt, y.y));
-        acc.z = __fadd_rn(acc.z, __fmul_rn(wt, y.z));
-        acc.w = __fadd_rn(acc.w, __fmul_rn(wt, y.w));
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const uint32_t sl = s0 + j;
+          if (sl > slots) break;
+          if (residual && sl == min(ep.top_k, slots)) {  // hidden + routed sum, before the shared expert's slot
+            const float4 r = __ldg(reinterpret_cast<const float4 *>(residual) + (size_t)t * (D / 4) + i4);
+            acc.x = __fadd_rn(r.x, acc.x), acc.y = __fadd_rn(r.y, acc.y), acc.z = __fadd_rn(r.z, acc.z), acc.w = __fadd_rn(r.w, acc.w);
+          }
+          if (sl == slots || !s_row[sl]) continue;
+          const float wt = s_w[sl];
+          acc.x = __fadd_rn(acc.x, __fmul_rn(wt, y[j].x));
+          acc.y = __fadd_rn(acc.y, __fmul_rn(wt, y[j].y));
+          acc.z = __fadd_rn(acc.z, __fmul_rn(wt, y[j].z));
+          acc.w = __fadd_rn(acc.w, __fmul_rn(wt, y[j].w));
+        }
       }
     }
     reinterpret_cast<float4 *>(out)[(size_t)t * (D / 4) + i4] = acc;
