@@ -94,8 +94,11 @@ struct EpDev {
 cudaError_t launch_ep_filter(const EpDev &ep, const uint32_t *ids_all, const float *w_all, uint32_t n_pairs, uint32_t slots,
                              uint32_t *pair_expert, float *pair_weight, cudaStream_t s, int *launches);
 // `epoch_counter`: device word, advanced by one by the signal kernel each of these launches starts with.
+// `group_count` non-null: the kernel also counts the local pairs per group (n_routed = routed experts of the layer), which
+// is the grouping kernels' first step (launch_groups_layer with `counted`).
 cudaError_t launch_ep_gather(const EpDev &ep, uint32_t *epoch_counter, uint32_t D, uint32_t slots, float *x_all, uint32_t *pair_expert,
-                             float *pair_weight, uint32_t *status, cudaStream_t s, int *launches);
+                             float *pair_weight, uint32_t *status, uint32_t *group_count, uint32_t n_routed, cudaStream_t s,
+                             int *launches);
 cudaError_t launch_ep_combine(const EpDev &ep, uint32_t *epoch_counter, uint32_t D, uint32_t slots, const uint32_t *ids, const float *w,
                               const float *residual, float *out, uint32_t *status, cudaStream_t s, int *launches);
 
@@ -109,7 +112,9 @@ cudaError_t launch_a2a_combine(uint32_t n_tokens, uint32_t D, uint32_t slots, ui
 
 // kernels_generic.cu
 // Groups pairs by expert for a whole layer whose routing is already in d.pair_expert (+ pass table).
-cudaError_t launch_groups_layer(const RouterDev &r, const MoeDispatch &d, cudaStream_t s, int *launches);
+// `counted`: the pairs per group are already in d.group_count (only honoured when groups_layer_on_grid(d)).
+bool groups_layer_on_grid(const MoeDispatch &d);
+cudaError_t launch_groups_layer(const RouterDev &r, const MoeDispatch &d, cudaStream_t s, int *launches, bool counted = false);
 // group = false: route only (the caller groups later, e.g. after gathering other ranks' tokens)
 cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max_tokens, cudaStream_t s, int *launches,
                           bool group = true);

@@ -85,7 +85,8 @@ __global__ void k_ep_signal(EpDev ep, uint32_t *epoch_counter) {
 // x rows only for tokens with at least one local pair.  One CTA per (source rank, token).
 __global__ void __launch_bounds__(256) k_ep_gather(EpDev ep, const uint32_t *__restrict__ epoch_counter, uint32_t D, uint32_t slots,
                                                    float *__restrict__ x_all, uint32_t *__restrict__ pair_expert,
-                                                   float *__restrict__ pair_weight, uint32_t *status) {
+                                                   float *__restrict__ pair_weight, uint32_t *status, uint32_t *group_count,
+                                                   uint32_t n_routed) {
   const uint32_t src = blockIdx.y, t = blockIdx.x;
   __shared__ int s_ok, s_any;
   const uint32_t epoch = __ldcg(epoch_counter);  // set by the signal kernel in front of this one
@@ -108,7 +109,11 @@ __global__ void __launch_bounds__(256) k_ep_gather(EpDev ep, const uint32_t *__r
     const bool local = pair_is_local(ep, e, threadIdx.x, src);
     pair_expert[tg * slots + threadIdx.x] = local ? e : MER_NONE;
     pair_weight[tg * slots + threadIdx.x] = local ? 1.0f : 0.0f;
-    if (local) s_any = 1;
+    if (local) {
+      s_any = 1;
+      // the grouping kernels' count step, done here: group = local expert index, or the shared-expert group
+      if (group_count) atomicAdd(group_count + (threadIdx.x >= ep.top_k ? n_routed : e - ep.id_base), 1u);
+    }
   }
   __syncthreads();
   if (!s_any) return;
@@ -265,10 +270,11 @@ cudaError_t launch_ep_filter(const EpDev &ep, const uint32_t *ids_all, const flo
 }
 
 cudaError_t launch_ep_gather(const EpDev &ep, uint32_t *epoch_counter, uint32_t D, uint32_t slots, float *x_all, uint32_t *pair_expert,
-                             float *pair_weight, uint32_t *status, cudaStream_t s, int *launches) {
+                             float *pair_weight, uint32_t *status, uint32_t *group_count, uint32_t n_routed, cudaStream_t s,
+                             int *launches) {
   k_ep_signal<<<1, 32, 0, s>>>(ep, epoch_counter);  // this rank's tokens and routing are published
   dim3 grid(ep.tokens_per_rank, ep.world);
-  k_ep_gather<<<grid, 256, 0, s>>>(ep, epoch_counter, D, slots, x_all, pair_expert, pair_weight, status);
+  k_ep_gather<<<grid, 256, 0, s>>>(ep, epoch_counter, D, slots, x_all, pair_expert, pair_weight, status, group_count, n_routed);
   if (launches) (*launches) += 2;
   return cudaGetLastError();
 }

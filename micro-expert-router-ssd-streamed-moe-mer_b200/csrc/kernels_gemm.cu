@@ -569,6 +569,26 @@ __global__ void __launch_bounds__(256) k_row_amax(const float *__restrict__ x, u
   if (lane == 0) amax[tok] = nan ? 0x7fc00000u : __float_as_uint(mx);
 }
 
+// Row maxima of the grouped rows of h only (perm lists them): in an expert-parallel dispatch most pairs belong to other
+// ranks and their rows of h are never written or read.
+__global__ void __launch_bounds__(256) k_row_amax_grouped(MoeDispatch d, const float *__restrict__ h, uint32_t K, uint32_t *__restrict__ amax) {
+  const uint32_t i = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (i >= d.offsets[d.n_groups]) return;
+  const uint32_t pair = d.perm[i];
+  const float4 *r4 = reinterpret_cast<const float4 *>(h + (size_t)pair * K);
+  float mx = 0.0f;
+  bool nan = false;
+  for (uint32_t k = lane; k < K / 4; k += 32) {
+    const float4 v = __ldg(r4 + k);
+    nan |= (v.x != v.x) | (v.y != v.y) | (v.z != v.z) | (v.w != v.w);
+    mx = fmaxf(fmaxf(fmaxf(fmaxf(mx, fabsf(v.x)), fabsf(v.y)), fabsf(v.z)), fabsf(v.w));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  nan = __any_sync(0xffffffffu, nan);
+  if (lane == 0) amax[pair] = nan ? 0x7fc00000u : __float_as_uint(mx);
+}
+
 // Builds, for every token pass, the activation operand images the GEMM kernel copies chunk by chunk.  A chunk is 64
 // values of K = 8 core-matrix columns; a column holds the pass's rows as 16-byte pieces, the f16 hi parts of all rows
 // first, then the lo parts (+32 B skew): [hi row 0 .. hi row w-1 | lo row 0 .. lo row w-1], w = the pass's width
@@ -713,7 +733,7 @@ cudaError_t launch_ffn_gemm(MoeDispatch &d, void *gemm_scratch_ptr, size_t gemm_
     if (phase == 0) {
       // row maxima of h = SiLU(gate) * up, the scale source of the down phase's operand image (the GEMM epilogue does
       // not collect them: a warp reduction per column sat on its critical path)
-      k_row_amax<<<(P + 7) / 8, 256, 0, s>>>(d.h, P, d.F, d.amax);
+      k_row_amax_grouped<<<(P + 7) / 8, 256, 0, s>>>(d, d.h, d.F, d.amax);
       if (ev_mid) cudaEventRecord(ev_mid, s);
     }
   }

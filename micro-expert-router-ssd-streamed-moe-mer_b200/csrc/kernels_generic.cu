@@ -1064,15 +1064,17 @@ cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max
   return cudaGetLastError();
 }
 
-cudaError_t launch_groups_layer(const RouterDev &r, const MoeDispatch &d, cudaStream_t s, int *launches) {
+bool groups_layer_on_grid(const MoeDispatch &d) { return d.n_tokens * d.slots >= GRID_GROUPING_PAIRS && d.group_count != nullptr; }
+
+cudaError_t launch_groups_layer(const RouterDev &r, const MoeDispatch &d, cudaStream_t s, int *launches, bool counted) {
   const uint32_t G = d.n_groups, P = d.n_tokens * d.slots;
-  if (P >= GRID_GROUPING_PAIRS && d.group_count != nullptr) {  // a large dispatch: count / scan / scatter over the grid
+  if (groups_layer_on_grid(d)) {  // a large dispatch: count / scan / scatter over the grid
     const unsigned blocks = (P + 1023) / 1024;
-    k_group_count<<<blocks, 256, 0, s>>>(r, d);
+    if (!counted) k_group_count<<<blocks, 256, 0, s>>>(r, d);
     k_group_scan<<<1, 256, 0, s>>>(r, d);
     k_group_scatter<<<blocks, 256, 0, s>>>(r, d);
     k_group_clear<<<1, 256, 0, s>>>(d);
-    if (launches) (*launches) += 4;
+    if (launches) (*launches) += counted ? 3 : 4;
     return cudaGetLastError();
   }
   size_t smem = (size_t)(G + 1 + (G <= STABLE_G ? ROUTER_ROWS * G : G) + (P <= SMALL_P ? P : 0)) * 4;

@@ -1533,7 +1533,7 @@ uint32_t ep_local_expert_count(const mer_backend *b, const RouterDev &r) {
 }
 
 // Dispatch over the tokens of all ranks whose routing (filtered to the local experts) is already in the workspace.
-int ep_run_local_experts(mer_backend *b, uint32_t layer, const RouterDev &r, MoeDispatch &d, cudaStream_t s, int *launches) {
+int ep_run_local_experts(mer_backend *b, uint32_t layer, const RouterDev &r, MoeDispatch &d, cudaStream_t s, int *launches, bool counted = false) {
   const uint32_t expert = MER_NONE;
   const uint32_t shared = r.shared_expert_id != MER_NONE ? 1u : 0u;
   d.slots = r.top_k + shared;
@@ -1543,7 +1543,7 @@ int ep_run_local_experts(mer_backend *b, uint32_t layer, const RouterDev &r, Moe
   // of all ranks' pairs, about one in `world` lands on a local expert (the shared expert takes the rank's own tokens)
   d.expected_pairs = std::max<uint32_t>(1u, d.n_tokens * d.slots / b->ep.world);
   bind_ffn(b, d);
-  CU(MER_ERR_SUBMISSION, "group kernel", launch_groups_layer(r, d, s, launches));
+  CU(MER_ERR_SUBMISSION, "group kernel", launch_groups_layer(r, d, s, launches, counted));
   CU(MER_ERR_SUBMISSION, "expert FFN kernels", run_ffn(b, d, s, launches));
   return MER_OK;
 }
@@ -1784,10 +1784,13 @@ int ep_enqueue(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens
   d.x = b->d_x;
   d.y = y_pub;
   d.out = d_out;
+  d.slots = slots;
+  const bool counted = groups_layer_on_grid(d);  // a large dispatch: the gather kernel does the grouping's count step
   CU(MER_ERR_SUBMISSION, "gather kernel",
-     launch_ep_gather(ep, epoch_counter, (uint32_t)D, slots, b->d_x, d.pair_expert, d.pair_weight, b->d_status, s, &launches));
+     launch_ep_gather(ep, epoch_counter, (uint32_t)D, slots, b->d_x, d.pair_expert, d.pair_weight, b->d_status,
+                      counted ? d.group_count : nullptr, r.num_experts, s, &launches));
   d.fuse_reduce = 1;  // the peers read final per-pair outputs, and only those of the local experts exist
-  int rc = ep_run_local_experts(b, layer, r, d, s, &launches);
+  int rc = ep_run_local_experts(b, layer, r, d, s, &launches, counted);
   if (rc) return rc;
   CU(MER_ERR_SUBMISSION, "partial-sum kernel", launch_reduce_parts(d, s, &launches));
   // weighted sum in slot order, every pair's output read from the rank that owns its expert
