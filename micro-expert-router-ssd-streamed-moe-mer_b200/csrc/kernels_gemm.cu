@@ -10,17 +10,19 @@
 //     owns one weight row), from where the MMA reads its A operand.  Eight A stages live in TMEM beside
 //     the two accumulators.
 //   * B is the activation tile as f16 hi + lo parts (22 significant bits after an exact power-of-two
-//     per-row scaling), laid out in the K-major no-swizzle core-matrix order by k_gemm_act_image and
-//     fetched with one bulk copy per 64 values of K into a five-stage shared-memory ring.
-//   * Three MMAs per 16 values of K (hi*hi, hi*lo, lo*hi; lo*lo is below fp32 resolution) accumulate
-//     in fp32 in TMEM, so the result matches the fp32 reference to ~1e-6 instead of f16's 1e-3.
-//   * Warp roles: 0 = producer of the activation stages, 1 = MMA issuer (one elected lane) and TMEM owner,
+//     per-row scaling), laid out in the K-major no-swizzle core-matrix order by k_gemm_act_image (per core-matrix
+//     column of K the hi pieces of the pass's rows, then the lo pieces; as wide as the pass, not as the widest one)
+//     and fetched with one bulk copy per 64 values of K, two per stage, into a two-stage shared-memory ring.
+//   * Three products per 16 values of K (hi*hi, hi*lo, lo*hi; lo*lo is below fp32 resolution) accumulate
+//     in fp32 in TMEM, so the result matches the fp32 reference to ~1e-4 of the output RMS instead of f16's 2e-3.
+//     A group of at most 64 tokens issues them as two instructions: W_hi * [x_hi | x_lo] with twice the width
+//     (two column sets of the accumulator, added in the epilogue) and W_lo * x_hi.
+//   * Warp roles: 0 = producer of the activation stages, 1 = MMA issuer (one elected lane issues predicated
+//     instructions; every operand is computed in uniform registers) and TMEM owner,
 //     2..9 = epilogue (four warps per accumulator buffer: tcgen05.ld, un-scaling, SiLU(gate)*up or plain store; two
 //     buffers let the epilogue of one item overlap the MMAs of the next two),
 //     10..17 = dequantisers (a warp reaches the 32 TMEM lanes of its quarter; the two warps of a quarter
-//     take alternate blocks).  Each dequantiser warp also issues the bulk copy of one of the eight packed
-//     tiles of every weight stage: issuing a bulk copy occupies a thread for ~100 cycles, and one producer
-//     warp issuing all ten copies of a group was what the whole pipeline waited for (clock64 probes).
+//     take alternate blocks), 18 = producer of the weight stages (lanes 0..7 copy one packed tile each).
 // Every wait is bounded; on expiry the CTA latches MER_DEVSTAT_TIMEOUT, stops issuing work, waits
 // (bounded) for its copies and MMAs in flight, frees its TMEM and returns.
 #include <cuda_fp16.h>
