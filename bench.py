@@ -770,6 +770,21 @@ def main():
             local = {l * cfg.num_experts + e for e in mine[l]}
             hit = [e for e in np.unique(ids[ids != 0xFFFFFFFF]) if int(e) in local]
             hit_bytes.append((len(hit) + (1 if cfg.shared else 0)) * exp_bytes)
+    ep_stages = None
+    if mode == "ep-peer":
+        # where a rank's layer time goes (plain launches with events between the stages; every rank runs the same steps):
+        # router_gate = router + publish + signal + gather (with its wait for the peers) + grouping, combine = signal +
+        # wait for the peers + pull
+        barrier()
+        be.stage_timing_enable(True)
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        t = be.stage_timings()
+        be.stage_timing_enable(False)
+        mine_ms = {k: round(v / max(t["samples"], 1), 4) for k, v in t.items() if k != "samples"}
+        ep_stages = [None] * world
+        dist.all_gather_object(ep_stages, mine_ms)
 
     # ---- end to end: host buffers in, host buffers out, copies inside the timed region
     e2e_ms = e2e_sync_ms = None
@@ -910,6 +925,8 @@ def main():
         line["sweep"] = run_sweep(mer_b200, synth, oracle, args, stack, local_rank, peaks, threads)
     elif stack is not None:
         stack.close()
+    if ep_stages is not None:
+        line["stage_ms_per_rank"] = ep_stages
     if ep_extra is not None:
         line["sweep"] = ep_extra
     json_out.write(json.dumps(line) + "\n")

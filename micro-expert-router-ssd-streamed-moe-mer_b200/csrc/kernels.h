@@ -25,6 +25,8 @@ struct RouterDev {
   const float *shared_scale;  // [n_tokens] mixing weight of the shared expert (its sigmoid gate scalar), or null = 1
 };
 
+#define MER_EP_MAX_WORLD 16
+
 // One MoE dispatch: P = n_tokens * slots pairs (token, slot); pair p belongs to token p / slots.
 // Pairs are grouped by expert: group g covers perm[offsets[g] .. offsets[g+1]) and runs expert
 // group_expert[g].
@@ -73,11 +75,25 @@ struct MoeDispatch {
   // in that order (add_residual after the routed sum, then the shared expert: model.rs:2742-2763).
   const float *residual;    // [n_tokens x D] or null
   uint32_t routed_slots;    // slots below this index are routed experts (used with `residual`)
+  // Expert-parallel push (push_tokens_per_rank > 0): tokens are numbered over all ranks, rank j brought tokens
+  // [j * tpr, (j + 1) * tpr), and the output of pair (token, slot) belongs in the per-pair output region of the token's
+  // home rank, row (token % tpr) * slots + slot.  The GEMM kernels' down epilogue stores there directly (peer stores
+  // over NVLink while the tile's successors are still being multiplied); other kernel families write `y` and a copy
+  // kernel moves the rows.
+  uint8_t *push_y[MER_EP_MAX_WORLD];
+  uint32_t push_tokens_per_rank;
 };
+
+// Where the down projection's output row of pair p goes.
+__device__ __forceinline__ float *pair_output_row(const MoeDispatch &d, float *y, uint32_t pair) {
+  if (d.push_tokens_per_rank == 0) return y + (size_t)pair * d.D;
+  const uint32_t tok = pair / d.slots, sl = pair - tok * d.slots;
+  const uint32_t home = tok / d.push_tokens_per_rank, t = tok - home * d.push_tokens_per_rank;
+  return reinterpret_cast<float *>(d.push_y[home]) + ((size_t)t * d.slots + sl) * d.D;
+}
 
 // Expert-parallel view of one rank: where every rank's exchange buffer is mapped and how experts
 // and tokens are partitioned.  Offsets are the same on every rank.
-#define MER_EP_MAX_WORLD 16
 struct EpDev {
   uint8_t *peer[MER_EP_MAX_WORLD];  // exchange buffer of rank j as mapped here (own buffer at [rank])
   uint32_t rank, world;
@@ -101,6 +117,8 @@ cudaError_t launch_ep_gather(const EpDev &ep, uint32_t *epoch_counter, uint32_t 
                              int *launches);
 cudaError_t launch_ep_combine(const EpDev &ep, uint32_t *epoch_counter, uint32_t D, uint32_t slots, const uint32_t *ids, const float *w,
                               const float *residual, float *out, uint32_t *status, cudaStream_t s, int *launches);
+// Copies the per-pair output rows of the grouped (= local) pairs from d.y to their tokens' home ranks (d.push_*).
+cudaError_t launch_ep_push_rows(const MoeDispatch &d, cudaStream_t s, int *launches);
 
 // NCCL all-to-all mode: pack every pair into the send segment of its expert's owner (segment d = rows [d * seg_rows, ...),
 // cursors[d] counts its rows, pos[p] = row the pair went to); combine from the rows that came back.

@@ -122,8 +122,9 @@ __global__ void __launch_bounds__(256) k_ep_gather(EpDev ep, const uint32_t *__r
   for (uint32_t i = threadIdx.x; i < D / 4; i += blockDim.x) dst[i] = __ldcg(srcx + i);
 }
 
-// (2c) out[t] = sum over slots, in slot order, of weight * y, where y of a pair is read from the
-// exchange buffer of the rank that owns the pair's expert (same order and rounding as k_combine).
+// (2c) out[t] = sum over slots, in slot order, of weight * y (same order and rounding as k_combine).  The rank that
+// owns a pair's expert has pushed y into this rank's exchange buffer, row (token, slot); the kernel waits for every
+// rank's flag (raised after its expert launches) and then reads local memory only.
 // One CTA per token, a thread four consecutive values.
 __global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, const uint32_t *__restrict__ epoch_counter, uint32_t D, uint32_t slots,
                                                     const uint32_t *__restrict__ ids, const float *__restrict__ w,
@@ -145,17 +146,14 @@ __global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, const uint32_t *__
       if (!ok) atomicOr(status, MER_DEVSTAT_TIMEOUT);
     }
   }
-  // where each slot's row lives (null = skipped slot), resolved once per token
-  const uint32_t tg = ep.rank * ep.tokens_per_rank + t;
+  // where each slot's row lives (null = skipped slot), resolved once per token: the owners of the experts pushed the
+  // rows into this rank's own buffer
   if (threadIdx.x >= 32 && threadIdx.x < 32 + slots && threadIdx.x < 96) {
     const uint32_t sl = threadIdx.x - 32;
     const uint32_t e = ids[t * slots + sl];
     const float wt = w[t * slots + sl];
     const float *row = nullptr;
-    if (e != MER_NONE && wt != 0.0f) {
-      const uint32_t owner = sl >= ep.top_k ? ep.rank : expert_owner(ep, e);
-      row = reinterpret_cast<const float *>(ep.peer[owner] + ep.off_y) + ((size_t)tg * slots + sl) * D;
-    }
+    if (e != MER_NONE && wt != 0.0f) row = reinterpret_cast<const float *>(ep.peer[ep.rank] + ep.off_y) + ((size_t)t * slots + sl) * D;
     s_row[sl] = row;
     s_w[sl] = wt;
   }
@@ -191,6 +189,17 @@ __global__ void __launch_bounds__(256) k_ep_combine(EpDev ep, const uint32_t *__
     }
     reinterpret_cast<float4 *>(out)[(size_t)t * (D / 4) + i4] = acc;
   }
+}
+
+// (2d) Kernel families that leave the per-pair outputs in the local array: one CTA per grouped pair copies its row to
+// the token's home rank.
+__global__ void __launch_bounds__(256) k_ep_push_rows(MoeDispatch d) {
+  const uint32_t i = blockIdx.x;
+  if (i >= d.offsets[d.n_groups]) return;
+  const uint32_t pair = d.perm[i];
+  const float4 *src = reinterpret_cast<const float4 *>(d.y + (size_t)pair * d.D);
+  float4 *dst = reinterpret_cast<float4 *>(pair_output_row(d, nullptr, pair));
+  for (uint32_t k = threadIdx.x; k < d.D / 4; k += blockDim.x) dst[k] = __ldcg(src + k);
 }
 
 // (3a) One warp per (token, slot) pair: claim the next row of the owner's send segment, copy the token's row and the
@@ -258,6 +267,12 @@ cudaError_t launch_a2a_pack(const EpDev &ep, uint32_t D, uint32_t slots, uint32_
 cudaError_t launch_a2a_combine(uint32_t n_tokens, uint32_t D, uint32_t slots, uint32_t routed_slots, const uint32_t *pos, const float *w,
                                const float *ret_y, const float *residual, float *out, cudaStream_t s, int *launches) {
   k_a2a_combine<<<n_tokens, 256, 0, s>>>(D, slots, routed_slots, pos, w, ret_y, residual, out);
+  if (launches) (*launches)++;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_push_rows(const MoeDispatch &d, cudaStream_t s, int *launches) {
+  k_ep_push_rows<<<d.n_tokens * d.slots, 256, 0, s>>>(d);
   if (launches) (*launches)++;
   return cudaGetLastError();
 }

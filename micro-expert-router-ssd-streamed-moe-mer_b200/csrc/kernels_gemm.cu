@@ -40,7 +40,7 @@ constexpr int G_WARPS = 19, G_THREADS = G_WARPS * 32;
 constexpr int W_PRODUCER = 0, W_MMA = 1, W_EPI0 = 2, W_DQ0 = 10, W_WEIGHTS = 18;
 constexpr int EPI_WARPS = 4, DQ_WARPS = 8;  // EPI_WARPS per accumulator
 constexpr uint32_t RAW_BLOCKS = 4;       // blocks of K per weight stage (per packed tile: one bulk copy)
-constexpr uint32_t G_HEADER = 4096;      // mbarriers, TMEM base, and from byte 1024 the epilogue groups' per-pass tables
+constexpr uint32_t G_HEADER = 5120;      // mbarriers, TMEM base, and from byte 1024 the epilogue groups' per-pass tables (2 KB each)
 constexpr uint32_t TMEM_COLS = 512;      // [0, 256): two accumulator buffers of up to 128 columns; [256, 512): A stages
 constexpr uint32_t TMEM_A0 = 256, A_STAGES = 8, A_STAGE_COLS = 32;  // a stage = one block: 16 columns hi + 16 columns lo
 constexpr uint32_t MAX_RING = 8;
@@ -452,8 +452,9 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
     const uint32_t q = warp & 3;         // a warp reads the TMEM lanes 32 * (warp % 4) ..
     const uint32_t row = q * 32 + lane;  // row of the item's 128-row tile
     const uint32_t buf = (warp - W_EPI0) >> 2, gw = (warp - W_EPI0) & 3;  // group, warp within the group
-    uint32_t *s_pair = reinterpret_cast<uint32_t *>(smem + 1024 + buf * 1024);
-    float *s_un = reinterpret_cast<float *>(smem + 1024 + buf * 1024 + 512);
+    uint32_t *s_pair = reinterpret_cast<uint32_t *>(smem + 1024 + buf * 2048);
+    float *s_un = reinterpret_cast<float *>(smem + 1024 + buf * 2048 + 512);
+    float **s_row = reinterpret_cast<float **>(smem + 1024 + buf * 2048 + 1024);  // down phase: each token's output row
     uint32_t n_item = 0, used = 0;  // resident items seen by the CTA; uses of this group's buffer
     // A group whose bounded wait expired goes "dead": it stops touching TMEM and waiting but keeps walking the items, so
     // that the group's named barriers always see all four warps.
@@ -477,6 +478,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
         const float un = have ? __ldg(p.unscale + (size_t)pass * p.bn + c) : 0.0f;
         asm volatile("bar.sync %0, 128;" ::"r"(1 + buf) : "memory");  // the group has finished reading the previous item's tables
         s_pair[c] = pr, s_un[c] = un;
+        if (p.phase == 1) s_row[c] = have ? pair_output_row(d, p.out, pr) : nullptr;
         asm volatile("bar.sync %0, 128;" ::"r"(1 + buf) : "memory");
       }
       if (resident && !dead) {
@@ -530,10 +532,10 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
           for (int i = 0; i < 32; i++)
             if (is_gate && cbase + i < pcount) dst[(size_t)s_pair[cbase + i] * d.F] = val[i];
         } else {
-          float *dst = p.out + mt * 128 + row;
+          const uint32_t off = mt * 128 + row;
 #pragma unroll
           for (int i = 0; i < 32; i++)
-            if (cbase + i < pcount) dst[(size_t)s_pair[cbase + i] * d.D] = val[i];
+            if (cbase + i < pcount) s_row[cbase + i][off] = val[i];
         }
       }
       if (resident && !dead) {

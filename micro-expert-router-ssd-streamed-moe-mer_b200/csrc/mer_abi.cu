@@ -1533,7 +1533,8 @@ uint32_t ep_local_expert_count(const mer_backend *b, const RouterDev &r) {
 }
 
 // Dispatch over the tokens of all ranks whose routing (filtered to the local experts) is already in the workspace.
-int ep_run_local_experts(mer_backend *b, uint32_t layer, const RouterDev &r, MoeDispatch &d, cudaStream_t s, int *launches, bool counted = false) {
+int ep_run_local_experts(mer_backend *b, uint32_t layer, const RouterDev &r, MoeDispatch &d, cudaStream_t s, int *launches, bool counted = false,
+                         cudaEvent_t *ev = nullptr) {
   const uint32_t expert = MER_NONE;
   const uint32_t shared = r.shared_expert_id != MER_NONE ? 1u : 0u;
   d.slots = r.top_k + shared;
@@ -1544,7 +1545,8 @@ int ep_run_local_experts(mer_backend *b, uint32_t layer, const RouterDev &r, Moe
   d.expected_pairs = std::max<uint32_t>(1u, d.n_tokens * d.slots / b->ep.world);
   bind_ffn(b, d);
   CU(MER_ERR_SUBMISSION, "group kernel", launch_groups_layer(r, d, s, launches, counted));
-  CU(MER_ERR_SUBMISSION, "expert FFN kernels", run_ffn(b, d, s, launches));
+  if (ev) cudaEventRecord(ev[1], s);
+  CU(MER_ERR_SUBMISSION, "expert FFN kernels", run_ffn(b, d, s, launches, ev ? ev[2] : nullptr));
   return MER_OK;
 }
 }  // namespace
@@ -1754,9 +1756,12 @@ int ep_enqueue(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens
   float *x_pub = reinterpret_cast<float *>(b->ep_buf + ep.off_x);
   uint32_t *ids_pub = reinterpret_cast<uint32_t *>(b->ep_buf + ep.off_ids);
   float *w_own = reinterpret_cast<float *>(b->ep_buf + b->ep_off_w);
-  float *y_pub = reinterpret_cast<float *>(b->ep_buf + ep.off_y);
   // the epoch the flags carry lives in device memory and advances by one per signal: the same launch sequence can be replayed
   uint32_t *epoch_counter = reinterpret_cast<uint32_t *>(b->ep_buf + 128);
+  // stage timers (plain launches only): router_gate = router + publish + signal + gather (with its wait for the peers) +
+  // grouping; gate/up and down as on one GPU; combine = signal + wait for the peers + pull
+  cudaEvent_t *ev = capturing ? nullptr : next_timing_set(b);
+  if (ev) cudaEventRecord(ev[0], s);
 
   CU(MER_ERR_SUBMISSION, "cudaMemsetAsync(status)", cudaMemsetAsync(b->d_status, 0, 4, s));
   if (!capturing) CU(MER_ERR_SUBMISSION, "wait for uploads", order_after_copies(b, s));
@@ -1782,21 +1787,27 @@ int ep_enqueue(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens
   MoeDispatch d = base_dispatch(b);
   d.n_tokens = (uint32_t)(n_tokens * ep.world);
   d.x = b->d_x;
-  d.y = y_pub;
   d.out = d_out;
+  // per-pair outputs go to the home rank of their token: the GEMM kernels' down epilogue stores them there, the other
+  // kernel families fill the local array (d.y) and a copy kernel moves the rows
+  for (uint32_t j = 0; j < ep.world; j++) d.push_y[j] = ep.peer[j] + ep.off_y;
+  d.push_tokens_per_rank = (uint32_t)n_tokens;
   d.slots = slots;
   const bool counted = groups_layer_on_grid(d);  // a large dispatch: the gather kernel does the grouping's count step
   CU(MER_ERR_SUBMISSION, "gather kernel",
      launch_ep_gather(ep, epoch_counter, (uint32_t)D, slots, b->d_x, d.pair_expert, d.pair_weight, b->d_status,
                       counted ? d.group_count : nullptr, r.num_experts, s, &launches));
   d.fuse_reduce = 1;  // the peers read final per-pair outputs, and only those of the local experts exist
-  int rc = ep_run_local_experts(b, layer, r, d, s, &launches, counted);
+  int rc = ep_run_local_experts(b, layer, r, d, s, &launches, counted, ev);
   if (rc) return rc;
   CU(MER_ERR_SUBMISSION, "partial-sum kernel", launch_reduce_parts(d, s, &launches));
+  if (!d.gemm_bn) CU(MER_ERR_SUBMISSION, "push kernel", launch_ep_push_rows(d, s, &launches));
+  if (ev) cudaEventRecord(ev[3], s);
   // weighted sum in slot order, every pair's output read from the rank that owns its expert
   CU(MER_ERR_SUBMISSION, "combine kernel",
      launch_ep_combine(ep, epoch_counter, (uint32_t)D, slots, ids_pub, w_own, (re.layer_flags & MER_LAYER_RESIDUAL) ? d_x : nullptr, d_out, b->d_status, s,
                        &launches));
+  if (ev) cudaEventRecord(ev[4], s);
   *launches_out = launches;
   return MER_OK;
 }
