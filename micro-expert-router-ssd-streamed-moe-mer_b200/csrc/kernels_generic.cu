@@ -570,23 +570,30 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
   }
 }
 
-// Router logits of a large batch as a tiled fp32 GEMM: logits[t][e] = x[t] . w[e].  A CTA of 128 threads computes
-// 32 tokens x 64 experts through shared memory in K chunks of 64 (the next chunk's global loads are in flight while
-// the current one is multiplied), a thread 4 tokens x 4 experts (8 shared loads per 64 FMAs).  k_router then runs
-// with `pre` set and only scores / selects.
-constexpr int RL_TT = 32, RL_TE = 64, RL_KC = 64, RL_LD = 68, RL_THREADS = 128;  // row stride 68 floats: conflict-free 128-bit loads
+// Router logits of a large batch as a tiled fp32 GEMM: logits[t][e] = x[t] . w[e].  A CTA computes 32 tokens x 64
+// experts through shared memory in K chunks of 64 (the next chunk's global loads are in flight while the current one
+// is multiplied); a thread holds 4 tokens x 4 experts (8 shared loads per 64 FMAs) over a quarter of every chunk.
+// k_router then runs with `pre` set and only scores / selects.
+constexpr int RL_KG = 4, RL_THREADS = 128 * RL_KG;  // four thread groups share every K chunk, a quarter (64 values) each
+constexpr int RL_TT = 32, RL_TE = 64, RL_KC = 64 * RL_KG, RL_LD = RL_KC + 4;  // row stride = 4 mod 32 floats: conflict-free 128-bit loads
+constexpr size_t RL_SMEM = (size_t)(RL_TT + RL_TE) * RL_LD * 4;
 __global__ void __launch_bounds__(RL_THREADS) k_router_logits_tiled(RouterDev r, MoeDispatch d) {
-  __shared__ __align__(16) float xs[RL_TT][RL_LD];
-  __shared__ __align__(16) float ws[RL_TE][RL_LD];
+  // With one thread group (4 warps per CTA, and a 2048-token batch makes only 128 CTAs) the kernel sat at 4 warps per
+  // SM and was bound by its own latencies: 55 us for 1 GFLOP.  Four groups split the K range of every chunk (a chunk
+  // is four times as long, so that a group still has 64 values of K to hide the next chunk's loads behind) and
+  // their partial sums are added at the end in a fixed order.
+  extern __shared__ __align__(16) float sm[];
+  float(*xs)[RL_LD] = reinterpret_cast<float(*)[RL_LD]>(sm);
+  float(*ws)[RL_LD] = reinterpret_cast<float(*)[RL_LD]>(sm + RL_TT * RL_LD);
   const uint32_t E = r.num_experts, D = d.D, T = d.n_tokens;
   const uint32_t t0 = blockIdx.y * RL_TT, e0 = blockIdx.x * RL_TE;
-  const uint32_t tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const uint32_t tid = threadIdx.x, kg = tid >> 7, lt = tid & 127, ty = lt >> 4, tx = lt & 15;
   float acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
-  const uint32_t lr = tid >> 4, lc = (tid & 15) * 4;  // this thread's float4 of an 8-row x 64-column slab
+  const uint32_t lr = tid >> 6, lc = (tid & 63) * 4;  // this thread's float4 of an 8-row x 256-column slab
   const float *xrow[4], *wrow[8];
 #pragma unroll
   for (int i = 0; i < 4; i++) xrow[i] = d.x + (size_t)min(t0 + 8 * i + lr, T - 1) * D + lc;
@@ -611,7 +618,8 @@ __global__ void __launch_bounds__(RL_THREADS) k_router_logits_tiled(RouterDev r,
       for (int j = 0; j < 8; j++) wv[j] = __ldg(reinterpret_cast<const float4 *>(wrow[j] + k0 + RL_KC));
     }
 #pragma unroll 4
-    for (int k = 0; k < RL_KC; k += 4) {
+    for (int kk = 0; kk < RL_KC / RL_KG; kk += 4) {
+      const int k = kg * (RL_KC / RL_KG) + kk;
       float4 a[4], b[4];
 #pragma unroll
       for (int i = 0; i < 4; i++) a[i] = *reinterpret_cast<const float4 *>(&xs[ty * 4 + i][k]);
@@ -628,13 +636,29 @@ __global__ void __launch_bounds__(RL_THREADS) k_router_logits_tiled(RouterDev r,
         }
     }
   }
+  // partial sums of groups 1..3 through shared memory (the operand tiles are done with), added to group 0's in group order
+  __syncthreads();
+  float *red = sm;  // [RL_KG - 1][RL_TT * RL_TE]
+  static_assert((RL_KG - 1) * RL_TT * RL_TE <= (RL_TT + RL_TE) * RL_LD, "the partial sums fit the operand tiles' memory");
+  if (kg > 0) {
 #pragma unroll
-  for (int i = 0; i < 4; i++)
+    for (int i = 0; i < 4; i++)
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-      const uint32_t t = t0 + ty * 4 + i, e = e0 + tx + 16 * j;
-      if (t < T && e < E) d.logits[(size_t)t * E + e] = acc[i][j];
-    }
+      for (int j = 0; j < 4; j++) red[(kg - 1) * RL_TT * RL_TE + (ty * 4 + i) * RL_TE + tx + 16 * j] = acc[i][j];
+  }
+  __syncthreads();
+  if (kg == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float v = acc[i][j];
+#pragma unroll
+        for (int g = 0; g < RL_KG - 1; g++) v += red[g * RL_TT * RL_TE + (ty * 4 + i) * RL_TE + tx + 16 * j];
+        const uint32_t t = t0 + ty * 4 + i, e = e0 + tx + 16 * j;
+        if (t < T && e < E) d.logits[(size_t)t * E + e] = v;
+      }
+  }
 }
 
 __global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispatch d, uint32_t max_tokens, int pre, int group_here) {
@@ -1046,7 +1070,9 @@ cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max
   const bool tiled = d.n_tokens >= 1024 && (d.D % RL_KC) == 0;  // large batches: logits as a tiled GEMM first (below: too few tiles to fill the SMs)
   if (tiled) {
     dim3 lgrid((E + RL_TE - 1) / RL_TE, (d.n_tokens + RL_TT - 1) / RL_TT);
-    k_router_logits_tiled<<<lgrid, RL_THREADS, 0, s>>>(r, d);
+    cudaError_t e = cudaFuncSetAttribute(k_router_logits_tiled, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RL_SMEM);
+    if (e != cudaSuccess) return e;
+    k_router_logits_tiled<<<lgrid, RL_THREADS, RL_SMEM, s>>>(r, d);
     if (launches) (*launches)++;
   }
   dim3 grid(tiled ? 1 : (E + ROUTER_ROWS - 1) / ROUTER_ROWS, (d.n_tokens + ROUTER_TT - 1) / ROUTER_TT);
