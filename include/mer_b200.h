@@ -505,9 +505,10 @@ int mer_ep_local_experts_forward_device(mer_backend *b, uint32_t layer, const fl
                                         size_t n_tokens_all, size_t tokens_per_rank,
                                         float *d_out_partial, void *stream);
 /* The whole layer for this rank's n_tokens rows with the exchange done by the kernels through peer
- * memory: route, publish, pull the tokens that hit a local expert, run the local experts, pull every
- * pair's output from its owner and sum in slot order (same order as a single GPU).  Every rank must
- * make the same sequence of calls with the same n_tokens. */
+ * memory: route, publish, pull the tokens that hit a local expert, run the local experts -- the down
+ * projection stores every pair's output straight into the exchange buffer of the token's home rank --
+ * and sum each token's rows in slot order (same order as a single GPU).  Every rank must make the
+ * same sequence of calls with the same n_tokens. */
 int mer_ep_layer_forward_device(mer_backend *b, uint32_t layer, const float *d_x, size_t n_tokens,
                                 float *d_out, void *stream);
 /* ---- the same layer with NCCL all-to-all dispatch and combine (the library calls NCCL itself; it binds libnccl.so.2

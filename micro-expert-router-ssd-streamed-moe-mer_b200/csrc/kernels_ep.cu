@@ -2,11 +2,14 @@
 // over the ranks.  Two ways to move tokens:
 //   (1) the host runs the collectives (all-gather of x and routing, reduce-scatter of partial
 //       outputs) and this file only filters the gathered routing down to the local experts;
-//   (2) the ranks exchange through peer memory: every rank publishes its tokens, routing and
-//       per-pair expert outputs in an exchange buffer the other ranks have mapped; a rank pulls
-//       the rows it needs with plain peer loads (no TMA, no multicast) after a flag barrier (a
-//       one-CTA signal kernel raises this rank's flag on every peer, then all CTAs of the gather /
-//       combine kernel wait for the flags of the ranks they read).
+//   (2) the ranks exchange through peer memory: every rank publishes its tokens and routing in an
+//       exchange buffer the other ranks have mapped; a rank pulls the token rows it needs with plain
+//       peer loads (no TMA, no multicast) after a flag barrier (a one-CTA signal kernel raises this
+//       rank's flag on every peer, then all CTAs of the gather kernel wait for the flags of the ranks
+//       they read).  Per-pair expert outputs travel the other way as plain peer stores: the owner of
+//       the expert writes them into the exchange buffer of the token's home rank (the GEMM kernels'
+//       down epilogue directly, k_ep_push_rows for the other kernel families), raises its flag, and
+//       the combine kernel reads local memory once every rank's flag is up.
 //   (3) NCCL all-to-all: every (token, slot) pair is packed into the send segment of the rank that owns its expert
 //       (k_a2a_pack), the library exchanges the segments with grouped ncclSend / ncclRecv, the owners run their
 //       experts over the rows they received and send the outputs back the same way; k_a2a_combine sums each
