@@ -607,15 +607,17 @@ __global__ void __launch_bounds__(256) k_gemm_act_image(MoeDispatch d, int phase
   const uint32_t n_chunks = K / 64;
   uint8_t *dst0 = img + ((size_t)pass * n_chunks + chunk) * 16 * b_lbo;  // slots are as large as the widest pass needs
   const uint32_t width = pass_width(bn, pcount), lbo = pass_lbo(width);
-  for (uint32_t idx = threadIdx.x; idx < width * 8; idx += blockDim.x) {
-    const uint32_t j = idx % width, k8 = idx / width;
-    uint4 hi = make_uint4(0, 0, 0, 0), lo = make_uint4(0, 0, 0, 0);
-    float un = 0.0f;
+  // per row of the pass, once: where it comes from and its scale
+  __shared__ float s_scale[128];
+  __shared__ uint32_t s_src[128];
+  for (uint32_t j = threadIdx.x; j < width; j += blockDim.x) {
+    float sc = 0.0f;  // rows beyond the pass's count are zero rows
+    uint32_t rowi = 0;
     if (j < pcount) {
       const uint32_t pair = d.perm[pstart + j];
-      const uint32_t rowi = phase == 0 ? pair / d.slots : pair;
+      rowi = phase == 0 ? pair / d.slots : pair;
       const float mx = __uint_as_float(phase == 0 ? amax_tok[rowi] : d.amax[pair]);
-      float sc = 1.0f;
+      sc = 1.0f;
       if (mx > 0.0f && isfinite(mx)) {
         int e;
         frexpf(mx, &e);
@@ -623,8 +625,17 @@ __global__ void __launch_bounds__(256) k_gemm_act_image(MoeDispatch d, int phase
       } else if (mx != mx || isinf(mx)) {
         sc = mx;  // non-finite activations poison the row, as they would in fp32
       }
-      un = 1.0f / sc;
-      const float4 *src = reinterpret_cast<const float4 *>(act + (size_t)rowi * K + chunk * 64 + k8 * 8);
+    }
+    s_scale[j] = sc, s_src[j] = rowi;
+    if (chunk == 0) unscale[(size_t)pass * bn + j] = j < pcount ? 1.0f / sc : 0.0f;
+  }
+  __syncthreads();
+  for (uint32_t idx = threadIdx.x; idx < width * 8; idx += blockDim.x) {
+    const uint32_t k8 = idx / width, j = idx - k8 * width;
+    uint4 hi = make_uint4(0, 0, 0, 0), lo = make_uint4(0, 0, 0, 0);
+    if (j < pcount) {
+      const float sc = s_scale[j];
+      const float4 *src = reinterpret_cast<const float4 *>(act + (size_t)s_src[j] * K + chunk * 64 + k8 * 8);
       const float4 a = __ldg(src), b = __ldg(src + 1);
       const float vs[8] = {a.x * sc, a.y * sc, a.z * sc, a.w * sc, b.x * sc, b.y * sc, b.z * sc, b.w * sc};
       uint32_t h[4], l[4];
@@ -640,7 +651,6 @@ __global__ void __launch_bounds__(256) k_gemm_act_image(MoeDispatch d, int phase
     uint8_t *dst = dst0 + (size_t)k8 * lbo + j * 16;
     *reinterpret_cast<uint4 *>(dst) = hi;
     *reinterpret_cast<uint4 *>(dst + width * 16) = lo;
-    if (chunk == 0 && k8 == 0) unscale[(size_t)pass * bn + j] = un;
   }
 }
 
