@@ -45,7 +45,8 @@ constexpr uint32_t TMEM_COLS = 512;      // [0, 256): two accumulator buffers of
 constexpr uint32_t TMEM_A0 = 256, A_STAGES = 8, A_STAGE_COLS = 32;  // a stage = one block: 16 columns hi + 16 columns lo
 constexpr uint32_t MAX_RING = 8;
 // The MMA issuer synchronises with its producers once per GROUP blocks of K: it waits for a whole group of A stages
-// (a_full) and for the group's activation stage (b_full), issues the group's MMAs and commits done[], which releases
+// and for the group's activation stage (both complete the same barrier, a_full: eight dequantiser arrivals, the
+// producer's expect-tx arrival and the bytes of its two copies), issues the group's MMAs and commits done[], which releases
 // both.  A waiter is never two phases behind a done[] barrier: the issuer leads its producers by at most two groups.
 constexpr uint32_t GROUP = 4, DONE_RING = 8;
 static_assert(GROUP == RAW_BLOCKS, "a weight stage holds exactly one group of blocks");
@@ -181,7 +182,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
   if (item_beg >= n_items) return;
 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
-  uint64_t *raw_full = bars, *raw_empty = bars + 8, *a_full = bars + 16, *done = bars + 24, *b_full = bars + 32,
+  uint64_t *raw_full = bars, *raw_empty = bars + 8, *a_full = bars + 16, *done = bars + 24,
            *acc_full = bars + 48, *acc_empty = bars + 50, *drain = bars + 52;
   uint32_t *s_tmem = reinterpret_cast<uint32_t *>(smem + 512);
   volatile uint32_t *s_abort = reinterpret_cast<volatile uint32_t *>(smem + 516);
@@ -192,8 +193,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < MAX_RING; s++) {
       mbar_init(&raw_full[s], 1), mbar_init(&raw_empty[s], DQ_WARPS);  // filled by the weight producer, left by every dequantiser warp
-      mbar_init(&a_full[s], DQ_WARPS), mbar_init(&done[s], 1);  // one arrival per dequantiser warp and group
-      mbar_init(&b_full[s], 1);
+      mbar_init(&a_full[s], DQ_WARPS + 1), mbar_init(&done[s], 1);  // per group: every dequantiser warp + the activation producer
     }
     for (uint32_t s = 0; s < 2; s++) mbar_init(&acc_full[s], 1), mbar_init(&acc_empty[s], EPI_WARPS);
     mbar_init(drain, 1);
@@ -246,17 +246,17 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
         if (*s_abort) ok = false;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (lane == 0) mbar_expect_tx(&b_full[rb.stage], 2 * bytes);
+        if (lane == 0) mbar_expect_tx(&a_full[rb.stage], 2 * bytes);  // stage = group parity: the barrier the group's A stages complete too
         __syncwarp();
         if (lane < 2)
-          bulk_g2s(s_b + ((size_t)rb.stage * 2 + lane) * b_stage, bsrc + ((size_t)gi * 2 + lane) * b_stage, bytes, &b_full[rb.stage]);
+          bulk_g2s(s_b + ((size_t)rb.stage * 2 + lane) * b_stage, bsrc + ((size_t)gi * 2 + lane) * b_stage, bytes, &a_full[rb.stage]);
         rb.advance();
       }
     }
     if (!ok) {
       if (lane == 0) *s_abort = 1, atomicOr(d.status, MER_DEVSTAT_TIMEOUT);
       // copies already in flight get a bounded chance to land before the CTA's shared memory is released
-      for (uint32_t s = 0; s < p.n_b; s++) (void)mbar_wait(&b_full[s], 0), (void)mbar_wait(&b_full[s], 1);
+      for (uint32_t s = 0; s < p.n_b; s++) (void)mbar_wait(&a_full[s], 0), (void)mbar_wait(&a_full[s], 1);
     }
   } else if (warp == W_MMA) {
     // -------------------------------------------------------------------------- MMA issuer
@@ -285,7 +285,6 @@ __global__ void __launch_bounds__(G_THREADS, 1) k_ffn_gemm(GemmParams p) {
         const uint32_t ag = grp & 1;
         if (st == 0 && use > 0) ok = mbar_wait(&acc_empty[buf], (use - 1) & 1);  // the buffer's previous item has been drained
         if (ok) ok = mbar_wait(&a_full[ag], (grp >> 1) & 1);
-        if (ok) ok = mbar_wait(&b_full[rb.stage], rb.round & 1);
         if (*s_abort) ok = false;
         ok = __all_sync(0xffffffffu, ok);  // warp-uniform by construction; the vote also tells the compiler so
         if (!ok) break;
