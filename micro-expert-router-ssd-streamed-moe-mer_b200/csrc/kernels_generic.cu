@@ -389,7 +389,7 @@ __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uin
 // Scoring, group filter, top-k and mixing weights of one token by one warp.
 // s_score / s_sel / s_ok are this warp's shared arrays of E entries; logits are already in s_score.
 __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t token, float *s_score, float *s_sel,
-                            uint8_t *s_ok, uint32_t *s_groups, float *s_gscore) {
+                            uint8_t *s_ok, uint32_t *s_groups, float *s_gscore, bool count_groups) {
   const uint32_t E = r.num_experts, lane = threadIdx.x & 31;
   constexpr int REG_E = 8;  // up to 32 * REG_E experts: selection keys live in registers
   const bool small = E <= 32 * REG_E;
@@ -560,10 +560,12 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
     bool have = lane < n_sel;
     d.pair_expert[(size_t)token * S + lane] = have ? r.id_base + my_id : MER_NONE;
     d.pair_weight[(size_t)token * S + lane] = have ? w : 0.0f;
+    if (count_groups && have) atomicAdd(d.group_count + my_id, 1u);  // the grid-wide grouping's count step, done here
   }
   if (lane == 0) {
     if (n_sel < k) atomicOr(d.status, MER_DEVSTAT_SHORT_SELECTION);
     if (S > k) {
+      if (count_groups) atomicAdd(d.group_count + E, 1u);
       d.pair_expert[(size_t)token * S + k] = r.shared_expert_id;
       d.pair_weight[(size_t)token * S + k] = r.shared_scale ? r.shared_scale[token] : 1.0f;
     }
@@ -764,9 +766,9 @@ __global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispa
     const uint32_t token = t0 + warp;
     for (uint32_t i = lane; i < E; i += 32) s_score[i] = single ? s_logit[warp][i] : __ldcg(d.logits + (size_t)token * E + i);
     __syncwarp();
-    route_token(r, d, token, s_score, s_sel, s_ok, s_groups[warp], s_gscore[warp]);
+    route_token(r, d, token, s_score, s_sel, s_ok, s_groups[warp], s_gscore[warp], group_here == 2);
   }
-  if (!group_here) return;  // a large dispatch is grouped by the grid-wide kernels that follow
+  if (group_here != 1) return;  // a large dispatch is grouped by the grid-wide kernels that follow (2: their count step is done above)
   __syncthreads();
   const uint32_t n_tiles = gridDim.y;
   if (n_tiles > 1) {
@@ -1119,15 +1121,14 @@ cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max
   }
   dim3 grid(tiled ? 1 : (E + ROUTER_ROWS - 1) / ROUTER_ROWS, (d.n_tokens + ROUTER_TT - 1) / ROUTER_TT);
   const bool grid_grouping = group && P >= GRID_GROUPING_PAIRS && d.group_count != nullptr;
-  k_router<<<grid, ROUTER_THREADS, smem, s>>>(r, d, max_tokens, tiled ? 1 : 0, (group && !grid_grouping) ? 1 : 0);
+  k_router<<<grid, ROUTER_THREADS, smem, s>>>(r, d, max_tokens, tiled ? 1 : 0, grid_grouping ? 2 : group ? 1 : 0);
   if (launches) (*launches)++;
-  if (grid_grouping) {
+  if (grid_grouping) {  // the router has counted the pairs per group
     const unsigned blocks = (P + 1023) / 1024;
-    k_group_count<<<blocks, 256, 0, s>>>(r, d);
     k_group_scan<<<1, 256, 0, s>>>(r, d);
     k_group_scatter<<<blocks, 256, 0, s>>>(r, d);
     k_group_clear<<<1, 256, 0, s>>>(d);
-    if (launches) (*launches) += 4;
+    if (launches) (*launches) += 3;
   }
   return cudaGetLastError();
 }

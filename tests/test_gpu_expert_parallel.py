@@ -228,6 +228,12 @@ def test_ep_argument_validation():
         with pytest.raises(mer_b200.GpuExpertDispatchError) as e:  # more tokens than the group was sized for
             ep.layer_forward_peer(0, 1, B + 1, 1)
         assert e.value.kind == Kind.ValidationDispatch
+        with pytest.raises(mer_b200.GpuExpertDispatchError):  # an owner outside the group
+            ep.set_placement(np.ones(E, np.uint16))
+        with pytest.raises(mer_b200.GpuExpertDispatchError):  # more ids than the backend's id space
+            ep.set_placement(np.zeros(10_000, np.uint16))
+        ep.set_placement(np.zeros(E, np.uint16))  # everything on rank 0 of a group of one
+        ep.set_placement(None)                    # back to the contiguous rule
     finally:
         b.close()
     stride = (256 + mer_b200.expert_bytes(dtype, D, F) + 4095) // 4096 * 4096
