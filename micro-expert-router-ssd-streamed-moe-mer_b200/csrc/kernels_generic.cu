@@ -573,91 +573,93 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
 }
 
 // Router logits of a large batch as a tiled fp32 GEMM: logits[t][e] = x[t] . w[e].  A CTA computes 32 tokens x 64
-// experts through shared memory in K chunks of 64 (the next chunk's global loads are in flight while the current one
-// is multiplied); a thread holds 4 tokens x 4 experts (8 shared loads per 64 FMAs) over a quarter of every chunk.
-// k_router then runs with `pre` set and only scores / selects.
-constexpr int RL_KG = 4, RL_THREADS = 128 * RL_KG;  // four thread groups share every K chunk, a quarter (64 values) each
-constexpr int RL_TT = 32, RL_TE = 64, RL_KC = 64 * RL_KG, RL_LD = RL_KC + 4;  // row stride = 4 mod 32 floats: conflict-free 128-bit loads
-constexpr size_t RL_SMEM = (size_t)(RL_TT + RL_TE) * RL_LD * 4;
+// experts; K runs in chunks of 256 values that cp.async double-buffers in shared memory.  Eight warps split every
+// chunk (32 values of K each); a thread holds 8 tokens x 8 experts (rows ty + 4 i and tx + 8 j: neighbouring lanes read
+// neighbouring rows, whose stride of 260 floats keeps every 128-bit load conflict-free), i.e. 16 shared 128-bit loads per 256 FMAs (the
+// 4 x 4 form before it, 8 loads per 64 FMAs, was bound by shared-memory bandwidth: 45 us for 1 GFLOP).  The eight
+// partial sums are added at the end in warp order.  k_router then runs with `pre` set and only scores / selects.
+constexpr int RL_WARPS = 8, RL_THREADS = 32 * RL_WARPS;
+constexpr int RL_TT = 32, RL_TE = 64, RL_KC = 32 * RL_WARPS, RL_LD = RL_KC + 4;  // row stride = 4 mod 32 floats: conflict-free 128-bit loads
+constexpr size_t RL_BUF = (size_t)(RL_TT + RL_TE) * RL_LD;                       // floats per buffer
+constexpr size_t RL_SMEM = 2 * RL_BUF * 4;
 __global__ void __launch_bounds__(RL_THREADS) k_router_logits_tiled(RouterDev r, MoeDispatch d) {
-  // With one thread group (4 warps per CTA, and a 2048-token batch makes only 128 CTAs) the kernel sat at 4 warps per
-  // SM and was bound by its own latencies: 55 us for 1 GFLOP.  Four groups split the K range of every chunk (a chunk
-  // is four times as long, so that a group still has 64 values of K to hide the next chunk's loads behind) and
-  // their partial sums are added at the end in a fixed order.
   extern __shared__ __align__(16) float sm[];
-  float(*xs)[RL_LD] = reinterpret_cast<float(*)[RL_LD]>(sm);
-  float(*ws)[RL_LD] = reinterpret_cast<float(*)[RL_LD]>(sm + RL_TT * RL_LD);
   const uint32_t E = r.num_experts, D = d.D, T = d.n_tokens;
   const uint32_t t0 = blockIdx.y * RL_TT, e0 = blockIdx.x * RL_TE;
-  const uint32_t tid = threadIdx.x, kg = tid >> 7, lt = tid & 127, ty = lt >> 4, tx = lt & 15;
-  float acc[4][4];
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, ty = lane >> 3, tx = lane & 7;
+  float acc[8][8];
 #pragma unroll
-  for (int i = 0; i < 4; i++)
+  for (int i = 0; i < 8; i++)
 #pragma unroll
-    for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
-  const uint32_t lr = tid >> 6, lc = (tid & 63) * 4;  // this thread's float4 of an 8-row x 256-column slab
-  const float *xrow[4], *wrow[8];
+    for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+  // global -> shared: a thread copies one 16-byte piece of every fourth row (64 pieces per 256-value row)
+  const uint32_t lr = tid >> 6, lc = (tid & 63) * 4;
+  auto issue_chunk = [&](uint32_t k0, uint32_t buf) {
+    float *xs = sm + buf * RL_BUF, *ws = xs + RL_TT * RL_LD;
 #pragma unroll
-  for (int i = 0; i < 4; i++) xrow[i] = d.x + (size_t)min(t0 + 8 * i + lr, T - 1) * D + lc;
-#pragma unroll
-  for (int j = 0; j < 8; j++) wrow[j] = r.w + (size_t)min(e0 + 8 * j + lr, E - 1) * D + lc;
-  float4 xv[4], wv[8];
-#pragma unroll
-  for (int i = 0; i < 4; i++) xv[i] = __ldg(reinterpret_cast<const float4 *>(xrow[i]));
-#pragma unroll
-  for (int j = 0; j < 8; j++) wv[j] = __ldg(reinterpret_cast<const float4 *>(wrow[j]));
-  for (uint32_t k0 = 0; k0 < D; k0 += RL_KC) {
-    __syncthreads();  // the previous chunk has been consumed
-#pragma unroll
-    for (int i = 0; i < 4; i++) *reinterpret_cast<float4 *>(&xs[8 * i + lr][lc]) = xv[i];
-#pragma unroll
-    for (int j = 0; j < 8; j++) *reinterpret_cast<float4 *>(&ws[8 * j + lr][lc]) = wv[j];
-    __syncthreads();
-    if (k0 + RL_KC < D) {
-#pragma unroll
-      for (int i = 0; i < 4; i++) xv[i] = __ldg(reinterpret_cast<const float4 *>(xrow[i] + k0 + RL_KC));
-#pragma unroll
-      for (int j = 0; j < 8; j++) wv[j] = __ldg(reinterpret_cast<const float4 *>(wrow[j] + k0 + RL_KC));
+    for (int i = 0; i < RL_TT / 4; i++) {
+      const uint32_t row = 4 * i + lr;
+      const float *src = d.x + (size_t)min(t0 + row, T - 1) * D + k0 + lc;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(xs + row * RL_LD + lc)), "l"(src) : "memory");
     }
-#pragma unroll 4
-    for (int kk = 0; kk < RL_KC / RL_KG; kk += 4) {
-      const int k = kg * (RL_KC / RL_KG) + kk;
-      float4 a[4], b[4];
 #pragma unroll
-      for (int i = 0; i < 4; i++) a[i] = *reinterpret_cast<const float4 *>(&xs[ty * 4 + i][k]);
+    for (int j = 0; j < RL_TE / 4; j++) {
+      const uint32_t row = 4 * j + lr;
+      const float *src = r.w + (size_t)min(e0 + row, E - 1) * D + k0 + lc;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(ws + row * RL_LD + lc)), "l"(src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const uint32_t n_chunks = D / RL_KC;
+  issue_chunk(0, 0);
+  for (uint32_t c = 0; c < n_chunks; c++) {
+    if (c + 1 < n_chunks) {
+      issue_chunk((c + 1) * RL_KC, (c + 1) & 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");  // chunk c has landed (this thread's pieces)
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();  // ... and everybody else's
+    const float *xs = sm + (c & 1) * RL_BUF, *ws = xs + RL_TT * RL_LD;
+#pragma unroll 2
+    for (int kk = 0; kk < RL_KC / RL_WARPS; kk += 4) {
+      const int k = warp * (RL_KC / RL_WARPS) + kk;
+      float4 a[8], b[8];
 #pragma unroll
-      for (int j = 0; j < 4; j++) b[j] = *reinterpret_cast<const float4 *>(&ws[tx + 16 * j][k]);
+      for (int i = 0; i < 8; i++) a[i] = *reinterpret_cast<const float4 *>(xs + (ty + 4 * i) * RL_LD + k);
 #pragma unroll
-      for (int i = 0; i < 4; i++)
+      for (int j = 0; j < 8; j++) b[j] = *reinterpret_cast<const float4 *>(ws + (tx + 8 * j) * RL_LD + k);
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
+      for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
           acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
           acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
           acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
           acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
         }
     }
+    __syncthreads();  // the buffer may be refilled two iterations from now
   }
-  // partial sums of groups 1..3 through shared memory (the operand tiles are done with), added to group 0's in group order
-  __syncthreads();
-  float *red = sm;  // [RL_KG - 1][RL_TT * RL_TE]
-  static_assert((RL_KG - 1) * RL_TT * RL_TE <= (RL_TT + RL_TE) * RL_LD, "the partial sums fit the operand tiles' memory");
-  if (kg > 0) {
+  // partial sums of warps 1..7 through shared memory (the operand buffers are done with), added to warp 0's in warp order
+  float *red = sm;  // [RL_WARPS - 1][RL_TT * RL_TE]
+  static_assert((RL_WARPS - 1) * RL_TT * RL_TE <= 2 * RL_BUF, "the partial sums fit the operand buffers");
+  if (warp > 0) {
 #pragma unroll
-    for (int i = 0; i < 4; i++)
+    for (int i = 0; i < 8; i++)
 #pragma unroll
-      for (int j = 0; j < 4; j++) red[(kg - 1) * RL_TT * RL_TE + (ty * 4 + i) * RL_TE + tx + 16 * j] = acc[i][j];
+      for (int j = 0; j < 8; j++) red[(warp - 1) * RL_TT * RL_TE + (ty + 4 * i) * RL_TE + tx + 8 * j] = acc[i][j];
   }
   __syncthreads();
-  if (kg == 0) {
+  if (warp == 0) {
 #pragma unroll
-    for (int i = 0; i < 4; i++)
+    for (int i = 0; i < 8; i++)
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
+      for (int j = 0; j < 8; j++) {
         float v = acc[i][j];
 #pragma unroll
-        for (int g = 0; g < RL_KG - 1; g++) v += red[g * RL_TT * RL_TE + (ty * 4 + i) * RL_TE + tx + 16 * j];
-        const uint32_t t = t0 + ty * 4 + i, e = e0 + tx + 16 * j;
+        for (int g = 0; g < RL_WARPS - 1; g++) v += red[g * RL_TT * RL_TE + (ty + 4 * i) * RL_TE + tx + 8 * j];
+        const uint32_t t = t0 + ty + 4 * i, e = e0 + tx + 8 * j;
         if (t < T && e < E) d.logits[(size_t)t * E + e] = v;
       }
   }
