@@ -582,7 +582,7 @@ constexpr int RL_WARPS = 8, RL_THREADS = 32 * RL_WARPS;
 constexpr int RL_TT = 32, RL_TE = 64, RL_KC = 32 * RL_WARPS, RL_LD = RL_KC + 4;  // row stride = 4 mod 32 floats: conflict-free 128-bit loads
 constexpr size_t RL_BUF = (size_t)(RL_TT + RL_TE) * RL_LD;                       // floats per buffer
 constexpr size_t RL_SMEM = 2 * RL_BUF * 4;
-__global__ void __launch_bounds__(RL_THREADS) k_router_logits_tiled(RouterDev r, MoeDispatch d) {
+__global__ void __launch_bounds__(RL_THREADS) k_router_logits_tiled(RouterDev r, MoeDispatch d, uint32_t ksplit) {
   extern __shared__ __align__(16) float sm[];
   const uint32_t E = r.num_experts, D = d.D, T = d.n_tokens;
   const uint32_t t0 = blockIdx.y * RL_TT, e0 = blockIdx.x * RL_TE;
@@ -610,11 +610,13 @@ __global__ void __launch_bounds__(RL_THREADS) k_router_logits_tiled(RouterDev r,
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  const uint32_t n_chunks = D / RL_KC;
-  issue_chunk(0, 0);
+  // A batch of a few hundred tokens makes too few tiles for the SMs: blockIdx.z then takes one of `ksplit` slices of K
+  // and writes its partial logits to set z of d.logits ([ksplit][T][E]); k_router adds the sets in order.
+  const uint32_t n_chunks = D / RL_KC / ksplit, c_base = blockIdx.z * n_chunks;
+  issue_chunk(c_base * RL_KC, 0);
   for (uint32_t c = 0; c < n_chunks; c++) {
     if (c + 1 < n_chunks) {
-      issue_chunk((c + 1) * RL_KC, (c + 1) & 1);
+      issue_chunk((c_base + c + 1) * RL_KC, (c + 1) & 1);
       asm volatile("cp.async.wait_group 1;" ::: "memory");  // chunk c has landed (this thread's pieces)
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -660,7 +662,7 @@ __global__ void __launch_bounds__(RL_THREADS) k_router_logits_tiled(RouterDev r,
 #pragma unroll
         for (int g = 0; g < RL_WARPS - 1; g++) v += red[g * RL_TT * RL_TE + (ty + 4 * i) * RL_TE + tx + 8 * j];
         const uint32_t t = t0 + ty + 4 * i, e = e0 + tx + 8 * j;
-        if (t < T && e < E) d.logits[(size_t)t * E + e] = v;
+        if (t < T && e < E) d.logits[((size_t)blockIdx.z * T + t) * E + e] = v;
       }
   }
 }
@@ -766,7 +768,15 @@ __global__ void __launch_bounds__(ROUTER_THREADS) k_router(RouterDev r, MoeDispa
     float *s_sel = s_score + E;                                                    // [E] selection scores
     uint8_t *s_ok = smem_raw + (size_t)ROUTER_TT * 2 * E * 4 + (size_t)warp * E;    // [E] allowed & not yet taken
     const uint32_t token = t0 + warp;
-    for (uint32_t i = lane; i < E; i += 32) s_score[i] = single ? s_logit[warp][i] : __ldcg(d.logits + (size_t)token * E + i);
+    if (pre > 1) {  // the logits kernel split K: add its partial sets in order
+      for (uint32_t i = lane; i < E; i += 32) {
+        float v = __ldcg(d.logits + (size_t)token * E + i);
+        for (int z = 1; z < pre; z++) v += __ldcg(d.logits + ((size_t)z * d.n_tokens + token) * E + i);
+        s_score[i] = v;
+      }
+    } else {
+      for (uint32_t i = lane; i < E; i += 32) s_score[i] = single ? s_logit[warp][i] : __ldcg(d.logits + (size_t)token * E + i);
+    }
     __syncwarp();
     route_token(r, d, token, s_score, s_sel, s_ok, s_groups[warp], s_gscore[warp], group_here == 2);
   }
@@ -1113,17 +1123,24 @@ cudaError_t launch_router(const RouterDev &r, const MoeDispatch &d, uint32_t max
     cudaError_t e = cudaFuncSetAttribute(k_router, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  const bool tiled = d.n_tokens >= 1024 && (d.D % RL_KC) == 0;  // large batches: logits as a tiled GEMM first (below: too few tiles to fill the SMs)
+  const bool tiled = d.n_tokens >= 256 && (d.D % RL_KC) == 0;  // from a few hundred tokens: logits as a tiled GEMM first
+  uint32_t ksplit = 1;
   if (tiled) {
     dim3 lgrid((E + RL_TE - 1) / RL_TE, (d.n_tokens + RL_TT - 1) / RL_TT);
+    // split K over blockIdx.z while the tiles alone leave SMs idle (the partial sets must fit the logits scratch,
+    // which holds max_tokens x 4096 floats, and a slice is a whole number of chunks)
+    const uint32_t n_chunks = d.D / RL_KC, tiles = lgrid.x * lgrid.y;
+    for (uint32_t ks = 2; ks <= 8 && ks <= n_chunks; ks++)
+      if (n_chunks % ks == 0 && tiles * ks <= 160 && (size_t)ks * E <= 4096) ksplit = ks;
+    lgrid.z = ksplit;
     cudaError_t e = cudaFuncSetAttribute(k_router_logits_tiled, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RL_SMEM);
     if (e != cudaSuccess) return e;
-    k_router_logits_tiled<<<lgrid, RL_THREADS, RL_SMEM, s>>>(r, d);
+    k_router_logits_tiled<<<lgrid, RL_THREADS, RL_SMEM, s>>>(r, d, ksplit);
     if (launches) (*launches)++;
   }
   dim3 grid(tiled ? 1 : (E + ROUTER_ROWS - 1) / ROUTER_ROWS, (d.n_tokens + ROUTER_TT - 1) / ROUTER_TT);
   const bool grid_grouping = group && P >= GRID_GROUPING_PAIRS && d.group_count != nullptr;
-  k_router<<<grid, ROUTER_THREADS, smem, s>>>(r, d, max_tokens, tiled ? 1 : 0, grid_grouping ? 2 : group ? 1 : 0);
+  k_router<<<grid, ROUTER_THREADS, smem, s>>>(r, d, max_tokens, tiled ? (int)ksplit : 0, grid_grouping ? 2 : group ? 1 : 0);
   if (launches) (*launches)++;
   if (grid_grouping) {  // the router has counted the pairs per group
     const unsigned blocks = (P + 1023) / 1024;
