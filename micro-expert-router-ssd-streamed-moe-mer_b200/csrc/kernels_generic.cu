@@ -96,10 +96,12 @@ __device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
   __shared__ uint8_t s_cost[1024];  // cost of each of the first 1024 passes (the weighted work split below)
   const uint32_t tpp = d.tokens_per_pass, P = d.n_tokens * d.slots;
   const uint32_t tpp_shift = 31 - __clz(tpp);  // tokens per pass is a power of two (4 or 8; 16 .. 128 for the GEMM kernels)
+#pragma unroll 1
   for (uint32_t i = threadIdx.x; i < P; i += 256) d.amax[i] = 0;
   const uint32_t per = (d.n_groups + 255) / 256;
   const uint32_t g0 = threadIdx.x * per, g1 = min(g0 + per, d.n_groups);
   uint32_t mine = 0;
+#pragma unroll 1
   for (uint32_t g = g0; g < g1; g++) mine += (off[g + 1] - off[g] + tpp - 1) >> tpp_shift;
   s_pcnt[threadIdx.x + 1] = mine;
   if (threadIdx.x == 0) s_pcnt[0] = 0;
@@ -120,8 +122,10 @@ __device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
   }
   __syncthreads();
   uint32_t np = s_pcnt[threadIdx.x];
+#pragma unroll 1
   for (uint32_t g = g0; g < g1; g++) {
     const uint32_t beg = off[g], end = off[g + 1];
+#pragma unroll 1
     for (uint32_t st = beg; st < end; st += tpp) {
       const uint32_t cnt = min(tpp, end - st);
       d.pass_group[np] = g;
@@ -178,6 +182,7 @@ __device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
     if (threadIdx.x == 255) s_cum[1024] = acc;
     __syncthreads();
   }
+#pragma unroll 1
   for (uint32_t i = threadIdx.x; i < 2 * (G + 1); i += 256) {
     const uint32_t phase = i / (G + 1), b = i % (G + 1);
     const uint32_t ipp = d.items_per_pass[phase];
@@ -190,6 +195,7 @@ __device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
       // on the critical path of every decode layer)
       const uint32_t total = s_cum[n_passes] * ipp, target = total * b / G;
       uint32_t lo = 0, hi = n_passes;  // largest pass index with cum[pass] * ipp <= target
+#pragma unroll 1
       while (lo < hi) {
         const uint32_t mid = (lo + hi + 1) >> 1;
         if (s_cum[mid] * ipp <= target) lo = mid; else hi = mid - 1;
@@ -204,6 +210,7 @@ __device__ void build_passes_block(const MoeDispatch &d, const uint32_t *off) {
     } else {
       const uint64_t total = (uint64_t)s_cum[n_passes] * ipp, target = total * b / G;
       uint32_t lo = 0, hi = n_passes;
+#pragma unroll 1
       while (lo < hi) {
         const uint32_t mid = (lo + hi + 1) >> 1;
         if ((uint64_t)s_cum[mid] * ipp <= target) lo = mid; else hi = mid - 1;
@@ -299,22 +306,28 @@ __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uin
     return e - r.id_base;
   };
   auto key_of = [&](uint32_t p) -> uint32_t { return staged ? s_key[p] : key_global(p); };
+#pragma unroll 1
   for (uint32_t g = tid; g < G; g += nt) d.group_expert[g] = (g < r.num_experts) ? r.id_base + g : r.shared_expert_id;
+#pragma unroll 1
   for (uint32_t i = tid; i < (stable ? ROUTER_ROWS * G : G); i += nt) s_cnt[i] = 0;
   if (staged)
+#pragma unroll 1
     for (uint32_t p = tid; p < P; p += nt) s_key[p] = key_global(p);
   __syncthreads();
   if (stable) {
     // every warp owns a contiguous run of pairs, so (warp, position in run) order = (token, slot) order
     const uint32_t chunk = ((P + ROUTER_ROWS - 1) / ROUTER_ROWS + 31) / 32 * 32;
     const uint32_t p0 = warp * chunk, p1 = min(P, p0 + chunk);
+#pragma unroll 1
     for (uint32_t p = p0 + lane; p < p1; p += 32) {
       uint32_t k = key_of(p);
       if (k != MER_NONE) atomicAdd(&s_cnt[warp * G + k], 1u);
     }
     __syncthreads();
+#pragma unroll 1
     for (uint32_t g = tid; g < G; g += nt) {  // per group: exclusive scan over the warps, total into s_off
       uint32_t run = 0;
+#pragma unroll 1
       for (uint32_t w = 0; w < ROUTER_ROWS; w++) {
         uint32_t c = s_cnt[w * G + g];
         s_cnt[w * G + g] = run;
@@ -326,6 +339,7 @@ __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uin
     if (warp == 0) {  // exclusive scan of the group totals
       const uint32_t per = (G + 31) / 32;
       uint32_t run = 0;
+#pragma unroll 1
       for (uint32_t i = 0; i < per; i++) {
         uint32_t g = lane * per + i;
         if (g < G) run += s_off[g];
@@ -337,6 +351,7 @@ __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uin
         if (lane >= (uint32_t)o) incl += up;
       }
       uint32_t base = incl - run;
+#pragma unroll 1
       for (uint32_t i = 0; i < per; i++) {
         uint32_t g = lane * per + i;
         if (g < G) {
@@ -348,6 +363,7 @@ __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uin
       if (lane == 31) s_off[G] = incl;
     }
     __syncthreads();
+#pragma unroll 1
     for (uint32_t pb = p0; pb < p1; pb += 32) {
       const uint32_t p = pb + lane;
       const uint32_t k = p < p1 ? key_of(p) : MER_NONE;
@@ -361,6 +377,7 @@ __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uin
       __syncwarp();
     }
   } else {
+#pragma unroll 1
     for (uint32_t p = tid; p < P; p += nt) {
       uint32_t k = key_of(p);
       if (k != MER_NONE) atomicAdd(&s_cnt[k], 1u);
@@ -368,6 +385,7 @@ __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uin
     __syncthreads();
     if (tid == 0) {
       uint32_t acc = 0;
+#pragma unroll 1
       for (uint32_t g = 0; g < G; g++) {
         s_off[g] = acc;
         acc += s_cnt[g];
@@ -376,12 +394,14 @@ __device__ void build_groups_layer(const RouterDev &r, const MoeDispatch &d, uin
       s_off[G] = acc;
     }
     __syncthreads();
+#pragma unroll 1
     for (uint32_t p = tid; p < P; p += nt) {
       uint32_t k = key_of(p);
       if (k != MER_NONE) d.perm[s_off[k] + atomicAdd(&s_cnt[k], 1u)] = p;
     }
   }
   __syncthreads();
+#pragma unroll 1
   for (uint32_t g = tid; g <= G; g += nt) d.offsets[g] = s_off[g];
   if (d.pass_group) build_passes_block(d, s_off);
 }
@@ -397,12 +417,14 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
 #pragma unroll
   for (int j = 0; j < REG_E; j++) cbias[j] = (small && r.correction_bias && lane + 32 * j < E) ? __ldg(r.correction_bias + lane + 32 * j) : 0.0f;
   if (r.logit_bias)
+#pragma unroll 1
     for (uint32_t i = lane; i < E; i += 32) s_score[i] += __ldg(r.logit_bias + i);
   __syncwarp();
   if (r.scoring == MER_SCORE_SOFTMAX) {
     // softmax_inplace (transformer.rs:2747-2819)
     float mx = -CUDART_INF_F;
     int nan = 0;
+#pragma unroll 1
     for (uint32_t i = lane; i < E; i += 32) {
       float v = s_score[i];
       if (v != v)
@@ -416,9 +438,11 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
       nan |= __shfl_xor_sync(0xffffffffu, nan, o);
     }
     if (nan || !isfinite(mx)) {
+#pragma unroll 1
       for (uint32_t i = lane; i < E; i += 32) s_score[i] = 1.0f / (float)E;
       if (lane == 0) atomicOr(d.status, MER_DEVSTAT_NONFINITE_ROUTER);
     } else {
+#pragma unroll 1
       for (uint32_t i = lane; i < E; i += 32) s_score[i] = expf(s_score[i] - mx);
       __syncwarp();
       float sum = 0.0f;
@@ -431,14 +455,17 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
             sum += v.x, sum += v.y, sum += v.z, sum += v.w;
           }
         } else {
+#pragma unroll 1
           for (uint32_t i = 0; i < E; i++) sum += s_score[i];
         }
       }
       sum = __shfl_sync(0xffffffffu, sum, 0);
       if (sum > 0.0f)
+#pragma unroll 1
         for (uint32_t i = lane; i < E; i += 32) s_score[i] = s_score[i] / sum;
     }
   } else {
+#pragma unroll 1
     for (uint32_t i = lane; i < E; i += 32) s_score[i] = 1.0f / (1.0f + expf(-s_score[i]));
   }
   __syncwarp();
@@ -449,6 +476,7 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
       if (i < E) s_sel[i] = r.correction_bias ? s_score[i] + cbias[j] : s_score[i], s_ok[i] = 1;
     }
   } else {
+#pragma unroll 1
     for (uint32_t i = lane; i < E; i += 32) {
       s_sel[i] = r.correction_bias ? s_score[i] + r.correction_bias[i] : s_score[i];
       s_ok[i] = 1;
@@ -460,8 +488,10 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
   const bool grouped = ng > 1 && r.topk_group > 0 && r.topk_group < ng && (E % ng) == 0 && ng <= 64;
   if (grouped) {
     const uint32_t gs = E / ng;
+#pragma unroll 1
     for (uint32_t gi = lane; gi < ng; gi += 32) {
       float top1 = -CUDART_INF_F, top2 = -CUDART_INF_F;
+#pragma unroll 1
       for (uint32_t i = 0; i < gs; i++) {
         float s = s_sel[gi * gs + i];
         if (s > top1) {
@@ -476,9 +506,11 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
     __syncwarp();
     if (lane == 0) {
       uint64_t taken = 0;
+#pragma unroll 1
       for (uint32_t n = 0; n < r.topk_group; n++) {
         int bk = 0;
         uint32_t bi = MER_NONE;
+#pragma unroll 1
         for (uint32_t g = 0; g < ng; g++) {
           if (taken >> g & 1) continue;
           int k = total_key(s_gscore[g]);
@@ -489,8 +521,10 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
       }
     }
     __syncwarp();
+#pragma unroll 1
     for (uint32_t i = lane; i < E; i += 32) {
       bool ok = false;
+#pragma unroll 1
       for (uint32_t n = 0; n < r.topk_group; n++) ok |= (s_groups[n] == i / gs);
       s_ok[i] = ok;
     }
@@ -509,6 +543,7 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
       const float sv = i < E ? s_sel[i] : 0.0f;
       keys[j] = (i < E && s_ok[i] && isfinite(sv)) ? total_key(sv) : INT_MIN;
     }
+#pragma unroll 1
     for (uint32_t n = 0; n < k; n++) {
       int bk = INT_MIN;
       uint32_t bj = 0;
@@ -527,9 +562,11 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
       n_sel++;
     }
   } else {
+#pragma unroll 1
     for (uint32_t n = 0; n < k; n++) {
       int bk = 0;
       uint32_t bi = MER_NONE;
+#pragma unroll 1
       for (uint32_t i = lane; i < E; i += 32) {
         float s = s_sel[i];
         if (!s_ok[i] || !isfinite(s)) continue;
@@ -552,6 +589,7 @@ __device__ void route_token(const RouterDev &r, const MoeDispatch &d, uint32_t t
   float w = (lane < n_sel && my_id != MER_NONE) ? s_score[my_id] : 0.0f;
   if (r.normalise) {
     float sum = 0.0f;
+#pragma unroll 1
     for (uint32_t i = 0; i < n_sel; i++) sum += __shfl_sync(0xffffffffu, w, i);  // slot order
     if (isfinite(sum) && sum > 0.0f) w = w / sum;
   }
