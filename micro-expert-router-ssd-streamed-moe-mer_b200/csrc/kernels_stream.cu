@@ -274,6 +274,7 @@ __device__ __forceinline__ void ffn_stream_body(const StreamParams &p) {
         float mx = 0.0f;
         if (has_row) {
           const float4 *r4 = reinterpret_cast<const float4 *>(row);
+#pragma unroll 1
           for (uint32_t i = my_sub * 32 + lane; i < K / 4; i += wpt * 32) {
             const float4 v = __ldg(r4 + i);
             mx = nan_max(nan_max(nan_max(nan_max(mx, fabsf(v.x)), fabsf(v.y)), fabsf(v.z)), fabsf(v.w));
@@ -302,6 +303,7 @@ __device__ __forceinline__ void ffn_stream_body(const StreamParams &p) {
         uint8_t *hi_dst = s_frag + (size_t)(2 * my_tok) * p.frag_stride, *lo_dst = hi_dst + p.frag_stride;
         float *seed_dst = s_init + (size_t)my_tok * seed_stride;
         // float4 groups of this K split: 8 per block; a warp converts 4 blocks per step
+#pragma unroll 1
         for (uint32_t q = my_sub * 32 + lane; q < kbn * 8; q += wpt * 32) {
           float4 v = __ldg(reinterpret_cast<const float4 *>(row + (size_t)kb0 * 32) + q);
           v.x *= sc, v.y *= sc, v.z *= sc, v.w *= sc;  // exact (power of two) unless it overflows
@@ -503,11 +505,13 @@ __device__ void ffn_stream_tail(const StreamParams &p) {
     const float *parts = p.out;
     const uint32_t F = d.F, fchunks = (F + 127) / 128;
     const uint32_t gw = blockIdx.x * (THREADS / 32) + warp, nw = gridDim.x * (THREADS / 32);
+#pragma unroll 1
     for (uint32_t u = gw; u < P * fchunks; u += nw) {  // a warp: 128 consecutive values of one pair's row
       const uint32_t pair = u / fchunks, f0 = (u % fchunks) * 128 + lane * 4;
       float mx = 0.0f;
       if (f0 < F) {
         float4 g = make_float4(0, 0, 0, 0), up = make_float4(0, 0, 0, 0);
+#pragma unroll 1
         for (uint32_t k = 0; k < p.n_ksplit; k++) {
           const float *base = parts + ((size_t)k * P + pair) * 2 * F;
           const float4 a = __ldcg(reinterpret_cast<const float4 *>(base + f0)), b = __ldcg(reinterpret_cast<const float4 *>(base + F + f0));
@@ -533,6 +537,7 @@ __device__ void ffn_stream_tail(const StreamParams &p) {
     const uint32_t D4 = d.D / 4;
     const float4 *yp = reinterpret_cast<const float4 *>(p.n_ksplit > 1 ? p.out : d.y);
     const size_t part4 = (size_t)P * D4;
+#pragma unroll 1
     for (uint32_t e = blockIdx.x * THREADS + threadIdx.x; e < d.n_tokens * D4; e += gridDim.x * THREADS) {
       const uint32_t token = e / D4, i4 = e % D4;
       float4 acc = make_float4(0, 0, 0, 0);
@@ -540,12 +545,14 @@ __device__ void ffn_stream_tail(const StreamParams &p) {
         const float4 r = __ldg(reinterpret_cast<const float4 *>(d.residual) + (size_t)token * D4 + i4);
         acc.x = __fadd_rn(r.x, acc.x), acc.y = __fadd_rn(r.y, acc.y), acc.z = __fadd_rn(r.z, acc.z), acc.w = __fadd_rn(r.w, acc.w);
       };
+#pragma unroll 1
       for (uint32_t sl = 0; sl < d.slots; sl++) {
         if (d.residual && sl == d.routed_slots) add_residual();
         const size_t pr = (size_t)token * d.slots + sl;
         const float w = d.pair_weight[pr];
         if (d.pair_expert[pr] == MER_NONE || w == 0.0f) continue;
         float4 yv = __ldcg(yp + pr * D4 + i4);
+#pragma unroll 1
         for (uint32_t k = 1; k < p.n_ksplit; k++) {
           const float4 t = __ldcg(yp + (size_t)k * part4 + pr * D4 + i4);
           yv.x += t.x, yv.y += t.y, yv.z += t.z, yv.w += t.w;
@@ -563,10 +570,12 @@ __device__ void ffn_stream_tail(const StreamParams &p) {
     const uint32_t D4 = d.D / 4, n_here = d.offsets[d.n_groups];
     const float4 *yp = reinterpret_cast<const float4 *>(p.out);
     const size_t part4 = (size_t)P * D4;
+#pragma unroll 1
     for (uint32_t e = blockIdx.x * THREADS + threadIdx.x; e < n_here * D4; e += gridDim.x * THREADS) {
       const size_t pr = d.perm[e / D4];
       const uint32_t i4 = e % D4;
       float4 yv = __ldcg(yp + pr * D4 + i4);
+#pragma unroll 1
       for (uint32_t k = 1; k < p.n_ksplit; k++) {
         const float4 t = __ldcg(yp + (size_t)k * part4 + pr * D4 + i4);
         yv.x += t.x, yv.y += t.y, yv.z += t.z, yv.w += t.w;
